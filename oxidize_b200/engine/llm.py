@@ -1,0 +1,199 @@
+"""``LLM``: the public engine object — load (or synthesise) a model, then ``generate`` or
+drive ``add_request`` / ``step`` yourself.
+
+It plays the role of the reference's ``ContinuousBatchEngine::{submit, step, cancel}``
+(``oxidize-core/src/model/inference/batch_engine.rs:128,180,157``) and of
+``GenerationStream`` (``model/generation.rs:1057``) for one-shot use, on top of a real paged
+KV pool.  Under tensor parallelism every rank constructs the same ``LLM`` and calls the same
+methods in lock step (SPMD): scheduling is deterministic and the sampled tokens are identical
+on all ranks, so no control-plane broadcast sits on the step path.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, Iterable, List, Optional, Sequence as Seq, Union
+
+import torch
+
+from ..formats.gguf import GGUFFile, load_gguf
+from ..models.config import ModelConfig, config_from_gguf
+from ..models.transformer import Transformer
+from ..models.weights import ModelWeights, load_weights
+from .kv_pool import BlockPool, KVCache, KVCacheSpec
+from .runner import ModelRunner, StepResult
+from .sampler import SamplingParams
+from .scheduler import Scheduler, SchedulerConfig, SchedulerOutput, Sequence
+
+
+@dataclass
+class EngineConfig:
+    """Typed engine configuration (CLI flags and YAML map onto these fields)."""
+
+    kv_cache_dtype: str = "auto"  # auto | f32 | f16 | bf16 | q8 | q4
+    kv_page_size: int = 16
+    num_kv_blocks: int = 0  # 0 = size from gpu_memory_utilization / max_model_len
+    gpu_memory_utilization: float = 0.90
+    max_model_len: int = 4096
+    max_num_seqs: int = 64
+    max_num_batched_tokens: int = 2048
+    prefill_chunk_size: int = 512
+    policy: str = "fcfs"
+    enable_prefix_cache: bool = True
+    cuda_graphs: bool = True
+    tp_size: int = 1
+    ep_size: int = 1
+    pp_size: int = 1
+    fused_comm: bool = True
+    eos_token_id: Optional[int] = None
+
+
+@dataclass
+class RequestOutput:
+    request_id: str
+    prompt_token_ids: List[int]
+    token_ids: List[int]
+    finished: bool
+    finish_reason: Optional[str] = None
+    ttft: Optional[float] = None
+    latency: Optional[float] = None
+    num_cached_tokens: int = 0
+    text: Optional[str] = None
+
+
+class LLM:
+    def __init__(self, weights: ModelWeights, config: Optional[EngineConfig] = None, comm=None, tokenizer=None):
+        self.config = config or EngineConfig()
+        c = self.config
+        self.weights = weights
+        self.cfg: ModelConfig = weights.cfg
+        self.model = Transformer(weights, comm)
+        self.device = self.model.device
+        self.tokenizer = tokenizer
+        kv_dtype = c.kv_cache_dtype
+        if kv_dtype == "auto":
+            kv_dtype = "bf16" if self.device.type == "cuda" else "f32"
+        spec = KVCacheSpec(len(weights.layers), self.model.n_kv_local, self.cfg.head_dim, c.kv_page_size, kv_dtype)
+        nblocks = c.num_kv_blocks or self._auto_blocks(spec)
+        self.kv = KVCache(spec, nblocks, self.device)
+        self.pool = BlockPool(nblocks, c.kv_page_size, c.enable_prefix_cache)
+        self.scheduler = Scheduler(SchedulerConfig(c.max_num_batched_tokens, c.prefill_chunk_size, c.max_num_seqs,
+                                                   c.policy, c.enable_prefix_cache, c.max_model_len), self.pool)
+        self.runner = ModelRunner(self.model, self.kv, max(c.max_num_batched_tokens, c.max_num_seqs), c.max_num_seqs,
+                                  c.max_model_len, c.cuda_graphs)
+        self.eos_token_id = c.eos_token_id
+        if self.eos_token_id is None and tokenizer is not None:
+            self.eos_token_id = tokenizer.special_tokens.eos
+        self._seqs: Dict[str, Sequence] = {}
+        self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "h2d_bytes": 0, "d2h_bytes": 0}
+
+    # ------------------------------------------------------------------ construction helpers
+    @classmethod
+    def from_gguf(cls, path: Union[str, GGUFFile], config: Optional[EngineConfig] = None, device=None, comm=None,
+                  tp_rank: int = 0, ep_rank: int = 0, rope_pairing: Optional[str] = None) -> "LLM":
+        from ..formats.tokenizer import TokenizerError, load_tokenizer_from_metadata
+
+        config = config or EngineConfig()
+        g = path if isinstance(path, GGUFFile) else load_gguf(path)
+        cfg = config_from_gguf(g)
+        if rope_pairing:
+            cfg.rope_pairing = rope_pairing
+        device = torch.device(device if device is not None else ("cuda" if torch.cuda.is_available() else "cpu"))
+        act = torch.bfloat16 if device.type == "cuda" else torch.float32
+        w = load_weights(g, cfg, device, act, tp_rank, config.tp_size, ep_rank, config.ep_size)
+        try:
+            tok = load_tokenizer_from_metadata(g.metadata)
+        except TokenizerError:
+            tok = None
+        return cls(w, config, comm, tok)
+
+    def _auto_blocks(self, spec: KVCacheSpec) -> int:
+        c = self.config
+        want = c.max_num_seqs * ((c.max_model_len + spec.page_size - 1) // spec.page_size + 1)
+        if self.device.type != "cuda":
+            return max(16, min(want, 4096))
+        free, total = torch.cuda.mem_get_info(self.device)
+        budget = int(free - (1.0 - c.gpu_memory_utilization) * total)
+        fit = max(16, budget // max(spec.bytes_per_block(), 1))
+        return int(min(want, fit))
+
+    # ------------------------------------------------------------------ request API
+    def add_request(self, prompt: Union[str, Seq[int]], params: Optional[SamplingParams] = None,
+                    request_id: Optional[str] = None) -> str:
+        params = params or SamplingParams()
+        params.validate()
+        if isinstance(prompt, str):
+            if self.tokenizer is None:
+                raise ValueError("text prompt given but the model has no tokenizer; pass token ids")
+            ids = self.tokenizer.encode_with_special_tokens(prompt)
+        else:
+            ids = [int(t) for t in prompt]
+        bad = [t for t in ids if not 0 <= t < self.cfg.vocab_size]
+        if bad:
+            raise ValueError(f"token id {bad[0]} outside vocabulary of {self.cfg.vocab_size}")
+        seq = Sequence(ids, params, request_id, arrival=time.perf_counter())
+        self.scheduler.add(seq)
+        self._seqs[seq.request_id] = seq
+        return seq.request_id
+
+    def abort(self, request_id: str) -> bool:
+        return self.scheduler.abort(request_id)
+
+    @property
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_work
+
+    def step(self) -> List[RequestOutput]:
+        """One engine iteration: schedule → forward → sample → postprocess."""
+        out = self.scheduler.schedule()
+        if out.is_empty:
+            if self.scheduler.has_work and not out.preempted:
+                raise RuntimeError("scheduler made no progress: KV pool too small for the waiting request")
+            return []
+        res = self.runner.execute(out)
+        now = time.perf_counter()
+        self.scheduler.postprocess(out, res.tokens, self.eos_token_id, now)
+        st = self.stats
+        st["steps"] += 1
+        st["prefill_tokens"] += out.num_prefill_tokens
+        st["decode_tokens"] += out.num_decode_tokens
+        st["h2d_bytes"] += res.h2d_bytes
+        st["d2h_bytes"] += res.d2h_bytes
+        self.last_step = (out, res)
+        outs = []
+        for ss in out.scheduled:
+            if ss.sample or ss.seq.is_finished:
+                outs.append(self._output(ss.seq))
+        return outs
+
+    def _output(self, seq: Sequence) -> RequestOutput:
+        gen = getattr(seq, "_preempted_outputs", []) + seq.output
+        ro = RequestOutput(seq.request_id, seq.prompt[: len(seq.prompt) - len(getattr(seq, "_preempted_outputs", []))],
+                           list(gen), seq.is_finished, seq.finish_reason,
+                           None if seq.first_token_time is None else seq.first_token_time - seq.arrival,
+                           None if seq.finish_time is None else seq.finish_time - seq.arrival, seq.num_cached_tokens)
+        if seq.is_finished:
+            self._seqs.pop(seq.request_id, None)
+        return ro
+
+    def generate(self, prompts: Iterable[Union[str, Seq[int]]], params: Union[SamplingParams, Seq[SamplingParams], None] = None,
+                 on_token: Optional[Callable[[RequestOutput], None]] = None) -> List[RequestOutput]:
+        """Run a set of prompts to completion with continuous batching; results in input order."""
+        prompts = list(prompts)
+        if params is None or isinstance(params, SamplingParams):
+            plist = [params or SamplingParams()] * len(prompts)
+        else:
+            plist = list(params)
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, plist)]
+        final: Dict[str, RequestOutput] = {}
+        while self.has_unfinished:
+            for ro in self.step():
+                if on_token is not None:
+                    on_token(ro)
+                if ro.finished:
+                    final[ro.request_id] = ro
+        outs = [final[i] for i in ids]
+        if self.tokenizer is not None:
+            for ro in outs:
+                ro.text = self.tokenizer.decode_without_special_tokens(ro.token_ids)
+        return outs

@@ -1,0 +1,252 @@
+"""Model runner: turns a scheduler output into one flat device batch, runs the forward pass
+(CUDA-graph replay for decode-only steps), samples, and hands tokens back to the host.
+
+Per step the host writes ONE pinned int32 staging buffer laid out as
+``[token_ids | positions | slot_mapping | query_start | seq_lens | logits_indices |
+block_tables]`` plus a small float section with per-sequence sampling knobs and this step's
+uniform draws; one async copy moves it to a device buffer of identical layout whose
+sub-views have fixed addresses, so captured graphs stay valid (the role of the reference's
+3-word ``{pos, context, token}`` device state, ``backends/cuda/cuda_decode_graph.rs:45-52``,
+generalised to a whole batch).  The only device→host traffic is the sampled token ids.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..models.transformer import BatchMeta, Transformer
+from .kv_pool import KVCache
+from .sampler import SamplingParams, sample as host_sample
+from .scheduler import ScheduledSeq, SchedulerOutput
+
+DECODE_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+
+def _bucket(n: int, buckets=DECODE_BUCKETS) -> int:
+    for b in buckets:
+        if n <= b:
+            return b
+    return n
+
+
+class StagingBuffers:
+    """Host (pinned on CUDA) + device mirror of the per-step integer/float inputs."""
+
+    def __init__(self, max_tokens: int, max_seqs: int, max_blocks_per_seq: int, device: torch.device):
+        self.max_tokens, self.max_seqs, self.max_blocks = max_tokens, max_seqs, max_blocks_per_seq
+        T, B, M = max_tokens, max_seqs, max_blocks_per_seq
+        sizes = [("token_ids", T), ("positions", T), ("slot_mapping", T), ("query_start", B + 1), ("seq_lens", B),
+                 ("logits_indices", T), ("top_k", B), ("block_tables", B * M)]
+        fsizes = [("temperature", B), ("top_p", B), ("min_p", B), ("random", B)]
+        self.offsets: Dict[str, Tuple[int, int]] = {}
+        off = 0
+        for name, n in sizes + fsizes:
+            n4 = (n + 3) // 4 * 4  # keep every section 16-byte aligned
+            self.offsets[name] = (off, n)
+            off += n4
+        self.total = off
+        pin = device.type == "cuda"
+        self.host = torch.zeros(self.total, dtype=torch.int32, pin_memory=pin)
+        self.host_np = self.host.numpy()
+        self.host_f = self.host_np.view(np.float32)
+        self.dev = torch.zeros(self.total, dtype=torch.int32, device=device) if pin else self.host
+        self.device = device
+        self._float_names = {n for n, _ in fsizes}
+
+    def h(self, name: str) -> np.ndarray:
+        o, n = self.offsets[name]
+        return (self.host_f if name in self._float_names else self.host_np)[o : o + n]
+
+    def d(self, name: str, n: Optional[int] = None) -> torch.Tensor:
+        o, full = self.offsets[name]
+        v = self.dev[o : o + (full if n is None else n)]
+        return v.view(torch.float32) if name in self._float_names else v
+
+    def upload(self) -> int:
+        """Async H2D of the whole staging area; returns bytes moved."""
+        if self.dev is not self.host:
+            self.dev.copy_(self.host, non_blocking=True)
+        return self.total * 4
+
+
+@dataclass
+class StepResult:
+    tokens: Dict[int, List[int]]  # seq_id -> sampled tokens
+    logits: Optional[torch.Tensor] = None
+    h2d_bytes: int = 0
+    d2h_bytes: int = 0
+    launches: int = 0
+
+
+class ModelRunner:
+    def __init__(self, model: Transformer, kv: KVCache, max_tokens: int, max_seqs: int, max_model_len: int,
+                 use_cuda_graphs: bool = True):
+        self.model = model
+        self.kv = kv
+        self.device = model.device
+        self.page = kv.page_size
+        self.max_blocks = (max_model_len + self.page - 1) // self.page
+        self.buf = StagingBuffers(max_tokens, max_seqs, self.max_blocks, self.device)
+        self.use_graphs = use_cuda_graphs and self.device.type == "cuda"
+        self.graphs: Dict[int, "torch.cuda.CUDAGraph"] = {}
+        self.graph_out: Dict[int, torch.Tensor] = {}
+        self.out_host = torch.zeros(max(max_tokens, max_seqs), dtype=torch.int32,
+                                    pin_memory=self.device.type == "cuda")
+        self.keep_logits = False
+
+    # ------------------------------------------------------------------ batch building
+    def build(self, scheduled: Sequence[ScheduledSeq], pad_to: Optional[int] = None):
+        """Fill the staging buffer; returns (T, B, n_logits, max_q, max_len, sample_rows)."""
+        b = self.buf
+        tok, pos, slot = b.h("token_ids"), b.h("positions"), b.h("slot_mapping")
+        qs, sl, li, bt = b.h("query_start"), b.h("seq_lens"), b.h("logits_indices"), b.h("block_tables")
+        M, ps = self.max_blocks, self.page
+        t = 0
+        nl = 0
+        max_q = 0
+        max_len = 0
+        rows: List[Tuple[ScheduledSeq, int, int]] = []  # (ss, first logits row, n rows)
+        qs[0] = 0
+        for i, ss in enumerate(scheduled):
+            seq = ss.seq
+            n = ss.num_tokens
+            if t + n > b.max_tokens or i >= b.max_seqs:
+                raise RuntimeError("scheduled batch exceeds runner capacity")
+            start = ss.start
+            if ss.is_prefill:
+                tok[t : t + n] = seq.prompt[start : start + n]
+            else:
+                tok[t] = seq.token_at(start)
+                if n > 1:
+                    tok[t + 1 : t + n] = seq.draft_tokens
+            p = np.arange(start, start + n, dtype=np.int32)
+            pos[t : t + n] = p
+            blocks = np.asarray(seq.blocks, dtype=np.int32)
+            slot[t : t + n] = blocks[p // ps] * ps + p % ps
+            nb = len(blocks)
+            bt[i * M : i * M + nb] = blocks
+            sl[i] = start + n
+            qs[i + 1] = t + n
+            if ss.sample:
+                k = n if (not ss.is_prefill and n > 1) else 1
+                li[nl : nl + k] = np.arange(t + n - k, t + n, dtype=np.int32)
+                rows.append((ss, nl, k))
+                nl += k
+            max_q = max(max_q, n)
+            max_len = max(max_len, start + n)
+            t += n
+        B = len(scheduled)
+        if pad_to is not None and pad_to > B:
+            # dummy sequences: zero context, no KV write; their logits rows are ignored
+            for i in range(B, pad_to):
+                tok[t] = 0
+                pos[t] = 0
+                slot[t] = -1
+                sl[i] = 0
+                qs[i + 1] = t + 1
+                li[nl] = t
+                nl += 1
+                t += 1
+            B = pad_to
+        return t, B, nl, max_q, max_len, rows
+
+    def _fill_sampling(self, rows, n_logits: int) -> bool:
+        """Per-logits-row sampling knobs; returns True when every row is greedy."""
+        b = self.buf
+        temp, tp, mp, rnd, tk = b.h("temperature"), b.h("top_p"), b.h("min_p"), b.h("random"), b.h("top_k")
+        all_greedy = True
+        temp[:n_logits] = 0.0
+        for ss, r0, k in rows:
+            p: SamplingParams = ss.seq.params
+            if p.is_greedy:
+                continue
+            all_greedy = False
+            for j in range(r0, r0 + k):
+                temp[j] = p.temperature
+                tp[j] = p.top_p if p.top_p is not None else 1.0
+                mp[j] = p.min_p if p.min_p is not None else 0.0
+                tk[j] = p.top_k if p.top_k is not None else 0
+                rnd[j] = ss.seq.rng.next()
+        return all_greedy
+
+    def _meta(self, T: int, B: int, nl: int, max_q: int, max_len: int) -> BatchMeta:
+        b = self.buf
+        return BatchMeta(
+            token_ids=b.d("token_ids", T), positions=b.d("positions", T), slot_mapping=b.d("slot_mapping", T),
+            query_start=b.d("query_start", B + 1), seq_lens=b.d("seq_lens", B),
+            block_tables=b.d("block_tables").view(b.max_seqs, self.max_blocks)[:B],
+            logits_indices=b.d("logits_indices", nl), max_query_len=max_q, max_seq_len=max_len, num_seqs=B)
+
+    # ------------------------------------------------------------------ execution
+    def _forward_sample(self, meta: BatchMeta, all_greedy: bool, tie: str):
+        logits = self.model.forward(meta, self.kv)
+        if all_greedy:
+            return ops.argmax(logits, tie), logits
+        from . import device_sampler
+
+        nl = logits.shape[0]
+        b = self.buf
+        return device_sampler.sample(logits, b.d("temperature", nl), b.d("top_k", nl), b.d("top_p", nl),
+                                     b.d("min_p", nl), b.d("random", nl), tie), logits
+
+    def execute(self, out: SchedulerOutput, needs_host_logits: bool = False) -> StepResult:
+        scheduled = out.scheduled
+        if not scheduled:
+            return StepResult({})
+        for src, dst in out.cow_copies:
+            self.kv.copy_block(src, dst)
+        decode_only = all((not s.is_prefill) and s.num_tokens == 1 for s in scheduled)
+        graphable = self.use_graphs and decode_only and not needs_host_logits and not self.keep_logits
+        pad_to = _bucket(len(scheduled)) if graphable else None
+        if pad_to is not None and pad_to > self.buf.max_seqs:
+            pad_to, graphable = None, False
+        T, B, nl, max_q, max_len, rows = self.build(scheduled, pad_to)
+        all_greedy = self._fill_sampling(rows, nl)
+        tie = scheduled[0].seq.params.tie
+        h2d = self.buf.upload()
+        logits = None
+        if graphable and all_greedy:
+            toks = self._replay(B, tie)
+        else:
+            meta = self._meta(T, B, nl, max_q, max_len)
+            toks, logits = self._forward_sample(meta, all_greedy and not needs_host_logits, tie)
+        n_out = toks.shape[0]
+        if self.device.type == "cuda":
+            self.out_host[:n_out].copy_(toks, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            host = self.out_host[:n_out].numpy()
+        else:
+            host = toks.numpy()
+        result: Dict[int, List[int]] = {}
+        for ss, r0, k in rows:
+            result[ss.seq.seq_id] = [int(x) for x in host[r0 : r0 + k]]
+        return StepResult(result, logits if (needs_host_logits or self.keep_logits) else None, h2d, n_out * 4)
+
+    def _replay(self, B: int, tie: str) -> torch.Tensor:
+        g = self.graphs.get(B)
+        if g is None:
+            g = self._capture(B, tie)
+        g.replay()
+        return self.graph_out[B]
+
+    def _capture(self, B: int, tie: str):
+        """Capture one decode step for bucket ``B`` (every sequence feeds exactly one row)."""
+        meta = self._meta(B, B, B, 1, self.max_blocks * self.page)
+        # warm up on a side stream so lazy initialisation does not land inside the capture
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                ops.argmax(self.model.forward(meta, self.kv), tie)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = ops.argmax(self.model.forward(meta, self.kv), tie)
+        self.graphs[B] = g
+        self.graph_out[B] = out
+        return g

@@ -1,0 +1,224 @@
+"""Model hyper-parameters read from GGUF metadata.
+
+Mirrors ``InferenceConfig::from_gguf`` (``oxidize-core/src/model/inference.rs:363-697``): every
+value comes from ``{arch}.*`` metadata with tensor-shape fallbacks, ``attention.key_length``
+wins over ``hidden/heads`` (``:490-495``), the vocabulary axis of ``token_embd`` is the larger
+one (``:425-428``), and the architecture string selects routing / norm conventions
+(``:62-96``).  Named presets for the benchmark shapes live in :func:`preset`.
+"""
+from __future__ import annotations
+
+import dataclasses
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+from ..formats.gguf import GGUFFile
+
+# architecture strings accepted (reference arch-string map inference.rs:62-96)
+DENSE_ARCHS = {"llama", "mistral", "qwen2", "qwen3", "gemma", "phi3", "deepseek"}
+MOE_ARCHS = {"mixtral", "qwen2moe", "qwen3moe", "deepseek2", "deepseek-moe", "deepseek_moe", "llama4"}
+QWEN_ARCHS = {"qwen", "qwen2", "qwen2moe", "qwen35", "qwen3", "qwen3moe", "qwen3_5_moe"}
+
+
+@dataclass
+class RopeScaling:
+    type: str = "none"  # none | linear | yarn
+    factor: float = 1.0
+    original_context_length: int = 0
+    beta_fast: float = 32.0
+    beta_slow: float = 1.0
+
+
+@dataclass
+class ModelConfig:
+    arch: str = "llama"
+    name: str = ""
+    vocab_size: int = 32000
+    hidden_size: int = 4096
+    n_layers: int = 32
+    n_heads: int = 32
+    n_kv_heads: int = 8
+    head_dim: int = 128
+    ffn_size: int = 14336
+    rms_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    rope_dim: int = 0  # 0 -> head_dim (full rotary)
+    rope_pairing: str = "split_half"  # split_half (NeoX; what all reference engines do) | adjacent
+    rope_scaling: RopeScaling = field(default_factory=RopeScaling)
+    context_length: int = 8192
+    sliding_window: int = 0
+    qk_norm: bool = False
+    attn_bias: bool = False
+    tie_embeddings: bool = False
+    # MoE
+    n_experts: int = 0
+    n_experts_used: int = 0
+    expert_ffn_size: int = 0
+    expert_gating: str = "softmax"  # softmax | sigmoid
+    expert_weights_scale: float = 1.0
+    expert_weights_norm: bool = True
+    expert_group_count: int = 0
+    expert_group_used_count: int = 0
+    leading_dense_blocks: int = 0
+    n_shared_experts: int = 0
+    shared_expert_ffn_size: int = 0
+    shared_expert_gate: bool = False
+    router_bias: bool = False
+    # multi-token prediction (in-GGUF nextn layers appended after the decoder stack)
+    nextn_layers: int = 0
+
+    @property
+    def is_moe(self) -> bool:
+        return self.n_experts > 0
+
+    @property
+    def rotary_dim(self) -> int:
+        return self.rope_dim or self.head_dim
+
+    @property
+    def q_size(self) -> int:
+        return self.n_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.n_kv_heads * self.head_dim
+
+    def layer_is_moe(self, layer: int) -> bool:
+        return self.is_moe and layer >= self.leading_dense_blocks
+
+    def param_count(self) -> int:
+        h = self.hidden_size
+        attn = h * self.q_size * 2 + h * self.kv_size * 2
+        dense = 3 * h * self.ffn_size
+        n = 0
+        for i in range(self.n_layers):
+            n += attn + 2 * h
+            if self.layer_is_moe(i):
+                n += self.n_experts * 3 * h * self.expert_ffn_size + h * self.n_experts
+                n += self.n_shared_experts * 3 * h * (self.shared_expert_ffn_size or self.expert_ffn_size)
+            else:
+                n += dense
+        n += self.vocab_size * h * (1 if self.tie_embeddings else 2) + h
+        return n
+
+    def to_dict(self) -> Dict[str, Any]:
+        return dataclasses.asdict(self)
+
+
+def _scalar(v, default):
+    if v is None:
+        return default
+    if isinstance(v, (list, tuple)):
+        return v[0] if v else default
+    return v
+
+
+def config_from_gguf(g: GGUFFile) -> ModelConfig:
+    arch = g.architecture
+    a = g.arch_get
+    c = ModelConfig(arch=arch, name=str(g.get("general.name", "")))
+    emb = g.tensors.get("token_embd.weight")
+    c.hidden_size = int(_scalar(a("embedding_length"), emb.dims[0] if emb else c.hidden_size))
+    if emb is not None:
+        rows = emb.n_elements // emb.dims[0]
+        # vocab axis is "the larger one"
+        c.vocab_size = max(rows, emb.dims[0]) if rows != emb.dims[0] and emb.dims[0] == c.hidden_size else rows
+    c.vocab_size = int(_scalar(a("vocab_size"), c.vocab_size))
+    toks = g.get("tokenizer.ggml.tokens")
+    if a("vocab_size") is None and emb is None and toks:
+        c.vocab_size = len(toks)
+    c.n_layers = int(_scalar(a("block_count"), c.n_layers))
+    c.nextn_layers = int(_scalar(a("nextn_predict_layers"), 0))
+    c.n_heads = int(_scalar(a("attention.head_count"), c.n_heads))
+    kvh = a("attention.head_count_kv")
+    if isinstance(kvh, (list, tuple)):
+        nz = [int(x) for x in kvh if int(x) > 0]
+        kvh = nz[0] if nz else c.n_heads
+    c.n_kv_heads = int(kvh if kvh is not None else c.n_heads)
+    key_len = a("attention.key_length")
+    c.head_dim = int(key_len) if key_len else c.hidden_size // c.n_heads
+    ffn = a("feed_forward_length")
+    if isinstance(ffn, (list, tuple)):
+        nz = [int(x) for x in ffn if int(x) > 0]
+        ffn = nz[0] if nz else None
+    if ffn is None:
+        t = g.tensors.get("blk.0.ffn_gate.weight") or g.tensors.get("blk.0.ffn_up.weight")
+        ffn = t.shape[0] if t is not None else 0
+    c.ffn_size = int(ffn)
+    c.rms_eps = float(_scalar(a("attention.layer_norm_rms_epsilon"), 1e-5))
+    c.rope_theta = float(_scalar(a("rope.freq_base"), 10000.0))
+    c.rope_dim = int(_scalar(a("rope.dimension_count"), 0))
+    if c.rope_dim >= c.head_dim:
+        c.rope_dim = 0
+    stype = a("rope.scaling.type")
+    if stype:
+        c.rope_scaling = RopeScaling(
+            type=str(stype),
+            factor=float(_scalar(a("rope.scaling.factor"), 1.0)),
+            original_context_length=int(_scalar(a("rope.scaling.original_context_length"), 0)),
+        )
+    c.context_length = int(_scalar(a("context_length"), 8192))
+    c.sliding_window = int(_scalar(a("attention.sliding_window"), 0))
+    c.qk_norm = g.has_tensor("blk.0.attn_q_norm.weight")
+    c.attn_bias = g.has_tensor("blk.0.attn_q.bias")
+    c.tie_embeddings = not g.has_tensor("output.weight")
+    # MoE
+    c.n_experts = int(_scalar(a("expert_count"), 0))
+    c.n_experts_used = int(_scalar(a("expert_used_count"), 0))
+    c.leading_dense_blocks = int(_scalar(a("leading_dense_block_count"), 0))
+    if c.n_experts:
+        eff = a("expert_feed_forward_length")
+        if eff is None:
+            for i in range(c.n_layers):
+                t = g.tensors.get(f"blk.{i}.ffn_gate_exps.weight")
+                if t is not None:
+                    eff = t.shape[-2]
+                    break
+        c.expert_ffn_size = int(eff or c.ffn_size)
+        gating = int(_scalar(a("expert_gating_func"), 1))
+        c.expert_gating = "sigmoid" if gating == 2 else "softmax"
+        c.expert_weights_scale = float(_scalar(a("expert_weights_scale"), 1.0)) or 1.0
+        c.expert_weights_norm = bool(_scalar(a("expert_weights_norm"), True))
+        c.expert_group_count = int(_scalar(a("expert_group_count"), 0))
+        c.expert_group_used_count = int(_scalar(a("expert_group_used_count"), 0))
+        for i in range(c.n_layers):
+            t = g.tensors.get(f"blk.{i}.ffn_gate_shexp.weight")
+            if t is not None:
+                c.shared_expert_ffn_size = int(t.shape[0])
+                c.n_shared_experts = max(1, int(_scalar(a("expert_shared_count"), 1)))
+                c.shared_expert_gate = g.has_tensor(f"blk.{i}.ffn_gate_inp_shexp.weight")
+                c.router_bias = g.has_tensor(f"blk.{i}.exp_probs_b.bias")
+                break
+    return c
+
+
+_PRESETS: Dict[str, Dict[str, Any]] = {
+    # CPU tiny Llama: 512 d, 8 L, 8/2 heads (hd 64), FFN 1408, vocab 32000
+    "tiny-llama": dict(arch="llama", vocab_size=32000, hidden_size=512, n_layers=8, n_heads=8, n_kv_heads=2,
+                       head_dim=64, ffn_size=1408, rms_eps=1e-5, rope_theta=10000.0, context_length=2048),
+    "llama3-8b": dict(arch="llama", vocab_size=128256, hidden_size=4096, n_layers=32, n_heads=32, n_kv_heads=8,
+                      head_dim=128, ffn_size=14336, rope_theta=500000.0, context_length=8192),
+    "llama3-70b": dict(arch="llama", vocab_size=128256, hidden_size=8192, n_layers=80, n_heads=64, n_kv_heads=8,
+                       head_dim=128, ffn_size=28672, rope_theta=500000.0, context_length=8192),
+    "mixtral-8x7b": dict(arch="mixtral", vocab_size=32000, hidden_size=4096, n_layers=32, n_heads=32, n_kv_heads=8,
+                         head_dim=128, ffn_size=14336, rope_theta=1000000.0, context_length=32768,
+                         n_experts=8, n_experts_used=2, expert_ffn_size=14336),
+    "qwen3-30b-a3b": dict(arch="qwen3moe", vocab_size=151936, hidden_size=2048, n_layers=48, n_heads=32, n_kv_heads=4,
+                          head_dim=128, ffn_size=6144, rope_theta=1000000.0, context_length=32768, qk_norm=True,
+                          n_experts=128, n_experts_used=8, expert_ffn_size=768),
+    "qwen-draft-0.5b": dict(arch="qwen2", vocab_size=151936, hidden_size=896, n_layers=24, n_heads=14, n_kv_heads=2,
+                            head_dim=64, ffn_size=4864, rope_theta=1000000.0, context_length=32768,
+                            tie_embeddings=True),
+}
+
+
+def preset(name: str, **overrides) -> ModelConfig:
+    if name not in _PRESETS:
+        raise KeyError(f"unknown preset {name!r}; have {sorted(_PRESETS)}")
+    kw = dict(_PRESETS[name])
+    kw.update(overrides)
+    return ModelConfig(name=name, **kw)
+
+
+def preset_names() -> List[str]:
+    return sorted(_PRESETS)

@@ -1,0 +1,173 @@
+"""Decoder-only transformer forward over a flat token batch and a paged KV cache.
+
+One code path serves decode (1 query row per sequence), chunked prefill and speculative
+verification (several rows per sequence) for Llama / Mistral / Qwen3 (per-head QK-norm)
+and the MoE families Mixtral / Qwen3-MoE / DeepSeek-MoE (shared expert, sigmoid+bias
+routing).  Layer semantics follow the reference's per-token layer loop
+(``oxidize-core/src/model/inference/layers.rs``: attention :893+, MoE + shared expert
+:1420-1475) and MoE math ``moe_ffn_forward_weights`` (``model/inference.rs:1662-1935``); the
+batching, paging and sharding are this framework's own.
+
+Tensor parallelism is Megatron-style: qkv / gate_up are column-parallel, attn_output /
+ffn_down are row-parallel and end in an all-reduce supplied by ``comm`` (fused into the
+GEMM kernel on the GPU path), the lm_head is vocabulary-parallel.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Tuple
+
+import torch
+
+from .. import ops
+from ..ops import ref as opref
+from .config import ModelConfig
+from .weights import LayerWeights, ModelWeights
+
+
+@dataclass
+class RopeState:
+    inv_freq: torch.Tensor
+    pairing: str
+    mscale: float
+    n_heads: int  # local (this rank's) head counts
+    n_kv_heads: int
+    head_dim: int
+
+
+@dataclass
+class BatchMeta:
+    """Flat description of one engine step (all int32 tensors on the model's device)."""
+
+    token_ids: torch.Tensor  # [T]
+    positions: torch.Tensor  # [T]
+    slot_mapping: torch.Tensor  # [T]  block*page + offset, -1 = do not write
+    query_start: torch.Tensor  # [B+1]
+    seq_lens: torch.Tensor  # [B] context length including this step's rows
+    block_tables: torch.Tensor  # [B, max_blocks]
+    logits_indices: torch.Tensor  # [L] rows that need logits
+    max_query_len: int = 1
+    max_seq_len: int = 0
+    num_seqs: int = 0
+    # host copies for CPU-side loops (reference path); optional on the GPU path
+    extra: dict = field(default_factory=dict)
+
+
+class SingleRankComm:
+    """Communication facade for tp=ep=1 (every collective is the identity)."""
+
+    rank = 0
+    size = 1
+
+    def all_reduce(self, x):
+        return x
+
+    def all_gather_cat(self, x, dim=-1):
+        return x
+
+
+class Transformer:
+    def __init__(self, weights: ModelWeights, comm=None, act_dtype: Optional[torch.dtype] = None):
+        self.w = weights
+        self.cfg: ModelConfig = weights.cfg
+        self.comm = comm or SingleRankComm()
+        dev = weights.embed.device
+        self.device = dev
+        self.act_dtype = act_dtype or (torch.bfloat16 if dev.type == "cuda" else torch.float32)
+        cfg = self.cfg
+        tp = weights.tp_size
+        self.n_heads_local = cfg.n_heads // tp
+        self.n_kv_local = max(1, cfg.n_kv_heads // tp)
+        self.rope = RopeState(
+            inv_freq=opref.rope_inv_freq(cfg.rotary_dim, cfg.rope_theta, cfg.rope_scaling, device=dev),
+            pairing=cfg.rope_pairing, mscale=opref.rope_mscale(cfg.rope_scaling),
+            n_heads=self.n_heads_local, n_kv_heads=self.n_kv_local, head_dim=cfg.head_dim)
+        self.attn_scale = cfg.head_dim ** -0.5
+
+    # ------------------------------------------------------------------ blocks
+    def _attention(self, lw: LayerWeights, layer: int, x: torch.Tensor, meta: BatchMeta, kv) -> torch.Tensor:
+        cfg = self.cfg
+        qkv = ops.linear(x, lw.wqkv)
+        q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, self.rope,
+                                 lw.q_norm, lw.k_norm, cfg.rms_eps)
+        attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, cfg.sliding_window)
+        out = ops.linear(attn.reshape(attn.shape[0], -1), lw.wo)
+        return self.comm.all_reduce(out)
+
+    def _dense_ffn(self, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
+        gu = ops.linear(x, lw.w_gate_up)
+        out = ops.linear(ops.silu_mul(gu), lw.w_down)
+        return self.comm.all_reduce(out)
+
+    def _moe_ffn(self, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
+        """Experts are partitioned across ranks (EP); tokens are replicated after the
+        attention all-reduce, so each rank runs its local experts on the rows routed to
+        them and the combine is the weighted sum + all-reduce."""
+        cfg = self.cfg
+        logits = ops.linear(x, lw.router).float()
+        ids, wts = ops.moe_route(logits, cfg, lw.router_bias)
+        out = moe_experts_forward(x, ids, wts, lw.experts)
+        if lw.shared_gate_up is not None:
+            sh = ops.linear(ops.silu_mul(ops.linear(x, lw.shared_gate_up)), lw.shared_down)
+            if lw.shared_gate is not None:
+                sh = (sh.float() * torch.sigmoid(ops.linear(x, lw.shared_gate).float())).to(sh.dtype)
+            out = out + sh
+        return self.comm.all_reduce(out)
+
+    def run_layers(self, h: torch.Tensor, residual: Optional[torch.Tensor], meta: BatchMeta, kv,
+                   layers: Optional[Tuple[int, int]] = None, capture: Optional[dict] = None):
+        """Run local layers; returns (h, residual) where the true hidden is h + residual."""
+        cfg = self.cfg
+        lo, hi = layers if layers is not None else (0, len(self.w.layers))
+        for li in range(lo, hi):
+            lw = self.w.layers[li]
+            gl = self.w.first_layer + li
+            x, residual = ops.add_rmsnorm(h, residual, lw.attn_norm, cfg.rms_eps)
+            h = self._attention(lw, li, x, meta, kv)
+            x, residual = ops.add_rmsnorm(h, residual, lw.ffn_norm, cfg.rms_eps)
+            h = self._moe_ffn(lw, x) if lw.router is not None else self._dense_ffn(lw, x)
+            if capture is not None and gl in capture.get("layers", ()):
+                capture.setdefault("hidden", {})[gl] = (h.float() + residual.float())
+        return h, residual
+
+    def embed(self, token_ids: torch.Tensor) -> torch.Tensor:
+        return ops.embed(token_ids, self.w.embed, self.act_dtype)
+
+    def head(self, h: torch.Tensor, residual: Optional[torch.Tensor], logits_indices: torch.Tensor,
+             return_hidden: bool = False):
+        """Final norm + vocabulary-parallel lm_head on the selected rows; logits float32."""
+        if logits_indices is not None:
+            idx = logits_indices.long()
+            h = h.index_select(0, idx)
+            residual = residual.index_select(0, idx) if residual is not None else None
+        x, hidden = ops.add_rmsnorm(h, residual, self.w.out_norm, self.cfg.rms_eps)
+        logits = ops.linear(x, self.w.lm_head).float()
+        if self.w.tp_size > 1 and self.w.lm_head.out_features != self.cfg.vocab_size:
+            logits = self.comm.all_gather_cat(logits, dim=-1)
+        return (logits, hidden) if return_hidden else logits
+
+    def forward(self, meta: BatchMeta, kv, return_hidden: bool = False, capture: Optional[dict] = None):
+        h = self.embed(meta.token_ids)
+        h, residual = self.run_layers(h, None, meta, kv, capture=capture)
+        return self.head(h, residual, meta.logits_indices, return_hidden)
+
+
+def moe_experts_forward(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, experts) -> torch.Tensor:
+    """Σ_k w[t,k] · down_e(silu(gate_e x) ⊙ up_e x) over the experts held locally."""
+    if x.is_cuda:
+        from ..ops import cuda as opcuda
+
+        return opcuda.moe_experts_forward(x, ids, wts, experts)
+    out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+    n_local = len(experts.gate_up)
+    for le in range(n_local):
+        e = experts.first_expert + le
+        sel = (ids == e)
+        rows = sel.any(dim=1).nonzero(as_tuple=True)[0]
+        if rows.numel() == 0:
+            continue
+        w = (wts * sel).sum(dim=1)[rows]
+        xe = x.index_select(0, rows)
+        y = ops.linear(ops.silu_mul(ops.linear(xe, experts.gate_up[le])), experts.down[le])
+        out.index_add_(0, rows, y.float() * w[:, None])
+    return out.to(x.dtype)

@@ -1,0 +1,362 @@
+"""Weight containers and the shard-aware GGUF loader.
+
+Weights stay in their checkpoint encoding on the device (packed Q4_K / Q6_K / Q8_0 / NVFP4
+rows, or bf16); a tensor-parallel rank copies only its slice of the mmap:
+
+* column-parallel (q, k, v, gate, up, experts' gate/up, lm_head): a contiguous range of rows;
+* row-parallel (attn_output, ffn_down): a contiguous range of *columns*, cut on quant-block
+  boundaries (256 for k-quants), i.e. a byte range inside every row.
+
+Tensor names are the GGUF ones the reference maps at ``model/inference/load.rs:81-431``;
+``output.weight`` absent means the head is tied to the embedding (``load.rs:436``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..formats.gguf import GGUFFile, GGMLTypeInfo, ggml_type
+from ..quant import ref as qref
+from .config import ModelConfig
+
+
+@dataclass
+class QTensor:
+    """A 2-D weight ``[out, in]`` in its storage encoding.
+
+    ``data`` is ``[out, in]`` for F32/F16/BF16 and ``uint8 [out, row_bytes]`` for block
+    formats.  ``FP8B`` is our block-scaled fp8 (e4m3 codes + one f32 scale per ``block``
+    input channels), which has no GGUF id."""
+
+    qtype: str
+    data: torch.Tensor
+    shape: Tuple[int, int]
+    scales: Optional[torch.Tensor] = None
+    block: int = 128
+    _dense: Optional[torch.Tensor] = field(default=None, repr=False)
+
+    @property
+    def out_features(self) -> int:
+        return self.shape[0]
+
+    @property
+    def in_features(self) -> int:
+        return self.shape[1]
+
+    @property
+    def device(self):
+        return self.data.device
+
+    def nbytes(self) -> int:
+        n = self.data.numel() * self.data.element_size()
+        if self.scales is not None:
+            n += self.scales.numel() * self.scales.element_size()
+        return n
+
+    def dense_cache(self) -> torch.Tensor:
+        """float32 dense copy, decoded once (CPU reference path / tests only)."""
+        if self._dense is None:
+            from ..ops import ref as opref
+
+            self._dense = opref.dequantize_weight(self)
+        return self._dense
+
+    def to(self, device) -> "QTensor":
+        return QTensor(self.qtype, self.data.to(device), self.shape,
+                       None if self.scales is None else self.scales.to(device), self.block)
+
+    def rows(self, start: int, stop: int) -> "QTensor":
+        return QTensor(self.qtype, self.data[start:stop], (stop - start, self.shape[1]),
+                       None if self.scales is None else self.scales[start:stop], self.block)
+
+
+def qtensor_from_dense(w: torch.Tensor, qtype: str = "BF16", device=None) -> QTensor:
+    """Encode a dense float weight ``[out, in]`` into ``qtype`` (host-side, NumPy oracle)."""
+    qtype = qtype.upper()
+    out_f, in_f = w.shape
+    dev = device if device is not None else w.device
+    if qtype == "F32":
+        return QTensor("F32", w.float().to(dev).contiguous(), (out_f, in_f))
+    if qtype == "BF16":
+        return QTensor("BF16", w.to(torch.bfloat16).to(dev).contiguous(), (out_f, in_f))
+    if qtype == "F16":
+        return QTensor("F16", w.to(torch.float16).to(dev).contiguous(), (out_f, in_f))
+    x = w.detach().float().cpu().numpy()
+    if qtype == "FP8B":
+        codes, scales = qref.quantize_fp8_block(x.reshape(-1), 128)
+        return QTensor("FP8B", torch.from_numpy(codes.reshape(out_f, in_f)).to(dev), (out_f, in_f),
+                       torch.from_numpy(scales.reshape(out_f, in_f // 128)).to(dev), 128)
+    t = ggml_type(qtype)
+    raw = qref.quantize(qtype, x.reshape(-1)).reshape(out_f, in_f // t.block_size * t.type_size)
+    return QTensor(t.name, torch.from_numpy(raw.copy()).to(dev), (out_f, in_f))
+
+
+@dataclass
+class LinearWeight:
+    """One logical projection made of row segments whose outputs are concatenated
+    (e.g. fused q|k|v where v may use a different quant type in a Q4_K_M file)."""
+
+    parts: List[QTensor]
+    bias: Optional[torch.Tensor] = None
+
+    @property
+    def out_features(self) -> int:
+        return sum(p.out_features for p in self.parts)
+
+    @property
+    def in_features(self) -> int:
+        return self.parts[0].in_features
+
+    def nbytes(self) -> int:
+        return sum(p.nbytes() for p in self.parts)
+
+
+def fuse_rows(parts: Sequence[QTensor]) -> List[QTensor]:
+    """Concatenate adjacent segments that share an encoding into one tensor."""
+    out: List[QTensor] = []
+    for p in parts:
+        if out and out[-1].qtype == p.qtype and out[-1].in_features == p.in_features and p.qtype != "FP8B":
+            a = out[-1]
+            out[-1] = QTensor(a.qtype, torch.cat([a.data, p.data], 0).contiguous(),
+                              (a.out_features + p.out_features, a.in_features))
+        else:
+            out.append(p)
+    return out
+
+
+@dataclass
+class ExpertWeights:
+    """Stacked expert matrices ``[n_local_experts, rows, cols]`` (packed rows for quants)."""
+
+    gate_up: List[QTensor]  # per local expert: fused [2*ffn, hidden]
+    down: List[QTensor]
+    first_expert: int = 0  # global id of local expert 0 (expert parallelism)
+
+
+@dataclass
+class LayerWeights:
+    attn_norm: torch.Tensor
+    wqkv: LinearWeight
+    wo: LinearWeight
+    ffn_norm: torch.Tensor
+    q_norm: Optional[torch.Tensor] = None
+    k_norm: Optional[torch.Tensor] = None
+    # dense FFN
+    w_gate_up: Optional[LinearWeight] = None
+    w_down: Optional[LinearWeight] = None
+    # MoE
+    router: Optional[QTensor] = None
+    router_bias: Optional[torch.Tensor] = None
+    experts: Optional[ExpertWeights] = None
+    shared_gate_up: Optional[LinearWeight] = None
+    shared_down: Optional[LinearWeight] = None
+    shared_gate: Optional[QTensor] = None
+
+
+@dataclass
+class MtpWeights:
+    """``blk.L.nextn.*`` tensors of an in-GGUF multi-token-prediction head
+    (``MtpWeights`` model/inference.rs:1403-1429)."""
+
+    enorm: torch.Tensor
+    hnorm: torch.Tensor
+    eh_proj: QTensor
+    layer: LayerWeights
+    shared_head_norm: torch.Tensor
+    shared_head: Optional[QTensor] = None
+    embed: Optional[QTensor] = None
+
+
+@dataclass
+class ModelWeights:
+    cfg: ModelConfig
+    embed: QTensor
+    layers: List[LayerWeights]
+    out_norm: torch.Tensor
+    lm_head: LinearWeight
+    mtp: List[MtpWeights] = field(default_factory=list)
+    tp_rank: int = 0
+    tp_size: int = 1
+    ep_rank: int = 0
+    ep_size: int = 1
+    first_layer: int = 0  # pipeline stage range [first_layer, first_layer+len(layers))
+    vocab_start: int = 0  # first vocabulary row held by this rank's lm_head shard
+
+    def nbytes(self) -> int:
+        n = self.embed.nbytes() + self.lm_head.nbytes()
+        for l in self.layers:
+            for lw in (l.wqkv, l.wo, l.w_gate_up, l.w_down, l.shared_gate_up, l.shared_down):
+                if lw is not None:
+                    n += lw.nbytes()
+            if l.experts is not None:
+                n += sum(e.nbytes() for e in l.experts.gate_up) + sum(e.nbytes() for e in l.experts.down)
+        return n
+
+
+# --------------------------------------------------------------------------- sharding helpers
+
+
+def shard_range(n: int, rank: int, size: int, multiple: int = 1) -> Tuple[int, int]:
+    """Contiguous [start, stop) of ``n`` items for ``rank``; ``n`` must split into ``size``
+    equal parts that are multiples of ``multiple``."""
+    if n % (size * multiple):
+        raise ValueError(f"cannot shard {n} into {size} parts of a multiple of {multiple}")
+    per = n // size
+    return rank * per, (rank + 1) * per
+
+
+def _np_to_torch(a: np.ndarray, device, dtype=None) -> torch.Tensor:
+    import warnings
+
+    with warnings.catch_warnings():
+        # read-only views of the GGUF mapping are never written through
+        warnings.simplefilter("ignore", UserWarning)
+        t = torch.from_numpy(np.ascontiguousarray(a))
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.to(device)
+
+
+class GGUFWeightSource:
+    """Reads (slices of) tensors from a GGUF mapping into device QTensors."""
+
+    def __init__(self, g: GGUFFile, device, act_dtype: torch.dtype):
+        self.g = g
+        self.device = device
+        self.act_dtype = act_dtype
+
+    def has(self, name: str) -> bool:
+        return self.g.has_tensor(name)
+
+    def vector(self, name: str) -> torch.Tensor:
+        info = self.g.tensors[name]
+        x = qref.dequantize(info.type.name, self.g.tensor_bytes(name), info.n_elements)
+        return torch.from_numpy(x.copy()).to(self.device, torch.float32)
+
+    def matrix(self, name: str, rows: Optional[Tuple[int, int]] = None, cols: Optional[Tuple[int, int]] = None,
+               expert: Optional[int] = None) -> QTensor:
+        info = self.g.tensors[name]
+        t: GGMLTypeInfo = info.type
+        shape = info.shape
+        in_f = shape[-1]
+        out_f = shape[-2] if len(shape) >= 2 else 1
+        raw = self.g.tensor_rows(name)  # [n_rows_total, row_nbytes]
+        if len(shape) == 3:
+            if expert is None:
+                raise ValueError(f"{name} is a stacked expert tensor; pass expert=")
+            raw = raw[expert * out_f : (expert + 1) * out_f]
+        r0, r1 = rows if rows is not None else (0, out_f)
+        raw = raw[r0:r1]
+        c0, c1 = cols if cols is not None else (0, in_f)
+        if (c0, c1) != (0, in_f):
+            if c0 % t.block_size or c1 % t.block_size:
+                raise ValueError(f"{name}: column shard [{c0},{c1}) not on {t.name} block boundary {t.block_size}")
+            raw = raw[:, c0 // t.block_size * t.type_size : c1 // t.block_size * t.type_size]
+        new_shape = (r1 - r0, c1 - c0)
+        if t.name == "F32":
+            x = np.ascontiguousarray(raw).view("<f4")
+            dt = torch.float32 if self.act_dtype == torch.float32 else torch.bfloat16
+            return QTensor("F32" if dt == torch.float32 else "BF16", _np_to_torch(x, self.device, dt), new_shape)
+        if t.name == "F16":
+            x = np.ascontiguousarray(raw).view("<f2")
+            if self.act_dtype == torch.float32:
+                return QTensor("F32", _np_to_torch(x, self.device, torch.float32), new_shape)
+            return QTensor("BF16", _np_to_torch(x, self.device, torch.bfloat16), new_shape)
+        if t.name == "BF16":
+            x = np.ascontiguousarray(raw).view("<i2")
+            tt = torch.from_numpy(x).view(torch.bfloat16)
+            if self.act_dtype == torch.float32:
+                return QTensor("F32", tt.float().to(self.device), new_shape)
+            return QTensor("BF16", tt.to(self.device), new_shape)
+        return QTensor(t.name, _np_to_torch(raw, self.device), new_shape)
+
+
+def _load_layer(src: GGUFWeightSource, cfg: ModelConfig, i: int, tp_rank: int, tp_size: int,
+                ep_rank: int, ep_size: int, prefix: Optional[str] = None) -> LayerWeights:
+    p = prefix or f"blk.{i}"
+    hd = cfg.head_dim
+    # attention heads are sharded by KV head; with fewer KV heads than ranks they replicate
+    kv_rep = max(1, tp_size // cfg.n_kv_heads)
+    kv_shards = min(tp_size, cfg.n_kv_heads)
+    q0, q1 = shard_range(cfg.n_heads, tp_rank, tp_size)
+    k0, k1 = shard_range(cfg.n_kv_heads, tp_rank // kv_rep, kv_shards)
+    qr, kr = (q0 * hd, q1 * hd), (k0 * hd, k1 * hd)
+    parts = [src.matrix(f"{p}.attn_q.weight", rows=qr), src.matrix(f"{p}.attn_k.weight", rows=kr),
+             src.matrix(f"{p}.attn_v.weight", rows=kr)]
+    bias = None
+    if src.has(f"{p}.attn_q.bias"):
+        bias = torch.cat([src.vector(f"{p}.attn_q.bias")[qr[0]:qr[1]], src.vector(f"{p}.attn_k.bias")[kr[0]:kr[1]],
+                          src.vector(f"{p}.attn_v.bias")[kr[0]:kr[1]]])
+    lw = LayerWeights(
+        attn_norm=src.vector(f"{p}.attn_norm.weight"),
+        wqkv=LinearWeight(fuse_rows(parts), bias),
+        wo=LinearWeight([src.matrix(f"{p}.attn_output.weight", cols=qr)]),
+        ffn_norm=src.vector(f"{p}.ffn_norm.weight"),
+    )
+    if src.has(f"{p}.attn_q_norm.weight"):
+        lw.q_norm = src.vector(f"{p}.attn_q_norm.weight")
+        lw.k_norm = src.vector(f"{p}.attn_k_norm.weight")
+    if src.has(f"{p}.ffn_gate_inp.weight"):
+        lw.router = src.matrix(f"{p}.ffn_gate_inp.weight")
+        if src.has(f"{p}.exp_probs_b.bias"):
+            lw.router_bias = src.vector(f"{p}.exp_probs_b.bias")
+        e0, e1 = shard_range(cfg.n_experts, ep_rank, ep_size)
+        gu, dn = [], []
+        for e in range(e0, e1):
+            g_ = src.matrix(f"{p}.ffn_gate_exps.weight", expert=e)
+            u_ = src.matrix(f"{p}.ffn_up_exps.weight", expert=e)
+            fused = fuse_rows([g_, u_])
+            if len(fused) != 1:
+                raise ValueError(f"{p}: expert gate/up use different encodings")
+            gu.append(fused[0])
+            dn.append(src.matrix(f"{p}.ffn_down_exps.weight", expert=e))
+        lw.experts = ExpertWeights(gu, dn, e0)
+        if src.has(f"{p}.ffn_gate_shexp.weight"):
+            sf = cfg.shared_expert_ffn_size
+            f0, f1 = shard_range(sf, tp_rank, tp_size, 256 if sf % (256 * tp_size) == 0 else 1)
+            lw.shared_gate_up = LinearWeight(fuse_rows([src.matrix(f"{p}.ffn_gate_shexp.weight", rows=(f0, f1)),
+                                                        src.matrix(f"{p}.ffn_up_shexp.weight", rows=(f0, f1))]))
+            lw.shared_down = LinearWeight([src.matrix(f"{p}.ffn_down_shexp.weight", cols=(f0, f1))])
+            if src.has(f"{p}.ffn_gate_inp_shexp.weight"):
+                lw.shared_gate = src.matrix(f"{p}.ffn_gate_inp_shexp.weight")
+    else:
+        ffn = src.g.tensors[f"{p}.ffn_gate.weight"].shape[0]
+        f0, f1 = shard_range(ffn, tp_rank, tp_size)
+        lw.w_gate_up = LinearWeight(fuse_rows([src.matrix(f"{p}.ffn_gate.weight", rows=(f0, f1)),
+                                               src.matrix(f"{p}.ffn_up.weight", rows=(f0, f1))]))
+        lw.w_down = LinearWeight([src.matrix(f"{p}.ffn_down.weight", cols=(f0, f1))])
+    return lw
+
+
+def load_weights(g: GGUFFile, cfg: ModelConfig, device="cpu", act_dtype: torch.dtype = torch.float32,
+                 tp_rank: int = 0, tp_size: int = 1, ep_rank: int = 0, ep_size: int = 1,
+                 layer_range: Optional[Tuple[int, int]] = None) -> ModelWeights:
+    """Load this rank's shard of a GGUF checkpoint.
+
+    ``layer_range`` selects a pipeline stage (only its own tensors are read, unlike the
+    reference's two-node pipeline where both nodes map the whole file, pipeline.rs:23)."""
+    src = GGUFWeightSource(g, device, act_dtype)
+    l0, l1 = layer_range if layer_range is not None else (0, cfg.n_layers)
+    layers = [_load_layer(src, cfg, i, tp_rank, tp_size, ep_rank, ep_size) for i in range(l0, l1)]
+    embed = src.matrix("token_embd.weight")
+    v0, v1 = shard_range(cfg.vocab_size, tp_rank, tp_size) if cfg.vocab_size % tp_size == 0 else (0, cfg.vocab_size)
+    head_name = "output.weight" if src.has("output.weight") else "token_embd.weight"
+    lm_head = LinearWeight([src.matrix(head_name, rows=(v0, v1))])
+    mw = ModelWeights(cfg, embed, layers, src.vector("output_norm.weight"), lm_head, [], tp_rank, tp_size,
+                      ep_rank, ep_size, l0, v0)
+    for j in range(cfg.nextn_layers):
+        L = cfg.n_layers + j
+        p = f"blk.{L}.nextn"
+        if not src.has(f"{p}.eh_proj.weight"):
+            continue
+        mw.mtp.append(MtpWeights(
+            enorm=src.vector(f"{p}.enorm.weight"), hnorm=src.vector(f"{p}.hnorm.weight"),
+            eh_proj=src.matrix(f"{p}.eh_proj.weight"),
+            layer=_load_layer(src, cfg, L, tp_rank, tp_size, ep_rank, ep_size),
+            shared_head_norm=src.vector(f"{p}.shared_head_norm.weight"),
+            shared_head=src.matrix(f"{p}.shared_head_head.weight") if src.has(f"{p}.shared_head_head.weight") else None,
+            embed=src.matrix(f"{p}.embed_tokens.weight") if src.has(f"{p}.embed_tokens.weight") else None))
+    return mw
