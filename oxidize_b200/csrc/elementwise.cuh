@@ -1,0 +1,251 @@
+// Memory-bound glue kernels: embedding gather (dense or block-quantized table), fused
+// residual-add + RMSNorm, SwiGLU, fused QK-norm + RoPE + paged-KV write (bf16/f16/q8/q4),
+// and greedy argmax.  Each fuses what the reference runs as separate launches
+// (oxidize-core/kernels/gemv_f32.cu: rms_norm :1680, residual_add :1720, silu_mul :1738,
+// rope :1928, kv_append :1990, embed :2258/:2271; oxidize-c k_residual_rms cuda.cu:561,
+// k_qk_norm_rope cuda_qwen35.cu:46, k_f_argmax cuda_fast.cu:495).
+#pragma once
+#include "common.cuh"
+#include "quant_blocks.cuh"
+
+namespace oxb {
+
+// ----------------------------------------------------------------------------- embedding
+// one CTA per token; qtype as in quant_blocks.cuh
+__global__ void embed_kernel(const int* __restrict__ tokens, const uint8_t* __restrict__ table, int qtype,
+                             size_t row_bytes, int H, int vocab, float scale, __nv_bfloat16* __restrict__ out) {
+  const int t = blockIdx.x;
+  int tok = tokens[t];
+  if (tok < 0 || tok >= vocab) tok = 0;
+  const uint8_t* row = table + (size_t)tok * row_bytes;
+  __nv_bfloat16* o = out + (size_t)t * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = __float2bfloat16(dequant_elem(qtype, row, i) * scale);
+}
+
+// ----------------------------------------------------------------------------- add + RMSNorm
+// y = rmsnorm(x + residual) * w ; residual <- x + residual (bf16, rounded before the norm)
+// one CTA per row; the summed row is staged in shared memory as fp32.
+__global__ void add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res_in,
+                                   __nv_bfloat16* __restrict__ res_out, const float* __restrict__ w,
+                                   __nv_bfloat16* __restrict__ y, int H, float eps) {
+  extern __shared__ float rowbuf[];
+  __shared__ float red[32];
+  const size_t base = (size_t)blockIdx.x * H;
+  float ss = 0.f;
+  const int H8 = H >> 3;
+  for (int i = threadIdx.x; i < H8; i += blockDim.x) {
+    uint4 xv = *reinterpret_cast<const uint4*>(x + base + i * 8);
+    uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w};
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = unpack_bf16x2(xs[j]);
+      v[2 * j] = f.x;
+      v[2 * j + 1] = f.y;
+    }
+    if (res_in != nullptr) {
+      uint4 rv = *reinterpret_cast<const uint4*>(res_in + base + i * 8);
+      uint32_t rs[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = unpack_bf16x2(rs[j]);
+        v[2 * j] += f.x;
+        v[2 * j + 1] += f.y;
+      }
+    }
+    uint4 ov;
+    uint32_t* os = reinterpret_cast<uint32_t*>(&ov);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      os[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+      float2 f = unpack_bf16x2(os[j]);  // the norm sees the rounded residual
+      rowbuf[i * 8 + 2 * j] = f.x;
+      rowbuf[i * 8 + 2 * j + 1] = f.y;
+      ss += f.x * f.x + f.y * f.y;
+    }
+    if (res_out != nullptr) *reinterpret_cast<uint4*>(res_out + base + i * 8) = ov;
+  }
+  for (int i = H8 * 8 + threadIdx.x; i < H; i += blockDim.x) {  // tail when H % 8 != 0
+    float v = __bfloat162float(x[base + i]);
+    if (res_in != nullptr) v += __bfloat162float(res_in[base + i]);
+    __nv_bfloat16 r = __float2bfloat16(v);
+    if (res_out != nullptr) res_out[base + i] = r;
+    v = __bfloat162float(r);
+    rowbuf[i] = v;
+    ss += v * v;
+  }
+  const float total = block_sum(ss, red);
+  const float inv = rsqrtf(total / (float)H + eps);
+  __syncthreads();
+  for (int i = threadIdx.x; i < H; i += blockDim.x) y[base + i] = __float2bfloat16(rowbuf[i] * inv * w[i]);
+}
+
+// ----------------------------------------------------------------------------- SwiGLU
+// out[t, i] = silu(gu[t, i]) * gu[t, I + i]
+__global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int T, int I) {
+  const int I8 = I >> 3;
+  const size_t total = (size_t)T * I8;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / I8;
+    const int i = (int)(idx % I8) * 8;
+    const uint4 g = *reinterpret_cast<const uint4*>(gu + t * 2 * I + i);
+    const uint4 u = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + i);
+    const uint32_t gs[4] = {g.x, g.y, g.z, g.w}, us[4] = {u.x, u.y, u.z, u.w};
+    uint4 o;
+    uint32_t* os = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 a = unpack_bf16x2(gs[j]), b = unpack_bf16x2(us[j]);
+      os[j] = pack_bf16x2(a.x / (1.f + __expf(-a.x)) * b.x, a.y / (1.f + __expf(-a.y)) * b.y);
+    }
+    *reinterpret_cast<uint4*>(out + t * I + i) = o;
+  }
+}
+
+// ----------------------------------------------------------------------------- QK-norm + RoPE + KV write
+// grid (T, nq + 2*nkv), block = head_dim threads.  Head h < nq: query (norm, rope, store to q_out);
+// nq <= h < nq+nkv: key (norm, rope, write to cache); else value (write to cache).
+// cos_sin: [max_pos, rot] fp32 (cos for pair i at [p, i], sin at [p, rot/2 + i]).
+// KV cache layout: [block, kv_head, 2, page, head_dim(/2 for q4)]; scales [block, kv_head, 2, page, hd/32].
+struct KvWriteArgs {
+  void* kv_data;
+  float* kv_scales;
+  int kv_mode;  // 0 bf16, 1 f16, 2 q8, 3 q4, 4 f32
+  int page;
+  int nkv;
+};
+
+__global__ void qk_rope_kvwrite_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                                       const int* __restrict__ slots, const float* __restrict__ cos_sin, int max_pos,
+                                       int rot, int pairing /*0 split-half, 1 adjacent*/, const float* __restrict__ qn,
+                                       const float* __restrict__ kn, float eps, int nq, int nkv, int hd,
+                                       __nv_bfloat16* __restrict__ q_out, KvWriteArgs kv) {
+  extern __shared__ float hbuf[];  // hd floats
+  __shared__ float red[32];
+  const int t = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  const int width = (nq + 2 * nkv) * hd;
+  float v = __bfloat162float(qkv[(size_t)t * width + (size_t)h * hd + d]);
+  const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+  if (is_q || is_k) {
+    const float* nw = is_q ? qn : kn;
+    if (nw != nullptr) {
+      const float ss = block_sum(v * v, red);
+      v = v * rsqrtf(ss / (float)hd + eps) * nw[d];
+    }
+    hbuf[d] = v;
+    __syncthreads();
+    if (d < rot) {
+      int p = positions[t];
+      p = p < 0 ? 0 : (p >= max_pos ? max_pos - 1 : p);
+      const int half = rot >> 1;
+      int pair, partner;
+      bool first;
+      if (pairing == 0) {
+        first = d < half;
+        pair = first ? d : d - half;
+        partner = first ? d + half : d - half;
+      } else {
+        first = (d & 1) == 0;
+        pair = d >> 1;
+        partner = d ^ 1;
+      }
+      const float c = cos_sin[(size_t)p * rot + pair], s = cos_sin[(size_t)p * rot + half + pair];
+      const float o = hbuf[partner];
+      v = first ? (v * c - o * s) : (v * c + o * s);
+    }
+  }
+  if (is_q) {
+    q_out[((size_t)t * nq + h) * hd + d] = __float2bfloat16(v);
+    return;
+  }
+  const int slot = slots[t];
+  if (slot < 0) return;
+  const int kvh = is_k ? h - nq : h - nq - nkv;
+  const int which = is_k ? 0 : 1;
+  const int blk = slot / kv.page, off = slot % kv.page;
+  const size_t row = (((size_t)blk * kv.nkv + kvh) * 2 + which) * kv.page + off;
+  if (kv.kv_mode == 0) {
+    reinterpret_cast<__nv_bfloat16*>(kv.kv_data)[row * hd + d] = __float2bfloat16(v);
+  } else if (kv.kv_mode == 1) {
+    reinterpret_cast<__half*>(kv.kv_data)[row * hd + d] = __float2half(v);
+  } else if (kv.kv_mode == 4) {
+    reinterpret_cast<float*>(kv.kv_data)[row * hd + d] = v;
+  } else {
+    // symmetric per-32-channel blocks; one warp == one block (hd is a multiple of 32)
+    const float qmax = kv.kv_mode == 2 ? 127.f : 7.f;
+    const float amax = warp_max(fabsf(v));
+    const float scale = amax / qmax;
+    const float inv = scale > 0.f ? 1.f / scale : 0.f;
+    const int q = (int)fminf(fmaxf(rintf(v * inv), -qmax), qmax) + (int)qmax;
+    if ((d & 31) == 0) kv.kv_scales[row * (hd >> 5) + (d >> 5)] = scale;
+    uint8_t* data = reinterpret_cast<uint8_t*>(kv.kv_data);
+    if (kv.kv_mode == 2) {
+      data[row * hd + d] = (uint8_t)q;
+    } else {
+      const int hi = __shfl_down_sync(0xffffffffu, q, 1);
+      if ((d & 1) == 0) data[row * (hd >> 1) + (d >> 1)] = (uint8_t)(q | (hi << 4));
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- argmax
+// one CTA per row of fp32 logits; tie_highest selects the last maximal index
+__global__ void argmax_kernel(const float* __restrict__ logits, int V, int ld, int tie_highest, int* __restrict__ out,
+                              float* __restrict__ out_val, int index_offset) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const float* row = logits + (size_t)blockIdx.x * ld;
+  float best = -INFINITY;
+  int bi = -1;  // -1 = nothing seen yet
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = row[i];
+    // per-thread indices increase, so on ties the later one wins only under tie_highest
+    if (bi < 0 || v > best || (v == best && tie_highest)) {
+      if (!(v != v)) {
+        best = v;
+        bi = i;
+      }
+    }
+  }
+  auto better = [&](float v, int i, float bv, int b) {
+    if (i < 0) return false;
+    if (b < 0) return true;
+    return v > bv || (v == bv && (tie_highest ? i > b : i < b));
+  };
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better(ov, oi, best, bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    sv[warp] = best;
+    si[warp] = bi;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    best = lane < nw ? sv[lane] : -INFINITY;
+    bi = lane < nw ? si[lane] : -1;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (better(ov, oi, best, bi)) {
+        best = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0) {
+      if (bi < 0) bi = 0;  // all-NaN row
+      out[blockIdx.x] = bi + index_offset;
+      if (out_val != nullptr) out_val[blockIdx.x] = best;
+    }
+  }
+}
+
+}  // namespace oxb

@@ -1,0 +1,245 @@
+// Y[T, N] = X[T, K] · W[N, K]^T  (bf16 in, fp32 accumulate in TMEM, bf16 out) for sm_100a.
+//
+// Weight-stationary orientation: the UMMA M dimension (128) runs over weight rows, the UMMA N
+// dimension (TN = 16..256) over tokens, so a decode batch of 1..256 tokens is ONE instruction
+// shape and the kernel is a pure weight stream: every CTA pulls 128-row × 64-column weight
+// tiles with TMA (128-byte swizzle) through a deep mbarrier ring, one elected thread issues
+// tcgen05.mma into a TMEM accumulator, and four epilogue warps read it back with tcgen05.ld.
+// Small-N projections are split along K across CTAs so that all 148 SMs stream; the last CTA
+// of a tile (atomic ticket) reduces the fp32 partials in a fixed order, which keeps the
+// result bit-reproducible.
+//
+// Replaces the reference's cuBLAS SGEMM / cuBLASLt f16 prefill GEMMs and its f16 GEMV
+// (oxidize-core/src/backends/cuda/gemm.rs:100, oxidize-cpp/src/cuda/gemm.cu:43,141-201).
+#pragma once
+#include "common.cuh"
+
+namespace oxb {
+
+constexpr int GEMM_BM = 128;  // weight rows per tile (UMMA M)
+constexpr int GEMM_BK = 64;   // bf16 per k-block = one 128-byte swizzle row
+constexpr int GEMM_THREADS = 192;
+
+template <int TN>
+struct GemmTile {
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int B_BYTES = TN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (TN <= 64) ? 8 : (TN == 128 ? 6 : 4);
+  static constexpr int TMEM_COLS = TN < 32 ? 32 : TN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+// Epilogue modes
+constexpr int EPI_STORE = 0;      // Y = acc (+bias)
+constexpr int EPI_ADD_INTO = 1;   // Y += acc (residual accumulate, bf16 read-modify-write)
+
+template <int TN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                 __nv_bfloat16* __restrict__ Y, const float* __restrict__ bias, int N, int T, int K, int ldY,
+                 int splits, float* __restrict__ ws, int* __restrict__ counters, int epi_mode) {
+  using Cfg = GemmTile<TN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* accum = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* ticket = const_cast<int*>(abort_flag) + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * GEMM_BM;
+  const int split = blockIdx.y;
+  const int t0 = blockIdx.z * TN;
+  const int kb_total = (K + GEMM_BK - 1) / GEMM_BK;
+  const int kb_begin = (int)((long long)split * kb_total / splits);
+  const int kb_end = (int)((long long)(split + 1) * kb_total / splits);
+  const int nkb = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    mbar_init(accum, 1);
+    *abort_flag = 0;
+    *ticket = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmW);
+      tma_prefetch_desc(&tmX);
+      const uint64_t pol_w = l2_policy_evict_first();  // weights are read once per step
+      const uint64_t pol_x = l2_policy_evict_last();   // activations are re-read by every CTA
+      for (int i = 0; i < nkb; ++i) {
+        const int st = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        if (!mbar_wait_bounded(&empty[st], ph ^ 1, abort_flag, OXB_TIMEOUT_TMA_EMPTY, blockIdx.x)) break;
+        uint8_t* sA = smem + st * Cfg::STAGE_BYTES;
+        uint8_t* sB = sA + Cfg::A_BYTES;
+        mbar_expect_tx(&full[st], Cfg::STAGE_BYTES);
+        tma_load_2d_hint(sA, &tmW, &full[st], (kb_begin + i) * GEMM_BK, n0, pol_w);
+        tma_load_2d_hint(sB, &tmX, &full[st], (kb_begin + i) * GEMM_BK, t0, pol_x);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(GEMM_BM, TN);
+      for (int i = 0; i < nkb; ++i) {
+        const int st = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        if (!mbar_wait_bounded(&full[st], ph, abort_flag, OXB_TIMEOUT_TMA_FULL, blockIdx.x)) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + st * Cfg::STAGE_BYTES);
+        const uint64_t adesc = umma_desc_k_sw128(a_addr);
+        const uint64_t bdesc = umma_desc_k_sw128(a_addr + Cfg::A_BYTES);
+#pragma unroll
+        for (int k = 0; k < GEMM_BK / 16; ++k) {
+          // advance 16 bf16 = 32 bytes inside the swizzle row: +2 in the (addr >> 4) field
+          umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty[st]);  // frees the stage when these MMAs have read it
+      }
+      umma_commit(accum);
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue: warps 2..5 own TMEM lane quarters (warp % 4)
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;  // row inside the 128-row tile
+    const int n = n0 + row;
+    mbar_wait_bounded(accum, 0, abort_flag, OXB_TIMEOUT_ACCUM, blockIdx.x);
+    // agree on one verdict for all 128 epilogue threads before any further named barrier
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (threadIdx.x == 64) ticket[1] = (*abort_flag == 0);
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const bool ok = ticket[1] != 0;
+    tc_fence_after();
+    const float b = (bias != nullptr && n < N) ? bias[n] : 0.f;
+    const int tile_id = blockIdx.z * gridDim.x + blockIdx.x;
+    if (ok && splits == 1) {
+#pragma unroll 1
+      for (int c = 0; c < TN / 16; ++c) {
+        uint32_t r[16];
+        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
+        tmem_ld_wait();
+        if (n < N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int t = t0 + c * 16 + j;
+            if (t < T) {
+              float v = __uint_as_float(r[j]) + b;
+              __nv_bfloat16* dst = Y + (size_t)t * ldY + n;
+              if (epi_mode == EPI_ADD_INTO) v += __bfloat162float(*dst);
+              *dst = __float2bfloat16(v);
+            }
+          }
+        }
+      }
+    } else if (ok) {
+      // fp32 partial -> workspace [tile][split][token][row]; the last CTA of the tile reduces
+      float* my = ws + ((size_t)tile_id * splits + split) * (size_t)(TN * GEMM_BM);
+#pragma unroll 1
+      for (int c = 0; c < TN / 16; ++c) {
+        uint32_t r[16];
+        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) my[(c * 16 + j) * GEMM_BM + row] = __uint_as_float(r[j]);
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) *ticket = atomicAdd(&counters[tile_id], 1);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*ticket == splits - 1) {
+        __threadfence();
+        const float* base = ws + (size_t)tile_id * splits * (size_t)(TN * GEMM_BM);
+        const int tmax = min(TN, T - t0);
+        if (n < N) {
+          for (int j = 0; j < tmax; ++j) {
+            float acc = b;
+            for (int s = 0; s < splits; ++s) acc += __ldcg(base + (size_t)s * (TN * GEMM_BM) + j * GEMM_BM + row);
+            __nv_bfloat16* dst = Y + (size_t)(t0 + j) * ldY + n;
+            if (epi_mode == EPI_ADD_INTO) acc += __bfloat162float(*dst);
+            *dst = __float2bfloat16(acc);
+          }
+        }
+        if (threadIdx.x == 64) counters[tile_id] = 0;  // ready for the next launch / graph replay
+      }
+    }
+  }
+
+  if (*abort_flag) {
+    // a wait gave up: give copies that may still be in flight time to land before the CTA exits
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+struct GemmPlan {
+  int tn, n_tiles, t_tiles, splits;
+  size_t ws_bytes;
+  int n_counters;
+};
+
+inline GemmPlan gemm_plan(int T, int N, int K, int splits_hint, int sm_count) {
+  GemmPlan p;
+  p.tn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+  p.n_tiles = (N + GEMM_BM - 1) / GEMM_BM;
+  p.t_tiles = (T + p.tn - 1) / p.tn;
+  const int kb_total = (K + GEMM_BK - 1) / GEMM_BK;
+  int splits = splits_hint;
+  if (splits <= 0) {
+    const int tiles = p.n_tiles * p.t_tiles;
+    splits = 1;
+    if (tiles < sm_count) {
+      splits = sm_count / tiles;
+      const int max_by_k = kb_total / 4 > 0 ? kb_total / 4 : 1;  // at least 4 k-blocks (256 columns) per split
+      if (splits > max_by_k) splits = max_by_k;
+      if (splits > 16) splits = 16;
+      if (splits < 1) splits = 1;
+    }
+  }
+  if (splits > kb_total) splits = kb_total;
+  p.splits = splits;
+  p.ws_bytes = splits > 1 ? (size_t)p.n_tiles * p.t_tiles * splits * p.tn * GEMM_BM * sizeof(float) : 0;
+  p.n_counters = p.n_tiles * p.t_tiles;
+  return p;
+}
+
+template <int TN>
+int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y, const float* bias, int N, int T, int K,
+                int ldY, const GemmPlan& p, float* ws, int* counters, int epi_mode, cudaStream_t stream) {
+  using Cfg = GemmTile<TN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(p.n_tiles, p.splits, p.t_tiles);
+  gemm_bf16_kernel<TN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmW, tmX, Y, bias, N, T, K, ldY, p.splits, ws,
+                                                                        counters, epi_mode);
+  OXB_CHECK_LAUNCH();
+  return 0;
+}
+
+}  // namespace oxb

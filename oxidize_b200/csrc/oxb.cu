@@ -1,0 +1,246 @@
+// liboxb: the sm_100a kernel library of oxidize_b200, exported with a plain C ABI
+// (loaded from Python with ctypes; every launcher takes raw device pointers and a stream and
+// returns a cudaError_t code, 0 on success).  Built as ONE translation unit.
+#include "common.cuh"
+#include "quant_blocks.cuh"
+#include "elementwise.cuh"
+#include "gemm_tcgen05.cuh"
+#include "attention.cuh"
+#include "sampling.cuh"
+#include "gemv_quant.cuh"
+#include "comm_fused.cuh"
+
+using namespace oxb;
+
+// ----------------------------------------------------------------------------- host utilities
+PFN_encodeTiled oxb_get_encode_tiled() {
+  static PFN_encodeTiled fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_encodeTiled>(p);
+  }
+  return fn;
+}
+
+int oxb_make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
+                     uint32_t box_rows, uint32_t box_cols, int elem_bytes) {
+  PFN_encodeTiled enc = oxb_get_encode_tiled();
+  if (enc == nullptr) return (int)cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (row_stride_bytes & 15) != 0) return (int)cudaErrorInvalidValue;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = enc(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+OXB_API int oxb_version() { return 100; }
+
+// Copy the device status word {code, detail, count, _} to the host (synchronises the device).
+OXB_API int oxb_status(int* out4, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out4, g_oxb_status, 4 * sizeof(int));
+  if (e != cudaSuccess) return (int)e;
+  if (reset) {
+    int z[4] = {0, 0, 0, 0};
+    e = cudaMemcpyToSymbol(g_oxb_status, z, sizeof(z));
+  }
+  return (int)e;
+}
+
+// ----------------------------------------------------------------------------- GEMM
+OXB_API int oxb_gemm_plan(int T, int N, int K, int splits_hint, int* out4, size_t* ws_bytes, int* n_counters) {
+  GemmPlan p = gemm_plan(T, N, K, splits_hint, sm_count());
+  out4[0] = p.tn;
+  out4[1] = p.n_tiles;
+  out4[2] = p.t_tiles;
+  out4[3] = p.splits;
+  *ws_bytes = p.ws_bytes;
+  *n_counters = p.n_counters;
+  return 0;
+}
+
+// Y[T, ldY>=N] (bf16) = X[T, K] (bf16, contiguous) · W[N, K]^T (bf16, contiguous) (+bias f32[N]).
+// `ws` (fp32 scratch) and `counters` (zero-initialised ints, left zeroed) are only touched when
+// the plan splits K; if they are too small the split count is reduced to fit.
+OXB_API int oxb_gemm_bf16(const void* X, const void* W, void* Y, const float* bias, int T, int N, int K, int ldY,
+                          int epi_mode, int splits_hint, void* ws, size_t ws_bytes, int* counters, int n_counters,
+                          cudaStream_t stream) {
+  if (T <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % 8 != 0) return (int)cudaErrorInvalidValue;  // TMA rows must be 16-byte multiples
+  GemmPlan p = gemm_plan(T, N, K, splits_hint, sm_count());
+  while (p.splits > 1 && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || ws == nullptr || counters == nullptr))
+    p = gemm_plan(T, N, K, p.splits - 1, sm_count());
+  CUtensorMap tmW, tmX;
+  int e = oxb_make_tmap_2d(&tmW, W, N, K, (uint64_t)K * 2, GEMM_BM, GEMM_BK, 2);
+  if (e) return e;
+  e = oxb_make_tmap_2d(&tmX, X, T, K, (uint64_t)K * 2, p.tn, GEMM_BK, 2);
+  if (e) return e;
+  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(Y);
+  float* wsf = reinterpret_cast<float*>(ws);
+  switch (p.tn) {
+    case 16: return gemm_launch<16>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, stream);
+    case 32: return gemm_launch<32>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, stream);
+    case 64: return gemm_launch<64>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, stream);
+    case 128: return gemm_launch<128>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, stream);
+    default: return gemm_launch<256>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, stream);
+  }
+}
+
+// ----------------------------------------------------------------------------- dequant / embed / norms
+__global__ void dequant_rows_kernel(const uint8_t* __restrict__ src, int qtype, size_t row_bytes, int cols,
+                                    __nv_bfloat16* __restrict__ dst) {
+  const uint8_t* row = src + (size_t)blockIdx.x * row_bytes;
+  __nv_bfloat16* o = dst + (size_t)blockIdx.x * cols;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) o[i] = __float2bfloat16(dequant_elem(qtype, row, i));
+}
+
+OXB_API int oxb_dequant_rows(const void* src, int qtype, size_t row_bytes, int rows, int cols, void* dst_bf16,
+                             cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  dequant_rows_kernel<<<rows, 256, 0, stream>>>(reinterpret_cast<const uint8_t*>(src), qtype, row_bytes, cols,
+                                                reinterpret_cast<__nv_bfloat16*>(dst_bf16));
+  OXB_CHECK_LAUNCH();
+  return 0;
+}
+
+OXB_API int oxb_embed(const int* tokens, const void* table, int qtype, size_t row_bytes, int H, int vocab, float scale,
+                      void* out_bf16, int T, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  embed_kernel<<<T, 256, 0, stream>>>(tokens, reinterpret_cast<const uint8_t*>(table), qtype, row_bytes, H, vocab,
+                                      scale, reinterpret_cast<__nv_bfloat16*>(out_bf16));
+  OXB_CHECK_LAUNCH();
+  return 0;
+}
+
+OXB_API int oxb_add_rmsnorm(const void* x, const void* res_in, void* res_out, const float* w, void* y, int T, int H,
+                            float eps, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H % 8 != 0 && false) return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)H * sizeof(float);
+  static size_t configured = 48 * 1024;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  const int threads = H >= 4096 ? 512 : 256;
+  add_rmsnorm_kernel<<<T, threads, smem, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(res_in),
+      reinterpret_cast<__nv_bfloat16*>(res_out), w, reinterpret_cast<__nv_bfloat16*>(y), H, eps);
+  OXB_CHECK_LAUNCH();
+  return 0;
+}
+
+OXB_API int oxb_silu_mul(const void* gu, void* out, int T, int I, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (I % 8 != 0) return (int)cudaErrorInvalidValue;
+  const size_t total = (size_t)T * (I / 8);
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
+  silu_mul_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(gu),
+                                              reinterpret_cast<__nv_bfloat16*>(out), T, I);
+  OXB_CHECK_LAUNCH();
+  return 0;
+}
+
+OXB_API int oxb_qk_rope_kvwrite(const void* qkv, const int* positions, const int* slots, const float* cos_sin,
+                                int max_pos, int rot, int pairing, const float* q_norm, const float* k_norm, float eps,
+                                int T, int nq, int nkv, int hd, void* q_out, void* kv_data, float* kv_scales,
+                                int kv_mode, int page, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (hd % 32 != 0 || hd > 1024) return (int)cudaErrorInvalidValue;
+  KvWriteArgs kv{kv_data, kv_scales, kv_mode, page, nkv};
+  dim3 grid(T, nq + 2 * nkv);
+  qk_rope_kvwrite_kernel<<<grid, hd, hd * sizeof(float), stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(qkv), positions, slots, cos_sin, max_pos, rot, pairing, q_norm, k_norm, eps,
+      nq, nkv, hd, reinterpret_cast<__nv_bfloat16*>(q_out), kv);
+  OXB_CHECK_LAUNCH();
+  return 0;
+}
+
+OXB_API int oxb_argmax(const float* logits, int R, int V, int ld, int tie_highest, int* out, float* out_val,
+                       int index_offset, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  argmax_kernel<<<R, 1024, 0, stream>>>(logits, V, ld, tie_highest, out, out_val, index_offset);
+  OXB_CHECK_LAUNCH();
+  return 0;
+}
+
+// ----------------------------------------------------------------------------- attention
+// Sizes of the split-KV scratch for a launch shape (floats).
+OXB_API int oxb_attn_ws_floats(int B, int nkv, int max_mtiles, int n_cta_splits, int hd, size_t* o_floats,
+                               size_t* ml_floats) {
+  const size_t tasks = (size_t)B * nkv * max_mtiles * n_cta_splits;
+  *o_floats = n_cta_splits > 1 ? tasks * 16 * hd : 0;
+  *ml_floats = n_cta_splits > 1 ? tasks * 16 * 2 : 0;
+  return 0;
+}
+
+template <int HD>
+static int attn_launch(const AttnArgs& a, int B, int G, cudaStream_t stream) {
+  constexpr int SMEM = ATT_WARPS * ATT_STAGES * 32 * (HD * 2 + 16);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(paged_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(a.max_mtiles * a.n_cta_splits, a.nkv, B);
+  paged_attention_kernel<HD><<<grid, ATT_WARPS * 32, SMEM, stream>>>(a, G);
+  OXB_CHECK_LAUNCH();
+  if (a.n_cta_splits > 1) {
+    dim3 mg(a.max_mtiles, a.nkv, B);
+    attn_merge_kernel<HD><<<mg, 128, 0, stream>>>(a, G);
+    OXB_CHECK_LAUNCH();
+  }
+  return 0;
+}
+
+OXB_API int oxb_paged_attention(const void* q, void* out, const void* kv_data, const float* kv_scales,
+                                const int* block_tables, const int* seq_lens, const int* query_start, int B,
+                                int max_blocks, int nq, int nkv, int hd, int kv_mode, int max_query_len,
+                                int n_cta_splits, int window, float scale, float* ws_o, float* ws_ml,
+                                cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (nq % nkv != 0) return (int)cudaErrorInvalidValue;
+  const int G = nq / nkv;
+  AttnArgs a;
+  a.q = reinterpret_cast<const __nv_bfloat16*>(q);
+  a.out = reinterpret_cast<__nv_bfloat16*>(out);
+  a.kv_data = kv_data;
+  a.kv_scales = kv_scales;
+  a.block_tables = block_tables;
+  a.seq_lens = seq_lens;
+  a.query_start = query_start;
+  a.max_blocks = max_blocks;
+  a.nq = nq;
+  a.nkv = nkv;
+  a.kv_mode = kv_mode;
+  a.n_cta_splits = n_cta_splits < 1 ? 1 : n_cta_splits;
+  a.max_mtiles = (max_query_len * G + 15) / 16;
+  a.window = window;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.ws_o = ws_o;
+  a.ws_ml = ws_ml;
+  if (a.n_cta_splits > 1 && (ws_o == nullptr || ws_ml == nullptr)) return (int)cudaErrorInvalidValue;
+  if (hd == 128) return attn_launch<128>(a, B, G, stream);
+  if (hd == 64) return attn_launch<64>(a, B, G, stream);
+  return (int)cudaErrorInvalidValue;
+}

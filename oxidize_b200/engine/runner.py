@@ -40,8 +40,8 @@ class StagingBuffers:
         self.max_tokens, self.max_seqs, self.max_blocks = max_tokens, max_seqs, max_blocks_per_seq
         T, B, M = max_tokens, max_seqs, max_blocks_per_seq
         sizes = [("token_ids", T), ("positions", T), ("slot_mapping", T), ("query_start", B + 1), ("seq_lens", B),
-                 ("logits_indices", T), ("top_k", B), ("block_tables", B * M)]
-        fsizes = [("temperature", B), ("top_p", B), ("min_p", B), ("random", B)]
+                 ("logits_indices", T), ("top_k", T), ("block_tables", B * M)]
+        fsizes = [("temperature", T), ("top_p", T), ("min_p", T), ("random", T)]
         self.offsets: Dict[str, Tuple[int, int]] = {}
         off = 0
         for name, n in sizes + fsizes:
@@ -183,6 +183,8 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ execution
     def _forward_sample(self, meta: BatchMeta, all_greedy: bool, tie: str):
+        if all_greedy and not self.keep_logits:
+            return self.model.greedy_tokens(meta, self.kv, tie), None
         logits = self.model.forward(meta, self.kv)
         if all_greedy:
             return ops.argmax(logits, tie), logits
@@ -241,12 +243,18 @@ class ModelRunner:
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
             for _ in range(2):
-                ops.argmax(self.model.forward(meta, self.kv), tie)
+                self.model.greedy_tokens(meta, self.kv, tie)
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
+        from ..ops import cuda as opcuda
+
+        n0 = opcuda.launch_count
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            out = ops.argmax(self.model.forward(meta, self.kv), tie)
+            out = self.model.greedy_tokens(meta, self.kv, tie)
+        if not hasattr(self, "launches_per_step"):
+            self.launches_per_step = {}
+        self.launches_per_step[B] = opcuda.launch_count - n0
         self.graphs[B] = g
         self.graph_out[B] = out
         return g

@@ -146,6 +146,39 @@ class Transformer:
             logits = self.comm.all_gather_cat(logits, dim=-1)
         return (logits, hidden) if return_hidden else logits
 
+    def greedy_tokens(self, meta: BatchMeta, kv, tie: str = "lowest") -> torch.Tensor:
+        """Forward + argmax without ever materialising full-vocabulary logits across ranks:
+        each rank takes the argmax of its vocabulary shard and only (value, index) pairs are
+        all-gathered (vocabulary-parallel head, distributed argmax)."""
+        h = self.embed(meta.token_ids)
+        h, residual = self.run_layers(h, None, meta, kv)
+        idx = meta.logits_indices.long()
+        h = h.index_select(0, idx)
+        residual = residual.index_select(0, idx) if residual is not None else None
+        x, _ = ops.add_rmsnorm(h, residual, self.w.out_norm, self.cfg.rms_eps)
+        logits = ops.linear(x, self.w.lm_head).float()
+        sharded = self.w.tp_size > 1 and self.w.lm_head.out_features != self.cfg.vocab_size
+        if not sharded:
+            return ops.argmax(logits, tie)
+        if logits.is_cuda:
+            from ..ops import cuda as opcuda
+
+            val = torch.empty(logits.shape[0], dtype=torch.float32, device=logits.device)
+            loc = opcuda.argmax(logits, tie, out_val=val, index_offset=self.w.vocab_start)
+        else:
+            loc = ops.argmax(logits, tie) + self.w.vocab_start
+            val = logits.gather(1, (loc - self.w.vocab_start).long()[:, None]).squeeze(1)
+        pair = torch.stack([val, loc.view(torch.float32) if loc.dtype == torch.int32 else loc.float()], dim=1)
+        allp = self.comm.all_gather_cat(pair.contiguous(), dim=0).reshape(self.w.tp_size, -1, 2)
+        vals = allp[:, :, 0]
+        ids = allp[:, :, 1].contiguous().view(torch.int32)
+        # shards are in ascending vocabulary order: first max = lowest index, last max = highest
+        if tie == "highest":
+            win = self.w.tp_size - 1 - torch.flip(vals, dims=[0]).argmax(dim=0)
+        else:
+            win = vals.argmax(dim=0)
+        return ids.gather(0, win[None, :]).squeeze(0)
+
     def forward(self, meta: BatchMeta, kv, return_hidden: bool = False, capture: Optional[dict] = None):
         h = self.embed(meta.token_ids)
         h, residual = self.run_layers(h, None, meta, kv, capture=capture)

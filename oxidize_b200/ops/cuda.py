@@ -1,0 +1,318 @@
+"""ctypes bindings to ``liboxb.so`` (the hand-written sm_100a kernels) operating on torch CUDA
+tensors.  Every function launches on the current torch stream, so the calls are captured by
+``torch.cuda.graph`` like any other kernel.  Nothing here falls back to PyTorch math: a missing
+library raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
+LIB_PATH = os.path.join(_CSRC, "liboxb.so")
+
+_lib = None
+_lock = threading.Lock()
+
+QTYPE_CODE = {"F32": 0, "F16": 1, "BF16": 2, "Q8_0": 3, "Q4_0": 4, "Q4_K": 5, "Q5_K": 6, "Q6_K": 7, "NVFP4": 8}
+KV_MODE = {"bf16": 0, "f16": 1, "q8": 2, "q4": 3, "f32": 4}
+
+launch_count = 0  # kernels launched through this module (bench.py reports it)
+
+
+class OxbError(RuntimeError):
+    pass
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                if not os.path.exists(LIB_PATH):
+                    from ..build import build_kernels
+
+                    build_kernels()
+                _lib = ctypes.CDLL(LIB_PATH)
+                _declare(_lib)
+    return _lib
+
+
+def _declare(L) -> None:
+    vp, i32, f32, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
+    L.oxb_version.restype = i32
+    L.oxb_status.argtypes = [ctypes.POINTER(i32), i32]
+    L.oxb_gemm_plan.argtypes = [i32, i32, i32, i32, ctypes.POINTER(i32), ctypes.POINTER(sz), ctypes.POINTER(i32)]
+    L.oxb_gemm_bf16.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, sz, vp, i32, vp]
+    L.oxb_dequant_rows.argtypes = [vp, i32, sz, i32, i32, vp, vp]
+    L.oxb_embed.argtypes = [vp, vp, i32, sz, i32, i32, f32, vp, i32, vp]
+    L.oxb_add_rmsnorm.argtypes = [vp, vp, vp, vp, vp, i32, i32, f32, vp]
+    L.oxb_silu_mul.argtypes = [vp, vp, i32, i32, vp]
+    L.oxb_qk_rope_kvwrite.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, vp, f32, i32, i32, i32, i32, vp, vp, vp, i32,
+                                      i32, vp]
+    L.oxb_argmax.argtypes = [vp, i32, i32, i32, i32, vp, vp, i32, vp]
+    L.oxb_paged_attention.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp,
+                                      vp, vp]
+    for name in dir(L):
+        pass
+
+
+def _check(code: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
+    if code != 0:
+        raise OxbError(f"{what} failed with CUDA error {code}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def status(reset: bool = True) -> Tuple[int, int, int]:
+    """(code, detail, count) of the device status word; code 0 means every bounded wait succeeded."""
+    out = (ctypes.c_int * 4)()
+    _check(lib().oxb_status(out, 1 if reset else 0), "oxb_status")
+    return out[0], out[1], out[2]
+
+
+# --------------------------------------------------------------------------- scratch
+class Scratch:
+    """Per-device scratch owned by the op layer: split-K partials + tickets, split-KV partials,
+    and the bf16 staging used to decode block-quantized weights ahead of the tensor-core GEMM."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.gemm_ws = torch.empty(16 << 20, dtype=torch.float32, device=device)  # 64 MB
+        self.gemm_counters = torch.zeros(8192, dtype=torch.int32, device=device)
+        self.attn_o: Optional[torch.Tensor] = None
+        self.attn_ml: Optional[torch.Tensor] = None
+        self.dequant: Optional[torch.Tensor] = None
+
+    def attn(self, o_floats: int, ml_floats: int):
+        if self.attn_o is None or self.attn_o.numel() < o_floats:
+            self.attn_o = torch.empty(max(o_floats, 1), dtype=torch.float32, device=self.device)
+        if self.attn_ml is None or self.attn_ml.numel() < ml_floats:
+            self.attn_ml = torch.empty(max(ml_floats, 1), dtype=torch.float32, device=self.device)
+        return self.attn_o, self.attn_ml
+
+    def dequant_buf(self, n: int) -> torch.Tensor:
+        if self.dequant is None or self.dequant.numel() < n:
+            self.dequant = torch.empty(n, dtype=torch.bfloat16, device=self.device)
+        return self.dequant
+
+
+_scratch: Dict[int, Scratch] = {}
+
+
+def scratch(device: torch.device) -> Scratch:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    s = _scratch.get(idx)
+    if s is None:
+        s = _scratch[idx] = Scratch(torch.device("cuda", idx))
+    return s
+
+
+# --------------------------------------------------------------------------- GEMM / linear
+def gemm_plan(T: int, N: int, K: int, splits_hint: int = 0):
+    out = (ctypes.c_int * 4)()
+    ws = ctypes.c_size_t()
+    nc = ctypes.c_int()
+    lib().oxb_gemm_plan(T, N, K, splits_hint, out, ctypes.byref(ws), ctypes.byref(nc))
+    return {"tn": out[0], "n_tiles": out[1], "t_tiles": out[2], "splits": out[3], "ws_bytes": ws.value,
+            "n_counters": nc.value}
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+              ld_out: Optional[int] = None, add_into: bool = False, splits: int = 0) -> torch.Tensor:
+    """out[T, N] = x[T, K] @ w[N, K]^T on the tcgen05 kernel; ``out`` may be a column slice of a
+    wider row-major buffer (pass its row stride as ``ld_out``)."""
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
+    T, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+        ld_out = N
+    elif ld_out is None:
+        ld_out = out.stride(0)
+    s = scratch(x.device)
+    _check(lib().oxb_gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), _p(bias), T, N, K, ld_out,
+                               1 if add_into else 0, splits, s.gemm_ws.data_ptr(), s.gemm_ws.numel() * 4,
+                               s.gemm_counters.data_ptr(), s.gemm_counters.numel(), _stream()), "oxb_gemm_bf16")
+    return out
+
+
+def dequant_rows(w, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decode a packed QTensor to a dense bf16 [out, in] matrix on the device."""
+    n, k = w.shape
+    if out is None:
+        out = torch.empty(n, k, dtype=torch.bfloat16, device=w.data.device)
+    _check(lib().oxb_dequant_rows(w.data.data_ptr(), QTYPE_CODE[w.qtype], w.data.stride(0) * w.data.element_size(), n, k,
+                                  out.data_ptr(), _stream()), "oxb_dequant_rows")
+    return out
+
+
+def linear(x: torch.Tensor, parts: Sequence, bias: Optional[torch.Tensor] = None,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if x.dtype != torch.bfloat16:
+        x = x.to(torch.bfloat16)
+    x = x.contiguous()
+    T = x.shape[0]
+    N = sum(p.shape[0] for p in parts)
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+    off = 0
+    for p in parts:
+        n = p.shape[0]
+        b = None if bias is None else bias[off : off + n]
+        view = out[:, off : off + n]
+        if p.qtype == "BF16":
+            gemm_bf16(x, p.data, view, b, ld_out=out.stride(0))
+        elif p.qtype in ("F32", "F16"):
+            if getattr(p, "_bf16", None) is None:
+                p._bf16 = p.data.to(torch.bfloat16).contiguous()
+            gemm_bf16(x, p._bf16, view, b, ld_out=out.stride(0))
+        elif p.qtype == "FP8B":
+            from . import cuda_quant
+
+            cuda_quant.linear_fp8(x, p, view, b, out.stride(0))
+        else:
+            from . import cuda_quant
+
+            cuda_quant.linear_quant(x, p, view, b, out.stride(0))
+        off += n
+    return out
+
+
+# --------------------------------------------------------------------------- glue ops
+def embed(tokens: torch.Tensor, table, dtype: torch.dtype, scale: float = 1.0) -> torch.Tensor:
+    T = tokens.shape[0]
+    V, H = table.shape
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=tokens.device)
+    row_bytes = table.data.stride(0) * table.data.element_size()
+    _check(lib().oxb_embed(tokens.data_ptr(), table.data.data_ptr(), QTYPE_CODE[table.qtype], row_bytes, H, V, scale,
+                           out.data_ptr(), T, _stream()), "oxb_embed")
+    return out if dtype == torch.bfloat16 else out.to(dtype)
+
+
+def add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], w: torch.Tensor, eps: float):
+    """(rmsnorm(x + residual) * w, x + residual); the sum overwrites ``residual`` in place."""
+    T, H = x.shape
+    y = torch.empty_like(x)
+    if residual is None:
+        _check(lib().oxb_add_rmsnorm(x.data_ptr(), None, None, w.data_ptr(), y.data_ptr(), T, H, eps, _stream()),
+               "oxb_add_rmsnorm")
+        return y, x
+    _check(lib().oxb_add_rmsnorm(x.data_ptr(), residual.data_ptr(), residual.data_ptr(), w.data_ptr(), y.data_ptr(),
+                                 T, H, eps, _stream()), "oxb_add_rmsnorm")
+    return y, residual
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    T, I2 = gate_up.shape
+    out = torch.empty(T, I2 // 2, dtype=gate_up.dtype, device=gate_up.device)
+    _check(lib().oxb_silu_mul(gate_up.data_ptr(), out.data_ptr(), T, I2 // 2, _stream()), "oxb_silu_mul")
+    return out
+
+
+def rope_table(rope, max_pos: int) -> torch.Tensor:
+    """[max_pos, rot] fp32: cos at [:, :rot/2], sin at [:, rot/2:], computed in float64."""
+    tab = getattr(rope, "_table", None)
+    if tab is None or tab.shape[0] < max_pos:
+        n = max(max_pos, 32768)
+        pos = torch.arange(n, dtype=torch.float64, device=rope.inv_freq.device)
+        ang = pos[:, None] * rope.inv_freq.double()[None, :]
+        tab = torch.cat([ang.cos() * rope.mscale, ang.sin() * rope.mscale], dim=1).float().contiguous()
+        rope._table = tab
+    return tab
+
+
+def qk_rope_kv_write(qkv, positions, slot_mapping, kv, layer, rope, q_norm=None, k_norm=None, eps=1e-6):
+    T = qkv.shape[0]
+    nq, nkv, hd = rope.n_heads, rope.n_kv_heads, rope.head_dim
+    tab = rope_table(rope, 0)
+    q = torch.empty(T, nq, hd, dtype=torch.bfloat16, device=qkv.device)
+    rot = tab.shape[1]
+    sc = kv.scales[layer]
+    _check(lib().oxb_qk_rope_kvwrite(qkv.data_ptr(), positions.data_ptr(), slot_mapping.data_ptr(), tab.data_ptr(),
+                                     tab.shape[0], rot, 0 if rope.pairing == "split_half" else 1, _p(q_norm),
+                                     _p(k_norm), eps, T, nq, nkv, hd, q.data_ptr(), kv.data[layer].data_ptr(), _p(sc),
+                                     KV_MODE[kv.dtype_name], kv.page_size, _stream()), "oxb_qk_rope_kvwrite")
+    return q
+
+
+_SM_COUNT: Dict[int, int] = {}
+
+
+def sm_count(device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _SM_COUNT[idx]
+
+
+def attn_splits(B: int, nkv: int, mtiles: int, max_seq_len: int, sms: int) -> int:
+    """CTA-level KV splits so that about two CTAs per SM are in flight; each warp of each
+    split should still see a few pages."""
+    base = max(1, B * nkv * mtiles)
+    want = (2 * sms + base - 1) // base
+    pages = max(1, (max_seq_len + 15) // 16)
+    cap = max(1, pages // 8)  # >= 2 pages per warp per split
+    return max(1, min(want, cap, 16))
+
+
+def paged_attention(q, kv, layer, meta, scale, sliding_window=0, splits: Optional[int] = None):
+    T, nq, hd = q.shape
+    nkv = kv.spec.n_kv_heads
+    B = meta.seq_lens.shape[0]
+    G = nq // nkv
+    mtiles = (max(1, meta.max_query_len) * G + 15) // 16
+    if splits is None:
+        splits = attn_splits(B, nkv, mtiles, meta.max_seq_len or kv.page_size, sm_count(q.device))
+    out = torch.empty_like(q)
+    ws_o = ws_ml = None
+    if splits > 1:
+        tasks = B * nkv * mtiles * splits
+        ws_o, ws_ml = scratch(q.device).attn(tasks * 16 * hd, tasks * 32)
+    _check(lib().oxb_paged_attention(q.data_ptr(), out.data_ptr(), kv.data[layer].data_ptr(), _p(kv.scales[layer]),
+                                     meta.block_tables.data_ptr(), meta.seq_lens.data_ptr(), meta.query_start.data_ptr(),
+                                     B, meta.block_tables.stride(0), nq, nkv, hd, KV_MODE[kv.dtype_name],
+                                     max(1, meta.max_query_len), splits, sliding_window, scale, _p(ws_o), _p(ws_ml),
+                                     _stream()), "oxb_paged_attention")
+    return out
+
+
+def argmax(logits: torch.Tensor, tie: str = "lowest", out_val: Optional[torch.Tensor] = None, index_offset: int = 0):
+    assert logits.dtype == torch.float32
+    R, V = logits.shape
+    out = torch.empty(R, dtype=torch.int32, device=logits.device)
+    _check(lib().oxb_argmax(logits.data_ptr(), R, V, logits.stride(0), 1 if tie == "highest" else 0, out.data_ptr(),
+                            _p(out_val), index_offset, _stream()), "oxb_argmax")
+    return out
+
+
+def sample(logits, temperature, top_k, top_p, min_p, random, tie="lowest"):
+    from . import cuda_sampling
+
+    return cuda_sampling.sample(logits, temperature, top_k, top_p, min_p, random, tie)
+
+
+def moe_route(logits, cfg, bias=None):
+    from . import cuda_moe
+
+    return cuda_moe.moe_route(logits, cfg, bias)
+
+
+def moe_experts_forward(x, ids, wts, experts):
+    from . import cuda_moe
+
+    return cuda_moe.moe_experts_forward(x, ids, wts, experts)

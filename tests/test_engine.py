@@ -1,0 +1,365 @@
+"""Block pool, scheduler, sampler and engine-level equivalence properties (CPU only).
+
+The equivalence properties mirror the reference's model tests (model/inference.rs:2759-3268):
+batched == standalone, chunked prefill == one-shot prefill, mid-flight admission == standalone,
+rewind-then-reforward is lossless."""
+import numpy as np
+import pytest
+import torch
+
+from oxidize_b200.engine.kv_pool import BlockPool, KVCache, KVCacheSpec, OutOfBlocks, block_hash
+from oxidize_b200.engine.llm import LLM, EngineConfig
+from oxidize_b200.engine.sampler import (SamplingError, SamplingParams, sample, speculative_accept)
+from oxidize_b200.engine.scheduler import Scheduler, SchedulerConfig, Sequence
+from oxidize_b200.models.config import preset
+from oxidize_b200.utils.synth import synth_gguf, synth_weights
+
+
+# --------------------------------------------------------------------------- block pool
+def test_block_hash_is_fnv_style():
+    h = 0xCBF29CE484222325
+    for t in (1, 2, 3):
+        h = (h * 0x100000001B3) % (1 << 64)
+        h ^= t
+    assert block_hash([1, 2, 3]) == h
+    assert block_hash([3], block_hash([1, 2])) == h
+
+
+def test_pool_alloc_free_refcount():
+    p = BlockPool(4, 16)
+    a, b = p.allocate(), p.allocate()
+    assert (a, b) == (0, 1) and p.num_free == 2
+    p.incref(a)
+    assert p.is_shared(a)
+    p.release(a)
+    assert not p.is_shared(a) and p.num_free == 2
+    p.release(a)
+    assert p.num_free == 3
+    with pytest.raises(RuntimeError):
+        p.release(a)
+    p.allocate(), p.allocate(), p.allocate()
+    with pytest.raises(OutOfBlocks):
+        p.allocate()
+
+
+def test_prefix_cache_hit_and_lru_eviction():
+    p = BlockPool(3, 4)
+    toks = list(range(10))
+    b0, b1 = p.allocate(), p.allocate()
+    h0 = block_hash(toks[:4])
+    h1 = block_hash(toks[4:8], h0)
+    p.publish(b0, h0)
+    p.publish(b1, h1)
+    p.release(b0)
+    p.release(b1)
+    assert p.num_free == 3  # cached blocks stay evictable
+    blocks, covered = p.match_prefix(toks)
+    assert blocks == [b0, b1] and covered == 8 and p.hits == 2
+    p.release_all(blocks)
+    # exhaust: the free block first, then the least recently used cached block
+    got = [p.allocate() for _ in range(3)]
+    assert sorted(got) == [0, 1, 2]
+    assert p.match_prefix(toks) == ([], 0)
+
+
+# --------------------------------------------------------------------------- scheduler
+def _sched(nblocks=64, **kw):
+    pool = BlockPool(nblocks, 16)
+    return Scheduler(SchedulerConfig(**kw), pool), pool
+
+
+def _run(s: Scheduler, steps=1000, tok=7):
+    order = []
+    for _ in range(steps):
+        out = s.schedule()
+        if out.is_empty:
+            break
+        order.append([(ss.seq.seq_id, ss.num_tokens, ss.is_prefill) for ss in out.scheduled])
+        s.postprocess(out, {ss.seq.seq_id: [tok] for ss in out.scheduled if ss.sample})
+    return order
+
+
+def test_decode_first_then_prefill_then_admit():
+    s, _ = _sched(max_num_batched_tokens=20, prefill_chunk_size=16, max_num_running_seqs=8, enable_prefix_cache=False)
+    a = Sequence(list(range(40)), SamplingParams(max_tokens=3))
+    s.add(a)
+    o1 = s.schedule()
+    assert [(x.num_tokens, x.is_prefill, x.sample) for x in o1.scheduled] == [(16, True, False)]
+    s.postprocess(o1, {})
+    b = Sequence(list(range(5)), SamplingParams(max_tokens=3))
+    s.add(b)
+    o2 = s.schedule()
+    # a continues its prefill (16), b is admitted with the 4 tokens of budget left
+    assert [(x.seq is a, x.num_tokens) for x in o2.scheduled] == [(True, 16), (False, 4)]
+    s.postprocess(o2, {})
+    o3 = s.schedule()
+    assert [(x.seq is a, x.num_tokens, x.sample) for x in o3.scheduled] == [(True, 8, True), (False, 1, True)]
+    s.postprocess(o3, {a.seq_id: [1], b.seq_id: [1]})
+    o4 = s.schedule()
+    assert all(not x.is_prefill and x.num_tokens == 1 for x in o4.scheduled) and o4.num_decode_tokens == 2
+
+
+def test_max_running_and_finish_reasons():
+    s, pool = _sched(max_num_batched_tokens=512, prefill_chunk_size=64, max_num_running_seqs=2, enable_prefix_cache=False)
+    seqs = [Sequence([1, 2, 3], SamplingParams(max_tokens=2, stop_token_ids=(9,))) for _ in range(3)]
+    for q in seqs:
+        s.add(q)
+    o = s.schedule()
+    assert len(o.scheduled) == 2 and len(s.waiting) == 1
+    s.postprocess(o, {seqs[0].seq_id: [9], seqs[1].seq_id: [4]})
+    assert seqs[0].finish_reason == "stop" and seqs[0].output == [9]  # the stop token is yielded
+    _run(s)
+    assert [q.finish_reason for q in seqs] == ["stop", "length", "length"]
+    assert pool.num_free == pool.num_blocks
+
+
+def test_eos_and_stop_sequences():
+    s, _ = _sched(enable_prefix_cache=False)
+    a = Sequence([1], SamplingParams(max_tokens=10, stop_sequences=((5, 6),)))
+    b = Sequence([1], SamplingParams(max_tokens=10))
+    c = Sequence([1], SamplingParams(max_tokens=10, ignore_eos=True))
+    for q in (a, b, c):
+        s.add(q)
+    feed = {a.seq_id: [5, 6, 7], b.seq_id: [2, 2, 2], c.seq_id: [2, 2, 2]}
+    for i in range(3):
+        o = s.schedule()
+        s.postprocess(o, {ss.seq.seq_id: [feed[ss.seq.seq_id][i]] for ss in o.scheduled}, eos_token_id=2)
+    assert a.finish_reason == "stop" and a.output == [5, 6]
+    assert b.finish_reason == "stop" and b.output == [2]
+    assert not c.is_finished and c.output == [2, 2, 2]
+
+
+def test_prefix_cache_shares_blocks_and_cow():
+    s, pool = _sched(nblocks=32, max_num_batched_tokens=512, prefill_chunk_size=512)
+    prompt = list(range(100, 140))  # 40 tokens: 2 full blocks + 8
+    a = Sequence(prompt, SamplingParams(max_tokens=2))
+    s.add(a)
+    _run(s)
+    used_after_a = pool.num_used
+    assert used_after_a == 0 and len(pool.cache) == 2
+    b = Sequence(prompt, SamplingParams(max_tokens=2))
+    s.add(b)
+    o = s.schedule()
+    assert b.num_cached_tokens == 32 and o.scheduled[0].start == 32 and o.scheduled[0].num_tokens == 8
+    # identical 32-token prompt: the last cached block may not be fully reused (last token recomputed)
+    c = Sequence(prompt[:32], SamplingParams(max_tokens=2))
+    s.add(c)
+    o2 = s.schedule()
+    sc = [x for x in o2.scheduled if x.seq is c][0]
+    assert c.num_cached_tokens == 16 and sc.start == 16
+
+
+def test_preemption_requeues_front_and_completes():
+    s, pool = _sched(nblocks=6, max_num_batched_tokens=512, prefill_chunk_size=512, max_num_running_seqs=4,
+                     enable_prefix_cache=False)
+    a = Sequence(list(range(30)), SamplingParams(max_tokens=40, ignore_eos=True))
+    b = Sequence(list(range(30)), SamplingParams(max_tokens=40, ignore_eos=True))
+    s.add(a)
+    s.add(b)
+    _run(s, steps=400)
+    assert a.is_finished and b.is_finished and s.num_preemptions >= 1
+    assert len(a.output) + len(getattr(a, "_preempted_outputs", [])) == 40
+    assert len(b.output) + len(getattr(b, "_preempted_outputs", [])) == 40
+    assert pool.num_free == pool.num_blocks
+
+
+def test_too_long_prompt_rejected():
+    s, _ = _sched(nblocks=2)
+    with pytest.raises(OutOfBlocks):
+        s.add(Sequence(list(range(100)), SamplingParams()))
+
+
+def test_sjf_policy_orders_by_job_size():
+    s, _ = _sched(max_num_running_seqs=1, policy="sjf", enable_prefix_cache=False, max_num_batched_tokens=512,
+                  prefill_chunk_size=512)
+    big = Sequence(list(range(50)), SamplingParams(max_tokens=5))
+    small = Sequence(list(range(5)), SamplingParams(max_tokens=5))
+    s.add(big)
+    s.add(small)
+    assert s.schedule().scheduled[0].seq is small
+
+
+# --------------------------------------------------------------------------- sampler
+def test_sampling_validation_and_greedy():
+    logits = np.array([0.1, 3.0, 3.0, -1.0], dtype=np.float32)
+    with pytest.raises(SamplingError):
+        sample(logits, SamplingParams(top_k=0), 0.5)
+    with pytest.raises(SamplingError):
+        sample(logits, SamplingParams(top_p=1.5), 0.5)
+    with pytest.raises(SamplingError):
+        sample(logits, SamplingParams(), 1.0)
+    assert sample(logits, SamplingParams(temperature=0.0), 0.3) == 1
+    assert sample(logits, SamplingParams(temperature=0.0, tie="highest"), 0.3) == 2
+    assert sample(logits, SamplingParams(temperature=1.0, top_k=1), 0.99) == 1
+    assert sample(logits, SamplingParams(temperature=0.0), 0.3, suppressed=[1, 2]) == 0
+
+
+def test_sampling_filters_and_distribution():
+    logits = np.log(np.array([0.5, 0.3, 0.15, 0.05], dtype=np.float64)).astype(np.float32)
+    p = SamplingParams(temperature=1.0, top_p=0.8)
+    draws = {sample(logits, p, r) for r in np.linspace(0, 0.999, 200)}
+    assert draws == {0, 1}  # 0.5 + 0.3 reaches 0.8
+    p = SamplingParams(temperature=1.0, min_p=0.5)
+    assert {sample(logits, p, r) for r in np.linspace(0, 0.999, 50)} == {0, 1}
+    p = SamplingParams(temperature=1.0, top_k=3)
+    assert {sample(logits, p, r) for r in np.linspace(0, 0.999, 200)} == {0, 1, 2}
+    # unfiltered: inverse CDF in index order
+    p = SamplingParams(temperature=1.0)
+    assert sample(logits, p, 0.49) == 0 and sample(logits, p, 0.51) == 1 and sample(logits, p, 0.96) == 3
+    # penalties are additive
+    p = SamplingParams(temperature=0.0, frequency_penalty=2.0)
+    assert sample(np.array([1.0, 0.5], dtype=np.float32), p, 0.1, recent=[0]) == 1
+
+
+def test_speculative_accept_rules():
+    V = 6
+    tl = np.full((4, V), -5.0, dtype=np.float32)
+    tl[0, 2] = tl[1, 3] = tl[2, 1] = tl[3, 4] = 5.0
+    toks, n = speculative_accept([2, 3, 1], None, tl, SamplingParams(temperature=0.0), [])
+    assert (toks, n) == ([2, 3, 1, 4], 3)  # all accepted + bonus
+    toks, n = speculative_accept([2, 0, 1], None, tl, SamplingParams(temperature=0.0), [])
+    assert (toks, n) == ([2, 3], 1)  # first mismatch replaced by the target's token
+    # stochastic: q puts all mass on a token the target dislikes -> reject and resample from max(p-q,0)
+    q = [np.eye(V)[0]]
+    tl2 = np.zeros((2, V), dtype=np.float32)
+    tl2[0, 0] = -50.0
+    toks, n = speculative_accept([0], q, tl2, SamplingParams(temperature=1.0), [0.5, 0.1, 0.2])
+    assert n == 0 and toks[0] != 0
+
+
+def test_device_sampler_matches_host_oracle():
+    from oxidize_b200.engine.device_sampler import sample_torch
+
+    rng = np.random.default_rng(0)
+    R, V = 16, 200
+    logits = torch.from_numpy(rng.standard_normal((R, V)).astype(np.float32) * 3)
+    temps = np.array([0.0, 1.0, 0.7, 1.3] * 4, dtype=np.float32)
+    topk = np.array([0, 0, 5, 50] * 4, dtype=np.int32)
+    topp = np.array([1.0, 0.9, 1.0, 0.5] * 4, dtype=np.float32)
+    minp = np.array([0.0, 0.0, 0.1, 0.0] * 4, dtype=np.float32)
+    rnd = rng.random(R).astype(np.float32) * 0.999
+    got = sample_torch(logits, torch.from_numpy(temps), torch.from_numpy(topk), torch.from_numpy(topp),
+                       torch.from_numpy(minp), torch.from_numpy(rnd)).tolist()
+    for r in range(R):
+        p = SamplingParams(temperature=float(temps[r]), top_k=int(topk[r]) or None,
+                           top_p=float(topp[r]) if topp[r] < 1 else (1.0 if topk[r] or minp[r] else None),
+                           min_p=float(minp[r]) or None)
+        if temps[r] > 0 and not p.has_filters:
+            continue  # the unfiltered oracle path draws in index order, the batched path in sorted order
+        assert got[r] == sample(logits[r].numpy(), p, float(rnd[r])), r
+
+
+# --------------------------------------------------------------------------- engine equivalences
+@pytest.fixture(scope="module")
+def tiny_path(tmp_path_factory):
+    cfg = preset("tiny-llama", n_layers=2, vocab_size=300)
+    p = str(tmp_path_factory.mktemp("m") / "tiny.gguf")
+    synth_gguf(p, cfg, "Q4_K_M", seed=0, norm_jitter=0.05)
+    return p
+
+
+def _gen(path, prompts, sp, **ec):
+    base = dict(max_model_len=256, max_num_seqs=4, num_kv_blocks=96, prefill_chunk_size=16, max_num_batched_tokens=64)
+    base.update(ec)
+    llm = LLM.from_gguf(path, EngineConfig(**base), device="cpu")
+    return [o.token_ids for o in llm.generate(prompts, sp)], llm
+
+
+def test_batched_equals_standalone_and_chunking_is_invisible(tiny_path):
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(3, 300, size=n).tolist() for n in (5, 33, 17, 64)]
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    batched, _ = _gen(tiny_path, prompts, sp)
+    for p, want in zip(prompts, batched):
+        solo, _ = _gen(tiny_path, [p], sp, max_num_seqs=1, prefill_chunk_size=256, max_num_batched_tokens=256,
+                       enable_prefix_cache=False)
+        assert solo[0] == want
+
+
+def test_midflight_admission_equals_standalone(tiny_path):
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    a, b = list(range(10, 40)), list(range(50, 70))
+    solo_a, _ = _gen(tiny_path, [a], sp)
+    solo_b, _ = _gen(tiny_path, [b], sp)
+    llm = LLM.from_gguf(tiny_path, EngineConfig(max_model_len=256, max_num_seqs=4, num_kv_blocks=96,
+                                                prefill_chunk_size=16, max_num_batched_tokens=64), device="cpu")
+    ra = llm.add_request(a, sp)
+    done = {}
+    for i in range(200):
+        if i == 5:
+            rb = llm.add_request(b, sp)
+        for ro in llm.step():
+            if ro.finished:
+                done[ro.request_id] = ro.token_ids
+        if i > 5 and not llm.has_unfinished:
+            break
+    assert done[ra] == solo_a[0] and done[rb] == solo_b[0]
+
+
+def test_prefix_cache_reuse_gives_same_tokens(tiny_path):
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    p = list(range(20, 70))
+    llm = LLM.from_gguf(tiny_path, EngineConfig(max_model_len=256, max_num_seqs=2, num_kv_blocks=64,
+                                                prefill_chunk_size=64, max_num_batched_tokens=128), device="cpu")
+    first = llm.generate([p], sp)[0]
+    second = llm.generate([p], sp)[0]
+    assert second.num_cached_tokens == 48 and second.token_ids == first.token_ids
+
+
+def test_preemption_recompute_is_lossless(tiny_path):
+    sp = SamplingParams(temperature=0.0, max_tokens=30, ignore_eos=True)
+    prompts = [list(range(3, 33)), list(range(40, 70))]
+    want, _ = _gen(tiny_path, prompts, sp)
+    got, llm = _gen(tiny_path, prompts, sp, num_kv_blocks=6, enable_prefix_cache=False)
+    assert llm.scheduler.num_preemptions >= 1
+    assert got == want
+
+
+@pytest.mark.parametrize("kvd", ["f16", "q8", "q4"])
+def test_quantized_kv_cache_close_to_f32(tiny_path, kvd):
+    sp = SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True)
+    p = list(range(5, 45))
+    outs = {}
+    for d in ("f32", kvd):
+        llm = LLM.from_gguf(tiny_path, EngineConfig(max_model_len=128, max_num_seqs=1, num_kv_blocks=16,
+                                                    prefill_chunk_size=16, max_num_batched_tokens=64,
+                                                    kv_cache_dtype=d), device="cpu")
+        llm.runner.keep_logits = True
+        llm.add_request(p, sp)
+        while llm.has_unfinished:
+            llm.step()
+        outs[d] = llm.last_step[1].logits
+    err = float((outs[kvd] - outs["f32"]).norm() / outs["f32"].norm())
+    assert err < {"f16": 1e-3, "q8": 2e-2, "q4": 0.25}[kvd]
+
+
+def test_moe_families_run_and_batch_consistently():
+    sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+    for name, kw in (("mixtral-8x7b", dict(n_experts=4, n_experts_used=2)),
+                     ("qwen3-30b-a3b", dict(n_experts=8, n_experts_used=2)),
+                     ("mixtral-8x7b", dict(arch="deepseek2", n_experts=8, n_experts_used=2, expert_gating="sigmoid",
+                                           expert_group_count=4, expert_group_used_count=2, n_shared_experts=1,
+                                           shared_expert_ffn_size=64, expert_weights_scale=2.5,
+                                           leading_dense_blocks=1))):
+        cfg = preset(name, hidden_size=64, n_layers=2, n_heads=4, n_kv_heads=2, head_dim=16, ffn_size=128,
+                     expert_ffn_size=64, vocab_size=128, **kw)
+        w = synth_weights(cfg, "cpu", "F32", seed=1)
+        ec = EngineConfig(max_model_len=64, max_num_seqs=3, num_kv_blocks=32, prefill_chunk_size=8,
+                          max_num_batched_tokens=32)
+        prompts = [[3, 4, 5, 6, 7, 8, 9, 10, 11], [20, 21, 22]]
+        both = [o.token_ids for o in LLM(w, ec).generate(prompts, sp)]
+        for p, want in zip(prompts, both):
+            assert LLM(w, ec).generate([p], sp)[0].token_ids == want
+
+
+def test_kv_cache_state_roundtrip():
+    spec = KVCacheSpec(2, 2, 32, 16, "q8")
+    kv = KVCache(spec, 8)
+    for d in kv.data:
+        d.random_(0, 255)
+    for s in kv.scales:
+        s.uniform_(0, 1)
+    st = kv.state_dict([1, 5])
+    kv2 = KVCache(spec, 8)
+    kv2.load_state_dict(st, [2, 3])
+    assert torch.equal(kv2.data[1][2], kv.data[1][1]) and torch.equal(kv2.scales[0][3], kv.scales[0][5])

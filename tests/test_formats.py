@@ -1,0 +1,237 @@
+"""GGUF reader/writer, quant oracle, tokenizer and chat-template tests (CPU only)."""
+import os
+import struct
+
+import numpy as np
+import pytest
+
+from oxidize_b200.formats import gguf as G
+from oxidize_b200.formats import tokenizer as T
+from oxidize_b200.quant import ref as Q
+
+FIXTURES = "/root/reference/oxidize-core/tests/fixtures"
+
+
+def _write_small(path, alignment=32):
+    w = G.GGUFWriter(path, arch="llama", alignment=alignment)
+    w.add("llama.block_count", 2, G.GGUFValueType.UINT32)
+    w.add("general.name", "unit")
+    w.add("some.float", 1.5)
+    w.add("some.bool", True)
+    w.add("some.i64", -5, G.GGUFValueType.INT64)
+    w.add("some.arr", [1, 2, 3])
+    w.add("some.strs", ["a", "bc"], G.GGUFValueType.ARRAY, G.GGUFValueType.STRING)
+    x = np.arange(12, dtype=np.float32).reshape(3, 4)
+    w.add_tensor("a.weight", x)
+    q = Q.quantize("Q4_K", np.random.default_rng(0).standard_normal(2 * 256).astype(np.float32))
+    w.add_tensor("b.weight", q, (2, 256), "Q4_K")
+    w.write()
+    return x, q
+
+
+def test_roundtrip(tmp_path):
+    p = str(tmp_path / "m.gguf")
+    x, q = _write_small(p)
+    g = G.load_gguf(p)
+    assert g.version == 3 and g.architecture == "llama" and g.alignment == 32
+    assert g.get("llama.block_count") == 2 and g.get("some.float") == 1.5 and g.get("some.bool") is True
+    assert g.get("some.i64") == -5 and g.get("some.arr") == [1, 2, 3] and g.get("some.strs") == ["a", "bc"]
+    assert g.tensors["a.weight"].shape == (3, 4) and g.tensors["a.weight"].dims == (4, 3)
+    np.testing.assert_array_equal(g.tensor("a.weight"), x)
+    assert g.tensors["b.weight"].type.name == "Q4_K" and g.tensor("b.weight").shape == (2, 144)
+    np.testing.assert_array_equal(g.tensor_bytes("b.weight"), q)
+    for info in g.tensors.values():
+        assert (g.data_offset + info.offset) % 32 == 0
+
+
+def test_custom_alignment(tmp_path):
+    p = str(tmp_path / "m64.gguf")
+    _write_small(p, alignment=64)
+    g = G.load_gguf(p)
+    assert g.alignment == 64 and g.data_offset % 64 == 0
+
+
+def test_pypi_reader_parses_our_file(tmp_path):
+    gguf = pytest.importorskip("gguf")
+    p = str(tmp_path / "m.gguf")
+    x, _ = _write_small(p)
+    r = gguf.GGUFReader(p)
+    names = [t.name for t in r.tensors]
+    assert names == ["a.weight", "b.weight"]
+    np.testing.assert_array_equal(np.asarray(r.tensors[0].data).reshape(3, 4), x)
+
+
+@pytest.mark.skipif(not os.path.isdir(FIXTURES), reason="reference fixtures not mounted")
+def test_reference_fixtures():
+    g = G.load_gguf(os.path.join(FIXTURES, "valid-v3.gguf"))
+    assert g.version == 3
+    for bad in ("invalid-magic.gguf", "invalid-alignment.gguf", "unsupported-version.gguf"):
+        with pytest.raises(G.GGUFError):
+            G.load_gguf(os.path.join(FIXTURES, bad))
+
+
+def test_rejects_malformed():
+    with pytest.raises(G.GGUFError):
+        G.parse_gguf(b"GGML" + b"\0" * 40)
+    with pytest.raises(G.GGUFError):
+        G.parse_gguf(b"GGUF" + struct.pack("<I", 9) + b"\0" * 16)
+    with pytest.raises(G.GGUFError):  # truncated metadata
+        G.parse_gguf(b"GGUF" + struct.pack("<IQQ", 3, 0, 5))
+    # tensor extent beyond the file
+    head = b"GGUF" + struct.pack("<IQQ", 3, 1, 0)
+    name = b"t"
+    head += struct.pack("<Q", 1) + name + struct.pack("<I", 1) + struct.pack("<Q", 1024) + struct.pack("<IQ", 0, 0)
+    with pytest.raises(G.GGUFError):
+        G.parse_gguf(head + b"\0" * 64)
+
+
+def test_fuzz_parser_never_crashes():
+    rng = np.random.default_rng(0)
+    base = bytearray(b"GGUF" + struct.pack("<IQQ", 3, 2, 3) + bytes(rng.integers(0, 256, 200, dtype=np.uint8)))
+    for _ in range(300):
+        b = bytearray(base)
+        for _ in range(4):
+            b[rng.integers(4, len(b))] = rng.integers(0, 256)
+        try:
+            G.parse_gguf(bytes(b))
+        except G.GGUFError:
+            pass
+
+
+def test_split_shards(tmp_path):
+    for i, name in enumerate(["x.weight", "y.weight"], 1):
+        w = G.GGUFWriter(str(tmp_path / f"m-{i:05d}-of-00002.gguf"))
+        w.add_tensor(name, np.full((2, 2), i, dtype=np.float32))
+        w.write()
+    g = G.load_gguf(str(tmp_path / "m-00002-of-00002.gguf"))
+    assert sorted(g.tensors) == ["x.weight", "y.weight"]
+    assert float(g.tensor("y.weight")[0, 0]) == 2.0 and float(g.tensor("x.weight")[0, 0]) == 1.0
+
+
+def test_hf_name_map():
+    assert G.map_hf_tensor_name("model.layers.3.self_attn.q_proj.weight") == ("blk.3.attn_q.weight", None)
+    assert G.map_hf_tensor_name("model.layers.0.mlp.experts.5.down_proj.weight") == ("blk.0.ffn_down_exps.weight", 5)
+    assert G.map_hf_tensor_name("lm_head.weight") == ("output.weight", None)
+    assert G.map_hf_tensor_name("nonsense") is None
+
+
+# --------------------------------------------------------------------------- quant
+@pytest.mark.parametrize("name", ["Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q8_0", "Q2_K", "Q3_K", "Q4_K", "Q5_K", "Q6_K",
+                                  "IQ4_NL", "IQ4_XS"])
+def test_decoders_match_pypi(name):
+    gguf = pytest.importorskip("gguf")
+    t = G.ggml_type(name)
+    rng = np.random.default_rng(1)
+    raw = rng.integers(0, 256, size=t.type_size * 16, dtype=np.uint8)
+    ours = Q.dequantize(name, raw)
+    theirs = gguf.quants.dequantize(raw, getattr(gguf.GGMLQuantizationType, name)).reshape(-1)
+    ok = np.isfinite(theirs)
+    np.testing.assert_allclose(ours[ok], theirs[ok], rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("name,tol", [("Q4_0", 0.12), ("Q5_0", 0.06), ("Q8_0", 0.01), ("Q4_K", 0.1), ("Q6_K", 0.03),
+                                      ("Q8_K", 0.01), ("NVFP4", 0.16), ("BF16", 0.005), ("F16", 0.001)])
+def test_quantize_roundtrip_error(name, tol):
+    x = (np.random.default_rng(2).standard_normal(8192) * 0.02).astype(np.float32)
+    y = Q.dequantize(name, Q.quantize(name, x), x.size)
+    assert np.sqrt(((x - y) ** 2).mean()) / x.std() < tol
+
+
+def test_size_validation():
+    with pytest.raises(G.GGUFError):
+        G.quantized_nbytes(G.ggml_type("Q4_K"), 1408)
+    assert G.quantized_nbytes(G.ggml_type("Q4_K"), 512) == 288
+    assert G.quantized_nbytes(G.ggml_type("NVFP4"), 128) == 72
+    assert G.ggml_type(40).name == "NVFP4" and G.ggml_type(12).name == "Q4_K" and G.ggml_type(14).name == "Q6_K"
+
+
+def test_nvfp4_scale_semantics():
+    assert Q.ue4m3_to_f32(np.array([0x00, 0x7F, 0x38], dtype=np.uint8)).tolist() == [0.0, 0.0, 0.5]
+    # bit 7 ignored by default (Rust decoder), honoured on request (CUDA decoder)
+    assert Q.ue4m3_to_f32(np.array([0xB8], dtype=np.uint8))[0] == 0.5
+    assert Q.ue4m3_to_f32(np.array([0xB8], dtype=np.uint8), honour_sign=True)[0] == -0.5
+
+
+def test_torch_quantizers_decode_with_numpy_oracle():
+    import torch
+
+    from oxidize_b200.quant import torch_quant as TQ
+
+    w = torch.randn(8, 512) * 0.02
+    for name, tol in (("Q8_0", 0.01), ("Q4_K", 0.12), ("Q6_K", 0.03), ("NVFP4", 0.16)):
+        raw = TQ.quantize(name, w).numpy()
+        y = Q.dequantize(name, raw, w.numel()).reshape(8, 512)
+        assert np.sqrt(((w.numpy() - y) ** 2).mean()) / w.numpy().std() < tol, name
+
+
+# --------------------------------------------------------------------------- tokenizer
+def _bpe():
+    b2u = T.gpt2_byte_table()
+    toks = ["<unk>", "<s>", "</s>"] + [b2u[b] for b in range(256)]
+    merges = []
+    for a, b in [("h", "e"), ("l", "l"), ("he", "ll"), ("hell", "o"), ("Ġ", "w")]:
+        toks.append(a + b)
+        merges.append(f"{a} {b}")
+    md = {"tokenizer.ggml.model": "gpt2", "tokenizer.ggml.tokens": toks, "tokenizer.ggml.merges": merges,
+          "tokenizer.ggml.token_type": [3, 3, 3] + [1] * (len(toks) - 3), "tokenizer.ggml.bos_token_id": 1,
+          "tokenizer.ggml.eos_token_id": 2, "tokenizer.ggml.unknown_token_id": 0}
+    return T.load_tokenizer_from_metadata(md)
+
+
+def test_bpe_roundtrip_and_merges():
+    tk = _bpe()
+    ids = tk.encode("hello world")
+    assert tk.tokens[ids[0]] == "hello"
+    assert tk.decode(ids) == "hello world"
+    assert tk.decode(tk.encode("héllo ✓ 日本")) == "héllo ✓ 日本"
+    assert not tk.add_bos_default()
+    assert tk.encode_with_special_tokens("a</s>b")[1] == 2
+    assert tk.encode_with_special_tokens("hi", add_bos=True)[0] == 1
+
+
+def test_streaming_detokenizer_holds_partial_utf8():
+    tk = _bpe()
+    ids = tk.encode("✓!")
+    sd = tk.streaming_detokenizer()
+    pieces = [sd.push(i) for i in ids]
+    assert "".join(pieces) + sd.finish() == "✓!"
+    assert pieces[0] == "" and "�" not in "".join(pieces)
+
+
+def test_heal_tokens():
+    tk = _bpe()
+    b2u = T.gpt2_byte_table()
+    split = [tk.vocab[b2u[ord(c)]] for c in "hello"]
+    assert tk.heal_tokens(split) == tk.encode("hello")
+
+
+def test_sentencepiece_and_wordpiece():
+    toks = ["<unk>", "<s>", "</s>", "▁hello", "▁world", "▁", "h", "e", "l", "o"] + [f"<0x{b:02X}>" for b in range(256)]
+    scores = [0, 0, 0, -1.0, -1.0, -5.0, -6, -6, -6, -6] + [-20.0] * 256
+    md = {"tokenizer.ggml.model": "llama", "tokenizer.ggml.tokens": toks, "tokenizer.ggml.scores": scores,
+          "tokenizer.ggml.bos_token_id": 1, "tokenizer.ggml.eos_token_id": 2, "tokenizer.ggml.unknown_token_id": 0}
+    sp = T.load_tokenizer_from_metadata(md)
+    assert sp.encode("hello world") == [3, 4]
+    assert sp.decode([3, 4]) == "hello world"
+    assert sp.add_bos_default()
+    assert sp.decode(sp.encode("hé")) == "hé"  # byte fallback
+    wp = T.load_tokenizer_from_metadata({"tokenizer.ggml.model": "bert", "tokenizer.ggml.tokens":
+                                         ["[UNK]", "un", "##aff", "##able", "hello"], "tokenizer.ggml.unknown_token_id": 0})
+    assert wp.encode("unaffable hello zzz") == [1, 2, 3, 4, 0]
+    assert wp.decode([1, 2, 3, 4]) == "unaffable hello"
+    with pytest.raises(T.TokenizerError):
+        T.load_tokenizer_from_metadata({"tokenizer.ggml.model": "mystery", "tokenizer.ggml.tokens": ["a"]})
+
+
+def test_chat_templates():
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}]
+    out = T.render_chat_template("{% for m in x %}<|im_start|>...", msgs, True)
+    assert out == "<|im_start|>system\nbe brief<|im_end|>\n<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\n"
+    llama3 = ("{% for message in messages %}{{ '<|start_header_id|>' + message['role'] + '<|end_header_id|>\\n\\n' + "
+              "message['content'] + '<|eot_id|>' }}{% endfor %}{% if add_generation_prompt %}"
+              "{{ '<|start_header_id|>assistant<|end_header_id|>\\n\\n' }}{% endif %}")
+    out = T.render_chat_template(llama3, msgs[1:], True)
+    assert out == "<|start_header_id|>user<|end_header_id|>\n\nhi<|eot_id|><|start_header_id|>assistant<|end_header_id|>\n\n"
+    assert T.render_chat_template(llama3, msgs[1:], False).endswith("<|eot_id|>")
+    assert T.chat_template_from_metadata({}, "qwen3") == T.CHATML_SENTINEL
+    assert T.chat_template_from_metadata({}, "llama") is None
