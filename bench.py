@@ -152,7 +152,7 @@ def main():
     torch.cuda.synchronize()
     load_s = time.time() - t0
 
-    sp = SamplingParams(temperature=0.0, max_tokens=10 ** 9, ignore_eos=True)
+    sp = SamplingParams(temperature=0.0, max_tokens=total_steps + 8, ignore_eos=True)
     ttft_p50 = None
     if args.no_prefill:
         # place every sequence directly in the running state with a random-filled context

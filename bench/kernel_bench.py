@@ -1,0 +1,121 @@
+#!/usr/bin/env python
+"""Micro-benchmarks of the hot kernels on the shapes of the headline config, with roofline
+fractions against the measured peaks in MEASURED_PEAKS.json (fallback 6.65 TB/s, 1.59 PFLOP/s).
+
+    python bench/kernel_bench.py [--what gemm,attn] [--json out.json]
+
+Timing: CUDA events on the launching stream, 5 warm-up launches, then 20 timed launches that
+rotate through enough distinct weight / KV copies to exceed the 126 MB L2.
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+from oxidize_b200.ops import cuda as C  # noqa: E402
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def timeit(fn, n_warm=5, n=20):
+    for i in range(n_warm):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(n):
+        fn(n_warm + i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / n * 1e-3
+
+
+def bench_gemm(rows):
+    hbm, tf, kind = peaks()
+    shapes = [("qkv/tp8", 1280, 8192), ("o/tp8", 8192, 1024), ("gate_up/tp8", 7168, 8192), ("down/tp8", 8192, 3584),
+              ("lm_head/tp8", 16032, 8192)]
+    for name, N, K in shapes:
+        copies = max(2, int(400e6 // (N * K * 2)) + 1)
+        ws = [(torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(copies)]
+        for T in (1, 16, 64, 256, 2048):
+            x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
+            out = torch.empty(T, N, dtype=torch.bfloat16, device="cuda")
+            plan = C.gemm_plan(T, N, K)
+            t = timeit(lambda i: C.gemm_bf16(x, ws[i % copies], out))
+            t_ref = timeit(lambda i: torch.matmul(x, ws[i % copies].t(), out=out))
+            by = (N * K + T * K + T * N) * 2
+            fl = 2.0 * T * N * K
+            roof = max(by / (hbm * 1e9), fl / (tf * 1e12))
+            rows.append({"kernel": "gemm_bf16", "shape": name, "T": T, "N": N, "K": K, "us": t * 1e6,
+                         "cublas_us": t_ref * 1e6, "GBps": by / t / 1e9, "TFLOPs": fl / t / 1e12,
+                         "frac_of_roofline": roof / t, "peaks": kind, "splits": plan["splits"], "tn": plan["tn"]})
+            print(rows[-1], flush=True)
+        del ws
+
+
+class _Meta:
+    pass
+
+
+def bench_attn(rows):
+    from oxidize_b200.engine.kv_pool import KVCache, KVCacheSpec
+
+    hbm, tf, kind = peaks()
+    for (B, ctx, nq, nkv, kvd) in [(64, 1400, 8, 1, "bf16"), (64, 1400, 64, 8, "bf16"), (1, 2048, 8, 1, "bf16"),
+                                   (64, 1400, 8, 1, "q8"), (32, 768, 32, 8, "q8")]:
+        hd, page = 128, 16
+        per = (ctx + page - 1) // page
+        layers = max(2, int(300e6 // (B * per * nkv * 2 * page * hd * 2)) + 1)
+        kv = KVCache(KVCacheSpec(layers, nkv, hd, page, kvd), B * per + 1, "cuda")
+        for d in kv.data:
+            if d.dtype == torch.uint8:
+                d.random_(0, 255)
+            else:
+                d.normal_()
+        for s in kv.scales:
+            if s is not None:
+                s.uniform_(0.001, 0.01)
+        m = _Meta()
+        m.block_tables = (torch.arange(B * per, dtype=torch.int32, device="cuda").view(B, per) + 1).contiguous()
+        m.seq_lens = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+        m.query_start = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+        m.max_query_len, m.max_seq_len = 1, ctx
+        q = torch.randn(B, nq, hd, device="cuda").to(torch.bfloat16)
+        for splits in (None, 1, 2, 4, 8):
+            t = timeit(lambda i: C.paged_attention(q, kv, i % layers, m, hd ** -0.5, 0, splits=splits))
+            eb = {"bf16": 2, "q8": 1 + 4 / 32}[kvd]
+            by = B * ctx * nkv * 2 * hd * eb
+            rows.append({"kernel": "paged_attention_decode", "B": B, "ctx": ctx, "nq": nq, "nkv": nkv, "kv": kvd,
+                         "splits": splits, "us": t * 1e6, "GBps": by / t / 1e9, "frac_of_hbm": by / t / 1e9 / hbm,
+                         "peaks": kind})
+            print(rows[-1], flush=True)
+        del kv
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--what", default="gemm,attn")
+    ap.add_argument("--json", default="")
+    a = ap.parse_args()
+    rows = []
+    if "gemm" in a.what:
+        bench_gemm(rows)
+    if "attn" in a.what:
+        bench_attn(rows)
+    print("status", C.status())
+    if a.json:
+        json.dump(rows, open(a.json, "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -60,13 +60,14 @@ __device__ __forceinline__ void mma_bf16_16816(float* d, const uint32_t* a, uint
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Bring one (K, V) page pair of a kv head into a warp-private stage: 32 rows of HD bf16,
-// row stride HD*2+16 bytes (bank-conflict-free ldmatrix).  Executed by one warp.
+// Bring one (K, V) page pair of a kv head into a warp-private stage with cp.async (one warp).
+// bf16 / f16 pages land as 32 rows of HD 16-bit values with row stride HD*2+16 bytes (bank-
+// conflict-free ldmatrix); q8 / q4 pages land raw: 32 rows of codes, then 32 rows of scales.
 template <int HD>
 __device__ __forceinline__ void load_page(uint8_t* stage, const AttnArgs& a, int blk, int kvh, int lane) {
   constexpr int ROWB = HD * 2 + 16;
   const size_t page_idx = ((size_t)blk * a.nkv + kvh) * 2;  // K page; V page follows
-  if (a.kv_mode == 0) {
+  if (a.kv_mode <= 1) {
     const uint8_t* src = reinterpret_cast<const uint8_t*>(a.kv_data) + page_idx * ATT_PAGE * HD * 2;
     constexpr int CPR = HD * 2 / 16;  // 16-byte chunks per row
 #pragma unroll
@@ -74,37 +75,55 @@ __device__ __forceinline__ void load_page(uint8_t* stage, const AttnArgs& a, int
       const int row = c / CPR, col = c % CPR;
       cp_async16(stage + row * ROWB + col * 16, src + (size_t)c * 16);
     }
-  } else if (a.kv_mode == 1) {
-    const __half* src = reinterpret_cast<const __half*>(a.kv_data) + page_idx * ATT_PAGE * HD;
+  } else {
+    const int rowbytes = a.kv_mode == 2 ? HD : HD / 2;
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(a.kv_data) + page_idx * ATT_PAGE * rowbytes;
+    const uint8_t* sc = reinterpret_cast<const uint8_t*>(a.kv_scales + page_idx * ATT_PAGE * (HD / 32));
+    const int ncode = 32 * rowbytes / 16;
+    for (int c = lane; c < ncode; c += 32) cp_async16(stage + c * 16, src + (size_t)c * 16);
+    constexpr int NSC = 32 * (HD / 32) * 4 / 16;
+    for (int c = lane; c < NSC; c += 32) cp_async16(stage + 32 * rowbytes + c * 16, sc + (size_t)c * 16);
+  }
+}
+
+// f16 pages: convert to bf16 in place.  q8 / q4 pages: decode codes * scale into `dec` (bf16,
+// padded rows).  One warp; the caller synchronises the warp before the tensor-core reads.
+template <int HD>
+__device__ __forceinline__ void decode_page(uint8_t* stage, uint8_t* dec, int kv_mode, int lane) {
+  constexpr int ROWB = HD * 2 + 16;
+  if (kv_mode == 1) {
     for (int c = lane; c < 32 * HD / 2; c += 32) {
       const int row = c / (HD / 2), col = (c % (HD / 2)) * 2;
-      const __half2 h = *reinterpret_cast<const __half2*>(src + (size_t)row * HD + col);
-      const float2 f = __half22float2(h);
-      *reinterpret_cast<uint32_t*>(stage + row * ROWB + col * 2) = pack_bf16x2(f.x, f.y);
+      uint32_t* p = reinterpret_cast<uint32_t*>(stage + row * ROWB + col * 2);
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(p));
+      *p = pack_bf16x2(f.x, f.y);
     }
   } else {
-    const bool q8 = a.kv_mode == 2;
+    const bool q8 = kv_mode == 2;
     const int rowbytes = q8 ? HD : HD / 2;
-    const uint8_t* src = reinterpret_cast<const uint8_t*>(a.kv_data) + page_idx * ATT_PAGE * rowbytes;
-    const float* sc = a.kv_scales + page_idx * ATT_PAGE * (HD / 32);
-    // each lane decodes 4 consecutive channels per step
-    for (int c = lane; c < 32 * HD / 4; c += 32) {
-      const int row = c / (HD / 4), col = (c % (HD / 4)) * 4;
-      const float s = sc[(size_t)row * (HD / 32) + (col >> 5)];
-      float v[4];
+    const float* sc = reinterpret_cast<const float*>(stage + 32 * rowbytes);
+    for (int c = lane; c < 32 * HD / 8; c += 32) {  // 8 channels per step
+      const int row = c / (HD / 8), col = (c % (HD / 8)) * 8;
+      const float s = sc[row * (HD / 32) + (col >> 5)];
+      float v[8];
       if (q8) {
-        const uint32_t w = *reinterpret_cast<const uint32_t*>(src + (size_t)row * rowbytes + col);
+        const uint2 w = *reinterpret_cast<const uint2*>(stage + row * rowbytes + col);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) v[j] = ((float)((w >> (8 * j)) & 0xFF) - 127.f) * s;
+        for (int j = 0; j < 4; ++j) {
+          v[j] = ((float)((w.x >> (8 * j)) & 0xFF) - 127.f) * s;
+          v[4 + j] = ((float)((w.y >> (8 * j)) & 0xFF) - 127.f) * s;
+        }
       } else {
-        const uint16_t w = *reinterpret_cast<const uint16_t*>(src + (size_t)row * rowbytes + (col >> 1));
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(stage + row * rowbytes + (col >> 1));
 #pragma unroll
-        for (int j = 0; j < 4; ++j) v[j] = ((float)((w >> (4 * j)) & 0xF) - 7.f) * s;
+        for (int j = 0; j < 8; ++j) v[j] = ((float)((w >> (4 * j)) & 0xF) - 7.f) * s;
       }
-      uint2 o;
+      uint4 o;
       o.x = pack_bf16x2(v[0], v[1]);
       o.y = pack_bf16x2(v[2], v[3]);
-      *reinterpret_cast<uint2*>(stage + row * ROWB + col * 2) = o;
+      o.z = pack_bf16x2(v[4], v[5]);
+      o.w = pack_bf16x2(v[6], v[7]);
+      *reinterpret_cast<uint4*>(dec + row * ROWB + col * 2) = o;
     }
   }
 }
@@ -172,22 +191,43 @@ paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
 
   uint8_t* my_stage = att_smem + (size_t)warp * ATT_STAGES * STAGE_BYTES;
   const int* bt = a.block_tables + (size_t)b * a.max_blocks;
+  // Page ids of this warp, fetched 32 at a time into registers (two batches held) so that the
+  // block-table load never sits in front of a page load on the critical path.
+  int id_base = 0;
+  int ids_a = (lane < my_pages) ? bt[page_lo + first + lane * stride] : 0;
+  int ids_b = (32 + lane < my_pages) ? bt[page_lo + first + (32 + lane) * stride] : 0;
+  auto page_id = [&](int i) {
+    const int r = i - id_base;
+    const int va = __shfl_sync(0xffffffffu, ids_a, r & 31);
+    const int vb = __shfl_sync(0xffffffffu, ids_b, r & 31);
+    return r < 32 ? va : vb;
+  };
 
   // prologue: fill the ring
 #pragma unroll
   for (int s = 0; s < ATT_STAGES - 1; ++s) {
-    if (s < my_pages) load_page<HD>(my_stage + s * STAGE_BYTES, a, bt[page_lo + first + s * stride], kvh, lane);
+    if (s < my_pages) load_page<HD>(my_stage + s * STAGE_BYTES, a, page_id(s), kvh, lane);
     cp_async_commit();
   }
 
   for (int it = 0; it < my_pages; ++it) {
+    if (it - id_base >= 32) {
+      id_base += 32;
+      ids_a = ids_b;
+      ids_b = (id_base + 32 + lane < my_pages) ? bt[page_lo + first + (id_base + 32 + lane) * stride] : 0;
+    }
     const int nxt = it + ATT_STAGES - 1;
-    if (nxt < my_pages)
-      load_page<HD>(my_stage + (nxt % ATT_STAGES) * STAGE_BYTES, a, bt[page_lo + first + nxt * stride], kvh, lane);
+    if (nxt < my_pages) load_page<HD>(my_stage + (nxt % ATT_STAGES) * STAGE_BYTES, a, page_id(nxt), kvh, lane);
     cp_async_commit();
     cp_async_wait<ATT_STAGES - 1>();
     __syncwarp();
-    const uint8_t* st = my_stage + (it % ATT_STAGES) * STAGE_BYTES;
+    uint8_t* st = my_stage + (it % ATT_STAGES) * STAGE_BYTES;
+    if (a.kv_mode != 0) {
+      uint8_t* dec = att_smem + (size_t)(ATT_WARPS * ATT_STAGES + warp) * STAGE_BYTES;
+      decode_page<HD>(st, dec, a.kv_mode, lane);
+      if (a.kv_mode >= 2) st = dec;
+      __syncwarp();
+    }
     const uint32_t k_base = smem_u32(st), v_base = k_base + 16 * ROWB;
     const int page = page_lo + first + it * stride;
 

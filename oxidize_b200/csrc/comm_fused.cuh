@@ -1,2 +1,169 @@
+// In-kernel collectives over NVLink peer memory, fused into the GEMM epilogue.
+//
+// One-shot all-reduce of a row-parallel GEMM (attn_output, ffn_down): as soon as a CTA has its
+// 128-row × T-token partial tile it pushes the tile (bf16) straight into every peer's symmetric
+// receive buffer with 16-byte P2P stores, raises a per-(source, tile) flag with a system-scope
+// release store, then waits (bounded) for the same tile from every peer and reduces the W
+// partials in fixed rank order — so every rank obtains bit-identical sums, tile by tile, while
+// other CTAs are still in their MMA main loop.  There is no separate collective launch and no
+// host involvement; the reference has nothing comparable (its only collectives are a TCP ring,
+// oxidize-core/src/mesh/ring.rs:245-365).
+//
+// Buffers alternate between two parities per call so that a fast peer, which can be at most
+// one call ahead, never overwrites data or flags that are still being read; the parity comes
+// from a device-side call counter, which keeps CUDA-graph replays consistent across ranks.
+// Plain peer loads/stores only: no multimem and no cluster-scope TMA here.
 #pragma once
 #include "common.cuh"
+
+namespace oxb {
+
+constexpr int AR_MAX_WORLD = 8;
+
+struct ArArgs {
+  int world;                          // 0 = no collective
+  int rank;
+  int t_max, n_max, max_tiles;        // receive buffer geometry
+  unsigned long long timeout_ns;      // bound on the peer-flag wait
+  __nv_bfloat16* data[AR_MAX_WORLD];  // peers' receive buffers [2][world][t_max][n_max]
+  uint32_t* flags[AR_MAX_WORLD];      // peers' flag arrays     [2][world][max_tiles]
+  int* ctrl;                          // local: [0] call counter, [1] CTAs done
+  const __nv_bfloat16* residual;      // optional: added to the reduced sum (local, [T, ldY])
+};
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Executed by the 128 epilogue threads (tid 0..127) of the CTA that holds the finished partial
+// tile in shared memory as bf16 [tn][128] (`stage`).  Pushes, signals, waits, reduces and
+// writes Y.  Returns false if the peer wait timed out (status word set, nothing written).
+__device__ __forceinline__ bool ar_exchange_tile(const ArArgs& ar, const uint8_t* stage, int parity, int tile_id,
+                                                 int n0, int t0, int tmax, int N, __nv_bfloat16* Y, int ldY,
+                                                 const float bias_v, volatile int* abort_flag, int tid) {
+  const int W = ar.world;
+  const int chunk = tid & 15;     // 16-byte chunk inside the 256-byte tile row
+  const int trow = tid >> 4;      // 8 tokens per pass
+  const bool col_ok = n0 + chunk * 8 < N;
+  const size_t slot_elems = (size_t)ar.t_max * ar.n_max;
+  // ---- push my partial to every rank (self last)
+  for (int k = 1; k <= W; ++k) {
+    const int d = (ar.rank + k) % W;
+    __nv_bfloat16* dst = ar.data[d] + ((size_t)parity * W + ar.rank) * slot_elems;
+    if (col_ok) {
+      for (int t = trow; t < tmax; t += 8) {
+        const uint4 v = *reinterpret_cast<const uint4*>(stage + t * 256 + chunk * 16);
+        *reinterpret_cast<uint4*>(dst + (size_t)(t0 + t) * ar.n_max + n0 + chunk * 8) = v;
+      }
+    }
+  }
+  __threadfence_system();
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  // ---- signal: one thread per destination
+  if (tid < W) st_release_sys(ar.flags[tid] + ((size_t)parity * W + ar.rank) * ar.max_tiles + tile_id, 1u);
+  // ---- wait for every source's copy of this tile (bounded)
+  if (tid < W) {
+    uint32_t* f = ar.flags[ar.rank] + ((size_t)parity * W + tid) * ar.max_tiles + tile_id;
+    const unsigned long long t_start = globaltimer_ns();
+    bool got = false;
+    for (unsigned it = 0;; ++it) {
+      if (ld_acquire_sys(f) != 0u) {
+        got = true;
+        break;
+      }
+      if (*abort_flag) break;
+      if ((it & 63) == 63 && globaltimer_ns() - t_start > ar.timeout_ns) break;
+    }
+    if (got) {
+      *f = 0u;  // consumed; the next writer of this flag is two calls away
+    } else if (!*abort_flag) {
+      *abort_flag = 1;
+      oxb_report(OXB_TIMEOUT_PEER_FLAG, tid);
+    }
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  if (*abort_flag) return false;
+  // ---- reduce the W partials in rank order (L2 loads: the lines were written by peers)
+  const __nv_bfloat16* mine = ar.data[ar.rank] + (size_t)parity * W * slot_elems;
+  if (col_ok) {
+    for (int t = trow; t < tmax; t += 8) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = bias_v;
+      for (int s = 0; s < W; ++s) {
+        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(mine + (size_t)s * slot_elems +
+                                                              (size_t)(t0 + t) * ar.n_max + n0 + chunk * 8));
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(u[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+      __nv_bfloat16* out = Y + (size_t)(t0 + t) * ldY + n0 + chunk * 8;
+      if (ar.residual != nullptr) {
+        const uint4 rv = *reinterpret_cast<const uint4*>(ar.residual + (size_t)(t0 + t) * ldY + n0 + chunk * 8);
+        const uint32_t u[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(u[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(out) = o;
+    }
+  }
+  return true;
+}
+
+// Stand-alone one-shot all-reduce of a [T, N] bf16 tensor through the same buffers (used for
+// tensors that do not come out of a GEMM, e.g. the MoE combine): grid = N/128 tiles.
+__global__ void __launch_bounds__(128)
+allreduce_oneshot_kernel(const ArArgs ar, const __nv_bfloat16* __restrict__ X, __nv_bfloat16* __restrict__ Y, int T, int N,
+                         int ld) {
+  extern __shared__ __align__(16) uint8_t ar_stage[];  // [T][256] bytes
+  __shared__ int s_parity, s_abort;
+  const int tid = threadIdx.x;
+  const int n0 = blockIdx.x * 128;
+  if (tid == 0) {
+    s_parity = ar.ctrl[0] & 1;
+    s_abort = 0;
+  }
+  const int chunk = tid & 15, trow = tid >> 4;
+  for (int t = trow; t < T; t += 8) {
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (n0 + chunk * 8 < N) v = *reinterpret_cast<const uint4*>(X + (size_t)t * ld + n0 + chunk * 8);
+    *reinterpret_cast<uint4*>(ar_stage + t * 256 + chunk * 16) = v;
+  }
+  __syncthreads();
+  ar_exchange_tile(ar, ar_stage, s_parity, blockIdx.x, n0, 0, T, N, Y, ld, 0.f, &s_abort, tid);
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const int done = atomicAdd(&ar.ctrl[1], 1);
+    if (done == (int)gridDim.x - 1) {
+      ar.ctrl[1] = 0;
+      __threadfence();
+      ar.ctrl[0] = ar.ctrl[0] + 1;
+    }
+  }
+}
+
+}  // namespace oxb

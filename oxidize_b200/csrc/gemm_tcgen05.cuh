@@ -5,14 +5,15 @@
 // shape and the kernel is a pure weight stream: every CTA pulls 128-row × 64-column weight
 // tiles with TMA (128-byte swizzle) through a deep mbarrier ring, one elected thread issues
 // tcgen05.mma into a TMEM accumulator, and four epilogue warps read it back with tcgen05.ld.
-// Small-N projections are split along K across CTAs so that all 148 SMs stream; the last CTA
-// of a tile (atomic ticket) reduces the fp32 partials in a fixed order, which keeps the
-// result bit-reproducible.
+// Small-N projections are split along K across CTAs so that all 148 SMs stream; the CTAs of a
+// tile meet at an arrive counter and each reduces its own slice of the tile's tokens from the
+// fp32 partials in a fixed split order, which keeps the result bit-reproducible.
 //
 // Replaces the reference's cuBLAS SGEMM / cuBLASLt f16 prefill GEMMs and its f16 GEMV
 // (oxidize-core/src/backends/cuda/gemm.rs:100, oxidize-cpp/src/cuda/gemm.cu:43,141-201).
 #pragma once
 #include "common.cuh"
+#include "comm_fused.cuh"
 
 namespace oxb {
 
@@ -34,11 +35,32 @@ struct GemmTile {
 constexpr int EPI_STORE = 0;      // Y = acc (+bias)
 constexpr int EPI_ADD_INTO = 1;   // Y += acc (residual accumulate, bf16 read-modify-write)
 
+// Sum `splits` fp32 partials for tokens [jb, je) of one tile row: JU tokens x SMAX splits of
+// independent L2 loads are in flight per thread; the adds run in split order (reproducible).
+template <int JU, int SMAX, class Emit>
+__device__ __forceinline__ void splitk_reduce(const float* base, int split_stride, int splits, int jb, int je, Emit emit) {
+  for (int j0 = jb; j0 < je; j0 += JU) {
+    float v[JU][SMAX];
+#pragma unroll
+    for (int u = 0; u < JU; ++u)
+#pragma unroll
+      for (int s = 0; s < SMAX; ++s)
+        v[u][s] = (j0 + u < je && s < splits) ? __ldcg(base + (size_t)s * split_stride + (j0 + u) * GEMM_BM) : 0.f;
+#pragma unroll
+    for (int u = 0; u < JU; ++u) {
+      float acc = 0.f;
+#pragma unroll
+      for (int s = 0; s < SMAX; ++s) acc += v[u][s];
+      if (j0 + u < je) emit(j0 + u, acc);
+    }
+  }
+}
+
 template <int TN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                  __nv_bfloat16* __restrict__ Y, const float* __restrict__ bias, int N, int T, int K, int ldY,
-                 int splits, float* __restrict__ ws, int* __restrict__ counters, int epi_mode) {
+                 int splits, float* __restrict__ ws, int* __restrict__ counters, int epi_mode, const ArArgs ar) {
   using Cfg = GemmTile<TN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -66,7 +88,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     }
     mbar_init(accum, 1);
     *abort_flag = 0;
-    *ticket = 0;
+    ticket[0] = 0;
+    ticket[2] = ar.world > 0 ? (ar.ctrl[0] & 1) : 0;  // buffer parity of this collective call
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -133,13 +156,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     tc_fence_after();
     const float b = (bias != nullptr && n < N) ? bias[n] : 0.f;
     const int tile_id = blockIdx.z * gridDim.x + blockIdx.x;
+    const bool use_ar = ar.world > 0;
     if (ok && splits == 1) {
 #pragma unroll 1
       for (int c = 0; c < TN / 16; ++c) {
         uint32_t r[16];
         tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
         tmem_ld_wait();
-        if (n < N) {
+        if (use_ar) {
+          // stage the bf16 partial tile [token][128 rows] in the (now idle) pipeline memory
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            reinterpret_cast<__nv_bfloat16*>(smem)[(c * 16 + j) * GEMM_BM + row] = __float2bfloat16(__uint_as_float(r[j]));
+        } else if (n < N) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int t = t0 + c * 16 + j;
@@ -152,8 +181,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           }
         }
       }
+      if (use_ar) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        ar_exchange_tile(ar, smem, ticket[2], tile_id, n0, t0, min(TN, T - t0), N, Y, ldY, 0.f, abort_flag,
+                         threadIdx.x - 64);
+      }
     } else if (ok) {
-      // fp32 partial -> workspace [tile][split][token][row]; the last CTA of the tile reduces
+      // fp32 partial -> workspace [tile][split][token][row]
       float* my = ws + ((size_t)tile_id * splits + split) * (size_t)(TN * GEMM_BM);
 #pragma unroll 1
       for (int c = 0; c < TN / 16; ++c) {
@@ -165,22 +199,75 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       }
       __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (threadIdx.x == 64) *ticket = atomicAdd(&counters[tile_id], 1);
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (*ticket == splits - 1) {
+      // All `splits` CTAs of a tile are co-resident (the host keeps the grid within one wave), so
+      // they meet at an arrive counter and then each reduces its own slice of the tile's tokens:
+      // the reduction is spread over the CTAs instead of serialised in the last one to arrive.
+      int* cnt = counters + 2 * tile_id;  // [arrive, depart]
+      if (threadIdx.x == 64) {
+        atomicAdd(&cnt[0], 1);
+        bool met = false;
+        for (unsigned it = 0; it < 20000000u; ++it) {
+          if (*reinterpret_cast<volatile int*>(&cnt[0]) >= splits) {
+            met = true;
+            break;
+          }
+          if (*abort_flag) break;
+          if (it > 64) __nanosleep(32);
+        }
+        if (!met && !*abort_flag) {
+          *abort_flag = 1;
+          oxb_report(OXB_TIMEOUT_SPLITK, tile_id);
+        }
+        ticket[1] = met ? 1 : 0;
         __threadfence();
-        const float* base = ws + (size_t)tile_id * splits * (size_t)(TN * GEMM_BM);
-        const int tmax = min(TN, T - t0);
-        if (n < N) {
-          for (int j = 0; j < tmax; ++j) {
-            float acc = b;
-            for (int s = 0; s < splits; ++s) acc += __ldcg(base + (size_t)s * (TN * GEMM_BM) + j * GEMM_BM + row);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ticket[1] != 0) {
+        const float* base = ws + (size_t)tile_id * splits * (size_t)(TN * GEMM_BM) + row;
+        const int tvalid = min(TN, T - t0);
+        const int chunk = (tvalid + splits - 1) / splits;
+        const int jb = min(tvalid, split * chunk), je = min(tvalid, jb + chunk);
+        __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(smem);
+        auto emit = [&](int j, float acc) {
+          if (use_ar) {
+            stage[(j - jb) * GEMM_BM + row] = __float2bfloat16(acc);
+          } else if (n < N) {
+            acc += b;
             __nv_bfloat16* dst = Y + (size_t)(t0 + j) * ldY + n;
             if (epi_mode == EPI_ADD_INTO) acc += __bfloat162float(*dst);
             *dst = __float2bfloat16(acc);
           }
+        };
+        if (splits <= 4) {
+          splitk_reduce<8, 4>(base, TN * GEMM_BM, splits, jb, je, emit);
+        } else if (splits <= 8) {
+          splitk_reduce<4, 8>(base, TN * GEMM_BM, splits, jb, je, emit);
+        } else {
+          splitk_reduce<2, 16>(base, TN * GEMM_BM, splits, jb, je, emit);
         }
-        if (threadIdx.x == 64) counters[tile_id] = 0;  // ready for the next launch / graph replay
+        if (use_ar) {
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (je > jb)
+            ar_exchange_tile(ar, smem, ticket[2], tile_id * splits + split, n0, t0 + jb, je - jb, N, Y, ldY, 0.f,
+                             abort_flag, threadIdx.x - 64);
+        }
+        // the last CTA to leave re-arms the counters for the next launch / graph replay
+        if (threadIdx.x == 64) {
+          if (atomicAdd(&cnt[1], 1) == splits - 1) {
+            cnt[1] = 0;
+            cnt[0] = 0;
+          }
+        }
+      }
+    }
+    if (use_ar && threadIdx.x == 64) {
+      // the last CTA of the grid advances the call counter (flips the buffer parity)
+      __threadfence();
+      const int done = atomicAdd(&ar.ctrl[1], 1);
+      if (done == (int)(gridDim.x * gridDim.y * gridDim.z) - 1) {
+        ar.ctrl[1] = 0;
+        __threadfence();
+        ar.ctrl[0] = ar.ctrl[0] + 1;
       }
     }
   }
@@ -221,13 +308,14 @@ inline GemmPlan gemm_plan(int T, int N, int K, int splits_hint, int sm_count) {
   if (splits > kb_total) splits = kb_total;
   p.splits = splits;
   p.ws_bytes = splits > 1 ? (size_t)p.n_tiles * p.t_tiles * splits * p.tn * GEMM_BM * sizeof(float) : 0;
-  p.n_counters = p.n_tiles * p.t_tiles;
+  p.n_counters = 2 * p.n_tiles * p.t_tiles;
   return p;
 }
 
 template <int TN>
 int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y, const float* bias, int N, int T, int K,
-                int ldY, const GemmPlan& p, float* ws, int* counters, int epi_mode, cudaStream_t stream) {
+                int ldY, const GemmPlan& p, float* ws, int* counters, int epi_mode, const ArArgs& ar,
+                cudaStream_t stream) {
   using Cfg = GemmTile<TN>;
   static bool configured = false;
   if (!configured) {
@@ -237,7 +325,7 @@ int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y
   }
   dim3 grid(p.n_tiles, p.splits, p.t_tiles);
   gemm_bf16_kernel<TN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmW, tmX, Y, bias, N, T, K, ldY, p.splits, ws,
-                                                                        counters, epi_mode);
+                                                                        counters, epi_mode, ar);
   OXB_CHECK_LAUNCH();
   return 0;
 }

@@ -9,7 +9,6 @@
 #include "sampling.cuh"
 #include "gemv_quant.cuh"
 #include "comm_fused.cuh"
-
 using namespace oxb;
 
 // ----------------------------------------------------------------------------- host utilities
@@ -85,7 +84,9 @@ OXB_API int oxb_gemm_bf16(const void* X, const void* W, void* Y, const float* bi
   if (T <= 0 || N <= 0 || K <= 0) return 0;
   if (K % 8 != 0) return (int)cudaErrorInvalidValue;  // TMA rows must be 16-byte multiples
   GemmPlan p = gemm_plan(T, N, K, splits_hint, sm_count());
-  while (p.splits > 1 && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || ws == nullptr || counters == nullptr))
+  // split-K CTAs of a tile wait for one another, so the whole grid has to fit in one wave
+  while (p.splits > 1 && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || ws == nullptr || counters == nullptr ||
+                          p.n_tiles * p.t_tiles * p.splits > sm_count()))
     p = gemm_plan(T, N, K, p.splits - 1, sm_count());
   CUtensorMap tmW, tmX;
   int e = oxb_make_tmap_2d(&tmW, W, N, K, (uint64_t)K * 2, GEMM_BM, GEMM_BK, 2);
@@ -94,13 +95,95 @@ OXB_API int oxb_gemm_bf16(const void* X, const void* W, void* Y, const float* bi
   if (e) return e;
   __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(Y);
   float* wsf = reinterpret_cast<float*>(ws);
+  ArArgs ar;
+  memset(&ar, 0, sizeof(ar));
   switch (p.tn) {
-    case 16: return gemm_launch<16>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, stream);
-    case 32: return gemm_launch<32>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, stream);
-    case 64: return gemm_launch<64>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, stream);
-    case 128: return gemm_launch<128>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, stream);
-    default: return gemm_launch<256>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, stream);
+    case 16: return gemm_launch<16>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream);
+    case 32: return gemm_launch<32>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream);
+    case 64: return gemm_launch<64>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream);
+    case 128: return gemm_launch<128>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream);
+    default: return gemm_launch<256>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream);
   }
+}
+
+static int fill_ar(ArArgs& ar, int world, int rank, const uint64_t* data_ptrs, const uint64_t* flag_ptrs, int* ctrl,
+                   int t_max, int n_max, int max_tiles, unsigned long long timeout_ns, const void* residual) {
+  memset(&ar, 0, sizeof(ar));
+  if (world < 1 || world > AR_MAX_WORLD || rank < 0 || rank >= world || ctrl == nullptr) return (int)cudaErrorInvalidValue;
+  ar.world = world;
+  ar.rank = rank;
+  ar.t_max = t_max;
+  ar.n_max = n_max;
+  ar.max_tiles = max_tiles;
+  ar.timeout_ns = timeout_ns;
+  ar.ctrl = ctrl;
+  ar.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  for (int i = 0; i < world; ++i) {
+    ar.data[i] = reinterpret_cast<__nv_bfloat16*>(data_ptrs[i]);
+    ar.flags[i] = reinterpret_cast<uint32_t*>(flag_ptrs[i]);
+  }
+  return 0;
+}
+
+// Row-parallel GEMM fused with a one-shot all-reduce over peer memory:
+//   Y[T, N] = sum over ranks of X_r[T, K_r] · W_r[N, K_r]^T  (+ residual), identical on every rank.
+// data_ptrs / flag_ptrs: every rank's symmetric receive buffer [2][world][t_max][n_max] bf16 and flag
+// array [2][world][max_tiles] u32 (zeroed once); ctrl: 2 local ints, zeroed once.
+// Limits: T <= min(t_max, 256), N <= n_max, N % 8 == 0, N/128 <= max_tiles, and the whole grid must be
+// co-resident (<= SM count) because CTAs wait on their peers' copies of the same tile.
+OXB_API int oxb_gemm_ar(const void* X, const void* W, void* Y, const void* residual, int T, int N, int K, int ldY,
+                        int world, int rank, const uint64_t* data_ptrs, const uint64_t* flag_ptrs, int* ctrl, int t_max,
+                        int n_max, int max_tiles, unsigned long long timeout_ns, void* ws, size_t ws_bytes, int* counters,
+                        int n_counters, cudaStream_t stream) {
+  if (T <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % 8 != 0 || N % 8 != 0 || T > 256 || T > t_max || N > n_max) return (int)cudaErrorInvalidValue;
+  GemmPlan p = gemm_plan(T, N, K, 0, sm_count());
+  while (p.splits > 1 && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || ws == nullptr || counters == nullptr ||
+                          p.n_tiles * p.splits > sm_count()))
+    p = gemm_plan(T, N, K, p.splits - 1, sm_count());
+  if (p.n_tiles * p.splits > max_tiles || p.n_tiles * p.splits * p.t_tiles > sm_count() || p.t_tiles != 1)
+    return (int)cudaErrorInvalidConfiguration;
+  ArArgs ar;
+  int e = fill_ar(ar, world, rank, data_ptrs, flag_ptrs, ctrl, t_max, n_max, max_tiles, timeout_ns, residual);
+  if (e) return e;
+  CUtensorMap tmW, tmX;
+  e = oxb_make_tmap_2d(&tmW, W, N, K, (uint64_t)K * 2, GEMM_BM, GEMM_BK, 2);
+  if (e) return e;
+  e = oxb_make_tmap_2d(&tmX, X, T, K, (uint64_t)K * 2, p.tn, GEMM_BK, 2);
+  if (e) return e;
+  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(Y);
+  float* wsf = reinterpret_cast<float*>(ws);
+  switch (p.tn) {
+    case 16: return gemm_launch<16>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream);
+    case 32: return gemm_launch<32>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream);
+    case 64: return gemm_launch<64>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream);
+    case 128: return gemm_launch<128>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream);
+    default: return gemm_launch<256>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream);
+  }
+}
+
+// One-shot all-reduce (sum) of X[T, N] bf16 (row stride ld) into Y through the same symmetric buffers.
+OXB_API int oxb_allreduce_oneshot(const void* X, void* Y, int T, int N, int ld, int world, int rank,
+                                  const uint64_t* data_ptrs, const uint64_t* flag_ptrs, int* ctrl, int t_max, int n_max,
+                                  int max_tiles, unsigned long long timeout_ns, cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return 0;
+  const int tiles = (N + 127) / 128;
+  if (N % 8 != 0 || T > t_max || N > n_max || tiles > max_tiles || tiles > sm_count() * 4 || T * 256 > 200 * 1024)
+    return (int)cudaErrorInvalidValue;
+  ArArgs ar;
+  int e = fill_ar(ar, world, rank, data_ptrs, flag_ptrs, ctrl, t_max, n_max, max_tiles, timeout_ns, nullptr);
+  if (e) return e;
+  const size_t smem = (size_t)T * 256;
+  static size_t configured = 48 * 1024;
+  if (smem > configured) {
+    cudaError_t ce = cudaFuncSetAttribute(allreduce_oneshot_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (ce != cudaSuccess) return (int)ce;
+    configured = smem;
+  }
+  allreduce_oneshot_kernel<<<tiles, 128, smem, stream>>>(ar, reinterpret_cast<const __nv_bfloat16*>(X),
+                                                         reinterpret_cast<__nv_bfloat16*>(Y), T, N, ld);
+  OXB_CHECK_LAUNCH();
+  return 0;
 }
 
 // ----------------------------------------------------------------------------- dequant / embed / norms
@@ -195,15 +278,18 @@ OXB_API int oxb_attn_ws_floats(int B, int nkv, int max_mtiles, int n_cta_splits,
 
 template <int HD>
 static int attn_launch(const AttnArgs& a, int B, int G, cudaStream_t stream) {
-  constexpr int SMEM = ATT_WARPS * ATT_STAGES * 32 * (HD * 2 + 16);
+  constexpr int STAGE = 32 * (HD * 2 + 16);
+  constexpr int SMEM_MAX = ATT_WARPS * (ATT_STAGES + 1) * STAGE;
+  // quantized KV needs one extra decode buffer per warp
+  const int smem = ATT_WARPS * (ATT_STAGES + (a.kv_mode >= 2 ? 1 : 0)) * STAGE;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(paged_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaError_t e = cudaFuncSetAttribute(paged_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_MAX);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   dim3 grid(a.max_mtiles * a.n_cta_splits, a.nkv, B);
-  paged_attention_kernel<HD><<<grid, ATT_WARPS * 32, SMEM, stream>>>(a, G);
+  paged_attention_kernel<HD><<<grid, ATT_WARPS * 32, smem, stream>>>(a, G);
   OXB_CHECK_LAUNCH();
   if (a.n_cta_splits > 1) {
     dim3 mg(a.max_mtiles, a.nkv, B);

@@ -65,6 +65,10 @@ class SingleRankComm:
     def all_gather_cat(self, x, dim=-1):
         return x
 
+    def linear_allreduce(self, x, w, residual=None):
+        out = ops.linear(x, w)
+        return out if residual is None else out + residual
+
 
 class Transformer:
     def __init__(self, weights: ModelWeights, comm=None, act_dtype: Optional[torch.dtype] = None):
@@ -91,13 +95,11 @@ class Transformer:
         q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, self.rope,
                                  lw.q_norm, lw.k_norm, cfg.rms_eps)
         attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, cfg.sliding_window)
-        out = ops.linear(attn.reshape(attn.shape[0], -1), lw.wo)
-        return self.comm.all_reduce(out)
+        return self.comm.linear_allreduce(attn.reshape(attn.shape[0], -1), lw.wo)
 
     def _dense_ffn(self, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
         gu = ops.linear(x, lw.w_gate_up)
-        out = ops.linear(ops.silu_mul(gu), lw.w_down)
-        return self.comm.all_reduce(out)
+        return self.comm.linear_allreduce(ops.silu_mul(gu), lw.w_down)
 
     def _moe_ffn(self, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
         """Experts are partitioned across ranks (EP); tokens are replicated after the

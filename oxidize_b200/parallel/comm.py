@@ -70,12 +70,20 @@ class TorchComm:
             self.num_collectives += 1
         return x
 
+    def linear_allreduce(self, x: torch.Tensor, w, residual=None) -> torch.Tensor:
+        """Row-parallel projection: local GEMM, then the all-reduce as a separate collective."""
+        from .. import ops
+
+        out = self.all_reduce(ops.linear(x, w))
+        return out if residual is None else out + residual
+
     def all_gather_cat(self, x: torch.Tensor, dim: int = -1) -> torch.Tensor:
         if self.size == 1:
             return x
         x = x.contiguous()
-        out = torch.empty((self.size,) + tuple(x.shape), dtype=x.dtype, device=x.device)
-        dist.all_gather_into_tensor(out, x, group=self.group)
+        flat = torch.empty((self.size * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(flat, x, group=self.group)
+        out = flat.view((self.size,) + tuple(x.shape))
         self.num_collectives += 1
         if dim in (-1, x.dim() - 1):
             return out.movedim(0, -2).reshape(*x.shape[:-1], self.size * x.shape[-1])

@@ -1,0 +1,193 @@
+"""Child process of the multi-rank tests (launched with torch.distributed.run).
+
+    python -m torch.distributed.run --nproc-per-node N tests/mp_worker.py <case> [--device cpu|cuda]
+
+Every case prints ``RANK r OK <case>`` on success and exits non-zero on failure.
+"""
+import argparse
+import os
+import sys
+import tempfile
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from oxidize_b200.engine.llm import LLM, EngineConfig  # noqa: E402
+from oxidize_b200.engine.sampler import SamplingParams  # noqa: E402
+from oxidize_b200.formats.gguf import load_gguf  # noqa: E402
+from oxidize_b200.models.config import config_from_gguf, preset  # noqa: E402
+from oxidize_b200.models.weights import load_weights  # noqa: E402
+from oxidize_b200.parallel.comm import TorchComm, init_distributed  # noqa: E402
+from oxidize_b200.utils.synth import synth_gguf  # noqa: E402
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).norm() / (b.norm() + 1e-12))
+
+
+def make_comm(kind, dev):
+    if kind == "fused":
+        from oxidize_b200.parallel.fused import FusedComm
+
+        return FusedComm(dev, max_tokens=256, hidden=8192)
+    return TorchComm()
+
+
+def case_gemm_ar(dev, comm_kind):
+    from oxidize_b200.models.weights import LinearWeight, QTensor
+    from oxidize_b200.ops import cuda as C
+
+    comm = make_comm("fused", dev)
+    W, rank = comm.size, comm.rank
+    for (T, N, K) in [(64, 8192, 1024), (64, 8192, 3584), (1, 1024, 512), (200, 2048, 256), (16, 4096, 1792)]:
+        for rep in range(3):
+            g = torch.Generator(device=dev)
+            g.manual_seed(1000 * rank + 17 * rep + T)
+            x = torch.randn(T, K, device=dev, generator=g).to(torch.bfloat16)
+            w = (torch.randn(N, K, device=dev, generator=g) * 0.03).to(torch.bfloat16)
+            res = torch.randn(T, N, device=dev, generator=g).to(torch.bfloat16) if rep == 2 else None
+            y = comm.linear_allreduce(x, LinearWeight([QTensor("BF16", w, (N, K))]), res)
+            part = x.float() @ w.float().t()
+            dist.all_reduce(part)
+            if res is not None:
+                part = part + res.float()
+            torch.cuda.synchronize()
+            assert rel_err(y, part) < 1e-2, (T, N, K, rep, rel_err(y, part))
+            allb = [torch.empty_like(y) for _ in range(W)]
+            dist.all_gather(allb, y.contiguous())
+            if res is None:
+                assert all(torch.equal(allb[0], t) for t in allb), "ranks disagree bitwise"
+    assert comm.fused_calls > 0
+    # stand-alone one-shot all-reduce
+    for T, N in [(64, 8192), (3, 1024), (256, 4096)]:
+        x = torch.randn(T, N, device=dev).to(torch.bfloat16)
+        want = x.float().clone()
+        dist.all_reduce(want)
+        got = comm.all_reduce(x.clone())
+        assert rel_err(got, want) < 1e-2
+    code, detail, count = C.status()
+    assert code == 0, (code, detail, count)
+
+
+def _tiny_file(rank):
+    path = os.path.join(tempfile.gettempdir(), f"oxb_tp_tiny_{os.environ.get('MASTER_PORT', '0')}.gguf")
+    if rank == 0:
+        cfg = preset("tiny-llama", n_layers=2, vocab_size=512, n_heads=8, n_kv_heads=2)
+        synth_gguf(path, cfg, "BF16", seed=0, norm_jitter=0.1)
+    dist.barrier()
+    return path
+
+
+def case_tp_model(dev, comm_kind):
+    layout = init_distributed()
+    path = _tiny_file(layout.rank)
+    g = load_gguf(path)
+    cfg = config_from_gguf(g)
+    act = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    ec = dict(max_model_len=128, max_num_seqs=4, num_kv_blocks=64, prefill_chunk_size=32, max_num_batched_tokens=64,
+              cuda_graphs=False)
+    comm = make_comm(comm_kind, dev) if dev.type == "cuda" else TorchComm()
+    w_tp = load_weights(g, cfg, dev, act, layout.rank, layout.world_size)
+    w_1 = load_weights(g, cfg, dev, act, 0, 1)
+    tp = LLM(w_tp, EngineConfig(tp_size=layout.world_size, **ec), comm)
+    one = LLM(w_1, EngineConfig(**ec))
+    tp.runner.keep_logits = one.runner.keep_logits = True
+    sp = SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True)
+    for p in ([5, 9, 200, 31, 7], list(range(3, 40))):
+        tp.add_request(p, sp)
+        one.add_request(p, sp)
+    while tp.has_unfinished:
+        tp.step()
+        one.step()
+        a, b = tp.last_step[1].logits, one.last_step[1].logits
+        tol = 3e-2 if dev.type == "cuda" else 1e-4
+        assert a.shape == b.shape and rel_err(a, b) < tol, rel_err(a, b)
+    # greedy generation: identical tokens on every rank (distributed argmax over vocabulary shards)
+    tp.runner.keep_logits = False
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    outs = tp.generate([[4, 8, 15, 16, 23, 42]], sp)
+    toks = torch.tensor(outs[0].token_ids, dtype=torch.int64, device=dev)
+    gathered = [torch.empty_like(toks) for _ in range(layout.world_size)]
+    dist.all_gather(gathered, toks)
+    assert all(torch.equal(gathered[0], t) for t in gathered)
+    if dev.type == "cuda":
+        from oxidize_b200.ops import cuda as C
+
+        assert C.status()[0] == 0
+        if comm_kind == "fused":
+            assert comm.fused_calls > 0
+
+
+def case_tp_graph(dev, comm_kind):
+    """Decode under CUDA graphs with the fused collectives gives the same tokens as eager."""
+    layout = init_distributed()
+    path = _tiny_file(layout.rank)
+    g = load_gguf(path)
+    cfg = config_from_gguf(g)
+    comm = make_comm(comm_kind, dev)
+    w_tp = load_weights(g, cfg, dev, torch.bfloat16, layout.rank, layout.world_size)
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    prompts = [[4, 8, 15, 16, 23, 42], list(range(50, 75)), [7, 7, 7]]
+    res = []
+    for graphs in (False, True):
+        llm = LLM(w_tp, EngineConfig(tp_size=layout.world_size, max_model_len=128, max_num_seqs=4, num_kv_blocks=64,
+                                     prefill_chunk_size=32, max_num_batched_tokens=64, cuda_graphs=graphs), comm)
+        res.append([o.token_ids for o in llm.generate(prompts, sp)])
+    assert res[0] == res[1], (res[0], res[1])
+    from oxidize_b200.ops import cuda as C
+
+    assert C.status()[0] == 0
+
+
+def case_rank_exit(dev, comm_kind):
+    """A rank that leaves between steps is noticed on the host (store heartbeat) before the
+    survivors launch their next collective."""
+    from oxidize_b200.parallel.health import Heartbeat
+
+    layout = init_distributed()
+    hb = Heartbeat.from_env(layout.rank, layout.world_size, interval_s=0.05, stale_after_s=0.5)
+    hb.start()
+    x = torch.ones(4, device=dev)
+    dist.all_reduce(x)
+    if dev.type == "cuda":
+        torch.cuda.synchronize()
+    if layout.rank == layout.world_size - 1:
+        hb.stop(announce_exit=True)
+        return
+    import time
+
+    deadline = time.time() + 10
+    while time.time() < deadline and not hb.dead_ranks():
+        time.sleep(0.05)
+    assert hb.dead_ranks() == [layout.world_size - 1], hb.dead_ranks()
+    hb.stop()
+
+
+CASES = {"gemm_ar": case_gemm_ar, "tp_model": case_tp_model, "tp_graph": case_tp_graph, "rank_exit": case_rank_exit}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case")
+    ap.add_argument("--device", default="cuda")
+    ap.add_argument("--comm", default="fused")
+    a = ap.parse_args()
+    layout = init_distributed("gloo" if a.device == "cpu" else None, timeout_s=120)
+    if a.device == "cuda":
+        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        torch.cuda.set_device(dev)
+    else:
+        dev = torch.device("cpu")
+    CASES[a.case](dev, a.comm)
+    print(f"RANK {layout.rank} OK {a.case}", flush=True)
+    if a.case != "rank_exit":
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -98,8 +98,8 @@ def test_embed_and_dequant(C, qtype):
         t = ggml_type("Q5_K")
         rng = np.random.default_rng(0)
         raw = rng.integers(0, 256, size=(V, H // 256, t.type_size), dtype=np.uint8)
-        raw[:, :, 0:2] = np.float16(0.01).view(np.uint8).reshape(1, 1, 2)
-        raw[:, :, 2:4] = np.float16(0.02).view(np.uint8).reshape(1, 1, 2)
+        raw[:, :, 0:2] = np.array([0.01], dtype=np.float16).view(np.uint8).reshape(1, 1, 2)
+        raw[:, :, 2:4] = np.array([0.02], dtype=np.float16).view(np.uint8).reshape(1, 1, 2)
         tab = QTensor("Q5_K", torch.from_numpy(raw.reshape(V, -1)).cuda(), (V, H))
     else:
         tab = qtensor_from_dense(dense, qtype, device="cuda")
