@@ -1,0 +1,208 @@
+"""Background engine thread for serving: one thread owns the ``LLM`` and all mutable serving
+state; HTTP handlers talk to it through queues.
+
+Role of the reference's ``BatchedEngineHandle`` / ``engine_loop``
+(``oxidize-server/src/runtime/batched_engine.rs:45-284``): submit over a channel, one batched
+forward per iteration over all active sequences, per-token routing to the caller, cancellation
+when the caller's channel is closed (``:194-218``), and — after a failed forward — every
+in-flight request is answered with an error and the engine keeps serving (``:266-284``).
+"""
+from __future__ import annotations
+
+import asyncio
+import queue
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Sequence
+
+from ..parallel.health import RunnerStatus, StepWatchdog
+from .llm import LLM, RequestOutput
+from .sampler import SamplingParams
+
+
+@dataclass
+class StreamEvent:
+    request_id: str
+    new_token_ids: List[int]
+    text_delta: str
+    finished: bool
+    finish_reason: Optional[str] = None
+    error: Optional[str] = None
+    prompt_tokens: int = 0
+    completion_tokens: int = 0
+    queue_wait_s: float = 0.0
+
+
+@dataclass
+class _Pending:
+    request_id: str
+    prompt: Any
+    params: SamplingParams
+    sink: Callable[[StreamEvent], None]
+    submitted: float = field(default_factory=time.perf_counter)
+    suppressed: Sequence[int] = ()
+
+
+class AsyncEngine:
+    def __init__(self, llm: LLM, step_deadline_s: float = 60.0, name: str = "oxidize-batch-engine"):
+        self.llm = llm
+        self._inbox: "queue.Queue[Any]" = queue.Queue()
+        self._sinks: Dict[str, Callable[[StreamEvent], None]] = {}
+        self._detok: Dict[str, Any] = {}
+        self._sent: Dict[str, int] = {}
+        self._meta: Dict[str, _Pending] = {}
+        self._stop = threading.Event()
+        self.watchdog = StepWatchdog(step_deadline_s)
+        self.failures = 0
+        self.tokens_generated = 0
+        self.prompt_tokens = 0
+        self._ids = 0
+        self._lock = threading.Lock()
+        self._thread = threading.Thread(target=self._loop, name=name, daemon=True)
+        self._thread.start()
+
+    # ------------------------------------------------------------------ caller side
+    def next_id(self, prefix: str = "req") -> str:
+        with self._lock:
+            self._ids += 1
+            return f"{prefix}-{self._ids}"
+
+    def submit(self, prompt, params: SamplingParams, sink: Callable[[StreamEvent], None],
+               request_id: Optional[str] = None) -> str:
+        rid = request_id or self.next_id()
+        self._inbox.put(_Pending(rid, prompt, params, sink))
+        return rid
+
+    def cancel(self, request_id: str) -> None:
+        self._inbox.put(("cancel", request_id))
+
+    @property
+    def healthy(self) -> bool:
+        return self.watchdog.healthy and self._thread.is_alive()
+
+    @property
+    def queue_depth(self) -> int:
+        return self._inbox.qsize() + len(self.llm.scheduler.waiting)
+
+    def shutdown(self, timeout: float = 5.0) -> None:
+        self._stop.set()
+        self._inbox.put(("wake", None))
+        self._thread.join(timeout)
+        self.watchdog.close()
+
+    async def stream(self, prompt, params: SamplingParams, request_id: Optional[str] = None):
+        """Async generator of :class:`StreamEvent`; cancels the sequence if the consumer goes away."""
+        loop = asyncio.get_running_loop()
+        q: "asyncio.Queue[StreamEvent]" = asyncio.Queue()
+        rid = self.submit(prompt, params, lambda ev: loop.call_soon_threadsafe(q.put_nowait, ev), request_id)
+        try:
+            while True:
+                ev = await q.get()
+                yield ev
+                if ev.finished:
+                    return
+        finally:
+            self.cancel(rid)
+
+    def generate_blocking(self, prompt, params: SamplingParams, timeout: Optional[float] = None) -> List[StreamEvent]:
+        done = threading.Event()
+        evs: List[StreamEvent] = []
+
+        def sink(ev: StreamEvent):
+            evs.append(ev)
+            if ev.finished:
+                done.set()
+
+        self.submit(prompt, params, sink)
+        if not done.wait(timeout):
+            raise TimeoutError("generation timed out")
+        return evs
+
+    # ------------------------------------------------------------------ engine thread
+    def _admit(self, p: _Pending) -> None:
+        try:
+            self.llm.add_request(p.prompt, p.params, p.request_id)
+        except Exception as e:  # noqa: BLE001 - reported to the caller
+            p.sink(StreamEvent(p.request_id, [], "", True, "error", error=str(e)))
+            return
+        self._sinks[p.request_id] = p.sink
+        self._sent[p.request_id] = 0
+        self._meta[p.request_id] = p
+        tok = self.llm.tokenizer
+        self._detok[p.request_id] = tok.streaming_detokenizer() if tok is not None else None
+
+    def _drain_inbox(self, block: bool) -> None:
+        try:
+            item = self._inbox.get(timeout=0.05) if block else self._inbox.get_nowait()
+        except queue.Empty:
+            return
+        while True:
+            if isinstance(item, _Pending):
+                self._admit(item)
+            elif isinstance(item, tuple) and item[0] == "cancel":
+                rid = item[1]
+                if rid in self._sinks:
+                    self.llm.abort(rid)
+                    self._forget(rid)
+            try:
+                item = self._inbox.get_nowait()
+            except queue.Empty:
+                return
+
+    def _forget(self, rid: str) -> None:
+        for d in (self._sinks, self._sent, self._detok, self._meta):
+            d.pop(rid, None)
+
+    def _route(self, ro: RequestOutput) -> None:
+        sink = self._sinks.get(ro.request_id)
+        if sink is None:
+            return
+        sent = self._sent[ro.request_id]
+        new = ro.token_ids[sent:]
+        self._sent[ro.request_id] = len(ro.token_ids)
+        det = self._detok.get(ro.request_id)
+        eos = self.llm.eos_token_id
+        text = ""
+        if det is not None:
+            for t in new:
+                if t == eos or self.llm.tokenizer.special_tokens.is_special(t):
+                    continue
+                text += det.push(t)
+            if ro.finished:
+                text += det.finish()
+        meta = self._meta.get(ro.request_id)
+        wait = 0.0 if ro.ttft is None or meta is None else max(0.0, ro.ttft)
+        self.tokens_generated += len(new)
+        ev = StreamEvent(ro.request_id, list(new), text, ro.finished, ro.finish_reason,
+                         prompt_tokens=len(ro.prompt_token_ids), completion_tokens=len(ro.token_ids), queue_wait_s=wait)
+        if ro.finished:
+            self.prompt_tokens += len(ro.prompt_token_ids)
+            self._forget(ro.request_id)
+        sink(ev)
+
+    def _fail_all(self, msg: str) -> None:
+        self.failures += 1
+        for rid, sink in list(self._sinks.items()):
+            try:
+                self.llm.abort(rid)
+            except Exception:
+                pass
+            sink(StreamEvent(rid, [], "", True, "error", error=msg))
+            self._forget(rid)
+
+    def _loop(self) -> None:
+        while not self._stop.is_set():
+            self._drain_inbox(block=not self.llm.has_unfinished)
+            if not self.llm.has_unfinished:
+                continue
+            self.watchdog.begin_step()
+            try:
+                outs = self.llm.step()
+            except Exception as e:  # noqa: BLE001 - engine survives a failed step
+                self.watchdog.end_step()
+                self._fail_all(f"engine step failed: {e}")
+                continue
+            self.watchdog.end_step()
+            for ro in outs:
+                self._route(ro)
