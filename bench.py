@@ -104,6 +104,10 @@ def main():
     args = parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    # last-resort guard: never sit on a GPU box forever if something blocks
+    guard = threading.Timer(1500.0, lambda: os._exit(3))
+    guard.daemon = True
+    guard.start()
     import torch
     import torch.distributed as dist
 
@@ -259,9 +263,14 @@ def main():
             "device_status": {"code": code, "detail": detail, "count": count},
         }
         print(json.dumps(out))
+    sys.stdout.flush()
+    sys.stderr.flush()
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        # The measurements are done and reduced.  Tearing down NCCL communicators that were
+        # captured into CUDA graphs (and the symmetric-memory mappings) can block at exit, so
+        # leave without running the teardown: every rank has finished its collectives.
+        torch.cuda.synchronize()
+        os._exit(0)
     return 0
 
 

@@ -1,0 +1,472 @@
+"""``oxidize`` command line: run / chat / serve / pull / show / list / inspect / bench / gpu-cluster.
+
+Ollama-style verbs are rewritten into flags before parsing, as the reference does
+(``oxidize-cli/src/main/command_rewrite.rs:8``; flag surface ``oxidize-cli/src/main.rs:74-209`` and
+``oxidize-server/src/cli.rs:72-160``).  Flag names and defaults are kept; ``--tp``, ``--pp``,
+``--kv-page-size``, ``--max-running``, ``--max-batched-tokens``, ``--fused-comm`` and ``--tokens``
+are additions.  ``--backend`` accepts the reference's values but only ``cpu`` and ``cuda`` run.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+from typing import List, Optional
+
+VERBS = ("run", "chat", "serve", "pull", "show", "list", "inspect", "bench", "gpu-cluster")
+DEAD_BACKENDS = ("metal", "mlx", "rocm", "vulkan", "intel-arc")
+MODEL_DIR = os.path.expanduser(os.environ.get("OXIDIZE_MODEL_DIR", "~/.cache/oxidize/models"))
+
+
+def rewrite_args(argv: List[str]) -> List[str]:
+    """``run M "prompt"`` → ``--model M --prompt "prompt"``; ``serve M`` → ``--model M --api-only`` …"""
+    if not argv or argv[0] not in VERBS:
+        return argv
+    verb, rest = argv[0], argv[1:]
+    pos = []
+    flags = []
+    i = 0
+    while i < len(rest):
+        a = rest[i]
+        if a.startswith("-"):
+            flags.append(a)
+            if "=" not in a and i + 1 < len(rest) and not rest[i + 1].startswith("-") and a not in _BOOL_FLAGS:
+                flags.append(rest[i + 1])
+                i += 1
+        else:
+            pos.append(a)
+        i += 1
+    out = ["--verb", verb]
+    if pos:
+        out += ["--model", pos[0]]
+    if verb == "run" and len(pos) > 1:
+        out += ["--prompt", " ".join(pos[1:])]
+    if verb == "chat":
+        out += ["--chat"]
+    if verb == "serve":
+        out += ["--api-only"]
+    return out + flags
+
+
+_BOOL_FLAGS = {"--chat", "--cpu-optimized", "--ram-offload", "--mmap-prefetch", "--mmap-hugepages", "--layer-wise",
+               "--turboquant-kv", "--no-turboquant-kv", "--mesh", "--auto", "--no-auto", "--no-api", "--serve-api",
+               "--api-only", "--vision", "--force-dflash", "--no-mtp", "--quantspec", "--pipe-head", "--pipe-tail",
+               "--turboquant", "--no-turboquant", "--json", "--bench-no-eos", "--cuda-graphs", "--no-cuda-graphs"}
+
+
+def build_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(prog="oxidize", description="Blackwell-native LLM inference engine")
+    a = p.add_argument
+    a("--verb", default="run", choices=VERBS, help=argparse.SUPPRESS)
+    a("--model", default=None)
+    a("--prompt", default="hello")
+    a("--tokens", default=None, help="raw token-id prompt, e.g. 1,2,3")
+    a("--chat", action="store_true")
+    a("--backend", default="auto", choices=["auto", "cpu", "cuda"] + list(DEAD_BACKENDS))
+    a("--batch-mode", default="paged", choices=["sequential", "paged"])
+    a("--model-id", default="oxidize-default")
+    a("--host", default="127.0.0.1")
+    a("--port", type=int, default=8080)
+    a("--api-host", default="127.0.0.1")
+    a("--api-port", type=int, default=8080)
+    a("--max-tokens", type=int, default=None)
+    a("--temperature", type=float, default=0.8)
+    a("--top-p", type=float, default=None)
+    a("--top-k", type=int, default=None)
+    a("--min-p", type=float, default=None)
+    a("--seed", type=int, default=None)
+    a("--ctx-size", type=int, default=0)
+    a("--prefill-batch-size", type=int, default=512)
+    a("--kv-cache-dtype", default="auto", choices=["auto", "f32", "f16", "bf16", "q8", "q4"])
+    a("--turboquant-kv", action="store_true")
+    a("--no-turboquant-kv", action="store_true")
+    a("--turboquant", action="store_true")
+    a("--no-turboquant", action="store_true")
+    a("--threads", type=int, default=0)
+    a("--n-gpu-layers", type=int, default=0)
+    a("--gpus", type=int, default=0)
+    a("--tp", type=int, default=0)
+    a("--ep", type=int, default=0)
+    a("--pp", type=int, default=1)
+    a("--parallelism", default="tensor", choices=["pipeline", "tensor"])
+    a("--kv-page-size", type=int, default=16)
+    a("--max-running", type=int, default=0)
+    a("--max-batched-tokens", type=int, default=2048)
+    a("--fused-comm", default="on", choices=["on", "off"])
+    a("--weights-dtype", default="auto", choices=["auto", "bf16", "fp8", "nvfp4"])
+    a("--rope-pairing", default=None, choices=["split_half", "adjacent"])
+    a("--cuda-graphs", action="store_true", default=True)
+    a("--no-cuda-graphs", action="store_true")
+    a("--draft-model", default=None)
+    a("--draft-tokens", type=int, default=4)
+    a("--force-dflash", action="store_true")
+    a("--no-mtp", action="store_true")
+    a("--quantspec", action="store_true")
+    a("--lora", nargs="*", default=[])
+    a("--tokenizer-model", default=None)
+    a("--auto", action="store_true", default=True)
+    a("--no-auto", action="store_true")
+    a("--print-plan", default="auto", choices=["auto", "yes", "json"])
+    a("--profile", default=None, choices=["perf", "samply", "torch"])
+    a("--profile-output", default=None)
+    a("--no-api", action="store_true")
+    a("--serve-api", action="store_true")
+    a("--api-only", action="store_true")
+    a("--mesh", action="store_true")
+    a("--mesh-port", type=int, default=0)
+    a("--pipe-head", action="store_true")
+    a("--pipe-tail", action="store_true")
+    a("--pipe-peer", default=None)
+    a("--pipe-listen", default=None)
+    a("--pipe-max-tokens", type=int, default=64)
+    a("--vision", action="store_true")
+    a("--image", default=None)
+    for f in ("--cpu-optimized", "--ram-offload", "--mmap-prefetch", "--mmap-hugepages", "--layer-wise"):
+        a(f, action="store_true")
+    a("--ram-offload-threads", type=int, default=0)
+    a("--layer-cache", type=int, default=1)
+    # bench (mirrors `oxidize-c bench`, oxidize-c/src/cli/commands.c:690-830)
+    a("--bench-prompt-tokens", type=int, default=512)
+    a("--bench-decode-tokens", type=int, default=128)
+    a("--bench-iters", type=int, default=3)
+    a("--bench-warmup", type=int, default=1)
+    a("--bench-batch", type=int, default=1)
+    a("--bench-no-eos", action="store_true")
+    a("--json", action="store_true")
+    # gpu-cluster
+    a("--cluster-name", default="oxidize")
+    a("--gpu-family", default="b200")
+    a("--nodes", type=int, default=1)
+    a("--output", default=None)
+    return p
+
+
+def user_passed(argv: List[str]) -> set:
+    return {a.split("=")[0].lstrip("-").replace("-", "_") for a in argv if a.startswith("--")}
+
+
+def resolve_model(name: Optional[str]) -> str:
+    if not name:
+        raise SystemExit("error: no model given (oxidize run MODEL.gguf \"prompt\")")
+    for cand in (name, os.path.join(MODEL_DIR, name), os.path.join(MODEL_DIR, name + ".gguf")):
+        if os.path.isfile(cand):
+            return cand
+    if name.startswith("hf://") or "/" in name and not os.path.exists(name):
+        raise SystemExit(f"error: {name!r} is not a local file and this build has no network access; "
+                         f"place the GGUF under {MODEL_DIR} or pass a path")
+    raise SystemExit(f"error: model {name!r} not found")
+
+
+def make_engine(args, passed: set):
+    import torch
+
+    from ..engine.llm import LLM, EngineConfig
+    from ..formats.gguf import load_gguf
+    from ..utils import autotune
+
+    if args.backend in DEAD_BACKENDS:
+        raise SystemExit(f"error: backend {args.backend!r} is not available in this build; use cpu or cuda")
+    path = resolve_model(args.model)
+    g = load_gguf(path)
+    inv = autotune.detect()
+    fp = autotune.fingerprint(g)
+    plan = autotune.plan(inv, fp, args.ctx_size, args.max_running)
+    if args.print_plan == "json":
+        print(plan.to_json())
+    elif args.print_plan == "yes" or (args.print_plan == "auto" and not args.no_auto and sys.stderr.isatty()):
+        print(plan.render(), file=sys.stderr)
+    use_plan = args.auto and not args.no_auto
+    backend = args.backend
+    if backend == "auto":
+        backend = plan.backend if use_plan else ("cuda" if torch.cuda.is_available() else "cpu")
+    if backend == "cuda" and not torch.cuda.is_available():
+        raise SystemExit("error: --backend cuda but no CUDA device is visible")
+    kvd = args.kv_cache_dtype
+    if args.turboquant_kv and "kv_cache_dtype" not in passed:
+        kvd = "q8"
+    if kvd == "auto":
+        kvd = plan.kv_cache_dtype if (use_plan and backend == plan.backend) else "auto"
+    tp = args.tp or (args.gpus if args.parallelism == "tensor" and args.gpus > 1 else 0) or 1
+    ec = EngineConfig(kv_cache_dtype=kvd, kv_page_size=args.kv_page_size,
+                      max_model_len=args.ctx_size or plan.ctx_size, max_num_seqs=args.max_running or plan.max_num_seqs,
+                      max_num_batched_tokens=args.max_batched_tokens, prefill_chunk_size=args.prefill_batch_size,
+                      cuda_graphs=not args.no_cuda_graphs, tp_size=tp, ep_size=args.ep or tp, pp_size=args.pp,
+                      fused_comm=args.fused_comm == "on")
+    if tp > 1 and int(os.environ.get("WORLD_SIZE", "1")) != tp:
+        from ..parallel.launcher import relaunch_under_torchrun
+
+        relaunch_under_torchrun(tp)
+    comm = None
+    rank = 0
+    if tp > 1:
+        from ..parallel.comm import TorchComm, init_distributed
+
+        layout = init_distributed()
+        rank = layout.rank
+        if backend == "cuda" and ec.fused_comm:
+            from ..parallel.fused import FusedComm
+
+            comm = FusedComm(torch.device("cuda", torch.cuda.current_device()), hidden=fp.hidden_size)
+        else:
+            comm = TorchComm()
+    dev = "cpu" if backend == "cpu" else f"cuda:{torch.cuda.current_device()}"
+    llm = LLM.from_gguf(g, ec, device=dev, comm=comm, tp_rank=rank, ep_rank=rank, rope_pairing=args.rope_pairing)
+    if args.tokenizer_model:
+        from ..formats.tokenizer import load_tokenizer_from_gguf
+
+        llm.tokenizer = load_tokenizer_from_gguf(args.tokenizer_model)
+    if args.draft_model or (fp.has_mtp and not args.no_mtp):
+        from ..engine.spec import attach_speculation
+
+        attach_speculation(llm, args.draft_model, args.draft_tokens, use_mtp=fp.has_mtp and not args.no_mtp, device=dev)
+    return llm, g
+
+
+def sampling_from_args(args, default_max: int):
+    from ..engine.sampler import SamplingParams
+
+    return SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k, min_p=args.min_p,
+                          seed=args.seed, max_tokens=args.max_tokens or default_max)
+
+
+def cmd_run(args, passed) -> int:
+    llm, g = make_engine(args, passed)
+    sp = sampling_from_args(args, 128)
+    if args.tokens:
+        prompt = [int(x) for x in args.tokens.replace(" ", "").split(",") if x]
+    else:
+        prompt = args.prompt
+        if llm.tokenizer is None:
+            raise SystemExit("error: the model has no tokenizer metadata; pass --tokens 1,2,3")
+    det = llm.tokenizer.streaming_detokenizer() if llm.tokenizer is not None else None
+    printed = [0]
+
+    def on_token(ro):
+        new = ro.token_ids[printed[0]:]
+        printed[0] = len(ro.token_ids)
+        if det is not None:
+            sys.stdout.write("".join(det.push(t) for t in new if not llm.tokenizer.special_tokens.is_special(t)))
+        else:
+            sys.stdout.write("".join(f"{t} " for t in new))
+        sys.stdout.flush()
+
+    t0 = time.perf_counter()
+    out = llm.generate([prompt], sp, on_token=on_token)[0]
+    dt = time.perf_counter() - t0
+    print()
+    n = len(out.token_ids)
+    print(f"generation stats: tokens={n} speed={n / max(dt, 1e-9):.2f} tok/s", file=sys.stderr)
+    return 0
+
+
+def cmd_chat(args, passed) -> int:
+    from ..formats.tokenizer import chat_template_from_metadata, render_chat_template
+
+    llm, g = make_engine(args, passed)
+    if llm.tokenizer is None:
+        raise SystemExit("error: chat needs a tokenizer in the GGUF")
+    tpl = chat_template_from_metadata(g.metadata)
+    sp = sampling_from_args(args, 512)
+    history = []
+    print("oxidize chat — empty line or /bye to quit", file=sys.stderr)
+    while True:
+        try:
+            line = input(">>> ").strip()
+        except EOFError:
+            break
+        if not line or line == "/bye":
+            break
+        history.append({"role": "user", "content": line})
+        out = llm.generate([render_chat_template(tpl, history, True)], sp)[0]
+        text = out.text or ""
+        print(text)
+        history.append({"role": "assistant", "content": text})
+    return 0
+
+
+def cmd_serve(args, passed) -> int:
+    import uvicorn
+
+    from ..engine.async_engine import AsyncEngine
+    from ..formats.tokenizer import chat_template_from_metadata
+    from ..serving.app import GenerationDefaults, ServerState, create_app
+
+    engine = None
+    tpl = None
+    if args.model:
+        llm, g = make_engine(args, passed)
+        tpl = chat_template_from_metadata(g.metadata)
+        from ..engine.server_control import install_suppressed_tokens
+
+        if int(os.environ.get("RANK", "0")) != 0:
+            from ..parallel.launcher import follower_loop
+
+            install_suppressed_tokens(llm)
+            follower_loop(llm)
+            return 0
+
+        install_suppressed_tokens(llm)
+        control = None
+        if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+            from ..engine.server_control import SpmdControl
+
+            control = SpmdControl()
+        engine = AsyncEngine(llm, control=control)
+    state = ServerState(engine, args.model_id, GenerationDefaults(max_tokens=args.max_tokens or 512,
+                                                                  temperature=args.temperature, top_p=args.top_p,
+                                                                  top_k=args.top_k), chat_template=tpl)
+    host = args.host if "host" in passed else args.api_host
+    port = args.port if "port" in passed else args.api_port
+    uvicorn.run(create_app(state), host=host, port=port, log_level="info")
+    return 0
+
+
+def cmd_show(args, passed, verbose: bool) -> int:
+    from ..formats.gguf import load_gguf
+
+    g = load_gguf(resolve_model(args.model))
+    info = {"path": g.path, "version": g.version, "architecture": g.architecture, "alignment": g.alignment,
+            "tensor_count": len(g.tensors), "metadata": {k: (v if not isinstance(v, list) or len(v) <= 8 else
+                                                             f"[{len(v)} items]") for k, v in g.metadata.items()}}
+    if verbose:
+        info["tensors"] = [{"name": t.name, "shape": list(t.shape), "type": t.type.name, "bytes": t.nbytes}
+                           for t in g.tensors.values()]
+    by_type = {}
+    for t in g.tensors.values():
+        by_type[t.type.name] = by_type.get(t.type.name, 0) + t.nbytes
+    info["bytes_by_type"] = by_type
+    print(json.dumps(info, indent=2, default=str))
+    return 0
+
+
+def cmd_list(args) -> int:
+    if not os.path.isdir(MODEL_DIR):
+        print(f"(no models under {MODEL_DIR})")
+        return 0
+    for f in sorted(os.listdir(MODEL_DIR)):
+        if f.endswith(".gguf"):
+            print(f"{f}\t{os.path.getsize(os.path.join(MODEL_DIR, f)) / 1e9:.2f} GB")
+    return 0
+
+
+def cmd_pull(args) -> int:
+    src = args.model
+    if src and os.path.isfile(src):
+        import shutil
+
+        os.makedirs(MODEL_DIR, exist_ok=True)
+        dst = os.path.join(MODEL_DIR, os.path.basename(src))
+        shutil.copyfile(src, dst)
+        print(f"copied to {dst}")
+        return 0
+    print(f"error: cannot fetch {src!r}: this build runs without network access; copy a GGUF into {MODEL_DIR}",
+          file=sys.stderr)
+    return 2
+
+
+def cmd_bench(args, passed) -> int:
+    import numpy as np
+
+    from ..engine.sampler import SamplingParams
+
+    llm, g = make_engine(args, passed)
+    rng = np.random.default_rng(0)
+    sp = SamplingParams(temperature=0.0, max_tokens=args.bench_decode_tokens, ignore_eos=args.bench_no_eos)
+    rows = []
+    for it in range(args.bench_warmup + args.bench_iters):
+        prompts = [rng.integers(3, llm.cfg.vocab_size, size=args.bench_prompt_tokens).tolist()
+                   for _ in range(args.bench_batch)]
+        t0 = time.perf_counter()
+        for p in prompts:
+            llm.add_request(p, sp)
+        first = None
+        ntok = 0
+        while llm.has_unfinished:
+            for ro in llm.step():
+                if first is None and ro.token_ids:
+                    first = time.perf_counter()
+                if ro.finished:
+                    ntok += len(ro.token_ids)
+        t1 = time.perf_counter()
+        if it >= args.bench_warmup:
+            pf = (first or t1) - t0
+            rows.append({"iter": it - args.bench_warmup,
+                         "prefill_tok_per_s": args.bench_prompt_tokens * args.bench_batch / max(pf, 1e-9),
+                         "decode_tok_per_s": max(ntok - args.bench_batch, 0) / max(t1 - (first or t1), 1e-9),
+                         "ttft_s": pf})
+    if args.json:
+        print(json.dumps({"engine": "oxidize_b200", "batch": args.bench_batch, "iterations": rows}))
+    else:
+        for r in rows:
+            print(f"iter {r['iter']}: prefill {r['prefill_tok_per_s']:.1f} tok/s, decode {r['decode_tok_per_s']:.1f} tok/s")
+    return 0
+
+
+def cmd_gpu_cluster(args) -> int:
+    from ..utils.gpu_cluster import render_cluster_manifests
+
+    text = render_cluster_manifests(args.cluster_name, args.gpu_family, args.nodes)
+    if args.output:
+        with open(args.output, "w") as f:
+            f.write(text)
+    else:
+        print(text)
+    return 0
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    argv = rewrite_args(argv)
+    passed = user_passed(argv)
+    args = build_parser().parse_args(argv)
+    if args.profile == "torch":
+        import torch
+
+        with torch.profiler.profile() as prof:
+            rc = dispatch(args, passed)
+        prof.export_chrome_trace(args.profile_output or "oxidize_trace.json")
+        return rc
+    if args.profile in ("perf", "samply") and not os.environ.get("OXIDIZE_PROFILE_CHILD"):
+        import shutil
+        import subprocess
+
+        tool = shutil.which(args.profile)
+        if tool is None:
+            raise SystemExit(f"error: profiler {args.profile!r} not found on PATH")
+        out = args.profile_output or ("perf.data" if args.profile == "perf" else "profile.json")
+        cmd = [tool, "record", "-o", out, "--", sys.executable, "-m", "oxidize_b200.cli.main"] + sys.argv[1:]
+        return subprocess.call(cmd, env=dict(os.environ, OXIDIZE_PROFILE_CHILD="1"))
+    return dispatch(args, passed)
+
+
+def dispatch(args, passed) -> int:
+    if args.pipe_head or args.pipe_tail:
+        from ..parallel.pp import run_pipe_cli
+
+        return run_pipe_cli(args)
+    v = args.verb
+    if v == "run":
+        return cmd_serve(args, passed) if args.api_only else (cmd_chat(args, passed) if args.chat else cmd_run(args, passed))
+    if v == "chat":
+        return cmd_chat(args, passed)
+    if v == "serve":
+        return cmd_serve(args, passed)
+    if v == "show":
+        return cmd_show(args, passed, False)
+    if v == "inspect":
+        return cmd_show(args, passed, True)
+    if v == "list":
+        return cmd_list(args)
+    if v == "pull":
+        return cmd_pull(args)
+    if v == "bench":
+        return cmd_bench(args, passed)
+    if v == "gpu-cluster":
+        return cmd_gpu_cluster(args)
+    return 2
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -45,8 +45,11 @@ class _Pending:
 
 
 class AsyncEngine:
-    def __init__(self, llm: LLM, step_deadline_s: float = 60.0, name: str = "oxidize-batch-engine"):
+    def __init__(self, llm: LLM, step_deadline_s: float = 60.0, name: str = "oxidize-batch-engine", control=None):
         self.llm = llm
+        self.control = control  # SpmdControl when follower ranks mirror this engine
+        self._step_admits: List[Any] = []
+        self._step_aborts: List[str] = []
         self._inbox: "queue.Queue[Any]" = queue.Queue()
         self._sinks: Dict[str, Callable[[StreamEvent], None]] = {}
         self._detok: Dict[str, Any] = {}
@@ -89,6 +92,8 @@ class AsyncEngine:
         self._stop.set()
         self._inbox.put(("wake", None))
         self._thread.join(timeout)
+        if self.control is not None:
+            self.control.leader_sync([], [], stop=True)
         self.watchdog.close()
 
     async def stream(self, prompt, params: SamplingParams, request_id: Optional[str] = None):
@@ -126,6 +131,9 @@ class AsyncEngine:
         except Exception as e:  # noqa: BLE001 - reported to the caller
             p.sink(StreamEvent(p.request_id, [], "", True, "error", error=str(e)))
             return
+        if self.control is not None:
+            seq = self.llm._seqs[p.request_id]
+            self._step_admits.append((p.request_id, list(seq.prompt), p.params))
         self._sinks[p.request_id] = p.sink
         self._sent[p.request_id] = 0
         self._meta[p.request_id] = p
@@ -145,6 +153,8 @@ class AsyncEngine:
                 if rid in self._sinks:
                     self.llm.abort(rid)
                     self._forget(rid)
+                    if self.control is not None:
+                        self._step_aborts.append(rid)
             try:
                 item = self._inbox.get_nowait()
             except queue.Empty:
@@ -194,6 +204,9 @@ class AsyncEngine:
     def _loop(self) -> None:
         while not self._stop.is_set():
             self._drain_inbox(block=not self.llm.has_unfinished)
+            if self.control is not None and (self._step_admits or self._step_aborts or self.llm.has_unfinished):
+                self.control.leader_sync(self._step_admits, self._step_aborts)
+                self._step_admits, self._step_aborts = [], []
             if not self.llm.has_unfinished:
                 continue
             self.watchdog.begin_step()

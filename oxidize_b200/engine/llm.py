@@ -145,14 +145,22 @@ class LLM:
 
     def step(self) -> List[RequestOutput]:
         """One engine iteration: schedule → forward → sample → postprocess."""
+        spec = getattr(self, "spec", None)
+        if spec is not None:
+            spec.before_schedule(self)
         out = self.scheduler.schedule()
         if out.is_empty:
             if self.scheduler.has_work and not out.preempted:
                 raise RuntimeError("scheduler made no progress: KV pool too small for the waiting request")
             return []
         res = self.runner.execute(out)
+        if spec is not None:
+            res.tokens = spec.after_forward(self, out, res.tokens)
         now = time.perf_counter()
-        self.scheduler.postprocess(out, res.tokens, self.eos_token_id, now)
+        done = self.scheduler.postprocess(out, res.tokens, self.eos_token_id, now)
+        if spec is not None:
+            for s in done:
+                spec.on_finished(s)
         st = self.stats
         st["steps"] += 1
         st["prefill_tokens"] += out.num_prefill_tokens

@@ -207,6 +207,7 @@ class ModelRunner:
         if pad_to is not None and pad_to > self.buf.max_seqs:
             pad_to, graphable = None, False
         T, B, nl, max_q, max_len, rows = self.build(scheduled, pad_to)
+        self.last_rows = rows
         all_greedy = self._fill_sampling(rows, nl)
         tie = scheduled[0].seq.params.tie
         h2d = self.buf.upload()

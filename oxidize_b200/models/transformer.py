@@ -157,7 +157,8 @@ class Transformer:
         idx = meta.logits_indices.long()
         h = h.index_select(0, idx)
         residual = residual.index_select(0, idx) if residual is not None else None
-        x, _ = ops.add_rmsnorm(h, residual, self.w.out_norm, self.cfg.rms_eps)
+        x, hid = ops.add_rmsnorm(h, residual, self.w.out_norm, self.cfg.rms_eps)
+        self.last_hidden = hid  # pre-norm hidden of the logits rows (input of an MTP head)
         logits = ops.linear(x, self.w.lm_head).float()
         sharded = self.w.tp_size > 1 and self.w.lm_head.out_features != self.cfg.vocab_size
         if not sharded:

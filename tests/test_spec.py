@@ -1,0 +1,74 @@
+"""Speculative decoding keeps greedy output exact, for a perfect draft, a bad draft and the MTP head."""
+import numpy as np
+import pytest
+
+from oxidize_b200.engine.llm import LLM, EngineConfig
+from oxidize_b200.engine.sampler import SamplingParams
+from oxidize_b200.engine.spec import (DraftModelProposer, MtpProposer, SpecDecoder, SpecStats, attach_speculation,
+                                      verify_greedy)
+from oxidize_b200.models.config import preset
+from oxidize_b200.utils.synth import synth_gguf, synth_weights
+
+EC = dict(max_model_len=160, max_num_seqs=4, num_kv_blocks=64, prefill_chunk_size=32, max_num_batched_tokens=96)
+SP = SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True)
+PROMPTS = [[5, 9, 200, 31, 7], list(range(3, 40)), [100, 101]]
+
+
+def test_verify_greedy_rule():
+    assert verify_greedy([1, 2, 3], [1, 2, 3, 9]) == [1, 2, 3, 9]
+    assert verify_greedy([1, 2, 3], [1, 7, 3, 9]) == [1, 7]
+    assert verify_greedy([4], [5, 6]) == [5]
+
+
+def test_stats():
+    s = SpecStats(proposed=40, accepted=30, target_forwards=10, emitted=40)
+    assert s.acceptance_rate == 0.75 and s.tokens_per_target_forward == 4.0
+    assert s.estimated_speedup(0.1, 4) == pytest.approx(4.0 / 1.4)
+
+
+@pytest.fixture(scope="module")
+def target_path(tmp_path_factory):
+    cfg = preset("tiny-llama", n_layers=2, vocab_size=300)
+    p = str(tmp_path_factory.mktemp("spec") / "target.gguf")
+    synth_gguf(p, cfg, "F16", seed=0, norm_jitter=0.05)
+    return p
+
+
+def _plain(path):
+    return [o.token_ids for o in LLM.from_gguf(path, EngineConfig(**EC), device="cpu").generate(PROMPTS, SP)]
+
+
+def test_perfect_draft_accepts_everything(target_path):
+    want = _plain(target_path)
+    llm = LLM.from_gguf(target_path, EngineConfig(**EC), device="cpu")
+    spec = attach_speculation(llm, target_path, k=3)
+    got = [o.token_ids for o in llm.generate(PROMPTS, SP)]
+    assert got == want
+    assert spec.stats.acceptance_rate > 0.95 and spec.stats.tokens_per_target_forward > 2.0
+    assert llm.pool.num_free == llm.pool.num_blocks and spec.proposer.pool.num_free == spec.proposer.pool.num_blocks
+
+
+def test_bad_draft_is_still_exact(target_path, tmp_path):
+    want = _plain(target_path)
+    dcfg = preset("tiny-llama", n_layers=1, vocab_size=300, hidden_size=128, n_heads=4, n_kv_heads=2, head_dim=32,
+                  ffn_size=256)
+    dpath = str(tmp_path / "draft.gguf")
+    synth_gguf(dpath, dcfg, "F16", seed=7)
+    llm = LLM.from_gguf(target_path, EngineConfig(**EC), device="cpu")
+    spec = attach_speculation(llm, dpath, k=4)
+    got = [o.token_ids for o in llm.generate(PROMPTS, SP)]
+    assert got == want
+    assert spec.stats.proposed > 0 and spec.stats.acceptance_rate < 0.9
+
+
+def test_mtp_head_is_exact(tmp_path):
+    cfg = preset("tiny-llama", n_layers=2, vocab_size=300, nextn_layers=1)
+    path = str(tmp_path / "mtp.gguf")
+    synth_gguf(path, cfg, "F16", seed=3, norm_jitter=0.05)
+    plain = LLM.from_gguf(path, EngineConfig(**EC), device="cpu")
+    assert len(plain.weights.mtp) == 1 and len(plain.weights.layers) == 2
+    want = [o.token_ids for o in plain.generate(PROMPTS, SP)]
+    llm = LLM.from_gguf(path, EngineConfig(**EC), device="cpu")
+    spec = attach_speculation(llm, None, k=2, use_mtp=True)
+    got = [o.token_ids for o in llm.generate(PROMPTS, SP)]
+    assert got == want and spec.stats.target_forwards > 0 and spec.stats.proposed > 0
