@@ -14,12 +14,14 @@
 #pragma once
 #include "common.cuh"
 #include "comm_fused.cuh"
+#include "mmq_producer.cuh"
 
 namespace oxb {
 
 constexpr int GEMM_BM = 128;  // weight rows per tile (UMMA M)
 constexpr int GEMM_BK = 64;   // bf16 per k-block = one 128-byte swizzle row
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 192;       // TMA warp, MMA warp, 4 epilogue warps
+constexpr int GEMM_THREADS_MMQ = 320;   // + 4 dequant producer warps for packed weights
 
 template <int TN>
 struct GemmTile {
@@ -56,11 +58,15 @@ __device__ __forceinline__ void splitk_reduce(const float* base, int split_strid
   }
 }
 
-template <int TN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+// QT == QT_BF16: both operands arrive by TMA.  Any other QT: the weight tile is produced by four
+// dequant warps from packed blocks (see mmq_producer.cuh) and only the activations use TMA.
+template <int TN, int QT>
+__global__ void __launch_bounds__(QT == QT_BF16 ? GEMM_THREADS : GEMM_THREADS_MMQ, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                  __nv_bfloat16* __restrict__ Y, const float* __restrict__ bias, int N, int T, int K, int ldY,
-                 int splits, float* __restrict__ ws, int* __restrict__ counters, int epi_mode, const ArArgs ar) {
+                 int splits, float* __restrict__ ws, int* __restrict__ counters, int epi_mode, const ArArgs ar,
+                 const QwArgs qw) {
+  constexpr bool MMQ = QT != QT_BF16;
   using Cfg = GemmTile<TN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -83,7 +89,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) {
-      mbar_init(&full[i], 1);
+      mbar_init(&full[i], MMQ ? 1 + 128 : 1);  // TMA expect_tx arrival (+ one per producer thread)
       mbar_init(&empty[i], 1);
     }
     mbar_init(accum, 1);
@@ -114,8 +120,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         if (!mbar_wait_bounded(&empty[st], ph ^ 1, abort_flag, OXB_TIMEOUT_TMA_EMPTY, blockIdx.x)) break;
         uint8_t* sA = smem + st * Cfg::STAGE_BYTES;
         uint8_t* sB = sA + Cfg::A_BYTES;
-        mbar_expect_tx(&full[st], Cfg::STAGE_BYTES);
-        tma_load_2d_hint(sA, &tmW, &full[st], (kb_begin + i) * GEMM_BK, n0, pol_w);
+        if constexpr (MMQ) {
+          mbar_expect_tx(&full[st], Cfg::B_BYTES);
+        } else {
+          mbar_expect_tx(&full[st], Cfg::STAGE_BYTES);
+          tma_load_2d_hint(sA, &tmW, &full[st], (kb_begin + i) * GEMM_BK, n0, pol_w);
+        }
         tma_load_2d_hint(sB, &tmX, &full[st], (kb_begin + i) * GEMM_BK, t0, pol_x);
       }
     }
@@ -142,6 +152,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       umma_commit(accum);
     }
     __syncwarp();
+  } else if (warp >= 6) {
+    // ---------------- dequant producers (MMQ only): thread r stages weight row n0 + r
+    if constexpr (MMQ) {
+      const int r = threadIdx.x - 192;
+      const int n = n0 + r;
+      const uint8_t* rowp = qw.w + (size_t)(n < N ? n : 0) * qw.row_bytes;
+      for (int i = 0; i < nkb; ++i) {
+        const int st = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        if (!mbar_wait_bounded(&empty[st], ph ^ 1, abort_flag, OXB_TIMEOUT_TMA_EMPTY, blockIdx.x)) break;
+        uint32_t v[32];
+        const int k0 = (kb_begin + i) * GEMM_BK;
+        if (n < N && k0 + GEMM_BK <= K) {
+          dequant64<QT>(rowp, k0, qw, n, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0u;
+        }
+        store_row_sw128(smem + st * Cfg::STAGE_BYTES, r, v);
+        fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+        mbar_arrive(&full[st]);
+      }
+    }
   } else {
     // ---------------- epilogue: warps 2..5 own TMEM lane quarters (warp % 4)
     const int quarter = warp & 3;
@@ -312,22 +345,37 @@ inline GemmPlan gemm_plan(int T, int N, int K, int splits_hint, int sm_count) {
   return p;
 }
 
-template <int TN>
+template <int TN, int QT = QT_BF16>
 int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y, const float* bias, int N, int T, int K,
                 int ldY, const GemmPlan& p, float* ws, int* counters, int epi_mode, const ArArgs& ar,
-                cudaStream_t stream) {
+                cudaStream_t stream, const QwArgs& qw = QwArgs{nullptr, 0, nullptr, 0}) {
   using Cfg = GemmTile<TN>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<TN, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   dim3 grid(p.n_tiles, p.splits, p.t_tiles);
-  gemm_bf16_kernel<TN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmW, tmX, Y, bias, N, T, K, ldY, p.splits, ws,
-                                                                        counters, epi_mode, ar);
+  gemm_bf16_kernel<TN, QT><<<grid, QT == QT_BF16 ? GEMM_THREADS : GEMM_THREADS_MMQ, Cfg::SMEM_BYTES, stream>>>(
+      tmW, tmX, Y, bias, N, T, K, ldY, p.splits, ws, counters, epi_mode, ar, qw);
   OXB_CHECK_LAUNCH();
   return 0;
+}
+
+// dispatch on the token tile for a packed-weight format
+template <int QT>
+int gemm_launch_mmq(const CUtensorMap& tmX, __nv_bfloat16* Y, const float* bias, int N, int T, int K, int ldY,
+                    const GemmPlan& p, float* ws, int* counters, int epi_mode, const ArArgs& ar, cudaStream_t stream,
+                    const QwArgs& qw) {
+  switch (p.tn) {
+    case 16: return gemm_launch<16, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw);
+    case 32: return gemm_launch<32, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw);
+    case 64: return gemm_launch<64, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw);
+    case 128: return gemm_launch<128, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw);
+    default: return gemm_launch<256, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw);
+  }
 }
 
 }  // namespace oxb

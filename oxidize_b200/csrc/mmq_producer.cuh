@@ -1,0 +1,155 @@
+// Dequant-fused operand staging for the tcgen05 GEMM ("MMQ"): producer warps read packed
+// weight blocks (Q4_K / Q6_K / Q8_0 / Q4_0 / NVFP4, or block-scaled fp8), decode 64 values of one
+// weight row to bf16 in registers with the scales folded in, and store them straight into the
+// 128-byte-swizzled K-major shared-memory tile that the UMMA descriptor expects — the weights are
+// never materialised as bf16 in global memory.
+//
+// Folding the scales during staging (not in the epilogue) is the lesson of the reference's first
+// tensor-core MMQ revision, whose fp32 scale epilogue took ~75 % of kernel time
+// (oxidize-c/src/backends/cuda_mmq.cu:1885-1892); its kernels are k_mmq_gemm_xh_q4k / _q6k
+// (:2158) on mma.sync.m16n8k8.
+#pragma once
+#include <cuda_fp8.h>
+#include "common.cuh"
+#include "quant_blocks.cuh"
+
+namespace oxb {
+
+constexpr int QT_FP8B = 9;  // e4m3 codes [N, K] + f32 scale per 128 input channels
+
+struct QwArgs {
+  const uint8_t* w;      // packed rows
+  size_t row_bytes;      // bytes per weight row
+  const float* scales;   // FP8B only: [N, K/128]
+  int scale_ld;          // FP8B only: scales per row
+};
+
+__device__ __forceinline__ uint32_t ld_u16(const uint8_t* p) { return *reinterpret_cast<const uint16_t*>(p); }
+
+// Decode values [k0, k0+64) of the row at `rowp` into 32 packed bf16 pairs.
+template <int QT>
+__device__ __forceinline__ void dequant64(const uint8_t* rowp, int k0, const QwArgs& qw, int n, uint32_t* out) {
+  if constexpr (QT == QT_Q4_K) {
+    const uint8_t* b = rowp + (size_t)(k0 >> 8) * 144;
+    const int c = (k0 & 255) >> 6;
+    const uint32_t dd = *reinterpret_cast<const uint32_t*>(b);
+    const float d = __half2float(__ushort_as_half((unsigned short)(dd & 0xFFFF)));
+    const float dmin = __half2float(__ushort_as_half((unsigned short)(dd >> 16)));
+    int sc0, m0, sc1, m1;
+    scale_min_k4(2 * c, b + 4, sc0, m0);
+    scale_min_k4(2 * c + 1, b + 4, sc1, m1);
+    const float s0 = d * (float)sc0, o0 = dmin * (float)m0, s1 = d * (float)sc1, o1 = dmin * (float)m1;
+    const uint4 qa = *reinterpret_cast<const uint4*>(b + 16 + 32 * c);
+    const uint4 qb = *reinterpret_cast<const uint4*>(b + 32 + 32 * c);
+    const uint32_t q[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t lo0 = (q[w] >> (16 * h)) & 0xF, lo1 = (q[w] >> (16 * h + 8)) & 0xF;
+        const uint32_t hi0 = (q[w] >> (16 * h + 4)) & 0xF, hi1 = (q[w] >> (16 * h + 12)) & 0xF;
+        out[w * 2 + h] = pack_bf16x2(s0 * (float)lo0 - o0, s0 * (float)lo1 - o0);
+        out[16 + w * 2 + h] = pack_bf16x2(s1 * (float)hi0 - o1, s1 * (float)hi1 - o1);
+      }
+    }
+  } else if constexpr (QT == QT_Q6_K) {
+    const uint8_t* b = rowp + (size_t)(k0 >> 8) * 210;
+    const int c = (k0 & 255) >> 6, half = c >> 1, hi_nib = c & 1;
+    const uint8_t* ql = b + half * 64;
+    const uint8_t* qh = b + 128 + half * 32;
+    const int8_t* sc = reinterpret_cast<const int8_t*>(b + 192) + half * 8 + 4 * hi_nib;
+    const float d = __half2float(__ushort_as_half((unsigned short)ld_u16(b + 208)));
+    // quarter kq = 2*hi_nib + s (s = 0: ql[0..31], s = 1: ql[32..63]); value index = s*32 + l
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const int kq = 2 * hi_nib + s;
+#pragma unroll
+      for (int l = 0; l < 32; l += 2) {
+        const uint32_t lo2 = ld_u16(ql + s * 32 + l), h2 = ld_u16(qh + l);
+        float v[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const uint32_t lb = (lo2 >> (8 * e)) & 0xFF, hb = (h2 >> (8 * e)) & 0xFF;
+          const int q4 = hi_nib ? (lb >> 4) : (lb & 0xF);
+          const int q = (q4 | (((hb >> (2 * kq)) & 3) << 4)) - 32;
+          v[e] = d * (float)sc[2 * s + ((l + e) >> 4)] * (float)q;
+        }
+        out[(s * 32 + l) >> 1] = pack_bf16x2(v[0], v[1]);
+      }
+    }
+  } else if constexpr (QT == QT_Q8_0) {
+#pragma unroll
+    for (int blk = 0; blk < 2; ++blk) {
+      const uint8_t* b = rowp + (size_t)((k0 >> 5) + blk) * 34;
+      const float d = __half2float(__ushort_as_half((unsigned short)ld_u16(b)));
+#pragma unroll
+      for (int l = 0; l < 32; l += 2) {
+        const uint32_t w = ld_u16(b + 2 + l);
+        out[blk * 16 + (l >> 1)] = pack_bf16x2(d * (float)(int8_t)(w & 0xFF), d * (float)(int8_t)(w >> 8));
+      }
+    }
+  } else if constexpr (QT == QT_Q4_0) {
+#pragma unroll
+    for (int blk = 0; blk < 2; ++blk) {
+      const uint8_t* b = rowp + (size_t)((k0 >> 5) + blk) * 18;
+      const float d = __half2float(__ushort_as_half((unsigned short)ld_u16(b)));
+      // byte j holds value j (low nibble) and value j+16 (high nibble)
+#pragma unroll
+      for (int j = 0; j < 16; j += 2) {
+        const uint32_t w = ld_u16(b + 2 + j);
+        out[blk * 16 + (j >> 1)] = pack_bf16x2(d * (float)((int)(w & 0xF) - 8), d * (float)((int)((w >> 8) & 0xF) - 8));
+        out[blk * 16 + 8 + (j >> 1)] = pack_bf16x2(d * (float)((int)((w >> 4) & 0xF) - 8), d * (float)((int)(w >> 12) - 8));
+      }
+    }
+  } else if constexpr (QT == QT_NVFP4) {
+    const uint32_t* b = reinterpret_cast<const uint32_t*>(rowp + (size_t)(k0 >> 6) * 36);
+    const uint32_t sw = b[0];
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const float sc = ue4m3_half((uint8_t)(sw >> (8 * s)));
+      const uint32_t w0 = b[1 + 2 * s], w1 = b[2 + 2 * s];
+      // byte j (0..7) holds value j (low) and j+8 (high) of the 16-value sub-block
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t byte = ((j < 4 ? w0 : w1) >> (8 * (j & 3))) & 0xFF;
+        v[j] = sc * e2m1_doubled((int)(byte & 0xF));
+        v[j + 8] = sc * e2m1_doubled((int)(byte >> 4));
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) out[s * 8 + j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+    }
+  } else if constexpr (QT == QT_FP8B) {
+    const uint8_t* b = rowp + k0;
+    const float sc = qw.scales[(size_t)n * qw.scale_ld + (k0 >> 7)];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint4 q = *reinterpret_cast<const uint4*>(b + 16 * c);
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)((w[i] >> (16 * h)) & 0xFFFF), __NV_E4M3);
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+          out[c * 8 + i * 2 + h] = pack_bf16x2(f.x * sc, f.y * sc);
+        }
+      }
+    }
+  }
+}
+
+// Store one row's 64 bf16 (32 packed words) into the 128B-swizzled tile: 16-byte chunk c of row r
+// lives at r*128 + ((c ^ (r & 7)) << 4), the same pattern a 128B-swizzle TMA load produces.
+__device__ __forceinline__ void store_row_sw128(uint8_t* tile, int r, const uint32_t* v) {
+  uint8_t* rowp = tile + r * 128;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint4 u = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+    *reinterpret_cast<uint4*>(rowp + ((c ^ (r & 7)) << 4)) = u;
+  }
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+}  // namespace oxb

@@ -106,6 +106,39 @@ OXB_API int oxb_gemm_bf16(const void* X, const void* W, void* Y, const float* bi
   }
 }
 
+// Y[T, N] = X[T, K] (bf16) · dequant(Wq)[N, K]^T for packed weights (qtype as in quant_blocks.cuh, or
+// 9 = block-scaled fp8 with `scales` [N, scale_ld]).  The blocks are decoded inside the GEMM by its
+// producer warps; nothing is dequantized to global memory.  K must be a multiple of 64.
+OXB_API int oxb_gemm_quant(const void* X, const void* Wq, int qtype, size_t row_bytes, const float* scales, int scale_ld,
+                           void* Y, const float* bias, int T, int N, int K, int ldY, int epi_mode, int splits_hint,
+                           void* ws, size_t ws_bytes, int* counters, int n_counters, cudaStream_t stream) {
+  if (T <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % 64 != 0) return (int)cudaErrorInvalidValue;
+  GemmPlan p = gemm_plan(T, N, K, splits_hint, sm_count());
+  while (p.splits > 1 && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || ws == nullptr || counters == nullptr ||
+                          p.n_tiles * p.t_tiles * p.splits > sm_count()))
+    p = gemm_plan(T, N, K, p.splits - 1, sm_count());
+  CUtensorMap tmX;
+  int e = oxb_make_tmap_2d(&tmX, X, T, K, (uint64_t)K * 2, p.tn, GEMM_BK, 2);
+  if (e) return e;
+  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(Y);
+  float* wsf = reinterpret_cast<float*>(ws);
+  ArArgs ar;
+  memset(&ar, 0, sizeof(ar));
+  QwArgs qw{reinterpret_cast<const uint8_t*>(Wq), row_bytes, scales, scale_ld};
+  switch (qtype) {
+    case QT_Q4_K: return gemm_launch_mmq<QT_Q4_K>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
+    case QT_Q6_K: return gemm_launch_mmq<QT_Q6_K>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
+    case QT_Q8_0: return gemm_launch_mmq<QT_Q8_0>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
+    case QT_Q4_0: return gemm_launch_mmq<QT_Q4_0>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
+    case QT_NVFP4: return gemm_launch_mmq<QT_NVFP4>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
+    case QT_FP8B:
+      if (scales == nullptr) return (int)cudaErrorInvalidValue;
+      return gemm_launch_mmq<QT_FP8B>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
+    default: return (int)cudaErrorInvalidValue;
+  }
+}
+
 static int fill_ar(ArArgs& ar, int world, int rank, const uint64_t* data_ptrs, const uint64_t* flag_ptrs, int* ctrl,
                    int t_max, int n_max, int max_tiles, unsigned long long timeout_ns, const void* residual) {
   memset(&ar, 0, sizeof(ar));

@@ -1,8 +1,10 @@
-"""Linear layers over block-quantized weights on the GPU.
+"""Linear layers over packed weights (Q4_K / Q6_K / Q8_0 / Q4_0 / NVFP4 GGUF blocks and
+block-scaled fp8) on the GPU.
 
-Small batches (the bandwidth-bound decode regime) run the fused dequant GEMV kernels that read
-the packed blocks once; larger batches decode the blocks to a bf16 staging buffer and run the
-tcgen05 GEMM on it.
+All batch sizes — single-token decode included — run ``oxb_gemm_quant``: the tcgen05 GEMM whose
+producer warps decode the blocks into the swizzled shared-memory operand tile, so the weights
+are read from HBM once, in their packed form.  Formats without a fused decoder (Q5_K, Q4_1 …),
+or a K that is not a multiple of 64, are decoded to a bf16 staging buffer first.
 """
 from __future__ import annotations
 
@@ -10,18 +12,24 @@ import torch
 
 from . import cuda as C
 
-GEMV_MAX_TOKENS = 8
+FUSED_TYPES = {"Q4_K": 5, "Q6_K": 7, "Q8_0": 3, "Q4_0": 4, "NVFP4": 8}
+QT_FP8B = 9
+
+
+def _launch(x, data_ptr, qt, row_bytes, scales_ptr, scale_ld, out_view, bias, ld_out, N, K):
+    s = C.scratch(x.device)
+    C._check(C.lib().oxb_gemm_quant(x.data_ptr(), data_ptr, qt, row_bytes, scales_ptr, scale_ld, out_view.data_ptr(),
+                                    C._p(bias), x.shape[0], N, K, ld_out, 0, 0, s.gemm_ws.data_ptr(),
+                                    s.gemm_ws.numel() * 4, s.gemm_counters.data_ptr(), s.gemm_counters.numel(),
+                                    C._stream()), "oxb_gemm_quant")
+    return out_view
 
 
 def linear_quant(x, p, out_view, bias, ld_out):
-    T = x.shape[0]
-    if T <= GEMV_MAX_TOKENS and hasattr(C.lib(), "oxb_gemv_quant") and C.QTYPE_CODE.get(p.qtype) is not None:
-        row_bytes = p.data.stride(0) * p.data.element_size()
-        C._check(C.lib().oxb_gemv_quant(x.data_ptr(), p.data.data_ptr(), C.QTYPE_CODE[p.qtype], row_bytes,
-                                        out_view.data_ptr(), C._p(bias), T, p.shape[0], p.shape[1], ld_out,
-                                        C._stream()), "oxb_gemv_quant")
-        return out_view
     n, k = p.shape
+    if p.qtype in FUSED_TYPES and k % 64 == 0:
+        row_bytes = p.data.stride(0) * p.data.element_size()
+        return _launch(x, p.data.data_ptr(), FUSED_TYPES[p.qtype], row_bytes, None, 0, out_view, bias, ld_out, n, k)
     buf = C.scratch(x.device).dequant_buf(n * k)[: n * k].view(n, k)
     C.dequant_rows(p, buf)
     C.gemm_bf16(x, buf, out_view, bias, ld_out=ld_out)
@@ -29,4 +37,7 @@ def linear_quant(x, p, out_view, bias, ld_out):
 
 
 def linear_fp8(x, p, out_view, bias, ld_out):
-    raise NotImplementedError("block-scaled fp8 linear is not built yet")
+    n, k = p.shape
+    if p.block != 128 or k % 128 != 0:
+        raise ValueError("block-scaled fp8 weights need 128-channel blocks and K % 128 == 0")
+    return _launch(x, p.data.data_ptr(), QT_FP8B, k, p.scales.data_ptr(), p.scales.shape[1], out_view, bias, ld_out, n, k)

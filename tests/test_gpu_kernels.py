@@ -265,3 +265,48 @@ def test_model_gpu_matches_cpu(C, tmp_path):
         lc, lg = cpu.last_step[1].logits, gpu.last_step[1].logits
         assert _rel_err(lg.cpu(), lc) < 3e-2
     _check_status(C)
+
+
+@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q8_0", "Q4_0", "NVFP4", "FP8B"])
+@pytest.mark.parametrize("T,N,K", [(1, 256, 512), (7, 200, 1024), (64, 1280, 2048), (300, 384, 768)])
+def test_linear_packed_weights_fused_dequant(C, qtype, T, N, K):
+    """tcgen05 GEMM with in-kernel block decode vs fp32 matmul on the NumPy-decoded weights."""
+    from oxidize_b200.models.weights import qtensor_from_dense
+
+    if qtype in ("Q4_K", "Q6_K") and K % 256:
+        pytest.skip("k-quants need whole 256-value super-blocks")
+    if qtype == "FP8B" and K % 128:
+        pytest.skip("fp8 blocks are 128 wide")
+    torch.manual_seed(T + N)
+    w = qtensor_from_dense(torch.randn(N, K) * 0.05, qtype, device="cuda")
+    x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
+    want = x.float().cpu() @ w.to("cpu").dense_cache().t()
+    got = C.linear(x, [w])
+    torch.cuda.synchronize()
+    _check_status(C)
+    assert _rel_err(got.cpu(), want) < 8e-3
+    assert torch.equal(got, C.linear(x, [w]))
+
+
+def test_quantized_model_gpu_matches_cpu(C, tmp_path):
+    from oxidize_b200.engine.llm import LLM, EngineConfig
+    from oxidize_b200.engine.sampler import SamplingParams
+    from oxidize_b200.models.config import preset
+    from oxidize_b200.utils.synth import synth_gguf
+
+    cfg = preset("tiny-llama", n_layers=2, vocab_size=512)
+    path = str(tmp_path / "tinyq.gguf")
+    synth_gguf(path, cfg, "Q4_K_M", seed=0, norm_jitter=0.1)
+    ec = dict(max_model_len=128, max_num_seqs=4, num_kv_blocks=64, prefill_chunk_size=32, max_num_batched_tokens=64)
+    sp = SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True)
+    cpu = LLM.from_gguf(path, EngineConfig(**ec), device="cpu")
+    gpu = LLM.from_gguf(path, EngineConfig(**ec, cuda_graphs=False, kv_cache_dtype="q8"), device="cuda")
+    cpu.runner.keep_logits = gpu.runner.keep_logits = True
+    for p in ([5, 9, 200, 31, 7], list(range(3, 40))):
+        cpu.add_request(p, sp)
+        gpu.add_request(p, sp)
+    while cpu.has_unfinished:
+        cpu.step()
+        gpu.step()
+        assert _rel_err(gpu.last_step[1].logits.cpu(), cpu.last_step[1].logits) < 5e-2
+    _check_status(C)
