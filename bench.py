@@ -48,6 +48,9 @@ def parse_args():
     ap.add_argument("--kv-dtype", default="bf16")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the result invalid)")
+    ap.add_argument("--shard-sim", type=int, default=0,
+                    help="debug only: run ONE rank's shard shapes of an N-way tensor-parallel job on one GPU, without "
+                         "collectives (marks the result invalid); used to profile per-GPU kernels of the TP8 config")
     ap.add_argument("--no-prefill", action="store_true",
                     help="fill the KV cache with random pages instead of running the prompts through prefill")
     return ap.parse_args()
@@ -128,6 +131,12 @@ def main():
     cfg = preset(args.model)
     if args.layers:
         cfg.n_layers = args.layers
+    if args.shard_sim > 1:
+        n = args.shard_sim
+        cfg.n_heads //= n
+        cfg.n_kv_heads = max(1, cfg.n_kv_heads // n)
+        cfg.ffn_size //= n
+        cfg.vocab_size //= n
     B = args.batch
     rng = np.random.default_rng(0)
     prompt_lens = rng.integers(args.prompt_min, args.prompt_max + 1, size=B)
@@ -254,7 +263,7 @@ def main():
                        "mean_context": float(ctx.mean()), "parallelism": f"tp{world}", "weights": args.quant,
                        "kv_cache": f"paged, {page}-token pages, {args.kv_dtype}", "comm": args.comm if world > 1 else "none",
                        "l2_policy": "inputs larger than L2 (weight shard + KV pages streamed every step)",
-                       "layers": cfg.n_layers, "valid": not bool(args.layers)},
+                       "layers": cfg.n_layers, "valid": not bool(args.layers or args.shard_sim)},
             "e2e": {"value": round(e2e_val, 2), "unit": "tok/s", "ms_per_step": round(max(e2e_ms, e2e_wall_ms) / args.steps, 4),
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": int(launches_per_step * args.steps) if graph is not None else int(C.launch_count),

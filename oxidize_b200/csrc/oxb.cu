@@ -299,6 +299,16 @@ OXB_API int oxb_argmax(const float* logits, int R, int V, int ld, int tie_highes
   return 0;
 }
 
+// Per-row sampling of fp32 logits [R, V] (row stride ld) with per-row knobs and uniforms.
+OXB_API int oxb_sample(const float* logits, int R, int V, int ld, const float* temperature, const int* top_k,
+                       const float* top_p, const float* min_p, const float* random, int tie_highest, int* out,
+                       cudaStream_t stream) {
+  if (R <= 0) return 0;
+  sample_kernel<<<R, SMP_THREADS, 0, stream>>>(logits, V, ld, temperature, top_k, top_p, min_p, random, tie_highest, out);
+  OXB_CHECK_LAUNCH();
+  return 0;
+}
+
 // ----------------------------------------------------------------------------- attention
 // Sizes of the split-KV scratch for a launch shape (floats).
 OXB_API int oxb_attn_ws_floats(int B, int nkv, int max_mtiles, int n_cta_splits, int hd, size_t* o_floats,

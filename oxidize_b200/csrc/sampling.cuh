@@ -1,2 +1,285 @@
+// Device sampling: one CTA per logits row.
+//
+// Row r draws with temperature[r] (<= 0: greedy with the configured tie rule), top_k[r] (0: off),
+// top_p[r], min_p[r] and the host-supplied uniform random[r], in the order of the reference's
+// sampler (oxidize-core/src/model/sampling.rs:268-463): softmax over the full vocabulary, keep a
+// prefix of the descending order (top-k, then top-p "through the first index whose cumulative
+// mass reaches p", then min-p), inverse CDF with target = random * sum(kept).  Rows without any
+// filter use the reference's single-pass rule: inverse CDF in *index* order (:465-490).
+//
+// The kept prefix is found without sorting the vocabulary: tokens are ordered by a 64-bit key
+// (probability bits descending, index ascending) and every question about the sorted order
+// ("how many tokens / how much mass lies before key x") is answered by a radix descent over
+// the key bits — 8 bits per pass, per-bin counts and masses accumulated in shared memory.
 #pragma once
 #include "common.cuh"
+
+namespace oxb {
+
+constexpr int SMP_THREADS = 1024;
+
+struct BlockScan {
+  // inclusive scan of one float per thread across the block; returns (inclusive, block total)
+  __device__ static float2 run(float v, float* warp_tot /*[32]*/) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    float x = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    __syncthreads();
+    if (lane == 31) warp_tot[warp] = x;
+    __syncthreads();
+    float base = 0.f, total = 0.f;
+    for (int w = 0; w < nw; ++w) {
+      const float t = warp_tot[w];
+      if (w < warp) base += t;
+      total += t;
+    }
+    return make_float2(x + base, total);
+  }
+};
+
+// monotone map float -> uint32 (larger float -> larger uint); probabilities are >= 0
+__device__ __forceinline__ uint32_t prob_bits(float p) { return __float_as_uint(p); }
+
+// For the tokens whose probability bits match `prefix` on the top `done_bits` bits, accumulate
+// per-bin (next 8 bits) count and mass into shared histograms.
+__device__ __forceinline__ void radix_pass(const float* __restrict__ row, int V, float mx, float inv_t, uint32_t prefix,
+                                           int done_bits, int* cnt, float* mass) {
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+    cnt[i] = 0;
+    mass[i] = 0.f;
+  }
+  __syncthreads();
+  const int shift = 24 - done_bits;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float p = __expf((row[i] - mx) * inv_t);
+    const uint32_t b = prob_bits(p);
+    if (done_bits == 0 || (b >> (32 - done_bits)) == (prefix >> (32 - done_bits))) {
+      const int bin = (b >> shift) & 0xFF;
+      atomicAdd(&cnt[bin], 1);
+      atomicAdd(&mass[bin], p);
+    }
+  }
+  __syncthreads();
+}
+
+// Find the probability-bits value x such that, walking the vocabulary in descending probability,
+// the walk crosses the boundary defined by (count limit, mass limit) inside the tokens whose
+// bits equal x.  Returns x and the count / mass strictly above x.
+__device__ void radix_descend(const float* row, int V, float mx, float inv_t, int count_limit, float mass_limit,
+                              int* cnt, float* mass, int* s_i, float* s_f, uint32_t& x, int& cnt_above, float& mass_above) {
+  uint32_t prefix = 0;
+  int ca = 0;
+  float ma = 0.f;
+  for (int done = 0; done < 32; done += 8) {
+    radix_pass(row, V, mx, inv_t, prefix, done, cnt, mass);
+    if (threadIdx.x == 0) {
+      int c = ca;
+      float m = ma;
+      int bin = 255;
+      for (; bin > 0; --bin) {
+        // stop in the first bin (from the top) where the boundary falls
+        if (c + cnt[bin] >= count_limit || m + mass[bin] >= mass_limit) break;
+        c += cnt[bin];
+        m += mass[bin];
+      }
+      s_i[0] = bin;
+      s_i[1] = c;
+      s_f[0] = m;
+    }
+    __syncthreads();
+    prefix |= (uint32_t)s_i[0] << (24 - done);
+    ca = s_i[1];
+    ma = s_f[0];
+    __syncthreads();
+  }
+  x = prefix;
+  cnt_above = ca;
+  mass_above = ma;
+}
+
+__global__ void __launch_bounds__(SMP_THREADS)
+sample_kernel(const float* __restrict__ logits, int V, int ld, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
+              const float* __restrict__ random, int tie_highest, int* __restrict__ out) {
+  __shared__ float red[32];
+  __shared__ int cnt[256];
+  __shared__ float mass[256];
+  __shared__ int s_i[4];
+  __shared__ float s_f[4];
+  __shared__ int s_best;
+  const int r = blockIdx.x;
+  const float* row = logits + (size_t)r * ld;
+  const float T = temperature[r];
+  // ---- max (and greedy argmax)
+  float mx = -INFINITY;
+  int bi = -1;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = row[i];
+    if (bi < 0 || v > mx || (v == mx && tie_highest)) {
+      if (!(v != v)) {
+        mx = v;
+        bi = i;
+      }
+    }
+  }
+  {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    auto better = [&](float v, int i, float bv, int b) {
+      if (i < 0) return false;
+      if (b < 0) return true;
+      return v > bv || (v == bv && (tie_highest ? i > b : i < b));
+    };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, mx, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (better(ov, oi, mx, bi)) {
+        mx = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0) {
+      sv[warp] = mx;
+      si[warp] = bi;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      mx = sv[lane];
+      bi = si[lane];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, mx, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, mx, bi)) {
+          mx = ov;
+          bi = oi;
+        }
+      }
+      if (lane == 0) {
+        s_f[1] = mx;
+        s_best = bi < 0 ? 0 : bi;
+      }
+    }
+    __syncthreads();
+    mx = s_f[1];
+  }
+  const int k = top_k[r];
+  if (T <= 0.f || k == 1 || !(mx > -INFINITY)) {
+    if (threadIdx.x == 0) out[r] = s_best;
+    return;
+  }
+  const float inv_t = 1.f / T;
+  // ---- total mass
+  float part = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) part += __expf((row[i] - mx) * inv_t);
+  const float total = block_sum(part, red);
+  if (!(total > 0.f) || !isfinite(total)) {
+    if (threadIdx.x == 0) out[r] = s_best;
+    return;
+  }
+  const float tp = top_p[r], mp = min_p[r], rnd = random[r];
+  const bool filtered = k > 0 || tp < 1.f || mp > 0.f;
+  if (threadIdx.x == 0) s_i[2] = 0x7fffffff;
+  __syncthreads();
+  if (!filtered) {
+    // inverse CDF in index order
+    const float target = rnd * total;
+    float run = 0.f;
+    for (int base = 0; base < V; base += blockDim.x) {
+      const int i = base + threadIdx.x;
+      const float p = i < V ? __expf((row[i] - mx) * inv_t) : 0.f;
+      const float2 sc = BlockScan::run(p, red);
+      const float incl = run + sc.x;
+      if (i < V && incl > target && incl - p <= target) atomicMin(&s_i[2], i);
+      run += sc.y;
+      __syncthreads();
+      if (s_i[2] != 0x7fffffff) break;
+    }
+    if (threadIdx.x == 0) out[r] = s_i[2] == 0x7fffffff ? V - 1 : s_i[2];
+    return;
+  }
+  // ---- filtered: find the end of the kept prefix of the descending order
+  // kept = first min(top_k, n_p, n_minp) tokens, where n_p counts tokens whose mass-before < top_p * total
+  const int klim = k > 0 ? k : V;
+  const float plim = tp < 1.f ? tp * total : INFINITY;
+  uint32_t xb;
+  int c_above;
+  float m_above;
+  radix_descend(row, V, mx, inv_t, klim, plim, cnt, mass, s_i, s_f, xb, c_above, m_above);
+  // tokens with bits > xb are kept entirely; tokens with bits == xb are kept in index order while
+  // the limits allow; min-p cuts by value on top of that
+  const float pmin_keep = mp > 0.f ? mp * 1.0f /* p_max = exp(0) = 1 */ : 0.f;
+  // kept mass: (a) everything above xb that also passes min-p, (b) the admitted part of the tie group
+  // First count how many of the tie group are admitted.
+  const float px = __uint_as_float(xb);
+  int admit = 0;
+  {
+    int room_k = klim - c_above;
+    // through the first index whose cumulative reaches top_p: tokens whose mass-before < plim
+    float room_p = plim - m_above;
+    int by_p = px > 0.f ? (int)ceilf(room_p / px) : 0x7fffffff;
+    if (room_p == INFINITY) by_p = 0x7fffffff;
+    admit = max(0, min(room_k, by_p));
+    if (c_above == 0 && admit == 0) admit = 1;  // always keep the top token
+  }
+  // kept sum
+  float ks = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float p = __expf((row[i] - mx) * inv_t);
+    if (prob_bits(p) > xb && p >= pmin_keep) ks += p;
+  }
+  float kept = block_sum(ks, red);
+  int tie_total = 0;
+  {
+    int tc = 0;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) tc += prob_bits(__expf((row[i] - mx) * inv_t)) == xb;
+    tie_total = (int)(block_sum((float)tc, red) + 0.5f);
+  }
+  const bool ties_pass_minp = px >= pmin_keep;
+  const int tie_kept = ties_pass_minp ? min(admit, tie_total) : 0;
+  kept += (float)tie_kept * px;
+  if (!(kept > 0.f)) {
+    if (threadIdx.x == 0) out[r] = s_best;
+    return;
+  }
+  // ---- draw: walk the kept prefix in sorted order until the running mass exceeds target
+  const float target = rnd * kept;
+  uint32_t yb;
+  int c2;
+  float m2;
+  // boundary where mass-before exceeds target (no count limit); restrict to kept tokens by
+  // noting that kept tokens form a prefix, so the walk never leaves it when target < kept
+  radix_descend(row, V, mx, inv_t, 0x7fffffff, nextafterf(target, INFINITY), cnt, mass, s_i, s_f, yb, c2, m2);
+  // inside the tie group of yb, tokens are ordered by index: pick the j-th
+  const float py = __uint_as_float(yb);
+  int j = py > 0.f ? (int)floorf((target - m2) / py) : 0;
+  if (yb == xb) j = min(j, max(tie_kept - 1, 0));
+  j = max(j, 0);
+  // select the j-th token (by index) with bits == yb
+  if (threadIdx.x == 0) s_i[2] = 0x7fffffff;
+  __syncthreads();
+  int seen = 0;
+  for (int base = 0; base < V; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    const int hit = (i < V && prob_bits(__expf((row[i] - mx) * inv_t)) == yb) ? 1 : 0;
+    const float2 sc = BlockScan::run((float)hit, red);
+    const int incl = seen + (int)(sc.x + 0.5f);
+    if (hit && incl - 1 == j) s_i[2] = i;
+    seen += (int)(sc.y + 0.5f);
+    __syncthreads();
+    if (s_i[2] != 0x7fffffff) break;
+  }
+  if (threadIdx.x == 0) {
+    int tok = s_i[2];
+    if (tok == 0x7fffffff) tok = s_best;  // numerical corner: fall back to the mode
+    out[r] = tok;
+  }
+}
+
+}  // namespace oxb

@@ -58,7 +58,8 @@ def _declare(L) -> None:
     L.oxb_argmax.argtypes = [vp, i32, i32, i32, i32, vp, vp, i32, vp]
     L.oxb_paged_attention.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp,
                                       vp, vp]
-    L.oxb_gemm_quant.argtypes = [vp, vp, i32, sz, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, sz, vp, i32, vp]
+    L.oxb_sample.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, vp, i32, vp, vp]
+    L.oxb_gemm_quant.argtypes =[vp, vp, i32, sz, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, sz, vp, i32, vp]
     u64p, ull = ctypes.POINTER(ctypes.c_uint64), ctypes.c_ulonglong
     L.oxb_gemm_ar.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, u64p, u64p, vp, i32, i32, i32, ull, vp, sz,
                               vp, i32, vp]
