@@ -5,8 +5,8 @@
 // shapes fill the M dimension of the tensor-core tile at decode time.  The CTA's four warps walk
 // disjoint, strided sets of 16-token KV pages (one page = one MMA k-step), each with a private
 // cp.async ring, and keep their own online-softmax state; partial (max, sum, O) results are
-// merged in shared memory, and across CTA splits by a small second kernel (split-KV with exact
-// log-sum-exp merge).  KV pages may be bf16, f16, or the symmetric per-32-channel q8 / q4
+// merged in shared memory, and across CTA splits by whichever split finishes last (atomic ticket;
+// split-KV with exact log-sum-exp merge, no second launch).  KV pages may be bf16, f16, or the symmetric per-32-channel q8 / q4
 // encodings, which are decoded to bf16 on the way into shared memory.
 //
 // Covers what the reference does with flash_attn_decode(_splitk/_reduce)
@@ -35,6 +35,7 @@ struct AttnArgs {
   float scale_log2;
   float* ws_o;   // [B*nkv*max_mtiles*n_cta_splits, 16, hd]
   float* ws_ml;  // [.., 16, 2]
+  int* counters; // [B*nkv*max_mtiles] zero-initialised tickets (CTA splits only)
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -128,6 +129,41 @@ __device__ __forceinline__ void decode_page(uint8_t* stage, uint8_t* dec, int kv
   }
 }
 
+// Merge the CTA-split partials of one (sequence, kv head, row tile): 128 threads = 16 rows x 8
+// column segments.  Partials were written by other CTAs, so they are read through L2 (__ldcg).
+template <int HD>
+__device__ __forceinline__ void attn_merge_rows(const AttnArgs& a, int G, int b, int kvh, int mtile, int q0, int R, int tid) {
+  const int row = tid >> 3, seg = (tid & 7) * (HD / 8);
+  const int r = mtile * 16 + row;
+  if (r >= R) return;
+  const int gx = a.max_mtiles * a.n_cta_splits;
+  const size_t task0 = ((size_t)b * a.nkv + kvh) * gx + (size_t)mtile * a.n_cta_splits;
+  float M = -INFINITY;
+  for (int s = 0; s < a.n_cta_splits; ++s) M = fmaxf(M, __ldcg(a.ws_ml + ((task0 + s) * 16 + row) * 2));
+  float L = 0.f;
+  float acc[HD / 8];
+#pragma unroll
+  for (int d = 0; d < HD / 8; ++d) acc[d] = 0.f;
+  for (int s = 0; s < a.n_cta_splits; ++s) {
+    const float ms = __ldcg(a.ws_ml + ((task0 + s) * 16 + row) * 2);
+    const float w = ms == -INFINITY ? 0.f : exp2f(ms - M);
+    L += w * __ldcg(a.ws_ml + ((task0 + s) * 16 + row) * 2 + 1);
+    const float4* src = reinterpret_cast<const float4*>(a.ws_o + ((task0 + s) * 16 + row) * HD + seg);
+#pragma unroll
+    for (int d = 0; d < HD / 32; ++d) {
+      const float4 v = __ldcg(src + d);
+      acc[4 * d] += w * v.x;
+      acc[4 * d + 1] += w * v.y;
+      acc[4 * d + 2] += w * v.z;
+      acc[4 * d + 3] += w * v.w;
+    }
+  }
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  __nv_bfloat16* dst = a.out + ((size_t)(q0 + r / G) * a.nq + kvh * G + r % G) * HD + seg;
+#pragma unroll
+  for (int d = 0; d < HD / 8; d += 2) *reinterpret_cast<uint32_t*>(dst + d) = pack_bf16x2(acc[d] * inv, acc[d + 1] * inv);
+}
+
 template <int HD>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
@@ -136,6 +172,8 @@ paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
   constexpr int KS = HD / 16;  // k-steps for QK^T
   constexpr int NT = HD / 8;   // n-tiles of the output
   extern __shared__ __align__(16) uint8_t att_smem[];
+  pdl_launch_dependents();
+  pdl_wait();
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
@@ -372,37 +410,20 @@ paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
       }
     }
   }
-}
-
-// Cross-CTA split merge: grid (max_mtiles, nkv, B), 128 threads (16 rows x 8 segments)
-template <int HD>
-__global__ void attn_merge_kernel(const AttnArgs a, int G) {
-  const int b = blockIdx.z, kvh = blockIdx.y, mtile = blockIdx.x;
-  const int q0 = a.query_start[b], qlen = a.query_start[b + 1] - q0;
-  const int R = qlen * G;
-  const int row = threadIdx.x >> 3, seg = (threadIdx.x & 7) * (HD / 8);
-  const int r = mtile * 16 + row;
-  if (r >= R) return;
-  const int gx = a.max_mtiles * a.n_cta_splits;
-  const size_t task0 = ((size_t)b * a.nkv + kvh) * gx + (size_t)mtile * a.n_cta_splits;
-  float M = -INFINITY;
-  for (int s = 0; s < a.n_cta_splits; ++s) M = fmaxf(M, a.ws_ml[((task0 + s) * 16 + row) * 2]);
-  float L = 0.f;
-  float acc[HD / 8];
-#pragma unroll
-  for (int d = 0; d < HD / 8; ++d) acc[d] = 0.f;
-  for (int s = 0; s < a.n_cta_splits; ++s) {
-    const float ms = a.ws_ml[((task0 + s) * 16 + row) * 2];
-    const float w = ms == -INFINITY ? 0.f : exp2f(ms - M);
-    L += w * a.ws_ml[((task0 + s) * 16 + row) * 2 + 1];
-    const float* src = a.ws_o + ((task0 + s) * 16 + row) * HD + seg;
-#pragma unroll
-    for (int d = 0; d < HD / 8; ++d) acc[d] += w * src[d];
+  if (a.n_cta_splits > 1) {
+    // the last CTA split of this row tile to finish merges all partials (no second launch)
+    __shared__ int s_ticket;
+    __threadfence();
+    __syncthreads();
+    int* cnt = a.counters + ((size_t)b * a.nkv + kvh) * a.max_mtiles + mtile;
+    if (threadIdx.x == 0) s_ticket = atomicAdd(cnt, 1);
+    __syncthreads();
+    if (s_ticket == a.n_cta_splits - 1) {
+      __threadfence();
+      attn_merge_rows<HD>(a, G, b, kvh, mtile, q0, R, threadIdx.x);
+      if (threadIdx.x == 0) *cnt = 0;  // re-armed for the next launch / graph replay
+    }
   }
-  const float inv = L > 0.f ? 1.f / L : 0.f;
-  __nv_bfloat16* dst = a.out + ((size_t)(q0 + r / G) * a.nq + kvh * G + r % G) * HD + seg;
-#pragma unroll
-  for (int d = 0; d < HD / 8; d += 2) *reinterpret_cast<uint32_t*>(dst + d) = pack_bf16x2(acc[d] * inv, acc[d + 1] * inv);
 }
 
 }  // namespace oxb

@@ -140,6 +140,8 @@ allreduce_oneshot_kernel(const ArArgs ar, const __nv_bfloat16* __restrict__ X, _
                          int ld) {
   extern __shared__ __align__(16) uint8_t ar_stage[];  // [T][256] bytes
   __shared__ int s_parity, s_abort;
+  pdl_launch_dependents();
+  pdl_wait();
   const int tid = threadIdx.x;
   const int n0 = blockIdx.x * 128;
   if (tid == 0) {

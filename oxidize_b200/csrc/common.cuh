@@ -237,3 +237,26 @@ PFN_encodeTiled oxb_get_encode_tiled();
 // 2-D row-major tensor [rows, cols] of `elem_bytes` elements, box [box_rows, box_cols], 128B swizzle
 int oxb_make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
                      uint32_t box_rows, uint32_t box_cols, int elem_bytes);
+
+// Programmatic dependent launch: a kernel started with this helper may begin (block scheduling,
+// shared-memory / barrier / TMEM set-up, loads of *static* data such as weights) while the previous
+// kernel in the stream is still draining; it must execute pdl_wait() before it touches anything the
+// previous kernel produced.  Kernels call pdl_launch_dependents() at their top so that the next
+// one can do the same.  With the switch off the launch is an ordinary stream-ordered one, in
+// which case griddepcontrol.* are no-ops.
+extern int g_oxb_pdl;  // 1 = on (default), 0 = off (OXB_PDL=0 or oxb_set_pdl(0))
+template <typename... KArgs, typename... Args>
+inline cudaError_t oxb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_oxb_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

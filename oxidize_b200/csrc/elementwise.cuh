@@ -14,6 +14,8 @@ namespace oxb {
 // one CTA per token; qtype as in quant_blocks.cuh
 __global__ void embed_kernel(const int* __restrict__ tokens, const uint8_t* __restrict__ table, int qtype,
                              size_t row_bytes, int H, int vocab, float scale, __nv_bfloat16* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   int tok = tokens[t];
   if (tok < 0 || tok >= vocab) tok = 0;
@@ -29,6 +31,8 @@ __global__ void add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __
                                    __nv_bfloat16* __restrict__ res_out, const float* __restrict__ w,
                                    __nv_bfloat16* __restrict__ y, int H, float eps) {
   extern __shared__ float rowbuf[];
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[32];
   const size_t base = (size_t)blockIdx.x * H;
   float ss = 0.f;
@@ -80,9 +84,73 @@ __global__ void add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __
   for (int i = threadIdx.x; i < H; i += blockDim.x) y[base + i] = __float2bfloat16(rowbuf[i] * inv * w[i]);
 }
 
+// Register-resident variant for H % 8 == 0 and H <= 8 * CH * 1024: every thread owns CH 16-byte
+// chunks of the row, the norm weights are fetched before the reduction so that only one memory
+// round trip sits in front of the block-wide sum, and nothing is staged in shared memory.
+template <int CH>
+__global__ void __launch_bounds__(1024)
+add_rmsnorm_reg_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res_in,
+                       __nv_bfloat16* __restrict__ res_out, const float* __restrict__ w,
+                       __nv_bfloat16* __restrict__ y, int H, float eps) {
+  __shared__ float red[32];
+  const size_t base = (size_t)blockIdx.x * H;
+  const int H8 = H >> 3;
+  float v[CH][8];
+  float4 w0[CH], w1[CH];
+  float ss = 0.f;
+  pdl_launch_dependents();
+  // the norm weights are static: fetch them before waiting for the upstream kernel
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int i = threadIdx.x + c * blockDim.x;
+    if (i < H8) {
+      w0[c] = *reinterpret_cast<const float4*>(w + i * 8);
+      w1[c] = *reinterpret_cast<const float4*>(w + i * 8 + 4);
+    }
+  }
+  pdl_wait();
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int i = threadIdx.x + c * blockDim.x;
+    if (i < H8) {
+      const uint4 xv = *reinterpret_cast<const uint4*>(x + base + i * 8);
+      uint4 rv = make_uint4(0, 0, 0, 0);
+      if (res_in != nullptr) rv = *reinterpret_cast<const uint4*>(res_in + base + i * 8);
+      const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w}, rs[4] = {rv.x, rv.y, rv.z, rv.w};
+      uint4 ov;
+      uint32_t* os = reinterpret_cast<uint32_t*>(&ov);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 a = unpack_bf16x2(xs[j]), b = unpack_bf16x2(rs[j]);
+        os[j] = pack_bf16x2(a.x + b.x, a.y + b.y);
+        const float2 f = unpack_bf16x2(os[j]);  // the norm sees the rounded residual
+        v[c][2 * j] = f.x;
+        v[c][2 * j + 1] = f.y;
+        ss += f.x * f.x + f.y * f.y;
+      }
+      if (res_out != nullptr) *reinterpret_cast<uint4*>(res_out + base + i * 8) = ov;
+    }
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / (float)H + eps);
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int i = threadIdx.x + c * blockDim.x;
+    if (i < H8) {
+      const float ww[8] = {w0[c].x, w0[c].y, w0[c].z, w0[c].w, w1[c].x, w1[c].y, w1[c].z, w1[c].w};
+      uint4 ov;
+      uint32_t* os = reinterpret_cast<uint32_t*>(&ov);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) os[j] = pack_bf16x2(v[c][2 * j] * inv * ww[2 * j], v[c][2 * j + 1] * inv * ww[2 * j + 1]);
+      *reinterpret_cast<uint4*>(y + base + i * 8) = ov;
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------- SwiGLU
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i]
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int T, int I) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int I8 = I >> 3;
   const size_t total = (size_t)T * I8;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -121,6 +189,8 @@ __global__ void qk_rope_kvwrite_kernel(const __nv_bfloat16* __restrict__ qkv, co
                                        const float* __restrict__ kn, float eps, int nq, int nkv, int hd,
                                        __nv_bfloat16* __restrict__ q_out, KvWriteArgs kv) {
   extern __shared__ float hbuf[];  // hd floats
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[32];
   const int t = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
   const int width = (nq + 2 * nkv) * hd;
@@ -194,6 +264,8 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int V, int ld, i
                               float* __restrict__ out_val, int index_offset) {
   __shared__ float sv[32];
   __shared__ int si[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const float* row = logits + (size_t)blockIdx.x * ld;
   float best = -INFINITY;
   int bi = -1;  // -1 = nothing seen yet

@@ -95,7 +95,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     mbar_init(accum, 1);
     *abort_flag = 0;
     ticket[0] = 0;
-    ticket[2] = ar.world > 0 ? (ar.ctrl[0] & 1) : 0;  // buffer parity of this collective call
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -106,6 +105,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();  // the next kernel may start its own set-up now
 
   if (warp == 0) {
     // ---------------- TMA producer
@@ -114,7 +114,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       tma_prefetch_desc(&tmX);
       const uint64_t pol_w = l2_policy_evict_first();  // weights are read once per step
       const uint64_t pol_x = l2_policy_evict_last();   // activations are re-read by every CTA
-      for (int i = 0; i < nkb; ++i) {
+      // Weights are static: the first ring's worth of weight tiles is requested before waiting for
+      // the upstream kernel, so the weight stream overlaps the previous kernel's tail.
+      const int npre = nkb < STAGES ? nkb : STAGES;
+      for (int i = 0; i < npre; ++i) {
+        uint8_t* sA = smem + i * Cfg::STAGE_BYTES;
+        if constexpr (MMQ) {
+          mbar_expect_tx(&full[i], Cfg::B_BYTES);
+        } else {
+          mbar_expect_tx(&full[i], Cfg::STAGE_BYTES);
+          tma_load_2d_hint(sA, &tmW, &full[i], (kb_begin + i) * GEMM_BK, n0, pol_w);
+        }
+      }
+      pdl_wait();  // activations come from the upstream kernel
+      for (int i = 0; i < npre; ++i) {
+        uint8_t* sB = smem + i * Cfg::STAGE_BYTES + Cfg::A_BYTES;
+        tma_load_2d_hint(sB, &tmX, &full[i], (kb_begin + i) * GEMM_BK, t0, pol_x);
+      }
+      for (int i = npre; i < nkb; ++i) {
         const int st = i % STAGES;
         const uint32_t ph = (i / STAGES) & 1;
         if (!mbar_wait_bounded(&empty[st], ph ^ 1, abort_flag, OXB_TIMEOUT_TMA_EMPTY, blockIdx.x)) break;
@@ -180,10 +197,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;  // row inside the 128-row tile
     const int n = n0 + row;
+    pdl_wait();  // everything below reads or writes global memory shared with the upstream kernel
     mbar_wait_bounded(accum, 0, abort_flag, OXB_TIMEOUT_ACCUM, blockIdx.x);
     // agree on one verdict for all 128 epilogue threads before any further named barrier
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (threadIdx.x == 64) ticket[1] = (*abort_flag == 0);
+    if (threadIdx.x == 64) {
+      ticket[1] = (*abort_flag == 0);
+      ticket[2] = ar.world > 0 ? (ar.ctrl[0] & 1) : 0;  // buffer parity of this collective call
+    }
     asm volatile("bar.sync 1, 128;" ::: "memory");
     const bool ok = ticket[1] != 0;
     tc_fence_after();
@@ -358,8 +379,10 @@ int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y
     configured = true;
   }
   dim3 grid(p.n_tiles, p.splits, p.t_tiles);
-  gemm_bf16_kernel<TN, QT><<<grid, QT == QT_BF16 ? GEMM_THREADS : GEMM_THREADS_MMQ, Cfg::SMEM_BYTES, stream>>>(
-      tmW, tmX, Y, bias, N, T, K, ldY, p.splits, ws, counters, epi_mode, ar, qw);
+  cudaError_t le = oxb_launch(gemm_bf16_kernel<TN, QT>, grid, dim3(QT == QT_BF16 ? GEMM_THREADS : GEMM_THREADS_MMQ),
+                              (size_t)Cfg::SMEM_BYTES, stream, tmW, tmX, Y, bias, N, T, K, ldY, p.splits, ws, counters,
+                              epi_mode, ar, qw);
+  if (le != cudaSuccess) return (int)le;
   OXB_CHECK_LAUNCH();
   return 0;
 }

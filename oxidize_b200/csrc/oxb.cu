@@ -11,6 +11,15 @@
 #include "comm_fused.cuh"
 using namespace oxb;
 
+int g_oxb_pdl = 1;
+
+// Switch programmatic dependent launch on or off (also: environment OXB_PDL=0 at load time).
+OXB_API int oxb_set_pdl(int on) {
+  const int old = g_oxb_pdl;
+  g_oxb_pdl = on ? 1 : 0;
+  return old;
+}
+
 // ----------------------------------------------------------------------------- host utilities
 PFN_encodeTiled oxb_get_encode_tiled() {
   static PFN_encodeTiled fn = nullptr;
@@ -213,8 +222,8 @@ OXB_API int oxb_allreduce_oneshot(const void* X, void* Y, int T, int N, int ld, 
     if (ce != cudaSuccess) return (int)ce;
     configured = smem;
   }
-  allreduce_oneshot_kernel<<<tiles, 128, smem, stream>>>(ar, reinterpret_cast<const __nv_bfloat16*>(X),
-                                                         reinterpret_cast<__nv_bfloat16*>(Y), T, N, ld);
+  oxb_launch(allreduce_oneshot_kernel, dim3(tiles), dim3(128), smem, stream, ar, reinterpret_cast<const __nv_bfloat16*>(X),
+             reinterpret_cast<__nv_bfloat16*>(Y), T, N, ld);
   OXB_CHECK_LAUNCH();
   return 0;
 }
@@ -239,8 +248,8 @@ OXB_API int oxb_dequant_rows(const void* src, int qtype, size_t row_bytes, int r
 OXB_API int oxb_embed(const int* tokens, const void* table, int qtype, size_t row_bytes, int H, int vocab, float scale,
                       void* out_bf16, int T, cudaStream_t stream) {
   if (T <= 0) return 0;
-  embed_kernel<<<T, 256, 0, stream>>>(tokens, reinterpret_cast<const uint8_t*>(table), qtype, row_bytes, H, vocab,
-                                      scale, reinterpret_cast<__nv_bfloat16*>(out_bf16));
+  oxb_launch(embed_kernel, dim3(T), dim3(256), 0, stream, tokens, reinterpret_cast<const uint8_t*>(table), qtype, row_bytes,
+             H, vocab, scale, reinterpret_cast<__nv_bfloat16*>(out_bf16));
   OXB_CHECK_LAUNCH();
   return 0;
 }
@@ -248,7 +257,20 @@ OXB_API int oxb_embed(const int* tokens, const void* table, int qtype, size_t ro
 OXB_API int oxb_add_rmsnorm(const void* x, const void* res_in, void* res_out, const float* w, void* y, int T, int H,
                             float eps, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (H % 8 != 0 && false) return (int)cudaErrorInvalidValue;
+  const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* rb = reinterpret_cast<const __nv_bfloat16*>(res_in);
+  __nv_bfloat16* ro = reinterpret_cast<__nv_bfloat16*>(res_out);
+  __nv_bfloat16* yb = reinterpret_cast<__nv_bfloat16*>(y);
+  if (H % 8 == 0 && H / 8 <= 4096) {
+    const int H8 = H / 8;
+    const int ch = H8 <= 1024 ? 1 : (H8 <= 2048 ? 2 : 4);
+    const int threads = ((H8 + ch - 1) / ch + 31) / 32 * 32;
+    if (ch == 1) oxb_launch(add_rmsnorm_reg_kernel<1>, dim3(T), dim3(threads), 0, stream, xb, rb, ro, w, yb, H, eps);
+    else if (ch == 2) oxb_launch(add_rmsnorm_reg_kernel<2>, dim3(T), dim3(threads), 0, stream, xb, rb, ro, w, yb, H, eps);
+    else oxb_launch(add_rmsnorm_reg_kernel<4>, dim3(T), dim3(threads), 0, stream, xb, rb, ro, w, yb, H, eps);
+    OXB_CHECK_LAUNCH();
+    return 0;
+  }
   const size_t smem = (size_t)H * sizeof(float);
   static size_t configured = 48 * 1024;
   if (smem > configured) {
@@ -270,8 +292,8 @@ OXB_API int oxb_silu_mul(const void* gu, void* out, int T, int I, cudaStream_t s
   const size_t total = (size_t)T * (I / 8);
   int blocks = (int)((total + 255) / 256);
   if (blocks > sm_count() * 16) blocks = sm_count() * 16;
-  silu_mul_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(gu),
-                                              reinterpret_cast<__nv_bfloat16*>(out), T, I);
+  oxb_launch(silu_mul_kernel, dim3(blocks), dim3(256), 0, stream, reinterpret_cast<const __nv_bfloat16*>(gu),
+             reinterpret_cast<__nv_bfloat16*>(out), T, I);
   OXB_CHECK_LAUNCH();
   return 0;
 }
@@ -284,9 +306,9 @@ OXB_API int oxb_qk_rope_kvwrite(const void* qkv, const int* positions, const int
   if (hd % 32 != 0 || hd > 1024) return (int)cudaErrorInvalidValue;
   KvWriteArgs kv{kv_data, kv_scales, kv_mode, page, nkv};
   dim3 grid(T, nq + 2 * nkv);
-  qk_rope_kvwrite_kernel<<<grid, hd, hd * sizeof(float), stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(qkv), positions, slots, cos_sin, max_pos, rot, pairing, q_norm, k_norm, eps,
-      nq, nkv, hd, reinterpret_cast<__nv_bfloat16*>(q_out), kv);
+  oxb_launch(qk_rope_kvwrite_kernel, grid, dim3(hd), hd * sizeof(float), stream,
+             reinterpret_cast<const __nv_bfloat16*>(qkv), positions, slots, cos_sin, max_pos, rot, pairing, q_norm, k_norm,
+             eps, nq, nkv, hd, reinterpret_cast<__nv_bfloat16*>(q_out), kv);
   OXB_CHECK_LAUNCH();
   return 0;
 }
@@ -294,7 +316,7 @@ OXB_API int oxb_qk_rope_kvwrite(const void* qkv, const int* positions, const int
 OXB_API int oxb_argmax(const float* logits, int R, int V, int ld, int tie_highest, int* out, float* out_val,
                        int index_offset, cudaStream_t stream) {
   if (R <= 0) return 0;
-  argmax_kernel<<<R, 1024, 0, stream>>>(logits, V, ld, tie_highest, out, out_val, index_offset);
+  oxb_launch(argmax_kernel, dim3(R), dim3(1024), 0, stream, logits, V, ld, tie_highest, out, out_val, index_offset);
   OXB_CHECK_LAUNCH();
   return 0;
 }
@@ -304,7 +326,8 @@ OXB_API int oxb_sample(const float* logits, int R, int V, int ld, const float* t
                        const float* top_p, const float* min_p, const float* random, int tie_highest, int* out,
                        cudaStream_t stream) {
   if (R <= 0) return 0;
-  sample_kernel<<<R, SMP_THREADS, 0, stream>>>(logits, V, ld, temperature, top_k, top_p, min_p, random, tie_highest, out);
+  oxb_launch(sample_kernel, dim3(R), dim3(SMP_THREADS), 0, stream, logits, V, ld, temperature, top_k, top_p, min_p, random,
+             tie_highest, out);
   OXB_CHECK_LAUNCH();
   return 0;
 }
@@ -332,20 +355,15 @@ static int attn_launch(const AttnArgs& a, int B, int G, cudaStream_t stream) {
     configured = true;
   }
   dim3 grid(a.max_mtiles * a.n_cta_splits, a.nkv, B);
-  paged_attention_kernel<HD><<<grid, ATT_WARPS * 32, smem, stream>>>(a, G);
+  oxb_launch(paged_attention_kernel<HD>, grid, dim3(ATT_WARPS * 32), (size_t)smem, stream, a, G);
   OXB_CHECK_LAUNCH();
-  if (a.n_cta_splits > 1) {
-    dim3 mg(a.max_mtiles, a.nkv, B);
-    attn_merge_kernel<HD><<<mg, 128, 0, stream>>>(a, G);
-    OXB_CHECK_LAUNCH();
-  }
   return 0;
 }
 
 OXB_API int oxb_paged_attention(const void* q, void* out, const void* kv_data, const float* kv_scales,
                                 const int* block_tables, const int* seq_lens, const int* query_start, int B,
                                 int max_blocks, int nq, int nkv, int hd, int kv_mode, int max_query_len,
-                                int n_cta_splits, int window, float scale, float* ws_o, float* ws_ml,
+                                int n_cta_splits, int window, float scale, float* ws_o, float* ws_ml, int* counters,
                                 cudaStream_t stream) {
   if (B <= 0) return 0;
   if (nq % nkv != 0) return (int)cudaErrorInvalidValue;
@@ -368,7 +386,8 @@ OXB_API int oxb_paged_attention(const void* q, void* out, const void* kv_data, c
   a.scale_log2 = scale * 1.4426950408889634f;
   a.ws_o = ws_o;
   a.ws_ml = ws_ml;
-  if (a.n_cta_splits > 1 && (ws_o == nullptr || ws_ml == nullptr)) return (int)cudaErrorInvalidValue;
+  a.counters = counters;
+  if (a.n_cta_splits > 1 && (ws_o == nullptr || ws_ml == nullptr || counters == nullptr)) return (int)cudaErrorInvalidValue;
   if (hd == 128) return attn_launch<128>(a, B, G, stream);
   if (hd == 64) return attn_launch<64>(a, B, G, stream);
   return (int)cudaErrorInvalidValue;

@@ -111,6 +111,8 @@ sample_kernel(const float* __restrict__ logits, int V, int ld, const float* __re
   __shared__ int s_i[4];
   __shared__ float s_f[4];
   __shared__ int s_best;
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * ld;
   const float T = temperature[r];

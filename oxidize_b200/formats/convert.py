@@ -1,0 +1,150 @@
+"""HF SafeTensors directory (``config.json`` + ``*.safetensors``) → GGUF, optionally quantizing.
+
+Counterpart of the reference's converter (``oxidize-core/src/format/safetensors_to_gguf.rs``:
+architecture metadata written from ``config.json`` ``:446-560``, tensor-name mapping via
+``map_hf_decoder_name``, per-expert tensors stacked into ``ffn_*_exps``).  Also usable as
+``python -m oxidize_b200.formats.convert SRC_DIR OUT.gguf --quant Q4_K_M``.
+"""
+from __future__ import annotations
+
+import glob
+import json
+import os
+from typing import Any, Dict, List, Optional, Tuple
+
+import numpy as np
+
+from ..quant import ref as qref
+from ..utils.synth import pick_type
+from .gguf import GGUFValueType, GGUFWriter, map_hf_tensor_name
+from .safetensors_io import SafeTensorsFile
+
+_ARCH = {"LlamaForCausalLM": "llama", "MistralForCausalLM": "llama", "MixtralForCausalLM": "mixtral",
+         "Qwen2ForCausalLM": "qwen2", "Qwen3ForCausalLM": "qwen3", "Qwen3MoeForCausalLM": "qwen3moe",
+         "Qwen2MoeForCausalLM": "qwen2moe", "DeepseekV2ForCausalLM": "deepseek2", "DeepseekV3ForCausalLM": "deepseek2"}
+
+
+def arch_from_config(cfg: Dict[str, Any]) -> str:
+    for a in cfg.get("architectures") or []:
+        if a in _ARCH:
+            return _ARCH[a]
+    mt = str(cfg.get("model_type", "llama")).lower()
+    return {"mistral": "llama", "qwen3_moe": "qwen3moe", "qwen2_moe": "qwen2moe", "deepseek_v2": "deepseek2",
+            "deepseek_v3": "deepseek2"}.get(mt, mt)
+
+
+def write_hf_metadata(w: GGUFWriter, arch: str, c: Dict[str, Any]) -> None:
+    U, F = GGUFValueType.UINT32, GGUFValueType.FLOAT32
+    heads = int(c["num_attention_heads"])
+    hidden = int(c["hidden_size"])
+    w.add("general.name", str(c.get("_name_or_path") or c.get("model_type") or "converted"))
+    w.add(f"{arch}.vocab_size", int(c["vocab_size"]), U)
+    w.add(f"{arch}.embedding_length", hidden, U)
+    w.add(f"{arch}.block_count", int(c["num_hidden_layers"]), U)
+    w.add(f"{arch}.context_length", int(c.get("max_position_embeddings", 4096)), U)
+    w.add(f"{arch}.feed_forward_length", int(c.get("intermediate_size", 0)), U)
+    w.add(f"{arch}.attention.head_count", heads, U)
+    w.add(f"{arch}.attention.head_count_kv", int(c.get("num_key_value_heads", heads)), U)
+    hd = int(c.get("head_dim") or hidden // heads)
+    w.add(f"{arch}.attention.key_length", hd, U)
+    w.add(f"{arch}.attention.value_length", hd, U)
+    w.add(f"{arch}.attention.layer_norm_rms_epsilon", float(c.get("rms_norm_eps", 1e-5)), F)
+    w.add(f"{arch}.rope.freq_base", float(c.get("rope_theta", 10000.0)), F)
+    w.add(f"{arch}.rope.dimension_count", int(hd * float(c.get("partial_rotary_factor", 1.0))), U)
+    if c.get("sliding_window"):
+        w.add(f"{arch}.attention.sliding_window", int(c["sliding_window"]), U)
+    rs = c.get("rope_scaling") or {}
+    if rs.get("type") or rs.get("rope_type"):
+        kind = str(rs.get("type") or rs.get("rope_type"))
+        if kind in ("linear", "yarn"):
+            w.add(f"{arch}.rope.scaling.type", kind)
+            w.add(f"{arch}.rope.scaling.factor", float(rs.get("factor", 1.0)), F)
+            w.add(f"{arch}.rope.scaling.original_context_length",
+                  int(rs.get("original_max_position_embeddings", c.get("max_position_embeddings", 0))), U)
+    n_exp = int(c.get("num_local_experts") or c.get("num_experts") or c.get("n_routed_experts") or 0)
+    if n_exp:
+        w.add(f"{arch}.expert_count", n_exp, U)
+        w.add(f"{arch}.expert_used_count", int(c.get("num_experts_per_tok", 2)), U)
+        w.add(f"{arch}.expert_feed_forward_length", int(c.get("moe_intermediate_size") or c.get("intermediate_size")), U)
+        w.add(f"{arch}.expert_gating_func", 2 if c.get("scoring_func") == "sigmoid" else 1, U)
+        w.add(f"{arch}.expert_weights_scale", float(c.get("routed_scaling_factor", 1.0)), F)
+        w.add(f"{arch}.expert_weights_norm", bool(c.get("norm_topk_prob", True)))
+        if c.get("n_group"):
+            w.add(f"{arch}.expert_group_count", int(c["n_group"]), U)
+            w.add(f"{arch}.expert_group_used_count", int(c.get("topk_group", 1)), U)
+        if c.get("first_k_dense_replace"):
+            w.add(f"{arch}.leading_dense_block_count", int(c["first_k_dense_replace"]), U)
+
+
+def _kind_of(gname: str) -> str:
+    base = gname.split(".")[-2] if gname.count(".") >= 2 else gname.split(".")[0]
+    return {"token_embd": "token_embd", "output": "output"}.get(base, base.replace("_exps", "").replace("_shexp", ""))
+
+
+def convert_safetensors_to_gguf(src_dir: str, out_path: str, quant: str = "F16", tokenizer_metadata: Dict = None) -> str:
+    with open(os.path.join(src_dir, "config.json")) as f:
+        cfg = json.load(f)
+    arch = arch_from_config(cfg)
+    files = [SafeTensorsFile(p) for p in sorted(glob.glob(os.path.join(src_dir, "*.safetensors")))]
+    if not files:
+        raise FileNotFoundError(f"no .safetensors files in {src_dir}")
+    w = GGUFWriter(out_path, arch=arch)
+    write_hf_metadata(w, arch, cfg)
+    for k, v in (tokenizer_metadata or {}).items():
+        w.add(k, v)
+    L = int(cfg["num_hidden_layers"])
+    plain: List[Tuple[str, SafeTensorsFile, str]] = []
+    experts: Dict[str, Dict[int, Tuple[SafeTensorsFile, str]]] = {}
+    for f in files:
+        for name in f.keys():
+            m = map_hf_tensor_name(name)
+            if m is None:
+                continue
+            gname, e = m
+            if e is None:
+                plain.append((gname, f, name))
+            else:
+                experts.setdefault(gname, {})[e] = (f, name)
+
+    def layer_of(gname: str) -> int:
+        parts = gname.split(".")
+        return int(parts[1]) if parts[0] == "blk" else 0
+
+    def encode(gname: str, arr_f32: np.ndarray):
+        if arr_f32.ndim == 1 or "norm" in gname or gname.endswith(".bias") or "ffn_gate_inp" in gname:
+            return arr_f32.astype(np.float32), "F32"
+        t = pick_type(quant, _kind_of(gname), layer_of(gname), L, arr_f32.shape[-1])
+        return qref.quantize(t, arr_f32.reshape(-1)), t
+
+    for gname, f, name in plain:
+        shape = f.shape(name)
+
+        def gen(f=f, name=name, gname=gname):
+            return encode(gname, f.tensor_f32(name))[0]
+
+        t = encode(gname, np.zeros(shape[-1:] if len(shape) == 1 else (1, shape[-1]), dtype=np.float32))[1]
+        w.add_tensor(gname, gen, shape, t)
+    for gname, per in experts.items():
+        n = max(per) + 1
+        f0, n0 = per[0]
+        rows, cols = f0.shape(n0)
+
+        def gen_e(per=per, n=n, gname=gname):
+            return np.concatenate([np.ascontiguousarray(encode(gname, per[e][0].tensor_f32(per[e][1]))[0]).view(np.uint8)
+                                   .reshape(-1) for e in range(n)])
+
+        t = pick_type(quant, _kind_of(gname), layer_of(gname), L, cols)
+        w.add_tensor(gname, gen_e, (n, rows, cols), t)
+    w.write()
+    return out_path
+
+
+if __name__ == "__main__":
+    import argparse
+
+    ap = argparse.ArgumentParser(description="HF SafeTensors → GGUF")
+    ap.add_argument("src")
+    ap.add_argument("out")
+    ap.add_argument("--quant", default="F16")
+    a = ap.parse_args()
+    print(convert_safetensors_to_gguf(a.src, a.out, a.quant))

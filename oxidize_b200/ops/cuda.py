@@ -40,6 +40,8 @@ def lib():
                     build_kernels()
                 _lib = ctypes.CDLL(LIB_PATH)
                 _declare(_lib)
+                if os.environ.get("OXB_PDL", "1") == "0":
+                    _lib.oxb_set_pdl(0)
     return _lib
 
 
@@ -57,7 +59,7 @@ def _declare(L) -> None:
                                       i32, vp]
     L.oxb_argmax.argtypes = [vp, i32, i32, i32, i32, vp, vp, i32, vp]
     L.oxb_paged_attention.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp,
-                                      vp, vp]
+                                      vp, vp, vp]
     L.oxb_sample.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, vp, i32, vp, vp]
     L.oxb_gemm_quant.argtypes =[vp, vp, i32, sz, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, sz, vp, i32, vp]
     u64p, ull = ctypes.POINTER(ctypes.c_uint64), ctypes.c_ulonglong
@@ -99,6 +101,7 @@ class Scratch:
         self.gemm_counters = torch.zeros(8192, dtype=torch.int32, device=device)
         self.attn_o: Optional[torch.Tensor] = None
         self.attn_ml: Optional[torch.Tensor] = None
+        self.attn_counters = torch.zeros(65536, dtype=torch.int32, device=device)
         self.dequant: Optional[torch.Tensor] = None
 
     def attn(self, o_floats: int, ml_floats: int):
@@ -283,15 +286,18 @@ def paged_attention(q, kv, layer, meta, scale, sliding_window=0, splits: Optiona
     if splits is None:
         splits = attn_splits(B, nkv, mtiles, meta.max_seq_len or kv.page_size, sm_count(q.device))
     out = torch.empty_like(q)
-    ws_o = ws_ml = None
+    ws_o = ws_ml = cnt = None
+    if splits > 1 and B * nkv * mtiles > scratch(q.device).attn_counters.numel():
+        splits = 1
     if splits > 1:
         tasks = B * nkv * mtiles * splits
         ws_o, ws_ml = scratch(q.device).attn(tasks * 16 * hd, tasks * 32)
+        cnt = scratch(q.device).attn_counters
     _check(lib().oxb_paged_attention(q.data_ptr(), out.data_ptr(), kv.data[layer].data_ptr(), _p(kv.scales[layer]),
                                      meta.block_tables.data_ptr(), meta.seq_lens.data_ptr(), meta.query_start.data_ptr(),
                                      B, meta.block_tables.stride(0), nq, nkv, hd, KV_MODE[kv.dtype_name],
                                      max(1, meta.max_query_len), splits, sliding_window, scale, _p(ws_o), _p(ws_ml),
-                                     _stream()), "oxb_paged_attention")
+                                     _p(cnt), _stream()), "oxb_paged_attention")
     return out
 
 
