@@ -392,3 +392,65 @@ OXB_API int oxb_paged_attention(const void* q, void* out, const void* kv_data, c
   if (hd == 64) return attn_launch<64>(a, B, G, stream);
   return (int)cudaErrorInvalidValue;
 }
+
+// ----------------------------------------------------------------------------- allocation-free GEMM
+// See oxb_noalloc.h for the contract.  The split-K scratch of the GEMM lives in this fixed device
+// array: [0, 16 KiB) rendezvous counters, the rest fp32 partials.
+#include "oxb_noalloc.h"
+#include <stdio.h>
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[OXB_NOALLOC_SCRATCH_BYTES];
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not a device address, so the
+// address is looked up once per device and cached here.
+static void* g_noalloc_dev_ptr[64] = {nullptr};
+
+extern "C" __attribute__((visibility("default"))) int oxb_gemm_bf16_noalloc(
+    const void* X, const void* W, void* Y, const float* bias, int T, int N, int K, int ldY, void* cuda_stream) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+  if (X == nullptr || W == nullptr || Y == nullptr || T <= 0 || N <= 0 || K <= 0 || K % 8 != 0 || ldY < N)
+    return OXB_NOALLOC_E_BAD_ARGUMENT;
+  if (T > OXB_NOALLOC_MAX_TOKENS) {
+    fprintf(stderr, "oxb_gemm_bf16_noalloc: T=%d exceeds the limit of %d tokens per call (static scratch of %d bytes)\n",
+            T, OXB_NOALLOC_MAX_TOKENS, (int)OXB_NOALLOC_SCRATCH_BYTES);
+    return OXB_NOALLOC_E_TOO_LARGE;
+  }
+  int dev = 0;
+  cudaError_t ce = cudaGetDevice(&dev);
+  if (ce != cudaSuccess) return (int)ce;
+  if (dev < 0 || dev >= 64) return OXB_NOALLOC_E_BAD_ARGUMENT;
+  if (g_noalloc_dev_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    ce = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (ce != cudaSuccess) return (int)ce;
+    g_noalloc_dev_ptr[dev] = p;
+  }
+  unsigned char* base = reinterpret_cast<unsigned char*>(g_noalloc_dev_ptr[dev]);
+  int* counters = reinterpret_cast<int*>(base);
+  float* ws = reinterpret_cast<float*>(base + OXB_NOALLOC_COUNTER_BYTES);
+  const size_t ws_bytes = OXB_NOALLOC_SCRATCH_BYTES - OXB_NOALLOC_COUNTER_BYTES;
+  const int n_counters = OXB_NOALLOC_COUNTER_BYTES / (int)sizeof(int);
+  GemmPlan p = gemm_plan(T, N, K, 0, sm_count());
+  while (p.splits > 1 && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || p.n_tiles * p.t_tiles * p.splits > sm_count()))
+    p = gemm_plan(T, N, K, p.splits - 1, sm_count());
+  if (p.splits > 1) {
+    // the counters must start at zero; an earlier call that gave up could have left them set
+    ce = cudaMemsetAsync(counters, 0, (size_t)p.n_counters * sizeof(int), stream);
+    if (ce != cudaSuccess) return (int)ce;
+  }
+  CUtensorMap tmW, tmX;
+  int e = oxb_make_tmap_2d(&tmW, W, N, K, (uint64_t)K * 2, GEMM_BM, GEMM_BK, 2);
+  if (e) return e;
+  e = oxb_make_tmap_2d(&tmX, X, T, K, (uint64_t)K * 2, p.tn, GEMM_BK, 2);
+  if (e) return e;
+  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(Y);
+  ArArgs ar;
+  memset(&ar, 0, sizeof(ar));
+  switch (p.tn) {
+    case 16: return gemm_launch<16>(tmW, tmX, y, bias, N, T, K, ldY, p, ws, counters, 0, ar, stream);
+    case 32: return gemm_launch<32>(tmW, tmX, y, bias, N, T, K, ldY, p, ws, counters, 0, ar, stream);
+    case 64: return gemm_launch<64>(tmW, tmX, y, bias, N, T, K, ldY, p, ws, counters, 0, ar, stream);
+    case 128: return gemm_launch<128>(tmW, tmX, y, bias, N, T, K, ldY, p, ws, counters, 0, ar, stream);
+    default: return gemm_launch<256>(tmW, tmX, y, bias, N, T, K, ldY, p, ws, counters, 0, ar, stream);
+  }
+}
