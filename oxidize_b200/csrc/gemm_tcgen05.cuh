@@ -58,6 +58,18 @@ __device__ __forceinline__ void splitk_reduce(const float* base, int split_strid
   }
 }
 
+// Grouped (per-expert) launches: blockIdx.z selects the group instead of a token tile.  Group z uses
+// weight rows [z*w_rows, z*w_rows + N), activation rows [z*x_rows, z*x_rows + T) (x_rows = 0: all
+// groups share X), writes Y + z*y_stride, and is skipped entirely when its row of per-token scales
+// is all zero (an expert no token was routed to) — so idle experts cost no weight traffic.
+struct GroupArgs {
+  int enabled;
+  int w_rows, x_rows;
+  long long y_stride;
+  const float* scale;  // [groups, scale_ld] or null (never skip)
+  int scale_ld;
+};
+
 // QT == QT_BF16: both operands arrive by TMA.  Any other QT: the weight tile is produced by four
 // dequant warps from packed blocks (see mmq_producer.cuh) and only the activations use TMA.
 template <int TN, int QT>
@@ -65,8 +77,20 @@ __global__ void __launch_bounds__(QT == QT_BF16 ? GEMM_THREADS : GEMM_THREADS_MM
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                  __nv_bfloat16* __restrict__ Y, const float* __restrict__ bias, int N, int T, int K, int ldY,
                  int splits, float* __restrict__ ws, int* __restrict__ counters, int epi_mode, const ArArgs ar,
-                 const QwArgs qw) {
+                 const QwArgs qw, const GroupArgs gr) {
   constexpr bool MMQ = QT != QT_BF16;
+  const int zg = gr.enabled ? (int)blockIdx.z : 0;
+  if (gr.enabled && gr.scale != nullptr) {
+    // the routing weights come from the upstream kernel
+    pdl_wait();
+    int any = 0;
+    for (int t = threadIdx.x; t < T; t += blockDim.x) any |= gr.scale[(size_t)zg * gr.scale_ld + t] != 0.f;
+    if (!__syncthreads_or(any)) {
+      pdl_launch_dependents();
+      return;
+    }
+  }
+  Y += (size_t)zg * gr.y_stride;
   using Cfg = GemmTile<TN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -81,7 +105,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * GEMM_BM;
   const int split = blockIdx.y;
-  const int t0 = blockIdx.z * TN;
+  const int t0 = gr.enabled ? 0 : blockIdx.z * TN;
+  const int w_row0 = n0 + zg * gr.w_rows;  // first weight row of this tile in the (stacked) matrix
+  const int x_row0 = t0 + zg * gr.x_rows;
   const int kb_total = (K + GEMM_BK - 1) / GEMM_BK;
   const int kb_begin = (int)((long long)split * kb_total / splits);
   const int kb_end = (int)((long long)(split + 1) * kb_total / splits);
@@ -123,13 +149,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           mbar_expect_tx(&full[i], Cfg::B_BYTES);
         } else {
           mbar_expect_tx(&full[i], Cfg::STAGE_BYTES);
-          tma_load_2d_hint(sA, &tmW, &full[i], (kb_begin + i) * GEMM_BK, n0, pol_w);
+          tma_load_2d_hint(sA, &tmW, &full[i], (kb_begin + i) * GEMM_BK, w_row0, pol_w);
         }
       }
       pdl_wait();  // activations come from the upstream kernel
       for (int i = 0; i < npre; ++i) {
         uint8_t* sB = smem + i * Cfg::STAGE_BYTES + Cfg::A_BYTES;
-        tma_load_2d_hint(sB, &tmX, &full[i], (kb_begin + i) * GEMM_BK, t0, pol_x);
+        tma_load_2d_hint(sB, &tmX, &full[i], (kb_begin + i) * GEMM_BK, x_row0, pol_x);
       }
       for (int i = npre; i < nkb; ++i) {
         const int st = i % STAGES;
@@ -141,9 +167,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           mbar_expect_tx(&full[st], Cfg::B_BYTES);
         } else {
           mbar_expect_tx(&full[st], Cfg::STAGE_BYTES);
-          tma_load_2d_hint(sA, &tmW, &full[st], (kb_begin + i) * GEMM_BK, n0, pol_w);
+          tma_load_2d_hint(sA, &tmW, &full[st], (kb_begin + i) * GEMM_BK, w_row0, pol_w);
         }
-        tma_load_2d_hint(sB, &tmX, &full[st], (kb_begin + i) * GEMM_BK, t0, pol_x);
+        tma_load_2d_hint(sB, &tmX, &full[st], (kb_begin + i) * GEMM_BK, x_row0, pol_x);
       }
     }
     __syncwarp();
@@ -174,7 +200,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     if constexpr (MMQ) {
       const int r = threadIdx.x - 192;
       const int n = n0 + r;
-      const uint8_t* rowp = qw.w + (size_t)(n < N ? n : 0) * qw.row_bytes;
+      const uint8_t* rowp = qw.w + ((size_t)zg * gr.w_rows + (size_t)(n < N ? n : 0)) * qw.row_bytes;
       for (int i = 0; i < nkb; ++i) {
         const int st = i % STAGES;
         const uint32_t ph = (i / STAGES) & 1;
@@ -237,8 +263,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       }
       if (use_ar) {
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        ar_exchange_tile(ar, smem, ticket[2], tile_id, n0, t0, min(TN, T - t0), N, Y, ldY, 0.f, abort_flag,
-                         threadIdx.x - 64);
+        ar_exchange(ar, smem, ticket[2], tile_id, n0, t0, min(TN, T - t0), N, Y, ldY, abort_flag, threadIdx.x - 64);
       }
     } else if (ok) {
       // fp32 partial -> workspace [tile][split][token][row]
@@ -302,8 +327,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         if (use_ar) {
           asm volatile("bar.sync 1, 128;" ::: "memory");
           if (je > jb)
-            ar_exchange_tile(ar, smem, ticket[2], tile_id * splits + split, n0, t0 + jb, je - jb, N, Y, ldY, 0.f,
-                             abort_flag, threadIdx.x - 64);
+            ar_exchange(ar, smem, ticket[2], tile_id * splits + split, n0, t0 + jb, je - jb, N, Y, ldY, abort_flag,
+                        threadIdx.x - 64);
         }
         // the last CTA to leave re-arms the counters for the next launch / graph replay
         if (threadIdx.x == 64) {
@@ -369,7 +394,8 @@ inline GemmPlan gemm_plan(int T, int N, int K, int splits_hint, int sm_count) {
 template <int TN, int QT = QT_BF16>
 int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y, const float* bias, int N, int T, int K,
                 int ldY, const GemmPlan& p, float* ws, int* counters, int epi_mode, const ArArgs& ar,
-                cudaStream_t stream, const QwArgs& qw = QwArgs{nullptr, 0, nullptr, 0}) {
+                cudaStream_t stream, const QwArgs& qw = QwArgs{nullptr, 0, nullptr, 0},
+                const GroupArgs& gr = GroupArgs{0, 0, 0, 0, nullptr, 0}, int groups = 1) {
   using Cfg = GemmTile<TN>;
   static bool configured = false;
   if (!configured) {
@@ -378,10 +404,10 @@ int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid(p.n_tiles, p.splits, p.t_tiles);
+  dim3 grid(p.n_tiles, p.splits, gr.enabled ? groups : p.t_tiles);
   cudaError_t le = oxb_launch(gemm_bf16_kernel<TN, QT>, grid, dim3(QT == QT_BF16 ? GEMM_THREADS : GEMM_THREADS_MMQ),
                               (size_t)Cfg::SMEM_BYTES, stream, tmW, tmX, Y, bias, N, T, K, ldY, p.splits, ws, counters,
-                              epi_mode, ar, qw);
+                              epi_mode, ar, qw, gr);
   if (le != cudaSuccess) return (int)le;
   OXB_CHECK_LAUNCH();
   return 0;
@@ -391,13 +417,13 @@ int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y
 template <int QT>
 int gemm_launch_mmq(const CUtensorMap& tmX, __nv_bfloat16* Y, const float* bias, int N, int T, int K, int ldY,
                     const GemmPlan& p, float* ws, int* counters, int epi_mode, const ArArgs& ar, cudaStream_t stream,
-                    const QwArgs& qw) {
+                    const QwArgs& qw, const GroupArgs& gr = GroupArgs{0, 0, 0, 0, nullptr, 0}, int groups = 1) {
   switch (p.tn) {
-    case 16: return gemm_launch<16, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw);
-    case 32: return gemm_launch<32, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw);
-    case 64: return gemm_launch<64, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw);
-    case 128: return gemm_launch<128, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw);
-    default: return gemm_launch<256, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw);
+    case 16: return gemm_launch<16, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
+    case 32: return gemm_launch<32, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
+    case 64: return gemm_launch<64, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
+    case 128: return gemm_launch<128, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
+    default: return gemm_launch<256, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
   }
 }
 

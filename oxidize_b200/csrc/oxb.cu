@@ -12,6 +12,13 @@
 using namespace oxb;
 
 int g_oxb_pdl = 1;
+int g_oxb_ar_twoshot_min_world = 4;  // rank counts from which the fused all-reduce goes two-shot
+
+OXB_API int oxb_set_ar_twoshot_min_world(int w) {
+  const int old = g_oxb_ar_twoshot_min_world;
+  g_oxb_ar_twoshot_min_world = w;
+  return old;
+}
 
 // Switch programmatic dependent launch on or off (also: environment OXB_PDL=0 at load time).
 OXB_API int oxb_set_pdl(int on) {
@@ -151,6 +158,7 @@ OXB_API int oxb_gemm_quant(const void* X, const void* Wq, int qtype, size_t row_
 static int fill_ar(ArArgs& ar, int world, int rank, const uint64_t* data_ptrs, const uint64_t* flag_ptrs, int* ctrl,
                    int t_max, int n_max, int max_tiles, unsigned long long timeout_ns, const void* residual) {
   memset(&ar, 0, sizeof(ar));
+  ar.mode = world >= g_oxb_ar_twoshot_min_world ? 1 : 0;
   if (world < 1 || world > AR_MAX_WORLD || rank < 0 || rank >= world || ctrl == nullptr) return (int)cudaErrorInvalidValue;
   ar.world = world;
   ar.rank = rank;
@@ -169,8 +177,8 @@ static int fill_ar(ArArgs& ar, int world, int rank, const uint64_t* data_ptrs, c
 
 // Row-parallel GEMM fused with a one-shot all-reduce over peer memory:
 //   Y[T, N] = sum over ranks of X_r[T, K_r] · W_r[N, K_r]^T  (+ residual), identical on every rank.
-// data_ptrs / flag_ptrs: every rank's symmetric receive buffer [2][world][t_max][n_max] bf16 and flag
-// array [2][world][max_tiles] u32 (zeroed once); ctrl: 2 local ints, zeroed once.
+// data_ptrs / flag_ptrs: every rank's symmetric receive buffer [2][world+1][t_max][n_max] bf16 and flag
+// array [2][world+1][max_tiles] u32 (zeroed once); ctrl: 2 local ints, zeroed once.
 // Limits: T <= min(t_max, 256), N <= n_max, N % 8 == 0, N/128 <= max_tiles, and the whole grid must be
 // co-resident (<= SM count) because CTAs wait on their peers' copies of the same tile.
 OXB_API int oxb_gemm_ar(const void* X, const void* W, void* Y, const void* residual, int T, int N, int K, int ldY,
@@ -452,5 +460,78 @@ extern "C" __attribute__((visibility("default"))) int oxb_gemm_bf16_noalloc(
     case 64: return gemm_launch<64>(tmW, tmX, y, bias, N, T, K, ldY, p, ws, counters, 0, ar, stream);
     case 128: return gemm_launch<128>(tmW, tmX, y, bias, N, T, K, ldY, p, ws, counters, 0, ar, stream);
     default: return gemm_launch<256>(tmW, tmX, y, bias, N, T, K, ldY, p, ws, counters, 0, ar, stream);
+  }
+}
+
+// ----------------------------------------------------------------------------- mixture of experts
+#include "moe.cuh"
+
+OXB_API int oxb_moe_route(const float* logits, int T, int E, int ld, int k, int sigmoid, const float* sel_bias, int renorm,
+                          float weight_scale, int* ids, float* wts, float* scale, int scale_ld, int first_local,
+                          int n_local, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E > MOE_MAX_EXPERTS || k > MOE_MAX_TOPK || k < 1 || k > E) return (int)cudaErrorInvalidValue;
+  const int warps = 4;
+  cudaError_t e = oxb_launch(moe_route_kernel, dim3((T + warps - 1) / warps), dim3(warps * 32), 0, stream, logits, T, E, ld,
+                             k, sigmoid, sel_bias, renorm, weight_scale, ids, wts, scale, scale_ld, first_local, n_local);
+  if (e != cudaSuccess) return (int)e;
+  OXB_CHECK_LAUNCH();
+  return 0;
+}
+
+OXB_API int oxb_moe_combine(const void* y, const float* scale, int scale_ld, const void* shared, void* out, int E, int T,
+                            int H, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H % 8 != 0) return (int)cudaErrorInvalidValue;
+  cudaError_t e = oxb_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, reinterpret_cast<const __nv_bfloat16*>(y),
+                             scale, scale_ld, reinterpret_cast<const __nv_bfloat16*>(shared),
+                             reinterpret_cast<__nv_bfloat16*>(out), E, T, H);
+  if (e != cudaSuccess) return (int)e;
+  OXB_CHECK_LAUNCH();
+  return 0;
+}
+
+// Grouped GEMM over `groups` experts in ONE launch: for group g,
+//   Y[g] [T, N] = X_g [T, K] · W_g [N, K]^T,   W stacked as [(groups*N), K] (bf16 or packed rows),
+//   X_g = X + g*x_rows rows (x_rows = 0: every group reads the same X),  Y[g] = Y + g*y_stride elements.
+// Groups whose `scale` row (per-token routing weights, [groups, scale_ld]) is all zero are skipped on the
+// device.  T <= 256.
+OXB_API int oxb_gemm_grouped(const void* X, int x_rows, const void* W, int qtype, size_t row_bytes, void* Y,
+                             long long y_stride, const float* scale, int scale_ld, int groups, int T, int N, int K,
+                             int ldY, void* ws, size_t ws_bytes, int* counters, int n_counters, cudaStream_t stream) {
+  if (T <= 0 || N <= 0 || K <= 0 || groups <= 0) return 0;
+  if (T > 256 || K % 64 != 0) return (int)cudaErrorInvalidValue;
+  GemmPlan p = gemm_plan(T, N, K, 0, sm_count());
+  while (p.splits > 1 && (p.ws_bytes * groups > ws_bytes || p.n_counters * groups > n_counters || ws == nullptr ||
+                          counters == nullptr || p.n_tiles * p.splits * groups > sm_count()))
+    p = gemm_plan(T, N, K, p.splits - 1, sm_count());
+  CUtensorMap tmW, tmX;
+  const uint64_t xr = x_rows > 0 ? (uint64_t)groups * x_rows : (uint64_t)T;
+  int e = oxb_make_tmap_2d(&tmX, X, xr, K, (uint64_t)K * 2, p.tn, GEMM_BK, 2);
+  if (e) return e;
+  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(Y);
+  float* wsf = reinterpret_cast<float*>(ws);
+  ArArgs ar;
+  memset(&ar, 0, sizeof(ar));
+  GroupArgs gr{1, N, x_rows, y_stride, scale, scale_ld};
+  QwArgs qw{reinterpret_cast<const uint8_t*>(W), row_bytes, nullptr, 0};
+  if (qtype == QT_BF16) {
+    e = oxb_make_tmap_2d(&tmW, W, (uint64_t)groups * N, K, (uint64_t)K * 2, GEMM_BM, GEMM_BK, 2);
+    if (e) return e;
+    switch (p.tn) {
+      case 16: return gemm_launch<16>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
+      case 32: return gemm_launch<32>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
+      case 64: return gemm_launch<64>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
+      case 128: return gemm_launch<128>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
+      default: return gemm_launch<256>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
+    }
+  }
+  switch (qtype) {
+    case QT_Q4_K: return gemm_launch_mmq<QT_Q4_K>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
+    case QT_Q6_K: return gemm_launch_mmq<QT_Q6_K>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
+    case QT_Q8_0: return gemm_launch_mmq<QT_Q8_0>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
+    case QT_Q4_0: return gemm_launch_mmq<QT_Q4_0>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
+    case QT_NVFP4: return gemm_launch_mmq<QT_NVFP4>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
+    default: return (int)cudaErrorInvalidValue;
   }
 }

@@ -107,12 +107,19 @@ class Transformer:
         them and the combine is the weighted sum + all-reduce."""
         cfg = self.cfg
         logits = ops.linear(x, lw.router).float()
-        ids, wts = ops.moe_route(logits, cfg, lw.router_bias)
-        out = moe_experts_forward(x, ids, wts, lw.experts)
+        sh = None
         if lw.shared_gate_up is not None:
             sh = ops.linear(ops.silu_mul(ops.linear(x, lw.shared_gate_up)), lw.shared_down)
             if lw.shared_gate is not None:
                 sh = (sh.float() * torch.sigmoid(ops.linear(x, lw.shared_gate).float())).to(sh.dtype)
+        if x.is_cuda:
+            from ..ops import cuda_moe
+
+            out = cuda_moe.moe_layer(x, logits, cfg, lw.router_bias, lw.experts, sh)
+            return self.comm.all_reduce(out)
+        ids, wts = ops.moe_route(logits, cfg, lw.router_bias)
+        out = moe_experts_forward(x, ids, wts, lw.experts)
+        if sh is not None:
             out = out + sh
         return self.comm.all_reduce(out)
 

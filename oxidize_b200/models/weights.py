@@ -134,6 +134,26 @@ class ExpertWeights:
     gate_up: List[QTensor]  # per local expert: fused [2*ffn, hidden]
     down: List[QTensor]
     first_expert: int = 0  # global id of local expert 0 (expert parallelism)
+    gate_up_stack: Optional[QTensor] = None  # [(E*2ffn), hidden] rows of all local experts, expert-major
+    down_stack: Optional[QTensor] = None
+
+    def stack(self) -> bool:
+        """Lay all local experts' rows out in one matrix per projection (what the grouped GEMM
+        reads); the per-expert tensors become views of it, so nothing is held twice.  Returns False
+        when the experts do not share one encoding."""
+        if self.gate_up_stack is not None:
+            return True
+        for lst in (self.gate_up, self.down):
+            if len({(q.qtype, q.shape) for q in lst}) != 1 or lst[0].qtype in ("FP8B", "F32", "F16"):
+                return False
+        for name in ("gate_up", "down"):
+            lst = getattr(self, name)
+            n, k = lst[0].shape
+            data = torch.cat([q.data for q in lst], dim=0).contiguous()
+            setattr(self, name + "_stack", QTensor(lst[0].qtype, data, (n * len(lst), k)))
+            for i, q in enumerate(lst):
+                q.data = data[i * n : (i + 1) * n]
+        return True
 
 
 @dataclass

@@ -50,8 +50,8 @@ class FusedComm(TorchComm):
                     enable(pg.group_name)
                 except Exception:
                     pass
-            self.data = symm.empty(2 * W * self.t_max * self.n_max, dtype=torch.bfloat16, device=self.device)
-            self.flags = symm.empty(2 * W * self.max_tiles, dtype=torch.int32, device=self.device)
+            self.data = symm.empty(2 * (W + 1) * self.t_max * self.n_max, dtype=torch.bfloat16, device=self.device)
+            self.flags = symm.empty(2 * (W + 1) * self.max_tiles, dtype=torch.int32, device=self.device)
             self.data.zero_()
             self.flags.zero_()
             h_data = symm.rendezvous(self.data, pg)
@@ -60,8 +60,8 @@ class FusedComm(TorchComm):
             data_ptrs = [int(p) for p in h_data.buffer_ptrs]
             flag_ptrs = [int(p) for p in h_flags.buffer_ptrs]
         else:
-            self.data = torch.zeros(2 * self.t_max * self.n_max, dtype=torch.bfloat16, device=self.device)
-            self.flags = torch.zeros(2 * self.max_tiles, dtype=torch.int32, device=self.device)
+            self.data = torch.zeros(2 * 9 * self.t_max * self.n_max, dtype=torch.bfloat16, device=self.device)
+            self.flags = torch.zeros(2 * 9 * self.max_tiles, dtype=torch.int32, device=self.device)
             data_ptrs, flag_ptrs = [self.data.data_ptr()], [self.flags.data_ptr()]
         self.set_peer_pointers(data_ptrs, flag_ptrs)
         self.ctrl = torch.zeros(4, dtype=torch.int32, device=self.device)
