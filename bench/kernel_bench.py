@@ -51,10 +51,13 @@ def bench_gemm(rows):
     hbm, tf, kind = peaks()
     shapes = [("qkv/tp8", 1280, 8192), ("o/tp8", 8192, 1024), ("gate_up/tp8", 7168, 8192), ("down/tp8", 8192, 3584),
               ("lm_head/tp8", 16032, 8192)]
+    only = os.environ.get("KB_SHAPES")
     for name, N, K in shapes:
+        if only and name.split("/")[0] not in only.split(","):
+            continue
         copies = max(2, int(400e6 // (N * K * 2)) + 1)
         ws = [(torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(copies)]
-        for T in (1, 16, 64, 256, 2048):
+        for T in [int(v) for v in os.environ.get("KB_TOKENS", "1,16,64,256,2048").split(",")]:
             x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
             out = torch.empty(T, N, dtype=torch.bfloat16, device="cuda")
             plan = C.gemm_plan(T, N, K)
@@ -109,11 +112,58 @@ def bench_attn(rows):
         del kv
 
 
+def small_case(spec: str, launches: int):
+    """A handful of eager launches of ONE kernel on a small case (for a profiler capture):
+    gemm:TxNxK rotates over weight copies that together exceed the L2; attn:BxCTXxNQxNKV[:kv] walks
+    layers of one KV cache the same way.  Device memory stays below 1 GB."""
+    kind, _, rest = spec.partition(":")
+    if kind == "gemm":
+        T, N, K = (int(v) for v in rest.split("x"))
+        copies = max(2, int(300e6 // (N * K * 2)) + 1)
+        ws = [(torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(copies)]
+        x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
+        out = torch.empty(T, N, dtype=torch.bfloat16, device="cuda")
+        for i in range(launches):
+            C.gemm_bf16(x, ws[i % copies], out)
+    elif kind == "attn":
+        from oxidize_b200.engine.kv_pool import KVCache, KVCacheSpec
+
+        dims, _, kvd = rest.partition(":")
+        B, ctx, nq, nkv = (int(v) for v in dims.split("x"))
+        kvd = kvd or "bf16"
+        hd, page = 128, 16
+        per = (ctx + page - 1) // page
+        layers = max(2, int(300e6 // (B * per * nkv * 2 * page * hd * 2)) + 1)
+        kv = KVCache(KVCacheSpec(layers, nkv, hd, page, kvd), B * per + 1, "cuda")
+        for d in kv.data:
+            d.random_(0, 255) if d.dtype == torch.uint8 else d.normal_()
+        for sc in kv.scales:
+            if sc is not None:
+                sc.uniform_(0.001, 0.01)
+        m = _Meta()
+        m.block_tables = (torch.arange(B * per, dtype=torch.int32, device="cuda").view(B, per) + 1).contiguous()
+        m.seq_lens = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+        m.query_start = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+        m.max_query_len, m.max_seq_len = 1, ctx
+        q = torch.randn(B, nq, hd, device="cuda").to(torch.bfloat16)
+        for i in range(launches):
+            C.paged_attention(q, kv, i % layers, m, hd ** -0.5, 0)
+    else:
+        raise SystemExit(f"unknown case {spec}")
+    torch.cuda.synchronize()
+    print("status", C.status())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--what", default="gemm,attn")
     ap.add_argument("--json", default="")
+    ap.add_argument("--case", default="", help="small case for a profiler: gemm:TxNxK or attn:BxCTXxNQxNKV[:kv]")
+    ap.add_argument("--launches", type=int, default=6)
     a = ap.parse_args()
+    if a.case:
+        small_case(a.case, a.launches)
+        return
     rows = []
     if "gemm" in a.what:
         bench_gemm(rows)

@@ -28,7 +28,11 @@ struct GemmTile {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
   static constexpr int B_BYTES = TN * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (TN <= 64) ? 8 : (TN == 128 ? 6 : 4);
+  // Decode-sized tiles keep the ring below half of the SM's shared memory: two CTAs fit per SM, so
+  // the CTAs of the NEXT kernel in the stream (launched early by programmatic dependent launch) can
+  // already stream their weights while this kernel drains, and a split-K grid may hold 2 CTAs per SM.
+  static constexpr int STAGES = TN <= 16 ? 6 : TN == 32 ? 5 : TN == 64 ? 4 : (TN == 128 ? 6 : 4);
+  static constexpr int CTAS_PER_SM = TN <= 64 ? 2 : 1;
   static constexpr int TMEM_COLS = TN < 32 ? 32 : TN;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 };
@@ -55,6 +59,53 @@ __device__ __forceinline__ void splitk_reduce(const float* base, int split_strid
       for (int s = 0; s < SMAX; ++s) acc += v[u][s];
       if (j0 + u < je) emit(j0 + u, acc);
     }
+  }
+}
+
+// Same reduction with the partials in the shared memory of the cluster's CTAs (CTA s holds split s
+// at the same shared-memory offset): `local_addr` is this thread's element of token 0 in its own CTA.
+template <int JU, int SMAX, class Emit>
+__device__ __forceinline__ void splitk_reduce_dsmem(uint32_t local_addr, int splits, int jb, int je, Emit emit) {
+  uint32_t peer[SMAX];
+#pragma unroll
+  for (int s = 0; s < SMAX; ++s) peer[s] = dsmem_map(local_addr, s < splits ? s : 0);
+  for (int j0 = jb; j0 < je; j0 += JU) {
+    float v[JU][SMAX];
+#pragma unroll
+    for (int u = 0; u < JU; ++u)
+#pragma unroll
+      for (int s = 0; s < SMAX; ++s)
+        v[u][s] = (j0 + u < je && s < splits) ? dsmem_ld_f32(peer[s] + (uint32_t)(j0 + u) * (GEMM_BM * 4)) : 0.f;
+#pragma unroll
+    for (int u = 0; u < JU; ++u) {
+      float acc = 0.f;
+#pragma unroll
+      for (int s = 0; s < SMAX; ++s) acc += v[u][s];
+      if (j0 + u < je) emit(j0 + u, acc);
+    }
+  }
+}
+
+// bf16 tile [ntok][128 rows] in shared memory -> Y rows with 16-byte stores (128 threads, tid 0..127)
+__device__ __forceinline__ void store_tile_rows(const uint8_t* stage, int ntok, int t_first, int n0, int N,
+                                                __nv_bfloat16* Y, int ldY, int epi_mode, int tid) {
+  const int chunk = tid & 15, trow = tid >> 4;
+  if (n0 + chunk * 8 >= N) return;
+  for (int t = trow; t < ntok; t += 8) {
+    uint4 v = *reinterpret_cast<const uint4*>(stage + t * 256 + chunk * 16);
+    __nv_bfloat16* dst = Y + (size_t)(t_first + t) * ldY + n0 + chunk * 8;
+    if (epi_mode == EPI_ADD_INTO) {
+      const uint4 o = *reinterpret_cast<const uint4*>(dst);
+      uint32_t a[4] = {v.x, v.y, v.z, v.w};
+      const uint32_t c[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 fa = unpack_bf16x2(a[j]), fc = unpack_bf16x2(c[j]);
+        a[j] = pack_bf16x2(fa.x + fc.x, fa.y + fc.y);
+      }
+      v = make_uint4(a[0], a[1], a[2], a[3]);
+    }
+    *reinterpret_cast<uint4*>(dst) = v;
   }
 }
 
@@ -112,6 +163,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   const int kb_begin = (int)((long long)split * kb_total / splits);
   const int kb_end = (int)((long long)(split + 1) * kb_total / splits);
   const int nkb = kb_end - kb_begin;
+  // launched as clusters of `splits` CTAs along y: split-K reduces through distributed shared memory
+  const bool csplit = splits > 1 && cluster_nctarank() == (uint32_t)splits;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) {
@@ -173,6 +226,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       }
     }
     __syncwarp();
+    if (csplit) {
+      cluster_sync_all();
+      cluster_sync_all();
+    }
   } else if (warp == 1) {
     // ---------------- MMA issuer
     if (lane == 0) {
@@ -195,6 +252,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       umma_commit(accum);
     }
     __syncwarp();
+    if (csplit) {
+      cluster_sync_all();
+      cluster_sync_all();
+    }
   } else if (warp >= 6) {
     // ---------------- dequant producers (MMQ only): thread r stages weight row n0 + r
     if constexpr (MMQ) {
@@ -218,18 +279,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         mbar_arrive(&full[st]);
       }
     }
+    __syncwarp();
+    if (csplit) {
+      cluster_sync_all();
+      cluster_sync_all();
+    }
   } else {
     // ---------------- epilogue: warps 2..5 own TMEM lane quarters (warp % 4)
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;  // row inside the 128-row tile
     const int n = n0 + row;
+    const int etid = threadIdx.x - 64;
     pdl_wait();  // everything below reads or writes global memory shared with the upstream kernel
     mbar_wait_bounded(accum, 0, abort_flag, OXB_TIMEOUT_ACCUM, blockIdx.x);
     // agree on one verdict for all 128 epilogue threads before any further named barrier
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (threadIdx.x == 64) {
       ticket[1] = (*abort_flag == 0);
-      ticket[2] = ar.world > 0 ? (ar.ctrl[0] & 1) : 0;  // buffer parity of this collective call
+      ticket[2] = ar.world > 0 ? ar.ctrl[0] : 0;  // call counter of this collective (buffer parity, epoch)
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
     const bool ok = ticket[1] != 0;
@@ -237,36 +304,103 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     const float b = (bias != nullptr && n < N) ? bias[n] : 0.f;
     const int tile_id = blockIdx.z * gridDim.x + blockIdx.x;
     const bool use_ar = ar.world > 0;
-    if (ok && splits == 1) {
+    const int tvalid = min(TN, T - t0);
+    // 16-byte output rows: the tile goes through shared memory as bf16 [token][128 rows] and leaves
+    // with coalesced vector stores (a TMEM lane holds ONE output column, so direct stores would be
+    // 2-byte writes strided by ldY).
+    const bool vec_ok = (N % 8 == 0) && (ldY % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
+    if (splits == 1) {
+      if (ok && (use_ar || vec_ok)) {
+        __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(smem);  // the pipeline memory is idle now
+        const float badd = use_ar ? 0.f : b;
 #pragma unroll 1
-      for (int c = 0; c < TN / 16; ++c) {
-        uint32_t r[16];
-        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
-        tmem_ld_wait();
+        for (int c = 0; c < TN / 16; ++c) {
+          uint32_t r[16];
+          tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) stage[(c * 16 + j) * GEMM_BM + row] = __float2bfloat16(__uint_as_float(r[j]) + badd);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
         if (use_ar) {
-          // stage the bf16 partial tile [token][128 rows] in the (now idle) pipeline memory
+          ar_exchange(ar, smem, ticket[2], tile_id, n0, t0, tvalid, N, Y, ldY, abort_flag, etid);
+        } else {
+          store_tile_rows(smem, tvalid, t0, n0, N, Y, ldY, epi_mode, etid);
+        }
+      } else if (ok) {
+#pragma unroll 1
+        for (int c = 0; c < TN / 16; ++c) {
+          uint32_t r[16];
+          tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
+          tmem_ld_wait();
+          if (n < N) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            reinterpret_cast<__nv_bfloat16*>(smem)[(c * 16 + j) * GEMM_BM + row] = __float2bfloat16(__uint_as_float(r[j]));
-        } else if (n < N) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int t = t0 + c * 16 + j;
-            if (t < T) {
-              float v = __uint_as_float(r[j]) + b;
-              __nv_bfloat16* dst = Y + (size_t)t * ldY + n;
-              if (epi_mode == EPI_ADD_INTO) v += __bfloat162float(*dst);
-              *dst = __float2bfloat16(v);
+            for (int j = 0; j < 16; ++j) {
+              const int t = t0 + c * 16 + j;
+              if (t < T) {
+                float v = __uint_as_float(r[j]) + b;
+                __nv_bfloat16* dst = Y + (size_t)t * ldY + n;
+                if (epi_mode == EPI_ADD_INTO) v += __bfloat162float(*dst);
+                *dst = __float2bfloat16(v);
+              }
             }
           }
         }
       }
-      if (use_ar) {
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        ar_exchange(ar, smem, ticket[2], tile_id, n0, t0, min(TN, T - t0), N, Y, ldY, abort_flag, threadIdx.x - 64);
+    } else if (csplit) {
+      // Split-K inside a thread-block cluster: the `splits` CTAs of a tile are one cluster.  Each
+      // writes its fp32 partial [token][128 rows] into its OWN shared memory, the cluster meets at a
+      // hardware barrier, and CTA r sums token slice r straight out of its peers' shared memory
+      // (distributed shared memory loads, fixed split order).  No global scratch, atomics or polling.
+      float* part = reinterpret_cast<float*>(smem);
+      if (ok) {
+#pragma unroll 1
+        for (int c = 0; c < TN / 16; ++c) {
+          uint32_t r[16];
+          tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) part[(c * 16 + j) * GEMM_BM + row] = __uint_as_float(r[j]);
+        }
+      }
+      cluster_sync_all();
+      const int chunk = (tvalid + splits - 1) / splits;
+      const int jb = min(tvalid, split * chunk), je = min(tvalid, jb + chunk);
+      uint8_t* stage_b = smem + TN * GEMM_BM * 4;
+      if (ok) {
+        __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(stage_b);
+        const float badd = use_ar ? 0.f : b;
+        const uint32_t a0 = smem_u32(part + row);
+        auto emit = [&](int j, float acc) { stage[(j - jb) * GEMM_BM + row] = __float2bfloat16(acc + badd); };
+        if (splits <= 2) {
+          splitk_reduce_dsmem<8, 2>(a0, splits, jb, je, emit);
+        } else if (splits <= 4) {
+          splitk_reduce_dsmem<8, 4>(a0, splits, jb, je, emit);
+        } else if (splits <= 8) {
+          splitk_reduce_dsmem<4, 8>(a0, splits, jb, je, emit);
+        } else {
+          splitk_reduce_dsmem<2, 16>(a0, splits, jb, je, emit);
+        }
+      }
+      cluster_sync_all();  // every peer has finished reading this CTA's partial
+      if (ok && je > jb) {
+        if (use_ar) {
+          ar_exchange(ar, stage_b, ticket[2], tile_id * splits + split, n0, t0 + jb, je - jb, N, Y, ldY, abort_flag, etid);
+        } else if (vec_ok) {
+          store_tile_rows(stage_b, je - jb, t0 + jb, n0, N, Y, ldY, epi_mode, etid);
+        } else if (n < N) {
+          const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(stage_b);
+          for (int j = jb; j < je; ++j) {
+            float v = __bfloat162float(stage[(j - jb) * GEMM_BM + row]);
+            __nv_bfloat16* dst = Y + (size_t)(t0 + j) * ldY + n;
+            if (epi_mode == EPI_ADD_INTO) v += __bfloat162float(*dst);
+            *dst = __float2bfloat16(v);
+          }
+        }
       }
     } else if (ok) {
-      // fp32 partial -> workspace [tile][split][token][row]
+      // Split-K through global scratch (launches without a cluster): fp32 partial -> workspace
+      // [tile][split][token][row]
       float* my = ws + ((size_t)tile_id * splits + split) * (size_t)(TN * GEMM_BM);
 #pragma unroll 1
       for (int c = 0; c < TN / 16; ++c) {
@@ -303,7 +437,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (ticket[1] != 0) {
         const float* base = ws + (size_t)tile_id * splits * (size_t)(TN * GEMM_BM) + row;
-        const int tvalid = min(TN, T - t0);
         const int chunk = (tvalid + splits - 1) / splits;
         const int jb = min(tvalid, split * chunk), je = min(tvalid, jb + chunk);
         __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(smem);
@@ -327,8 +460,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         if (use_ar) {
           asm volatile("bar.sync 1, 128;" ::: "memory");
           if (je > jb)
-            ar_exchange(ar, smem, ticket[2], tile_id * splits + split, n0, t0 + jb, je - jb, N, Y, ldY, abort_flag,
-                        threadIdx.x - 64);
+            ar_exchange(ar, smem, ticket[2], tile_id * splits + split, n0, t0 + jb, je - jb, N, Y, ldY, abort_flag, etid);
         }
         // the last CTA to leave re-arms the counters for the next launch / graph replay
         if (threadIdx.x == 64) {
@@ -362,33 +494,83 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 
 struct GemmPlan {
   int tn, n_tiles, t_tiles, splits;
+  int cluster;  // 1: the splits of a tile form a thread-block cluster (no global scratch needed)
   size_t ws_bytes;
   int n_counters;
 };
 
-inline GemmPlan gemm_plan(int T, int N, int K, int splits_hint, int sm_count) {
+extern int g_oxb_cluster_splitk;  // 1 = split-K through clusters / distributed shared memory (default)
+
+// cluster_ok < 0: follow g_oxb_cluster_splitk.  max_ctas > 0 bounds tiles*splits (kernels whose CTAs wait
+// for CTAs of other GPUs must be resident all at once).
+inline GemmPlan gemm_plan(int T, int N, int K, int splits_hint, int sm_count, int cluster_ok = -1, int max_ctas = 0) {
   GemmPlan p;
+  if (cluster_ok < 0) cluster_ok = g_oxb_cluster_splitk;
   p.tn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
   p.n_tiles = (N + GEMM_BM - 1) / GEMM_BM;
   p.t_tiles = (T + p.tn - 1) / p.tn;
   const int kb_total = (K + GEMM_BK - 1) / GEMM_BK;
   int splits = splits_hint;
   if (splits <= 0) {
+    // Among the admissible split counts pick the one with the smallest critical path: k-blocks
+    // streamed by the busiest SM plus a fixed cost per split for the reduction.  Without clusters
+    // the CTAs of a split tile meet at a global counter and must all be resident, which bounds
+    // tiles*splits by the SMs' capacity; clusters are co-scheduled by the hardware.
     const int tiles = p.n_tiles * p.t_tiles;
+    const int resident = sm_count * (p.tn <= 64 ? 2 : 1);
+    // Tiles wider than 64 tokens hold one CTA per SM, and their partials are large: split only
+    // within one wave.  Nothing is split once the tiles alone fill the SMs.
+    const int wave_cap = p.tn <= 64 ? (1 << 30) : sm_count;
+    int capacity = max_ctas > 0 ? max_ctas : (cluster_ok ? wave_cap : resident);
+    if (capacity > wave_cap) capacity = wave_cap;
+    const int max_by_k = kb_total / 4 > 0 ? kb_total / 4 : 1;  // at least 4 k-blocks (256 columns) per split
+    const int epi = p.tn / 32;                                 // k-block equivalents of writing and reducing a partial
+    long long best_cost = -1;
     splits = 1;
-    if (tiles < sm_count) {
-      splits = sm_count / tiles;
-      const int max_by_k = kb_total / 4 > 0 ? kb_total / 4 : 1;  // at least 4 k-blocks (256 columns) per split
-      if (splits > max_by_k) splits = max_by_k;
-      if (splits > 16) splits = 16;
-      if (splits < 1) splits = 1;
+    for (int s = 1; s <= 16 && s <= max_by_k && (long long)tiles * s <= capacity && (s == 1 || tiles < sm_count); ++s) {
+      const int per_cta = (kb_total + s - 1) / s;
+      const int ctas_on_busiest = (tiles * s + sm_count - 1) / sm_count;
+      const long long cost = (long long)ctas_on_busiest * (per_cta + 3) + (s > 1 ? 2 + s / 4 + epi : 0);
+      if (best_cost < 0 || cost < best_cost) {
+        best_cost = cost;
+        splits = s;
+      }
     }
   }
   if (splits > kb_total) splits = kb_total;
   p.splits = splits;
-  p.ws_bytes = splits > 1 ? (size_t)p.n_tiles * p.t_tiles * splits * p.tn * GEMM_BM * sizeof(float) : 0;
-  p.n_counters = 2 * p.n_tiles * p.t_tiles;
+  p.cluster = (cluster_ok && splits > 1 && splits <= 16) ? 1 : 0;
+  const bool scratch = splits > 1 && !p.cluster;
+  p.ws_bytes = scratch ? (size_t)p.n_tiles * p.t_tiles * splits * p.tn * GEMM_BM * sizeof(float) : 0;
+  p.n_counters = scratch ? 2 * p.n_tiles * p.t_tiles : 0;
   return p;
+}
+
+// Largest cluster the kernel instance can be launched with: 16 where the device accepts the
+// non-portable size for this footprint, else the portable 8.
+template <int TN, int QT>
+int gemm_max_cluster() {
+  static int cached = 0;
+  if (cached) return cached;
+  cached = 8;
+  auto kfn = gemm_bf16_kernel<TN, QT>;
+  if (cudaFuncSetAttribute(kfn, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, 16, 1);
+    cfg.blockDim = dim3(QT == QT_BF16 ? GEMM_THREADS : GEMM_THREADS_MMQ);
+    cfg.dynamicSmemBytes = GemmTile<TN>::SMEM_BYTES;
+    cudaLaunchAttribute at;
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = 1;
+    at.val.clusterDim.y = 16;
+    at.val.clusterDim.z = 1;
+    cfg.attrs = &at;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kfn, &cfg) == cudaSuccess && n > 0) cached = 16;
+  }
+  cudaGetLastError();
+  return cached;
 }
 
 template <int TN, int QT = QT_BF16>
@@ -404,10 +586,21 @@ int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid(p.n_tiles, p.splits, gr.enabled ? groups : p.t_tiles);
-  cudaError_t le = oxb_launch(gemm_bf16_kernel<TN, QT>, grid, dim3(QT == QT_BF16 ? GEMM_THREADS : GEMM_THREADS_MMQ),
-                              (size_t)Cfg::SMEM_BYTES, stream, tmW, tmX, Y, bias, N, T, K, ldY, p.splits, ws, counters,
-                              epi_mode, ar, qw, gr);
+  int splits = p.splits;
+  if (p.cluster) {
+    const int mc = gemm_max_cluster<TN, QT>();
+    if (splits > mc) splits = mc;
+  }
+  dim3 grid(p.n_tiles, splits, gr.enabled ? groups : p.t_tiles);
+  const dim3 block(QT == QT_BF16 ? GEMM_THREADS : GEMM_THREADS_MMQ);
+  cudaError_t le;
+  if (p.cluster && splits > 1) {
+    le = oxb_launch_cluster(gemm_bf16_kernel<TN, QT>, grid, block, dim3(1, splits, 1), (size_t)Cfg::SMEM_BYTES, stream, tmW,
+                            tmX, Y, bias, N, T, K, ldY, splits, ws, counters, epi_mode, ar, qw, gr);
+  } else {
+    le = oxb_launch(gemm_bf16_kernel<TN, QT>, grid, block, (size_t)Cfg::SMEM_BYTES, stream, tmW, tmX, Y, bias, N, T, K, ldY,
+                    splits, ws, counters, epi_mode, ar, qw, gr);
+  }
   if (le != cudaSuccess) return (int)le;
   OXB_CHECK_LAUNCH();
   return 0;

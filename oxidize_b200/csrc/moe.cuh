@@ -24,7 +24,8 @@ constexpr int MOE_MAX_TOPK = 16;
 __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E, int ld, int k, int sigmoid,
                                  const float* __restrict__ sel_bias, int renorm, float weight_scale,
                                  int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ scale,
-                                 int scale_ld, int first_local, int n_local) {
+                                 int scale_ld, int first_local, int n_local, int n_groups, int groups_used) {
+  __shared__ float s_sel[4][MOE_MAX_EXPERTS];  // launch uses 4 warps per block
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -60,6 +61,41 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E,
   for (int j = 0; j < PER; ++j) {
     const int e = lane + 32 * j;
     sel[j] = e < E ? score[j] + (sel_bias != nullptr ? sel_bias[e] : 0.f) : -INFINITY;
+  }
+  if (n_groups > 1 && groups_used > 0) {
+    // group-limited routing (DeepSeek): experts form n_groups (<= 32) contiguous groups; only the
+    // groups_used best groups stay eligible.  Group score = sum of the two best biased scores when a
+    // selection bias exists, else the best score.  Lane g scores group g from the warp's row in shared memory.
+    float* row_sel = s_sel[threadIdx.x >> 5];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) row_sel[lane + 32 * j] = sel[j];
+    __syncwarp();
+    const int gs = E / n_groups;
+    float gscore = -INFINITY;
+    if (lane < n_groups) {
+      float b1 = -INFINITY, b2 = -INFINITY;
+      for (int i = 0; i < gs; ++i) {
+        const float v = row_sel[lane * gs + i];
+        if (v > b1) {
+          b2 = b1;
+          b1 = v;
+        } else if (v > b2) {
+          b2 = v;
+        }
+      }
+      gscore = (sel_bias != nullptr && gs >= 2) ? b1 + b2 : b1;
+    }
+    int better = 0;
+    for (int g = 0; g < n_groups; ++g) {
+      const float og = __shfl_sync(0xffffffffu, gscore, g);
+      better += (og > gscore || (og == gscore && g < lane)) ? 1 : 0;
+    }
+    const unsigned keep = __ballot_sync(0xffffffffu, lane < n_groups && better < groups_used);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int e = lane + 32 * j;
+      if (e < E && !((keep >> (e / gs)) & 1u)) sel[j] = -INFINITY;
+    }
   }
   // iterative top-k: warp arg-max, ties to the lowest expert index
   int my_id[MOE_MAX_TOPK];

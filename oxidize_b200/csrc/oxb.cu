@@ -12,11 +12,23 @@
 using namespace oxb;
 
 int g_oxb_pdl = 1;
-int g_oxb_ar_twoshot_min_world = 4;  // rank counts from which the fused all-reduce goes two-shot
+int oxb::g_oxb_cluster_splitk = 1;
 
-OXB_API int oxb_set_ar_twoshot_min_world(int w) {
-  const int old = g_oxb_ar_twoshot_min_world;
-  g_oxb_ar_twoshot_min_world = w;
+OXB_API int oxb_set_cluster_splitk(int on) {
+  const int old = g_oxb_cluster_splitk;
+  g_oxb_cluster_splitk = on ? 1 : 0;
+  return old;
+}
+int g_oxb_ar_ll_min_world = 2;  // rank counts from which the fused all-reduce uses the LL two-shot exchange
+
+static unsigned long long* g_oxb_ar_trace = nullptr;
+
+// Device buffer of 16 u64 that receives phase timestamps of piece 0 of each fused all-reduce (null = off).
+OXB_API void oxb_set_ar_trace(unsigned long long* p) { g_oxb_ar_trace = p; }
+
+OXB_API int oxb_set_ar_ll_min_world(int w) {
+  const int old = g_oxb_ar_ll_min_world;
+  g_oxb_ar_ll_min_world = w;
   return old;
 }
 
@@ -101,7 +113,7 @@ OXB_API int oxb_gemm_bf16(const void* X, const void* W, void* Y, const float* bi
   if (K % 8 != 0) return (int)cudaErrorInvalidValue;  // TMA rows must be 16-byte multiples
   GemmPlan p = gemm_plan(T, N, K, splits_hint, sm_count());
   // split-K CTAs of a tile wait for one another, so the whole grid has to fit in one wave
-  while (p.splits > 1 && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || ws == nullptr || counters == nullptr ||
+  while (p.splits > 1 && !p.cluster && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || ws == nullptr || counters == nullptr ||
                           p.n_tiles * p.t_tiles * p.splits > sm_count()))
     p = gemm_plan(T, N, K, p.splits - 1, sm_count());
   CUtensorMap tmW, tmX;
@@ -131,7 +143,7 @@ OXB_API int oxb_gemm_quant(const void* X, const void* Wq, int qtype, size_t row_
   if (T <= 0 || N <= 0 || K <= 0) return 0;
   if (K % 64 != 0) return (int)cudaErrorInvalidValue;
   GemmPlan p = gemm_plan(T, N, K, splits_hint, sm_count());
-  while (p.splits > 1 && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || ws == nullptr || counters == nullptr ||
+  while (p.splits > 1 && !p.cluster && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || ws == nullptr || counters == nullptr ||
                           p.n_tiles * p.t_tiles * p.splits > sm_count()))
     p = gemm_plan(T, N, K, p.splits - 1, sm_count());
   CUtensorMap tmX;
@@ -158,7 +170,8 @@ OXB_API int oxb_gemm_quant(const void* X, const void* Wq, int qtype, size_t row_
 static int fill_ar(ArArgs& ar, int world, int rank, const uint64_t* data_ptrs, const uint64_t* flag_ptrs, int* ctrl,
                    int t_max, int n_max, int max_tiles, unsigned long long timeout_ns, const void* residual) {
   memset(&ar, 0, sizeof(ar));
-  ar.mode = world >= g_oxb_ar_twoshot_min_world ? 1 : 0;
+  ar.mode = world >= g_oxb_ar_ll_min_world ? 1 : 0;
+  ar.trace = g_oxb_ar_trace;
   if (world < 1 || world > AR_MAX_WORLD || rank < 0 || rank >= world || ctrl == nullptr) return (int)cudaErrorInvalidValue;
   ar.world = world;
   ar.rank = rank;
@@ -187,12 +200,16 @@ OXB_API int oxb_gemm_ar(const void* X, const void* W, void* Y, const void* resid
                         int n_counters, cudaStream_t stream) {
   if (T <= 0 || N <= 0 || K <= 0) return 0;
   if (K % 8 != 0 || N % 8 != 0 || T > 256 || T > t_max || N > n_max) return (int)cudaErrorInvalidValue;
-  GemmPlan p = gemm_plan(T, N, K, 0, sm_count());
-  while (p.splits > 1 && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || ws == nullptr || counters == nullptr ||
-                          p.n_tiles * p.splits > sm_count()))
-    p = gemm_plan(T, N, K, p.splits - 1, sm_count());
-  if (p.n_tiles * p.splits > max_tiles || p.n_tiles * p.splits * p.t_tiles > sm_count() || p.t_tiles != 1)
-    return (int)cudaErrorInvalidConfiguration;
+  // CTAs wait for the CTAs with the same piece index on the other GPUs, so the whole grid has to be
+  // resident at once on every rank: bound tiles*splits by what the SMs can hold.
+  const int ll = world >= g_oxb_ar_ll_min_world;
+  int resident = sm_count() * (T <= 64 ? GemmTile<64>::CTAS_PER_SM : 1);
+  if (!ll && resident > max_tiles) resident = max_tiles;  // the one-shot exchange has one flag per piece
+  GemmPlan p = gemm_plan(T, N, K, 0, sm_count(), -1, resident);
+  while (p.splits > 1 && !p.cluster && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || ws == nullptr || counters == nullptr ||
+                                        p.n_tiles * p.splits > sm_count()))
+    p = gemm_plan(T, N, K, p.splits - 1, sm_count(), -1, resident);
+  if (p.n_tiles * p.splits > resident || p.t_tiles != 1) return (int)cudaErrorInvalidConfiguration;
   ArArgs ar;
   int e = fill_ar(ar, world, rank, data_ptrs, flag_ptrs, ctrl, t_max, n_max, max_tiles, timeout_ns, residual);
   if (e) return e;
@@ -218,20 +235,25 @@ OXB_API int oxb_allreduce_oneshot(const void* X, void* Y, int T, int N, int ld, 
                                   int max_tiles, unsigned long long timeout_ns, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
   const int tiles = (N + 127) / 128;
-  if (N % 8 != 0 || T > t_max || N > n_max || tiles > max_tiles || tiles > sm_count() * 4 || T * 256 > 200 * 1024)
+  // LL exchange: pieces of 16 tokens (more CTAs, shorter polls); one-shot: one piece per column tile (one flag each)
+  const int ll = world >= g_oxb_ar_ll_min_world;
+  const int tg = ll ? 16 : T;
+  const int groups = (T + tg - 1) / tg;
+  if (N % 8 != 0 || T > t_max || N > n_max || (!ll && tiles > max_tiles) || tiles * groups > sm_count() * 8 ||
+      tg * 256 > 200 * 1024)
     return (int)cudaErrorInvalidValue;
   ArArgs ar;
   int e = fill_ar(ar, world, rank, data_ptrs, flag_ptrs, ctrl, t_max, n_max, max_tiles, timeout_ns, nullptr);
   if (e) return e;
-  const size_t smem = (size_t)T * 256;
+  const size_t smem = (size_t)tg * 256;
   static size_t configured = 48 * 1024;
   if (smem > configured) {
     cudaError_t ce = cudaFuncSetAttribute(allreduce_oneshot_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (ce != cudaSuccess) return (int)ce;
     configured = smem;
   }
-  oxb_launch(allreduce_oneshot_kernel, dim3(tiles), dim3(128), smem, stream, ar, reinterpret_cast<const __nv_bfloat16*>(X),
-             reinterpret_cast<__nv_bfloat16*>(Y), T, N, ld);
+  oxb_launch(allreduce_oneshot_kernel, dim3(tiles, groups), dim3(128), smem, stream, ar,
+             reinterpret_cast<const __nv_bfloat16*>(X), reinterpret_cast<__nv_bfloat16*>(Y), T, N, ld, tg);
   OXB_CHECK_LAUNCH();
   return 0;
 }
@@ -438,9 +460,9 @@ extern "C" __attribute__((visibility("default"))) int oxb_gemm_bf16_noalloc(
   float* ws = reinterpret_cast<float*>(base + OXB_NOALLOC_COUNTER_BYTES);
   const size_t ws_bytes = OXB_NOALLOC_SCRATCH_BYTES - OXB_NOALLOC_COUNTER_BYTES;
   const int n_counters = OXB_NOALLOC_COUNTER_BYTES / (int)sizeof(int);
-  GemmPlan p = gemm_plan(T, N, K, 0, sm_count());
+  GemmPlan p = gemm_plan(T, N, K, 0, sm_count(), 0);  // always the global-scratch split-K: that is what this entry is for
   while (p.splits > 1 && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || p.n_tiles * p.t_tiles * p.splits > sm_count()))
-    p = gemm_plan(T, N, K, p.splits - 1, sm_count());
+    p = gemm_plan(T, N, K, p.splits - 1, sm_count(), 0);
   if (p.splits > 1) {
     // the counters must start at zero; an earlier call that gave up could have left them set
     ce = cudaMemsetAsync(counters, 0, (size_t)p.n_counters * sizeof(int), stream);
@@ -468,12 +490,14 @@ extern "C" __attribute__((visibility("default"))) int oxb_gemm_bf16_noalloc(
 
 OXB_API int oxb_moe_route(const float* logits, int T, int E, int ld, int k, int sigmoid, const float* sel_bias, int renorm,
                           float weight_scale, int* ids, float* wts, float* scale, int scale_ld, int first_local,
-                          int n_local, cudaStream_t stream) {
+                          int n_local, int n_groups, int groups_used, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (E > MOE_MAX_EXPERTS || k > MOE_MAX_TOPK || k < 1 || k > E) return (int)cudaErrorInvalidValue;
+  if (n_groups > 1 && (n_groups > 32 || E % n_groups != 0 || groups_used > n_groups)) return (int)cudaErrorInvalidValue;
   const int warps = 4;
   cudaError_t e = oxb_launch(moe_route_kernel, dim3((T + warps - 1) / warps), dim3(warps * 32), 0, stream, logits, T, E, ld,
-                             k, sigmoid, sel_bias, renorm, weight_scale, ids, wts, scale, scale_ld, first_local, n_local);
+                             k, sigmoid, sel_bias, renorm, weight_scale, ids, wts, scale, scale_ld, first_local, n_local,
+                             n_groups, groups_used);
   if (e != cudaSuccess) return (int)e;
   OXB_CHECK_LAUNCH();
   return 0;
@@ -502,7 +526,7 @@ OXB_API int oxb_gemm_grouped(const void* X, int x_rows, const void* W, int qtype
   if (T <= 0 || N <= 0 || K <= 0 || groups <= 0) return 0;
   if (T > 256 || K % 64 != 0) return (int)cudaErrorInvalidValue;
   GemmPlan p = gemm_plan(T, N, K, 0, sm_count());
-  while (p.splits > 1 && (p.ws_bytes * groups > ws_bytes || p.n_counters * groups > n_counters || ws == nullptr ||
+  while (p.splits > 1 && !p.cluster && (p.ws_bytes * groups > ws_bytes || p.n_counters * groups > n_counters || ws == nullptr ||
                           counters == nullptr || p.n_tiles * p.splits * groups > sm_count()))
     p = gemm_plan(T, N, K, p.splits - 1, sm_count());
   CUtensorMap tmW, tmX;

@@ -42,6 +42,8 @@ def lib():
                 _declare(_lib)
                 if os.environ.get("OXB_PDL", "1") == "0":
                     _lib.oxb_set_pdl(0)
+                if os.environ.get("OXB_CLUSTER_SPLITK", "1") == "0":
+                    _lib.oxb_set_cluster_splitk(0)
     return _lib
 
 

@@ -29,7 +29,7 @@ def _declare(L):
     if getattr(L, "_moe_declared", False):
         return
     vp, i32, f32, sz, ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t, ctypes.c_longlong
-    L.oxb_moe_route.argtypes = [vp, i32, i32, i32, i32, i32, vp, i32, f32, vp, vp, vp, i32, i32, i32, vp]
+    L.oxb_moe_route.argtypes = [vp, i32, i32, i32, i32, i32, vp, i32, f32, vp, vp, vp, i32, i32, i32, i32, i32, vp]
     L.oxb_moe_combine.argtypes = [vp, vp, i32, vp, vp, i32, i32, i32, vp]
     L.oxb_gemm_grouped.argtypes = [vp, i32, vp, i32, sz, vp, ll, vp, i32, i32, i32, i32, i32, i32, vp, sz, vp, i32, vp]
     L._moe_declared = True
@@ -37,18 +37,19 @@ def _declare(L):
 
 def moe_route(logits: torch.Tensor, cfg, bias: Optional[torch.Tensor] = None, scale_out: Optional[torch.Tensor] = None,
               first_local: int = 0, n_local: int = 0):
-    """(ids [T,k] int32, weights [T,k] f32); group-limited routing falls back to the torch statement."""
-    if cfg.expert_group_count > 1 and cfg.expert_group_used_count > 0 or cfg.n_experts > 256 or cfg.n_experts_used > 16:
+    """(ids [T,k] int32, weights [T,k] f32); shapes beyond the kernel's limits use the torch statement
+    (no host synchronisation either way, so both can be captured in a CUDA graph)."""
+    grouped = cfg.expert_group_count > 1 and cfg.expert_group_used_count > 0
+    if (cfg.n_experts > 256 or cfg.n_experts_used > 16
+            or grouped and (cfg.expert_group_count > 32 or cfg.n_experts % cfg.expert_group_count)):
         from . import ref
 
         ids, w = ref.moe_route(logits, cfg, bias)
         if scale_out is not None:
-            scale_out.zero_()
             T = ids.shape[0]
-            for j in range(ids.shape[1]):
-                loc = ids[:, j].long() - first_local
-                ok = (loc >= 0) & (loc < n_local)
-                scale_out[loc[ok], torch.arange(T, device=ids.device)[ok]] += w[ok, j]
+            full = torch.zeros(T, cfg.n_experts, dtype=torch.float32, device=ids.device)
+            full.scatter_add_(1, ids.long(), w.float())
+            scale_out[:, :T].copy_(full[:, first_local:first_local + n_local].t())
         return ids, w
     L = C.lib()
     _declare(L)
@@ -60,7 +61,9 @@ def moe_route(logits: torch.Tensor, cfg, bias: Optional[torch.Tensor] = None, sc
     C._check(L.oxb_moe_route(logits.data_ptr(), T, E, logits.stride(0), k, 1 if cfg.expert_gating == "sigmoid" else 0,
                              C._p(bias), 1 if cfg.expert_weights_norm else 0, float(cfg.expert_weights_scale),
                              ids.data_ptr(), w.data_ptr(), C._p(scale_out),
-                             0 if scale_out is None else scale_out.stride(0), first_local, n_local, C._stream()),
+                             0 if scale_out is None else scale_out.stride(0), first_local, n_local,
+                             cfg.expert_group_count if grouped else 1, cfg.expert_group_used_count if grouped else 0,
+                             C._stream()),
              "oxb_moe_route")
     return ids, w
 

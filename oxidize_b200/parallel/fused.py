@@ -27,7 +27,7 @@ AR_MAX_TOKENS = 256  # one token tile per fused call
 
 class FusedComm(TorchComm):
     def __init__(self, device: torch.device, max_tokens: int = 256, hidden: int = 8192, group=None,
-                 timeout_s: float = 5.0, max_tiles: int = 160):
+                 timeout_s: float = 5.0, max_tiles: int = 320):
         super().__init__(group)
         self.device = torch.device(device)
         self.t_max = max(16, min(int(max_tokens), AR_MAX_TOKENS))
@@ -50,7 +50,8 @@ class FusedComm(TorchComm):
                     enable(pg.group_name)
                 except Exception:
                     pass
-            self.data = symm.empty(2 * (W + 1) * self.t_max * self.n_max, dtype=torch.bfloat16, device=self.device)
+            # 4 bytes per element: the LL exchange carries a 4-byte epoch beside every 4 bytes of payload
+            self.data = symm.empty(2 * (W + 1) * self.t_max * self.n_max * 2, dtype=torch.bfloat16, device=self.device)
             self.flags = symm.empty(2 * (W + 1) * self.max_tiles, dtype=torch.int32, device=self.device)
             self.data.zero_()
             self.flags.zero_()
@@ -60,10 +61,16 @@ class FusedComm(TorchComm):
             data_ptrs = [int(p) for p in h_data.buffer_ptrs]
             flag_ptrs = [int(p) for p in h_flags.buffer_ptrs]
         else:
-            self.data = torch.zeros(2 * 9 * self.t_max * self.n_max, dtype=torch.bfloat16, device=self.device)
+            self.data = torch.zeros(2 * 9 * self.t_max * self.n_max * 2, dtype=torch.bfloat16, device=self.device)
             self.flags = torch.zeros(2 * 9 * self.max_tiles, dtype=torch.int32, device=self.device)
             data_ptrs, flag_ptrs = [self.data.data_ptr()], [self.flags.data_ptr()]
         self.set_peer_pointers(data_ptrs, flag_ptrs)
+        import os
+
+        if os.environ.get("OXB_AR_LL_MIN_WORLD"):
+            from ..ops import cuda as C
+
+            C.lib().oxb_set_ar_ll_min_world(int(os.environ["OXB_AR_LL_MIN_WORLD"]))
         self.ctrl = torch.zeros(4, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize(self.device)
         self.barrier()
@@ -88,8 +95,7 @@ class FusedComm(TorchComm):
             return False
         from ..ops import cuda as C
 
-        plan = C.gemm_plan(T, N, K)
-        return plan["t_tiles"] == 1 and plan["n_tiles"] * plan["splits"] <= min(self.max_tiles, C.sm_count(x.device))
+        return (N + 127) // 128 <= min(self.max_tiles, C.sm_count(x.device))
 
     def linear_allreduce(self, x: torch.Tensor, w, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         """sum_r x_r @ W_r^T (+ residual) on every rank; fused when the shape allows."""
@@ -119,7 +125,7 @@ class FusedComm(TorchComm):
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         if (self.size > 1 and x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
                 and 0 < x.shape[0] <= min(self.t_max, 512) and x.shape[1] <= self.n_max and x.shape[1] % 8 == 0
-                and (x.shape[1] + 127) // 128 <= self.max_tiles):
+                and (x.shape[1] + 127) // 128 <= min(self.max_tiles, 148)):
             from ..ops import cuda as C
 
             T, N = x.shape

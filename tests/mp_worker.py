@@ -46,7 +46,7 @@ def case_gemm_ar(dev, comm_kind):
     shapes = [(64, 8192, 1024), (64, 8192, 3584), (1, 1024, 512), (200, 2048, 256), (16, 4096, 1792)]
     # both exchanges at every rank count: one-shot (push to all) and two-shot (owner reduces, broadcasts)
     for min_world, (T, N, K) in [(m, s) for m in (99, 2) for s in shapes]:
-        C.lib().oxb_set_ar_twoshot_min_world(min_world)
+        C.lib().oxb_set_ar_ll_min_world(min_world)
         for rep in range(3):
             g = torch.Generator(device=dev)
             g.manual_seed(1000 * rank + 17 * rep + T)
@@ -67,14 +67,14 @@ def case_gemm_ar(dev, comm_kind):
     assert comm.fused_calls > 0
     # stand-alone all-reduce, both exchanges
     for min_world in (99, 2):
-        C.lib().oxb_set_ar_twoshot_min_world(min_world)
+        C.lib().oxb_set_ar_ll_min_world(min_world)
         for T, N in [(64, 8192), (3, 1024), (256, 4096)]:
             x = torch.randn(T, N, device=dev).to(torch.bfloat16)
             want = x.float().clone()
             dist.all_reduce(want)
             got = comm.all_reduce(x.clone())
             assert rel_err(got, want) < 1e-2
-    C.lib().oxb_set_ar_twoshot_min_world(4)
+    C.lib().oxb_set_ar_ll_min_world(2)
     code, detail, count = C.status()
     assert code == 0, (code, detail, count)
 

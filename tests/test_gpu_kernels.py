@@ -340,13 +340,16 @@ def test_device_sampler_matches_host_oracle(C):
     assert match >= int(0.9 * R), f"{match}/{R} rows agree"
 
 
-@pytest.mark.parametrize("E,k,gating,bias", [(8, 2, "softmax", False), (128, 8, "softmax", False), (64, 6, "sigmoid", True)])
-def test_moe_route_kernel(C, E, k, gating, bias):
+@pytest.mark.parametrize("E,k,gating,bias,groups", [(8, 2, "softmax", False, (0, 0)), (128, 8, "softmax", False, (0, 0)),
+                                                    (64, 6, "sigmoid", True, (0, 0)), (64, 6, "sigmoid", True, (8, 4)),
+                                                    (256, 8, "sigmoid", False, (8, 3))])
+def test_moe_route_kernel(C, E, k, gating, bias, groups):
     from oxidize_b200.models.config import ModelConfig
     from oxidize_b200.ops import cuda_moe, ref
 
     torch.manual_seed(E)
-    cfg = ModelConfig(n_experts=E, n_experts_used=k, expert_gating=gating, expert_weights_scale=2.5 if bias else 1.0)
+    cfg = ModelConfig(n_experts=E, n_experts_used=k, expert_gating=gating, expert_weights_scale=2.5 if bias else 1.0,
+                      expert_group_count=groups[0], expert_group_used_count=groups[1])
     T = 37
     logits = torch.randn(T, E, device="cuda")
     b = torch.randn(E, device="cuda") * 0.1 if bias else None
