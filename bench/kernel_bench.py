@@ -101,6 +101,19 @@ def bench_attn(rows):
         m.query_start = torch.arange(B + 1, dtype=torch.int32, device="cuda")
         m.max_query_len, m.max_seq_len = 1, ctx
         q = torch.randn(B, nq, hd, device="cuda").to(torch.bfloat16)
+        if os.environ.get("KB_ATTN_TRACE"):
+            import ctypes
+
+            trace = torch.zeros(16, dtype=torch.int64, device="cuda")
+            C.lib().oxb_set_attn_trace.argtypes = [ctypes.c_void_p]
+            C.lib().oxb_set_attn_trace(trace.data_ptr())
+            for i in range(3):
+                C.paged_attention(q, kv, i % layers, m, hd ** -0.5, 0)
+                torch.cuda.synchronize()
+            tr = trace.cpu().tolist()
+            print("attention phases of CTA 0 (ns): entry->dep wait, ->setup, ->first page, ->pages done, ->drain, ->cta merge, "
+                  "->ticket+final", [tr[i + 1] - tr[i] for i in range(7)], flush=True)
+            C.lib().oxb_set_attn_trace(None)
         for splits in (None, 1, 2, 4, 8):
             t = timeit(lambda i: C.paged_attention(q, kv, i % layers, m, hd ** -0.5, 0, splits=splits))
             eb = {"bf16": 2, "q8": 1 + 4 / 32}[kvd]

@@ -36,7 +36,17 @@ struct AttnArgs {
   float* ws_o;   // [B*nkv*max_mtiles*n_cta_splits, 16, hd]
   float* ws_ml;  // [.., 16, 2]
   int* counters; // [B*nkv*max_mtiles] zero-initialised tickets (CTA splits only)
+  unsigned long long* trace;  // optional: phase timestamps (globaltimer ns) of CTA (0,0,0), for latency analysis
 };
+
+#define ATT_STAMP(i)                                                                                          \
+  do {                                                                                                        \
+    if (a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {    \
+      unsigned long long t_;                                                                                  \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                                \
+      a.trace[i] = t_;                                                                                        \
+    }                                                                                                         \
+  } while (0)
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
@@ -172,8 +182,10 @@ paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
   constexpr int KS = HD / 16;  // k-steps for QK^T
   constexpr int NT = HD / 8;   // n-tiles of the output
   extern __shared__ __align__(16) uint8_t att_smem[];
+  ATT_STAMP(0);
   pdl_launch_dependents();
   pdl_wait();
+  ATT_STAMP(1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
@@ -241,6 +253,7 @@ paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
     return r < 32 ? va : vb;
   };
 
+  ATT_STAMP(2);
   // prologue: fill the ring
 #pragma unroll
   for (int s = 0; s < ATT_STAGES - 1; ++s) {
@@ -259,6 +272,7 @@ paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
     cp_async_commit();
     cp_async_wait<ATT_STAGES - 1>();
     __syncwarp();
+    if (it == 0) ATT_STAMP(3);
     uint8_t* st = my_stage + (it % ATT_STAGES) * STAGE_BYTES;
     if (a.kv_mode != 0) {
       uint8_t* dec = att_smem + (size_t)(ATT_WARPS * ATT_STAGES + warp) * STAGE_BYTES;
@@ -344,8 +358,10 @@ paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
     }
     __syncwarp();
   }
+  ATT_STAMP(4);
   cp_async_wait<0>();
   __syncthreads();
+  ATT_STAMP(5);
 
   // ---- merge the four warps through shared memory (reusing the stage area)
   float* mo = reinterpret_cast<float*>(att_smem);             // [4][16][HD]
@@ -410,6 +426,7 @@ paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
       }
     }
   }
+  ATT_STAMP(6);
   if (a.n_cta_splits > 1) {
     // the last CTA split of this row tile to finish merges all partials (no second launch)
     __shared__ int s_ticket;
@@ -424,6 +441,7 @@ paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
       if (threadIdx.x == 0) *cnt = 0;  // re-armed for the next launch / graph replay
     }
   }
+  ATT_STAMP(7);
 }
 
 }  // namespace oxb

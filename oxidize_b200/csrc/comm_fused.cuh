@@ -204,11 +204,13 @@ __device__ __forceinline__ bool ar_wait_flag(uint32_t* f, unsigned long long tim
 // no flag reset, and the latency of a hop is one NVLink traversal instead of a round trip plus one.  The
 // price is 2x bytes on the wire, which the two-shot shape more than pays for: each rank moves
 // 2*(W-1)/W of the tensor (x2) instead of (W-1)x.
-// The piece is cut into 16-byte chunks q (token q/16, 8 columns q%16); chunk q is reduced by rank q mod W.
+// The piece is cut into 16-byte chunks q (token q/16, 8 columns q%16); token t of the piece is reduced
+// by rank t mod W, so a warp's stores to one destination stay contiguous (256-byte rows: scattering
+// single chunks over the ranks gave NVLink packets of 32 bytes and a third of the throughput).
 // For the 128 epilogue threads of the CTA that holds the piece:
-//   1. chunk q = tid + 128 i goes to rank (q mod W), slot [this rank];
-//   2. the chunks owned by this rank ((tid + 128 i) * W + rank) are polled from all W slots, summed in
-//      rank order (bit-identical everywhere) and the sum is written to every rank's result slot;
+//   1. chunk q = tid + 128 i goes to rank ((q / 16) mod W), slot [this rank];
+//   2. the chunks of the tokens owned by this rank are polled from all W slots, summed in rank order
+//      (bit-identical everywhere) and the sum is written to every rank's result slot;
 //   3. chunk q = tid + 128 i is polled from the result slot and written to Y (+ residual).
 // The CTAs with the same piece index on the W ranks thus form one team; all of them do equal work.
 // Buffers alternate between two parities per call (a rank can be at most one call ahead of another).
@@ -242,7 +244,7 @@ __device__ __forceinline__ bool ar_exchange_ll(const ArArgs& ar, const uint8_t* 
     const int t = q >> 4, c = q & 15;
     if (n0 + c * 8 >= N) continue;
     const uint4 v = *reinterpret_cast<const uint4*>(stage + t * 256 + c * 16);
-    uint8_t* dst = reinterpret_cast<uint8_t*>(ar.data[q % W]) + (pbase + ar.rank) * slot_bytes +
+    uint8_t* dst = reinterpret_cast<uint8_t*>(ar.data[t % W]) + (pbase + ar.rank) * slot_bytes +
                    ((size_t)(t0 + t) * ar.n_max + n0 + c * 8) * 4;
     ll_store32(dst, v, epoch);
   }
@@ -251,9 +253,9 @@ __device__ __forceinline__ bool ar_exchange_ll(const ArArgs& ar, const uint8_t* 
   const unsigned long long t_start = globaltimer_ns();
   bool fail = false;
   // ---- 2. reduce the chunks this rank owns, broadcast the sums
-  for (int j = tid; j * W + ar.rank < Q && !fail; j += 128) {
-    const int q = j * W + ar.rank;
-    const int t = q >> 4, c = q & 15;
+  for (int j = tid; !fail; j += 128) {
+    const int t = (j >> 4) * W + ar.rank, c = j & 15;  // j-th chunk of the tokens this rank owns
+    if (t >= tmax) break;
     if (n0 + c * 8 >= N) continue;
     const size_t off = ((size_t)(t0 + t) * ar.n_max + n0 + c * 8) * 4;
     uint4 v[AR_MAX_WORLD];

@@ -124,6 +124,14 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* d) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(d)) : "memory");
 }
+// Ask the memory system to bring one tile of a tensor map into the L2 (no shared memory, no barrier):
+// used before the grid dependency resolves, so that the weight stream keeps HBM busy while the
+// upstream kernel drains.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* d, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(d)), "r"(c0),
+               "r"(c1)
+               : "memory");
+}
 // 2-D tiled load into this CTA's own shared memory (every CTA fetches its own tiles)
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* d, uint64_t* bar, int c0, int c1) {
   asm volatile(

@@ -23,6 +23,12 @@ constexpr int GEMM_BK = 64;   // bf16 per k-block = one 128-byte swizzle row
 constexpr int GEMM_THREADS = 192;       // TMA warp, MMA warp, 4 epilogue warps
 constexpr int GEMM_THREADS_MMQ = 320;   // + 4 dequant producer warps for packed weights
 
+// k-blocks (16 KB of weights each) a CTA requests into the L2 before the grid dependency resolves
+// (GroupArgs::l2_prefetch_kb, set per launch).  Behind an HBM-bound kernel this LOSES 10-20% (the
+// requests compete with the running kernel's own stream), so the default is 0; behind a collective,
+// whose wait leaves HBM idle, it turns the wait into the next GEMM's weight stream.
+extern int g_oxb_gemm_l2_prefetch_kb;
+
 template <int TN>
 struct GemmTile {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
@@ -119,6 +125,7 @@ struct GroupArgs {
   long long y_stride;
   const float* scale;  // [groups, scale_ld] or null (never skip)
   int scale_ld;
+  int l2_prefetch_kb;  // weight k-blocks to request into the L2 before the grid dependency (any launch)
 };
 
 // QT == QT_BF16: both operands arrive by TMA.  Any other QT: the weight tile is produced by four
@@ -204,6 +211,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           mbar_expect_tx(&full[i], Cfg::STAGE_BYTES);
           tma_load_2d_hint(sA, &tmW, &full[i], (kb_begin + i) * GEMM_BK, w_row0, pol_w);
         }
+      }
+      if constexpr (!MMQ) {
+        // ... and the rest of this CTA's weight slice is requested into the L2, where the main loop
+        // will find it once the activations are there.
+        const int npf = nkb < gr.l2_prefetch_kb ? nkb : gr.l2_prefetch_kb;
+        for (int i = npre; i < npf; ++i) tma_prefetch_l2_2d(&tmW, (kb_begin + i) * GEMM_BK, w_row0);
       }
       pdl_wait();  // activations come from the upstream kernel
       for (int i = 0; i < npre; ++i) {
@@ -577,7 +590,7 @@ template <int TN, int QT = QT_BF16>
 int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y, const float* bias, int N, int T, int K,
                 int ldY, const GemmPlan& p, float* ws, int* counters, int epi_mode, const ArArgs& ar,
                 cudaStream_t stream, const QwArgs& qw = QwArgs{nullptr, 0, nullptr, 0},
-                const GroupArgs& gr = GroupArgs{0, 0, 0, 0, nullptr, 0}, int groups = 1) {
+                const GroupArgs& gr = GroupArgs{0, 0, 0, 0, nullptr, 0, 0}, int groups = 1) {
   using Cfg = GemmTile<TN>;
   static bool configured = false;
   if (!configured) {
@@ -594,12 +607,14 @@ int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y
   dim3 grid(p.n_tiles, splits, gr.enabled ? groups : p.t_tiles);
   const dim3 block(QT == QT_BF16 ? GEMM_THREADS : GEMM_THREADS_MMQ);
   cudaError_t le;
+  GroupArgs grl = gr;
+  grl.l2_prefetch_kb = g_oxb_gemm_l2_prefetch_kb;
   if (p.cluster && splits > 1) {
     le = oxb_launch_cluster(gemm_bf16_kernel<TN, QT>, grid, block, dim3(1, splits, 1), (size_t)Cfg::SMEM_BYTES, stream, tmW,
-                            tmX, Y, bias, N, T, K, ldY, splits, ws, counters, epi_mode, ar, qw, gr);
+                            tmX, Y, bias, N, T, K, ldY, splits, ws, counters, epi_mode, ar, qw, grl);
   } else {
     le = oxb_launch(gemm_bf16_kernel<TN, QT>, grid, block, (size_t)Cfg::SMEM_BYTES, stream, tmW, tmX, Y, bias, N, T, K, ldY,
-                    splits, ws, counters, epi_mode, ar, qw, gr);
+                    splits, ws, counters, epi_mode, ar, qw, grl);
   }
   if (le != cudaSuccess) return (int)le;
   OXB_CHECK_LAUNCH();
@@ -610,7 +625,7 @@ int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y
 template <int QT>
 int gemm_launch_mmq(const CUtensorMap& tmX, __nv_bfloat16* Y, const float* bias, int N, int T, int K, int ldY,
                     const GemmPlan& p, float* ws, int* counters, int epi_mode, const ArArgs& ar, cudaStream_t stream,
-                    const QwArgs& qw, const GroupArgs& gr = GroupArgs{0, 0, 0, 0, nullptr, 0}, int groups = 1) {
+                    const QwArgs& qw, const GroupArgs& gr = GroupArgs{0, 0, 0, 0, nullptr, 0, 0}, int groups = 1) {
   switch (p.tn) {
     case 16: return gemm_launch<16, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
     case 32: return gemm_launch<32, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);

@@ -13,6 +13,15 @@ using namespace oxb;
 
 int g_oxb_pdl = 1;
 int oxb::g_oxb_cluster_splitk = 1;
+int oxb::g_oxb_gemm_l2_prefetch_kb = 0;
+
+// Weight k-blocks (16 KB each) per CTA that GEMMs launched from now on request into the L2 before their grid
+// dependency resolves; the caller sets it around a GEMM that follows a collective and resets it to 0.
+OXB_API int oxb_set_gemm_l2_prefetch(int kb) {
+  const int old = oxb::g_oxb_gemm_l2_prefetch_kb;
+  oxb::g_oxb_gemm_l2_prefetch_kb = kb < 0 ? 0 : kb;
+  return old;
+}
 
 OXB_API int oxb_set_cluster_splitk(int on) {
   const int old = g_oxb_cluster_splitk;
@@ -22,6 +31,9 @@ OXB_API int oxb_set_cluster_splitk(int on) {
 int g_oxb_ar_ll_min_world = 2;  // rank counts from which the fused all-reduce uses the LL two-shot exchange
 
 static unsigned long long* g_oxb_ar_trace = nullptr;
+
+static unsigned long long* g_oxb_attn_trace = nullptr;
+OXB_API void oxb_set_attn_trace(unsigned long long* p) { g_oxb_attn_trace = p; }
 
 // Device buffer of 16 u64 that receives phase timestamps of piece 0 of each fused all-reduce (null = off).
 OXB_API void oxb_set_ar_trace(unsigned long long* p) { g_oxb_ar_trace = p; }
@@ -385,6 +397,10 @@ static int attn_launch(const AttnArgs& a, int B, int G, cudaStream_t stream) {
     configured = true;
   }
   dim3 grid(a.max_mtiles * a.n_cta_splits, a.nkv, B);
+  // (Merging the KV splits of a row tile inside a thread-block cluster was measured and is slower here:
+  // every CTA then waits for the slowest split, 21.7 vs 19.0 us on 64 x 1400-token decode.  The splits
+  // stay independent CTAs; the last one to finish merges.)
+  if (a.n_cta_splits > 1 && (a.ws_o == nullptr || a.ws_ml == nullptr || a.counters == nullptr)) return (int)cudaErrorInvalidValue;
   oxb_launch(paged_attention_kernel<HD>, grid, dim3(ATT_WARPS * 32), (size_t)smem, stream, a, G);
   OXB_CHECK_LAUNCH();
   return 0;
@@ -417,7 +433,7 @@ OXB_API int oxb_paged_attention(const void* q, void* out, const void* kv_data, c
   a.ws_o = ws_o;
   a.ws_ml = ws_ml;
   a.counters = counters;
-  if (a.n_cta_splits > 1 && (ws_o == nullptr || ws_ml == nullptr || counters == nullptr)) return (int)cudaErrorInvalidValue;
+  a.trace = g_oxb_attn_trace;
   if (hd == 128) return attn_launch<128>(a, B, G, stream);
   if (hd == 64) return attn_launch<64>(a, B, G, stream);
   return (int)cudaErrorInvalidValue;
@@ -537,7 +553,7 @@ OXB_API int oxb_gemm_grouped(const void* X, int x_rows, const void* W, int qtype
   float* wsf = reinterpret_cast<float*>(ws);
   ArArgs ar;
   memset(&ar, 0, sizeof(ar));
-  GroupArgs gr{1, N, x_rows, y_stride, scale, scale_ld};
+  GroupArgs gr{1, N, x_rows, y_stride, scale, scale_ld, 0};
   QwArgs qw{reinterpret_cast<const uint8_t*>(W), row_bytes, nullptr, 0};
   if (qtype == QT_BF16) {
     e = oxb_make_tmap_2d(&tmW, W, (uint64_t)groups * N, K, (uint64_t)K * 2, GEMM_BM, GEMM_BK, 2);

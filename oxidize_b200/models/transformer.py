@@ -87,19 +87,35 @@ class Transformer:
             pairing=cfg.rope_pairing, mscale=opref.rope_mscale(cfg.rope_scaling),
             n_heads=self.n_heads_local, n_kv_heads=self.n_kv_local, head_dim=cfg.head_dim)
         self.attn_scale = cfg.head_dim ** -0.5
+        # The qkv and gate_up GEMMs run right behind the all-reduce of the previous row-parallel
+        # projection (plus one small norm kernel).  With more than one rank that wait leaves HBM
+        # idle, so those two GEMMs ask for the head of their weight stream into the L2 meanwhile.
+        import os
+
+        self._post_collective_prefetch_kb = 0
+        if dev.type == "cuda" and getattr(self.comm, "size", 1) > 1:
+            self._post_collective_prefetch_kb = int(os.environ.get("OXB_L2_PREFETCH_KB", "12"))
 
     # ------------------------------------------------------------------ blocks
     def _attention(self, lw: LayerWeights, layer: int, x: torch.Tensor, meta: BatchMeta, kv) -> torch.Tensor:
         cfg = self.cfg
-        qkv = ops.linear(x, lw.wqkv)
+        qkv = self._linear_after_collective(x, lw.wqkv)
         q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, self.rope,
                                  lw.q_norm, lw.k_norm, cfg.rms_eps)
         attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, cfg.sliding_window)
         return self.comm.linear_allreduce(attn.reshape(attn.shape[0], -1), lw.wo)
 
     def _dense_ffn(self, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
-        gu = ops.linear(x, lw.w_gate_up)
+        gu = self._linear_after_collective(x, lw.w_gate_up)
         return self.comm.linear_allreduce(ops.silu_mul(gu), lw.w_down)
+
+    def _linear_after_collective(self, x: torch.Tensor, w) -> torch.Tensor:
+        if self._post_collective_prefetch_kb <= 0:
+            return ops.linear(x, w)
+        from ..ops import cuda as opcuda
+
+        with opcuda.l2_prefetch(self._post_collective_prefetch_kb):
+            return ops.linear(x, w)
 
     def _moe_ffn(self, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
         """Experts are partitioned across ranks (EP); tokens are replicated after the
