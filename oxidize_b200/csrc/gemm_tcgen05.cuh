@@ -540,7 +540,8 @@ inline GemmPlan gemm_plan(int T, int N, int K, int splits_hint, int sm_count, in
     const int epi = p.tn / 32;                                 // k-block equivalents of writing and reducing a partial
     long long best_cost = -1;
     splits = 1;
-    for (int s = 1; s <= 16 && s <= max_by_k && (long long)tiles * s <= capacity && (s == 1 || tiles < sm_count); ++s) {
+    const int s_max = p.tn <= 64 ? 16 : 4;  // wide tiles have large partials: a deep split costs more than it streams
+    for (int s = 1; s <= s_max && s <= max_by_k && (long long)tiles * s <= capacity && (s == 1 || tiles < sm_count); ++s) {
       const int per_cta = (kb_total + s - 1) / s;
       const int ctas_on_busiest = (tiles * s + sm_count - 1) / sm_count;
       const long long cost = (long long)ctas_on_busiest * (per_cta + 3) + (s > 1 ? 2 + s / 4 + epi : 0);
