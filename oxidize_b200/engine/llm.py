@@ -175,9 +175,16 @@ class LLM:
         return outs
 
     def _output(self, seq: Sequence) -> RequestOutput:
-        gen = getattr(seq, "_preempted_outputs", []) + seq.output
-        ro = RequestOutput(seq.request_id, seq.prompt[: len(seq.prompt) - len(getattr(seq, "_preempted_outputs", []))],
-                           list(gen), seq.is_finished, seq.finish_reason,
+        # A running request's output references the sequence's own lists (no per-step copies of the
+        # prompt and of everything generated so far); a finished one gets its own copy.
+        pre = getattr(seq, "_preempted_outputs", None)
+        if pre:
+            gen = pre + seq.output
+            prompt = seq.prompt[: len(seq.prompt) - len(pre)]
+        else:
+            gen = list(seq.output) if seq.is_finished else seq.output
+            prompt = seq.prompt
+        ro = RequestOutput(seq.request_id, prompt, gen, seq.is_finished, seq.finish_reason,
                            None if seq.first_token_time is None else seq.first_token_time - seq.arrival,
                            None if seq.finish_time is None else seq.finish_time - seq.arrival, seq.num_cached_tokens)
         if seq.is_finished:

@@ -117,6 +117,31 @@ class ModelRunner:
             if t + n > b.max_tokens or i >= b.max_seqs:
                 raise RuntimeError("scheduled batch exceeds runner capacity")
             start = ss.start
+            blist = seq.blocks
+            nb = len(blist)
+            # the block list changes once per page: keep its array form on the sequence
+            cache = getattr(seq, "_blocks_np", None)
+            if cache is None or cache[0] != nb or cache[1] != (blist[-1] if nb else -1):
+                cache = (nb, blist[-1] if nb else -1, np.asarray(blist, dtype=np.int32))
+                seq._blocks_np = cache
+            bt[i * M : i * M + nb] = cache[2]
+            if n == 1 and not ss.is_prefill:
+                # decode row: plain integer arithmetic, no temporaries
+                tok[t] = seq.token_at(start)
+                pos[t] = start
+                slot[t] = blist[start // ps] * ps + start % ps
+                sl[i] = start + 1
+                qs[i + 1] = t + 1
+                if ss.sample:
+                    li[nl] = t
+                    rows.append((ss, nl, 1))
+                    nl += 1
+                if max_q < 1:
+                    max_q = 1
+                if start + 1 > max_len:
+                    max_len = start + 1
+                t += 1
+                continue
             if ss.is_prefill:
                 tok[t : t + n] = seq.prompt[start : start + n]
             else:
@@ -125,10 +150,7 @@ class ModelRunner:
                     tok[t + 1 : t + n] = seq.draft_tokens
             p = np.arange(start, start + n, dtype=np.int32)
             pos[t : t + n] = p
-            blocks = np.asarray(seq.blocks, dtype=np.int32)
-            slot[t : t + n] = blocks[p // ps] * ps + p % ps
-            nb = len(blocks)
-            bt[i * M : i * M + nb] = blocks
+            slot[t : t + n] = cache[2][p // ps] * ps + p % ps
             sl[i] = start + n
             qs[i + 1] = t + n
             if ss.sample:
