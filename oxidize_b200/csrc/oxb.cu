@@ -7,7 +7,6 @@
 #include "gemm_tcgen05.cuh"
 #include "attention.cuh"
 #include "sampling.cuh"
-#include "gemv_quant.cuh"
 #include "comm_fused.cuh"
 using namespace oxb;
 

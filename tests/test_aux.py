@@ -1,0 +1,189 @@
+"""CLI surface, converter, SafeTensors IO, auto-tuner, GPU-cluster manifests, pipeline split (all CPU).
+
+Mirrors the reference's unit tests for the same pieces: CLI rewriting (`oxidize/src/cli.rs`),
+auto-tuner tiers with synthetic inventories (`oxidize-core/src/autotune.rs`), GPU classification
+(`oxidize/src/gpu_cluster.rs`), pipeline layer split (`oxidize-core/src/pipeline.rs`).
+"""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+# --------------------------------------------------------------------------- CLI
+def test_cli_rewrites_verbs():
+    from oxidize_b200.cli.main import rewrite_args
+
+    assert rewrite_args(["run", "m.gguf", "hello", "world", "--max-tokens", "7"]) == [
+        "--verb", "run", "--model", "m.gguf", "--prompt", "hello world", "--max-tokens", "7"]
+    assert rewrite_args(["serve", "m.gguf", "--port=9"]) == ["--verb", "serve", "--model", "m.gguf", "--api-only", "--port=9"]
+    assert rewrite_args(["chat", "m.gguf"])[-1] == "--chat"
+    # a boolean flag must not swallow the positional that follows it
+    assert rewrite_args(["run", "--json", "m.gguf", "hi"]) == ["--verb", "run", "--model", "m.gguf", "--prompt", "hi", "--json"]
+    assert rewrite_args(["--model", "x"]) == ["--model", "x"]
+
+
+def test_cli_parser_keeps_reference_flag_names():
+    from oxidize_b200.cli.main import build_parser, user_passed
+
+    p = build_parser()
+    a = p.parse_args(["--model", "m", "--ctx-size", "2048", "--temperature", "0.5", "--top-k", "10", "--kv-cache-dtype", "q8",
+                      "--port", "8081", "--draft-model", "d.gguf", "--draft-tokens", "3", "--tp", "2"])
+    assert a.ctx_size == 2048 and a.temperature == 0.5 and a.top_k == 10 and a.kv_cache_dtype == "q8" and a.port == 8081
+    assert a.draft_model == "d.gguf" and a.draft_tokens == 3 and a.tp == 2
+    passed = user_passed(["--ctx-size", "2048", "--top-k=10"])
+    assert "ctx_size" in passed and "top_k" in passed and "temperature" not in passed
+
+
+def test_cli_run_and_show_end_to_end(tmp_path):
+    from oxidize_b200.models.config import preset
+    from oxidize_b200.utils.synth import synth_gguf
+
+    cfg = preset("tiny-llama", n_layers=1, vocab_size=300, n_heads=4, n_kv_heads=2)
+    path = str(tmp_path / "tiny.gguf")
+    synth_gguf(path, cfg, "F32", seed=3, tokenizer=True)
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "oxidize_b200.cli.main", "run", path, "hello", "--max-tokens", "4", "--backend",
+                        "cpu", "--temperature", "0", "--no-auto"], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    r2 = subprocess.run([sys.executable, "-m", "oxidize_b200.cli.main", "show", path], capture_output=True, text=True, env=env,
+                        timeout=300)
+    assert r2.returncode == 0, r2.stderr[-2000:]
+    assert "llama" in r2.stdout.lower()
+
+
+# --------------------------------------------------------------------------- SafeTensors + converter
+def test_safetensors_roundtrip_and_errors(tmp_path):
+    from oxidize_b200.formats.safetensors_io import SafeTensorsError, SafeTensorsFile, save_file
+
+    t = {"a": np.arange(12, dtype=np.float32).reshape(3, 4), "b": np.arange(6, dtype=np.float16),
+         "c": (np.arange(8, dtype=np.float32) * 0.5).astype(np.float32)}
+    p = str(tmp_path / "x.safetensors")
+    save_file(t, p, metadata={"format": "pt"})
+    f = SafeTensorsFile(p)
+    assert sorted(f.keys()) == ["a", "b", "c"]
+    assert f.shape("a") == (3, 4) and f.dtype("b") == "F16"
+    np.testing.assert_array_equal(f.tensor("a"), t["a"])
+    np.testing.assert_array_equal(f.tensor_f32("b"), t["b"].astype(np.float32))
+    bad = str(tmp_path / "bad.safetensors")
+    with open(bad, "wb") as fh:
+        fh.write((1 << 40).to_bytes(8, "little") + b"{}")
+    with pytest.raises(SafeTensorsError):
+        SafeTensorsFile(bad)
+
+
+def test_convert_hf_directory_to_gguf_and_run(tmp_path):
+    from oxidize_b200.engine.llm import LLM, EngineConfig
+    from oxidize_b200.engine.sampler import SamplingParams
+    from oxidize_b200.formats.convert import convert_safetensors_to_gguf
+    from oxidize_b200.formats.gguf import load_gguf
+    from oxidize_b200.formats.safetensors_io import save_file
+
+    rng = np.random.default_rng(0)
+    H, F, L, V, nh, nkv = 64, 128, 2, 96, 4, 2
+    hd = H // nh
+    t = {"model.embed_tokens.weight": rng.normal(0, 0.05, (V, H)).astype(np.float32),
+         "model.norm.weight": np.ones(H, dtype=np.float32),
+         "lm_head.weight": rng.normal(0, 0.05, (V, H)).astype(np.float32)}
+    for i in range(L):
+        pre = f"model.layers.{i}."
+        t[pre + "input_layernorm.weight"] = np.ones(H, dtype=np.float32)
+        t[pre + "post_attention_layernorm.weight"] = np.ones(H, dtype=np.float32)
+        t[pre + "self_attn.q_proj.weight"] = rng.normal(0, 0.05, (nh * hd, H)).astype(np.float32)
+        t[pre + "self_attn.k_proj.weight"] = rng.normal(0, 0.05, (nkv * hd, H)).astype(np.float32)
+        t[pre + "self_attn.v_proj.weight"] = rng.normal(0, 0.05, (nkv * hd, H)).astype(np.float32)
+        t[pre + "self_attn.o_proj.weight"] = rng.normal(0, 0.05, (H, nh * hd)).astype(np.float32)
+        t[pre + "mlp.gate_proj.weight"] = rng.normal(0, 0.05, (F, H)).astype(np.float32)
+        t[pre + "mlp.up_proj.weight"] = rng.normal(0, 0.05, (F, H)).astype(np.float32)
+        t[pre + "mlp.down_proj.weight"] = rng.normal(0, 0.05, (H, F)).astype(np.float32)
+    src = tmp_path / "hf"
+    src.mkdir()
+    save_file(t, str(src / "model.safetensors"))
+    json.dump({"architectures": ["LlamaForCausalLM"], "hidden_size": H, "intermediate_size": F, "num_hidden_layers": L,
+               "num_attention_heads": nh, "num_key_value_heads": nkv, "vocab_size": V, "rms_norm_eps": 1e-5,
+               "rope_theta": 10000.0, "max_position_embeddings": 256}, open(src / "config.json", "w"))
+    out = str(tmp_path / "m.gguf")
+    convert_safetensors_to_gguf(str(src), out, quant="F16")
+    g = load_gguf(out)
+    assert g.metadata["general.architecture"] == "llama"
+    assert g.metadata["llama.block_count"] == L and g.metadata["llama.attention.head_count_kv"] == nkv
+    assert "blk.1.ffn_down.weight" in g.tensors and "token_embd.weight" in g.tensors
+    llm = LLM.from_gguf(out, EngineConfig(max_model_len=64, max_num_seqs=2, num_kv_blocks=16), device="cpu")
+    o = llm.generate([[1, 2, 3, 4]], SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True))
+    assert len(o[0].token_ids) == 3
+
+
+# --------------------------------------------------------------------------- auto-tuner
+def _fp(weight_gb, **kw):
+    from oxidize_b200.utils.autotune import ModelFingerprint
+
+    base = dict(arch="llama", n_layers=80, hidden_size=8192, n_heads=64, n_kv_heads=8, head_dim=128, is_moe=False,
+                n_experts=0, weight_bytes=int(weight_gb * 1e9), context_length=8192, has_mtp=False, dominant_quant="BF16")
+    base.update(kw)
+    fields = ModelFingerprint.__dataclass_fields__.keys()
+    return ModelFingerprint(**{k: v for k, v in base.items() if k in fields})
+
+
+def test_autotune_tiers_with_synthetic_inventories():
+    from oxidize_b200.utils.autotune import GpuInfo, HardwareInventory, apply_plan, parse_nvidia_smi_csv, plan
+
+    gpus = parse_nvidia_smi_csv("0, NVIDIA B200, 183359\n1, NVIDIA B200, 183359\nbogus line\n")
+    assert [g.index for g in gpus] == [0, 1] and gpus[0].memory_bytes == 183359 << 20
+    eight = HardwareInventory(64, 2 << 40, [GpuInfo(i, "NVIDIA B200", 183359 << 20) for i in range(8)])
+    p70 = plan(eight, _fp(141))
+    assert p70.backend == "cuda" and p70.tp_size == 1 or p70.tp_size in (2, 4, 8)
+    assert p70.kv_cache_dtype in ("bf16", "q8", "q4") and p70.num_kv_blocks > 0
+    big = plan(eight, _fp(800))
+    assert big.tp_size == 8
+    cpu = plan(HardwareInventory(16, 64 << 30, []), _fp(4))
+    assert cpu.backend == "cpu" and not cpu.cuda_graphs and cpu.threads == 16
+    mtp = plan(eight, _fp(30, has_mtp=True))
+    assert mtp.speculative == "mtp"
+    # explicit beats implicit
+    merged = apply_plan({"tp": 2, "kv_cache_dtype": "bf16", "ctx_size": 0}, {"tp"}, big)
+    assert merged["tp"] == 2 and merged["kv_cache_dtype"] == big.kv_cache_dtype and merged["ctx_size"] == big.ctx_size
+    assert "Rationale" in big.render() and json.loads(big.to_json())["tp_size"] == 8
+
+
+# --------------------------------------------------------------------------- GPU cluster helper
+def test_gpu_cluster_classification_and_manifests():
+    from oxidize_b200.utils.gpu_cluster import classify_gpu, classify_inventory, render_cluster_manifests
+
+    assert classify_gpu("NVIDIA B200") == "b200"
+    assert classify_gpu("NVIDIA A100-SXM4-80GB") == "a100"
+    assert classify_gpu("NVIDIA RTX PRO 6000 Blackwell Workstation Edition") == "rtx-pro-6000"
+    assert classify_gpu("Some Unknown Accelerator") is None
+    inv = classify_inventory(["NVIDIA B200"] * 8 + ["Quadro K620"])
+    assert inv.get("b200") == 8
+    files = render_cluster_manifests("prod", "b200", 2)
+    text = "\n".join(files.values()) if isinstance(files, dict) else str(files)
+    assert "nvidia.com/gpu" in text and "prod" in text
+
+
+# --------------------------------------------------------------------------- pipeline split / launcher
+def test_pipeline_layer_split_covers_all_layers():
+    from oxidize_b200.parallel.pp import split_layers
+
+    for n_layers, n_stages in [(80, 2), (80, 3), (32, 4), (5, 5), (7, 2)]:
+        parts = split_layers(n_layers, n_stages)
+        assert len(parts) == n_stages and parts[0][0] == 0 and parts[-1][1] == n_layers
+        assert all(a[1] == b[0] for a, b in zip(parts, parts[1:]))
+        sizes = [hi - lo for lo, hi in parts]
+        assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        split_layers(2, 3)
+
+
+def test_torchrun_command_uses_loopback():
+    from oxidize_b200.parallel.launcher import free_port, torchrun_command
+
+    cmd = torchrun_command(4, ["serve", "m.gguf", "--tp", "4"], port=29999)
+    s = " ".join(cmd)
+    assert "--nproc-per-node" in s and "4" in cmd and "127.0.0.1" in s and "29999" in s and "serve" in cmd
+    assert 1024 < free_port() < 65536
