@@ -46,12 +46,12 @@ def build_kernels(force: bool = False, verbose: bool = False) -> str:
 def build_runtime(force: bool = False) -> str:
     out = os.path.join(CSRC, "liboxbrt.so")
     srcs = _sources((".cpp", ".hpp", ".h"))
-    if not srcs:
+    cpps = [s for s in srcs if s.endswith(".cpp")]
+    if not cpps:
         return ""
     if not force and _newer(out, srcs):
         return out
     cxx = shutil.which("g++") or "g++"
-    cpps = [s for s in srcs if s.endswith(".cpp")]
     cmd = [cxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-o", out] + cpps
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
