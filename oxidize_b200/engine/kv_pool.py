@@ -144,6 +144,16 @@ class BlockPool:
         return out, len(out) * ps
 
 
+def make_block_pool(num_blocks: int, page_size: int = 16, enable_prefix_cache: bool = True):
+    """The C++ pool (``csrc/runtime.cpp``) when the host runtime library is available, else the
+    Python one; both hand out the same block ids for the same sequence of calls."""
+    from . import native
+
+    if native.lib() is not None:
+        return native.NativeBlockPool(num_blocks, page_size, enable_prefix_cache)
+    return BlockPool(num_blocks, page_size, enable_prefix_cache)
+
+
 KV_DTYPES = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16, "q8": torch.uint8, "q4": torch.uint8}
 
 

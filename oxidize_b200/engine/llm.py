@@ -20,7 +20,7 @@ from ..formats.gguf import GGUFFile, load_gguf
 from ..models.config import ModelConfig, config_from_gguf
 from ..models.transformer import Transformer
 from ..models.weights import ModelWeights, load_weights
-from .kv_pool import BlockPool, KVCache, KVCacheSpec
+from .kv_pool import BlockPool, KVCache, KVCacheSpec, make_block_pool
 from .runner import ModelRunner, StepResult
 from .sampler import SamplingParams
 from .scheduler import Scheduler, SchedulerConfig, SchedulerOutput, Sequence
@@ -76,7 +76,7 @@ class LLM:
         spec = KVCacheSpec(len(weights.layers), self.model.n_kv_local, self.cfg.head_dim, c.kv_page_size, kv_dtype)
         nblocks = c.num_kv_blocks or self._auto_blocks(spec)
         self.kv = KVCache(spec, nblocks, self.device)
-        self.pool = BlockPool(nblocks, c.kv_page_size, c.enable_prefix_cache)
+        self.pool = make_block_pool(nblocks, c.kv_page_size, c.enable_prefix_cache)
         self.scheduler = Scheduler(SchedulerConfig(c.max_num_batched_tokens, c.prefill_chunk_size, c.max_num_seqs,
                                                    c.policy, c.enable_prefix_cache, c.max_model_len), self.pool)
         self.runner = ModelRunner(self.model, self.kv, max(c.max_num_batched_tokens, c.max_num_seqs), c.max_num_seqs,

@@ -18,7 +18,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .. import ops
-from .kv_pool import BlockPool, KVCache, KVCacheSpec
+from .kv_pool import BlockPool, KVCache, KVCacheSpec, make_block_pool
 from .runner import ModelRunner
 from .sampler import GREEDY, SamplingParams
 from .scheduler import ScheduledSeq, SchedulerOutput, Sequence
@@ -76,7 +76,7 @@ class DraftModelProposer:
         nblocks = num_blocks or max_seqs * ((max_model_len + page - 1) // page + 1)
         kvd = "bf16" if dev.type == "cuda" else "f32"
         self.kv = KVCache(KVCacheSpec(len(draft_weights.layers), self.model.n_kv_local, cfg.head_dim, page, kvd), nblocks, dev)
-        self.pool = BlockPool(nblocks, page, enable_prefix_cache=False)
+        self.pool = make_block_pool(nblocks, page, enable_prefix_cache=False)
         self.runner = ModelRunner(self.model, self.kv, max(2048, max_seqs * (k + 2)), max_seqs, max_model_len, False)
         self.shadow: Dict[int, Sequence] = {}
         self.computed: Dict[int, int] = {}
@@ -146,7 +146,7 @@ class MtpProposer:
         nblocks = max_seqs * ((max_model_len + page - 1) // page + 1)
         kvd = "bf16" if dev.type == "cuda" else "f32"
         self.kv = KVCache(KVCacheSpec(1, target_model.n_kv_local, cfg.head_dim, page, kvd), nblocks, dev)
-        self.pool = BlockPool(nblocks, page, enable_prefix_cache=False)
+        self.pool = make_block_pool(nblocks, page, enable_prefix_cache=False)
         self.blocks: Dict[int, List[int]] = {}
         self.start: Dict[int, int] = {}
         self.hidden: Dict[int, torch.Tensor] = {}  # last verified hidden state per sequence

@@ -363,3 +363,88 @@ def test_kv_cache_state_roundtrip():
     kv2 = KVCache(spec, 8)
     kv2.load_state_dict(st, [2, 3])
     assert torch.equal(kv2.data[1][2], kv.data[1][1]) and torch.equal(kv2.scales[0][3], kv.scales[0][5])
+
+
+# --------------------------------------------------------------------------- C++ host runtime
+def test_native_block_pool_matches_python_pool_on_random_traces():
+    """The C++ pool must hand out the same block ids as the Python specification for the same calls."""
+    import random
+
+    from oxidize_b200.engine import native
+    from oxidize_b200.engine.kv_pool import FNV_OFFSET, BlockPool, OutOfBlocks, block_hash
+
+    if native.lib() is None:
+        pytest.skip("liboxbrt could not be built")
+    assert native.block_hash([1, 2, 3, 70000], FNV_OFFSET) == block_hash([1, 2, 3, 70000], FNV_OFFSET)
+    for seed in range(6):
+        rng = random.Random(seed)
+        py, cc = BlockPool(24, 4), native.NativeBlockPool(24, 4)
+        held = []  # blocks we hold a reference on (same list for both pools)
+        for step in range(600):
+            op = rng.random()
+            if op < 0.35:
+                try:
+                    a = py.allocate()
+                except OutOfBlocks:
+                    with pytest.raises(OutOfBlocks):
+                        cc.allocate()
+                    continue
+                assert cc.allocate() == a
+                held.append(a)
+            elif op < 0.6 and held:
+                b = held.pop(rng.randrange(len(held)))
+                py.release(b)
+                cc.release(b)
+            elif op < 0.75 and held:
+                b, h = rng.choice(held), rng.randrange(1, 40)
+                py.publish(b, h)
+                cc.publish(b, h)
+            elif op < 0.9:
+                h = rng.randrange(1, 40)
+                a, c = py.lookup(h), cc.lookup(h)
+                assert a == c
+                if a is not None:
+                    held.append(a)
+            else:
+                toks = [rng.randrange(3) for _ in range(rng.randrange(1, 14))]
+                pa, na = py.match_prefix(toks)
+                pc, nc = cc.match_prefix(toks)
+                assert pa == pc and na == nc
+                held += pa
+            assert py.num_free == cc.num_free
+            assert all(py.ref[b] == cc.ref[b] for b in range(24))
+        assert (py.hits, py.misses) == (cc.hits, cc.misses)
+    with pytest.raises(RuntimeError):
+        cc2 = native.NativeBlockPool(2, 4)
+        b = cc2.allocate()
+        cc2.release(b)
+        cc2.release(b)
+
+
+def test_native_pool_prefix_sharing_through_the_engine(tmp_path):
+    """Same generations with the C++ pool and with the Python pool (OXB_NATIVE_RUNTIME=0 semantics)."""
+    from oxidize_b200.engine import native
+    from oxidize_b200.engine.kv_pool import BlockPool
+    from oxidize_b200.engine.llm import LLM, EngineConfig
+    from oxidize_b200.engine.sampler import SamplingParams
+    from oxidize_b200.models.config import preset
+    from oxidize_b200.utils.synth import synth_gguf
+
+    if native.lib() is None:
+        pytest.skip("liboxbrt could not be built")
+    cfg = preset("tiny-llama", n_layers=1, vocab_size=300, n_heads=4, n_kv_heads=2)
+    path = str(tmp_path / "t.gguf")
+    synth_gguf(path, cfg, "F32", seed=5)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    prompts = [list(range(5, 45)), list(range(5, 45)) + [7, 8], [9] * 20]
+    outs = []
+    for use_native in (True, False):
+        llm = LLM.from_gguf(path, EngineConfig(max_model_len=128, max_num_seqs=4, num_kv_blocks=40), device="cpu")
+        if not use_native:
+            llm.pool = llm.scheduler.pool = BlockPool(llm.pool.num_blocks, llm.pool.page_size, True)
+        else:
+            assert isinstance(llm.pool, native.NativeBlockPool)
+        outs.append([o.token_ids for o in llm.generate(prompts, sp)])
+        second = llm.generate(prompts[:1], sp)  # served from the prefix cache
+        assert second[0].num_cached_tokens >= 32
+    assert outs[0] == outs[1]
