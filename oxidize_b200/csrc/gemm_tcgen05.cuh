@@ -46,6 +46,8 @@ struct GemmTile {
 // Epilogue modes
 constexpr int EPI_STORE = 0;      // Y = acc (+bias)
 constexpr int EPI_ADD_INTO = 1;   // Y += acc (residual accumulate, bf16 read-modify-write)
+constexpr int EPI_SWIGLU = 2;     // weight rows interleaved per tile (64 gate rows, then their 64 up rows):
+                                  // Y[t, n0/2 + c] = silu(acc[c]) * acc[64 + c], Y has N/2 columns
 
 // Sum `splits` fp32 partials for tokens [jb, je) of one tile row: JU tokens x SMAX splits of
 // independent L2 loads are in flight per thread; the adds run in split order (reproducible).
@@ -112,6 +114,25 @@ __device__ __forceinline__ void store_tile_rows(const uint8_t* stage, int ntok, 
       v = make_uint4(a[0], a[1], a[2], a[3]);
     }
     *reinterpret_cast<uint4*>(dst) = v;
+  }
+}
+
+// SwiGLU epilogue: the staged tile holds 64 gate columns followed by the 64 matching up columns of each
+// token; writes the 64 activations with 16-byte stores (128 threads: 8 chunks x 16 token rows per pass).
+__device__ __forceinline__ void store_tile_rows_swiglu(const uint8_t* stage, int ntok, int t_first, int n0,
+                                                       __nv_bfloat16* Y, int ldY, int tid) {
+  const int chunk = tid & 7, trow = tid >> 3;
+  for (int t = trow; t < ntok; t += 16) {
+    const uint4 g = *reinterpret_cast<const uint4*>(stage + t * 256 + chunk * 16);
+    const uint4 u = *reinterpret_cast<const uint4*>(stage + t * 256 + 128 + chunk * 16);
+    const uint32_t gv[4] = {g.x, g.y, g.z, g.w}, uv[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 a = unpack_bf16x2(gv[j]), b = unpack_bf16x2(uv[j]);
+      o[j] = pack_bf16x2(a.x / (1.f + __expf(-a.x)) * b.x, a.y / (1.f + __expf(-a.y)) * b.y);
+    }
+    *reinterpret_cast<uint4*>(Y + (size_t)(t_first + t) * ldY + (n0 >> 1) + chunk * 8) = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 
@@ -337,6 +358,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (use_ar) {
           ar_exchange(ar, smem, ticket[2], tile_id, n0, t0, tvalid, N, Y, ldY, abort_flag, etid);
+        } else if (epi_mode == EPI_SWIGLU) {
+          store_tile_rows_swiglu(smem, tvalid, t0, n0, Y, ldY, etid);
         } else {
           store_tile_rows(smem, tvalid, t0, n0, N, Y, ldY, epi_mode, etid);
         }
@@ -399,6 +422,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       if (ok && je > jb) {
         if (use_ar) {
           ar_exchange(ar, stage_b, ticket[2], tile_id * splits + split, n0, t0 + jb, je - jb, N, Y, ldY, abort_flag, etid);
+        } else if (epi_mode == EPI_SWIGLU) {
+          store_tile_rows_swiglu(stage_b, je - jb, t0 + jb, n0, Y, ldY, etid);
         } else if (vec_ok) {
           store_tile_rows(stage_b, je - jb, t0 + jb, n0, N, Y, ldY, epi_mode, etid);
         } else if (n < N) {

@@ -122,7 +122,11 @@ OXB_API int oxb_gemm_bf16(const void* X, const void* W, void* Y, const float* bi
                           cudaStream_t stream) {
   if (T <= 0 || N <= 0 || K <= 0) return 0;
   if (K % 8 != 0) return (int)cudaErrorInvalidValue;  // TMA rows must be 16-byte multiples
-  GemmPlan p = gemm_plan(T, N, K, splits_hint, sm_count());
+  const bool swiglu = epi_mode == EPI_SWIGLU;
+  // the SwiGLU epilogue exists on the staged (vector-store) paths only: whole 128-row tiles, 16-byte output rows
+  if (swiglu && (N % GEMM_BM != 0 || ldY % 8 != 0 || (reinterpret_cast<uintptr_t>(Y) & 15) != 0 || bias != nullptr))
+    return (int)cudaErrorInvalidValue;
+  GemmPlan p = gemm_plan(T, N, K, splits_hint, sm_count(), swiglu ? 1 : -1);
   // split-K CTAs of a tile wait for one another, so the whole grid has to fit in one wave
   while (p.splits > 1 && !p.cluster && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || ws == nullptr || counters == nullptr ||
                           p.n_tiles * p.t_tiles * p.splits > sm_count()))

@@ -101,6 +101,8 @@ class LinearWeight:
 
     parts: List[QTensor]
     bias: Optional[torch.Tensor] = None
+    # gate|up projection whose rows were interleaved per 128-row tile for the GEMM's SwiGLU epilogue
+    swiglu_interleaved: bool = False
 
     @property
     def out_features(self) -> int:

@@ -141,7 +141,7 @@ def gemm_plan(T: int, N: int, K: int, splits_hint: int = 0):
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
-              ld_out: Optional[int] = None, add_into: bool = False, splits: int = 0) -> torch.Tensor:
+              ld_out: Optional[int] = None, add_into: bool = False, splits: int = 0, swiglu: bool = False) -> torch.Tensor:
     """out[T, N] = x[T, K] @ w[N, K]^T on the tcgen05 kernel; ``out`` may be a column slice of a
     wider row-major buffer (pass its row stride as ``ld_out``)."""
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
@@ -149,13 +149,13 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     N = w.shape[0]
     assert w.shape[1] == K
     if out is None:
-        out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
-        ld_out = N
+        out = torch.empty(T, N // 2 if swiglu else N, dtype=torch.bfloat16, device=x.device)
+        ld_out = out.stride(0)
     elif ld_out is None:
         ld_out = out.stride(0)
     s = scratch(x.device)
     _check(lib().oxb_gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), _p(bias), T, N, K, ld_out,
-                               1 if add_into else 0, splits, s.gemm_ws.data_ptr(), s.gemm_ws.numel() * 4,
+                               2 if swiglu else (1 if add_into else 0), splits, s.gemm_ws.data_ptr(), s.gemm_ws.numel() * 4,
                                s.gemm_counters.data_ptr(), s.gemm_counters.numel(), _stream()), "oxb_gemm_bf16")
     return out
 
@@ -218,6 +218,22 @@ def linear(x: torch.Tensor, parts: Sequence, bias: Optional[torch.Tensor] = None
             cuda_quant.linear_quant(x, p, view, b, out.stride(0))
         off += n
     return out
+
+
+def interleave_gate_up(w: torch.Tensor) -> torch.Tensor:
+    """[gate (F rows); up (F rows)] -> per 128-row tile: 64 gate rows followed by their 64 up rows
+    (the layout the GEMM's SwiGLU epilogue expects).  F must be a multiple of 64."""
+    F = w.shape[0] // 2
+    g = w[:F].reshape(F // 64, 64, -1)
+    u = w[F:].reshape(F // 64, 64, -1)
+    return torch.cat([g, u], dim=1).reshape(2 * F, -1).contiguous()
+
+
+def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
+    """silu(x W_gate^T) * (x W_up^T) in ONE kernel: the activation is the GEMM's epilogue."""
+    if x.dtype != torch.bfloat16:
+        x = x.to(torch.bfloat16)
+    return gemm_bf16(x.contiguous(), w_interleaved, swiglu=True)
 
 
 # --------------------------------------------------------------------------- glue ops

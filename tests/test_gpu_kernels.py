@@ -406,3 +406,23 @@ def test_moe_models_gpu_match_cpu(C, tmp_path, name, kw, quant):
         outs.append([o.token_ids for o in llm.generate([[4, 8, 15, 16, 23, 42], [7, 7, 7]], sp)])
     assert outs[0] == outs[1]
     _check_status(C)
+
+
+@pytest.mark.parametrize("T,F,K", [(1, 128, 256), (64, 3584, 8192), (37, 256, 1024), (200, 1024, 512), (600, 512, 2048)])
+def test_gemm_swiglu_epilogue(C, T, F, K):
+    """silu(x Wg^T) * (x Wu^T) as the GEMM's epilogue (rows interleaved per tile) vs the fp32 statement;
+    covers one split, cluster split-K and several token tiles."""
+    torch.manual_seed(T + F)
+    x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(2 * F, K, device="cuda") * (K ** -0.5)).to(torch.bfloat16)
+    got = C.linear_swiglu(x, C.interleave_gate_up(w))
+    g = x.float() @ w[:F].float().t()
+    u = x.float() @ w[F:].float().t()
+    # the kernel rounds gate and up to bf16 before the activation, like the unfused path
+    g, u = g.to(torch.bfloat16).float(), u.to(torch.bfloat16).float()
+    want = torch.nn.functional.silu(g) * u
+    assert got.shape == (T, F)
+    assert _rel_err(got, want) < 1e-2
+    unfused = C.silu_mul(C.gemm_bf16(x, w))
+    assert _rel_err(got, unfused) < 1e-2
+    _check_status(C)
