@@ -154,7 +154,7 @@ def main():
         if args.comm == "fused":
             from oxidize_b200.parallel.fused import FusedComm
 
-            comm = FusedComm(dev, max_tokens=max(B, 512), hidden=cfg.hidden_size)
+            comm = FusedComm(dev, max_tokens=max(B, 2048), hidden=cfg.hidden_size)
         else:
             comm = TorchComm()
     weights = synth_weights(cfg, dev, args.quant, seed=0, tp_rank=rank, tp_size=world, ep_rank=rank, ep_size=world)

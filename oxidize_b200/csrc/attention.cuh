@@ -184,8 +184,8 @@ paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
   extern __shared__ __align__(16) uint8_t att_smem[];
   ATT_STAMP(0);
   pdl_launch_dependents();
-  pdl_wait();
-  ATT_STAMP(1);
+  // Everything up to the grid-dependency wait below reads only what earlier STEPS wrote: the step's
+  // metadata (copied in before the first kernel) and KV pages that lie wholly below this step's rows.
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
@@ -222,18 +222,6 @@ paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
   const int first = csplit * ATT_WARPS + warp;  // this warp takes pages first, first+stride, ...
   const int my_pages = n_pages > first ? (n_pages - first + stride - 1) / stride : 0;
 
-  // Q fragments (A operand), straight from global memory
-  uint32_t qf[KS][4];
-#pragma unroll
-  for (int ks = 0; ks < KS; ++ks) {
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const __nv_bfloat16* qp = a.q + ((size_t)(q0 + qtok[i]) * a.nq + kvh * G + hg[i]) * HD + ks * 16 + 2 * t4;
-      qf[ks][i] = rvalid[i] ? *reinterpret_cast<const uint32_t*>(qp) : 0u;
-      qf[ks][i + 2] = rvalid[i] ? *reinterpret_cast<const uint32_t*>(qp + 8) : 0u;
-    }
-  }
-
   float o[NT][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
@@ -252,6 +240,33 @@ paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
     const int vb = __shfl_sync(0xffffffffu, ids_b, r & 31);
     return r < 32 ? va : vb;
   };
+
+  // While the upstream kernels (qkv GEMM tail, RoPE + KV write) finish, ask for this warp's stable
+  // pages into the L2: K and V page of one (block, head) are 2 * 16 * HD * 2 contiguous bytes.
+  if (a.kv_mode <= 1) {
+    const int n_stable = (seq_len - qlen) / ATT_PAGE;
+    for (int i = lane; i < my_pages; i += 32) {
+      const int page = page_lo + first + i * stride;
+      if (page < n_stable) {
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(a.kv_data) +
+                             ((size_t)bt[page] * a.nkv + kvh) * 2 * (size_t)(ATT_PAGE * HD * 2);
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(2 * ATT_PAGE * HD * 2) : "memory");
+      }
+    }
+  }
+  pdl_wait();
+  ATT_STAMP(1);
+  // Q fragments (A operand), straight from global memory
+  uint32_t qf[KS][4];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const __nv_bfloat16* qp = a.q + ((size_t)(q0 + qtok[i]) * a.nq + kvh * G + hg[i]) * HD + ks * 16 + 2 * t4;
+      qf[ks][i] = rvalid[i] ? *reinterpret_cast<const uint32_t*>(qp) : 0u;
+      qf[ks][i + 2] = rvalid[i] ? *reinterpret_cast<const uint32_t*>(qp + 8) : 0u;
+    }
+  }
 
   ATT_STAMP(2);
   // prologue: fill the ring

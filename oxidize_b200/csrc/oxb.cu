@@ -214,17 +214,26 @@ OXB_API int oxb_gemm_ar(const void* X, const void* W, void* Y, const void* resid
                         int n_max, int max_tiles, unsigned long long timeout_ns, void* ws, size_t ws_bytes, int* counters,
                         int n_counters, cudaStream_t stream) {
   if (T <= 0 || N <= 0 || K <= 0) return 0;
-  if (K % 8 != 0 || N % 8 != 0 || T > 256 || T > t_max || N > n_max) return (int)cudaErrorInvalidValue;
-  // CTAs wait for the CTAs with the same piece index on the other GPUs, so the whole grid has to be
-  // resident at once on every rank: bound tiles*splits by what the SMs can hold.
   const int ll = world >= g_oxb_ar_ll_min_world;
-  int resident = sm_count() * (T <= 64 ? GemmTile<64>::CTAS_PER_SM : 1);
-  if (!ll && resident > max_tiles) resident = max_tiles;  // the one-shot exchange has one flag per piece
-  GemmPlan p = gemm_plan(T, N, K, 0, sm_count(), -1, resident);
-  while (p.splits > 1 && !p.cluster && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || ws == nullptr || counters == nullptr ||
-                                        p.n_tiles * p.splits > sm_count()))
-    p = gemm_plan(T, N, K, p.splits - 1, sm_count(), -1, resident);
-  if (p.n_tiles * p.splits > resident || p.t_tiles != 1) return (int)cudaErrorInvalidConfiguration;
+  if (K % 8 != 0 || N % 8 != 0 || (T > 256 && !ll) || T > t_max || N > n_max) return (int)cudaErrorInvalidValue;
+  GemmPlan p;
+  if (T <= 256) {
+    // CTAs wait for the CTAs with the same piece index on the other GPUs, so the whole grid is kept
+    // resident at once on every rank: bound tiles*splits by what the SMs can hold.
+    int resident = sm_count() * (T <= 64 ? GemmTile<64>::CTAS_PER_SM : 1);
+    if (!ll && resident > max_tiles) resident = max_tiles;  // the one-shot exchange has one flag per piece
+    p = gemm_plan(T, N, K, 0, sm_count(), -1, resident);
+    while (p.splits > 1 && !p.cluster && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || ws == nullptr ||
+                                          counters == nullptr || p.n_tiles * p.splits > sm_count()))
+      p = gemm_plan(T, N, K, p.splits - 1, sm_count(), -1, resident);
+    if (p.n_tiles * p.splits > resident || p.t_tiles != 1) return (int)cudaErrorInvalidConfiguration;
+  } else {
+    // Prefill-sized calls (LL exchange only): several waves of 256-token tiles, no split-K.  A tile's
+    // exchange overlaps the MMAs of the tiles behind it.  Progress relies on both ranks dispatching
+    // CTAs in block-index order, so that the lowest unfinished piece is resident everywhere; the
+    // bounded polls turn a violation into an error status, not a hang.
+    p = gemm_plan(T, N, K, 1, sm_count(), 0);
+  }
   ArArgs ar;
   int e = fill_ar(ar, world, rank, data_ptrs, flag_ptrs, ctrl, t_max, n_max, max_tiles, timeout_ns, residual);
   if (e) return e;

@@ -2,11 +2,12 @@
 
 ``FusedComm`` owns this rank's symmetric receive buffers (``torch.distributed._symmetric_memory``
 gives every rank a device pointer to every peer's copy) and routes the row-parallel projections
-(attn_output, ffn_down) to ``oxb_gemm_ar``: one sm_100a kernel whose tcgen05 GEMM epilogue pushes
-each finished tile to all peers with P2P stores, raises per-tile flags and reduces the partials as
-they arrive.  Everything the fused kernels cannot take (more than 256 tokens per call, quantized
-row-parallel weights, odd shapes) falls back to the unfused GEMM followed by an NCCL all-reduce,
-i.e. to the baseline, never to a wrong answer.
+(attn_output, ffn_down) to ``oxb_gemm_ar``: one sm_100a kernel whose tcgen05 GEMM epilogue exchanges
+each finished tile with the peers through P2P stores into their symmetric buffers and reduces the
+partials as they arrive (decode batches: the whole grid is resident; prefill chunks: tile by tile,
+overlapping the MMAs of the tiles behind).  Everything the fused kernels cannot take (more tokens
+than the buffers hold, quantized row-parallel weights, odd shapes) falls back to the unfused GEMM
+followed by an NCCL all-reduce, i.e. to the baseline, never to a wrong answer.
 
 The reference has no GPU collectives (its data plane is a TCP ring,
 ``oxidize-core/src/mesh/ring.rs:245-365``); this module is what replaces it on NVSwitch.
@@ -22,7 +23,7 @@ import torch.distributed as dist
 from .. import ops
 from .comm import TorchComm
 
-AR_MAX_TOKENS = 256  # one token tile per fused call
+AR_MAX_TOKENS = 4096  # receive buffers hold this many token rows at most (8 bytes x hidden x 2 x (W+1) each)
 
 
 class FusedComm(TorchComm):

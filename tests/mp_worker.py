@@ -33,7 +33,7 @@ def make_comm(kind, dev):
     if kind == "fused":
         from oxidize_b200.parallel.fused import FusedComm
 
-        return FusedComm(dev, max_tokens=256, hidden=8192)
+        return FusedComm(dev, max_tokens=1024, hidden=8192)
     return TorchComm()
 
 
@@ -45,7 +45,9 @@ def case_gemm_ar(dev, comm_kind):
     W, rank = comm.size, comm.rank
     shapes = [(64, 8192, 1024), (64, 8192, 3584), (1, 1024, 512), (200, 2048, 256), (16, 4096, 1792)]
     # both exchanges at every rank count: one-shot (push to all) and two-shot (owner reduces, broadcasts)
-    for min_world, (T, N, K) in [(m, s) for m in (99, 2) for s in shapes]:
+    cases = [(m, s) for m in (99, 2) for s in shapes]
+    cases += [(2, (600, 2048, 256)), (2, (1024, 8192, 512))]  # prefill-sized: several waves of 256-token tiles
+    for min_world, (T, N, K) in cases:
         C.lib().oxb_set_ar_ll_min_world(min_world)
         for rep in range(3):
             g = torch.Generator(device=dev)
