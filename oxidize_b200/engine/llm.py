@@ -20,6 +20,7 @@ from ..formats.gguf import GGUFFile, load_gguf
 from ..models.config import ModelConfig, config_from_gguf
 from ..models.transformer import Transformer
 from ..models.weights import ModelWeights, load_weights
+from ..utils import profiler as _profiler
 from .kv_pool import BlockPool, KVCache, KVCacheSpec, make_block_pool
 from .runner import ModelRunner, StepResult
 from .sampler import SamplingParams
@@ -80,7 +81,7 @@ class LLM:
         self.scheduler = Scheduler(SchedulerConfig(c.max_num_batched_tokens, c.prefill_chunk_size, c.max_num_seqs,
                                                    c.policy, c.enable_prefix_cache, c.max_model_len), self.pool)
         self.runner = ModelRunner(self.model, self.kv, max(c.max_num_batched_tokens, c.max_num_seqs), c.max_num_seqs,
-                                  c.max_model_len, c.cuda_graphs)
+                                  c.max_model_len, c.cuda_graphs and not _profiler.PROFILE and not _profiler.TRACE_FWD)
         self.eos_token_id = c.eos_token_id
         if self.eos_token_id is None and tokenizer is not None:
             self.eos_token_id = tokenizer.special_tokens.eos

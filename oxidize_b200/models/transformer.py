@@ -20,6 +20,7 @@ from typing import List, Optional, Tuple
 import torch
 
 from .. import ops
+from ..utils import profiler as _profiler
 from ..ops import ref as opref
 from .config import ModelConfig
 from .weights import LayerWeights, ModelWeights
@@ -176,6 +177,8 @@ class Transformer:
             h = self._moe_ffn(lw, x) if lw.router is not None else self._dense_ffn(lw, x)
             if capture is not None and gl in capture.get("layers", ()):
                 capture.setdefault("hidden", {})[gl] = (h.float() + residual.float())
+            if _profiler.TRACE_FWD:
+                _profiler.trace_hidden(gl, h, residual)
         return h, residual
 
     def embed(self, token_ids: torch.Tensor) -> torch.Tensor:

@@ -12,6 +12,7 @@ from typing import Optional
 import torch
 
 from . import ref
+from ..utils.profiler import instrument
 
 
 def _cuda():
@@ -20,6 +21,7 @@ def _cuda():
     return _c
 
 
+@instrument("linear")
 def linear(x: torch.Tensor, w, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y = x @ W^T (+bias) for a :class:`LinearWeight` (row segments concatenated) or a QTensor."""
     parts = getattr(w, "parts", None)
@@ -36,30 +38,35 @@ def linear(x: torch.Tensor, w, bias: Optional[torch.Tensor] = None, out: Optiona
     return y
 
 
+@instrument("embed")
 def embed(tokens: torch.Tensor, table, dtype: torch.dtype, scale: float = 1.0) -> torch.Tensor:
     if tokens.is_cuda:
         return _cuda().embed(tokens, table, dtype, scale)
     return ref.embed(tokens, table, scale).to(dtype)
 
 
+@instrument("rmsnorm")
 def rmsnorm(x, w, eps):
     if x.is_cuda:
         return _cuda().add_rmsnorm(x, None, w, eps)[0]
     return ref.rmsnorm(x, w, eps)
 
 
+@instrument("add_rmsnorm")
 def add_rmsnorm(x, residual, w, eps):
     if x.is_cuda:
         return _cuda().add_rmsnorm(x, residual, w, eps)
     return ref.add_rmsnorm(x, residual, w, eps)
 
 
+@instrument("silu_mul")
 def silu_mul(gate_up):
     if gate_up.is_cuda:
         return _cuda().silu_mul(gate_up)
     return ref.silu_mul(gate_up)
 
 
+@instrument("qk_rope_kv_write")
 def qk_rope_kv_write(qkv, positions, slot_mapping, kv, layer, rope, q_norm=None, k_norm=None, eps=1e-6):
     """Split fused qkv [T, (nq+2nkv)*hd], optional per-head QK RMSNorm, RoPE on q and k,
     write K/V into the paged cache.  Returns rotated q as [T, nq, hd]."""
@@ -79,18 +86,21 @@ def qk_rope_kv_write(qkv, positions, slot_mapping, kv, layer, rope, q_norm=None,
     return q
 
 
+@instrument("paged_attention")
 def paged_attention(q, kv, layer, meta, scale, sliding_window=0):
     if q.is_cuda:
         return _cuda().paged_attention(q, kv, layer, meta, scale, sliding_window)
     return ref.paged_attention(q, kv, layer, meta, scale, sliding_window)
 
 
+@instrument("moe_route")
 def moe_route(logits, cfg, bias=None):
     if logits.is_cuda:
         return _cuda().moe_route(logits, cfg, bias)
     return ref.moe_route(logits, cfg, bias)
 
 
+@instrument("argmax")
 def argmax(logits, tie="lowest"):
     if logits.is_cuda:
         return _cuda().argmax(logits, tie)

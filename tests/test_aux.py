@@ -187,3 +187,19 @@ def test_torchrun_command_uses_loopback():
     s = " ".join(cmd)
     assert "--nproc-per-node" in s and "4" in cmd and "127.0.0.1" in s and "29999" in s and "serve" in cmd
     assert 1024 < free_port() < 65536
+
+
+# --------------------------------------------------------------------------- decode profiler / tracing
+def test_decode_profiler_and_value_trace(tmp_path):
+    from oxidize_b200.models.config import preset
+    from oxidize_b200.utils.synth import synth_gguf
+
+    cfg = preset("tiny-llama", n_layers=2, vocab_size=300, n_heads=4, n_kv_heads=2)
+    path = str(tmp_path / "tiny.gguf")
+    synth_gguf(path, cfg, "F32", seed=3)
+    env = dict(os.environ, PYTHONPATH=ROOT, OXIDIZE_DECODE_PROFILE="1", OXIDIZE_TRACE_FWD="1")
+    r = subprocess.run([sys.executable, "-m", "oxidize_b200.cli.main", "run", path, "hello", "--max-tokens", "3", "--backend",
+                        "cpu", "--temperature", "0", "--no-auto"], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "[trace] layer   1" in r.stderr
+    assert "operator" in r.stderr and "linear" in r.stderr and "paged_attention" in r.stderr
