@@ -244,10 +244,32 @@ def main():
     sampler.stop_flag.set()
     sampler.join(timeout=3)
 
-    times = torch.tensor([dev_ms, e2e_ms, e2e_wall_ms], dtype=torch.float64, device=dev)
+    # ---- batch 1: the first sequence alone (same engine, same weights), decode step device-timed
+    bs1_ms = 0.0
+    if llm.scheduler.running:
+        keep = llm.scheduler.running[0]
+        parked = [s for s in llm.scheduler.running if s is not keep]
+        llm.scheduler.running = [keep]
+        for _ in range(max(args.warmup, 3)):
+            llm.step()
+        g1 = llm.runner.graphs.get(_bucket(1))
+        barrier()
+        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b0.record()
+        for _ in range(args.steps):
+            if g1 is not None:
+                g1.replay()
+            else:
+                llm.step()
+        b1.record()
+        barrier()
+        bs1_ms = b0.elapsed_time(b1) / args.steps
+        llm.scheduler.running = [keep] + parked
+
+    times = torch.tensor([dev_ms, e2e_ms, e2e_wall_ms, bs1_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms, e2e_wall_ms = [float(x) for x in times.tolist()]
+    dev_ms, e2e_ms, e2e_wall_ms, bs1_ms = [float(x) for x in times.tolist()]
     code, detail, count = C.status()
     tokens = B * args.steps
     value = tokens / (dev_ms / 1e3)
@@ -268,7 +290,8 @@ def main():
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": int(launches_per_step * args.steps) if graph is not None else int(C.launch_count),
             "clocks": sampler.summary(),
-            "ttft_p50_s": ttft_p50, "load_s": round(load_s, 1),
+            "ttft_p50_s": ttft_p50, "bs1_tok_s": round(1e3 / bs1_ms, 2) if bs1_ms > 0 else None,
+            "bs1_ms_per_step": round(bs1_ms, 4), "load_s": round(load_s, 1),
             "device_status": {"code": code, "detail": detail, "count": count},
         }
         print(json.dumps(out))

@@ -54,6 +54,14 @@ class BatchMeta:
     extra: dict = field(default_factory=dict)
 
 
+class _NullCtx:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
 class SingleRankComm:
     """Communication facade for tp=ep=1 (every collective is the identity)."""
 
@@ -96,6 +104,9 @@ class Transformer:
         self._post_collective_prefetch_kb = 0
         if dev.type == "cuda" and getattr(self.comm, "size", 1) > 1:
             self._post_collective_prefetch_kb = int(os.environ.get("OXB_L2_PREFETCH_KB", "12"))
+        # per-projection override "qkv:o:gate_up:down" in weight k-blocks per CTA (experiments)
+        pf = os.environ.get("OXB_PF", "")
+        self._pf = [int(v) for v in pf.split(":")] if pf and dev.type == "cuda" else None
         if dev.type == "cuda" and os.environ.get("OXB_FUSED_SWIGLU", "1") != "0":
             self._interleave_gate_up()
 
@@ -117,28 +128,32 @@ class Transformer:
     # ------------------------------------------------------------------ blocks
     def _attention(self, lw: LayerWeights, layer: int, x: torch.Tensor, meta: BatchMeta, kv) -> torch.Tensor:
         cfg = self.cfg
-        qkv = self._linear_after_collective(x, lw.wqkv)
+        qkv = self._linear_after_collective(x, lw.wqkv, 0)
         q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, self.rope,
                                  lw.q_norm, lw.k_norm, cfg.rms_eps)
         attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, cfg.sliding_window)
-        return self.comm.linear_allreduce(attn.reshape(attn.shape[0], -1), lw.wo)
+        with self._prefetch(1, 0):
+            return self.comm.linear_allreduce(attn.reshape(attn.shape[0], -1), lw.wo)
+
+    def _prefetch(self, which: int, default_kb: int):
+        from ..ops import cuda as opcuda
+
+        kb = self._pf[which] if self._pf is not None else default_kb
+        return opcuda.l2_prefetch(kb) if self.device.type == "cuda" else _NullCtx()
 
     def _dense_ffn(self, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
         if lw.w_gate_up.swiglu_interleaved:
             from ..ops import cuda as opcuda
 
-            with opcuda.l2_prefetch(self._post_collective_prefetch_kb):
+            with self._prefetch(2, self._post_collective_prefetch_kb):
                 act = opcuda.linear_swiglu(x, lw.w_gate_up.parts[0].data)
+        else:
+            act = ops.silu_mul(self._linear_after_collective(x, lw.w_gate_up, 2))
+        with self._prefetch(3, 0):
             return self.comm.linear_allreduce(act, lw.w_down)
-        gu = self._linear_after_collective(x, lw.w_gate_up)
-        return self.comm.linear_allreduce(ops.silu_mul(gu), lw.w_down)
 
-    def _linear_after_collective(self, x: torch.Tensor, w) -> torch.Tensor:
-        if self._post_collective_prefetch_kb <= 0:
-            return ops.linear(x, w)
-        from ..ops import cuda as opcuda
-
-        with opcuda.l2_prefetch(self._post_collective_prefetch_kb):
+    def _linear_after_collective(self, x: torch.Tensor, w, which: int) -> torch.Tensor:
+        with self._prefetch(which, self._post_collective_prefetch_kb):
             return ops.linear(x, w)
 
     def _moe_ffn(self, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
