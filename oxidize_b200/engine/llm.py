@@ -192,6 +192,37 @@ class LLM:
             self._seqs.pop(seq.request_id, None)
         return ro
 
+    def next_token_logits(self, token_lists: Seq[Seq[int]]) -> "np.ndarray":
+        """Logits of the token that would follow each sequence, [n, vocab] float32 (scored as one-token
+        requests through the normal scheduler, so shared prefixes are served by the prefix cache)."""
+        import numpy as np
+
+        sp = SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True)
+        ids = [self.add_request(list(t), sp) for t in token_lists]
+        want = set(ids)
+        got = {}
+        keep, self.runner.keep_logits = self.runner.keep_logits, True
+        try:
+            while len(got) < len(ids):
+                if not self.step() and not self.has_unfinished:
+                    break
+                _, res = self.last_step
+                for ss, r0, k in self.runner.last_rows:
+                    rid = ss.seq.request_id
+                    if rid in want and ss.sample and res.logits is not None:
+                        got[rid] = res.logits[r0 + k - 1].float().cpu().numpy()
+        finally:
+            self.runner.keep_logits = keep
+        return np.stack([got[i] for i in ids])
+
+    def beam_search(self, prompt: Union[str, Seq[int]], beam_width: int = 4, max_tokens: int = 32,
+                    length_penalty: float = 1.0):
+        """Width-``beam_width`` search; returns [(generated token ids, normalised log-probability)], best first."""
+        from .constrained import beam_search
+
+        toks = self.tokenizer.encode(prompt) if isinstance(prompt, str) else list(prompt)
+        return beam_search(self.next_token_logits, toks, beam_width, max_tokens, self.eos_token_id, length_penalty)
+
     def generate(self, prompts: Iterable[Union[str, Seq[int]]], params: Union[SamplingParams, Seq[SamplingParams], None] = None,
                  on_token: Optional[Callable[[RequestOutput], None]] = None) -> List[RequestOutput]:
         """Run a set of prompts to completion with continuous batching; results in input order."""

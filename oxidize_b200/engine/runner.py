@@ -230,6 +230,9 @@ class ModelRunner:
             pad_to, graphable = None, False
         T, B, nl, max_q, max_len, rows = self.build(scheduled, pad_to)
         self.last_rows = rows
+        host_rows = [r for r in rows if r[0].seq.params.needs_host_sampler]
+        needs_host_logits = needs_host_logits or bool(host_rows)
+        graphable = graphable and not host_rows
         all_greedy = self._fill_sampling(rows, nl)
         tie = scheduled[0].seq.params.tie
         h2d = self.buf.upload()
@@ -249,7 +252,32 @@ class ModelRunner:
         result: Dict[int, List[int]] = {}
         for ss, r0, k in rows:
             result[ss.seq.seq_id] = [int(x) for x in host[r0 : r0 + k]]
+        if host_rows:
+            self._host_sample(host_rows, logits, result)
         return StepResult(result, logits if (needs_host_logits or self.keep_logits) else None, h2d, n_out * 4)
+
+    def _host_sample(self, host_rows, logits: torch.Tensor, result: Dict[int, List[int]]) -> None:
+        """Rows whose parameters the device kernel does not cover (penalties, typical / tail-free,
+        Mirostat, grammar) are drawn on the host from their logits; the grammar state advances here."""
+        idx = torch.tensor([r0 + j for _, r0, k in host_rows for j in range(k)], dtype=torch.long, device=logits.device)
+        lg = logits.index_select(0, idx).float().cpu().numpy()
+        n = 0
+        for ss, r0, k in host_rows:
+            seq = ss.seq
+            state = seq.__dict__.setdefault("sampler_state", {})
+            recent = seq.all_tokens
+            toks = []
+            for j in range(k):
+                tok = host_sample(lg[n], seq.params, seq.rng.next(), recent, state=state)
+                n += 1
+                toks.append(tok)
+                if j + 1 < k and tok != result[seq.seq_id][j]:
+                    break  # a speculative row diverged from the draft: later rows are void
+                recent = recent + [tok]
+            if seq.params.grammar is not None:
+                for t in toks:
+                    seq.params.grammar.advance(state, t)
+            result[seq.seq_id] = toks
 
     def _replay(self, B: int, tie: str) -> torch.Tensor:
         g = self.graphs.get(B)

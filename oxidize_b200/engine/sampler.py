@@ -40,6 +40,9 @@ class SamplingParams:
     stop_sequences: Tuple[Tuple[int, ...], ...] = ()
     ignore_eos: bool = False
     tie: str = "lowest"  # argmax tie rule: lowest (C port) | highest (Rust engine)
+    mirostat_tau: Optional[float] = None  # Mirostat v2 target surprise (bits); None = off
+    mirostat_eta: float = 0.1
+    grammar: Optional[object] = None  # engine.constrained.TokenGrammar: only tokens it allows can be drawn
 
     def validate(self) -> None:
         if self.top_k is not None and self.top_k == 0:
@@ -52,6 +55,8 @@ class SamplingParams:
             raise SamplingError("penalties must be non-negative")
         if self.max_tokens < 0:
             raise SamplingError("max_tokens must be >= 0")
+        if self.mirostat_tau is not None and not (self.mirostat_tau > 0 and self.mirostat_eta > 0):
+            raise SamplingError("mirostat_tau and mirostat_eta must be positive")
 
     @property
     def is_greedy(self) -> bool:
@@ -60,6 +65,13 @@ class SamplingParams:
     @property
     def has_penalties(self) -> bool:
         return self.frequency_penalty > 0 or self.presence_penalty > 0
+
+    @property
+    def needs_host_sampler(self) -> bool:
+        """Knobs the device sampler kernel does not implement: those rows are drawn on the host from
+        their logits (penalties, typical / tail-free filters, Mirostat, grammar constraint)."""
+        return (self.has_penalties or self.typical_p is not None or self.tail_free_z is not None
+                or self.mirostat_tau is not None or self.grammar is not None)
 
     @property
     def has_filters(self) -> bool:
@@ -85,9 +97,28 @@ def apply_penalties(logits: np.ndarray, recent: Sequence[int], freq_pen: float, 
     return out
 
 
+def mirostat_v2(logits: np.ndarray, p: SamplingParams, random: float, state: dict) -> int:
+    """Mirostat v2 (sampling.rs Mirostat variant): drop tokens whose surprise exceeds ``mu``, draw from
+    the rest, then move ``mu`` toward the target surprise ``tau`` by ``eta`` times the error."""
+    mu = state.setdefault("mirostat_mu", 2.0 * p.mirostat_tau)
+    t = p.temperature if p.temperature > 0 else 1.0
+    z = (logits.astype(np.float64) - float(np.max(logits))) / t
+    probs = np.exp(z)
+    probs /= probs.sum()
+    order = np.argsort(-probs, kind="stable")
+    sp = probs[order]
+    surprise = -np.log2(np.maximum(sp, 1e-300))
+    keep = max(1, int(np.sum(surprise <= mu)))
+    ps = sp[:keep] / sp[:keep].sum()
+    j = min(int(np.searchsorted(np.cumsum(ps), random, side="right")), keep - 1)
+    state["mirostat_mu"] = mu - p.mirostat_eta * (float(-np.log2(max(ps[j], 1e-300))) - p.mirostat_tau)
+    return int(order[j])
+
+
 def sample(logits: np.ndarray, p: SamplingParams, random: float, recent: Sequence[int] = (),
-           suppressed: Sequence[int] = ()) -> int:
-    """Draw one token from float32 ``logits`` using the uniform ``random`` in [0, 1)."""
+           suppressed: Sequence[int] = (), state: Optional[dict] = None) -> int:
+    """Draw one token from float32 ``logits`` using the uniform ``random`` in [0, 1).  ``state`` is the
+    request's mutable sampler state (Mirostat's running ``mu``, the grammar's parse stacks)."""
     if not (0.0 <= random < 1.0):
         raise SamplingError("random must be in [0, 1)")
     p.validate()
@@ -95,6 +126,17 @@ def sample(logits: np.ndarray, p: SamplingParams, random: float, recent: Sequenc
     if len(suppressed):
         logits = logits.copy()
         logits[np.asarray(suppressed, dtype=np.int64)] = -np.inf
+    if p.grammar is not None and state is not None:
+        allowed = p.grammar.allowed_tokens(state)
+        if allowed is not None:
+            masked = np.full_like(logits, -np.inf)
+            idx = np.asarray(sorted(t for t in allowed if 0 <= t < len(logits)), dtype=np.int64)
+            masked[idx] = logits[idx]
+            logits = masked
+    if p.mirostat_tau is not None and state is not None and math.isfinite(float(np.max(logits))):
+        if p.has_penalties:
+            logits = apply_penalties(logits, list(recent)[-p.repetition_window:], p.frequency_penalty, p.presence_penalty)
+        return mirostat_v2(logits, p, random, state)
     if p.is_greedy:
         return argmax_np(logits, p.tie)
     if p.has_penalties:

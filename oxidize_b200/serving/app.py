@@ -52,6 +52,10 @@ class _Common(BaseModel):
     min_p: Optional[float] = None
     typical_p: Optional[float] = None
     tail_free_z: Optional[float] = None
+    frequency_penalty: Optional[float] = None
+    presence_penalty: Optional[float] = None
+    mirostat_tau: Optional[float] = None
+    mirostat_eta: Optional[float] = None
     stop: Optional[Union[str, List[str]]] = None
     seed: Optional[int] = None
     n: Optional[int] = None
@@ -128,6 +132,9 @@ def build_sampling(req: _Common, state: ServerState, max_tokens: Optional[int]) 
                        top_p=d.top_p if req.top_p is None else req.top_p,
                        top_k=d.top_k if req.top_k is None else req.top_k, min_p=req.min_p, typical_p=req.typical_p,
                        tail_free_z=req.tail_free_z, seed=req.seed, max_tokens=max_tokens or d.max_tokens,
+                       frequency_penalty=max(0.0, req.frequency_penalty or 0.0),
+                       presence_penalty=max(0.0, req.presence_penalty or 0.0), mirostat_tau=req.mirostat_tau,
+                       mirostat_eta=req.mirostat_eta or 0.1,
                        stop_sequences=tuple(stop_seqs))
     p.validate()
     return p

@@ -448,3 +448,103 @@ def test_native_pool_prefix_sharing_through_the_engine(tmp_path):
         second = llm.generate(prompts[:1], sp)  # served from the prefix cache
         assert second[0].num_cached_tokens >= 32
     assert outs[0] == outs[1]
+
+
+# --------------------------------------------------------------------------- host sampler paths, grammar, beam search
+def _tiny_llm(tmp_path, **kw):
+    from oxidize_b200.engine.llm import LLM, EngineConfig
+    from oxidize_b200.models.config import preset
+    from oxidize_b200.utils.synth import synth_gguf
+
+    cfg = preset("tiny-llama", n_layers=1, vocab_size=64, n_heads=4, n_kv_heads=2)
+    path = str(tmp_path / "t.gguf")
+    synth_gguf(path, cfg, "F32", seed=11)
+    return LLM.from_gguf(path, EngineConfig(max_model_len=128, max_num_seqs=8, num_kv_blocks=64, **kw), device="cpu")
+
+
+def test_mirostat_and_penalties_reach_the_host_sampler(tmp_path):
+    import numpy as np
+
+    from oxidize_b200.engine.sampler import SamplingParams, sample
+
+    # unit: Mirostat keeps the observed surprise near tau and updates mu
+    rng = np.random.default_rng(0)
+    logits = rng.normal(0, 2, 200).astype(np.float32)
+    p = SamplingParams(temperature=1.0, mirostat_tau=3.0, mirostat_eta=0.2)
+    state = {}
+    toks = [sample(logits, p, float(rng.random()), state=state) for _ in range(200)]
+    assert "mirostat_mu" in state and 0.5 < state["mirostat_mu"] < 12.0
+    assert len(set(toks)) > 3
+    # engine: a presence penalty strong enough forbids immediate repeats under greedy-like sampling
+    llm = _tiny_llm(tmp_path)
+    base = llm.generate([[1, 2, 3]], SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))[0].token_ids
+    pen = llm.generate([[1, 2, 3]], SamplingParams(temperature=1e-6, top_k=1, presence_penalty=50.0, max_tokens=12,
+                                                   ignore_eos=True))[0].token_ids
+    assert len(pen) == 12 and len(set(pen)) == 12  # every token new: the penalty was applied
+    assert len(base) == 12
+    mir = llm.generate([[1, 2, 3]], SamplingParams(temperature=1.0, mirostat_tau=2.0, seed=3, max_tokens=8, ignore_eos=True))
+    assert len(mir[0].token_ids) == 8
+
+
+def test_token_grammar_constrains_generation(tmp_path):
+    from oxidize_b200.engine.constrained import GrammarError, TokenGrammar
+    from oxidize_b200.engine.sampler import SamplingParams
+
+    # root := 10 list 11 ; list := item | item 12 list ; item := 20 | 21 | 22
+    g = TokenGrammar({"root": [[10, "list", 11]], "list": [["item"], ["item", 12, "list"]], "item": [[20], [21], [22]]},
+                     eos_token_ids=[2])
+    assert g.accepts([10, 20, 11]) and g.accepts([10, 21, 12, 22, 11])
+    assert not g.accepts([10, 11]) and not g.accepts([10, 20, 12, 11]) and not g.accepts([10, 20])
+    st = {}
+    assert g.allowed_tokens(st) == {10}
+    g.advance(st, 10)
+    assert g.allowed_tokens(st) == {20, 21, 22}
+    with pytest.raises(GrammarError):
+        g.advance(st, 11)
+    with pytest.raises(GrammarError):
+        TokenGrammar({"root": [["missing"]]})
+    llm = _tiny_llm(tmp_path)
+    for seed in range(4):
+        sp = SamplingParams(temperature=1.0, seed=seed, max_tokens=30, grammar=g, stop_token_ids=(2,))
+        out = llm.generate([[5, 6, 7]], sp)[0].token_ids
+        body = out[:-1] if out and out[-1] == 2 else out
+        state = {}
+        for t in body:  # every prefix is a valid parse prefix
+            g.advance(state, t)
+        if out and out[-1] == 2:
+            assert g.accepts(body)
+
+
+def test_beam_search_finds_the_best_sequence(tmp_path):
+    import numpy as np
+
+    from oxidize_b200.engine.constrained import beam_search
+
+    # toy scorer: token 1 then 2 then EOS(0) is the best path, but greedy's first step prefers token 3
+    def scorer(seqs):
+        out = []
+        for s in seqs:
+            g = s[1:]  # drop the prompt token
+            if not g:
+                row = [-9, np.log(0.4), -9, np.log(0.6)]
+            elif g == [1]:
+                row = [-9, -9, np.log(0.95), np.log(0.05)]
+            elif g == [1, 2]:
+                row = [np.log(0.99), -9, -9, np.log(0.01)]
+            else:
+                row = [np.log(0.3), np.log(0.3), np.log(0.2), np.log(0.2)]
+            out.append(row)
+        return np.asarray(out, dtype=np.float64)
+
+    best = beam_search(scorer, [7], beam_width=3, max_new_tokens=4, eos_token_id=0, length_penalty=0.0)
+    assert best[0][0] == [1, 2, 0]
+    llm = _tiny_llm(tmp_path)
+    beams = llm.beam_search([1, 2, 3, 4], beam_width=3, max_tokens=4)
+    assert 1 <= len(beams) <= 3 and all(len(t) <= 4 for t, _ in beams)
+    assert beams[0][1] >= beams[-1][1]
+    # width 1 is greedy decoding
+    from oxidize_b200.engine.sampler import SamplingParams
+
+    greedy = llm.generate([[1, 2, 3, 4]], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))[0].token_ids
+    one = llm.beam_search([1, 2, 3, 4], beam_width=1, max_tokens=4)
+    assert one[0][0][: len(greedy)] == greedy[: len(one[0][0])]
