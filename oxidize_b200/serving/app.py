@@ -136,6 +136,15 @@ def build_sampling(req: _Common, state: ServerState, max_tokens: Optional[int]) 
                        presence_penalty=max(0.0, req.presence_penalty or 0.0), mirostat_tau=req.mirostat_tau,
                        mirostat_eta=req.mirostat_eta or 0.1,
                        stop_sequences=tuple(stop_seqs))
+    if req.guided_choice and tok is not None:
+        # the answer must be exactly one of the choices: a grammar whose alternatives are their token ids
+        from ..engine.constrained import TokenGrammar
+
+        alts = [tok.encode_with_special_tokens(c, add_bos=False) for c in req.guided_choice if c]
+        eos = getattr(getattr(state.engine, "llm", None), "eos_token_id", None)
+        if alts and eos is not None:
+            p.grammar = TokenGrammar({"root": [list(a) for a in alts if a]}, eos_token_ids=[eos])
+            p.stop_token_ids = tuple(set(p.stop_token_ids) | {eos})
     p.validate()
     return p
 

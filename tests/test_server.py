@@ -140,3 +140,21 @@ def test_suppressed_tokens_and_stop_trim(engine):
     assert llm.weights.lm_head.bias is not None and float(llm.weights.lm_head.bias[ids[0]]) == float("-inf")
     assert trim_stop_text("hello END world", ["END", "zzz"]) == "hello "
     assert trim_stop_text("abc", []) == "abc"
+
+
+def test_guided_choice_and_penalty_fields_with_model(engine):
+    st = ServerState(engine, "tiny", GenerationDefaults(max_tokens=12, temperature=0.8), api_keys=[])
+    c = TestClient(create_app(st))
+    tok = st.tokenizer
+    if tok is None or engine.llm.eos_token_id is None:
+        pytest.skip("synthetic model has no tokenizer / EOS")
+    choices = ["yes", "no", "maybe"]
+    for seed in range(3):
+        r = c.post("/v1/completions", json={"model": "tiny", "prompt": "answer:", "guided_choice": choices, "seed": seed,
+                                            "max_tokens": 12})
+        assert r.status_code == 200, r.text
+        ids = tok.encode_with_special_tokens(r.json()["choices"][0]["text"], add_bos=False)
+        assert any(ids == tok.encode_with_special_tokens(ch, add_bos=False) for ch in choices), r.json()
+    r = c.post("/v1/completions", json={"model": "tiny", "prompt": "hello", "max_tokens": 6, "temperature": 0.5, "seed": 1,
+                                        "frequency_penalty": 0.5, "presence_penalty": 0.5})
+    assert r.status_code == 200 and r.json()["usage"]["completion_tokens"] >= 1
