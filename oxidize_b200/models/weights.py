@@ -116,6 +116,10 @@ class LinearWeight:
         return sum(p.nbytes() for p in self.parts)
 
 
+# weight encodings the sm_100a kernels read directly (ops/cuda.py::QTYPE_CODE + the fp8-block path)
+DEVICE_PACKED_TYPES = ("F32", "F16", "BF16", "Q8_0", "Q4_0", "Q4_K", "Q5_K", "Q6_K", "NVFP4", "FP8B")
+
+
 def fuse_rows(parts: Sequence[QTensor]) -> List[QTensor]:
     """Concatenate adjacent segments that share an encoding into one tensor."""
     out: List[QTensor] = []
@@ -293,6 +297,10 @@ class GGUFWeightSource:
             if self.act_dtype == torch.float32:
                 return QTensor("F32", tt.float().to(self.device), new_shape)
             return QTensor("BF16", tt.to(self.device), new_shape)
+        if self.device.type == "cuda" and t.name not in DEVICE_PACKED_TYPES:
+            # encodings the device kernels do not decode (Q2_K, Q3_K, Q4_1, Q5_0/1, IQ*) become bf16 at load time
+            x = qref.dequantize(t.name, np.ascontiguousarray(raw).reshape(-1), new_shape[0] * new_shape[1])
+            return QTensor("BF16", _np_to_torch(x.reshape(new_shape), self.device, torch.bfloat16), new_shape)
         return QTensor(t.name, _np_to_torch(raw, self.device), new_shape)
 
 

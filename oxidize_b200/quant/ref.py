@@ -502,6 +502,23 @@ _QUANT: Dict[str, Callable[[np.ndarray], np.ndarray]] = {
 }
 
 
+# i-quants whose decode needs the large ggml codebook grids (256-2048 entries each).  The grids are data
+# of the ggml format, not of this framework: they come from the `gguf` package when it is installed.
+_CODEBOOK_TYPES = ("IQ1_S", "IQ1_M", "IQ2_XXS", "IQ2_XS", "IQ2_S", "IQ3_XXS", "IQ3_S")
+
+
+def _dequantize_codebook(t, raw: np.ndarray) -> np.ndarray:
+    try:
+        import gguf
+        from gguf import quants as gq
+    except Exception as e:  # pragma: no cover - depends on the environment
+        raise GGUFError(f"{t.name} needs the ggml codebook grids from the `gguf` package, which is not installed") from e
+    if raw.size % t.type_size:
+        raise GGUFError(f"{t.name}: {raw.size} bytes is not whole {t.type_size}-byte blocks")
+    qtype = getattr(gguf.GGMLQuantizationType, t.name)
+    return np.asarray(gq.dequantize(raw.reshape(-1, t.type_size), qtype), dtype=np.float32).reshape(-1)
+
+
 def dequantize(type_name, raw: np.ndarray, n_elements: int | None = None) -> np.ndarray:
     """Decode ``raw`` block bytes of the given ggml type to float32 (dispatch like
     ``dequantize_scalar`` quant_dispatch.rs:4)."""
@@ -517,6 +534,8 @@ def dequantize(type_name, raw: np.ndarray, n_elements: int | None = None) -> np.
         if raw.size % t.type_size:
             raise GGUFError(f"{t.name}: {raw.size} bytes is not whole {t.type_size}-byte blocks")
         out = _DEQ[t.name](raw)
+    elif t.name in _CODEBOOK_TYPES:
+        out = _dequantize_codebook(t, raw)
     else:
         raise GGUFError(f"no dequantizer for {t.name}")
     if n_elements is not None and out.size != n_elements:

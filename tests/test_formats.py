@@ -235,3 +235,35 @@ def test_chat_templates():
     assert T.render_chat_template(llama3, msgs[1:], False).endswith("<|eot_id|>")
     assert T.chat_template_from_metadata({}, "qwen3") == T.CHATML_SENTINEL
     assert T.chat_template_from_metadata({}, "llama") is None
+
+
+def test_codebook_iquants_decode_through_gguf_package():
+    """IQ1/IQ2/IQ3 decode needs ggml's codebook grids; they come from the `gguf` package.  Round trip:
+    quantize with the package, decode with ours, compare with the package's own decode."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants as gq
+
+    from oxidize_b200.quant import ref as qref
+
+    rng = np.random.default_rng(0)
+    x = rng.normal(0, 1, (4, 512)).astype(np.float32)
+    done = 0
+    for name in ("IQ2_XXS", "IQ2_XS", "IQ2_S", "IQ3_XXS", "IQ3_S", "IQ1_S", "IQ1_M"):
+        qt = getattr(gguf.GGMLQuantizationType, name)
+        try:
+            raw = gq.quantize(x, qt)
+        except Exception:
+            continue  # the package decodes these types but cannot always encode them
+        want = gq.dequantize(raw, qt).reshape(-1)
+        got = qref.dequantize(name, raw.reshape(-1), x.size)
+        np.testing.assert_array_equal(got, want.astype(np.float32))
+        done += 1
+    # decode-only check on random block bytes for every codebook type (structure, size, finiteness of scales aside)
+    for name in qref._CODEBOOK_TYPES:
+        t = qref.ggml_type(name)
+        raw = rng.integers(0, 255, size=t.type_size * 3, dtype=np.uint8)
+        raw[:2] = np.array([0.01], dtype=np.float16).view(np.uint8)  # a sane first scale
+        out = qref.dequantize(name, raw)
+        assert out.shape == (3 * t.block_size,)
+    with pytest.raises(Exception):
+        qref.dequantize("IQ2_XS", np.zeros(10, dtype=np.uint8))
