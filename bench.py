@@ -143,7 +143,10 @@ def main():
     # steady state: every request is somewhere inside its generation
     gen_so_far = rng.integers(0, max(1, args.out_tokens - args.steps - args.warmup - 8), size=B)
     ctx = (prompt_lens + gen_so_far).astype(int)
-    total_steps = args.steps * 2 + args.warmup * 2 + 8
+    total_steps = args.steps * 3 + args.warmup * 3 + 8
+    if not args.no_prefill:
+        # sequences that finish their prefill early keep decoding while the others are still prefilling
+        total_steps += int(ctx.sum()) // 2048 + B
     max_len = int(ctx.max() + total_steps + 16)
     page = 16
     nblocks = int(sum((c + total_steps + page) // page + 1 for c in ctx)) + 8

@@ -32,6 +32,7 @@ struct AttnArgs {
   const int* query_start;   // [B+1]
   int max_blocks, nq, nkv, kv_mode /*0 bf16,1 f16,2 q8,3 q4*/;
   int n_cta_splits, max_mtiles, window;
+  int num_blocks;  // pages in the KV pool: block ids are checked against it
   float scale_log2;
   float* ws_o;   // [B*nkv*max_mtiles*n_cta_splits, 16, hd]
   float* ws_ml;  // [.., 16, 2]
@@ -238,7 +239,12 @@ paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
     const int r = i - id_base;
     const int va = __shfl_sync(0xffffffffu, ids_a, r & 31);
     const int vb = __shfl_sync(0xffffffffu, ids_b, r & 31);
-    return r < 32 ? va : vb;
+    int id = r < 32 ? va : vb;
+    if ((unsigned)id >= (unsigned)a.num_blocks) {  // never follow a bad block id: record it, read page 0
+      if (lane == 0) oxb_report(OXB_BAD_BLOCK_ID, id);
+      id = 0;
+    }
+    return id;
   };
 
   // While the upstream kernels (qkv GEMM tail, RoPE + KV write) finish, ask for this warp's stable
@@ -247,10 +253,13 @@ paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
     const int n_stable = (seq_len - qlen) / ATT_PAGE;
     for (int i = lane; i < my_pages; i += 32) {
       const int page = page_lo + first + i * stride;
-      if (page < n_stable) {
-        const uint8_t* src = reinterpret_cast<const uint8_t*>(a.kv_data) +
-                             ((size_t)bt[page] * a.nkv + kvh) * 2 * (size_t)(ATT_PAGE * HD * 2);
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(2 * ATT_PAGE * HD * 2) : "memory");
+      if (page < n_stable && page < a.max_blocks) {
+        const int blk = bt[page];
+        if ((unsigned)blk < (unsigned)a.num_blocks) {
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(a.kv_data) +
+                               ((size_t)blk * a.nkv + kvh) * 2 * (size_t)(ATT_PAGE * HD * 2);
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(2 * ATT_PAGE * HD * 2) : "memory");
+        }
       }
     }
   }

@@ -28,6 +28,8 @@ enum OxbStatus : int {
   OXB_TIMEOUT_ACCUM = 3,
   OXB_TIMEOUT_PEER_FLAG = 4,
   OXB_TIMEOUT_SPLITK = 5,
+  OXB_BAD_BLOCK_ID = 6,   // a block table entry outside the KV pool (access skipped)
+  OXB_BAD_SLOT = 7,       // a KV write slot outside the KV pool (write skipped)
   OXB_BAD_ARGUMENT = 6,
 };
 

@@ -181,6 +181,7 @@ struct KvWriteArgs {
   int kv_mode;  // 0 bf16, 1 f16, 2 q8, 3 q4, 4 f32
   int page;
   int nkv;
+  int num_blocks;  // pages in the KV pool: slots are checked against it
 };
 
 __global__ void qk_rope_kvwrite_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
@@ -233,6 +234,10 @@ __global__ void qk_rope_kvwrite_kernel(const __nv_bfloat16* __restrict__ qkv, co
   const int kvh = is_k ? h - nq : h - nq - nkv;
   const int which = is_k ? 0 : 1;
   const int blk = slot / kv.page, off = slot % kv.page;
+  if (blk >= kv.num_blocks) {  // never write outside the pool: record the slot and skip
+    if (d == 0) oxb_report(OXB_BAD_SLOT, slot);
+    return;
+  }
   const size_t row = (((size_t)blk * kv.nkv + kvh) * 2 + which) * kv.page + off;
   if (kv.kv_mode == 0) {
     reinterpret_cast<__nv_bfloat16*>(kv.kv_data)[row * hd + d] = __float2bfloat16(v);

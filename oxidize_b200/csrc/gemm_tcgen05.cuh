@@ -46,6 +46,7 @@ struct GemmTile {
 // Epilogue modes
 constexpr int EPI_STORE = 0;      // Y = acc (+bias)
 constexpr int EPI_ADD_INTO = 1;   // Y += acc (residual accumulate, bf16 read-modify-write)
+constexpr int EPI_ROPE = 3;       // fused qkv projection: RoPE on q/k heads, q -> q_out, k/v -> paged KV cache (RopeArgs)
 constexpr int EPI_SWIGLU = 2;     // weight rows interleaved per tile (64 gate rows, then their 64 up rows):
                                   // Y[t, n0/2 + c] = silu(acc[c]) * acc[64 + c], Y has N/2 columns
 
@@ -136,6 +137,85 @@ __device__ __forceinline__ void store_tile_rows_swiglu(const uint8_t* stage, int
   }
 }
 
+// RoPE + KV-write epilogue of the fused qkv projection (EPI_ROPE): a 128-row tile is exactly one head
+// (head_dim 128).  Query heads are rotated and written to q_out [T, nq, 128]; key heads are rotated and
+// written into the paged cache at the token's slot; value heads are written as they are.  Same
+// arithmetic as qk_rope_kvwrite_kernel (table of cos | sin per position, both pairings), bf16 KV only.
+struct RopeArgs {
+  const int* positions;   // [T]
+  const int* slots;       // [T] block * page + offset, < 0 = do not write K/V
+  const float* cos_sin;   // [max_pos, rot]: cos for the rot/2 pairs, then sin
+  int max_pos, rot, pairing /*0 split-half, 1 adjacent*/;
+  int nq, nkv, page, num_blocks;
+  __nv_bfloat16* q_out;   // [T, nq, 128]
+  __nv_bfloat16* kv_data; // layer base: [blocks, nkv, 2, page, 128]
+};
+
+__device__ __forceinline__ void store_tile_rows_rope(const uint8_t* stage, int ntok, int t_first, int n0, const RopeArgs& ro,
+                                                     int tid) {
+  const int head = n0 >> 7;
+  const bool is_q = head < ro.nq, is_k = !is_q && head < ro.nq + ro.nkv;
+  const int chunk = tid & 15, trow = tid >> 4;
+  const int half = ro.rot >> 1;
+  for (int t = trow; t < ntok; t += 8) {
+    const int tok = t_first + t;
+    const uint4 raw = *reinterpret_cast<const uint4*>(stage + t * 256 + chunk * 16);
+    const uint32_t rv[4] = {raw.x, raw.y, raw.z, raw.w};
+    float x[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(rv[j]);
+      x[2 * j] = f.x;
+      x[2 * j + 1] = f.y;
+    }
+    if (is_q || is_k) {
+      int p = ro.positions[tok];
+      p = p < 0 ? 0 : (p >= ro.max_pos ? ro.max_pos - 1 : p);
+      const float* cs = ro.cos_sin + (size_t)p * ro.rot;
+      if (ro.pairing == 0) {
+        const uint4 praw = *reinterpret_cast<const uint4*>(stage + t * 256 + (chunk ^ 8) * 16);
+        const uint32_t pv[4] = {praw.x, praw.y, praw.z, praw.w};
+        const bool first = chunk < 8;
+        const int pair0 = (chunk & 7) * 8;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 o = unpack_bf16x2(pv[j]);
+          const float c0 = cs[pair0 + 2 * j], s0 = cs[half + pair0 + 2 * j];
+          const float c1 = cs[pair0 + 2 * j + 1], s1 = cs[half + pair0 + 2 * j + 1];
+          const float v0 = x[2 * j], v1 = x[2 * j + 1];
+          x[2 * j] = first ? (v0 * c0 - o.x * s0) : (v0 * c0 + o.x * s0);
+          x[2 * j + 1] = first ? (v1 * c1 - o.y * s1) : (v1 * c1 + o.y * s1);
+        }
+      } else {
+        const int pair0 = chunk * 4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float c = cs[pair0 + j], s = cs[half + pair0 + j];
+          const float a = x[2 * j], b = x[2 * j + 1];
+          x[2 * j] = a * c - b * s;
+          x[2 * j + 1] = b * c + a * s;
+        }
+      }
+    }
+    const uint4 o = make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
+    if (is_q) {
+      *reinterpret_cast<uint4*>(ro.q_out + ((size_t)tok * ro.nq + head) * 128 + chunk * 8) = o;
+    } else {
+      const int slot = ro.slots[tok];
+      if (slot >= 0) {
+        const int kvh = is_k ? head - ro.nq : head - ro.nq - ro.nkv;
+        const int blk = slot / ro.page, off = slot % ro.page;
+        if (blk < ro.num_blocks) {
+          const size_t row = (((size_t)blk * ro.nkv + kvh) * 2 + (is_k ? 0 : 1)) * ro.page + off;
+          *reinterpret_cast<uint4*>(ro.kv_data + row * 128 + chunk * 8) = o;
+        } else if (chunk == 0) {
+          oxb_report(OXB_BAD_SLOT, slot);  // never write outside the pool
+        }
+      }
+    }
+  }
+}
+
 // Grouped (per-expert) launches: blockIdx.z selects the group instead of a token tile.  Group z uses
 // weight rows [z*w_rows, z*w_rows + N), activation rows [z*x_rows, z*x_rows + T) (x_rows = 0: all
 // groups share X), writes Y + z*y_stride, and is skipped entirely when its row of per-token scales
@@ -156,7 +236,7 @@ __global__ void __launch_bounds__(QT == QT_BF16 ? GEMM_THREADS : GEMM_THREADS_MM
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                  __nv_bfloat16* __restrict__ Y, const float* __restrict__ bias, int N, int T, int K, int ldY,
                  int splits, float* __restrict__ ws, int* __restrict__ counters, int epi_mode, const ArArgs ar,
-                 const QwArgs qw, const GroupArgs gr) {
+                 const QwArgs qw, const GroupArgs gr, const RopeArgs ro) {
   constexpr bool MMQ = QT != QT_BF16;
   const int zg = gr.enabled ? (int)blockIdx.z : 0;
   if (gr.enabled && gr.scale != nullptr) {
@@ -360,6 +440,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           ar_exchange(ar, smem, ticket[2], tile_id, n0, t0, tvalid, N, Y, ldY, abort_flag, etid);
         } else if (epi_mode == EPI_SWIGLU) {
           store_tile_rows_swiglu(smem, tvalid, t0, n0, Y, ldY, etid);
+        } else if (epi_mode == EPI_ROPE) {
+          store_tile_rows_rope(smem, tvalid, t0, n0, ro, etid);
         } else {
           store_tile_rows(smem, tvalid, t0, n0, N, Y, ldY, epi_mode, etid);
         }
@@ -424,6 +506,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           ar_exchange(ar, stage_b, ticket[2], tile_id * splits + split, n0, t0 + jb, je - jb, N, Y, ldY, abort_flag, etid);
         } else if (epi_mode == EPI_SWIGLU) {
           store_tile_rows_swiglu(stage_b, je - jb, t0 + jb, n0, Y, ldY, etid);
+        } else if (epi_mode == EPI_ROPE) {
+          store_tile_rows_rope(stage_b, je - jb, t0 + jb, n0, ro, etid);
         } else if (vec_ok) {
           store_tile_rows(stage_b, je - jb, t0 + jb, n0, N, Y, ldY, epi_mode, etid);
         } else if (n < N) {
@@ -616,7 +700,8 @@ template <int TN, int QT = QT_BF16>
 int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y, const float* bias, int N, int T, int K,
                 int ldY, const GemmPlan& p, float* ws, int* counters, int epi_mode, const ArArgs& ar,
                 cudaStream_t stream, const QwArgs& qw = QwArgs{nullptr, 0, nullptr, 0},
-                const GroupArgs& gr = GroupArgs{0, 0, 0, 0, nullptr, 0, 0}, int groups = 1) {
+                const GroupArgs& gr = GroupArgs{0, 0, 0, 0, nullptr, 0, 0}, int groups = 1,
+                const RopeArgs& ro = RopeArgs{nullptr, nullptr, nullptr, 0, 0, 0, 0, 0, 0, 0, nullptr, nullptr}) {
   using Cfg = GemmTile<TN>;
   static bool configured = false;
   if (!configured) {
@@ -637,10 +722,10 @@ int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y
   grl.l2_prefetch_kb = g_oxb_gemm_l2_prefetch_kb;
   if (p.cluster && splits > 1) {
     le = oxb_launch_cluster(gemm_bf16_kernel<TN, QT>, grid, block, dim3(1, splits, 1), (size_t)Cfg::SMEM_BYTES, stream, tmW,
-                            tmX, Y, bias, N, T, K, ldY, splits, ws, counters, epi_mode, ar, qw, grl);
+                            tmX, Y, bias, N, T, K, ldY, splits, ws, counters, epi_mode, ar, qw, grl, ro);
   } else {
     le = oxb_launch(gemm_bf16_kernel<TN, QT>, grid, block, (size_t)Cfg::SMEM_BYTES, stream, tmW, tmX, Y, bias, N, T, K, ldY,
-                    splits, ws, counters, epi_mode, ar, qw, grl);
+                    splits, ws, counters, epi_mode, ar, qw, grl, ro);
   }
   if (le != cudaSuccess) return (int)le;
   OXB_CHECK_LAUNCH();

@@ -355,16 +355,48 @@ OXB_API int oxb_silu_mul(const void* gu, void* out, int T, int I, cudaStream_t s
 OXB_API int oxb_qk_rope_kvwrite(const void* qkv, const int* positions, const int* slots, const float* cos_sin,
                                 int max_pos, int rot, int pairing, const float* q_norm, const float* k_norm, float eps,
                                 int T, int nq, int nkv, int hd, void* q_out, void* kv_data, float* kv_scales,
-                                int kv_mode, int page, cudaStream_t stream) {
+                                int kv_mode, int page, int num_blocks, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (hd % 32 != 0 || hd > 1024) return (int)cudaErrorInvalidValue;
-  KvWriteArgs kv{kv_data, kv_scales, kv_mode, page, nkv};
+  KvWriteArgs kv{kv_data, kv_scales, kv_mode, page, nkv, num_blocks};
   dim3 grid(T, nq + 2 * nkv);
   oxb_launch(qk_rope_kvwrite_kernel, grid, dim3(hd), hd * sizeof(float), stream,
              reinterpret_cast<const __nv_bfloat16*>(qkv), positions, slots, cos_sin, max_pos, rot, pairing, q_norm, k_norm,
              eps, nq, nkv, hd, reinterpret_cast<__nv_bfloat16*>(q_out), kv);
   OXB_CHECK_LAUNCH();
   return 0;
+}
+
+// Fused qkv projection: qkv = X · Wqkv^T with RoPE + KV write as the GEMM's epilogue (EPI_ROPE).  Wqkv rows
+// are [nq heads | nkv key heads | nkv value heads] of head_dim 128; bf16 KV pages only; full rotary (rot == 128).
+OXB_API int oxb_gemm_qkv_rope(const void* X, const void* W, int T, int K, const int* positions, const int* slots,
+                              const float* cos_sin, int max_pos, int rot, int pairing, int nq, int nkv, void* q_out,
+                              void* kv_data, int page, int num_blocks, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const int N = (nq + 2 * nkv) * 128;
+  if (K % 8 != 0 || rot != 128 || page <= 0 || (reinterpret_cast<uintptr_t>(q_out) & 15) != 0 ||
+      (reinterpret_cast<uintptr_t>(kv_data) & 15) != 0)
+    return (int)cudaErrorInvalidValue;
+  GemmPlan p = gemm_plan(T, N, K, 0, sm_count(), 1);
+  CUtensorMap tmW, tmX;
+  int e = oxb_make_tmap_2d(&tmW, W, N, K, (uint64_t)K * 2, GEMM_BM, GEMM_BK, 2);
+  if (e) return e;
+  e = oxb_make_tmap_2d(&tmX, X, T, K, (uint64_t)K * 2, p.tn, GEMM_BK, 2);
+  if (e) return e;
+  ArArgs ar;
+  memset(&ar, 0, sizeof(ar));
+  RopeArgs ro{positions, slots, cos_sin, max_pos, rot, pairing, nq, nkv, page, num_blocks, reinterpret_cast<__nv_bfloat16*>(q_out),
+              reinterpret_cast<__nv_bfloat16*>(kv_data)};
+  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(q_out);  // only its alignment is looked at
+  const QwArgs qw{nullptr, 0, nullptr, 0};
+  const GroupArgs gr{0, 0, 0, 0, nullptr, 0, 0};
+  switch (p.tn) {
+    case 16: return gemm_launch<16>(tmW, tmX, y, nullptr, N, T, K, N, p, nullptr, nullptr, EPI_ROPE, ar, stream, qw, gr, 1, ro);
+    case 32: return gemm_launch<32>(tmW, tmX, y, nullptr, N, T, K, N, p, nullptr, nullptr, EPI_ROPE, ar, stream, qw, gr, 1, ro);
+    case 64: return gemm_launch<64>(tmW, tmX, y, nullptr, N, T, K, N, p, nullptr, nullptr, EPI_ROPE, ar, stream, qw, gr, 1, ro);
+    case 128: return gemm_launch<128>(tmW, tmX, y, nullptr, N, T, K, N, p, nullptr, nullptr, EPI_ROPE, ar, stream, qw, gr, 1, ro);
+    default: return gemm_launch<256>(tmW, tmX, y, nullptr, N, T, K, N, p, nullptr, nullptr, EPI_ROPE, ar, stream, qw, gr, 1, ro);
+  }
 }
 
 OXB_API int oxb_argmax(const float* logits, int R, int V, int ld, int tie_highest, int* out, float* out_val,
@@ -422,7 +454,7 @@ OXB_API int oxb_paged_attention(const void* q, void* out, const void* kv_data, c
                                 const int* block_tables, const int* seq_lens, const int* query_start, int B,
                                 int max_blocks, int nq, int nkv, int hd, int kv_mode, int max_query_len,
                                 int n_cta_splits, int window, float scale, float* ws_o, float* ws_ml, int* counters,
-                                cudaStream_t stream) {
+                                int num_blocks, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (nq % nkv != 0) return (int)cudaErrorInvalidValue;
   const int G = nq / nkv;
@@ -445,6 +477,7 @@ OXB_API int oxb_paged_attention(const void* q, void* out, const void* kv_data, c
   a.ws_o = ws_o;
   a.ws_ml = ws_ml;
   a.counters = counters;
+  a.num_blocks = num_blocks;
   a.trace = g_oxb_attn_trace;
   if (hd == 128) return attn_launch<128>(a, B, G, stream);
   if (hd == 64) return attn_launch<64>(a, B, G, stream);

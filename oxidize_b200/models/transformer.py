@@ -107,6 +107,7 @@ class Transformer:
         # per-projection override "qkv:o:gate_up:down" in weight k-blocks per CTA (experiments)
         pf = os.environ.get("OXB_PF", "")
         self._pf = [int(v) for v in pf.split(":")] if pf and dev.type == "cuda" else None
+        self._fuse_qkv_rope = dev.type == "cuda" and os.environ.get("OXB_FUSED_QKV_ROPE", "1") != "0"
         if dev.type == "cuda" and os.environ.get("OXB_FUSED_SWIGLU", "1") != "0":
             self._interleave_gate_up()
 
@@ -128,6 +129,16 @@ class Transformer:
     # ------------------------------------------------------------------ blocks
     def _attention(self, lw: LayerWeights, layer: int, x: torch.Tensor, meta: BatchMeta, kv) -> torch.Tensor:
         cfg = self.cfg
+        if self._fuse_qkv_rope and x.is_cuda and lw.wqkv.bias is None:
+            from ..ops import cuda as opcuda
+
+            if opcuda.qkv_rope_fusable(lw.wqkv.parts, kv, self.rope, lw.q_norm, lw.k_norm):
+                with self._prefetch(0, self._post_collective_prefetch_kb):
+                    q = opcuda.linear_qkv_rope(x, lw.wqkv.parts[0].data, meta.positions, meta.slot_mapping, kv, layer,
+                                               self.rope)
+                attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, cfg.sliding_window)
+                with self._prefetch(1, 0):
+                    return self.comm.linear_allreduce(attn.reshape(attn.shape[0], -1), lw.wo)
         qkv = self._linear_after_collective(x, lw.wqkv, 0)
         q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, self.rope,
                                  lw.q_norm, lw.k_norm, cfg.rms_eps)

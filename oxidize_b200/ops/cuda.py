@@ -58,10 +58,10 @@ def _declare(L) -> None:
     L.oxb_add_rmsnorm.argtypes = [vp, vp, vp, vp, vp, i32, i32, f32, vp]
     L.oxb_silu_mul.argtypes = [vp, vp, i32, i32, vp]
     L.oxb_qk_rope_kvwrite.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, vp, f32, i32, i32, i32, i32, vp, vp, vp, i32,
-                                      i32, vp]
+                                      i32, i32, vp]
     L.oxb_argmax.argtypes = [vp, i32, i32, i32, i32, vp, vp, i32, vp]
     L.oxb_paged_attention.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp,
-                                      vp, vp, vp]
+                                      vp, vp, i32, vp]
     L.oxb_sample.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, vp, i32, vp, vp]
     L.oxb_gemm_quant.argtypes =[vp, vp, i32, sz, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, sz, vp, i32, vp]
     u64p, ull = ctypes.POINTER(ctypes.c_uint64), ctypes.c_ulonglong
@@ -105,8 +105,21 @@ class Scratch:
         self.attn_ml: Optional[torch.Tensor] = None
         self.attn_counters = torch.zeros(65536, dtype=torch.int32, device=device)
         self.dequant: Optional[torch.Tensor] = None
+        self._cap_attn = None
+        self._cap_dequant = None
 
+    # The two growable buffers below must never be handed to a CUDA graph: growing them later would
+    # free memory that the captured kernels still point to.  While a stream is capturing, the buffers
+    # come from the graph's own memory pool instead (allocated once per capture, shared by its layers);
+    # the eager warm-up that precedes every capture resets that per-capture arena.
     def attn(self, o_floats: int, ml_floats: int):
+        if torch.cuda.is_current_stream_capturing():
+            a = self._cap_attn
+            if a is None or a[0].numel() < o_floats or a[1].numel() < ml_floats:
+                a = self._cap_attn = (torch.empty(max(o_floats, 1), dtype=torch.float32, device=self.device),
+                                      torch.empty(max(ml_floats, 1), dtype=torch.float32, device=self.device))
+            return a
+        self._cap_attn = None
         if self.attn_o is None or self.attn_o.numel() < o_floats:
             self.attn_o = torch.empty(max(o_floats, 1), dtype=torch.float32, device=self.device)
         if self.attn_ml is None or self.attn_ml.numel() < ml_floats:
@@ -114,6 +127,11 @@ class Scratch:
         return self.attn_o, self.attn_ml
 
     def dequant_buf(self, n: int) -> torch.Tensor:
+        if torch.cuda.is_current_stream_capturing():
+            if self._cap_dequant is None or self._cap_dequant.numel() < n:
+                self._cap_dequant = torch.empty(n, dtype=torch.bfloat16, device=self.device)
+            return self._cap_dequant
+        self._cap_dequant = None
         if self.dequant is None or self.dequant.numel() < n:
             self.dequant = torch.empty(n, dtype=torch.bfloat16, device=self.device)
         return self.dequant
@@ -289,7 +307,36 @@ def qk_rope_kv_write(qkv, positions, slot_mapping, kv, layer, rope, q_norm=None,
     _check(lib().oxb_qk_rope_kvwrite(qkv.data_ptr(), positions.data_ptr(), slot_mapping.data_ptr(), tab.data_ptr(),
                                      tab.shape[0], rot, 0 if rope.pairing == "split_half" else 1, _p(q_norm),
                                      _p(k_norm), eps, T, nq, nkv, hd, q.data_ptr(), kv.data[layer].data_ptr(), _p(sc),
-                                     KV_MODE[kv.dtype_name], kv.page_size, _stream()), "oxb_qk_rope_kvwrite")
+                                     KV_MODE[kv.dtype_name], kv.page_size, kv.num_blocks, _stream()), "oxb_qk_rope_kvwrite")
+    return q
+
+
+def qkv_rope_fusable(w_parts, kv, rope, q_norm, k_norm) -> bool:
+    """The fused qkv GEMM + RoPE + KV-write kernel covers the common case: one bf16 weight, head_dim 128,
+    full rotary, no QK-norm, bf16 KV pages."""
+    return (len(w_parts) == 1 and w_parts[0].qtype == "BF16" and rope.head_dim == 128 and q_norm is None
+            and k_norm is None and kv.dtype_name == "bf16" and rope_table(rope, 0).shape[1] == 128
+            and w_parts[0].shape[0] == (rope.n_heads + 2 * rope.n_kv_heads) * 128)
+
+
+def linear_qkv_rope(x: torch.Tensor, w: torch.Tensor, positions, slot_mapping, kv, layer, rope) -> torch.Tensor:
+    """q = RoPE(x Wq^T) as [T, nq, 128]; RoPE(x Wk^T) and x Wv^T go straight into the paged KV cache:
+    one kernel instead of the qkv GEMM followed by the RoPE / KV-write kernel."""
+    if x.dtype != torch.bfloat16:
+        x = x.to(torch.bfloat16)
+    x = x.contiguous()
+    T, K = x.shape
+    nq, nkv = rope.n_heads, rope.n_kv_heads
+    tab = rope_table(rope, 0)
+    q = torch.empty(T, nq, 128, dtype=torch.bfloat16, device=x.device)
+    L = lib()
+    if not getattr(L, "_qkv_rope_declared", False):
+        vp, i32 = ctypes.c_void_p, ctypes.c_int
+        L.oxb_gemm_qkv_rope.argtypes = [vp, vp, i32, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, vp]
+        L._qkv_rope_declared = True
+    _check(L.oxb_gemm_qkv_rope(x.data_ptr(), w.data_ptr(), T, K, positions.data_ptr(), slot_mapping.data_ptr(),
+                               tab.data_ptr(), tab.shape[0], tab.shape[1], 0 if rope.pairing == "split_half" else 1, nq, nkv,
+                               q.data_ptr(), kv.data[layer].data_ptr(), kv.page_size, kv.num_blocks, _stream()), "oxb_gemm_qkv_rope")
     return q
 
 
@@ -334,7 +381,7 @@ def paged_attention(q, kv, layer, meta, scale, sliding_window=0, splits: Optiona
                                      meta.block_tables.data_ptr(), meta.seq_lens.data_ptr(), meta.query_start.data_ptr(),
                                      B, meta.block_tables.stride(0), nq, nkv, hd, KV_MODE[kv.dtype_name],
                                      max(1, meta.max_query_len), splits, sliding_window, scale, _p(ws_o), _p(ws_ml),
-                                     _p(cnt), _stream()), "oxb_paged_attention")
+                                     _p(cnt), kv.num_blocks, _stream()), "oxb_paged_attention")
     return out
 
 

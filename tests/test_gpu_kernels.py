@@ -426,3 +426,80 @@ def test_gemm_swiglu_epilogue(C, T, F, K):
     unfused = C.silu_mul(C.gemm_bf16(x, w))
     assert _rel_err(got, unfused) < 1e-2
     _check_status(C)
+
+
+@pytest.mark.parametrize("pairing", ["split_half", "adjacent"])
+@pytest.mark.parametrize("T,nq,nkv,K", [(1, 8, 1, 1024), (64, 8, 1, 8192), (37, 4, 2, 512), (300, 8, 2, 1024)])
+def test_qkv_gemm_with_rope_kvwrite_epilogue(C, pairing, T, nq, nkv, K):
+    """qkv GEMM with RoPE + KV write as its epilogue == qkv GEMM followed by the RoPE / KV-write kernel, bit for bit."""
+    from oxidize_b200.engine.kv_pool import KVCache, KVCacheSpec
+    from oxidize_b200.models.transformer import RopeState
+    from oxidize_b200.ops import ref as opref
+
+    torch.manual_seed(T * 7 + nq)
+    hd, page = 128, 16
+    dev = torch.device("cuda")
+    rope = RopeState(inv_freq=opref.rope_inv_freq(hd, 500000.0, None, device=dev), pairing=pairing, mscale=1.0, n_heads=nq,
+                     n_kv_heads=nkv, head_dim=hd)
+    x = torch.randn(T, K, device=dev).to(torch.bfloat16)
+    w = (torch.randn((nq + 2 * nkv) * hd, K, device=dev) * K ** -0.5).to(torch.bfloat16)
+    nblocks = (T + page - 1) // page + 3
+    perm = torch.randperm(nblocks * page, device=dev)[:T].to(torch.int32)
+    slots = perm.clone()
+    slots[::5] = -1  # some rows must not touch the cache
+    positions = torch.randint(0, 4000, (T,), device=dev, dtype=torch.int32)
+    spec = KVCacheSpec(1, nkv, hd, page, "bf16")
+    kv_a, kv_b = KVCache(spec, nblocks, dev), KVCache(spec, nblocks, dev)
+    for kvc in (kv_a, kv_b):
+        kvc.data[0].fill_(7.0)
+    from oxidize_b200.models.weights import QTensor
+
+    part = QTensor("BF16", w, tuple(w.shape))
+    assert C.qkv_rope_fusable([part], kv_a, rope, None, None)
+    q_ref = C.qk_rope_kv_write(C.gemm_bf16(x, w), positions, slots, kv_a, 0, rope)
+    q = C.linear_qkv_rope(x, w, positions, slots, kv_b, 0, rope)
+    torch.cuda.synchronize()
+    assert torch.equal(q, q_ref)
+    assert torch.equal(kv_a.data[0], kv_b.data[0])
+    assert (kv_b.data[0] == 7.0).any()  # untouched slots stayed untouched
+    _check_status(C)
+
+
+def test_decode_graph_with_padded_rows_after_sequences_finish(C):
+    """The serving steady state: a 64-row decode graph keeps running while sequences finish, so some of
+    its rows become padding; the captured step is then replayed back to back (as the benchmark's
+    device-timed loop does).  Per-rank shapes of the 70B model under TP8, two layers."""
+    from oxidize_b200.engine.llm import LLM, EngineConfig
+    from oxidize_b200.engine.runner import _bucket
+    from oxidize_b200.engine.sampler import SamplingParams
+    from oxidize_b200.models.config import preset
+    from oxidize_b200.utils.synth import synth_weights
+
+    dev = torch.device("cuda", 0)
+    cfg = preset("llama3-70b", n_layers=2, vocab_size=4096)
+    cfg.n_heads //= 8
+    cfg.n_kv_heads = 1
+    cfg.ffn_size //= 8
+    w = synth_weights(cfg, dev, "BF16", seed=0, tp_rank=0, tp_size=8)
+    llm = LLM(w, EngineConfig(max_model_len=512, max_num_seqs=64, num_kv_blocks=64 * 12, max_num_batched_tokens=2048,
+                              prefill_chunk_size=512, enable_prefix_cache=False, tp_size=8))
+    g = torch.Generator().manual_seed(0)
+    for i in range(64):
+        n = int(torch.randint(40, 120, (1,), generator=g))
+        llm.add_request(torch.randint(3, 4000, (n,), generator=g).tolist(),
+                        SamplingParams(temperature=0.0, max_tokens=6 if i % 8 == 0 else 60, ignore_eos=True))
+    steps = 0
+    while llm.has_unfinished and steps < 40:
+        llm.step()
+        steps += 1
+    running = len(llm.scheduler.running)
+    assert 48 < running < 64, running  # the short requests are gone, the 64-row bucket is now padded
+    graph = llm.runner.graphs.get(_bucket(running))
+    assert graph is not None
+    for _ in range(8):
+        graph.replay()
+    torch.cuda.synchronize()
+    for _ in range(3):
+        llm.step()
+    torch.cuda.synchronize()
+    _check_status(C)
