@@ -431,7 +431,8 @@ def test_gemm_swiglu_epilogue(C, T, F, K):
 @pytest.mark.parametrize("pairing", ["split_half", "adjacent"])
 @pytest.mark.parametrize("T,nq,nkv,K", [(1, 8, 1, 1024), (64, 8, 1, 8192), (37, 4, 2, 512), (300, 8, 2, 1024)])
 def test_qkv_gemm_with_rope_kvwrite_epilogue(C, pairing, T, nq, nkv, K):
-    """qkv GEMM with RoPE + KV write as its epilogue == qkv GEMM followed by the RoPE / KV-write kernel, bit for bit."""
+    """qkv GEMM with RoPE + KV write as its epilogue == qkv GEMM followed by the RoPE / KV-write kernel (same
+    bf16 inputs to the rotation; the two kernels may contract the multiply-adds differently: one bf16 ulp)."""
     from oxidize_b200.engine.kv_pool import KVCache, KVCacheSpec
     from oxidize_b200.models.transformer import RopeState
     from oxidize_b200.ops import ref as opref
@@ -459,8 +460,9 @@ def test_qkv_gemm_with_rope_kvwrite_epilogue(C, pairing, T, nq, nkv, K):
     q_ref = C.qk_rope_kv_write(C.gemm_bf16(x, w), positions, slots, kv_a, 0, rope)
     q = C.linear_qkv_rope(x, w, positions, slots, kv_b, 0, rope)
     torch.cuda.synchronize()
-    assert torch.equal(q, q_ref)
-    assert torch.equal(kv_a.data[0], kv_b.data[0])
+    assert _rel_err(q, q_ref) < 4e-3
+    assert _rel_err(kv_b.data[0], kv_a.data[0]) < 4e-3
+    assert torch.equal(kv_a.data[0] == 7.0, kv_b.data[0] == 7.0)  # exactly the same slots were written
     assert (kv_b.data[0] == 7.0).any()  # untouched slots stayed untouched
     _check_status(C)
 
@@ -480,9 +482,9 @@ def test_decode_graph_with_padded_rows_after_sequences_finish(C):
     cfg.n_heads //= 8
     cfg.n_kv_heads = 1
     cfg.ffn_size //= 8
-    w = synth_weights(cfg, dev, "BF16", seed=0, tp_rank=0, tp_size=8)
+    w = synth_weights(cfg, dev, "BF16", seed=0)
     llm = LLM(w, EngineConfig(max_model_len=512, max_num_seqs=64, num_kv_blocks=64 * 12, max_num_batched_tokens=2048,
-                              prefill_chunk_size=512, enable_prefix_cache=False, tp_size=8))
+                              prefill_chunk_size=512, enable_prefix_cache=False))
     g = torch.Generator().manual_seed(0)
     for i in range(64):
         n = int(torch.randint(40, 120, (1,), generator=g))
