@@ -622,6 +622,7 @@ struct GemmPlan {
 };
 
 extern int g_oxb_cluster_splitk;  // 1 = split-K through clusters / distributed shared memory (default)
+extern int g_oxb_gemm_prefill_tn;  // 0 = pick the token tile of prefill-sized calls by wave count, 128 / 256 = force
 
 // cluster_ok < 0: follow g_oxb_cluster_splitk.  max_ctas > 0 bounds tiles*splits (kernels whose CTAs wait
 // for CTAs of other GPUs must be resident all at once).
@@ -630,6 +631,13 @@ inline GemmPlan gemm_plan(int T, int N, int K, int splits_hint, int sm_count, in
   if (cluster_ok < 0) cluster_ok = g_oxb_cluster_splitk;
   p.tn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
   p.n_tiles = (N + GEMM_BM - 1) / GEMM_BM;
+  if (T > 256 && sm_count > 0) {
+    // Prefill-sized calls run one CTA per SM in waves; a nearly empty last wave costs a whole tile time.
+    // 128-token tiles take half as long as 256-token ones, so compare the wave counts in half-tile units.
+    const long long w256 = ((long long)p.n_tiles * ((T + 255) / 256) + sm_count - 1) / sm_count * 2;
+    const long long w128 = ((long long)p.n_tiles * ((T + 127) / 128) + sm_count - 1) / sm_count;
+    if (g_oxb_gemm_prefill_tn == 128 || (g_oxb_gemm_prefill_tn == 0 && w128 < w256)) p.tn = 128;
+  }
   p.t_tiles = (T + p.tn - 1) / p.tn;
   const int kb_total = (K + GEMM_BK - 1) / GEMM_BK;
   int splits = splits_hint;

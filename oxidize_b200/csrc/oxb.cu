@@ -13,6 +13,13 @@ using namespace oxb;
 int g_oxb_pdl = 1;
 int oxb::g_oxb_cluster_splitk = 1;
 int oxb::g_oxb_gemm_l2_prefetch_kb = 0;
+int oxb::g_oxb_gemm_prefill_tn = 256;  // until the 128-token choice is measured: keep 256
+
+OXB_API int oxb_set_gemm_prefill_tn(int tn) {
+  const int old = oxb::g_oxb_gemm_prefill_tn;
+  oxb::g_oxb_gemm_prefill_tn = (tn == 128 || tn == 256) ? tn : 0;  // 0 = choose by wave count
+  return old;
+}
 
 // Weight k-blocks (16 KB each) per CTA that GEMMs launched from now on request into the L2 before their grid
 // dependency resolves; the caller sets it around a GEMM that follows a collective and resets it to 0.

@@ -44,6 +44,8 @@ def lib():
                     _lib.oxb_set_pdl(0)
                 if os.environ.get("OXB_CLUSTER_SPLITK", "1") == "0":
                     _lib.oxb_set_cluster_splitk(0)
+                if os.environ.get("OXB_GEMM_PREFILL_TN"):
+                    _lib.oxb_set_gemm_prefill_tn(int(os.environ["OXB_GEMM_PREFILL_TN"]))
     return _lib
 
 

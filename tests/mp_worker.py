@@ -130,6 +130,92 @@ def case_tp_model(dev, comm_kind):
             assert comm.fused_calls > 0
 
 
+def case_ep_model(dev, comm_kind):
+    """Expert parallelism (experts split over the ranks, attention tensor-parallel) == single rank."""
+    layout = init_distributed()
+    path = os.path.join(tempfile.gettempdir(), f"oxb_ep_tiny_{os.environ.get('MASTER_PORT', '0')}.gguf")
+    if layout.rank == 0:
+        cfg = preset("mixtral-8x7b", hidden_size=128, n_layers=2, n_heads=4, n_kv_heads=2, head_dim=32, ffn_size=256,
+                     expert_ffn_size=64, vocab_size=256, n_experts=4, n_experts_used=2)
+        synth_gguf(path, cfg, "BF16", seed=2, norm_jitter=0.1)
+    dist.barrier()
+    g = load_gguf(path)
+    cfg = config_from_gguf(g)
+    act = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    ec = dict(max_model_len=128, max_num_seqs=4, num_kv_blocks=64, prefill_chunk_size=32, max_num_batched_tokens=64,
+              cuda_graphs=False)
+    comm = make_comm(comm_kind, dev) if dev.type == "cuda" else TorchComm()
+    W = layout.world_size
+    w_ep = load_weights(g, cfg, dev, act, layout.rank, W, layout.rank, W)
+    assert len(w_ep.layers[0].experts.gate_up) == cfg.n_experts // W
+    w_1 = load_weights(g, cfg, dev, act, 0, 1)
+    ep = LLM(w_ep, EngineConfig(tp_size=W, ep_size=W, **ec), comm)
+    one = LLM(w_1, EngineConfig(**ec))
+    ep.runner.keep_logits = one.runner.keep_logits = True
+    sp = SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True)
+    for p in ([5, 9, 200, 31, 7], list(range(3, 40))):
+        ep.add_request(p, sp)
+        one.add_request(p, sp)
+    while ep.has_unfinished:
+        ep.step()
+        one.step()
+        a, b = ep.last_step[1].logits, one.last_step[1].logits
+        tol = 3e-2 if dev.type == "cuda" else 1e-4
+        assert a.shape == b.shape and rel_err(a, b) < tol, rel_err(a, b)
+
+
+def case_pp_model(dev, comm_kind):
+    """Two pipeline stages (each holds half of the layers) produce the single-process tokens."""
+    from oxidize_b200.engine.kv_pool import KVCache, KVCacheSpec
+    from oxidize_b200.models.transformer import BatchMeta, Transformer
+    from oxidize_b200.parallel.pp import PipelineStage, StageIO, split_layers
+
+    layout = init_distributed()
+    path = _tiny_file(layout.rank)
+    g = load_gguf(path)
+    cfg = config_from_gguf(g)
+    act = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    W, rank = layout.world_size, layout.rank
+    lo, hi = split_layers(cfg.n_layers, W)[rank]
+    w_stage = load_weights(g, cfg, dev, act, 0, 1, layer_range=(lo, hi))
+    assert len(w_stage.layers) == hi - lo
+    stage = PipelineStage(Transformer(w_stage), StageIO(rank, W))
+    kv = KVCache(KVCacheSpec(hi - lo, cfg.n_kv_heads, cfg.head_dim, 16, "f32" if dev.type == "cpu" else "bf16"), 8, dev)
+    prompt = [4, 8, 15, 16, 23, 42, 7]
+    n_new = 5
+
+    def meta_for(tokens, start):
+        n = len(tokens)
+        i32 = dict(dtype=torch.int32, device=dev)
+        pos = torch.arange(start, start + n, **i32)
+        return BatchMeta(token_ids=torch.tensor(tokens, **i32), positions=pos, slot_mapping=pos.clone(),
+                         query_start=torch.tensor([0, n], **i32), seq_lens=torch.tensor([start + n], **i32),
+                         block_tables=torch.arange(8, **i32)[None, :], logits_indices=torch.tensor([n - 1], **i32),
+                         max_query_len=n, max_seq_len=start + n, num_seqs=1)
+
+    toks = list(prompt)
+    feed, start = list(prompt), 0
+    out = []
+    for _ in range(n_new):
+        t = stage.forward_microbatch(meta_for(feed, start), kv)
+        if stage.io.is_last:
+            nxt = int(t[0])
+        else:
+            nxt = int(stage.io.recv_tokens_from_last(1, dev)[0]) if stage.io.is_first else 0
+        stage.drain()
+        b = torch.tensor([nxt], dtype=torch.int64, device=dev)
+        dist.broadcast(b, src=W - 1)
+        nxt = int(b[0])
+        out.append(nxt)
+        start += len(feed)
+        feed = [nxt]
+    # single-process reference
+    ref = LLM(load_weights(g, cfg, dev, act, 0, 1), EngineConfig(max_model_len=64, max_num_seqs=2, num_kv_blocks=16,
+                                                                  cuda_graphs=False))
+    want = ref.generate([prompt], SamplingParams(temperature=0.0, max_tokens=n_new, ignore_eos=True))[0].token_ids
+    assert out == want, (out, want)
+
+
 def case_tp_graph(dev, comm_kind):
     """Decode under CUDA graphs with the fused collectives gives the same tokens as eager."""
     layout = init_distributed()
@@ -175,7 +261,7 @@ def case_rank_exit(dev, comm_kind):
     hb.stop()
 
 
-CASES = {"gemm_ar": case_gemm_ar, "tp_model": case_tp_model, "tp_graph": case_tp_graph, "rank_exit": case_rank_exit}
+CASES = {"gemm_ar": case_gemm_ar, "tp_model": case_tp_model, "tp_graph": case_tp_graph, "rank_exit": case_rank_exit, "ep_model": case_ep_model, "pp_model": case_pp_model}
 
 
 def main():

@@ -37,6 +37,18 @@ def test_tp2_logits_match_tp1_on_cpu():
     assert r.stdout.count("OK tp_model") == 2
 
 
+def test_ep2_moe_logits_match_single_rank_on_cpu():
+    r = run_ranks("ep_model")
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("OK ep_model") == 2
+
+
+def test_pp2_tokens_match_single_process_on_cpu():
+    r = run_ranks("pp_model")
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("OK pp_model") == 2
+
+
 def test_rank_exit_detected_by_heartbeat():
     r = run_ranks("rank_exit")
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
