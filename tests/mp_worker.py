@@ -135,8 +135,10 @@ def case_ep_model(dev, comm_kind):
     layout = init_distributed()
     path = os.path.join(tempfile.gettempdir(), f"oxb_ep_tiny_{os.environ.get('MASTER_PORT', '0')}.gguf")
     if layout.rank == 0:
-        cfg = preset("mixtral-8x7b", hidden_size=128, n_layers=2, n_heads=4, n_kv_heads=2, head_dim=32, ffn_size=256,
-                     expert_ffn_size=64, vocab_size=256, n_experts=4, n_experts_used=2)
+        big = dev.type == "cuda"  # the GPU attention kernels take head_dim 64 / 128
+        cfg = preset("mixtral-8x7b", hidden_size=256 if big else 128, n_layers=2, n_heads=4, n_kv_heads=2,
+                     head_dim=64 if big else 32, ffn_size=512 if big else 256, expert_ffn_size=128 if big else 64,
+                     vocab_size=256, n_experts=4, n_experts_used=2)
         synth_gguf(path, cfg, "BF16", seed=2, norm_jitter=0.1)
     dist.barrier()
     g = load_gguf(path)

@@ -36,6 +36,12 @@ def test_tp_decode_under_cuda_graphs():
 
 
 @NEED2
+def test_expert_parallel_moe_matches_single_rank():
+    r = run_ranks("ep_model", n=2, device="cuda", comm="fused", env_extra=ENV)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@NEED2
 def test_rank_exit_between_steps_is_detected():
     r = run_ranks("rank_exit", n=2, device="cuda", comm="nccl", env_extra=ENV)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
