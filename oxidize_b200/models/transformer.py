@@ -103,7 +103,8 @@ class Transformer:
 
         self._post_collective_prefetch_kb = 0
         if dev.type == "cuda" and getattr(self.comm, "size", 1) > 1:
-            self._post_collective_prefetch_kb = int(os.environ.get("OXB_L2_PREFETCH_KB", "12"))
+            # measured at 2 and 8 GPUs: no effect on the step (10.42 vs 10.43 ms at 8), so it is off by default
+            self._post_collective_prefetch_kb = int(os.environ.get("OXB_L2_PREFETCH_KB", "0"))
         # per-projection override "qkv:o:gate_up:down" in weight k-blocks per CTA (experiments)
         pf = os.environ.get("OXB_PF", "")
         self._pf = [int(v) for v in pf.split(":")] if pf and dev.type == "cuda" else None

@@ -33,7 +33,7 @@ def make_comm(kind, dev):
     if kind == "fused":
         from oxidize_b200.parallel.fused import FusedComm
 
-        return FusedComm(dev, max_tokens=1024, hidden=8192)
+        return FusedComm(dev, max_tokens=1024, hidden=8192, fused_max_tokens=1024)
     return TorchComm()
 
 
