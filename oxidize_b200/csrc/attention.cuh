@@ -247,22 +247,9 @@ paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
     return id;
   };
 
-  // While the upstream kernels (qkv GEMM tail, RoPE + KV write) finish, ask for this warp's stable
-  // pages into the L2: K and V page of one (block, head) are 2 * 16 * HD * 2 contiguous bytes.
-  if (a.kv_mode <= 1) {
-    const int n_stable = (seq_len - qlen) / ATT_PAGE;
-    for (int i = lane; i < my_pages; i += 32) {
-      const int page = page_lo + first + i * stride;
-      if (page < n_stable && page < a.max_blocks) {
-        const int blk = bt[page];
-        if ((unsigned)blk < (unsigned)a.num_blocks) {
-          const uint8_t* src = reinterpret_cast<const uint8_t*>(a.kv_data) +
-                               ((size_t)blk * a.nkv + kvh) * 2 * (size_t)(ATT_PAGE * HD * 2);
-          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(2 * ATT_PAGE * HD * 2) : "memory");
-        }
-      }
-    }
-  }
+  // (Requesting this warp's stable KV pages into the L2 here, before the dependency resolves, was
+  // measured: it only pays when the upstream kernel leaves HBM idle; behind the qkv GEMM it costs
+  // 5-30 %, so the kernel does not do it.)
   pdl_wait();
   ATT_STAMP(1);
   // Q fragments (A operand), straight from global memory
