@@ -154,7 +154,9 @@ def case_ep_model(dev, comm_kind):
     ep = LLM(w_ep, EngineConfig(tp_size=W, ep_size=W, **ec), comm)
     one = LLM(w_1, EngineConfig(**ec))
     ep.runner.keep_logits = one.runner.keep_logits = True
-    sp = SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True)
+    # one sampled token: the logits of the prompt are compared; with more, a near-tie in bf16 may pick
+    # different tokens in the two runs and the later logits are no longer comparable
+    sp = SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True)
     for p in ([5, 9, 200, 31, 7], list(range(3, 40))):
         ep.add_request(p, sp)
         one.add_request(p, sp)
