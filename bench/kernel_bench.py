@@ -161,6 +161,55 @@ def small_case(spec: str, launches: int):
         q = torch.randn(B, nq, hd, device="cuda").to(torch.bfloat16)
         for i in range(launches):
             C.paged_attention(q, kv, i % layers, m, hd ** -0.5, 0)
+    elif kind == "mmq":  # mmq:QTYPE:TxNxK  dequant-fused tcgen05 GEMM on packed weights
+        from oxidize_b200.models.weights import QTensor
+        from oxidize_b200.quant.torch_quant import random_quantized
+
+        qt, _, dims = rest.partition(":")
+        T, N, K = (int(v) for v in dims.split("x"))
+        copies = 3
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(0)
+        ws = [random_quantized(N, K, qt, torch.device("cuda"), gen, 0.02) for _ in range(copies)]
+        x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
+        for i in range(launches):
+            C.linear(x, [ws[i % copies]])
+    elif kind == "swiglu":  # swiglu:TxFxK  gate_up GEMM with the SwiGLU epilogue
+        T, F, K = (int(v) for v in rest.split("x"))
+        copies = max(2, int(300e6 // (2 * F * K * 2)) + 1)
+        ws = [C.interleave_gate_up((torch.randn(2 * F, K, device="cuda") * 0.02).to(torch.bfloat16)) for _ in range(copies)]
+        x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
+        for i in range(launches):
+            C.linear_swiglu(x, ws[i % copies])
+    elif kind == "rmsnorm":  # rmsnorm:TxH  residual add + RMSNorm
+        T, H = (int(v) for v in rest.split("x"))
+        w = torch.ones(H, device="cuda")
+        hs = [torch.randn(T, H, device="cuda").to(torch.bfloat16) for _ in range(4)]
+        res = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+        for i in range(launches):
+            C.add_rmsnorm(hs[i % 4], res, w, 1e-5)
+    elif kind == "sample":  # sample:RxV  device sampler (top-k / top-p rows)
+        from oxidize_b200.ops import cuda_sampling
+
+        R, V = (int(v) for v in rest.split("x"))
+        logits = torch.randn(R, V, device="cuda")
+        temp = torch.full((R,), 0.8, device="cuda")
+        topk = torch.full((R,), 40, dtype=torch.int32, device="cuda")
+        topp = torch.full((R,), 0.9, device="cuda")
+        minp = torch.zeros(R, device="cuda")
+        rnd = torch.rand(R, device="cuda")
+        for i in range(launches):
+            cuda_sampling.sample(logits, temp, topk, topp, minp, rnd, "lowest")
+    elif kind == "moe":  # moe:TxExKtop  routing kernel
+        from oxidize_b200.models.config import ModelConfig
+        from oxidize_b200.ops import cuda_moe
+
+        T, E, k = (int(v) for v in rest.split("x"))
+        cfg = ModelConfig(n_experts=E, n_experts_used=k)
+        logits = torch.randn(T, E, device="cuda")
+        scale = torch.empty(E, T, device="cuda")
+        for i in range(launches):
+            cuda_moe.moe_route(logits, cfg, None, scale, 0, E)
     else:
         raise SystemExit(f"unknown case {spec}")
     torch.cuda.synchronize()

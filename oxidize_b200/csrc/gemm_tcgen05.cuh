@@ -376,21 +376,36 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       const int r = threadIdx.x - 192;
       const int n = n0 + r;
       const uint8_t* rowp = qw.w + ((size_t)zg * gr.w_rows + (size_t)(n < N ? n : 0)) * qw.row_bytes;
-      for (int i = 0; i < nkb; ++i) {
-        const int st = i % STAGES;
-        const uint32_t ph = (i / STAGES) & 1;
-        if (!mbar_wait_bounded(&empty[st], ph ^ 1, abort_flag, OXB_TIMEOUT_TMA_EMPTY, blockIdx.x)) break;
-        uint32_t v[32];
-        const int k0 = (kb_begin + i) * GEMM_BK;
+      // Each thread walks its own packed row.  Two k-blocks are decoded per iteration, and both are
+      // decoded into registers BEFORE the thread waits for their ring slots: the global loads of
+      // the two blocks overlap each other and the tensor core's work on the slots still in use
+      // (waiting first and loading afterwards left every k-block with a cold, dependent load:
+      // 95 us instead of the 24 us the same matrix takes in bf16).
+      auto decode = [&](int kb, uint32_t* v) {
+        const int k0 = kb * GEMM_BK;
         if (n < N && k0 + GEMM_BK <= K) {
           dequant64<QT>(rowp, k0, qw, n, v);
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0u;
         }
+      };
+      auto publish = [&](int i, const uint32_t* v) -> bool {
+        const int st = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        if (!mbar_wait_bounded(&empty[st], ph ^ 1, abort_flag, OXB_TIMEOUT_TMA_EMPTY, blockIdx.x)) return false;
         store_row_sw128(smem + st * Cfg::STAGE_BYTES, r, v);
         fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
         mbar_arrive(&full[st]);
+        return true;
+      };
+      for (int i = 0; i < nkb; i += 2) {
+        uint32_t v0[32], v1[32];
+        const bool two = i + 1 < nkb;
+        decode(kb_begin + i, v0);
+        if (two) decode(kb_begin + i + 1, v1);
+        if (!publish(i, v0)) break;
+        if (two && !publish(i + 1, v1)) break;
       }
     }
     __syncwarp();

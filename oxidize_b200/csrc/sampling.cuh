@@ -47,17 +47,61 @@ __device__ __forceinline__ uint32_t prob_bits(float p) { return __float_as_uint(
 // For the tokens whose probability bits match `prefix` on the top `done_bits` bits, accumulate
 // per-bin (next 8 bits) count and mass into shared histograms.
 __device__ __forceinline__ void radix_pass(const float* __restrict__ row, int V, float mx, float inv_t, uint32_t prefix,
-                                           int done_bits, int* cnt, float* mass) {
+                                           int done_bits, int* cnt, float* mass, int* wcnt, float* wmass) {
   for (int i = threadIdx.x; i < 256; i += blockDim.x) {
     cnt[i] = 0;
     mass[i] = 0.f;
+  }
+  if (done_bits == 0 && wcnt[32 * 64] != 0) {
+    // the first-pass histogram of this row was built by an earlier descent: reuse it
+    __syncthreads();
+    if (threadIdx.x < 64) {
+      cnt[threadIdx.x] = wcnt[32 * 64 + 1 + threadIdx.x];
+      mass[threadIdx.x] = wmass[32 * 64 + 1 + threadIdx.x];
+    }
+    __syncthreads();
+    return;
+  }
+  if (done_bits == 0) {
+    // First pass: EVERY token lands in one of a handful of bins (probabilities are <= 1, so the top
+    // byte of their bits is <= 63, and real rows use ~10 of those), and 1024 threads adding into the
+    // same few shared-memory words serialise.  Each warp therefore fills a private 64-bin histogram,
+    // summed afterwards (this pass was 95 % of the kernel's time before).
+    const int warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < 32 * 64; i += blockDim.x) {
+      wcnt[i] = 0;
+      wmass[i] = 0.f;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float p = __expf((row[i] - mx) * inv_t);
+      const int bin = min((int)(prob_bits(p) >> 24), 63);
+      atomicAdd(&wcnt[warp * 64 + bin], 1);
+      atomicAdd(&wmass[warp * 64 + bin], p);
+    }
+    __syncthreads();
+    if (threadIdx.x < 64) {
+      int c = 0;
+      float m = 0.f;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) {
+        c += wcnt[w * 64 + threadIdx.x];
+        m += wmass[w * 64 + threadIdx.x];
+      }
+      cnt[threadIdx.x] = c;
+      mass[threadIdx.x] = m;
+      wcnt[32 * 64 + 1 + threadIdx.x] = c;  // kept for the row's next descent
+      wmass[32 * 64 + 1 + threadIdx.x] = m;
+    }
+    if (threadIdx.x == 0) wcnt[32 * 64] = 1;
+    __syncthreads();
+    return;
   }
   __syncthreads();
   const int shift = 24 - done_bits;
   for (int i = threadIdx.x; i < V; i += blockDim.x) {
     const float p = __expf((row[i] - mx) * inv_t);
     const uint32_t b = prob_bits(p);
-    if (done_bits == 0 || (b >> (32 - done_bits)) == (prefix >> (32 - done_bits))) {
+    if ((b >> (32 - done_bits)) == (prefix >> (32 - done_bits))) {
       const int bin = (b >> shift) & 0xFF;
       atomicAdd(&cnt[bin], 1);
       atomicAdd(&mass[bin], p);
@@ -70,12 +114,13 @@ __device__ __forceinline__ void radix_pass(const float* __restrict__ row, int V,
 // the walk crosses the boundary defined by (count limit, mass limit) inside the tokens whose
 // bits equal x.  Returns x and the count / mass strictly above x.
 __device__ void radix_descend(const float* row, int V, float mx, float inv_t, int count_limit, float mass_limit,
-                              int* cnt, float* mass, int* s_i, float* s_f, uint32_t& x, int& cnt_above, float& mass_above) {
+                              int* cnt, float* mass, int* wcnt, float* wmass, int* s_i, float* s_f, uint32_t& x, int& cnt_above,
+                              float& mass_above) {
   uint32_t prefix = 0;
   int ca = 0;
   float ma = 0.f;
   for (int done = 0; done < 32; done += 8) {
-    radix_pass(row, V, mx, inv_t, prefix, done, cnt, mass);
+    radix_pass(row, V, mx, inv_t, prefix, done, cnt, mass, wcnt, wmass);
     if (threadIdx.x == 0) {
       int c = ca;
       float m = ma;
@@ -108,11 +153,14 @@ sample_kernel(const float* __restrict__ logits, int V, int ld, const float* __re
   __shared__ float red[32];
   __shared__ int cnt[256];
   __shared__ float mass[256];
+  __shared__ int wcnt[32 * 64 + 65];     // per-warp histograms of the first radix pass; [2048] = "saved" flag,
+  __shared__ float wmass[32 * 64 + 65];  // [2049..2112] = the summed first-pass histogram, reused by the draw
   __shared__ int s_i[4];
   __shared__ float s_f[4];
   __shared__ int s_best;
   pdl_launch_dependents();
   pdl_wait();
+  if (threadIdx.x == 0) wcnt[32 * 64] = 0;
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * ld;
   const float T = temperature[r];
@@ -213,7 +261,7 @@ sample_kernel(const float* __restrict__ logits, int V, int ld, const float* __re
   uint32_t xb;
   int c_above;
   float m_above;
-  radix_descend(row, V, mx, inv_t, klim, plim, cnt, mass, s_i, s_f, xb, c_above, m_above);
+  radix_descend(row, V, mx, inv_t, klim, plim, cnt, mass, wcnt, wmass, s_i, s_f, xb, c_above, m_above);
   // tokens with bits > xb are kept entirely; tokens with bits == xb are kept in index order while
   // the limits allow; min-p cuts by value on top of that
   const float pmin_keep = mp > 0.f ? mp * 1.0f /* p_max = exp(0) = 1 */ : 0.f;
@@ -257,7 +305,7 @@ sample_kernel(const float* __restrict__ logits, int V, int ld, const float* __re
   float m2;
   // boundary where mass-before exceeds target (no count limit); restrict to kept tokens by
   // noting that kept tokens form a prefix, so the walk never leaves it when target < kept
-  radix_descend(row, V, mx, inv_t, 0x7fffffff, nextafterf(target, INFINITY), cnt, mass, s_i, s_f, yb, c2, m2);
+  radix_descend(row, V, mx, inv_t, 0x7fffffff, nextafterf(target, INFINITY), cnt, mass, wcnt, wmass, s_i, s_f, yb, c2, m2);
   // inside the tie group of yb, tokens are ordered by index: pick the j-th
   const float py = __uint_as_float(yb);
   int j = py > 0.f ? (int)floorf((target - m2) / py) : 0;
