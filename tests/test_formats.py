@@ -9,7 +9,10 @@ from oxidize_b200.formats import gguf as G
 from oxidize_b200.formats import tokenizer as T
 from oxidize_b200.quant import ref as Q
 
-FIXTURES = "/root/reference/oxidize-core/tests/fixtures"
+# the reference checkout, when one sits beside this repository (or where OXIDIZE_REFERENCE_DIR points)
+_REF = os.environ.get("OXIDIZE_REFERENCE_DIR",
+                      os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference"))
+FIXTURES = os.path.join(_REF, "oxidize-core", "tests", "fixtures")
 
 
 def _write_small(path, alignment=32):
