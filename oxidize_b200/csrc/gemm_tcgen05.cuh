@@ -381,11 +381,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       // the two blocks overlap each other and the tensor core's work on the slots still in use
       // (waiting first and loading afterwards left every k-block with a cold, dependent load:
       // 95 us instead of the 24 us the same matrix takes in bf16).
+      // straight-line on purpose: no branch between the two decodes, so that the compiler can issue the
+      // loads of both k-blocks before the arithmetic of the first (addresses are clamped to valid
+      // blocks; out-of-range results are zeroed afterwards)
+      const int kb_last = (K / GEMM_BK) - 1;
       auto decode = [&](int kb, uint32_t* v) {
-        const int k0 = kb * GEMM_BK;
-        if (n < N && k0 + GEMM_BK <= K) {
-          dequant64<QT>(rowp, k0, qw, n, v);
-        } else {
+        const int kbc = kb < kb_last ? kb : kb_last;
+        dequant64<QT>(rowp, kbc * GEMM_BK, qw, n < N ? n : 0, v);
+      };
+      auto mask = [&](int kb, uint32_t* v) {
+        if (!(n < N && kb <= kb_last)) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0u;
         }
@@ -403,7 +408,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         uint32_t v0[32], v1[32];
         const bool two = i + 1 < nkb;
         decode(kb_begin + i, v0);
-        if (two) decode(kb_begin + i + 1, v1);
+        decode(kb_begin + i + 1, v1);
+        mask(kb_begin + i, v0);
+        mask(kb_begin + i + 1, v1);
         if (!publish(i, v0)) break;
         if (two && !publish(i + 1, v1)) break;
       }

@@ -78,28 +78,64 @@ __device__ __forceinline__ void dequant64(const uint8_t* rowp, int k0, const QwA
       }
     }
   } else if constexpr (QT == QT_Q8_0) {
+    // two 34-byte blocks = 68 bytes = 17 aligned words (k0 is a multiple of 64, rows are 4-byte aligned):
+    // word 0 = {d0, q0 q1}, words 1..7 = q2..q29, word 8 = {q30 q31, d1}, words 9..16 = block 1's codes
+    const uint32_t* wp = reinterpret_cast<const uint32_t*>(rowp + (size_t)(k0 >> 6) * 68);
+    uint32_t x[17];
 #pragma unroll
-    for (int blk = 0; blk < 2; ++blk) {
-      const uint8_t* b = rowp + (size_t)((k0 >> 5) + blk) * 34;
-      const float d = __half2float(__ushort_as_half((unsigned short)ld_u16(b)));
+    for (int i = 0; i < 17; ++i) x[i] = wp[i];
+    const float d0 = __half2float(__ushort_as_half((unsigned short)(x[0] & 0xFFFF)));
+    const float d1 = __half2float(__ushort_as_half((unsigned short)(x[8] >> 16)));
+    auto pair = [](uint32_t h16, float d) {
+      return pack_bf16x2(d * (float)(int8_t)(h16 & 0xFF), d * (float)(int8_t)((h16 >> 8) & 0xFF));
+    };
+    out[0] = pair(x[0] >> 16, d0);
 #pragma unroll
-      for (int l = 0; l < 32; l += 2) {
-        const uint32_t w = ld_u16(b + 2 + l);
-        out[blk * 16 + (l >> 1)] = pack_bf16x2(d * (float)(int8_t)(w & 0xFF), d * (float)(int8_t)(w >> 8));
-      }
+    for (int i = 1; i <= 7; ++i) {
+      out[2 * i - 1] = pair(x[i] & 0xFFFF, d0);
+      out[2 * i] = pair(x[i] >> 16, d0);
+    }
+    out[15] = pair(x[8] & 0xFFFF, d0);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      out[16 + 2 * i] = pair(x[9 + i] & 0xFFFF, d1);
+      out[16 + 2 * i + 1] = pair(x[9 + i] >> 16, d1);
     }
   } else if constexpr (QT == QT_Q4_0) {
+    // two 18-byte blocks = 36 bytes = 9 aligned words: word 0 = {d0, b0 b1}, words 1..3 = b2..b13,
+    // word 4 = {b14 b15, d1}, words 5..8 = block 1's bytes; byte j holds value j (low nibble) and j+16 (high)
+    const uint32_t* wp = reinterpret_cast<const uint32_t*>(rowp + (size_t)(k0 >> 6) * 36);
+    uint32_t x[9];
 #pragma unroll
-    for (int blk = 0; blk < 2; ++blk) {
-      const uint8_t* b = rowp + (size_t)((k0 >> 5) + blk) * 18;
-      const float d = __half2float(__ushort_as_half((unsigned short)ld_u16(b)));
-      // byte j holds value j (low nibble) and value j+16 (high nibble)
+    for (int i = 0; i < 9; ++i) x[i] = wp[i];
+    const float d0 = __half2float(__ushort_as_half((unsigned short)(x[0] & 0xFFFF)));
+    const float d1 = __half2float(__ushort_as_half((unsigned short)(x[4] >> 16)));
+    // h16 = bytes (j, j+1): low nibbles -> values j, j+1; high nibbles -> values j+16, j+17
+    auto lo = [](uint32_t h16, float d) {
+      return pack_bf16x2(d * (float)((int)(h16 & 0xF) - 8), d * (float)((int)((h16 >> 8) & 0xF) - 8));
+    };
+    auto hi = [](uint32_t h16, float d) {
+      return pack_bf16x2(d * (float)((int)((h16 >> 4) & 0xF) - 8), d * (float)((int)((h16 >> 12) & 0xF) - 8));
+    };
+    uint32_t h0[8], h1[8];  // the 8 byte pairs of each block
+    h0[0] = x[0] >> 16;
 #pragma unroll
-      for (int j = 0; j < 16; j += 2) {
-        const uint32_t w = ld_u16(b + 2 + j);
-        out[blk * 16 + (j >> 1)] = pack_bf16x2(d * (float)((int)(w & 0xF) - 8), d * (float)((int)((w >> 8) & 0xF) - 8));
-        out[blk * 16 + 8 + (j >> 1)] = pack_bf16x2(d * (float)((int)((w >> 4) & 0xF) - 8), d * (float)((int)(w >> 12) - 8));
-      }
+    for (int i = 1; i <= 3; ++i) {
+      h0[2 * i - 1] = x[i] & 0xFFFF;
+      h0[2 * i] = x[i] >> 16;
+    }
+    h0[7] = x[4] & 0xFFFF;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      h1[2 * i] = x[5 + i] & 0xFFFF;
+      h1[2 * i + 1] = x[5 + i] >> 16;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      out[j] = lo(h0[j], d0);
+      out[8 + j] = hi(h0[j], d0);
+      out[16 + j] = lo(h1[j], d1);
+      out[24 + j] = hi(h1[j], d1);
     }
   } else if constexpr (QT == QT_NVFP4) {
     const uint32_t* b = reinterpret_cast<const uint32_t*>(rowp + (size_t)(k0 >> 6) * 36);
