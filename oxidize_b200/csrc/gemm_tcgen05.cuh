@@ -43,6 +43,19 @@ struct GemmTile {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
+// Q4_K weights with decode-sized token tiles are staged through shared memory: one TMA box of
+// 128 rows x 144 bytes (one 256-value super-block of every row of the tile) per four k-blocks, double
+// buffered; the producer warps decode from there.  (Reading the packed rows straight from global memory,
+// one thread per row, makes every warp-wide load touch 32 cache lines.)
+constexpr int MMQ_SB_BYTES = 144;                          // Q4_K super-block
+constexpr int MMQ_PACKED_BYTES = GEMM_BM * MMQ_SB_BYTES;   // 18432
+template <int TN, int QT>
+struct MmqStaged {
+  static constexpr bool value = QT == QT_Q4_K && TN <= 64;
+};
+template <int TN, int QT>
+constexpr int gemm_smem_bytes() { return GemmTile<TN>::SMEM_BYTES + (MmqStaged<TN, QT>::value ? 2 * MMQ_PACKED_BYTES : 0); }
+
 // Epilogue modes
 constexpr int EPI_STORE = 0;      // Y = acc (+bias)
 constexpr int EPI_ADD_INTO = 1;   // Y += acc (residual accumulate, bf16 read-modify-write)
@@ -260,6 +273,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* ticket = const_cast<int*>(abort_flag) + 1;
+  constexpr bool STAGED = MmqStaged<TN, QT>::value;
+  uint64_t* packed_full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES + 192);  // [2] (STAGED only)
+  uint8_t* packed_buf = smem + STAGES * Cfg::STAGE_BYTES + 256;                                  // [2][128][144]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * GEMM_BM;
@@ -280,6 +296,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       mbar_init(&empty[i], 1);
     }
     mbar_init(accum, 1);
+    if constexpr (STAGED) {
+      mbar_init(&packed_full[0], 1);
+      mbar_init(&packed_full[1], 1);
+    }
     *abort_flag = 0;
     ticket[0] = 0;
     mbar_fence_init();
@@ -404,15 +424,47 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         mbar_arrive(&full[st]);
         return true;
       };
-      for (int i = 0; i < nkb; i += 2) {
-        uint32_t v0[32], v1[32];
-        const bool two = i + 1 < nkb;
-        decode(kb_begin + i, v0);
-        decode(kb_begin + i + 1, v1);
-        mask(kb_begin + i, v0);
-        mask(kb_begin + i + 1, v1);
-        if (!publish(i, v0)) break;
-        if (two && !publish(i + 1, v1)) break;
+      if constexpr (STAGED) {
+        // Packed super-blocks arrive by TMA (tmW maps the packed rows as bytes): thread 192 keeps two
+        // boxes in flight, all 128 producers decode their own row out of shared memory.  Weights are
+        // static, so none of this waits for the upstream kernel.
+        const int sb_begin = kb_begin >> 2, sb_end = (kb_end + 3) >> 2;  // super-blocks touched by [kb_begin, kb_end)
+        auto issue = [&](int j) {  // j-th super-block of this CTA -> buffer j & 1
+          mbar_expect_tx(&packed_full[j & 1], MMQ_PACKED_BYTES);
+          tma_load_2d(packed_buf + (j & 1) * MMQ_PACKED_BYTES, &tmW, &packed_full[j & 1], (sb_begin + j) * MMQ_SB_BYTES, w_row0);
+        };
+        const int nsb = sb_end - sb_begin;
+        if (r == 0) {
+          tma_prefetch_desc(&tmW);
+          for (int j = 0; j < 2 && j < nsb; ++j) issue(j);
+        }
+        bool alive = true;
+        for (int j = 0; j < nsb; ++j) {
+          if (alive) alive = mbar_wait_bounded(&packed_full[j & 1], (j >> 1) & 1, abort_flag, OXB_TIMEOUT_TMA_FULL, blockIdx.x);
+          if (alive) {
+            const uint8_t* srow = packed_buf + (j & 1) * MMQ_PACKED_BYTES + r * MMQ_SB_BYTES;
+            const int kb0 = max(kb_begin, (sb_begin + j) * 4), kb1 = min(kb_end, (sb_begin + j) * 4 + 4);
+            for (int kb = kb0; kb < kb1 && alive; ++kb) {
+              uint32_t v[32];
+              dequant64<QT>(srow, (kb & 3) * GEMM_BK, qw, 0, v);  // rows past N were zero-filled by the TMA
+              alive = publish(kb - kb_begin, v);
+            }
+          }
+          // every producer is done with this buffer before it is refilled (all 128 take part, alive or not)
+          asm volatile("bar.sync 2, 128;" ::: "memory");
+          if (r == 0 && alive && j + 2 < nsb) issue(j + 2);
+        }
+      } else {
+        for (int i = 0; i < nkb; i += 2) {
+          uint32_t v0[32], v1[32];
+          const bool two = i + 1 < nkb;
+          decode(kb_begin + i, v0);
+          decode(kb_begin + i + 1, v1);
+          mask(kb_begin + i, v0);
+          mask(kb_begin + i + 1, v1);
+          if (!publish(i, v0)) break;
+          if (two && !publish(i + 1, v1)) break;
+        }
       }
     }
     __syncwarp();
@@ -711,7 +763,7 @@ int gemm_max_cluster() {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1, 16, 1);
     cfg.blockDim = dim3(QT == QT_BF16 ? GEMM_THREADS : GEMM_THREADS_MMQ);
-    cfg.dynamicSmemBytes = GemmTile<TN>::SMEM_BYTES;
+    cfg.dynamicSmemBytes = gemm_smem_bytes<TN, QT>();
     cudaLaunchAttribute at;
     at.id = cudaLaunchAttributeClusterDimension;
     at.val.clusterDim.x = 1;
@@ -736,7 +788,7 @@ int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<TN, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::SMEM_BYTES);
+                                         gemm_smem_bytes<TN, QT>());
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -751,10 +803,10 @@ int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y
   GroupArgs grl = gr;
   grl.l2_prefetch_kb = g_oxb_gemm_l2_prefetch_kb;
   if (p.cluster && splits > 1) {
-    le = oxb_launch_cluster(gemm_bf16_kernel<TN, QT>, grid, block, dim3(1, splits, 1), (size_t)Cfg::SMEM_BYTES, stream, tmW,
+    le = oxb_launch_cluster(gemm_bf16_kernel<TN, QT>, grid, block, dim3(1, splits, 1), (size_t)gemm_smem_bytes<TN, QT>(), stream, tmW,
                             tmX, Y, bias, N, T, K, ldY, splits, ws, counters, epi_mode, ar, qw, grl, ro);
   } else {
-    le = oxb_launch(gemm_bf16_kernel<TN, QT>, grid, block, (size_t)Cfg::SMEM_BYTES, stream, tmW, tmX, Y, bias, N, T, K, ldY,
+    le = oxb_launch(gemm_bf16_kernel<TN, QT>, grid, block, (size_t)gemm_smem_bytes<TN, QT>(), stream, tmW, tmX, Y, bias, N, T, K, ldY,
                     splits, ws, counters, epi_mode, ar, qw, grl, ro);
   }
   if (le != cudaSuccess) return (int)le;
@@ -766,11 +818,14 @@ int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y
 template <int QT>
 int gemm_launch_mmq(const CUtensorMap& tmX, __nv_bfloat16* Y, const float* bias, int N, int T, int K, int ldY,
                     const GemmPlan& p, float* ws, int* counters, int epi_mode, const ArArgs& ar, cudaStream_t stream,
-                    const QwArgs& qw, const GroupArgs& gr = GroupArgs{0, 0, 0, 0, nullptr, 0, 0}, int groups = 1) {
+                    const QwArgs& qw, const GroupArgs& gr = GroupArgs{0, 0, 0, 0, nullptr, 0, 0}, int groups = 1,
+                    const CUtensorMap* tmWq = nullptr) {
+  // tmWq: byte map of the packed rows (needed by the staged Q4_K path); other formats never touch tmW
+  const CUtensorMap& tmW = tmWq != nullptr ? *tmWq : tmX;
   switch (p.tn) {
-    case 16: return gemm_launch<16, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
-    case 32: return gemm_launch<32, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
-    case 64: return gemm_launch<64, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
+    case 16: return gemm_launch<16, QT>(tmW, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
+    case 32: return gemm_launch<32, QT>(tmW, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
+    case 64: return gemm_launch<64, QT>(tmW, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
     case 128: return gemm_launch<128, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
     default: return gemm_launch<256, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
   }

@@ -85,6 +85,23 @@ int oxb_make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+// Byte view of packed weight rows for the staged MMQ path: [rows, row_bytes] uint8, no swizzle.
+int oxb_make_tmap_bytes(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
+                        uint32_t box_bytes) {
+  PFN_encodeTiled enc = oxb_get_encode_tiled();
+  if (enc == nullptr) return (int)cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (row_bytes & 15) != 0 || (box_bytes & 15) != 0 || box_bytes > 256)
+    return (int)cudaErrorInvalidValue;
+  cuuint64_t dims[2] = {row_bytes, rows};
+  cuuint64_t strides[1] = {row_bytes};
+  cuuint32_t box[2] = {box_bytes, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
 static int sm_count() {
   static int n = 0;
   if (n == 0) {
@@ -177,7 +194,15 @@ OXB_API int oxb_gemm_quant(const void* X, const void* Wq, int qtype, size_t row_
   memset(&ar, 0, sizeof(ar));
   QwArgs qw{reinterpret_cast<const uint8_t*>(Wq), row_bytes, scales, scale_ld};
   switch (qtype) {
-    case QT_Q4_K: return gemm_launch_mmq<QT_Q4_K>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
+    case QT_Q4_K: {
+      CUtensorMap tmWq;
+      if (p.tn <= 64) {  // staged path: packed super-blocks by TMA
+        e = oxb_make_tmap_bytes(&tmWq, Wq, (uint64_t)N, row_bytes, GEMM_BM, MMQ_SB_BYTES);
+        if (e) return e;
+      }
+      return gemm_launch_mmq<QT_Q4_K>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw,
+                                      GroupArgs{0, 0, 0, 0, nullptr, 0, 0}, 1, p.tn <= 64 ? &tmWq : nullptr);
+    }
     case QT_Q6_K: return gemm_launch_mmq<QT_Q6_K>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
     case QT_Q8_0: return gemm_launch_mmq<QT_Q8_0>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
     case QT_Q4_0: return gemm_launch_mmq<QT_Q4_0>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
@@ -619,7 +644,15 @@ OXB_API int oxb_gemm_grouped(const void* X, int x_rows, const void* W, int qtype
     }
   }
   switch (qtype) {
-    case QT_Q4_K: return gemm_launch_mmq<QT_Q4_K>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
+    case QT_Q4_K: {
+      CUtensorMap tmWq;
+      if (p.tn <= 64) {
+        e = oxb_make_tmap_bytes(&tmWq, W, (uint64_t)groups * N, row_bytes, GEMM_BM, MMQ_SB_BYTES);
+        if (e) return e;
+      }
+      return gemm_launch_mmq<QT_Q4_K>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups,
+                                      p.tn <= 64 ? &tmWq : nullptr);
+    }
     case QT_Q6_K: return gemm_launch_mmq<QT_Q6_K>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
     case QT_Q8_0: return gemm_launch_mmq<QT_Q8_0>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
     case QT_Q4_0: return gemm_launch_mmq<QT_Q4_0>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
