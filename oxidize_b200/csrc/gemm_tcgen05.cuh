@@ -43,18 +43,25 @@ struct GemmTile {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
-// Q4_K weights with decode-sized token tiles are staged through shared memory: one TMA box of
-// 128 rows x 144 bytes (one 256-value super-block of every row of the tile) per four k-blocks, double
-// buffered; the producer warps decode from there.  (Reading the packed rows straight from global memory,
-// one thread per row, makes every warp-wide load touch 32 cache lines.)
-constexpr int MMQ_SB_BYTES = 144;                          // Q4_K super-block
-constexpr int MMQ_PACKED_BYTES = GEMM_BM * MMQ_SB_BYTES;   // 18432
-template <int TN, int QT>
-struct MmqStaged {
-  static constexpr bool value = QT == QT_Q4_K && TN <= 64;
+// Q4_K and Q6_K weights with decode-sized token tiles are staged through shared memory: one TMA box of
+// 128 rows x one 256-value super-block of every row of the tile per four k-blocks, double buffered; the
+// producer warps decode from there.  (Reading the packed rows straight from global memory, one thread per
+// row, makes every warp-wide load touch 32 cache lines.)  A Q6_K super-block is 210 bytes, which TMA cannot
+// address (16-byte rule): its box starts at the 16-byte boundary below the block and is 240 bytes wide, and
+// the decoder starts at the remainder inside the row.  Rows must be 16-byte multiples (QwArgs::staged says
+// whether the host could build the byte map; otherwise the producers read global memory as before).
+template <int QT>
+struct MmqStage {
+  static constexpr int SB = QT == QT_Q4_K ? 144 : QT == QT_Q6_K ? 210 : 0;    // super-block bytes
+  static constexpr int BOX = QT == QT_Q4_K ? 144 : QT == QT_Q6_K ? 240 : 0;   // bytes fetched per row
+  static constexpr int BYTES = GEMM_BM * BOX;
 };
 template <int TN, int QT>
-constexpr int gemm_smem_bytes() { return GemmTile<TN>::SMEM_BYTES + (MmqStaged<TN, QT>::value ? 2 * MMQ_PACKED_BYTES : 0); }
+struct MmqStaged {
+  static constexpr bool value = (QT == QT_Q4_K || QT == QT_Q6_K) && TN <= 64;
+};
+template <int TN, int QT>
+constexpr int gemm_smem_bytes() { return GemmTile<TN>::SMEM_BYTES + (MmqStaged<TN, QT>::value ? 2 * MmqStage<QT>::BYTES : 0); }
 
 // Epilogue modes
 constexpr int EPI_STORE = 0;      // Y = acc (+bias)
@@ -424,14 +431,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         mbar_arrive(&full[st]);
         return true;
       };
-      if constexpr (STAGED) {
+      bool staged_done = false;
+      if constexpr (STAGED) if (qw.staged) {
+        staged_done = true;
+        constexpr int SB = MmqStage<QT>::SB, BOX = MmqStage<QT>::BOX, PBYTES = MmqStage<QT>::BYTES;
         // Packed super-blocks arrive by TMA (tmW maps the packed rows as bytes): thread 192 keeps two
         // boxes in flight, all 128 producers decode their own row out of shared memory.  Weights are
         // static, so none of this waits for the upstream kernel.
         const int sb_begin = kb_begin >> 2, sb_end = (kb_end + 3) >> 2;  // super-blocks touched by [kb_begin, kb_end)
         auto issue = [&](int j) {  // j-th super-block of this CTA -> buffer j & 1
-          mbar_expect_tx(&packed_full[j & 1], MMQ_PACKED_BYTES);
-          tma_load_2d(packed_buf + (j & 1) * MMQ_PACKED_BYTES, &tmW, &packed_full[j & 1], (sb_begin + j) * MMQ_SB_BYTES, w_row0);
+          mbar_expect_tx(&packed_full[j & 1], PBYTES);
+          tma_load_2d(packed_buf + (j & 1) * PBYTES, &tmW, &packed_full[j & 1], ((sb_begin + j) * SB) & ~15, w_row0);
         };
         const int nsb = sb_end - sb_begin;
         if (r == 0) {
@@ -442,7 +452,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         for (int j = 0; j < nsb; ++j) {
           if (alive) alive = mbar_wait_bounded(&packed_full[j & 1], (j >> 1) & 1, abort_flag, OXB_TIMEOUT_TMA_FULL, blockIdx.x);
           if (alive) {
-            const uint8_t* srow = packed_buf + (j & 1) * MMQ_PACKED_BYTES + r * MMQ_SB_BYTES;
+            const uint8_t* srow = packed_buf + (j & 1) * PBYTES + r * BOX + (((sb_begin + j) * SB) & 15);
             const int kb0 = max(kb_begin, (sb_begin + j) * 4), kb1 = min(kb_end, (sb_begin + j) * 4 + 4);
             for (int kb = kb0; kb < kb1 && alive; ++kb) {
               uint32_t v[32];
@@ -454,7 +464,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           asm volatile("bar.sync 2, 128;" ::: "memory");
           if (r == 0 && alive && j + 2 < nsb) issue(j + 2);
         }
-      } else {
+      }
+      if (!staged_done) {
         for (int i = 0; i < nkb; i += 2) {
           uint32_t v0[32], v1[32];
           const bool two = i + 1 < nkb;

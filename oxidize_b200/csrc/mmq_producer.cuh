@@ -22,6 +22,7 @@ struct QwArgs {
   size_t row_bytes;      // bytes per weight row
   const float* scales;   // FP8B only: [N, K/128]
   int scale_ld;          // FP8B only: scales per row
+  int staged;            // Q4_K / Q6_K: tmW is a byte map of the packed rows (shared-memory staging is possible)
 };
 
 __device__ __forceinline__ uint32_t ld_u16(const uint8_t* p) { return *reinterpret_cast<const uint16_t*>(p); }

@@ -192,18 +192,21 @@ OXB_API int oxb_gemm_quant(const void* X, const void* Wq, int qtype, size_t row_
   float* wsf = reinterpret_cast<float*>(ws);
   ArArgs ar;
   memset(&ar, 0, sizeof(ar));
-  QwArgs qw{reinterpret_cast<const uint8_t*>(Wq), row_bytes, scales, scale_ld};
+  QwArgs qw{reinterpret_cast<const uint8_t*>(Wq), row_bytes, scales, scale_ld, 0};
   switch (qtype) {
-    case QT_Q4_K: {
+    case QT_Q4_K:
+    case QT_Q6_K: {
+      // staged path (packed super-blocks by TMA) when the byte map can be built: 16-byte rows and base
       CUtensorMap tmWq;
-      if (p.tn <= 64) {  // staged path: packed super-blocks by TMA
-        e = oxb_make_tmap_bytes(&tmWq, Wq, (uint64_t)N, row_bytes, GEMM_BM, MMQ_SB_BYTES);
-        if (e) return e;
-      }
-      return gemm_launch_mmq<QT_Q4_K>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw,
-                                      GroupArgs{0, 0, 0, 0, nullptr, 0, 0}, 1, p.tn <= 64 ? &tmWq : nullptr);
+      const int box = qtype == QT_Q4_K ? MmqStage<QT_Q4_K>::BOX : MmqStage<QT_Q6_K>::BOX;
+      if (p.tn <= 64 && oxb_make_tmap_bytes(&tmWq, Wq, (uint64_t)N, row_bytes, GEMM_BM, box) == 0) qw.staged = 1;
+      const GroupArgs g0{0, 0, 0, 0, nullptr, 0, 0};
+      if (qtype == QT_Q4_K)
+        return gemm_launch_mmq<QT_Q4_K>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw, g0, 1,
+                                        qw.staged ? &tmWq : nullptr);
+      return gemm_launch_mmq<QT_Q6_K>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw, g0, 1,
+                                      qw.staged ? &tmWq : nullptr);
     }
-    case QT_Q6_K: return gemm_launch_mmq<QT_Q6_K>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
     case QT_Q8_0: return gemm_launch_mmq<QT_Q8_0>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
     case QT_Q4_0: return gemm_launch_mmq<QT_Q4_0>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
     case QT_NVFP4: return gemm_launch_mmq<QT_NVFP4>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
@@ -420,7 +423,7 @@ OXB_API int oxb_gemm_qkv_rope(const void* X, const void* W, int T, int K, const 
   RopeArgs ro{positions, slots, cos_sin, max_pos, rot, pairing, nq, nkv, page, num_blocks, reinterpret_cast<__nv_bfloat16*>(q_out),
               reinterpret_cast<__nv_bfloat16*>(kv_data)};
   __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(q_out);  // only its alignment is looked at
-  const QwArgs qw{nullptr, 0, nullptr, 0};
+  const QwArgs qw{nullptr, 0, nullptr, 0, 0};
   const GroupArgs gr{0, 0, 0, 0, nullptr, 0, 0};
   switch (p.tn) {
     case 16: return gemm_launch<16>(tmW, tmX, y, nullptr, N, T, K, N, p, nullptr, nullptr, EPI_ROPE, ar, stream, qw, gr, 1, ro);
@@ -631,7 +634,7 @@ OXB_API int oxb_gemm_grouped(const void* X, int x_rows, const void* W, int qtype
   ArArgs ar;
   memset(&ar, 0, sizeof(ar));
   GroupArgs gr{1, N, x_rows, y_stride, scale, scale_ld, 0};
-  QwArgs qw{reinterpret_cast<const uint8_t*>(W), row_bytes, nullptr, 0};
+  QwArgs qw{reinterpret_cast<const uint8_t*>(W), row_bytes, nullptr, 0, 0};
   if (qtype == QT_BF16) {
     e = oxb_make_tmap_2d(&tmW, W, (uint64_t)groups * N, K, (uint64_t)K * 2, GEMM_BM, GEMM_BK, 2);
     if (e) return e;
@@ -644,16 +647,17 @@ OXB_API int oxb_gemm_grouped(const void* X, int x_rows, const void* W, int qtype
     }
   }
   switch (qtype) {
-    case QT_Q4_K: {
+    case QT_Q4_K:
+    case QT_Q6_K: {
       CUtensorMap tmWq;
-      if (p.tn <= 64) {
-        e = oxb_make_tmap_bytes(&tmWq, W, (uint64_t)groups * N, row_bytes, GEMM_BM, MMQ_SB_BYTES);
-        if (e) return e;
-      }
-      return gemm_launch_mmq<QT_Q4_K>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups,
-                                      p.tn <= 64 ? &tmWq : nullptr);
+      const int box = qtype == QT_Q4_K ? MmqStage<QT_Q4_K>::BOX : MmqStage<QT_Q6_K>::BOX;
+      if (p.tn <= 64 && oxb_make_tmap_bytes(&tmWq, W, (uint64_t)groups * N, row_bytes, GEMM_BM, box) == 0) qw.staged = 1;
+      if (qtype == QT_Q4_K)
+        return gemm_launch_mmq<QT_Q4_K>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups,
+                                        qw.staged ? &tmWq : nullptr);
+      return gemm_launch_mmq<QT_Q6_K>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups,
+                                      qw.staged ? &tmWq : nullptr);
     }
-    case QT_Q6_K: return gemm_launch_mmq<QT_Q6_K>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
     case QT_Q8_0: return gemm_launch_mmq<QT_Q8_0>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
     case QT_Q4_0: return gemm_launch_mmq<QT_Q4_0>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
     case QT_NVFP4: return gemm_launch_mmq<QT_NVFP4>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);

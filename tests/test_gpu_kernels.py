@@ -268,7 +268,7 @@ def test_model_gpu_matches_cpu(C, tmp_path):
 
 
 @pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q8_0", "Q4_0", "NVFP4", "FP8B"])
-@pytest.mark.parametrize("T,N,K", [(1, 256, 512), (7, 200, 1024), (64, 1280, 2048), (300, 384, 768)])
+@pytest.mark.parametrize("T,N,K", [(1, 256, 512), (7, 200, 1024), (64, 1280, 2048), (300, 384, 768), (16, 520, 4096)])
 def test_linear_packed_weights_fused_dequant(C, qtype, T, N, K):
     """tcgen05 GEMM with in-kernel block decode vs fp32 matmul on the NumPy-decoded weights."""
     from oxidize_b200.models.weights import qtensor_from_dense
