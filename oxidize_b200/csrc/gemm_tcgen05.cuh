@@ -299,7 +299,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) {
-      mbar_init(&full[i], MMQ ? 1 + 128 : 1);  // TMA expect_tx arrival (+ one per producer thread)
+      mbar_init(&full[i], MMQ ? 1 + 4 : 1);  // TMA expect_tx arrival (+ one per producer warp)
       mbar_init(&empty[i], 1);
     }
     mbar_init(accum, 1);
@@ -428,7 +428,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         if (!mbar_wait_bounded(&empty[st], ph ^ 1, abort_flag, OXB_TIMEOUT_TMA_EMPTY, blockIdx.x)) return false;
         store_row_sw128(smem + st * Cfg::STAGE_BYTES, r, v);
         fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
-        mbar_arrive(&full[st]);
+        __syncwarp();              // the warp's 32 rows are written: one arrival per warp instead of 32
+        if (lane == 0) mbar_arrive(&full[st]);
         return true;
       };
       bool staged_done = false;
