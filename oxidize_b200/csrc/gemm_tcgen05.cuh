@@ -425,7 +425,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       auto publish = [&](int i, const uint32_t* v) -> bool {
         const int st = i % STAGES;
         const uint32_t ph = (i / STAGES) & 1;
-        if (!mbar_wait_bounded(&empty[st], ph ^ 1, abort_flag, OXB_TIMEOUT_TMA_EMPTY, blockIdx.x)) return false;
+        // warp-uniform verdict: the warp-level synchronisation below must be reached by all 32 lanes or none
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&empty[st], ph ^ 1, abort_flag, OXB_TIMEOUT_TMA_EMPTY, blockIdx.x)))
+          return false;
         store_row_sw128(smem + st * Cfg::STAGE_BYTES, r, v);
         fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
         __syncwarp();              // the warp's 32 rows are written: one arrival per warp instead of 32
@@ -451,7 +453,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         }
         bool alive = true;
         for (int j = 0; j < nsb; ++j) {
-          if (alive) alive = mbar_wait_bounded(&packed_full[j & 1], (j >> 1) & 1, abort_flag, OXB_TIMEOUT_TMA_FULL, blockIdx.x);
+          if (alive)
+            alive = __all_sync(0xffffffffu, mbar_wait_bounded(&packed_full[j & 1], (j >> 1) & 1, abort_flag,
+                                                              OXB_TIMEOUT_TMA_FULL, blockIdx.x));
           if (alive) {
             const uint8_t* srow = packed_buf + (j & 1) * PBYTES + r * BOX + (((sb_begin + j) * SB) & 15);
             const int kb0 = max(kb_begin, (sb_begin + j) * 4), kb1 = min(kb_end, (sb_begin + j) * 4 + 4);
