@@ -146,7 +146,7 @@ def main():
     total_steps = args.steps * 3 + args.warmup * 3 + 8
     if not args.no_prefill:
         # sequences that finish their prefill early keep decoding while the others are still prefilling
-        total_steps += int(ctx.sum()) // 2048 + B
+        total_steps += int(ctx.sum()) // 1900 + 8
     max_len = int(ctx.max() + total_steps + 16)
     page = 16
     nblocks = int(sum((c + total_steps + page) // page + 1 for c in ctx)) + 8
