@@ -27,9 +27,13 @@ def lib():
     if os.environ.get("OXB_NATIVE_RUNTIME", "1") == "0":
         return None
     try:
-        from ..build import build_runtime
+        from ..build import CSRC, build_runtime
 
-        path = build_runtime()
+        # Load what is there; build only when nothing is (several ranks start at once, and a rebuild
+        # triggered by file times after a copy would have them all write the same file).
+        path = os.path.join(CSRC, "liboxbrt.so")
+        if not os.path.exists(path):
+            path = build_runtime()
         if not path:
             return None
         L = ctypes.CDLL(path)
