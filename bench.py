@@ -64,25 +64,43 @@ class ClockSampler(threading.Thread):
         self.index = index
         self.samples = []
         self.stop_flag = threading.Event()
-        self.max_mhz = None
+        self.begin = 0.0  # samples older than this (nvidia-smi start-up, warm-up) are dropped
+
+    def mark_begin(self):
+        self.begin = time.time()
 
     def run(self):
+        # one nvidia-smi process that prints a line every 100 ms (read-only query), read until told to stop
         q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-        while not self.stop_flag.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-i",
-                                      str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
-                f = [x.strip() for x in out.split(",")]
+        try:
+            proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                                     str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            return
+        self.proc = proc
+        try:
+            for line in proc.stdout:
+                f = [x.strip() for x in line.split(",")]
                 if len(f) >= 6:
-                    self.samples.append((float(f[0]), float(f[1]), f[2], f[3], f[4], f[5]))
+                    try:
+                        self.samples.append((float(f[0]), float(f[1]), f[2], f[3], f[4], f[5], time.time()))
+                    except ValueError:
+                        pass
+                if self.stop_flag.is_set():
+                    break
+        finally:
+            try:
+                proc.terminate()
+                proc.wait(timeout=2)
             except Exception:
                 pass
-            self.stop_flag.wait(0.2)
 
     def summary(self):
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        timed = [s for s in self.samples if s[6] >= self.begin]
+        self.samples = timed or self.samples[-1:]
         mhz = sorted(s[0] for s in self.samples)
         reasons = []
         for name, col in (("hw_slowdown", 2), ("hw_thermal_slowdown", 3), ("sw_thermal_slowdown", 4), ("sw_power_cap", 5)):
@@ -205,10 +223,13 @@ def main():
         torch.cuda.synchronize()
 
     # ---- e2e: K steps through the public API (scheduler + H2D + forward + sample + D2H)
+    sampler = ClockSampler(local)  # started now so that nvidia-smi is up when the timed regions begin
+    sampler.start()
     for _ in range(args.warmup):
         llm.step()
     st0 = dict(llm.stats)
     barrier()
+    sampler.mark_begin()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     w0 = time.perf_counter()
     e0.record()
@@ -228,11 +249,9 @@ def main():
     Bk = _bucket(B)
     graph = llm.runner.graphs.get(Bk)
     launches_per_step = getattr(llm.runner, "launches_per_step", {}).get(Bk, 0)
-    sampler = ClockSampler(local)
     for _ in range(args.warmup):
         llm.step()
     barrier()
-    sampler.start()
     k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     k0.record()
     if graph is not None:
