@@ -111,6 +111,7 @@ class ModelRunner:
         max_len = 0
         rows: List[Tuple[ScheduledSeq, int, int]] = []  # (ss, first logits row, n rows)
         qs[0] = 0
+        self._bt_owner = [None] * b.max_seqs  # this path rewrites block-table rows: the decode path's record is void
         for i, ss in enumerate(scheduled):
             seq = ss.seq
             n = ss.num_tokens
@@ -176,15 +177,77 @@ class ModelRunner:
             B = pad_to
         return t, B, nl, max_q, max_len, rows
 
+    def build_decode(self, scheduled: Sequence[ScheduledSeq], pad_to: Optional[int] = None):
+        """``build`` for the steady state: every sequence feeds exactly one decode row.  Whole-column
+        writes instead of per-row scalar stores, and a block-table row is rewritten only when its
+        sequence or that sequence's block list changed since the previous step."""
+        b = self.buf
+        n = len(scheduled)
+        if n > b.max_tokens or n > b.max_seqs:
+            raise RuntimeError("scheduled batch exceeds runner capacity")
+        tok, pos, slot = b.h("token_ids"), b.h("positions"), b.h("slot_mapping")
+        qs, sl, li, bt = b.h("query_start"), b.h("seq_lens"), b.h("logits_indices"), b.h("block_tables")
+        M, ps = self.max_blocks, self.page
+        owner = getattr(self, "_bt_owner", None)
+        if owner is None or len(owner) != b.max_seqs:
+            owner = self._bt_owner = [None] * b.max_seqs
+        ar = getattr(self, "_arange", None)
+        if ar is None:
+            ar = self._arange = np.arange(max(b.max_seqs, b.max_tokens) + 1, dtype=np.int32)
+        seqs = [ss.seq for ss in scheduled]
+        starts = [ss.start for ss in scheduled]
+        for i, seq in enumerate(seqs):
+            bl = seq.blocks
+            nb = len(bl)
+            key = (seq.seq_id, id(bl), nb, bl[-1] if nb else -1)
+            if owner[i] != key:
+                bt[i * M : i * M + nb] = bl
+                owner[i] = key
+        tok[:n] = [seq.token_at(st) for seq, st in zip(seqs, starts)]
+        pos[:n] = starts
+        slot[:n] = [seq.blocks[st // ps] * ps + st % ps for seq, st in zip(seqs, starts)]
+        np.add(pos[:n], 1, out=sl[:n])
+        qs[: n + 1] = ar[: n + 1]
+        if all(ss.sample for ss in scheduled):
+            rows = [(ss, i, 1) for i, ss in enumerate(scheduled)]
+            nl = n
+            li[:n] = ar[:n]
+        else:
+            rows, nl = [], 0
+            for i, ss in enumerate(scheduled):
+                if ss.sample:
+                    li[nl] = i
+                    rows.append((ss, nl, 1))
+                    nl += 1
+        t, B = n, n
+        max_len = max(starts) + 1
+        if pad_to is not None and pad_to > B:
+            # dummy sequences: zero context, no KV write; their logits rows are ignored
+            k = pad_to - B
+            tok[t : t + k] = 0
+            pos[t : t + k] = 0
+            slot[t : t + k] = -1
+            sl[B:pad_to] = 0
+            qs[B + 1 : pad_to + 1] = ar[t + 1 : t + k + 1]
+            li[nl : nl + k] = ar[t : t + k]
+            nl += k
+            t += k
+            B = pad_to
+        return t, B, nl, 1, max_len, rows
+
     def _fill_sampling(self, rows, n_logits: int) -> bool:
         """Per-logits-row sampling knobs; returns True when every row is greedy."""
         b = self.buf
         temp, tp, mp, rnd, tk = b.h("temperature"), b.h("top_p"), b.h("min_p"), b.h("random"), b.h("top_k")
         all_greedy = True
         temp[:n_logits] = 0.0
+        greedy: Dict[int, bool] = {}  # many requests share one params object
         for ss, r0, k in rows:
             p: SamplingParams = ss.seq.params
-            if p.is_greedy:
+            g = greedy.get(id(p))
+            if g is None:
+                g = greedy[id(p)] = p.is_greedy
+            if g:
                 continue
             all_greedy = False
             for j in range(r0, r0 + k):
@@ -228,9 +291,10 @@ class ModelRunner:
         pad_to = _bucket(len(scheduled)) if graphable else None
         if pad_to is not None and pad_to > self.buf.max_seqs:
             pad_to, graphable = None, False
-        T, B, nl, max_q, max_len, rows = self.build(scheduled, pad_to)
+        T, B, nl, max_q, max_len, rows = (self.build_decode if decode_only else self.build)(scheduled, pad_to)
         self.last_rows = rows
-        host_rows = [r for r in rows if r[0].seq.params.needs_host_sampler]
+        on_host = {id(p): p.needs_host_sampler for p in {id(r[0].seq.params): r[0].seq.params for r in rows}.values()}
+        host_rows = [r for r in rows if on_host[id(r[0].seq.params)]] if any(on_host.values()) else []
         needs_host_logits = needs_host_logits or bool(host_rows)
         graphable = graphable and not host_rows
         all_greedy = self._fill_sampling(rows, nl)
@@ -249,9 +313,8 @@ class ModelRunner:
             host = self.out_host[:n_out].numpy()
         else:
             host = toks.numpy()
-        result: Dict[int, List[int]] = {}
-        for ss, r0, k in rows:
-            result[ss.seq.seq_id] = [int(x) for x in host[r0 : r0 + k]]
+        hl = host.tolist()
+        result: Dict[int, List[int]] = {ss.seq.seq_id: hl[r0 : r0 + k] for ss, r0, k in rows}
         if host_rows:
             self._host_sample(host_rows, logits, result)
         return StepResult(result, logits if (needs_host_logits or self.keep_logits) else None, h2d, n_out * 4)

@@ -179,9 +179,14 @@ class Scheduler:
         ps = self.pool.page_size
         need = (upto_tokens + ps - 1) // ps
         fresh = need - len(seq.blocks)
-        # copy-on-write: the block that receives this step's first write may be shared
+        # copy-on-write: the block that receives this step's first write may be shared.  Blocks are
+        # shared only through the prefix cache, i.e. among the first ``_published`` blocks of a sequence
+        # (those it matched at admission or published itself), so later blocks need no pool query.
         first_write_block = seq.num_computed // ps
-        cow = (first_write_block < len(seq.blocks) and self.pool.is_shared(seq.blocks[first_write_block]))
+        cow = (first_write_block < seq._published and first_write_block < len(seq.blocks)
+               and self.pool.is_shared(seq.blocks[first_write_block]))
+        if fresh <= 0 and not cow:
+            return True
         if not self.pool.can_allocate(max(fresh, 0) + (1 if cow else 0)):
             return False
         if cow:
@@ -225,13 +230,22 @@ class Scheduler:
         budget = cfg.max_num_batched_tokens
 
         # Phase 1: decode for fully-prefilled running sequences (highest priority)
+        RUNNING = SeqStatus.RUNNING
+        partial = False  # some running sequence is still in prefill
         for seq in list(self.running):
-            if seq not in self.running or seq.remaining_prefill > 0:
+            # (a sequence preempted earlier in this loop is WAITING again)
+            if seq.status is not RUNNING:
                 continue
-            n = 1 + len(seq.draft_tokens)
+            if not seq.output and seq.num_computed < len(seq.prompt):  # remaining_prefill > 0
+                partial = True
+                continue
+            nd = len(seq.draft_tokens)
+            n = 1 + nd
             if budget < n:
+                partial = True  # the rest of the list was not looked at
                 break
-            while not self._ensure_blocks(seq, seq.num_tokens + len(seq.draft_tokens), out):
+            ntok = len(seq.prompt) + len(seq.output)
+            while not self._ensure_blocks(seq, ntok + nd, out):
                 victim = self._pick_victim(exclude=seq)
                 if victim is None:
                     break
@@ -239,7 +253,7 @@ class Scheduler:
                 out.preempted.append(victim)
                 out.scheduled = [s for s in out.scheduled if s.seq is not victim]
             else:
-                out.scheduled.append(ScheduledSeq(seq, seq.num_tokens - 1, n, False, True))
+                out.scheduled.append(ScheduledSeq(seq, ntok - 1, n, False, True))
                 budget -= n
                 out.num_decode_tokens += n
                 continue
@@ -248,8 +262,8 @@ class Scheduler:
             out.preempted.append(seq)
 
         # Phase 2: continue partial prefills
-        for seq in list(self.running):
-            if seq not in self.running or seq.remaining_prefill == 0:
+        for seq in (list(self.running) if partial else ()):
+            if seq.status is not RUNNING or seq.remaining_prefill == 0:
                 continue
             chunk = min(seq.remaining_prefill, cfg.prefill_chunk_size, budget)
             if chunk <= 0:
@@ -304,18 +318,23 @@ class Scheduler:
         for it this step (one, or several after a speculative verify).  Returns the sequences
         that finished."""
         done: List[Sequence] = []
+        ps = self.pool.page_size
+        publish = self.config.enable_prefix_cache
+        FINISHED = SeqStatus.FINISHED
         for ss in out.scheduled:
             seq = ss.seq
-            if seq.is_finished:
+            if seq.status is FINISHED:
                 continue
             toks = new_tokens.get(seq.seq_id, [])
             if ss.is_prefill:
                 seq.num_computed += ss.num_tokens
             else:
                 # rows fed: last token + drafts; accepted drafts = len(toks)-1
-                seq.num_computed = seq.num_tokens - 1 + max(len(toks), 1)
-            seq.draft_tokens = []
-            self._publish_full_blocks(seq)
+                seq.num_computed = len(seq.prompt) + len(seq.output) - 1 + max(len(toks), 1)
+            if seq.draft_tokens:
+                seq.draft_tokens = []
+            if publish and seq._published < len(seq.prompt) // ps:
+                self._publish_full_blocks(seq)
             if not ss.sample:
                 continue
             for t in toks:
@@ -328,8 +347,8 @@ class Scheduler:
                     self._finish(seq, reason)
                     done.append(seq)
                     break
-            if not seq.is_finished:
-                self._trim_blocks(seq)
+            if seq.status is not FINISHED and (len(seq.blocks) - 1) * ps >= len(seq.prompt) + len(seq.output):
+                self._trim_blocks(seq)  # more pages than the tokens need (speculative rows that were rejected)
         return done
 
     def _trim_blocks(self, seq: Sequence) -> None:
