@@ -286,7 +286,9 @@ class ModelRunner:
             return StepResult({})
         for src, dst in out.cow_copies:
             self.kv.copy_block(src, dst)
-        decode_only = all((not s.is_prefill) and s.num_tokens == 1 for s in scheduled)
+        # the scheduler's own counts settle the common case without a scan of the rows
+        decode_only = ((out.num_prefill_tokens == 0 and out.num_decode_tokens == len(scheduled))
+                       or all((not s.is_prefill) and s.num_tokens == 1 for s in scheduled))
         graphable = self.use_graphs and decode_only and not needs_host_logits and not self.keep_logits
         pad_to = _bucket(len(scheduled)) if graphable else None
         if pad_to is not None and pad_to > self.buf.max_seqs:

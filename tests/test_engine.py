@@ -548,3 +548,47 @@ def test_beam_search_finds_the_best_sequence(tmp_path):
     greedy = llm.generate([[1, 2, 3, 4]], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))[0].token_ids
     one = llm.beam_search([1, 2, 3, 4], beam_width=1, max_tokens=4)
     assert one[0][0][: len(greedy)] == greedy[: len(one[0][0])]
+
+
+def test_decode_builder_writes_the_same_batch_as_the_general_builder(tmp_path):
+    import numpy as np
+
+    from oxidize_b200.engine.sampler import SamplingParams
+
+    llm = _tiny_llm(tmp_path)
+    rng = np.random.default_rng(3)
+    for n, mt in ((5, 40), (21, 3), (33, 40), (16, 40), (9, 6)):
+        llm.add_request(rng.integers(3, 64, size=n).tolist(), SamplingParams(temperature=0.0, max_tokens=mt, ignore_eos=True))
+    names = ("token_ids", "positions", "slot_mapping", "query_start", "seq_lens", "logits_indices", "block_tables")
+    r = llm.runner
+    checked = 0
+    sizes = set()
+    for _ in range(30):
+        out = llm.scheduler.schedule()
+        sch = out.scheduled
+        if sch and all((not s.is_prefill) and s.num_tokens == 1 for s in sch):
+            for pad in (None, 8):
+                a = r.build(sch, pad)
+                want = {k: r.buf.h(k).copy() for k in names}
+                b = r.build_decode(sch, pad)  # also exercises the row-ownership record right after build() voided it
+                b2 = r.build_decode(sch, pad)  # ... and with the record in place
+                assert a[:5] == b[:5] == b2[:5]
+                assert [(x[0].seq.seq_id, x[1], x[2]) for x in a[5]] == [(x[0].seq.seq_id, x[1], x[2]) for x in b[5]]
+                T, B, nl = a[0], a[1], a[2]
+                M = r.max_blocks
+                for k in names:
+                    got = r.buf.h(k)
+                    if k == "block_tables":
+                        for i, s in enumerate(sch):
+                            nb = len(s.seq.blocks)
+                            assert np.array_equal(got[i * M : i * M + nb], want[k][i * M : i * M + nb])
+                    else:
+                        n = {"token_ids": T, "positions": T, "slot_mapping": T, "query_start": B + 1, "seq_lens": B,
+                             "logits_indices": nl}[k]
+                        assert np.array_equal(got[:n], want[k][:n]), k
+                checked += 1
+            sizes.add(len(sch))
+        # let the step run for real so sequences grow, finish and shift rows
+        res = r.execute(out)
+        llm.scheduler.postprocess(out, res.tokens, None, 0.0)
+    assert checked >= 10 and len(sizes) >= 2  # rows moved to other sequences at least once
