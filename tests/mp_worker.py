@@ -84,7 +84,8 @@ def case_gemm_ar(dev, comm_kind):
 def _tiny_file(rank):
     path = os.path.join(tempfile.gettempdir(), f"oxb_tp_tiny_{os.environ.get('MASTER_PORT', '0')}.gguf")
     if rank == 0:
-        cfg = preset("tiny-llama", n_layers=2, vocab_size=512, n_heads=8, n_kv_heads=2)
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        cfg = preset("tiny-llama", n_layers=2, vocab_size=512, n_heads=8, n_kv_heads=max(2, min(world, 8)))
         synth_gguf(path, cfg, "BF16", seed=0, norm_jitter=0.1)
     dist.barrier()
     return path

@@ -1,4 +1,4 @@
-"""Multi-process tensor parallelism and failure detection on CPU ranks (gloo, world 2)."""
+"""Multi-process tensor parallelism and failure detection on CPU ranks (gloo, world 2 and 4)."""
 import os
 import socket
 import subprocess
@@ -35,6 +35,12 @@ def test_tp2_logits_match_tp1_on_cpu():
     r = run_ranks("tp_model")
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("OK tp_model") == 2
+
+
+def test_tp4_logits_match_tp1_on_cpu():
+    r = run_ranks("tp_model", n=4)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("OK tp_model") == 4
 
 
 def test_ep2_moe_logits_match_single_rank_on_cpu():
