@@ -111,14 +111,11 @@ class ClockSampler(threading.Thread):
 
 
 def reference_arm(args):
-    # The reference (a Rust workspace plus C / C++ / Go / Python ports) has no installable Python
-    # package at its root and no multi-GPU or batched-GPU decode path, so the 70B TP bs64 metric
-    # cannot be produced by it.
-    why = ("reference not installable offline (pip: neither setup.py nor pyproject.toml at its root; Rust crates "
-           "need cargo) and it has no multi-GPU / batched GPU decode path for this metric")
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why}))
-    return 0
+    """The unmodified reference engine through its own CLI (see baseline/reference_arm.py)."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as ra
+
+    return ra.main(args)
 
 
 def main():

@@ -43,7 +43,7 @@ class EngineConfig:
     enable_prefix_cache: bool = True
     cuda_graphs: bool = True
     tp_size: int = 1
-    ep_size: int = 1
+    ep_size: int = 0  # experts partitioned over this many ranks; 0 = tp_size, 1 = replicated on every rank
     pp_size: int = 1
     fused_comm: bool = True
     eos_token_id: Optional[int] = None
@@ -101,7 +101,12 @@ class LLM:
             cfg.rope_pairing = rope_pairing
         device = torch.device(device if device is not None else ("cuda" if torch.cuda.is_available() else "cpu"))
         act = torch.bfloat16 if device.type == "cuda" else torch.float32
-        w = load_weights(g, cfg, device, act, tp_rank, config.tp_size, ep_rank, config.ep_size)
+        ep_size = config.ep_size or config.tp_size
+        if ep_size == config.tp_size and ep_rank == 0:
+            ep_rank = tp_rank  # the expert partition follows the tensor-parallel rank
+        if ep_size == 1:
+            ep_rank = 0
+        w = load_weights(g, cfg, device, act, tp_rank, config.tp_size, ep_rank, ep_size)
         try:
             tok = load_tokenizer_from_metadata(g.metadata)
         except TokenizerError:

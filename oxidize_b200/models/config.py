@@ -15,9 +15,25 @@ from typing import Any, Dict, List, Optional
 from ..formats.gguf import GGUFFile
 
 # architecture strings accepted (reference arch-string map inference.rs:62-96)
-DENSE_ARCHS = {"llama", "mistral", "qwen2", "qwen3", "gemma", "phi3", "deepseek"}
-MOE_ARCHS = {"mixtral", "qwen2moe", "qwen3moe", "deepseek2", "deepseek-moe", "deepseek_moe", "llama4"}
-QWEN_ARCHS = {"qwen", "qwen2", "qwen2moe", "qwen35", "qwen3", "qwen3moe", "qwen3_5_moe"}
+DENSE_ARCHS = {"llama", "mistral", "qwen2", "qwen3", "deepseek"}
+MOE_ARCHS = {"mixtral", "qwen2moe", "qwen3moe", "deepseek2", "deepseek-moe", "deepseek_moe"}
+# Architectures whose layers need math this engine does not have (GeGLU and embedding scaling, sandwich
+# norms, fused qkv with partial windows, recurrent or convolutional mixers): loading one would run it as
+# a plain Llama and produce wrong tokens, so they are refused by name.
+UNSUPPORTED_ARCHS = {"gemma", "gemma2", "gemma3", "gemma4", "phi3", "phi", "llama4", "qwen35", "qwen3_5_moe", "mamba",
+                     "lfm2", "glm4", "falcon", "gpt2", "bert"}
+
+
+class UnsupportedArchitecture(ValueError):
+    pass
+
+
+def check_architecture(arch: str) -> None:
+    if arch in DENSE_ARCHS or arch in MOE_ARCHS:
+        return
+    if arch in UNSUPPORTED_ARCHS:
+        raise UnsupportedArchitecture(f"architecture {arch!r} needs layer semantics this engine does not implement")
+    raise UnsupportedArchitecture(f"unknown architecture {arch!r}; supported: {sorted(DENSE_ARCHS | MOE_ARCHS)}")
 
 
 @dataclass
@@ -115,6 +131,10 @@ def _scalar(v, default):
 
 def config_from_gguf(g: GGUFFile) -> ModelConfig:
     arch = g.architecture
+    check_architecture(arch)
+    if any(g.has_tensor(f"blk.{i}.attn_kv_a_mqa.weight") for i in (0, 1)):
+        raise UnsupportedArchitecture("multi-head latent attention (attn_kv_a_mqa / attn_kv_b tensors) is not implemented; "
+                                      "only the grouped-query DeepSeek-MoE variants load")
     a = g.arch_get
     c = ModelConfig(arch=arch, name=str(g.get("general.name", "")))
     emb = g.tensors.get("token_embd.weight")

@@ -89,6 +89,14 @@ class Transformer:
         self.act_dtype = act_dtype or (torch.bfloat16 if dev.type == "cuda" else torch.float32)
         cfg = self.cfg
         tp = weights.tp_size
+        group = getattr(self.comm, "size", 1)
+        if tp != group:
+            raise ValueError(f"weights are sharded {tp}-way (tp_size) but the communication group has {group} ranks")
+        if cfg.is_moe and weights.ep_size not in (1, group):
+            raise ValueError(f"expert parallelism must span the whole group: ep_size={weights.ep_size}, group size={group} "
+                             "(use ep_size=1 to replicate the experts)")
+        if cfg.is_moe and weights.ep_size > 1 and weights.ep_rank != getattr(self.comm, "rank", 0):
+            raise ValueError(f"ep_rank={weights.ep_rank} does not match this rank ({getattr(self.comm, 'rank', 0)})")
         self.n_heads_local = cfg.n_heads // tp
         self.n_kv_local = max(1, cfg.n_kv_heads // tp)
         self.rope = RopeState(
@@ -169,26 +177,34 @@ class Transformer:
             return ops.linear(x, w)
 
     def _moe_ffn(self, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
-        """Experts are partitioned across ranks (EP); tokens are replicated after the
-        attention all-reduce, so each rank runs its local experts on the rows routed to
-        them and the combine is the weighted sum + all-reduce."""
+        """Routed experts + optional shared expert.
+
+        With expert parallelism (``ep_size`` = group size) the experts are partitioned across ranks;
+        tokens are replicated after the attention all-reduce, so each rank runs its local experts on
+        the rows routed to them and the combine is the weighted sum + all-reduce (the shared expert,
+        sharded by ``tp_rank``, rides in the same all-reduce).  With ``ep_size`` = 1 every rank holds
+        all experts and computes the whole routed sum itself; only the tensor-parallel shared expert
+        is all-reduced.  Any other combination is rejected when the model is built."""
         cfg = self.cfg
         logits = ops.linear(x, lw.router).float()
+        ep_sharded = self.w.ep_size > 1
         sh = None
         if lw.shared_gate_up is not None:
             sh = ops.linear(ops.silu_mul(ops.linear(x, lw.shared_gate_up)), lw.shared_down)
+            if not ep_sharded and self.w.tp_size > 1:
+                sh = self.comm.all_reduce(sh)
             if lw.shared_gate is not None:
                 sh = (sh.float() * torch.sigmoid(ops.linear(x, lw.shared_gate).float())).to(sh.dtype)
         if x.is_cuda:
             from ..ops import cuda_moe
 
             out = cuda_moe.moe_layer(x, logits, cfg, lw.router_bias, lw.experts, sh)
-            return self.comm.all_reduce(out)
+            return self.comm.all_reduce(out) if ep_sharded else out
         ids, wts = ops.moe_route(logits, cfg, lw.router_bias)
         out = moe_experts_forward(x, ids, wts, lw.experts)
         if sh is not None:
             out = out + sh
-        return self.comm.all_reduce(out)
+        return self.comm.all_reduce(out) if ep_sharded else out
 
     def run_layers(self, h: torch.Tensor, residual: Optional[torch.Tensor], meta: BatchMeta, kv,
                    layers: Optional[Tuple[int, int]] = None, capture: Optional[dict] = None):

@@ -122,10 +122,22 @@ def write_config_metadata(w: GGUFWriter, cfg: ModelConfig) -> None:
 
 
 def synth_gguf(path: str, cfg: ModelConfig, quant: str = "Q4_K_M", seed: int = 0, tokenizer: bool = True,
-               norm_jitter: float = 0.0) -> str:
+               norm_jitter: float = 0.0, device=None, embed_type: Optional[str] = None) -> str:
     """Write a random-init GGUF of shape ``cfg``; matrices N(0, 0.02) encoded per ``quant``
-    (``Q4_K_M`` = llama.cpp-style Q4_K/Q6_K mix), norms f32 ones."""
+    (``Q4_K_M`` = llama.cpp-style Q4_K/Q6_K mix), norms f32 ones.
+
+    With ``device`` (a CUDA device) the matrices are drawn and block-encoded there with the torch
+    encoders and only the packed bytes cross to the host, which turns the minutes a NumPy encode of a
+    multi-billion-parameter shape takes into the time of the file write.  ``embed_type`` stores the
+    token-embedding table in another type than ``quant`` picks (the reference's CUDA backend has no row
+    lookup for a bf16 / f16 table: ``oxidize-c/src/backends/cuda.cu`` ``cuda_embed`` hands every "packed"
+    table to ``oc_cuda_mmq_get_row``, which knows the block-quantized types only)."""
     rng = np.random.default_rng(seed)
+    dev = torch.device(device) if device is not None else None
+    tgen = None
+    if dev is not None:
+        tgen = torch.Generator(device=dev)
+        tgen.manual_seed(seed)
     w = GGUFWriter(path, arch=cfg.arch)
     write_config_metadata(w, cfg)
     if tokenizer:
@@ -135,11 +147,16 @@ def synth_gguf(path: str, cfg: ModelConfig, quant: str = "Q4_K_M", seed: int = 0
 
     def mat(gname: str, kind: str, layer: int, out_f: int, in_f: int, n_exp: int = 0):
         t = pick_type(quant, kind, layer, L, in_f)
+        if kind == "token_embd" and embed_type:
+            t = embed_type.upper()
         shape = (n_exp, out_f, in_f) if n_exp else (out_f, in_f)
         n = int(np.prod(shape))
         sd = int(rng.integers(0, 2**63 - 1))
 
-        def gen(n=n, sd=sd, t=t):
+        def gen(n=n, sd=sd, t=t, in_f=in_f):
+            if dev is not None and t in ("BF16", "F16", "F32", "Q8_0", "Q4_K", "Q6_K", "NVFP4"):
+                q = _rand_matrix(n // in_f, in_f, t, dev, tgen).data
+                return q.contiguous().view(torch.uint8).reshape(-1).cpu().numpy()
             x = np.random.default_rng(sd).standard_normal(n, dtype=np.float32) * WEIGHT_STD
             return qref.quantize(t, x)
 
@@ -268,3 +285,35 @@ def synth_weights(cfg: ModelConfig, device, quant: str = "BF16", seed: int = 0, 
     else:
         head = _rand_matrix(v1 - v0, h, pick_type(quant, "output", 0, L, h), device, own)
     return ModelWeights(cfg, embed, layers, ones(h), LinearWeight([head]), [], tp_rank, tp_size, ep_rank, ep_size, l0, v0)
+
+
+def _main(argv=None) -> int:
+    """``python -m oxidize_b200.utils.synth --preset llama3-8b --quant Q4_K_M --out model.gguf``"""
+    import argparse
+
+    from ..models.config import preset, preset_names
+
+    ap = argparse.ArgumentParser(description="write a random-init GGUF of a named shape")
+    ap.add_argument("--preset", required=True, choices=preset_names())
+    ap.add_argument("--quant", default="Q4_K_M")
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count")
+    ap.add_argument("--context", type=int, default=0, help="override the advertised context length")
+    ap.add_argument("--embed-type", default=None, help="store the token embedding table in this type")
+    ap.add_argument("--device", default="auto", help="cuda device used to draw and encode the weights; 'cpu' = NumPy")
+    a = ap.parse_args(argv)
+    cfg = preset(a.preset)
+    if a.layers:
+        cfg.n_layers = a.layers
+    if a.context:
+        cfg.context_length = a.context
+    dev = a.device
+    if dev == "auto":
+        dev = "cuda" if torch.cuda.is_available() else "cpu"
+    synth_gguf(a.out, cfg, a.quant, seed=a.seed, device=None if dev == "cpu" else dev, embed_type=a.embed_type)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(_main())

@@ -131,7 +131,12 @@ def case_tp_model(dev, comm_kind):
             assert comm.fused_calls > 0
 
 
-def case_ep_model(dev, comm_kind):
+def case_ep1_model(dev, comm_kind):
+    """Tensor parallelism with every expert replicated on every rank (ep_size = 1) == single rank."""
+    return case_ep_model(dev, comm_kind, replicate_experts=True)
+
+
+def case_ep_model(dev, comm_kind, replicate_experts=False):
     """Expert parallelism (experts split over the ranks, attention tensor-parallel) == single rank."""
     layout = init_distributed()
     path = os.path.join(tempfile.gettempdir(), f"oxb_ep_tiny_{os.environ.get('MASTER_PORT', '0')}.gguf")
@@ -139,7 +144,8 @@ def case_ep_model(dev, comm_kind):
         big = dev.type == "cuda"  # the GPU attention kernels take head_dim 64 / 128
         cfg = preset("mixtral-8x7b", hidden_size=256 if big else 128, n_layers=2, n_heads=4, n_kv_heads=2,
                      head_dim=64 if big else 32, ffn_size=512 if big else 256, expert_ffn_size=128 if big else 64,
-                     vocab_size=256, n_experts=4, n_experts_used=2)
+                     vocab_size=256, n_experts=4, n_experts_used=2, n_shared_experts=1 if replicate_experts else 0,
+                     shared_expert_ffn_size=(128 if big else 64) if replicate_experts else 0)
         synth_gguf(path, cfg, "BF16", seed=2, norm_jitter=0.1)
     dist.barrier()
     g = load_gguf(path)
@@ -149,10 +155,14 @@ def case_ep_model(dev, comm_kind):
               cuda_graphs=False)
     comm = make_comm(comm_kind, dev) if dev.type == "cuda" else TorchComm()
     W = layout.world_size
-    w_ep = load_weights(g, cfg, dev, act, layout.rank, W, layout.rank, W)
-    assert len(w_ep.layers[0].experts.gate_up) == cfg.n_experts // W
+    if replicate_experts:
+        w_ep = load_weights(g, cfg, dev, act, layout.rank, W, 0, 1)
+        assert len(w_ep.layers[0].experts.gate_up) == cfg.n_experts and w_ep.layers[0].shared_gate_up is not None
+    else:
+        w_ep = load_weights(g, cfg, dev, act, layout.rank, W, layout.rank, W)
+        assert len(w_ep.layers[0].experts.gate_up) == cfg.n_experts // W
     w_1 = load_weights(g, cfg, dev, act, 0, 1)
-    ep = LLM(w_ep, EngineConfig(tp_size=W, ep_size=W, **ec), comm)
+    ep = LLM(w_ep, EngineConfig(tp_size=W, ep_size=1 if replicate_experts else W, **ec), comm)
     one = LLM(w_1, EngineConfig(**ec))
     ep.runner.keep_logits = one.runner.keep_logits = True
     # one sampled token: the logits of the prompt are compared; with more, a near-tie in bf16 may pick
@@ -266,7 +276,7 @@ def case_rank_exit(dev, comm_kind):
     hb.stop()
 
 
-CASES = {"gemm_ar": case_gemm_ar, "tp_model": case_tp_model, "tp_graph": case_tp_graph, "rank_exit": case_rank_exit, "ep_model": case_ep_model, "pp_model": case_pp_model}
+CASES = {"gemm_ar": case_gemm_ar, "tp_model": case_tp_model, "tp_graph": case_tp_graph, "rank_exit": case_rank_exit, "ep_model": case_ep_model, "ep1_model": case_ep1_model, "pp_model": case_pp_model}
 
 
 def main():

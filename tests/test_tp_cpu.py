@@ -49,6 +49,26 @@ def test_ep2_moe_logits_match_single_rank_on_cpu():
     assert r.stdout.count("OK ep_model") == 2
 
 
+def test_tp2_with_replicated_experts_matches_single_rank_on_cpu():
+    r = run_ranks("ep1_model")
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("OK ep1_model") == 2
+
+
+def test_mismatched_expert_partition_is_rejected():
+    import torch
+
+    from oxidize_b200.models.config import preset
+    from oxidize_b200.models.transformer import Transformer
+    from oxidize_b200.utils.synth import synth_weights
+
+    cfg = preset("mixtral-8x7b", hidden_size=64, n_layers=1, n_heads=2, n_kv_heads=2, head_dim=32, ffn_size=64,
+                 expert_ffn_size=32, vocab_size=64, n_experts=4, n_experts_used=2)
+    w = synth_weights(cfg, torch.device("cpu"), "F32", ep_rank=0, ep_size=2)
+    with pytest.raises(ValueError, match="expert parallelism must span the whole group"):
+        Transformer(w)
+
+
 def test_pp2_tokens_match_single_process_on_cpu():
     r = run_ranks("pp_model")
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
