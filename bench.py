@@ -53,6 +53,10 @@ def parse_args():
                          "collectives (marks the result invalid); used to profile per-GPU kernels of the TP8 config")
     ap.add_argument("--no-prefill", action="store_true",
                     help="fill the KV cache with random pages instead of running the prompts through prefill")
+    ap.add_argument("--no-workload", action="store_true",
+                    help="skip the whole-workload run (all requests from arrival to their last token)")
+    ap.add_argument("--sync-decode", action="store_true", help="do not keep a decode step in flight ahead of the host")
+    ap.add_argument("--no-fold-norms", action="store_true", help="keep RMSNorm as stand-alone kernels (A/B measurement)")
     return ap.parse_args()
 
 
@@ -162,9 +166,10 @@ def main():
     if not args.no_prefill:
         # sequences that finish their prefill early keep decoding while the others are still prefilling
         total_steps += int(ctx.sum()) // 1900 + 8
-    max_len = int(ctx.max() + total_steps + 16)
+    max_len = int(max(ctx.max() + total_steps, args.prompt_max + args.out_tokens) + 16)
     page = 16
     nblocks = int(sum((c + total_steps + page) // page + 1 for c in ctx)) + 8
+    nblocks_workload = int(sum((p + args.out_tokens + page) // page + 1 for p in prompt_lens)) + 8
 
     t0 = time.time()
     comm = None
@@ -176,12 +181,60 @@ def main():
         else:
             comm = TorchComm()
     weights = synth_weights(cfg, dev, args.quant, seed=0, tp_rank=rank, tp_size=world, ep_rank=rank, ep_size=world)
+    # The whole-workload run needs KV for every request's prompt and all of its output tokens at once; it is run only
+    # where that fits beside the weights (it does not beside 141 GB of bf16 weights on a single GPU).
+    run_workload = not (args.no_workload or args.no_prefill or args.shard_sim or args.layers)
+    if run_workload and nblocks_workload > nblocks:
+        kvh = max(1, cfg.n_kv_heads // world)
+        bpe = {"bf16": 2, "f16": 2, "f32": 4, "q8": 1.125, "q4": 0.625}.get(args.kv_dtype, 2)
+        extra = (nblocks_workload - nblocks) * page * kvh * cfg.head_dim * 2 * bpe * cfg.n_layers
+        need_now = nblocks * page * kvh * cfg.head_dim * 2 * bpe * cfg.n_layers
+        free_b, _ = torch.cuda.mem_get_info(dev)
+        fits = torch.tensor([1 if free_b > need_now + extra + (8 << 30) else 0], device=dev)
+        if world > 1:
+            dist.all_reduce(fits, op=dist.ReduceOp.MIN)
+        if int(fits.item()):
+            nblocks = nblocks_workload
+        else:
+            run_workload = False
     ec = EngineConfig(kv_cache_dtype=args.kv_dtype, kv_page_size=page, num_kv_blocks=nblocks, max_model_len=max_len,
                       max_num_seqs=B, max_num_batched_tokens=max(B, 2048 if not args.no_prefill else B),
-                      prefill_chunk_size=512, enable_prefix_cache=False, tp_size=world, ep_size=world)
+                      prefill_chunk_size=512, enable_prefix_cache=False, tp_size=world, ep_size=world,
+                      fold_norms=not args.no_fold_norms, async_decode=not args.sync_decode)
     llm = LLM(weights, ec, comm)
     torch.cuda.synchronize()
     load_s = time.time() - t0
+
+    # ---- the whole workload: every request from its arrival (all at t = 0) to its last output token
+    workload = None
+    if run_workload:
+        wsp = SamplingParams(temperature=0.0, max_tokens=args.out_tokens, ignore_eos=True)
+        wrng = np.random.default_rng(1)
+        for i in range(B):
+            llm.add_request(wrng.integers(3, cfg.vocab_size, size=int(prompt_lens[i])).tolist(), wsp)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        w_t0 = time.perf_counter()
+        w_first, w_done, w_tokens = {}, 0, 0
+        while llm.has_unfinished:
+            for ro in llm.step():
+                if ro.token_ids and ro.request_id not in w_first:
+                    w_first[ro.request_id] = time.perf_counter() - w_t0
+                if ro.finished:
+                    w_done += 1
+                    w_tokens += len(ro.token_ids)
+        torch.cuda.synchronize()
+        w_s = time.perf_counter() - w_t0
+        wt = torch.tensor([w_s], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(wt, op=dist.ReduceOp.MAX)
+        w_s = float(wt.item())
+        workload = {"output_tok_s": round(w_tokens / w_s, 2), "seconds": round(w_s, 3), "requests": w_done,
+                    "output_tokens": w_tokens, "prompt_tokens": int(prompt_lens.sum()),
+                    "ttft_p50_s": round(float(np.median(list(w_first.values()))), 4) if w_first else None,
+                    "ttft_max_s": round(float(max(w_first.values())), 4) if w_first else None,
+                    "note": "all requests arrive at t=0; first arrival to last finished token, prefill included, through LLM.step()"}
 
     sp = SamplingParams(temperature=0.0, max_tokens=total_steps + 8, ignore_eos=True)
     ttft_p50 = None
@@ -236,6 +289,8 @@ def main():
     barrier()
     e2e_ms = max(e0.elapsed_time(e1), 0.0)
     e2e_wall_ms = (time.perf_counter() - w0) * 1e3
+    llm.drain()
+    torch.cuda.synchronize()
     st1 = dict(llm.stats)
     h2d = (st1["h2d_bytes"] - st0["h2d_bytes"]) / args.steps
     d2h = (st1["d2h_bytes"] - st0["d2h_bytes"]) / args.steps
@@ -248,6 +303,7 @@ def main():
     launches_per_step = getattr(llm.runner, "launches_per_step", {}).get(Bk, 0)
     for _ in range(args.warmup):
         llm.step()
+    llm.drain()
     barrier()
     k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     k0.record()
@@ -271,6 +327,7 @@ def main():
         llm.scheduler.running = [keep]
         for _ in range(max(args.warmup, 3)):
             llm.step()
+        llm.drain()
         g1 = llm.runner.graphs.get(_bucket(1))
         barrier()
         b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -304,12 +361,14 @@ def main():
                        "mean_context": float(ctx.mean()), "parallelism": f"tp{world}", "weights": args.quant,
                        "kv_cache": f"paged, {page}-token pages, {args.kv_dtype}", "comm": args.comm if world > 1 else "none",
                        "l2_policy": "inputs larger than L2 (weight shard + KV pages streamed every step)",
-                       "layers": cfg.n_layers, "valid": not bool(args.layers or args.shard_sim)},
+                       "layers": cfg.n_layers, "valid": not bool(args.layers or args.shard_sim),
+                       "async_decode": not args.sync_decode},
             "e2e": {"value": round(e2e_val, 2), "unit": "tok/s", "ms_per_step": round(max(e2e_ms, e2e_wall_ms) / args.steps, 4),
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": int(launches_per_step * args.steps) if graph is not None else int(C.launch_count),
             "clocks": sampler.summary(),
-            "ttft_p50_s": ttft_p50, "bs1_tok_s": round(1e3 / bs1_ms, 2) if bs1_ms > 0 else None,
+            "workload": workload, "steady_state_prefill_ttft_p50_s": ttft_p50,
+            "ttft_p50_s": workload["ttft_p50_s"] if workload else ttft_p50, "bs1_tok_s": round(1e3 / bs1_ms, 2) if bs1_ms > 0 else None,
             "bs1_ms_per_step": round(bs1_ms, 4), "load_s": round(load_s, 1),
             "device_status": {"code": code, "detail": detail, "count": count},
         }

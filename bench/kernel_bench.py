@@ -47,17 +47,20 @@ def timeit(fn, n_warm=5, n=20):
     return e0.elapsed_time(e1) / n * 1e-3
 
 
+OPTS = {}  # command-line options shared with the bench functions
+
+
 def bench_gemm(rows):
     hbm, tf, kind = peaks()
     shapes = [("qkv/tp8", 1280, 8192), ("o/tp8", 8192, 1024), ("gate_up/tp8", 7168, 8192), ("down/tp8", 8192, 3584),
               ("lm_head/tp8", 16032, 8192)]
-    only = os.environ.get("KB_SHAPES")
+    only = OPTS.get("shapes")
     for name, N, K in shapes:
         if only and name.split("/")[0] not in only.split(","):
             continue
         copies = max(2, int(400e6 // (N * K * 2)) + 1)
         ws = [(torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(copies)]
-        for T in [int(v) for v in os.environ.get("KB_TOKENS", "1,16,64,256,2048").split(",")]:
+        for T in [int(v) for v in OPTS.get("tokens", "1,16,64,256,2048").split(",")]:
             x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
             out = torch.empty(T, N, dtype=torch.bfloat16, device="cuda")
             plan = C.gemm_plan(T, N, K)
@@ -101,7 +104,7 @@ def bench_attn(rows):
         m.query_start = torch.arange(B + 1, dtype=torch.int32, device="cuda")
         m.max_query_len, m.max_seq_len = 1, ctx
         q = torch.randn(B, nq, hd, device="cuda").to(torch.bfloat16)
-        if os.environ.get("KB_ATTN_TRACE"):
+        if OPTS.get("attn_trace"):
             import ctypes
 
             trace = torch.zeros(16, dtype=torch.int64, device="cuda")
@@ -222,7 +225,14 @@ def main():
     ap.add_argument("--json", default="")
     ap.add_argument("--case", default="", help="small case for a profiler: gemm:TxNxK or attn:BxCTXxNQxNKV[:kv]")
     ap.add_argument("--launches", type=int, default=6)
+    ap.add_argument("--shapes", default="", help="GEMM shapes to run, by name before the slash (qkv,o,gate_up,down,lm_head)")
+    ap.add_argument("--tokens", default="1,16,64,256,2048", help="token counts of the GEMM sweep")
+    ap.add_argument("--attn-trace", action="store_true", help="print the in-kernel phase timestamps of attention CTA 0")
+    ap.add_argument("--prefill-tn", type=int, default=-1, help="force the token tile of prefill-sized GEMMs (128 / 256 / 0 = auto)")
     a = ap.parse_args()
+    OPTS.update(shapes=a.shapes, tokens=a.tokens, attn_trace=a.attn_trace)
+    if a.prefill_tn >= 0:
+        C.lib().oxb_set_gemm_prefill_tn(a.prefill_tn)
     if a.case:
         small_case(a.case, a.launches)
         return

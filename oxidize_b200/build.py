@@ -1,6 +1,7 @@
 """Builds the native libraries in-tree with nvcc / g++ (no torch headers, seconds per file).
 
-``liboxb.so``  — sm_100a CUDA kernels (``csrc/oxb.cu``, one translation unit)
+``liboxb.so``  — sm_100a CUDA kernels (``csrc/oxb*.cu``: translation units compiled in parallel as relocatable
+device code and linked, device link included, into one shared object)
 ``liboxbrt.so`` — host runtime pieces in C++ (``csrc/runtime.cpp``)
 """
 from __future__ import annotations
@@ -13,8 +14,9 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 
-NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--shared",
-              "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = ARCH_FLAGS + ["-lineinfo", "-O3", "-std=c++17", "-rdc=true", "-Xcompiler", "-fPIC", "-Xcompiler",
+                           "-fvisibility=hidden"]
 
 
 def _newer(target: str, sources) -> bool:
@@ -30,16 +32,37 @@ def _sources(exts):
 
 def build_kernels(force: bool = False, verbose: bool = False) -> str:
     out = os.path.join(CSRC, "liboxb.so")
-    srcs = _sources((".cu", ".cuh"))
+    srcs = _sources((".cu", ".cuh", ".h"))
     if not force and _newer(out, srcs):
         return out
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", out, os.path.join(CSRC, "oxb.cu")]
-    r = subprocess.run(cmd, capture_output=True, text=True)
-    if r.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + r.stdout + r.stderr)
+    units = [s for s in srcs if s.endswith(".cu")]
+    headers = [s for s in srcs if not s.endswith(".cu")]
+    objdir = os.path.join(CSRC, "build")
+    os.makedirs(objdir, exist_ok=True)
+    hdr_time = max(os.path.getmtime(h) for h in headers)
+
+    def compile_unit(src: str):
+        obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
+        if not force and os.path.exists(obj) and os.path.getmtime(obj) >= max(os.path.getmtime(src), hdr_time):
+            return obj, ""
+        cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", "-o", obj, src]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {os.path.basename(src)}:\n" + r.stdout + r.stderr)
+        return obj, r.stderr
+
+    from concurrent.futures import ThreadPoolExecutor
+
+    with ThreadPoolExecutor(max_workers=max(1, min(len(units), os.cpu_count() or 4))) as ex:
+        results = list(ex.map(compile_unit, units))
     if verbose:
-        sys.stderr.write(r.stderr)
+        for _, err in results:
+            sys.stderr.write(err)
+    link = [nvcc] + ARCH_FLAGS + ["--shared", "-Xcompiler", "-fPIC", "-o", out] + [o for o, _ in results]
+    r = subprocess.run(link, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("nvcc link failed:\n" + r.stdout + r.stderr)
     return out
 
 

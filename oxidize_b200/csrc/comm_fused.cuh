@@ -232,7 +232,7 @@ __device__ __forceinline__ bool ll_try_load32(const uint8_t* src, uint32_t e, ui
 
 __device__ __forceinline__ bool ar_exchange_ll(const ArArgs& ar, const uint8_t* stage, uint32_t call, int tile_id, int n0,
                                                int t0, int tmax, int N, __nv_bfloat16* Y, int ldY, volatile int* abort_flag,
-                                               int tid) {
+                                               int tid, unsigned long long* ssq_out = nullptr) {
   const int W = ar.world;
   const uint32_t epoch = (call + 1u) != 0u ? call + 1u : 1u;
   const size_t slot_bytes = (size_t)ar.t_max * ar.n_max * 4;  // 4 bytes per bf16 element on the wire
@@ -282,7 +282,11 @@ __device__ __forceinline__ bool ar_exchange_ll(const ArArgs& ar, const uint8_t* 
   }
   AR_STAMP(2);
   // ---- 3. gather the reduced piece
+  // (the 16 lanes that hold one token row take every branch below together: the verdict of a failed poll
+  // is shared inside that half warp, so the row's sum of squares can be formed with shuffles)
+  const unsigned hmask = (tid & 16) ? 0xFFFF0000u : 0x0000FFFFu;
   const uint8_t* res = mine + (size_t)W * slot_bytes;
+  fail = __any_sync(hmask, fail);
   for (int q0 = tid; q0 < Q && !fail; q0 += 128 * 4) {
     uint4 v[4];
     unsigned pending = 0u;
@@ -292,6 +296,15 @@ __device__ __forceinline__ bool ar_exchange_ll(const ArArgs& ar, const uint8_t* 
       if (q < Q && n0 + (q & 15) * 8 < N) pending |= 1u << u;
     }
     const unsigned valid = pending;
+    // the residual rows are local: their reads are issued before the poll, whose wait hides them
+    uint4 resid[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int q = q0 + 128 * u;
+      resid[u] = make_uint4(0, 0, 0, 0);
+      if (ar.residual != nullptr && ((valid >> u) & 1u))
+        resid[u] = *reinterpret_cast<const uint4*>(ar.residual + (size_t)(t0 + (q >> 4)) * ldY + n0 + (q & 15) * 8);
+    }
     for (unsigned it = 0; pending != 0u; ++it) {
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
@@ -305,22 +318,41 @@ __device__ __forceinline__ bool ar_exchange_ll(const ArArgs& ar, const uint8_t* 
         break;
       }
     }
+    fail = __any_sync(hmask, fail);
     if (fail) break;
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      if (!((valid >> u) & 1u)) continue;
       const int q = q0 + 128 * u;
-      const size_t yo = (size_t)(t0 + (q >> 4)) * ldY + n0 + (q & 15) * 8;
-      uint4 o = v[u];
-      if (ar.residual != nullptr) {
-        float acc[8];
+      float ss = 0.f;
+      if ((valid >> u) & 1u) {
+        const size_t yo = (size_t)(t0 + (q >> 4)) * ldY + n0 + (q & 15) * 8;
+        uint4 o = v[u];
+        if (ar.residual != nullptr) {
+          float acc[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-        ar_add8(acc, o);
-        ar_add8(acc, *reinterpret_cast<const uint4*>(ar.residual + yo));
-        o = ar_pack8(acc);
+          for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+          ar_add8(acc, o);
+          ar_add8(acc, resid[u]);
+          o = ar_pack8(acc);
+        }
+        *reinterpret_cast<uint4*>(Y + yo) = o;
+        if (ssq_out != nullptr) {
+          const uint32_t w4[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = unpack_bf16x2(w4[i]);
+            ss += f.x * f.x + f.y * f.y;
+          }
+        }
       }
-      *reinterpret_cast<uint4*>(Y + yo) = o;
+      if (ssq_out != nullptr && q < Q) {  // q < Q holds for all 16 lanes of the row or for none
+#pragma unroll
+        for (int o2 = 8; o2 > 0; o2 >>= 1) ss += __shfl_xor_sync(hmask, ss, o2);
+        if ((q & 15) == 0) {  // fixed-point add: the total does not depend on the order of the tiles (NormArgs)
+          ss = fminf(ss, 3.0e10f);
+          atomicAdd(ssq_out + t0 + (q >> 4), (unsigned long long)(ss * 268435456.f + 0.5f));
+        }
+      }
     }
   }
   AR_STAMP(3);
@@ -333,14 +365,38 @@ __device__ __forceinline__ bool ar_exchange_ll(const ArArgs& ar, const uint8_t* 
 
 // picks the exchange by ar.mode; `call` is the device-side call counter of this collective
 __device__ __forceinline__ bool ar_exchange(const ArArgs& ar, const uint8_t* stage, int call, int tile_id, int n0, int t0,
-                                            int tmax, int N, __nv_bfloat16* Y, int ldY, volatile int* abort_flag, int tid) {
-  if (ar.mode == 1) return ar_exchange_ll(ar, stage, (uint32_t)call, tile_id, n0, t0, tmax, N, Y, ldY, abort_flag, tid);
+                                            int tmax, int N, __nv_bfloat16* Y, int ldY, volatile int* abort_flag, int tid,
+                                            unsigned long long* ssq_out = nullptr) {
+  // (the per-row sums of squares exist on the two-shot exchange only; the host does not ask for them otherwise)
+  if (ar.mode == 1) return ar_exchange_ll(ar, stage, (uint32_t)call, tile_id, n0, t0, tmax, N, Y, ldY, abort_flag, tid, ssq_out);
   return ar_exchange_tile(ar, stage, call & 1, tile_id, n0, t0, tmax, N, Y, ldY, 0.f, abort_flag, tid);
+}
+
+// Host side: fill the kernel argument block of one collective call from the symmetric-buffer pointers.
+inline int fill_ar(ArArgs& ar, int world, int rank, const uint64_t* data_ptrs, const uint64_t* flag_ptrs, int* ctrl,
+                   int t_max, int n_max, int max_tiles, unsigned long long timeout_ns, const void* residual) {
+  memset(&ar, 0, sizeof(ar));
+  ar.mode = world >= g_oxb_ar_ll_min_world ? 1 : 0;
+  ar.trace = g_oxb_ar_trace;
+  if (world < 1 || world > AR_MAX_WORLD || rank < 0 || rank >= world || ctrl == nullptr) return (int)cudaErrorInvalidValue;
+  ar.world = world;
+  ar.rank = rank;
+  ar.t_max = t_max;
+  ar.n_max = n_max;
+  ar.max_tiles = max_tiles;
+  ar.timeout_ns = timeout_ns;
+  ar.ctrl = ctrl;
+  ar.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  for (int i = 0; i < world; ++i) {
+    ar.data[i] = reinterpret_cast<__nv_bfloat16*>(data_ptrs[i]);
+    ar.flags[i] = reinterpret_cast<uint32_t*>(flag_ptrs[i]);
+  }
+  return 0;
 }
 
 // Stand-alone one-shot all-reduce of a [T, N] bf16 tensor through the same buffers (used for
 // tensors that do not come out of a GEMM, e.g. the MoE combine): grid = N/128 tiles.
-__global__ void __launch_bounds__(128)
+static __global__ void __launch_bounds__(128)
 allreduce_oneshot_kernel(const ArArgs ar, const __nv_bfloat16* __restrict__ X, __nv_bfloat16* __restrict__ Y, int T, int N,
                          int ld, int tg) {
   extern __shared__ __align__(16) uint8_t ar_stage[];  // [tg][256] bytes

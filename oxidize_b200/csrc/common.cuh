@@ -30,12 +30,12 @@ enum OxbStatus : int {
   OXB_TIMEOUT_SPLITK = 5,
   OXB_BAD_BLOCK_ID = 6,   // a block table entry outside the KV pool (access skipped)
   OXB_BAD_SLOT = 7,       // a KV write slot outside the KV pool (write skipped)
-  OXB_BAD_ARGUMENT = 6,
+  OXB_BAD_ARGUMENT = 8,   // a kernel argument outside its documented range (work skipped)
 };
 
 // Device status word (one per loaded library per device); host reads it with oxb_status().
-// The library is built as a single translation unit, so there is exactly one copy.
-__device__ int g_oxb_status[4];  // [0]=code, [1]=detail (block / stage / rank), [2]=count
+// Defined once in oxb.cu; the translation units are compiled as relocatable device code and share it.
+extern __device__ int g_oxb_status[4];  // [0]=code, [1]=detail (block / stage / rank), [2]=count
 
 __device__ __forceinline__ void oxb_report(int code, int detail) {
   if (atomicCAS(&g_oxb_status[0], 0, code) == 0) g_oxb_status[1] = detail;
@@ -244,6 +244,14 @@ typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_
                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 PFN_encodeTiled oxb_get_encode_tiled();
+int oxb_sm_count();  // SM count of the current device
+// Byte view of packed weight rows: [rows, row_bytes] uint8, no swizzle (box_bytes <= 256, 16-byte multiples)
+int oxb_make_tmap_bytes(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
+                        uint32_t box_bytes);
+extern int g_oxb_ar_ll_min_world;          // rank counts from which the fused all-reduce uses the LL two-shot exchange
+extern int g_oxb_gemv_max_t;               // packed-weight calls of at most this many tokens take the dp4a GEMV
+extern unsigned long long* g_oxb_ar_trace;    // optional device buffers for in-kernel phase timestamps
+extern unsigned long long* g_oxb_attn_trace;
 // 2-D row-major tensor [rows, cols] of `elem_bytes` elements, box [box_rows, box_cols], 128B swizzle
 int oxb_make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
                      uint32_t box_rows, uint32_t box_cols, int elem_bytes);

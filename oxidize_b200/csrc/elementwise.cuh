@@ -12,7 +12,7 @@ namespace oxb {
 
 // ----------------------------------------------------------------------------- embedding
 // one CTA per token; qtype as in quant_blocks.cuh
-__global__ void embed_kernel(const int* __restrict__ tokens, const uint8_t* __restrict__ table, int qtype,
+static __global__ void embed_kernel(const int* __restrict__ tokens, const uint8_t* __restrict__ table, int qtype,
                              size_t row_bytes, int H, int vocab, float scale, __nv_bfloat16* __restrict__ out) {
   pdl_launch_dependents();
   pdl_wait();
@@ -27,7 +27,7 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const uint8_t* __re
 // ----------------------------------------------------------------------------- add + RMSNorm
 // y = rmsnorm(x + residual) * w ; residual <- x + residual (bf16, rounded before the norm)
 // one CTA per row; the summed row is staged in shared memory as fp32.
-__global__ void add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res_in,
+static __global__ void add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res_in,
                                    __nv_bfloat16* __restrict__ res_out, const float* __restrict__ w,
                                    __nv_bfloat16* __restrict__ y, int H, float eps) {
   extern __shared__ float rowbuf[];
@@ -148,7 +148,43 @@ add_rmsnorm_reg_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
 
 // ----------------------------------------------------------------------------- SwiGLU
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i]
-__global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int T, int I) {
+// Sum of squares of every row of X[T, H] (bf16) as 64-bit fixed point (2^-28 units): seeds the folded RMSNorm of
+// the first layer (later layers get these sums from the epilogue that writes the residual stream).  One warp per row.
+static __global__ void row_sumsq_kernel(const __nv_bfloat16* __restrict__ X, int ldX, int T, int H,
+                                        unsigned long long* __restrict__ out, unsigned long long* __restrict__ clear) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (t >= T) return;
+  // per 128-column tile, as the GEMM epilogues do, so that both routes round alike
+  unsigned long long total = 0ull;
+  for (int c0 = 0; c0 < H; c0 += 256) {
+    const int c = c0 + lane * 8;
+    float s = 0.f;
+    if (c < H) {
+      const uint4 v = *reinterpret_cast<const uint4*>(X + (size_t)t * ldX + c);
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(u[j]);
+        s += f.x * f.x + f.y * f.y;
+      }
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float other = __shfl_xor_sync(0xffffffffu, s, 16);
+    if (lane == 0) {
+      total += (unsigned long long)(fminf(s, 3.0e10f) * 268435456.f + 0.5f);
+      if (c0 + 128 < H) total += (unsigned long long)(fminf(other, 3.0e10f) * 268435456.f + 0.5f);
+    }
+  }
+  if (lane == 0) {
+    out[t] = total;
+    if (clear != nullptr) clear[t] = 0ull;
+  }
+}
+
+static __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int T, int I) {
   pdl_launch_dependents();
   pdl_wait();
   const int I8 = I >> 3;
@@ -184,7 +220,7 @@ struct KvWriteArgs {
   int num_blocks;  // pages in the KV pool: slots are checked against it
 };
 
-__global__ void qk_rope_kvwrite_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+static __global__ void qk_rope_kvwrite_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
                                        const int* __restrict__ slots, const float* __restrict__ cos_sin, int max_pos,
                                        int rot, int pairing /*0 split-half, 1 adjacent*/, const float* __restrict__ qn,
                                        const float* __restrict__ kn, float eps, int nq, int nkv, int hd,
@@ -265,7 +301,7 @@ __global__ void qk_rope_kvwrite_kernel(const __nv_bfloat16* __restrict__ qkv, co
 
 // ----------------------------------------------------------------------------- argmax
 // one CTA per row of fp32 logits; tie_highest selects the last maximal index
-__global__ void argmax_kernel(const float* __restrict__ logits, int V, int ld, int tie_highest, int* __restrict__ out,
+static __global__ void argmax_kernel(const float* __restrict__ logits, int V, int ld, int tie_highest, int* __restrict__ out,
                               float* __restrict__ out_val, int index_offset) {
   __shared__ float sv[32];
   __shared__ int si[32];
@@ -321,6 +357,157 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int V, int ld, i
       if (bi < 0) bi = 0;  // all-NaN row
       out[blockIdx.x] = bi + index_offset;
       if (out_val != nullptr) out_val[blockIdx.x] = best;
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- vocabulary-parallel argmax
+// Greedy sampling over a vocabulary that is sharded across tensor-parallel ranks, in ONE kernel: every rank
+// reduces its own logits shard to a (value, index) pair per row, pushes the pair into every peer's exchange
+// buffer over NVLink (8-byte words {payload, epoch}: a word that carries this call's epoch also carries its
+// payload, so no fence or separate flag is needed), waits (bounded) for the pairs of the other ranks and picks the
+// winner.  Shards are in ascending vocabulary order, so the first maximum is the lowest index and the last one
+// the highest.  All ranks obtain the same token.  The token can be written to a second array as well (the next
+// step's input ids, so that decode never needs the host to feed the token back).
+// Replaces the reference's k_f_argmax + host feedback (oxidize-c/src/backends/cuda_fast.cu:495) for the sharded case.
+struct ArgmaxXchg {
+  int world, rank;                        // world <= 1: no exchange
+  unsigned long long* bufs[8];            // peers' buffers: [2 parities][world][rmax][2] u64
+  int* ctrl;                              // local: [0] call counter, [1] rows done
+  int rmax;
+  unsigned long long timeout_ns;
+};
+
+__device__ __forceinline__ unsigned long long gtimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+template <typename TIn>
+static __global__ void __launch_bounds__(1024)
+argmax_tp_kernel(const TIn* __restrict__ logits, int V, int ld, int tie_highest, int* __restrict__ out, int* __restrict__ out2,
+                 int index_offset, const ArgmaxXchg xa) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  __shared__ float cand_v[8];
+  __shared__ int cand_i[8];
+  __shared__ int s_call, s_fail;
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    s_call = xa.world > 1 ? *reinterpret_cast<volatile int*>(xa.ctrl) : 0;
+    s_fail = 0;
+  }
+  const TIn* row = logits + (size_t)blockIdx.x * ld;
+  float best = -INFINITY;
+  int bi = -1;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = (float)row[i];
+    if (bi < 0 || v > best || (v == best && tie_highest)) {
+      if (!(v != v)) {
+        best = v;
+        bi = i;
+      }
+    }
+  }
+  auto better = [&](float v, int i, float bv, int b) {
+    if (i < 0) return false;
+    if (b < 0) return true;
+    return v > bv || (v == bv && (tie_highest ? i > b : i < b));
+  };
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better(ov, oi, best, bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    sv[warp] = best;
+    si[warp] = bi;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    best = lane < nw ? sv[lane] : -INFINITY;
+    bi = lane < nw ? si[lane] : -1;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (better(ov, oi, best, bi)) {
+        best = ov;
+        bi = oi;
+      }
+    }
+    if (bi < 0) {  // all-NaN shard
+      bi = 0;
+      best = -INFINITY;
+    }
+    bi += index_offset;
+    if (xa.world > 1) {
+      const unsigned epoch = (unsigned)s_call + 1u != 0u ? (unsigned)s_call + 1u : 1u;
+      const size_t par = (size_t)(s_call & 1) * xa.world;
+      const int r = blockIdx.x;
+      if (lane < xa.world) {
+        // push this rank's pair to peer `lane` (self included)
+        volatile unsigned long long* dst = xa.bufs[lane] + ((par + xa.rank) * xa.rmax + r) * 2;
+        dst[0] = ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(best);
+        dst[1] = ((unsigned long long)epoch << 32) | (unsigned long long)(unsigned)bi;
+        // wait for the pair of source rank `lane`
+        volatile unsigned long long* src = xa.bufs[xa.rank] + ((par + lane) * xa.rmax + r) * 2;
+        const unsigned long long t0 = gtimer_ns();
+        unsigned long long w0 = 0ull, w1 = 0ull;
+        bool got = false;
+        for (unsigned it = 0;; ++it) {
+          w0 = src[0];
+          w1 = src[1];
+          if ((unsigned)(w0 >> 32) == epoch && (unsigned)(w1 >> 32) == epoch) {
+            got = true;
+            break;
+          }
+          if ((it & 63u) == 63u && gtimer_ns() - t0 > xa.timeout_ns) break;
+        }
+        if (got) {
+          cand_v[lane] = __uint_as_float((unsigned)(w0 & 0xFFFFFFFFull));
+          cand_i[lane] = (int)(unsigned)(w1 & 0xFFFFFFFFull);
+        } else {
+          cand_v[lane] = -INFINITY;
+          cand_i[lane] = 0;
+          s_fail = 1;
+          oxb_report(OXB_TIMEOUT_PEER_FLAG, lane);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        float wv = cand_v[0];
+        int wi = cand_i[0];
+        for (int s = 1; s < xa.world; ++s) {
+          const float v = cand_v[s];
+          if (v > wv || (v == wv && tie_highest)) {
+            wv = v;
+            wi = cand_i[s];
+          }
+        }
+        bi = wi;
+      }
+    }
+    if (lane == 0) {
+      out[blockIdx.x] = bi;
+      if (out2 != nullptr) out2[blockIdx.x] = bi;
+      if (xa.world > 1) {
+        // the last row of the grid advances the call counter (flips the buffer parity)
+        __threadfence();
+        if (atomicAdd(&xa.ctrl[1], 1) == (int)gridDim.x - 1) {
+          xa.ctrl[1] = 0;
+          __threadfence();
+          xa.ctrl[0] = s_call + 1;
+        }
+      }
     }
   }
 }

@@ -40,7 +40,7 @@ struct GemmTile {
   static constexpr int STAGES = TN <= 16 ? 6 : TN == 32 ? 5 : TN == 64 ? 4 : (TN == 128 ? 6 : 4);
   static constexpr int CTAS_PER_SM = TN <= 64 ? 2 : 1;
   static constexpr int TMEM_COLS = TN < 32 ? 32 : TN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + 1024 /*token scales*/;
 };
 
 // Q4_K and Q6_K weights with decode-sized token tiles are staged through shared memory: one TMA box of
@@ -69,6 +69,45 @@ constexpr int EPI_ADD_INTO = 1;   // Y += acc (residual accumulate, bf16 read-mo
 constexpr int EPI_ROPE = 3;       // fused qkv projection: RoPE on q/k heads, q -> q_out, k/v -> paged KV cache (RopeArgs)
 constexpr int EPI_SWIGLU = 2;     // weight rows interleaved per tile (64 gate rows, then their 64 up rows):
                                   // Y[t, n0/2 + c] = silu(acc[c]) * acc[64 + c], Y has N/2 columns
+
+// RMSNorm folded into the GEMMs around it.  The norm weight is multiplied into the consuming projection's
+// columns when the model is loaded; what remains of the norm is one scalar per token, 1/rms(x_t), which
+// commutes with the matrix product and is applied to the accumulator in the consumer's epilogue (before
+// bias, RoPE or SiLU).  The producer of x (the row-parallel projection whose epilogue writes the new
+// residual stream) adds, for every 128-column tile and token, the sum of squares of what it wrote into one
+// 64-bit fixed-point accumulator per token (2^-28 units).  Integer addition is associative, so the total does
+// not depend on the order in which the tiles arrive: every rank and every replay computes the same scale.
+// Two accumulator arrays alternate; the consumer of one clears the other for the producer that follows it.
+constexpr float SUMSQ_FIX = 268435456.f;  // 2^28
+struct NormArgs {
+  const unsigned long long* sumsq_in;  // consumer: [T] fixed-point sums of squares of the token rows of X, or null
+  float inv_dim, eps;                  // scale_t = rsqrt(sum_t * inv_dim + eps)
+  unsigned long long* clear;           // consumer: [T] accumulator to reset for the next producer, or null
+  unsigned long long* sumsq_out;       // producer: [T] accumulator that receives the rows written, or null
+};
+
+__device__ __forceinline__ void sumsq_add(unsigned long long* dst, float ss) {
+  ss = fminf(ss, 3.0e10f);  // 2^63 / 2^28 with headroom for the other tiles of the row
+  atomicAdd(dst, (unsigned long long)(ss * SUMSQ_FIX + 0.5f));
+}
+
+__device__ __forceinline__ float sumsq_bf16x8(const uint4 v) {
+  const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = unpack_bf16x2(u[j]);
+    s += f.x * f.x + f.y * f.y;
+  }
+  return s;
+}
+// sum over the 16 lanes that share bit 4 of the lane id (one token row of a 128-column tile)
+__device__ __forceinline__ float half_warp_sum(float v) {
+  const unsigned mask = (threadIdx.x & 16) ? 0xFFFF0000u : 0x0000FFFFu;
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(mask, v, o);
+  return v;
+}
 
 // Sum `splits` fp32 partials for tokens [jb, je) of one tile row: JU tokens x SMAX splits of
 // independent L2 loads are in flight per thread; the adds run in split order (reproducible).
@@ -115,26 +154,50 @@ __device__ __forceinline__ void splitk_reduce_dsmem(uint32_t local_addr, int spl
   }
 }
 
-// bf16 tile [ntok][128 rows] in shared memory -> Y rows with 16-byte stores (128 threads, tid 0..127)
+// bf16 tile [ntok][128 rows] in shared memory -> Y rows with 16-byte stores (128 threads, tid 0..127).
+// With ssq_out, the sum of squares of every row written (its 128 columns) is added to ssq_out[t_first + t].
 __device__ __forceinline__ void store_tile_rows(const uint8_t* stage, int ntok, int t_first, int n0, int N,
-                                                __nv_bfloat16* Y, int ldY, int epi_mode, int tid) {
+                                                __nv_bfloat16* Y, int ldY, int epi_mode, int tid,
+                                                unsigned long long* ssq_out = nullptr) {
   const int chunk = tid & 15, trow = tid >> 4;
-  if (n0 + chunk * 8 >= N) return;
-  for (int t = trow; t < ntok; t += 8) {
-    uint4 v = *reinterpret_cast<const uint4*>(stage + t * 256 + chunk * 16);
-    __nv_bfloat16* dst = Y + (size_t)(t_first + t) * ldY + n0 + chunk * 8;
-    if (epi_mode == EPI_ADD_INTO) {
-      const uint4 o = *reinterpret_cast<const uint4*>(dst);
-      uint32_t a[4] = {v.x, v.y, v.z, v.w};
-      const uint32_t c[4] = {o.x, o.y, o.z, o.w};
+  const bool col_ok = n0 + chunk * 8 < N;
+  if (!col_ok && ssq_out == nullptr) return;
+  const bool add = epi_mode == EPI_ADD_INTO;
+  // eight rows per thread and pass: when the tile is added into Y, the eight reads of Y are issued together
+  // (one memory latency per pass instead of one per row)
+  for (int tb = trow; tb < ntok; tb += 64) {
+    uint4 prev[8];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 fa = unpack_bf16x2(a[j]), fc = unpack_bf16x2(c[j]);
-        a[j] = pack_bf16x2(fa.x + fc.x, fa.y + fc.y);
-      }
-      v = make_uint4(a[0], a[1], a[2], a[3]);
+    for (int i = 0; i < 8; ++i) {
+      const int t = tb + 8 * i;
+      prev[i] = make_uint4(0, 0, 0, 0);
+      if (add && col_ok && t < ntok) prev[i] = *reinterpret_cast<const uint4*>(Y + (size_t)(t_first + t) * ldY + n0 + chunk * 8);
     }
-    *reinterpret_cast<uint4*>(dst) = v;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int t = tb + 8 * i;
+      if (t >= ntok) break;  // the 16 lanes of a row share t
+      float ss = 0.f;
+      if (col_ok) {
+        uint4 v = *reinterpret_cast<const uint4*>(stage + t * 256 + chunk * 16);
+        if (add) {
+          uint32_t a[4] = {v.x, v.y, v.z, v.w};
+          const uint32_t c[4] = {prev[i].x, prev[i].y, prev[i].z, prev[i].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 fa = unpack_bf16x2(a[j]), fc = unpack_bf16x2(c[j]);
+            a[j] = pack_bf16x2(fa.x + fc.x, fa.y + fc.y);
+          }
+          v = make_uint4(a[0], a[1], a[2], a[3]);
+        }
+        *reinterpret_cast<uint4*>(Y + (size_t)(t_first + t) * ldY + n0 + chunk * 8) = v;
+        ss = sumsq_bf16x8(v);
+      }
+      if (ssq_out != nullptr) {
+        ss = half_warp_sum(ss);
+        if (chunk == 0) sumsq_add(ssq_out + t_first + t, ss);
+      }
+    }
   }
 }
 
@@ -256,7 +319,7 @@ __global__ void __launch_bounds__(QT == QT_BF16 ? GEMM_THREADS : GEMM_THREADS_MM
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                  __nv_bfloat16* __restrict__ Y, const float* __restrict__ bias, int N, int T, int K, int ldY,
                  int splits, float* __restrict__ ws, int* __restrict__ counters, int epi_mode, const ArArgs ar,
-                 const QwArgs qw, const GroupArgs gr, const RopeArgs ro) {
+                 const QwArgs qw, const GroupArgs gr, const RopeArgs ro, const NormArgs nm) {
   constexpr bool MMQ = QT != QT_BF16;
   const int zg = gr.enabled ? (int)blockIdx.z : 0;
   if (gr.enabled && gr.scale != nullptr) {
@@ -283,6 +346,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   constexpr bool STAGED = MmqStaged<TN, QT>::value;
   uint64_t* packed_full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES + 192);  // [2] (STAGED only)
   uint8_t* packed_buf = smem + STAGES * Cfg::STAGE_BYTES + 256;                                  // [2][128][144]
+  float* tok_scale = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES + 256 + (STAGED ? 2 * MmqStage<QT>::BYTES : 0));  // [TN]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * GEMM_BM;
@@ -495,6 +559,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     const int n = n0 + row;
     const int etid = threadIdx.x - 64;
     pdl_wait();  // everything below reads or writes global memory shared with the upstream kernel
+    const bool use_nm = nm.sumsq_in != nullptr;
+    if (use_nm) {
+      // 1/rms of every token of this tile; computed while the MMAs run, published by the barrier below
+      for (int j = etid; j < TN; j += 128) {
+        const float s = t0 + j < T ? (float)__ldcg(nm.sumsq_in + t0 + j) * (1.f / SUMSQ_FIX) : 0.f;
+        tok_scale[j] = rsqrtf(s * nm.inv_dim + nm.eps);
+      }
+    }
+    if (nm.clear != nullptr && blockIdx.x == 0 && blockIdx.y == 0) {
+      // the accumulator that the next producer adds into: its last reader finished before this grid's dependency
+      const int tt = gr.enabled ? T : min(TN, T - t0);
+      for (int j = etid; j < tt; j += 128) nm.clear[t0 + j] = 0ull;
+    }
+    unsigned long long* const ssq_dst = nm.sumsq_out;
     mbar_wait_bounded(accum, 0, abort_flag, OXB_TIMEOUT_ACCUM, blockIdx.x);
     // agree on one verdict for all 128 epilogue threads before any further named barrier
     asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -523,17 +601,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) stage[(c * 16 + j) * GEMM_BM + row] = __float2bfloat16(__uint_as_float(r[j]) + badd);
+          for (int j = 0; j < 16; ++j) {
+            const float sc = use_nm ? tok_scale[c * 16 + j] : 1.f;
+            stage[(c * 16 + j) * GEMM_BM + row] = __float2bfloat16(__uint_as_float(r[j]) * sc + badd);
+          }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (use_ar) {
-          ar_exchange(ar, smem, ticket[2], tile_id, n0, t0, tvalid, N, Y, ldY, abort_flag, etid);
+          ar_exchange(ar, smem, ticket[2], tile_id, n0, t0, tvalid, N, Y, ldY, abort_flag, etid, ssq_dst);
         } else if (epi_mode == EPI_SWIGLU) {
           store_tile_rows_swiglu(smem, tvalid, t0, n0, Y, ldY, etid);
         } else if (epi_mode == EPI_ROPE) {
           store_tile_rows_rope(smem, tvalid, t0, n0, ro, etid);
         } else {
-          store_tile_rows(smem, tvalid, t0, n0, N, Y, ldY, epi_mode, etid);
+          store_tile_rows(smem, tvalid, t0, n0, N, Y, ldY, epi_mode, etid, ssq_dst);
         }
       } else if (ok) {
 #pragma unroll 1
@@ -546,7 +627,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             for (int j = 0; j < 16; ++j) {
               const int t = t0 + c * 16 + j;
               if (t < T) {
-                float v = __uint_as_float(r[j]) + b;
+                float v = __uint_as_float(r[j]) * (use_nm ? tok_scale[c * 16 + j] : 1.f) + b;
                 __nv_bfloat16* dst = Y + (size_t)t * ldY + n;
                 if (epi_mode == EPI_ADD_INTO) v += __bfloat162float(*dst);
                 *dst = __float2bfloat16(v);
@@ -579,7 +660,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(stage_b);
         const float badd = use_ar ? 0.f : b;
         const uint32_t a0 = smem_u32(part + row);
-        auto emit = [&](int j, float acc) { stage[(j - jb) * GEMM_BM + row] = __float2bfloat16(acc + badd); };
+        auto emit = [&](int j, float acc) {
+          stage[(j - jb) * GEMM_BM + row] = __float2bfloat16(acc * (use_nm ? tok_scale[j] : 1.f) + badd);
+        };
         if (splits <= 2) {
           splitk_reduce_dsmem<8, 2>(a0, splits, jb, je, emit);
         } else if (splits <= 4) {
@@ -593,13 +676,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       cluster_sync_all();  // every peer has finished reading this CTA's partial
       if (ok && je > jb) {
         if (use_ar) {
-          ar_exchange(ar, stage_b, ticket[2], tile_id * splits + split, n0, t0 + jb, je - jb, N, Y, ldY, abort_flag, etid);
+          ar_exchange(ar, stage_b, ticket[2], tile_id * splits + split, n0, t0 + jb, je - jb, N, Y, ldY, abort_flag, etid, ssq_dst);
         } else if (epi_mode == EPI_SWIGLU) {
           store_tile_rows_swiglu(stage_b, je - jb, t0 + jb, n0, Y, ldY, etid);
         } else if (epi_mode == EPI_ROPE) {
           store_tile_rows_rope(stage_b, je - jb, t0 + jb, n0, ro, etid);
         } else if (vec_ok) {
-          store_tile_rows(stage_b, je - jb, t0 + jb, n0, N, Y, ldY, epi_mode, etid);
+          store_tile_rows(stage_b, je - jb, t0 + jb, n0, N, Y, ldY, epi_mode, etid, ssq_dst);
         } else if (n < N) {
           const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(stage_b);
           for (int j = jb; j < je; ++j) {
@@ -653,6 +736,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         const int jb = min(tvalid, split * chunk), je = min(tvalid, jb + chunk);
         __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(smem);
         auto emit = [&](int j, float acc) {
+          if (use_nm) acc *= tok_scale[j];
           if (use_ar) {
             stage[(j - jb) * GEMM_BM + row] = __float2bfloat16(acc);
           } else if (n < N) {
@@ -672,7 +756,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         if (use_ar) {
           asm volatile("bar.sync 1, 128;" ::: "memory");
           if (je > jb)
-            ar_exchange(ar, smem, ticket[2], tile_id * splits + split, n0, t0 + jb, je - jb, N, Y, ldY, abort_flag, etid);
+            ar_exchange(ar, smem, ticket[2], tile_id * splits + split, n0, t0 + jb, je - jb, N, Y, ldY, abort_flag, etid, ssq_dst);
         }
         // the last CTA to leave re-arms the counters for the next launch / graph replay
         if (threadIdx.x == 64) {
@@ -771,7 +855,11 @@ inline GemmPlan gemm_plan(int T, int N, int K, int splits_hint, int sm_count, in
 // non-portable size for this footprint, else the portable 8.
 template <int TN, int QT>
 int gemm_max_cluster() {
-  static int cached = 0;
+  static int cached_dev[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  int& cached = cached_dev[dev];
   if (cached) return cached;
   cached = 8;
   auto kfn = gemm_bf16_kernel<TN, QT>;
@@ -799,14 +887,18 @@ int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y
                 int ldY, const GemmPlan& p, float* ws, int* counters, int epi_mode, const ArArgs& ar,
                 cudaStream_t stream, const QwArgs& qw = QwArgs{nullptr, 0, nullptr, 0},
                 const GroupArgs& gr = GroupArgs{0, 0, 0, 0, nullptr, 0, 0}, int groups = 1,
-                const RopeArgs& ro = RopeArgs{nullptr, nullptr, nullptr, 0, 0, 0, 0, 0, 0, 0, nullptr, nullptr}) {
+                const RopeArgs& ro = RopeArgs{nullptr, nullptr, nullptr, 0, 0, 0, 0, 0, 0, 0, nullptr, nullptr},
+                const NormArgs& nm = NormArgs{nullptr, 0.f, 0.f, nullptr, nullptr}) {
   using Cfg = GemmTile<TN>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {false};  // per device ordinal: the attribute belongs to the device's copy of the kernel
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+  if (!configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<TN, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          gemm_smem_bytes<TN, QT>());
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured[dev] = true;
   }
   int splits = p.splits;
   if (p.cluster) {
@@ -820,10 +912,10 @@ int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y
   grl.l2_prefetch_kb = g_oxb_gemm_l2_prefetch_kb;
   if (p.cluster && splits > 1) {
     le = oxb_launch_cluster(gemm_bf16_kernel<TN, QT>, grid, block, dim3(1, splits, 1), (size_t)gemm_smem_bytes<TN, QT>(), stream, tmW,
-                            tmX, Y, bias, N, T, K, ldY, splits, ws, counters, epi_mode, ar, qw, grl, ro);
+                            tmX, Y, bias, N, T, K, ldY, splits, ws, counters, epi_mode, ar, qw, grl, ro, nm);
   } else {
     le = oxb_launch(gemm_bf16_kernel<TN, QT>, grid, block, (size_t)gemm_smem_bytes<TN, QT>(), stream, tmW, tmX, Y, bias, N, T, K, ldY,
-                    splits, ws, counters, epi_mode, ar, qw, grl, ro);
+                    splits, ws, counters, epi_mode, ar, qw, grl, ro, nm);
   }
   if (le != cudaSuccess) return (int)le;
   OXB_CHECK_LAUNCH();

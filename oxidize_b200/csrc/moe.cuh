@@ -21,7 +21,7 @@ constexpr int MOE_MAX_EXPERTS = 256;  // 8 logits per lane
 constexpr int MOE_MAX_TOPK = 16;
 
 // logits [T, E] fp32 (row stride ld); ids/wts [T, k]; scale [n_local, scale_ld] (may be null)
-__global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E, int ld, int k, int sigmoid,
+static __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E, int ld, int k, int sigmoid,
                                  const float* __restrict__ sel_bias, int renorm, float weight_scale,
                                  int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ scale,
                                  int scale_ld, int first_local, int n_local, int n_groups, int groups_used) {
@@ -154,7 +154,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E,
 }
 
 // y [E, T, H] bf16 (expert-major), scale [E, scale_ld] f32, shared [T, H] bf16 or null -> out [T, H] bf16
-__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ scale, int scale_ld,
+static __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ scale, int scale_ld,
                                    const __nv_bfloat16* __restrict__ shared, __nv_bfloat16* __restrict__ out, int E, int T,
                                    int H) {
   pdl_launch_dependents();

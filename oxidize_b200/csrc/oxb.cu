@@ -1,14 +1,21 @@
 // liboxb: the sm_100a kernel library of oxidize_b200, exported with a plain C ABI
 // (loaded from Python with ctypes; every launcher takes raw device pointers and a stream and
-// returns a cudaError_t code, 0 on success).  Built as ONE translation unit.
+// returns a cudaError_t code, 0 on success).  The library is several translation units compiled as
+// relocatable device code and linked into one shared object (oxb.cu: globals, host utilities and the
+// small kernels; oxb_gemm.cu: the tcgen05 GEMM entry points; oxb_mmq_*.cu: one packed-weight format each;
+// oxb_gemv.cu; oxb_attn.cu), so that a rebuild takes the time of the slowest unit.
 #include "common.cuh"
 #include "quant_blocks.cuh"
 #include "elementwise.cuh"
 #include "gemm_tcgen05.cuh"
-#include "attention.cuh"
+#include "gemv_quant.cuh"
 #include "sampling.cuh"
 #include "comm_fused.cuh"
+#include <string.h>
 using namespace oxb;
+
+// the one device status word of the library (declared in common.cuh)
+__device__ int g_oxb_status[4];
 
 int g_oxb_pdl = 1;
 int oxb::g_oxb_cluster_splitk = 1;
@@ -34,19 +41,28 @@ OXB_API int oxb_set_cluster_splitk(int on) {
   g_oxb_cluster_splitk = on ? 1 : 0;
   return old;
 }
+// Packed-weight calls of at most this many tokens take the dp4a GEMV (0 = never).  Above 4 tokens the GEMV re-reads
+// its int8 activations from shared memory once per token and falls behind the tensor-core path.
+int g_oxb_gemv_max_t = 4;
+OXB_API int oxb_set_gemv_max_tokens(int t) {
+  const int old = g_oxb_gemv_max_t;
+  g_oxb_gemv_max_t = t < 0 ? 0 : (t > GV_MAX_T ? GV_MAX_T : t);
+  return old;
+}
 int g_oxb_ar_ll_min_world = 2;  // rank counts from which the fused all-reduce uses the LL two-shot exchange
 
-static unsigned long long* g_oxb_ar_trace = nullptr;
+unsigned long long* g_oxb_ar_trace = nullptr;
 
-static unsigned long long* g_oxb_attn_trace = nullptr;
+unsigned long long* g_oxb_attn_trace = nullptr;
 OXB_API void oxb_set_attn_trace(unsigned long long* p) { g_oxb_attn_trace = p; }
 
 // Device buffer of 16 u64 that receives phase timestamps of piece 0 of each fused all-reduce (null = off).
 OXB_API void oxb_set_ar_trace(unsigned long long* p) { g_oxb_ar_trace = p; }
 
+// w < 0 only reads the current value
 OXB_API int oxb_set_ar_ll_min_world(int w) {
   const int old = g_oxb_ar_ll_min_world;
-  g_oxb_ar_ll_min_world = w;
+  if (w >= 0) g_oxb_ar_ll_min_world = w;
   return old;
 }
 
@@ -102,16 +118,20 @@ int oxb_make_tmap_bytes(CUtensorMap* out, const void* base, uint64_t rows, uint6
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-static int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
+// SM count of the current device (cached per device ordinal)
+int oxb_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev] == 0) {
+    int n = 0;
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
+    cached[dev] = n > 0 ? n : 148;
   }
-  return n;
+  return cached[dev];
 }
+static int sm_count() { return oxb_sm_count(); }
 
 OXB_API int oxb_version() { return 100; }
 
@@ -124,168 +144,6 @@ OXB_API int oxb_status(int* out4, int reset) {
     e = cudaMemcpyToSymbol(g_oxb_status, z, sizeof(z));
   }
   return (int)e;
-}
-
-// ----------------------------------------------------------------------------- GEMM
-OXB_API int oxb_gemm_plan(int T, int N, int K, int splits_hint, int* out4, size_t* ws_bytes, int* n_counters) {
-  GemmPlan p = gemm_plan(T, N, K, splits_hint, sm_count());
-  out4[0] = p.tn;
-  out4[1] = p.n_tiles;
-  out4[2] = p.t_tiles;
-  out4[3] = p.splits;
-  *ws_bytes = p.ws_bytes;
-  *n_counters = p.n_counters;
-  return 0;
-}
-
-// Y[T, ldY>=N] (bf16) = X[T, K] (bf16, contiguous) · W[N, K]^T (bf16, contiguous) (+bias f32[N]).
-// `ws` (fp32 scratch) and `counters` (zero-initialised ints, left zeroed) are only touched when
-// the plan splits K; if they are too small the split count is reduced to fit.
-OXB_API int oxb_gemm_bf16(const void* X, const void* W, void* Y, const float* bias, int T, int N, int K, int ldY,
-                          int epi_mode, int splits_hint, void* ws, size_t ws_bytes, int* counters, int n_counters,
-                          cudaStream_t stream) {
-  if (T <= 0 || N <= 0 || K <= 0) return 0;
-  if (K % 8 != 0) return (int)cudaErrorInvalidValue;  // TMA rows must be 16-byte multiples
-  const bool swiglu = epi_mode == EPI_SWIGLU;
-  // the SwiGLU epilogue exists on the staged (vector-store) paths only: whole 128-row tiles, 16-byte output rows
-  if (swiglu && (N % GEMM_BM != 0 || ldY % 8 != 0 || (reinterpret_cast<uintptr_t>(Y) & 15) != 0 || bias != nullptr))
-    return (int)cudaErrorInvalidValue;
-  GemmPlan p = gemm_plan(T, N, K, splits_hint, sm_count(), swiglu ? 1 : -1);
-  // split-K CTAs of a tile wait for one another, so the whole grid has to fit in one wave
-  while (p.splits > 1 && !p.cluster && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || ws == nullptr || counters == nullptr ||
-                          p.n_tiles * p.t_tiles * p.splits > sm_count()))
-    p = gemm_plan(T, N, K, p.splits - 1, sm_count());
-  CUtensorMap tmW, tmX;
-  int e = oxb_make_tmap_2d(&tmW, W, N, K, (uint64_t)K * 2, GEMM_BM, GEMM_BK, 2);
-  if (e) return e;
-  e = oxb_make_tmap_2d(&tmX, X, T, K, (uint64_t)K * 2, p.tn, GEMM_BK, 2);
-  if (e) return e;
-  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(Y);
-  float* wsf = reinterpret_cast<float*>(ws);
-  ArArgs ar;
-  memset(&ar, 0, sizeof(ar));
-  switch (p.tn) {
-    case 16: return gemm_launch<16>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream);
-    case 32: return gemm_launch<32>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream);
-    case 64: return gemm_launch<64>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream);
-    case 128: return gemm_launch<128>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream);
-    default: return gemm_launch<256>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream);
-  }
-}
-
-// Y[T, N] = X[T, K] (bf16) · dequant(Wq)[N, K]^T for packed weights (qtype as in quant_blocks.cuh, or
-// 9 = block-scaled fp8 with `scales` [N, scale_ld]).  The blocks are decoded inside the GEMM by its
-// producer warps; nothing is dequantized to global memory.  K must be a multiple of 64.
-OXB_API int oxb_gemm_quant(const void* X, const void* Wq, int qtype, size_t row_bytes, const float* scales, int scale_ld,
-                           void* Y, const float* bias, int T, int N, int K, int ldY, int epi_mode, int splits_hint,
-                           void* ws, size_t ws_bytes, int* counters, int n_counters, cudaStream_t stream) {
-  if (T <= 0 || N <= 0 || K <= 0) return 0;
-  if (K % 64 != 0) return (int)cudaErrorInvalidValue;
-  GemmPlan p = gemm_plan(T, N, K, splits_hint, sm_count());
-  while (p.splits > 1 && !p.cluster && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || ws == nullptr || counters == nullptr ||
-                          p.n_tiles * p.t_tiles * p.splits > sm_count()))
-    p = gemm_plan(T, N, K, p.splits - 1, sm_count());
-  CUtensorMap tmX;
-  int e = oxb_make_tmap_2d(&tmX, X, T, K, (uint64_t)K * 2, p.tn, GEMM_BK, 2);
-  if (e) return e;
-  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(Y);
-  float* wsf = reinterpret_cast<float*>(ws);
-  ArArgs ar;
-  memset(&ar, 0, sizeof(ar));
-  QwArgs qw{reinterpret_cast<const uint8_t*>(Wq), row_bytes, scales, scale_ld, 0};
-  switch (qtype) {
-    case QT_Q4_K:
-    case QT_Q6_K: {
-      // staged path (packed super-blocks by TMA) when the byte map can be built: 16-byte rows and base
-      CUtensorMap tmWq;
-      const int box = qtype == QT_Q4_K ? MmqStage<QT_Q4_K>::BOX : MmqStage<QT_Q6_K>::BOX;
-      if (p.tn <= 64 && oxb_make_tmap_bytes(&tmWq, Wq, (uint64_t)N, row_bytes, GEMM_BM, box) == 0) qw.staged = 1;
-      const GroupArgs g0{0, 0, 0, 0, nullptr, 0, 0};
-      if (qtype == QT_Q4_K)
-        return gemm_launch_mmq<QT_Q4_K>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw, g0, 1,
-                                        qw.staged ? &tmWq : nullptr);
-      return gemm_launch_mmq<QT_Q6_K>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw, g0, 1,
-                                      qw.staged ? &tmWq : nullptr);
-    }
-    case QT_Q8_0: return gemm_launch_mmq<QT_Q8_0>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
-    case QT_Q4_0: return gemm_launch_mmq<QT_Q4_0>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
-    case QT_NVFP4: return gemm_launch_mmq<QT_NVFP4>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
-    case QT_FP8B:
-      if (scales == nullptr) return (int)cudaErrorInvalidValue;
-      return gemm_launch_mmq<QT_FP8B>(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
-    default: return (int)cudaErrorInvalidValue;
-  }
-}
-
-static int fill_ar(ArArgs& ar, int world, int rank, const uint64_t* data_ptrs, const uint64_t* flag_ptrs, int* ctrl,
-                   int t_max, int n_max, int max_tiles, unsigned long long timeout_ns, const void* residual) {
-  memset(&ar, 0, sizeof(ar));
-  ar.mode = world >= g_oxb_ar_ll_min_world ? 1 : 0;
-  ar.trace = g_oxb_ar_trace;
-  if (world < 1 || world > AR_MAX_WORLD || rank < 0 || rank >= world || ctrl == nullptr) return (int)cudaErrorInvalidValue;
-  ar.world = world;
-  ar.rank = rank;
-  ar.t_max = t_max;
-  ar.n_max = n_max;
-  ar.max_tiles = max_tiles;
-  ar.timeout_ns = timeout_ns;
-  ar.ctrl = ctrl;
-  ar.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
-  for (int i = 0; i < world; ++i) {
-    ar.data[i] = reinterpret_cast<__nv_bfloat16*>(data_ptrs[i]);
-    ar.flags[i] = reinterpret_cast<uint32_t*>(flag_ptrs[i]);
-  }
-  return 0;
-}
-
-// Row-parallel GEMM fused with a one-shot all-reduce over peer memory:
-//   Y[T, N] = sum over ranks of X_r[T, K_r] · W_r[N, K_r]^T  (+ residual), identical on every rank.
-// data_ptrs / flag_ptrs: every rank's symmetric receive buffer [2][world+1][t_max][n_max] bf16 and flag
-// array [2][world+1][max_tiles] u32 (zeroed once); ctrl: 2 local ints, zeroed once.
-// Limits: T <= min(t_max, 256), N <= n_max, N % 8 == 0, N/128 <= max_tiles, and the whole grid must be
-// co-resident (<= SM count) because CTAs wait on their peers' copies of the same tile.
-OXB_API int oxb_gemm_ar(const void* X, const void* W, void* Y, const void* residual, int T, int N, int K, int ldY,
-                        int world, int rank, const uint64_t* data_ptrs, const uint64_t* flag_ptrs, int* ctrl, int t_max,
-                        int n_max, int max_tiles, unsigned long long timeout_ns, void* ws, size_t ws_bytes, int* counters,
-                        int n_counters, cudaStream_t stream) {
-  if (T <= 0 || N <= 0 || K <= 0) return 0;
-  const int ll = world >= g_oxb_ar_ll_min_world;
-  if (K % 8 != 0 || N % 8 != 0 || (T > 256 && !ll) || T > t_max || N > n_max) return (int)cudaErrorInvalidValue;
-  GemmPlan p;
-  if (T <= 256) {
-    // CTAs wait for the CTAs with the same piece index on the other GPUs, so the whole grid is kept
-    // resident at once on every rank: bound tiles*splits by what the SMs can hold.
-    int resident = sm_count() * (T <= 64 ? GemmTile<64>::CTAS_PER_SM : 1);
-    if (!ll && resident > max_tiles) resident = max_tiles;  // the one-shot exchange has one flag per piece
-    p = gemm_plan(T, N, K, 0, sm_count(), -1, resident);
-    while (p.splits > 1 && !p.cluster && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || ws == nullptr ||
-                                          counters == nullptr || p.n_tiles * p.splits > sm_count()))
-      p = gemm_plan(T, N, K, p.splits - 1, sm_count(), -1, resident);
-    if (p.n_tiles * p.splits > resident || p.t_tiles != 1) return (int)cudaErrorInvalidConfiguration;
-  } else {
-    // Prefill-sized calls (LL exchange only): several waves of 256-token tiles, no split-K.  A tile's
-    // exchange overlaps the MMAs of the tiles behind it.  Progress relies on both ranks dispatching
-    // CTAs in block-index order, so that the lowest unfinished piece is resident everywhere; the
-    // bounded polls turn a violation into an error status, not a hang.
-    p = gemm_plan(T, N, K, 1, sm_count(), 0);
-  }
-  ArArgs ar;
-  int e = fill_ar(ar, world, rank, data_ptrs, flag_ptrs, ctrl, t_max, n_max, max_tiles, timeout_ns, residual);
-  if (e) return e;
-  CUtensorMap tmW, tmX;
-  e = oxb_make_tmap_2d(&tmW, W, N, K, (uint64_t)K * 2, GEMM_BM, GEMM_BK, 2);
-  if (e) return e;
-  e = oxb_make_tmap_2d(&tmX, X, T, K, (uint64_t)K * 2, p.tn, GEMM_BK, 2);
-  if (e) return e;
-  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(Y);
-  float* wsf = reinterpret_cast<float*>(ws);
-  switch (p.tn) {
-    case 16: return gemm_launch<16>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream);
-    case 32: return gemm_launch<32>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream);
-    case 64: return gemm_launch<64>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream);
-    case 128: return gemm_launch<128>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream);
-    default: return gemm_launch<256>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream);
-  }
 }
 
 // One-shot all-reduce (sum) of X[T, N] bf16 (row stride ld) into Y through the same symmetric buffers.
@@ -375,6 +233,16 @@ OXB_API int oxb_add_rmsnorm(const void* x, const void* res_in, void* res_out, co
   return 0;
 }
 
+// out[t] = fixed-point sum of squares of row t of x[T, H] (bf16); `clear` (optional, [T]) is reset to zero.
+OXB_API int oxb_row_sumsq(const void* x, int ldx, int T, int H, void* out, void* clear, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H % 8 != 0 || ldx % 8 != 0) return (int)cudaErrorInvalidValue;
+  oxb_launch(row_sumsq_kernel, dim3((T + 7) / 8), dim3(256), 0, stream, reinterpret_cast<const __nv_bfloat16*>(x), ldx, T, H,
+             reinterpret_cast<unsigned long long*>(out), reinterpret_cast<unsigned long long*>(clear));
+  OXB_CHECK_LAUNCH();
+  return 0;
+}
+
 OXB_API int oxb_silu_mul(const void* gu, void* out, int T, int I, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (I % 8 != 0) return (int)cudaErrorInvalidValue;
@@ -402,42 +270,41 @@ OXB_API int oxb_qk_rope_kvwrite(const void* qkv, const int* positions, const int
   return 0;
 }
 
-// Fused qkv projection: qkv = X · Wqkv^T with RoPE + KV write as the GEMM's epilogue (EPI_ROPE).  Wqkv rows
-// are [nq heads | nkv key heads | nkv value heads] of head_dim 128; bf16 KV pages only; full rotary (rot == 128).
-OXB_API int oxb_gemm_qkv_rope(const void* X, const void* W, int T, int K, const int* positions, const int* slots,
-                              const float* cos_sin, int max_pos, int rot, int pairing, int nq, int nkv, void* q_out,
-                              void* kv_data, int page, int num_blocks, cudaStream_t stream) {
-  if (T <= 0) return 0;
-  const int N = (nq + 2 * nkv) * 128;
-  if (K % 8 != 0 || rot != 128 || page <= 0 || (reinterpret_cast<uintptr_t>(q_out) & 15) != 0 ||
-      (reinterpret_cast<uintptr_t>(kv_data) & 15) != 0)
-    return (int)cudaErrorInvalidValue;
-  GemmPlan p = gemm_plan(T, N, K, 0, sm_count(), 1);
-  CUtensorMap tmW, tmX;
-  int e = oxb_make_tmap_2d(&tmW, W, N, K, (uint64_t)K * 2, GEMM_BM, GEMM_BK, 2);
-  if (e) return e;
-  e = oxb_make_tmap_2d(&tmX, X, T, K, (uint64_t)K * 2, p.tn, GEMM_BK, 2);
-  if (e) return e;
-  ArArgs ar;
-  memset(&ar, 0, sizeof(ar));
-  RopeArgs ro{positions, slots, cos_sin, max_pos, rot, pairing, nq, nkv, page, num_blocks, reinterpret_cast<__nv_bfloat16*>(q_out),
-              reinterpret_cast<__nv_bfloat16*>(kv_data)};
-  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(q_out);  // only its alignment is looked at
-  const QwArgs qw{nullptr, 0, nullptr, 0, 0};
-  const GroupArgs gr{0, 0, 0, 0, nullptr, 0, 0};
-  switch (p.tn) {
-    case 16: return gemm_launch<16>(tmW, tmX, y, nullptr, N, T, K, N, p, nullptr, nullptr, EPI_ROPE, ar, stream, qw, gr, 1, ro);
-    case 32: return gemm_launch<32>(tmW, tmX, y, nullptr, N, T, K, N, p, nullptr, nullptr, EPI_ROPE, ar, stream, qw, gr, 1, ro);
-    case 64: return gemm_launch<64>(tmW, tmX, y, nullptr, N, T, K, N, p, nullptr, nullptr, EPI_ROPE, ar, stream, qw, gr, 1, ro);
-    case 128: return gemm_launch<128>(tmW, tmX, y, nullptr, N, T, K, N, p, nullptr, nullptr, EPI_ROPE, ar, stream, qw, gr, 1, ro);
-    default: return gemm_launch<256>(tmW, tmX, y, nullptr, N, T, K, N, p, nullptr, nullptr, EPI_ROPE, ar, stream, qw, gr, 1, ro);
-  }
-}
-
 OXB_API int oxb_argmax(const float* logits, int R, int V, int ld, int tie_highest, int* out, float* out_val,
                        int index_offset, cudaStream_t stream) {
   if (R <= 0) return 0;
   oxb_launch(argmax_kernel, dim3(R), dim3(1024), 0, stream, logits, V, ld, tie_highest, out, out_val, index_offset);
+  OXB_CHECK_LAUNCH();
+  return 0;
+}
+
+// Greedy token per row of this rank's logits shard [R, V] (dtype: 0 = fp32, 2 = bf16), exchanged with the other
+// tensor-parallel ranks inside the kernel when world > 1 (peer_bufs: every rank's exchange buffer
+// [2][world][rmax][2] u64, zeroed once; ctrl: 2 local ints, zeroed once).  out2 (optional) receives the tokens too.
+OXB_API int oxb_argmax_tp(const void* logits, int dtype, int R, int V, int ld, int tie_highest, int* out, int* out2,
+                          int index_offset, int world, int rank, const uint64_t* peer_bufs, int* ctrl, int rmax,
+                          unsigned long long timeout_ns, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  ArgmaxXchg xa;
+  memset(&xa, 0, sizeof(xa));
+  if (world > 1) {
+    if (world > 8 || rank < 0 || rank >= world || peer_bufs == nullptr || ctrl == nullptr || R > rmax) return (int)cudaErrorInvalidValue;
+    xa.world = world;
+    xa.rank = rank;
+    xa.ctrl = ctrl;
+    xa.rmax = rmax;
+    xa.timeout_ns = timeout_ns;
+    for (int i = 0; i < world; ++i) xa.bufs[i] = reinterpret_cast<unsigned long long*>(peer_bufs[i]);
+  }
+  if (dtype == 0) {
+    oxb_launch(argmax_tp_kernel<float>, dim3(R), dim3(1024), 0, stream, reinterpret_cast<const float*>(logits), V, ld, tie_highest,
+               out, out2, index_offset, xa);
+  } else if (dtype == 2) {
+    oxb_launch(argmax_tp_kernel<__nv_bfloat16>, dim3(R), dim3(1024), 0, stream, reinterpret_cast<const __nv_bfloat16*>(logits), V,
+               ld, tie_highest, out, out2, index_offset, xa);
+  } else {
+    return (int)cudaErrorInvalidValue;
+  }
   OXB_CHECK_LAUNCH();
   return 0;
 }
@@ -451,134 +318,6 @@ OXB_API int oxb_sample(const float* logits, int R, int V, int ld, const float* t
              tie_highest, out);
   OXB_CHECK_LAUNCH();
   return 0;
-}
-
-// ----------------------------------------------------------------------------- attention
-// Sizes of the split-KV scratch for a launch shape (floats).
-OXB_API int oxb_attn_ws_floats(int B, int nkv, int max_mtiles, int n_cta_splits, int hd, size_t* o_floats,
-                               size_t* ml_floats) {
-  const size_t tasks = (size_t)B * nkv * max_mtiles * n_cta_splits;
-  *o_floats = n_cta_splits > 1 ? tasks * 16 * hd : 0;
-  *ml_floats = n_cta_splits > 1 ? tasks * 16 * 2 : 0;
-  return 0;
-}
-
-template <int HD>
-static int attn_launch(const AttnArgs& a, int B, int G, cudaStream_t stream) {
-  constexpr int STAGE = 32 * (HD * 2 + 16);
-  constexpr int SMEM_MAX = ATT_WARPS * (ATT_STAGES + 1) * STAGE;
-  // quantized KV needs one extra decode buffer per warp
-  const int smem = ATT_WARPS * (ATT_STAGES + (a.kv_mode >= 2 ? 1 : 0)) * STAGE;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(paged_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_MAX);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
-  dim3 grid(a.max_mtiles * a.n_cta_splits, a.nkv, B);
-  // (Merging the KV splits of a row tile inside a thread-block cluster was measured and is slower here:
-  // every CTA then waits for the slowest split, 21.7 vs 19.0 us on 64 x 1400-token decode.  The splits
-  // stay independent CTAs; the last one to finish merges.)
-  if (a.n_cta_splits > 1 && (a.ws_o == nullptr || a.ws_ml == nullptr || a.counters == nullptr)) return (int)cudaErrorInvalidValue;
-  oxb_launch(paged_attention_kernel<HD>, grid, dim3(ATT_WARPS * 32), (size_t)smem, stream, a, G);
-  OXB_CHECK_LAUNCH();
-  return 0;
-}
-
-OXB_API int oxb_paged_attention(const void* q, void* out, const void* kv_data, const float* kv_scales,
-                                const int* block_tables, const int* seq_lens, const int* query_start, int B,
-                                int max_blocks, int nq, int nkv, int hd, int kv_mode, int max_query_len,
-                                int n_cta_splits, int window, float scale, float* ws_o, float* ws_ml, int* counters,
-                                int num_blocks, cudaStream_t stream) {
-  if (B <= 0) return 0;
-  if (nq % nkv != 0) return (int)cudaErrorInvalidValue;
-  const int G = nq / nkv;
-  AttnArgs a;
-  a.q = reinterpret_cast<const __nv_bfloat16*>(q);
-  a.out = reinterpret_cast<__nv_bfloat16*>(out);
-  a.kv_data = kv_data;
-  a.kv_scales = kv_scales;
-  a.block_tables = block_tables;
-  a.seq_lens = seq_lens;
-  a.query_start = query_start;
-  a.max_blocks = max_blocks;
-  a.nq = nq;
-  a.nkv = nkv;
-  a.kv_mode = kv_mode;
-  a.n_cta_splits = n_cta_splits < 1 ? 1 : n_cta_splits;
-  a.max_mtiles = (max_query_len * G + 15) / 16;
-  a.window = window;
-  a.scale_log2 = scale * 1.4426950408889634f;
-  a.ws_o = ws_o;
-  a.ws_ml = ws_ml;
-  a.counters = counters;
-  a.num_blocks = num_blocks;
-  a.trace = g_oxb_attn_trace;
-  if (hd == 128) return attn_launch<128>(a, B, G, stream);
-  if (hd == 64) return attn_launch<64>(a, B, G, stream);
-  return (int)cudaErrorInvalidValue;
-}
-
-// ----------------------------------------------------------------------------- allocation-free GEMM
-// See oxb_noalloc.h for the contract.  The split-K scratch of the GEMM lives in this fixed device
-// array: [0, 16 KiB) rendezvous counters, the rest fp32 partials.
-#include "oxb_noalloc.h"
-#include <stdio.h>
-
-static __device__ __align__(256) unsigned char g_noalloc_scratch[OXB_NOALLOC_SCRATCH_BYTES];
-
-// In host code `g_noalloc_scratch` is only a handle for the runtime, not a device address, so the
-// address is looked up once per device and cached here.
-static void* g_noalloc_dev_ptr[64] = {nullptr};
-
-extern "C" __attribute__((visibility("default"))) int oxb_gemm_bf16_noalloc(
-    const void* X, const void* W, void* Y, const float* bias, int T, int N, int K, int ldY, void* cuda_stream) {
-  cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
-  if (X == nullptr || W == nullptr || Y == nullptr || T <= 0 || N <= 0 || K <= 0 || K % 8 != 0 || ldY < N)
-    return OXB_NOALLOC_E_BAD_ARGUMENT;
-  if (T > OXB_NOALLOC_MAX_TOKENS) {
-    fprintf(stderr, "oxb_gemm_bf16_noalloc: T=%d exceeds the limit of %d tokens per call (static scratch of %d bytes)\n",
-            T, OXB_NOALLOC_MAX_TOKENS, (int)OXB_NOALLOC_SCRATCH_BYTES);
-    return OXB_NOALLOC_E_TOO_LARGE;
-  }
-  int dev = 0;
-  cudaError_t ce = cudaGetDevice(&dev);
-  if (ce != cudaSuccess) return (int)ce;
-  if (dev < 0 || dev >= 64) return OXB_NOALLOC_E_BAD_ARGUMENT;
-  if (g_noalloc_dev_ptr[dev] == nullptr) {
-    void* p = nullptr;
-    ce = cudaGetSymbolAddress(&p, g_noalloc_scratch);
-    if (ce != cudaSuccess) return (int)ce;
-    g_noalloc_dev_ptr[dev] = p;
-  }
-  unsigned char* base = reinterpret_cast<unsigned char*>(g_noalloc_dev_ptr[dev]);
-  int* counters = reinterpret_cast<int*>(base);
-  float* ws = reinterpret_cast<float*>(base + OXB_NOALLOC_COUNTER_BYTES);
-  const size_t ws_bytes = OXB_NOALLOC_SCRATCH_BYTES - OXB_NOALLOC_COUNTER_BYTES;
-  const int n_counters = OXB_NOALLOC_COUNTER_BYTES / (int)sizeof(int);
-  GemmPlan p = gemm_plan(T, N, K, 0, sm_count(), 0);  // always the global-scratch split-K: that is what this entry is for
-  while (p.splits > 1 && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || p.n_tiles * p.t_tiles * p.splits > sm_count()))
-    p = gemm_plan(T, N, K, p.splits - 1, sm_count(), 0);
-  if (p.splits > 1) {
-    // the counters must start at zero; an earlier call that gave up could have left them set
-    ce = cudaMemsetAsync(counters, 0, (size_t)p.n_counters * sizeof(int), stream);
-    if (ce != cudaSuccess) return (int)ce;
-  }
-  CUtensorMap tmW, tmX;
-  int e = oxb_make_tmap_2d(&tmW, W, N, K, (uint64_t)K * 2, GEMM_BM, GEMM_BK, 2);
-  if (e) return e;
-  e = oxb_make_tmap_2d(&tmX, X, T, K, (uint64_t)K * 2, p.tn, GEMM_BK, 2);
-  if (e) return e;
-  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(Y);
-  ArArgs ar;
-  memset(&ar, 0, sizeof(ar));
-  switch (p.tn) {
-    case 16: return gemm_launch<16>(tmW, tmX, y, bias, N, T, K, ldY, p, ws, counters, 0, ar, stream);
-    case 32: return gemm_launch<32>(tmW, tmX, y, bias, N, T, K, ldY, p, ws, counters, 0, ar, stream);
-    case 64: return gemm_launch<64>(tmW, tmX, y, bias, N, T, K, ldY, p, ws, counters, 0, ar, stream);
-    case 128: return gemm_launch<128>(tmW, tmX, y, bias, N, T, K, ldY, p, ws, counters, 0, ar, stream);
-    default: return gemm_launch<256>(tmW, tmX, y, bias, N, T, K, ldY, p, ws, counters, 0, ar, stream);
-  }
 }
 
 // ----------------------------------------------------------------------------- mixture of experts
@@ -611,56 +350,3 @@ OXB_API int oxb_moe_combine(const void* y, const float* scale, int scale_ld, con
   return 0;
 }
 
-// Grouped GEMM over `groups` experts in ONE launch: for group g,
-//   Y[g] [T, N] = X_g [T, K] · W_g [N, K]^T,   W stacked as [(groups*N), K] (bf16 or packed rows),
-//   X_g = X + g*x_rows rows (x_rows = 0: every group reads the same X),  Y[g] = Y + g*y_stride elements.
-// Groups whose `scale` row (per-token routing weights, [groups, scale_ld]) is all zero are skipped on the
-// device.  T <= 256.
-OXB_API int oxb_gemm_grouped(const void* X, int x_rows, const void* W, int qtype, size_t row_bytes, void* Y,
-                             long long y_stride, const float* scale, int scale_ld, int groups, int T, int N, int K,
-                             int ldY, void* ws, size_t ws_bytes, int* counters, int n_counters, cudaStream_t stream) {
-  if (T <= 0 || N <= 0 || K <= 0 || groups <= 0) return 0;
-  if (T > 256 || K % 64 != 0) return (int)cudaErrorInvalidValue;
-  GemmPlan p = gemm_plan(T, N, K, 0, sm_count());
-  while (p.splits > 1 && !p.cluster && (p.ws_bytes * groups > ws_bytes || p.n_counters * groups > n_counters || ws == nullptr ||
-                          counters == nullptr || p.n_tiles * p.splits * groups > sm_count()))
-    p = gemm_plan(T, N, K, p.splits - 1, sm_count());
-  CUtensorMap tmW, tmX;
-  const uint64_t xr = x_rows > 0 ? (uint64_t)groups * x_rows : (uint64_t)T;
-  int e = oxb_make_tmap_2d(&tmX, X, xr, K, (uint64_t)K * 2, p.tn, GEMM_BK, 2);
-  if (e) return e;
-  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(Y);
-  float* wsf = reinterpret_cast<float*>(ws);
-  ArArgs ar;
-  memset(&ar, 0, sizeof(ar));
-  GroupArgs gr{1, N, x_rows, y_stride, scale, scale_ld, 0};
-  QwArgs qw{reinterpret_cast<const uint8_t*>(W), row_bytes, nullptr, 0, 0};
-  if (qtype == QT_BF16) {
-    e = oxb_make_tmap_2d(&tmW, W, (uint64_t)groups * N, K, (uint64_t)K * 2, GEMM_BM, GEMM_BK, 2);
-    if (e) return e;
-    switch (p.tn) {
-      case 16: return gemm_launch<16>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
-      case 32: return gemm_launch<32>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
-      case 64: return gemm_launch<64>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
-      case 128: return gemm_launch<128>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
-      default: return gemm_launch<256>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
-    }
-  }
-  switch (qtype) {
-    case QT_Q4_K:
-    case QT_Q6_K: {
-      CUtensorMap tmWq;
-      const int box = qtype == QT_Q4_K ? MmqStage<QT_Q4_K>::BOX : MmqStage<QT_Q6_K>::BOX;
-      if (p.tn <= 64 && oxb_make_tmap_bytes(&tmWq, W, (uint64_t)groups * N, row_bytes, GEMM_BM, box) == 0) qw.staged = 1;
-      if (qtype == QT_Q4_K)
-        return gemm_launch_mmq<QT_Q4_K>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups,
-                                        qw.staged ? &tmWq : nullptr);
-      return gemm_launch_mmq<QT_Q6_K>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups,
-                                      qw.staged ? &tmWq : nullptr);
-    }
-    case QT_Q8_0: return gemm_launch_mmq<QT_Q8_0>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
-    case QT_Q4_0: return gemm_launch_mmq<QT_Q4_0>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
-    case QT_NVFP4: return gemm_launch_mmq<QT_NVFP4>(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
-    default: return (int)cudaErrorInvalidValue;
-  }
-}

@@ -146,7 +146,7 @@ __device__ void radix_descend(const float* row, int V, float mx, float inv_t, in
   mass_above = ma;
 }
 
-__global__ void __launch_bounds__(SMP_THREADS)
+static __global__ void __launch_bounds__(SMP_THREADS)
 sample_kernel(const float* __restrict__ logits, int V, int ld, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
               const float* __restrict__ random, int tie_highest, int* __restrict__ out) {

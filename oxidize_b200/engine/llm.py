@@ -24,7 +24,7 @@ from ..utils import profiler as _profiler
 from .kv_pool import BlockPool, KVCache, KVCacheSpec, make_block_pool
 from .runner import ModelRunner, StepResult
 from .sampler import SamplingParams
-from .scheduler import Scheduler, SchedulerConfig, SchedulerOutput, Sequence
+from .scheduler import ScheduledSeq, Scheduler, SchedulerConfig, SchedulerOutput, Sequence
 
 
 @dataclass
@@ -46,6 +46,13 @@ class EngineConfig:
     ep_size: int = 0  # experts partitioned over this many ranks; 0 = tp_size, 1 = replicated on every rank
     pp_size: int = 1
     fused_comm: bool = True
+    fold_norms: bool = True  # dense bf16 layers: RMSNorm folded into the GEMM epilogues around it (GPU only)
+    # Steady-state greedy decode: launch step k+1 (input ids taken from step k's kernel on the device) before
+    # reading step k's tokens, so that the host's scheduling and batch building overlap the GPU's work.
+    async_decode: bool = True
+    fuse_qkv_rope: bool = True  # RoPE + KV write as the qkv GEMM's epilogue where the shapes allow
+    fuse_swiglu: bool = True  # SiLU(gate) * up as the gate_up GEMM's epilogue for dense bf16 FFNs
+    kernel_options: Optional[object] = None  # ops.cuda.KernelOptions; None = the library's defaults
     eos_token_id: Optional[int] = None
 
 
@@ -68,7 +75,12 @@ class LLM:
         c = self.config
         self.weights = weights
         self.cfg: ModelConfig = weights.cfg
-        self.model = Transformer(weights, comm)
+        if weights.embed.device.type == "cuda" and c.kernel_options is not None:
+            from ..ops import cuda as _opcuda
+
+            _opcuda.configure(c.kernel_options)
+        self.model = Transformer(weights, comm, fold_norms=c.fold_norms, fuse_qkv_rope=c.fuse_qkv_rope,
+                                 fuse_swiglu=c.fuse_swiglu)
         self.device = self.model.device
         self.tokenizer = tokenizer
         kv_dtype = c.kv_cache_dtype
@@ -147,19 +159,37 @@ class LLM:
 
     @property
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_work
+        return self.scheduler.has_work or getattr(self, "_inflight", None) is not None
 
     def step(self) -> List[RequestOutput]:
-        """One engine iteration: schedule → forward → sample → postprocess."""
+        """One engine iteration: schedule → forward → sample → postprocess.
+
+        In the steady state of greedy decoding the engine keeps one step in flight: before it waits for the tokens
+        of step k it has already launched step k+1 for the same sequences, whose input ids never leave the device
+        (the role of the reference's device-resident ``{token, pos, step}`` state,
+        ``oxidize-c/src/backends/cuda_fast.cu:58-63,495``).  A call then returns the results of the step launched
+        one call earlier.  A sequence that turns out to have ended on step k (EOS, stop sequence, abort) has one
+        surplus row in step k+1, whose token is dropped."""
         spec = getattr(self, "spec", None)
-        if spec is not None:
-            spec.before_schedule(self)
-        out = self.scheduler.schedule()
-        if out.is_empty:
-            if self.scheduler.has_work and not out.preempted:
-                raise RuntimeError("scheduler made no progress: KV pool too small for the waiting request")
-            return []
-        res = self.runner.execute(out)
+        inflight = getattr(self, "_inflight", None)
+        if inflight is not None:
+            out, pending = inflight
+            self._inflight = None
+        else:
+            if spec is not None:
+                spec.before_schedule(self)
+            out = self.scheduler.schedule()
+            if out.is_empty:
+                if self.scheduler.has_work and not out.preempted:
+                    raise RuntimeError("scheduler made no progress: KV pool too small for the waiting request")
+                return []
+            pending = self.runner.launch(out)
+        if self.config.async_decode and spec is None:
+            nxt = self._schedule_ahead(out, pending)
+            if nxt is not None:
+                self._inflight = (nxt, self.runner.launch(nxt, tokens_on_device=True))
+        was_finished = [ss.seq.is_finished for ss in out.scheduled]
+        res = self.runner.collect(pending)
         if spec is not None:
             res.tokens = spec.after_forward(self, out, res.tokens)
         now = time.perf_counter()
@@ -175,10 +205,61 @@ class LLM:
         st["d2h_bytes"] += res.d2h_bytes
         self.last_step = (out, res)
         outs = []
-        for ss in out.scheduled:
+        for ss, gone in zip(out.scheduled, was_finished):
+            if gone:
+                continue  # ended on the step before: this row ran ahead for nothing
             if ss.sample or ss.seq.is_finished:
                 outs.append(self._output(ss.seq))
         return outs
+
+    def drain(self) -> List[RequestOutput]:
+        """Finish the step that is in flight, if any, without launching another one ahead of it."""
+        if getattr(self, "_inflight", None) is None:
+            return []
+        keep, self.config.async_decode = self.config.async_decode, False
+        try:
+            return self.step()
+        finally:
+            self.config.async_decode = keep
+
+    def _schedule_ahead(self, out: SchedulerOutput, pending) -> Optional[SchedulerOutput]:
+        """The decode step that follows ``out`` if nothing unexpected happens, or None when the next step needs the
+        scheduler proper: anything but a pure greedy graph-replayed decode step, requests waiting, a sequence about
+        to reach its token limit, or a KV pool that cannot give every sequence its next slot."""
+        sch = self.scheduler
+        if pending is None or pending.bucket == 0 and self.device.type == "cuda":
+            return None
+        if pending.host_rows or pending.keep_logits or not pending.seq_ids:
+            return None
+        if sch.waiting or len(out.scheduled) != len(sch.running) or out.cow_copies or out.preempted:
+            return None
+        ps = self.pool.page_size
+        nxt = SchedulerOutput([])
+        max_len = self.config.max_model_len
+        for ss in out.scheduled:
+            seq = ss.seq
+            if ss.is_prefill or ss.num_tokens != 1 or not ss.sample or seq.is_finished or seq.draft_tokens:
+                return None
+            p = seq.params
+            if not p.is_greedy or p.needs_host_sampler:
+                return None
+            # after the step in flight the sequence holds one more token; the step after it must still be wanted
+            produced = len(seq.output) + len(getattr(seq, "_preempted_outputs", ())) + 1
+            if produced >= p.max_tokens:
+                return None
+            start = ss.start + 1
+            if start + 1 > max_len:
+                return None
+            nxt.scheduled.append(ScheduledSeq(seq, start, 1, False, True))
+        # every sequence needs a slot for position `start`; nothing is taken unless all of them can have one
+        need = sum(1 for s2 in nxt.scheduled if (s2.start + ps) // ps > len(s2.seq.blocks))
+        if need and not self.pool.can_allocate(need):
+            return None
+        for s2 in nxt.scheduled:
+            while (s2.start + ps) // ps > len(s2.seq.blocks):
+                s2.seq.blocks.append(self.pool.allocate())
+        nxt.num_decode_tokens = len(nxt.scheduled)
+        return nxt
 
     def _output(self, seq: Sequence) -> RequestOutput:
         # A running request's output references the sequence's own lists (no per-step copies of the

@@ -50,12 +50,25 @@ class StagingBuffers:
             off += n4
         self.total = off
         pin = device.type == "cuda"
-        self.host = torch.zeros(self.total, dtype=torch.int32, pin_memory=pin)
-        self.host_np = self.host.numpy()
-        self.host_f = self.host_np.view(np.float32)
+        # Two pinned host copies, used alternately: with one step running ahead of the host (LLM.step), the copy of
+        # step k may not have been read by the copy engine yet when the host fills in step k + 1.
+        self.hosts = [torch.zeros(self.total, dtype=torch.int32, pin_memory=pin) for _ in range(2 if pin else 1)]
+        self._np = [h.numpy() for h in self.hosts]
+        self._npf = [a.view(np.float32) for a in self._np]
+        self.which = 0
+        self.host = self.hosts[0]
+        self.host_np = self._np[0]
+        self.host_f = self._npf[0]
         self.dev = torch.zeros(self.total, dtype=torch.int32, device=device) if pin else self.host
         self.device = device
         self._float_names = {n for n, _ in fsizes}
+        self.tokens_end = self.offsets["positions"][0]  # the token ids are the first section
+
+    def flip(self) -> int:
+        """Switch to the other host copy; returns its index."""
+        self.which = (self.which + 1) % len(self.hosts)
+        self.host, self.host_np, self.host_f = self.hosts[self.which], self._np[self.which], self._npf[self.which]
+        return self.which
 
     def h(self, name: str) -> np.ndarray:
         o, n = self.offsets[name]
@@ -66,11 +79,12 @@ class StagingBuffers:
         v = self.dev[o : o + (full if n is None else n)]
         return v.view(torch.float32) if name in self._float_names else v
 
-    def upload(self) -> int:
-        """Async H2D of the whole staging area; returns bytes moved."""
+    def upload(self, skip_tokens: bool = False) -> int:
+        """Async H2D of the staging area (without the token ids when the device already holds them); returns bytes moved."""
+        o = self.tokens_end if skip_tokens else 0
         if self.dev is not self.host:
-            self.dev.copy_(self.host, non_blocking=True)
-        return self.total * 4
+            self.dev[o:].copy_(self.host[o:], non_blocking=True)
+        return (self.total - o) * 4
 
 
 @dataclass
@@ -80,6 +94,23 @@ class StepResult:
     h2d_bytes: int = 0
     d2h_bytes: int = 0
     launches: int = 0
+
+
+@dataclass
+class Pending:
+    """A launched step whose sampled tokens have not been read back yet."""
+
+    rows: list
+    n_out: int
+    toks: Optional[torch.Tensor]
+    host_buf: Optional[torch.Tensor]
+    event: object
+    logits: Optional[torch.Tensor]
+    host_rows: list
+    keep_logits: bool
+    h2d_bytes: int
+    bucket: int = 0  # decode-graph bucket the step replayed, 0 = eager
+    seq_ids: tuple = ()  # row order of the step (decode-only steps)
 
 
 class ModelRunner:
@@ -94,9 +125,11 @@ class ModelRunner:
         self.use_graphs = use_cuda_graphs and self.device.type == "cuda"
         self.graphs: Dict[int, "torch.cuda.CUDAGraph"] = {}
         self.graph_out: Dict[int, torch.Tensor] = {}
-        self.out_host = torch.zeros(max(max_tokens, max_seqs), dtype=torch.int32,
-                                    pin_memory=self.device.type == "cuda")
+        self.out_hosts = [torch.zeros(max(max_tokens, max_seqs), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+                          for _ in range(2)]
+        self._out_which = 0
         self.keep_logits = False
+        self._bt_owners = [[None] * max_seqs for _ in self.buf.hosts]
 
     # ------------------------------------------------------------------ batch building
     def build(self, scheduled: Sequence[ScheduledSeq], pad_to: Optional[int] = None):
@@ -111,7 +144,7 @@ class ModelRunner:
         max_len = 0
         rows: List[Tuple[ScheduledSeq, int, int]] = []  # (ss, first logits row, n rows)
         qs[0] = 0
-        self._bt_owner = [None] * b.max_seqs  # this path rewrites block-table rows: the decode path's record is void
+        self._bt_owners[b.which] = [None] * b.max_seqs  # this path rewrites block-table rows: the decode path's record is void
         for i, ss in enumerate(scheduled):
             seq = ss.seq
             n = ss.num_tokens
@@ -177,7 +210,7 @@ class ModelRunner:
             B = pad_to
         return t, B, nl, max_q, max_len, rows
 
-    def build_decode(self, scheduled: Sequence[ScheduledSeq], pad_to: Optional[int] = None):
+    def build_decode(self, scheduled: Sequence[ScheduledSeq], pad_to: Optional[int] = None, skip_tokens: bool = False):
         """``build`` for the steady state: every sequence feeds exactly one decode row.  Whole-column
         writes instead of per-row scalar stores, and a block-table row is rewritten only when its
         sequence or that sequence's block list changed since the previous step."""
@@ -188,9 +221,7 @@ class ModelRunner:
         tok, pos, slot = b.h("token_ids"), b.h("positions"), b.h("slot_mapping")
         qs, sl, li, bt = b.h("query_start"), b.h("seq_lens"), b.h("logits_indices"), b.h("block_tables")
         M, ps = self.max_blocks, self.page
-        owner = getattr(self, "_bt_owner", None)
-        if owner is None or len(owner) != b.max_seqs:
-            owner = self._bt_owner = [None] * b.max_seqs
+        owner = self._bt_owners[b.which]
         ar = getattr(self, "_arange", None)
         if ar is None:
             ar = self._arange = np.arange(max(b.max_seqs, b.max_tokens) + 1, dtype=np.int32)
@@ -203,7 +234,8 @@ class ModelRunner:
             if owner[i] != key:
                 bt[i * M : i * M + nb] = bl
                 owner[i] = key
-        tok[:n] = [seq.token_at(st) for seq, st in zip(seqs, starts)]
+        if not skip_tokens:  # (skipped: the previous step's kernel left the ids in the device copy)
+            tok[:n] = [seq.token_at(st) for seq, st in zip(seqs, starts)]
         pos[:n] = starts
         slot[:n] = [seq.blocks[st // ps] * ps + st % ps for seq, st in zip(seqs, starts)]
         np.add(pos[:n], 1, out=sl[:n])
@@ -224,7 +256,8 @@ class ModelRunner:
         if pad_to is not None and pad_to > B:
             # dummy sequences: zero context, no KV write; their logits rows are ignored
             k = pad_to - B
-            tok[t : t + k] = 0
+            if not skip_tokens:
+                tok[t : t + k] = 0
             pos[t : t + k] = 0
             slot[t : t + k] = -1
             sl[B:pad_to] = 0
@@ -258,18 +291,19 @@ class ModelRunner:
                 rnd[j] = ss.seq.rng.next()
         return all_greedy
 
-    def _meta(self, T: int, B: int, nl: int, max_q: int, max_len: int) -> BatchMeta:
+    def _meta(self, T: int, B: int, nl: int, max_q: int, max_len: int, logits_all: bool = False) -> BatchMeta:
         b = self.buf
         return BatchMeta(
+            logits_all=logits_all,
             token_ids=b.d("token_ids", T), positions=b.d("positions", T), slot_mapping=b.d("slot_mapping", T),
             query_start=b.d("query_start", B + 1), seq_lens=b.d("seq_lens", B),
             block_tables=b.d("block_tables").view(b.max_seqs, self.max_blocks)[:B],
             logits_indices=b.d("logits_indices", nl), max_query_len=max_q, max_seq_len=max_len, num_seqs=B)
 
     # ------------------------------------------------------------------ execution
-    def _forward_sample(self, meta: BatchMeta, all_greedy: bool, tie: str):
+    def _forward_sample(self, meta: BatchMeta, all_greedy: bool, tie: str, feed: Optional[torch.Tensor] = None):
         if all_greedy and not self.keep_logits:
-            return self.model.greedy_tokens(meta, self.kv, tie), None
+            return self.model.greedy_tokens(meta, self.kv, tie, feed=feed), None
         logits = self.model.forward(meta, self.kv)
         if all_greedy:
             return ops.argmax(logits, tie), logits
@@ -281,9 +315,16 @@ class ModelRunner:
                                      b.d("min_p", nl), b.d("random", nl), tie), logits
 
     def execute(self, out: SchedulerOutput, needs_host_logits: bool = False) -> StepResult:
+        p = self.launch(out, needs_host_logits)
+        return self.collect(p) if p is not None else StepResult({})
+
+    def launch(self, out: SchedulerOutput, needs_host_logits: bool = False, tokens_on_device: bool = False) -> Optional[Pending]:
+        """Build, upload and enqueue one step and the copy of its sampled tokens to the host, without waiting for it.
+        ``tokens_on_device``: the step continues the decode step launched just before it with the same sequences in
+        the same rows, whose kernel left each row's next input id in the device staging buffer."""
         scheduled = out.scheduled
         if not scheduled:
-            return StepResult({})
+            return None
         for src, dst in out.cow_copies:
             self.kv.copy_block(src, dst)
         # the scheduler's own counts settle the common case without a scan of the rows
@@ -293,7 +334,11 @@ class ModelRunner:
         pad_to = _bucket(len(scheduled)) if graphable else None
         if pad_to is not None and pad_to > self.buf.max_seqs:
             pad_to, graphable = None, False
-        T, B, nl, max_q, max_len, rows = (self.build_decode if decode_only else self.build)(scheduled, pad_to)
+        self.buf.flip()
+        if decode_only:
+            T, B, nl, max_q, max_len, rows = self.build_decode(scheduled, pad_to, skip_tokens=tokens_on_device)
+        else:
+            T, B, nl, max_q, max_len, rows = self.build(scheduled, pad_to)
         self.last_rows = rows
         on_host = {id(p): p.needs_host_sampler for p in {id(r[0].seq.params): r[0].seq.params for r in rows}.values()}
         host_rows = [r for r in rows if on_host[id(r[0].seq.params)]] if any(on_host.values()) else []
@@ -301,25 +346,43 @@ class ModelRunner:
         graphable = graphable and not host_rows
         all_greedy = self._fill_sampling(rows, nl)
         tie = scheduled[0].seq.params.tie
-        h2d = self.buf.upload()
+        if tokens_on_device and not (decode_only and all_greedy and (graphable or self.device.type != "cuda")):
+            raise RuntimeError("a step that takes its input ids from the device must be a greedy decode step")
+        h2d = self.buf.upload(skip_tokens=tokens_on_device)
         logits = None
+        bucket = 0
+        feed = self.buf.d("token_ids", B) if decode_only and all_greedy and nl == T else None
         if graphable and all_greedy:
             toks = self._replay(B, tie)
+            bucket = B
         else:
-            meta = self._meta(T, B, nl, max_q, max_len)
-            toks, logits = self._forward_sample(meta, all_greedy and not needs_host_logits, tie)
+            meta = self._meta(T, B, nl, max_q, max_len, logits_all=decode_only and nl == T)
+            toks, logits = self._forward_sample(meta, all_greedy and not needs_host_logits, tie,
+                                                feed=feed if not needs_host_logits else None)
         n_out = toks.shape[0]
         if self.device.type == "cuda":
-            self.out_host[:n_out].copy_(toks, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-            host = self.out_host[:n_out].numpy()
+            self._out_which ^= 1
+            hb = self.out_hosts[self._out_which]
+            hb[:n_out].copy_(toks, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
         else:
-            host = toks.numpy()
+            hb, ev = None, None
+        return Pending(rows, n_out, toks, hb, ev, logits, host_rows, needs_host_logits or self.keep_logits, h2d, bucket,
+                       tuple(ss.seq.seq_id for ss in scheduled) if decode_only else ())
+
+    def collect(self, p: Pending) -> StepResult:
+        """Wait for a launched step and return its tokens."""
+        if p.event is not None:
+            p.event.synchronize()
+            host = p.host_buf[: p.n_out].numpy()
+        else:
+            host = p.toks.numpy()
         hl = host.tolist()
-        result: Dict[int, List[int]] = {ss.seq.seq_id: hl[r0 : r0 + k] for ss, r0, k in rows}
-        if host_rows:
-            self._host_sample(host_rows, logits, result)
-        return StepResult(result, logits if (needs_host_logits or self.keep_logits) else None, h2d, n_out * 4)
+        result: Dict[int, List[int]] = {ss.seq.seq_id: hl[r0 : r0 + k] for ss, r0, k in p.rows}
+        if p.host_rows:
+            self._host_sample(p.host_rows, p.logits, result)
+        return StepResult(result, p.logits if p.keep_logits else None, p.h2d_bytes, p.n_out * 4)
 
     def _host_sample(self, host_rows, logits: torch.Tensor, result: Dict[int, List[int]]) -> None:
         """Rows whose parameters the device kernel does not cover (penalties, typical / tail-free,
@@ -353,12 +416,14 @@ class ModelRunner:
 
     def _capture(self, B: int, tie: str):
         """Capture one decode step for bucket ``B`` (every sequence feeds exactly one row)."""
-        meta = self._meta(B, B, B, 1, self.max_blocks * self.page)
+        meta = self._meta(B, B, B, 1, self.max_blocks * self.page, logits_all=True)
+        feed = self.buf.d("token_ids", B)  # every row's next input id, left on the device for a step that runs ahead
         # warm up on a side stream so lazy initialisation does not land inside the capture
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
             for _ in range(2):
+                # (no token feed here: these runs execute for real and must leave the step's input ids alone)
                 self.model.greedy_tokens(meta, self.kv, tie)
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
@@ -367,7 +432,7 @@ class ModelRunner:
         n0 = opcuda.launch_count
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            out = self.model.greedy_tokens(meta, self.kv, tie)
+            out = self.model.greedy_tokens(meta, self.kv, tie, feed=feed)
         if not hasattr(self, "launches_per_step"):
             self.launches_per_step = {}
         self.launches_per_step[B] = opcuda.launch_count - n0

@@ -50,16 +50,9 @@ class BatchMeta:
     max_query_len: int = 1
     max_seq_len: int = 0
     num_seqs: int = 0
+    logits_all: bool = False  # logits_indices is the identity (every row is a logits row): no row gather needed
     # host copies for CPU-side loops (reference path); optional on the GPU path
     extra: dict = field(default_factory=dict)
-
-
-class _NullCtx:
-    def __enter__(self):
-        return self
-
-    def __exit__(self, *exc):
-        return False
 
 
 class SingleRankComm:
@@ -80,7 +73,8 @@ class SingleRankComm:
 
 
 class Transformer:
-    def __init__(self, weights: ModelWeights, comm=None, act_dtype: Optional[torch.dtype] = None):
+    def __init__(self, weights: ModelWeights, comm=None, act_dtype: Optional[torch.dtype] = None, fold_norms: bool = True,
+                 fuse_qkv_rope: bool = True, fuse_swiglu: bool = True):
         self.w = weights
         self.cfg: ModelConfig = weights.cfg
         self.comm = comm or SingleRankComm()
@@ -104,21 +98,79 @@ class Transformer:
             pairing=cfg.rope_pairing, mscale=opref.rope_mscale(cfg.rope_scaling),
             n_heads=self.n_heads_local, n_kv_heads=self.n_kv_local, head_dim=cfg.head_dim)
         self.attn_scale = cfg.head_dim ** -0.5
-        # The qkv and gate_up GEMMs run right behind the all-reduce of the previous row-parallel
-        # projection (plus one small norm kernel).  With more than one rank that wait leaves HBM
-        # idle, so those two GEMMs ask for the head of their weight stream into the L2 meanwhile.
-        import os
-
-        self._post_collective_prefetch_kb = 0
-        if dev.type == "cuda" and getattr(self.comm, "size", 1) > 1:
-            # measured at 2 and 8 GPUs: no effect on the step (10.42 vs 10.43 ms at 8), so it is off by default
-            self._post_collective_prefetch_kb = int(os.environ.get("OXB_L2_PREFETCH_KB", "0"))
-        # per-projection override "qkv:o:gate_up:down" in weight k-blocks per CTA (experiments)
-        pf = os.environ.get("OXB_PF", "")
-        self._pf = [int(v) for v in pf.split(":")] if pf and dev.type == "cuda" else None
-        self._fuse_qkv_rope = dev.type == "cuda" and os.environ.get("OXB_FUSED_QKV_ROPE", "1") != "0"
-        if dev.type == "cuda" and os.environ.get("OXB_FUSED_SWIGLU", "1") != "0":
+        self._fuse_qkv_rope = dev.type == "cuda" and fuse_qkv_rope
+        if dev.type == "cuda" and fuse_swiglu:
             self._interleave_gate_up()
+        if dev.type == "cuda" and fold_norms:
+            self._fold_norm_weights()
+
+    def _fold_norm_weights(self) -> None:
+        """Fold the two RMSNorm weight vectors of a dense bf16 layer into the columns of the projections that
+        consume them (qkv, gate_up).  What is left of a norm is one scalar per token, which the consuming GEMM
+        applies in its epilogue from sums of squares that the epilogue writing the residual stream leaves behind
+        (``run_layers``): two kernels per layer disappear.  The norm vectors become all-ones, so the unfused
+        kernels still compute the same function on these weights."""
+        cfg = self.cfg
+        if cfg.hidden_size % 8:
+            return
+
+        def bf16_single(w) -> bool:
+            return (w is not None and len(w.parts) == 1 and w.parts[0].qtype == "BF16" and w.bias is None
+                    and w.parts[0].data.is_contiguous())
+
+        for lw in self.w.layers:
+            if lw.router is not None or not (bf16_single(lw.wqkv) and bf16_single(lw.wo) and bf16_single(lw.w_gate_up)
+                                            and bf16_single(lw.w_down) and lw.w_gate_up.swiglu_interleaved):
+                continue
+            if lw.wo.parts[0].shape[0] % 8 or lw.w_down.parts[0].shape[0] % 8:
+                continue
+            for w, norm in ((lw.wqkv, lw.attn_norm), (lw.w_gate_up, lw.ffn_norm)):
+                d = w.parts[0].data
+                step = max(1, (1 << 27) // d.shape[1])
+                nv = norm.float()[None, :]
+                for r in range(0, d.shape[0], step):  # in row chunks: no second copy of a large matrix
+                    d[r : r + step] = (d[r : r + step].float() * nv).to(d.dtype)
+            lw.attn_norm = torch.ones_like(lw.attn_norm)
+            lw.ffn_norm = torch.ones_like(lw.ffn_norm)
+            lw.norms_folded = True  # on the layer object: layer lists are swapped in and out (MTP head)
+
+    def _row_parallel_into(self, x: torch.Tensor, w, r: torch.Tensor, acc: torch.Tensor) -> None:
+        """r += all_reduce(x @ w^T) in place; ``acc`` (cleared by the preceding consumer) receives the sums of squares
+        of the new rows of r."""
+        from ..ops import cuda as opcuda
+
+        comm = self.comm
+        if getattr(comm, "size", 1) == 1:
+            xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+            opcuda.gemm_bf16(xb.contiguous(), w.parts[0].data, out=r, add_into=True, sumsq_out=acc)
+            return
+        into = getattr(comm, "linear_allreduce_into", None)
+        if into is None or not into(x, w, r, acc):  # prefill-sized calls, or a comm without the fused kernels
+            r.add_(comm.linear_allreduce(x, w))
+            opcuda.row_sumsq(r, acc)
+
+    def _layer_folded(self, lw: LayerWeights, layer: int, r: torch.Tensor, acc: torch.Tensor, cur: int, meta: BatchMeta,
+                      kv) -> int:
+        """One dense layer on the residual stream ``r`` (updated in place) with both norms folded: five kernels.
+        ``acc`` is the pair of per-token sum-of-squares accumulators, ``acc[cur]`` describes r; returns the new ``cur``."""
+        from ..ops import cuda as opcuda
+
+        cfg = self.cfg
+        eps = cfg.rms_eps
+        wq = lw.wqkv.parts[0].data
+        if self._fuse_qkv_rope and opcuda.qkv_rope_fusable(lw.wqkv.parts, kv, self.rope, lw.q_norm, lw.k_norm):
+            q = opcuda.linear_qkv_rope(r, wq, meta.positions, meta.slot_mapping, kv, layer, self.rope, sumsq_in=acc[cur],
+                                       eps=eps, clear=acc[1 - cur])
+        else:
+            qkv = opcuda.gemm_bf16(r, wq, sumsq_in=acc[cur], eps=eps, clear=acc[1 - cur])
+            q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, self.rope, lw.q_norm, lw.k_norm, eps)
+        attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, cfg.sliding_window)
+        cur = 1 - cur
+        self._row_parallel_into(attn.reshape(attn.shape[0], -1), lw.wo, r, acc[cur])
+        act = opcuda.linear_swiglu(r, lw.w_gate_up.parts[0].data, sumsq_in=acc[cur], eps=eps, clear=acc[1 - cur])
+        cur = 1 - cur
+        self._row_parallel_into(act, lw.w_down, r, acc[cur])
+        return cur
 
     def _interleave_gate_up(self) -> None:
         """Dense bf16 gate|up projections are re-laid out once so that SiLU(gate) * up becomes the
@@ -142,39 +194,23 @@ class Transformer:
             from ..ops import cuda as opcuda
 
             if opcuda.qkv_rope_fusable(lw.wqkv.parts, kv, self.rope, lw.q_norm, lw.k_norm):
-                with self._prefetch(0, self._post_collective_prefetch_kb):
-                    q = opcuda.linear_qkv_rope(x, lw.wqkv.parts[0].data, meta.positions, meta.slot_mapping, kv, layer,
-                                               self.rope)
+                q = opcuda.linear_qkv_rope(x, lw.wqkv.parts[0].data, meta.positions, meta.slot_mapping, kv, layer, self.rope)
                 attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, cfg.sliding_window)
-                with self._prefetch(1, 0):
-                    return self.comm.linear_allreduce(attn.reshape(attn.shape[0], -1), lw.wo)
-        qkv = self._linear_after_collective(x, lw.wqkv, 0)
+                return self.comm.linear_allreduce(attn.reshape(attn.shape[0], -1), lw.wo)
+        qkv = ops.linear(x, lw.wqkv)
         q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, self.rope,
                                  lw.q_norm, lw.k_norm, cfg.rms_eps)
         attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, cfg.sliding_window)
-        with self._prefetch(1, 0):
-            return self.comm.linear_allreduce(attn.reshape(attn.shape[0], -1), lw.wo)
-
-    def _prefetch(self, which: int, default_kb: int):
-        from ..ops import cuda as opcuda
-
-        kb = self._pf[which] if self._pf is not None else default_kb
-        return opcuda.l2_prefetch(kb) if self.device.type == "cuda" else _NullCtx()
+        return self.comm.linear_allreduce(attn.reshape(attn.shape[0], -1), lw.wo)
 
     def _dense_ffn(self, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
         if lw.w_gate_up.swiglu_interleaved:
             from ..ops import cuda as opcuda
 
-            with self._prefetch(2, self._post_collective_prefetch_kb):
-                act = opcuda.linear_swiglu(x, lw.w_gate_up.parts[0].data)
+            act = opcuda.linear_swiglu(x, lw.w_gate_up.parts[0].data)
         else:
-            act = ops.silu_mul(self._linear_after_collective(x, lw.w_gate_up, 2))
-        with self._prefetch(3, 0):
-            return self.comm.linear_allreduce(act, lw.w_down)
-
-    def _linear_after_collective(self, x: torch.Tensor, w, which: int) -> torch.Tensor:
-        with self._prefetch(which, self._post_collective_prefetch_kb):
-            return ops.linear(x, w)
+            act = ops.silu_mul(ops.linear(x, lw.w_gate_up))
+        return self.comm.linear_allreduce(act, lw.w_down)
 
     def _moe_ffn(self, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
         """Routed experts + optional shared expert.
@@ -211,9 +247,33 @@ class Transformer:
         """Run local layers; returns (h, residual) where the true hidden is h + residual."""
         cfg = self.cfg
         lo, hi = layers if layers is not None else (0, len(self.w.layers))
+        acc, cur = None, 0  # per-token sum-of-squares accumulators of the residual stream while it is in folded form
         for li in range(lo, hi):
             lw = self.w.layers[li]
             gl = self.w.first_layer + li
+            if getattr(lw, "norms_folded", False) and (h if h is not None else residual).dtype == torch.bfloat16:
+                from ..ops import cuda as opcuda
+
+                if acc is None:
+                    # enter the folded form: the residual stream becomes one tensor, updated in place from here on
+                    # (a stream that arrives as h alone, e.g. the embedding output, is taken over as it is)
+                    if residual is not None:
+                        residual.add_(h)
+                    else:
+                        residual = h.contiguous()
+                    h = None
+                    acc = torch.empty(2, residual.shape[0], dtype=torch.int64, device=residual.device)
+                    cur = 0
+                    opcuda.row_sumsq(residual, acc[0])
+                cur = self._layer_folded(lw, li, residual, acc, cur, meta, kv)
+                if capture is not None and gl in capture.get("layers", ()):
+                    capture.setdefault("hidden", {})[gl] = residual.float()
+                if _profiler.TRACE_FWD:
+                    _profiler.trace_hidden(gl, residual, None)
+                continue
+            if acc is not None:
+                # leave the folded form: h + residual must again be the hidden state
+                h, acc = torch.zeros_like(residual), None
             x, residual = ops.add_rmsnorm(h, residual, lw.attn_norm, cfg.rms_eps)
             h = self._attention(lw, li, x, meta, kv)
             x, residual = ops.add_rmsnorm(h, residual, lw.ffn_norm, cfg.rms_eps)
@@ -222,6 +282,8 @@ class Transformer:
                 capture.setdefault("hidden", {})[gl] = (h.float() + residual.float())
             if _profiler.TRACE_FWD:
                 _profiler.trace_hidden(gl, h, residual)
+        if acc is not None:
+            return residual, None
         return h, residual
 
     def embed(self, token_ids: torch.Tensor) -> torch.Tensor:
@@ -240,39 +302,51 @@ class Transformer:
             logits = self.comm.all_gather_cat(logits, dim=-1)
         return (logits, hidden) if return_hidden else logits
 
-    def greedy_tokens(self, meta: BatchMeta, kv, tie: str = "lowest") -> torch.Tensor:
+    def greedy_tokens(self, meta: BatchMeta, kv, tie: str = "lowest", feed: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Forward + argmax without ever materialising full-vocabulary logits across ranks:
         each rank takes the argmax of its vocabulary shard and only (value, index) pairs are
-        all-gathered (vocabulary-parallel head, distributed argmax)."""
+        exchanged (vocabulary-parallel head, distributed argmax).  ``feed`` (int32, one entry per logits
+        row) also receives the tokens: the next decode step's input ids, written where its kernels read them."""
         h = self.embed(meta.token_ids)
         h, residual = self.run_layers(h, None, meta, kv)
-        idx = meta.logits_indices.long()
-        h = h.index_select(0, idx)
-        residual = residual.index_select(0, idx) if residual is not None else None
+        if not meta.logits_all:
+            idx = meta.logits_indices.long()
+            h = h.index_select(0, idx)
+            residual = residual.index_select(0, idx) if residual is not None else None
         x, hid = ops.add_rmsnorm(h, residual, self.w.out_norm, self.cfg.rms_eps)
         self.last_hidden = hid  # pre-norm hidden of the logits rows (input of an MTP head)
-        logits = ops.linear(x, self.w.lm_head).float()
+        logits = ops.linear(x, self.w.lm_head)
         sharded = self.w.tp_size > 1 and self.w.lm_head.out_features != self.cfg.vocab_size
-        if not sharded:
-            return ops.argmax(logits, tie)
         if logits.is_cuda:
             from ..ops import cuda as opcuda
 
-            val = torch.empty(logits.shape[0], dtype=torch.float32, device=logits.device)
-            loc = opcuda.argmax(logits, tie, out_val=val, index_offset=self.w.vocab_start)
+            xchg = getattr(self.comm, "argmax_exchange", None) if sharded else None
+            if not sharded or (xchg is not None and logits.shape[0] <= getattr(self.comm, "argmax_rows", 0)):
+                # one kernel: shard argmax, pair exchange over peer memory, winner, token fed to the next step
+                return opcuda.argmax_tp(logits, tie, self.w.vocab_start if sharded else 0, self.comm if sharded else None, feed)
+        logits = logits.float()
+        if not sharded:
+            toks = ops.argmax(logits, tie)
         else:
-            loc = ops.argmax(logits, tie) + self.w.vocab_start
-            val = logits.gather(1, (loc - self.w.vocab_start).long()[:, None]).squeeze(1)
-        pair = torch.stack([val, loc.view(torch.float32) if loc.dtype == torch.int32 else loc.float()], dim=1)
-        allp = self.comm.all_gather_cat(pair.contiguous(), dim=0).reshape(self.w.tp_size, -1, 2)
-        vals = allp[:, :, 0]
-        ids = allp[:, :, 1].contiguous().view(torch.int32)
-        # shards are in ascending vocabulary order: first max = lowest index, last max = highest
-        if tie == "highest":
-            win = self.w.tp_size - 1 - torch.flip(vals, dims=[0]).argmax(dim=0)
-        else:
-            win = vals.argmax(dim=0)
-        return ids.gather(0, win[None, :]).squeeze(0)
+            if logits.is_cuda:
+                val = torch.empty(logits.shape[0], dtype=torch.float32, device=logits.device)
+                loc = opcuda.argmax(logits, tie, out_val=val, index_offset=self.w.vocab_start)
+            else:
+                loc = ops.argmax(logits, tie) + self.w.vocab_start
+                val = logits.gather(1, (loc - self.w.vocab_start).long()[:, None]).squeeze(1)
+            pair = torch.stack([val, loc.view(torch.float32) if loc.dtype == torch.int32 else loc.float()], dim=1)
+            allp = self.comm.all_gather_cat(pair.contiguous(), dim=0).reshape(self.w.tp_size, -1, 2)
+            vals = allp[:, :, 0]
+            ids = allp[:, :, 1].contiguous().view(torch.int32)
+            # shards are in ascending vocabulary order: first max = lowest index, last max = highest
+            if tie == "highest":
+                win = self.w.tp_size - 1 - torch.flip(vals, dims=[0]).argmax(dim=0)
+            else:
+                win = vals.argmax(dim=0)
+            toks = ids.gather(0, win[None, :]).squeeze(0)
+        if feed is not None:
+            feed[: toks.shape[0]].copy_(toks.to(feed.dtype))
+        return toks
 
     def forward(self, meta: BatchMeta, kv, return_hidden: bool = False, capture: Optional[dict] = None):
         h = self.embed(meta.token_ids)

@@ -180,6 +180,7 @@ class LayerWeights:
     shared_gate_up: Optional[LinearWeight] = None
     shared_down: Optional[LinearWeight] = None
     shared_gate: Optional[QTensor] = None
+    norms_folded: bool = False  # attn_norm / ffn_norm were multiplied into wqkv / w_gate_up (Transformer._fold_norm_weights)
 
 
 @dataclass

@@ -8,6 +8,7 @@ from __future__ import annotations
 import ctypes
 import os
 import threading
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -40,13 +41,28 @@ def lib():
                     build_kernels()
                 _lib = ctypes.CDLL(LIB_PATH)
                 _declare(_lib)
-                if os.environ.get("OXB_PDL", "1") == "0":
-                    _lib.oxb_set_pdl(0)
-                if os.environ.get("OXB_CLUSTER_SPLITK", "1") == "0":
-                    _lib.oxb_set_cluster_splitk(0)
-                if os.environ.get("OXB_GEMM_PREFILL_TN"):
-                    _lib.oxb_set_gemm_prefill_tn(int(os.environ["OXB_GEMM_PREFILL_TN"]))
     return _lib
+
+
+@dataclass
+class KernelOptions:
+    """Process-wide switches of the kernel library (``EngineConfig.kernel_options``; the defaults are the tuned path,
+    the alternatives exist for A/B measurements)."""
+
+    pdl: bool = True  # programmatic dependent launch: a kernel's set-up overlaps the tail of the one before it
+    cluster_splitk: bool = True  # split-K partials meet in distributed shared memory instead of global scratch
+    gemm_prefill_tn: int = 256  # token tile of prefill-sized GEMM calls: 128, 256, or 0 = by wave count
+    gemv_max_tokens: int = 4  # packed-weight calls of at most this many tokens take the dp4a GEMV (0 = never)
+    ar_ll_min_world: int = 2  # rank counts from which the fused all-reduce uses the two-shot exchange
+
+
+def configure(opts: "KernelOptions") -> None:
+    L = lib()
+    L.oxb_set_pdl(1 if opts.pdl else 0)
+    L.oxb_set_cluster_splitk(1 if opts.cluster_splitk else 0)
+    L.oxb_set_gemm_prefill_tn(int(opts.gemm_prefill_tn))
+    L.oxb_set_gemv_max_tokens(int(opts.gemv_max_tokens))
+    L.oxb_set_ar_ll_min_world(int(opts.ar_ll_min_world))
 
 
 def _declare(L) -> None:
@@ -70,6 +86,14 @@ def _declare(L) -> None:
     L.oxb_gemm_ar.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, u64p, u64p, vp, i32, i32, i32, ull, vp, sz,
                               vp, i32, vp]
     L.oxb_allreduce_oneshot.argtypes = [vp, vp, i32, i32, i32, i32, i32, u64p, u64p, vp, i32, i32, i32, ull, vp]
+    L.oxb_gemm_bf16_norm.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, sz, vp, i32, vp, i32, f32, vp, vp, vp]
+    L.oxb_gemm_ar_norm.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, u64p, u64p, vp, i32, i32, i32, ull, vp, sz,
+                                   vp, i32, vp, vp]
+    L.oxb_gemm_qkv_rope.argtypes = [vp, vp, i32, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, vp]
+    L.oxb_gemm_qkv_rope_norm.argtypes = [vp, vp, i32, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, vp, i32, f32,
+                                         vp, vp]
+    L.oxb_row_sumsq.argtypes = [vp, i32, i32, i32, vp, vp, vp]
+    L.oxb_set_gemv_max_tokens.argtypes = [i32]
 
 
 def _check(code: int, what: str) -> None:
@@ -161,9 +185,16 @@ def gemm_plan(T: int, N: int, K: int, splits_hint: int = 0):
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
-              ld_out: Optional[int] = None, add_into: bool = False, splits: int = 0, swiglu: bool = False) -> torch.Tensor:
+              ld_out: Optional[int] = None, add_into: bool = False, splits: int = 0, swiglu: bool = False,
+              sumsq_in: Optional[torch.Tensor] = None, eps: float = 0.0, clear: Optional[torch.Tensor] = None,
+              sumsq_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[T, N] = x[T, K] @ w[N, K]^T on the tcgen05 kernel; ``out`` may be a column slice of a
-    wider row-major buffer (pass its row stride as ``ld_out``)."""
+    wider row-major buffer (pass its row stride as ``ld_out``).
+
+    The three accumulator arguments ([>= T] int64 tensors of 2^-28 fixed-point sums of squares, see :func:`row_sumsq`)
+    make the call one half of a folded RMSNorm.  ``sumsq_in``: ``x`` holds un-normalised rows and token t's result is
+    scaled by 1/rms(x_t); ``clear`` is zeroed on the way for the producer that follows.  ``sumsq_out``: the epilogue adds
+    the sums of squares of the rows it writes (the producer half; the array must have been cleared)."""
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
     T, K = x.shape
     N = w.shape[0]
@@ -174,9 +205,23 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     elif ld_out is None:
         ld_out = out.stride(0)
     s = scratch(x.device)
-    _check(lib().oxb_gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), _p(bias), T, N, K, ld_out,
-                               2 if swiglu else (1 if add_into else 0), splits, s.gemm_ws.data_ptr(), s.gemm_ws.numel() * 4,
-                               s.gemm_counters.data_ptr(), s.gemm_counters.numel(), _stream()), "oxb_gemm_bf16")
+    epi = 2 if swiglu else (1 if add_into else 0)
+    if sumsq_in is None and sumsq_out is None:
+        _check(lib().oxb_gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), _p(bias), T, N, K, ld_out, epi, splits,
+                                   s.gemm_ws.data_ptr(), s.gemm_ws.numel() * 4, s.gemm_counters.data_ptr(),
+                                   s.gemm_counters.numel(), _stream()), "oxb_gemm_bf16")
+        return out
+    _check(lib().oxb_gemm_bf16_norm(x.data_ptr(), w.data_ptr(), out.data_ptr(), _p(bias), T, N, K, ld_out, epi, splits,
+                                    s.gemm_ws.data_ptr(), s.gemm_ws.numel() * 4, s.gemm_counters.data_ptr(),
+                                    s.gemm_counters.numel(), _p(sumsq_in), K, eps, _p(clear), _p(sumsq_out), _stream()),
+           "oxb_gemm_bf16_norm")
+    return out
+
+
+def row_sumsq(x: torch.Tensor, out: torch.Tensor, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] (int64, 2^-28 fixed point) = sum of squares of row t of ``x`` (bf16 [T, H]); ``clear`` is zeroed."""
+    T, H = x.shape
+    _check(lib().oxb_row_sumsq(x.data_ptr(), x.stride(0), T, H, out.data_ptr(), _p(clear), _stream()), "oxb_row_sumsq")
     return out
 
 
@@ -249,11 +294,12 @@ def interleave_gate_up(w: torch.Tensor) -> torch.Tensor:
     return torch.cat([g, u], dim=1).reshape(2 * F, -1).contiguous()
 
 
-def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
+def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, sumsq_in: Optional[torch.Tensor] = None,
+                  eps: float = 0.0, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
     """silu(x W_gate^T) * (x W_up^T) in ONE kernel: the activation is the GEMM's epilogue."""
     if x.dtype != torch.bfloat16:
         x = x.to(torch.bfloat16)
-    return gemm_bf16(x.contiguous(), w_interleaved, swiglu=True)
+    return gemm_bf16(x.contiguous(), w_interleaved, swiglu=True, sumsq_in=sumsq_in, eps=eps, clear=clear)
 
 
 # --------------------------------------------------------------------------- glue ops
@@ -321,9 +367,12 @@ def qkv_rope_fusable(w_parts, kv, rope, q_norm, k_norm) -> bool:
             and w_parts[0].shape[0] == (rope.n_heads + 2 * rope.n_kv_heads) * 128)
 
 
-def linear_qkv_rope(x: torch.Tensor, w: torch.Tensor, positions, slot_mapping, kv, layer, rope) -> torch.Tensor:
+def linear_qkv_rope(x: torch.Tensor, w: torch.Tensor, positions, slot_mapping, kv, layer, rope,
+                    sumsq_in: Optional[torch.Tensor] = None, eps: float = 0.0,
+                    clear: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q = RoPE(x Wq^T) as [T, nq, 128]; RoPE(x Wk^T) and x Wv^T go straight into the paged KV cache:
-    one kernel instead of the qkv GEMM followed by the RoPE / KV-write kernel."""
+    one kernel instead of the qkv GEMM followed by the RoPE / KV-write kernel.  With ``sumsq_in`` the rows of
+    ``x`` are un-normalised and the kernel applies 1/rms per token (folded RMSNorm, see :func:`gemm_bf16`)."""
     if x.dtype != torch.bfloat16:
         x = x.to(torch.bfloat16)
     x = x.contiguous()
@@ -332,13 +381,16 @@ def linear_qkv_rope(x: torch.Tensor, w: torch.Tensor, positions, slot_mapping, k
     tab = rope_table(rope, 0)
     q = torch.empty(T, nq, 128, dtype=torch.bfloat16, device=x.device)
     L = lib()
-    if not getattr(L, "_qkv_rope_declared", False):
-        vp, i32 = ctypes.c_void_p, ctypes.c_int
-        L.oxb_gemm_qkv_rope.argtypes = [vp, vp, i32, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, vp]
-        L._qkv_rope_declared = True
-    _check(L.oxb_gemm_qkv_rope(x.data_ptr(), w.data_ptr(), T, K, positions.data_ptr(), slot_mapping.data_ptr(),
-                               tab.data_ptr(), tab.shape[0], tab.shape[1], 0 if rope.pairing == "split_half" else 1, nq, nkv,
-                               q.data_ptr(), kv.data[layer].data_ptr(), kv.page_size, kv.num_blocks, _stream()), "oxb_gemm_qkv_rope")
+    pairing = 0 if rope.pairing == "split_half" else 1
+    if sumsq_in is None:
+        _check(L.oxb_gemm_qkv_rope(x.data_ptr(), w.data_ptr(), T, K, positions.data_ptr(), slot_mapping.data_ptr(),
+                                   tab.data_ptr(), tab.shape[0], tab.shape[1], pairing, nq, nkv, q.data_ptr(),
+                                   kv.data[layer].data_ptr(), kv.page_size, kv.num_blocks, _stream()), "oxb_gemm_qkv_rope")
+    else:
+        _check(L.oxb_gemm_qkv_rope_norm(x.data_ptr(), w.data_ptr(), T, K, positions.data_ptr(), slot_mapping.data_ptr(),
+                                        tab.data_ptr(), tab.shape[0], tab.shape[1], pairing, nq, nkv, q.data_ptr(),
+                                        kv.data[layer].data_ptr(), kv.page_size, kv.num_blocks, sumsq_in.data_ptr(), K, eps,
+                                        _p(clear), _stream()), "oxb_gemm_qkv_rope_norm")
     return q
 
 
@@ -393,6 +445,29 @@ def argmax(logits: torch.Tensor, tie: str = "lowest", out_val: Optional[torch.Te
     out = torch.empty(R, dtype=torch.int32, device=logits.device)
     _check(lib().oxb_argmax(logits.data_ptr(), R, V, logits.stride(0), 1 if tie == "highest" else 0, out.data_ptr(),
                             _p(out_val), index_offset, _stream()), "oxb_argmax")
+    return out
+
+
+def argmax_tp(logits: torch.Tensor, tie: str = "lowest", index_offset: int = 0, comm=None,
+              feed: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Greedy token per row from this rank's logits shard (fp32 or bf16); with ``comm`` (a FusedComm) the
+    (value, index) pairs of all tensor-parallel ranks are exchanged inside the kernel.  ``feed`` also receives the tokens."""
+    R, V = logits.shape
+    dt = {torch.float32: 0, torch.bfloat16: 2}[logits.dtype]
+    out = torch.empty(R, dtype=torch.int32, device=logits.device)
+    L = lib()
+    if not getattr(L, "_argmax_tp_declared", False):
+        vp, i32 = ctypes.c_void_p, ctypes.c_int
+        L.oxb_argmax_tp.argtypes = [vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, i32, ctypes.POINTER(ctypes.c_uint64), vp, i32,
+                                    ctypes.c_ulonglong, vp]
+        L._argmax_tp_declared = True
+    if comm is None:
+        _check(L.oxb_argmax_tp(logits.data_ptr(), dt, R, V, logits.stride(0), 1 if tie == "highest" else 0, out.data_ptr(),
+                               _p(feed), index_offset, 1, 0, None, None, 0, 0, _stream()), "oxb_argmax_tp")
+    else:
+        _check(L.oxb_argmax_tp(logits.data_ptr(), dt, R, V, logits.stride(0), 1 if tie == "highest" else 0, out.data_ptr(),
+                               _p(feed), index_offset, comm.size, comm.rank, comm._amax_ptrs, comm.amax_ctrl.data_ptr(),
+                               comm.argmax_rows, ctypes.c_ulonglong(comm.timeout_ns), _stream()), "oxb_argmax_tp")
     return out
 
 

@@ -1,10 +1,12 @@
 """Linear layers over packed weights (Q4_K / Q6_K / Q8_0 / Q4_0 / NVFP4 GGUF blocks and
 block-scaled fp8) on the GPU.
 
-All batch sizes — single-token decode included — run ``oxb_gemm_quant``: the tcgen05 GEMM whose
-producer warps decode the blocks into the swizzled shared-memory operand tile, so the weights
-are read from HBM once, in their packed form.  Formats without a fused decoder (Q5_K, Q4_1 …),
-or a K that is not a multiple of 64, are decoded to a bf16 staging buffer first.
+Everything goes through ``oxb_gemm_quant``.  Decode batches of up to 8 tokens take the dp4a GEMV
+(``csrc/gemv_quant.cuh``: int8 activations, the packed bytes go straight into the arithmetic); larger
+batches the tcgen05 GEMM whose producer warps decode the blocks into the swizzled shared-memory
+operand tile.  Either way the weights are read from HBM once, in their packed form.  Formats without a
+fused decoder (Q5_K, Q4_1 …), or a K that is not a multiple of 64, are decoded to a bf16 staging
+buffer first.
 """
 from __future__ import annotations
 
@@ -32,7 +34,15 @@ def linear_quant(x, p, out_view, bias, ld_out):
         return _launch(x, p.data.data_ptr(), FUSED_TYPES[p.qtype], row_bytes, None, 0, out_view, bias, ld_out, n, k)
     buf = C.scratch(x.device).dequant_buf(n * k)[: n * k].view(n, k)
     C.dequant_rows(p, buf)
-    C.gemm_bf16(x, buf, out_view, bias, ld_out=ld_out)
+    # The GEMM requests its first weight tiles before it waits for the upstream kernel, which is only safe
+    # for weights that no kernel writes.  Here the "weights" were written by the launch just before, so this
+    # GEMM is launched without programmatic stream serialization (plain stream order).
+    L = C.lib()
+    old = L.oxb_set_pdl(0)
+    try:
+        C.gemm_bf16(x, buf, out_view, bias, ld_out=ld_out)
+    finally:
+        L.oxb_set_pdl(old)
     return out_view
 
 

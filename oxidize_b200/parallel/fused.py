@@ -41,6 +41,7 @@ class FusedComm(TorchComm):
         self.timeout_ns = int(timeout_s * 1e9)
         self.fused_calls = 0
         self.fallback_calls = 0
+        self.argmax_rows = 0
         W = self.size
         if W > 8:
             raise ValueError("fused collectives support up to 8 ranks (one NVSwitch domain)")
@@ -62,20 +63,21 @@ class FusedComm(TorchComm):
             self.flags.zero_()
             h_data = symm.rendezvous(self.data, pg)
             h_flags = symm.rendezvous(self.flags, pg)
-            self._handles = [h_data, h_flags]
+            # (value, index) pairs of the vocabulary-parallel argmax: [2 parities][W][rows][2] u64
+            self.argmax_rows = 512
+            self.amax = symm.empty(2 * W * self.argmax_rows * 2, dtype=torch.int64, device=self.device)
+            self.amax.zero_()
+            h_amax = symm.rendezvous(self.amax, pg)
+            self._handles = [h_data, h_flags, h_amax]
             data_ptrs = [int(p) for p in h_data.buffer_ptrs]
             flag_ptrs = [int(p) for p in h_flags.buffer_ptrs]
+            self._amax_ptrs = (ctypes.c_uint64 * 8)(*([int(p) for p in h_amax.buffer_ptrs] + [0] * (8 - W)))
+            self.amax_ctrl = torch.zeros(4, dtype=torch.int32, device=self.device)
         else:
             self.data = torch.zeros(2 * 9 * self.t_max * self.n_max * 2, dtype=torch.bfloat16, device=self.device)
             self.flags = torch.zeros(2 * 9 * self.max_tiles, dtype=torch.int32, device=self.device)
             data_ptrs, flag_ptrs = [self.data.data_ptr()], [self.flags.data_ptr()]
         self.set_peer_pointers(data_ptrs, flag_ptrs)
-        import os
-
-        if os.environ.get("OXB_AR_LL_MIN_WORLD"):
-            from ..ops import cuda as C
-
-            C.lib().oxb_set_ar_ll_min_world(int(os.environ["OXB_AR_LL_MIN_WORLD"]))
         self.ctrl = torch.zeros(4, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize(self.device)
         self.barrier()
@@ -88,6 +90,12 @@ class FusedComm(TorchComm):
             self.rank = rank
         self._data_ptrs = (ctypes.c_uint64 * 8)(*(list(data_ptrs) + [0] * (8 - len(data_ptrs))))
         self._flag_ptrs = (ctypes.c_uint64 * 8)(*(list(flag_ptrs) + [0] * (8 - len(flag_ptrs))))
+
+    def argmax_exchange(self, logits: torch.Tensor, index_offset: int, tie: str = "lowest", feed=None) -> torch.Tensor:
+        """Vocabulary-parallel greedy sampling in one kernel (see ``ops.cuda.argmax_tp``)."""
+        from ..ops import cuda as C
+
+        return C.argmax_tp(logits, tie, index_offset, self, feed)
 
     # ------------------------------------------------------------------ fused row-parallel linear
     def _fusable(self, x: torch.Tensor, w) -> bool:
@@ -125,6 +133,31 @@ class FusedComm(TorchComm):
                                      s.gemm_counters.numel(), C._stream()), "oxb_gemm_ar")
         self.fused_calls += 1
         return out
+
+    def linear_allreduce_into(self, x: torch.Tensor, w, residual: torch.Tensor, sumsq_out: torch.Tensor) -> bool:
+        """residual += sum_r x_r @ W_r^T in place, inside the fused kernel, whose exchange also adds the sums of squares
+        of the updated rows to ``sumsq_out`` ([>= T] int64, cleared beforehand: the producer half of a folded RMSNorm).
+        False when the call cannot take the fused two-shot path (the caller then uses the unfused route)."""
+        from ..ops import cuda as C
+
+        if self.size == 1 or not self._fusable(x, w) or self.size < C.lib().oxb_set_ar_ll_min_world(-1):
+            return False
+        part = getattr(w, "parts", [w])[0]
+        N = part.shape[0]
+        if not residual.is_contiguous() or residual.dtype != torch.bfloat16:
+            return False
+        if x.dtype != torch.bfloat16:
+            x = x.to(torch.bfloat16)
+        x = x.contiguous()
+        T, K = x.shape
+        s = C.scratch(x.device)
+        C._check(C.lib().oxb_gemm_ar_norm(x.data_ptr(), part.data.data_ptr(), residual.data_ptr(), residual.data_ptr(), T, N,
+                                          K, N, self.size, self.rank, self._data_ptrs, self._flag_ptrs, self.ctrl.data_ptr(),
+                                          self.t_max, self.n_max, self.max_tiles, ctypes.c_ulonglong(self.timeout_ns),
+                                          s.gemm_ws.data_ptr(), s.gemm_ws.numel() * 4, s.gemm_counters.data_ptr(),
+                                          s.gemm_counters.numel(), sumsq_out.data_ptr(), C._stream()), "oxb_gemm_ar_norm")
+        self.fused_calls += 1
+        return True
 
     # ------------------------------------------------------------------ stand-alone one-shot all-reduce
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:

@@ -592,3 +592,83 @@ def test_decode_builder_writes_the_same_batch_as_the_general_builder(tmp_path):
         res = r.execute(out)
         llm.scheduler.postprocess(out, res.tokens, None, 0.0)
     assert checked >= 10 and len(sizes) >= 2  # rows moved to other sequences at least once
+
+
+def _tiny_async_llm(tmp_path, async_decode, **kw):
+    from oxidize_b200.engine.llm import LLM, EngineConfig
+    from oxidize_b200.models.config import preset
+    from oxidize_b200.utils.synth import synth_gguf
+
+    cfg = preset("tiny-llama", n_layers=2, vocab_size=97, hidden_size=64, n_heads=4, n_kv_heads=2, head_dim=16, ffn_size=96)
+    path = str(tmp_path / "tiny_async.gguf")
+    synth_gguf(path, cfg, "F32", seed=5, norm_jitter=0.2)
+    ec = dict(max_model_len=96, max_num_seqs=8, num_kv_blocks=64, prefill_chunk_size=16, max_num_batched_tokens=64,
+              kv_page_size=4, enable_prefix_cache=False)
+    ec.update(kw)
+    return LLM.from_gguf(path, EngineConfig(async_decode=async_decode, **ec), device="cpu")
+
+
+def test_run_ahead_decode_matches_synchronous_decode(tmp_path):
+    """One step in flight ahead of the host: same tokens, finish reasons and step count as the synchronous loop, with
+    sequences that end by length, by a stop token in the middle of the run, and a request that arrives late."""
+    from oxidize_b200.engine.sampler import SamplingParams
+
+    prompts = [[5, 9, 20, 31, 7], list(range(3, 30)), [1, 2, 3], [40, 41, 42, 43, 44, 45, 46, 47, 48]]
+    ref = _tiny_async_llm(tmp_path, False)
+    base = ref.generate(prompts, SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True))
+    # a stop token that really occurs in the middle of one of the generations
+    stop_tok = base[1].token_ids[9]
+    lens = [24, 17, 24, 5]
+
+    def run(async_decode):
+        llm = _tiny_async_llm(tmp_path, async_decode)
+        sps = [SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True, stop_token_ids=[stop_tok] if i == 1 else [])
+               for i, n in enumerate(lens)]
+        ids = [llm.add_request(p, sp) for p, sp in zip(prompts[:3], sps[:3])]
+        final, steps, ahead = {}, 0, 0
+        late = False
+        while llm.has_unfinished or not late:
+            if steps == 6 and not late:
+                ids.append(llm.add_request(prompts[3], sps[3]))
+                late = True
+            for ro in llm.step():
+                if ro.finished:
+                    assert ro.request_id not in final, "a request finished twice"
+                    final[ro.request_id] = ro
+            ahead += getattr(llm, "_inflight", None) is not None
+            steps += 1
+            assert steps < 200
+        assert llm.pool.num_free == llm.pool.num_blocks, "blocks leaked"
+        return [final[i] for i in ids], ahead
+
+    sync, a0 = run(False)
+    asyn, a1 = run(True)
+    assert a0 == 0 and a1 > 5, "the run-ahead path was not taken"
+    for x, y in zip(sync, asyn):
+        assert x.token_ids == y.token_ids and x.finish_reason == y.finish_reason
+    assert sync[1].finish_reason == "stop" and len(sync[1].token_ids) <= 17
+
+
+def test_run_ahead_decode_survives_abort_and_drain(tmp_path):
+    from oxidize_b200.engine.sampler import SamplingParams
+
+    llm = _tiny_async_llm(tmp_path, True)
+    sp = SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True)
+    a = llm.add_request([5, 6, 7, 8], sp)
+    b = llm.add_request([9, 10, 11], sp)
+    for _ in range(6):
+        llm.step()
+    assert getattr(llm, "_inflight", None) is not None
+    assert llm.abort(a)
+    outs = llm.step()  # the surplus row of the aborted request is dropped, the other request goes on
+    assert [o.request_id for o in outs] == [b]
+    n_before = len(llm._seqs[b].output)
+    llm.drain()
+    assert getattr(llm, "_inflight", None) is None and len(llm._seqs[b].output) >= n_before
+    final = {}
+    while llm.has_unfinished:
+        for ro in llm.step():
+            if ro.finished:
+                final[ro.request_id] = ro
+    assert len(final[b].token_ids) == 40
+    assert llm.pool.num_free == llm.pool.num_blocks

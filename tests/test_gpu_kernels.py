@@ -288,6 +288,44 @@ def test_linear_packed_weights_fused_dequant(C, qtype, T, N, K):
     assert torch.equal(got, C.linear(x, [w]))
 
 
+@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q8_0", "Q4_0"])
+@pytest.mark.parametrize("T,N,K", [(1, 4096, 4096), (1, 1000, 14336), (2, 257, 2048), (3, 520, 1024), (5, 64, 8192), (8, 1280, 4096)])
+def test_gemv_packed_weights_small_batches(C, qtype, T, N, K):
+    """dp4a GEMV (int8 activations, packed weights) vs fp32 matmul on the NumPy-decoded weights, and vs the
+    tensor-core path on the same call; bias and accumulate-into-output variants included."""
+    from oxidize_b200.models.weights import qtensor_from_dense
+
+    L = C.lib()
+    default_max = L.oxb_set_gemv_max_tokens(8)  # the kernel covers up to 8 tokens; the default hands 5..8 to the GEMM
+    torch.manual_seed(T * 7 + N)
+    w = qtensor_from_dense(torch.randn(N, K) * 0.05, qtype, device="cuda")
+    x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
+    want = x.float().cpu() @ w.to("cpu").dense_cache().t()
+    got = C.linear(x, [w])
+    torch.cuda.synchronize()
+    _check_status(C)
+    # int8 activations with one scale per 32 values: ~0.5 % relative error in the l2 sense
+    assert _rel_err(got.cpu(), want) < 1.2e-2
+    assert torch.equal(got, C.linear(x, [w])), "not reproducible"
+    old = L.oxb_set_gemv_max_tokens(0)
+    try:
+        mmq = C.linear(x, [w])
+    finally:
+        L.oxb_set_gemv_max_tokens(old)
+    torch.cuda.synchronize()
+    assert old >= T, "the GEMV is switched off"
+    assert _rel_err(got.cpu(), mmq.cpu()) < 1.5e-2
+    # zero rows and rows of very different magnitude
+    x2 = x.clone()
+    x2[0, : K // 2] = 0
+    x2[-1] *= 37.0
+    got2 = C.linear(x2, [w])
+    want2 = x2.float().cpu() @ w.to("cpu").dense_cache().t()
+    L.oxb_set_gemv_max_tokens(default_max)
+    assert _rel_err(got2.cpu(), want2) < 1.2e-2
+    _check_status(C)
+
+
 def test_quantized_model_gpu_matches_cpu(C, tmp_path):
     from oxidize_b200.engine.llm import LLM, EngineConfig
     from oxidize_b200.engine.sampler import SamplingParams
@@ -425,6 +463,73 @@ def test_gemm_swiglu_epilogue(C, T, F, K):
     assert _rel_err(got, want) < 1e-2
     unfused = C.silu_mul(C.gemm_bf16(x, w))
     assert _rel_err(got, unfused) < 1e-2
+    _check_status(C)
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 256, 512), (64, 8192, 1024), (37, 1024, 3584), (300, 512, 2048), (16, 1280, 8192)])
+def test_gemm_folded_rmsnorm_halves(C, T, N, K):
+    """Consumer half: per-token 1/rms from partial sums of squares applied in the epilogue.  Producer half: the
+    accumulate-into epilogue also leaves the sums of squares of the rows it wrote."""
+    torch.manual_seed(T + N + K)
+    x = (torch.randn(T, K, device="cuda") * 3).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    eps = 1e-5
+    FIX = float(1 << 28)
+    acc = torch.full((2, T), 12345, dtype=torch.int64, device="cuda")
+    C.row_sumsq(x, acc[0], clear=acc[1])
+    want_ss = x.float().pow(2).sum(-1)
+    assert _rel_err(acc[0].double() / FIX, want_ss.double()) < 1e-5 and int(acc[1].abs().sum()) == 0
+    rstd = torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + eps)
+    want = (x.float() * rstd) @ w.float().t()
+    acc[1].fill_(777)
+    got = C.gemm_bf16(x, w, sumsq_in=acc[0], eps=eps, clear=acc[1])
+    torch.cuda.synchronize()
+    assert _rel_err(got, want) < 6e-3
+    assert int(acc[1].abs().sum()) == 0, "the consumer clears the other accumulator"
+    assert torch.equal(got, C.gemm_bf16(x, w, sumsq_in=acc[0], eps=eps))
+    # producer: r += x @ w^T, with the sums of squares of the new r added to a cleared accumulator
+    r0 = torch.randn(T, N, device="cuda").to(torch.bfloat16)
+    r = r0.clone()
+    C.gemm_bf16(x, w, out=r, add_into=True, sumsq_out=acc[1])
+    torch.cuda.synchronize()
+    want_r = r0.float() + x.float() @ w.float().t()
+    assert _rel_err(r, want_r) < 6e-3
+    assert _rel_err(acc[1].double() / FIX, r.double().pow(2).sum(-1)) < 1e-5
+    _check_status(C)
+
+
+def test_folded_norm_model_matches_unfolded(C):
+    """The same random 70B-shaped slice with the norms folded into the GEMM epilogues and with the stand-alone
+    norm kernels: same logits within bf16 noise, decode and prefill, CUDA graphs on."""
+    from oxidize_b200.engine.llm import LLM, EngineConfig
+    from oxidize_b200.engine.sampler import SamplingParams
+    from oxidize_b200.models.config import preset
+    from oxidize_b200.utils.synth import synth_weights
+
+    cfg = preset("llama3-70b", n_layers=3, vocab_size=2048, hidden_size=1024, n_heads=8, n_kv_heads=2, ffn_size=2048)
+    ec = dict(max_model_len=256, max_num_seqs=8, num_kv_blocks=128, max_num_batched_tokens=256, prefill_chunk_size=64)
+    outs = {}
+    for fold in (True, False):
+        w = synth_weights(cfg, torch.device("cuda"), "BF16", seed=3)
+        for lw in w.layers:  # norm weights that are not all ones, identical in both runs
+            g = torch.Generator(device="cuda")
+            g.manual_seed(11)
+            lw.attn_norm = 1.0 + 0.2 * torch.randn(cfg.hidden_size, device="cuda", generator=g)
+            lw.ffn_norm = 1.0 + 0.2 * torch.randn(cfg.hidden_size, device="cuda", generator=g)
+        llm = LLM(w, EngineConfig(fold_norms=fold, **ec))
+        assert any(getattr(lw, "norms_folded", False) for lw in w.layers) == fold
+        llm.runner.keep_logits = True
+        sp = SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True)
+        for p in ([5, 9, 200, 31, 7], list(range(3, 100)), [1, 2, 3]):
+            llm.add_request(p, sp)
+        logs = []
+        while llm.has_unfinished:
+            llm.step()
+            logs.append(llm.last_step[1].logits.float().cpu())
+        outs[fold] = logs
+    assert len(outs[True]) == len(outs[False])
+    for a, b in zip(outs[True], outs[False]):
+        assert a.shape == b.shape and _rel_err(a, b) < 3e-2
     _check_status(C)
 
 
