@@ -192,27 +192,36 @@ def make_engine(args, passed: set):
     ec = EngineConfig(kv_cache_dtype=kvd, kv_page_size=args.kv_page_size,
                       max_model_len=args.ctx_size or plan.ctx_size, max_num_seqs=args.max_running or plan.max_num_seqs,
                       max_num_batched_tokens=args.max_batched_tokens, prefill_chunk_size=args.prefill_batch_size,
-                      cuda_graphs=not args.no_cuda_graphs, tp_size=tp, ep_size=args.ep or tp, pp_size=args.pp,
+                      cuda_graphs=not args.no_cuda_graphs, tp_size=tp, ep_size=args.ep or tp, pp_size=max(1, args.pp),
                       fused_comm=args.fused_comm == "on")
-    if tp > 1 and int(os.environ.get("WORLD_SIZE", "1")) != tp:
+    pp = ec.pp_size
+    if ec.ep_size not in (1, tp):
+        raise SystemExit(f"error: --ep must be 1 (experts replicated) or equal to --tp ({tp})")
+    if tp * pp > 1 and int(os.environ.get("WORLD_SIZE", "1")) != tp * pp:
         from ..parallel.launcher import relaunch_under_torchrun
 
-        relaunch_under_torchrun(tp)
+        relaunch_under_torchrun(tp * pp)
     comm = None
-    rank = 0
-    if tp > 1:
+    pipe = None
+    tp_rank = 0
+    if tp * pp > 1:
         from ..parallel.comm import TorchComm, init_distributed
+        from ..parallel.pp import make_pipeline_groups
 
         layout = init_distributed()
-        rank = layout.rank
-        if backend == "cuda" and ec.fused_comm:
-            from ..parallel.fused import FusedComm
+        # stage-major layout: global rank = stage * tp + tp_rank
+        pipe, tp_group = make_pipeline_groups(layout.world_size, layout.rank, tp, pp)
+        tp_rank = layout.rank % tp
+        if tp > 1:
+            if backend == "cuda" and ec.fused_comm:
+                from ..parallel.fused import FusedComm
 
-            comm = FusedComm(torch.device("cuda", torch.cuda.current_device()), hidden=fp.hidden_size)
-        else:
-            comm = TorchComm()
+                comm = FusedComm(torch.device("cuda", torch.cuda.current_device()), hidden=fp.hidden_size, group=tp_group)
+            else:
+                comm = TorchComm(tp_group)
     dev = "cpu" if backend == "cpu" else f"cuda:{torch.cuda.current_device()}"
-    llm = LLM.from_gguf(g, ec, device=dev, comm=comm, tp_rank=rank, ep_rank=rank, rope_pairing=args.rope_pairing)
+    llm = LLM.from_gguf(g, ec, device=dev, comm=comm, tp_rank=tp_rank, ep_rank=tp_rank, rope_pairing=args.rope_pairing,
+                        pipe=pipe)
     if args.tokenizer_model:
         from ..formats.tokenizer import load_tokenizer_from_gguf
 

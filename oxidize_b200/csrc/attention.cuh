@@ -377,38 +377,47 @@ paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
   // ---- merge the four warps through shared memory (reusing the stage area)
   float* mo = reinterpret_cast<float*>(att_smem);             // [4][16][HD]
   float* mml = mo + ATT_WARPS * 16 * HD;                       // [4][16][2]
+  // (rows past R do not exist — at decode with 8 query heads per KV head that is half of the tile: they are
+  // neither staged nor merged)
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-      float* dst = mo + ((size_t)warp * 16 + g + 8 * i) * HD + nt * 8 + 2 * t4;
-      dst[0] = o[nt][2 * i];
-      dst[1] = o[nt][2 * i + 1];
+      if (rvalid[i]) {
+        float2* dst = reinterpret_cast<float2*>(mo + ((size_t)warp * 16 + g + 8 * i) * HD + nt * 8 + 2 * t4);
+        *dst = make_float2(o[nt][2 * i], o[nt][2 * i + 1]);
+      }
     }
   }
   if (t4 == 0) {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-      mml[(warp * 16 + g + 8 * i) * 2] = m_run[i];
-      mml[(warp * 16 + g + 8 * i) * 2 + 1] = l_run[i];
+      if (rvalid[i]) {
+        mml[(warp * 16 + g + 8 * i) * 2] = m_run[i];
+        mml[(warp * 16 + g + 8 * i) * 2 + 1] = l_run[i];
+      }
     }
   }
   __syncthreads();
   {
     const int row = threadIdx.x >> 3;          // 0..15
     const int seg = (threadIdx.x & 7) * (HD / 8);
-    float M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, mml[(w * 16 + row) * 2]);
-    float L = 0.f, wgt[ATT_WARPS];
-#pragma unroll
-    for (int w = 0; w < ATT_WARPS; ++w) {
-      const float mw = mml[(w * 16 + row) * 2];
-      wgt[w] = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-      L += wgt[w] * mml[(w * 16 + row) * 2 + 1];
-    }
     const int r = row_base + row;
     const bool valid = active && r < R;
+    float M = -INFINITY;
+    float L = 0.f, wgt[ATT_WARPS];
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) wgt[w] = 0.f;
+    if (valid) {
+#pragma unroll
+      for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, mml[(w * 16 + row) * 2]);
+#pragma unroll
+      for (int w = 0; w < ATT_WARPS; ++w) {
+        const float mw = mml[(w * 16 + row) * 2];
+        wgt[w] = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+        L += wgt[w] * mml[(w * 16 + row) * 2 + 1];
+      }
+    }
     if (a.n_cta_splits == 1) {
       if (valid) {
         const float inv = L > 0.f ? 1.f / L : 0.f;
@@ -424,12 +433,20 @@ paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
         }
       }
     } else {
-      float* wo = a.ws_o + (task * 16 + row) * HD + seg;
-      for (int d = 0; d < HD / 8; ++d) {
-        float v = 0.f;
+      if (valid) {
+        float4* wo = reinterpret_cast<float4*>(a.ws_o + (task * 16 + row) * HD + seg);
+        for (int d = 0; d < HD / 8; d += 4) {
+          float v[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int w = 0; w < ATT_WARPS; ++w) v += wgt[w] * mo[((size_t)w * 16 + row) * HD + seg + d];
-        wo[d] = v;
+          for (int w = 0; w < ATT_WARPS; ++w) {
+            const float4 x = *reinterpret_cast<const float4*>(mo + ((size_t)w * 16 + row) * HD + seg + d);
+            v[0] += wgt[w] * x.x;
+            v[1] += wgt[w] * x.y;
+            v[2] += wgt[w] * x.z;
+            v[3] += wgt[w] * x.w;
+          }
+          wo[d >> 2] = make_float4(v[0], v[1], v[2], v[3]);
+        }
       }
       if ((threadIdx.x & 7) == 0) {
         a.ws_ml[(task * 16 + row) * 2] = valid ? M : -INFINITY;

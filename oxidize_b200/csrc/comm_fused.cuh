@@ -350,7 +350,7 @@ __device__ __forceinline__ bool ar_exchange_ll(const ArArgs& ar, const uint8_t* 
         for (int o2 = 8; o2 > 0; o2 >>= 1) ss += __shfl_xor_sync(hmask, ss, o2);
         if ((q & 15) == 0) {  // fixed-point add: the total does not depend on the order of the tiles (NormArgs)
           ss = fminf(ss, 3.0e10f);
-          atomicAdd(ssq_out + t0 + (q >> 4), (unsigned long long)(ss * 268435456.f + 0.5f));
+          atomicAdd(ssq_out + (size_t)(t0 + (q >> 4)) * 16 /*SUMSQ_STRIDE*/, (unsigned long long)(ss * 268435456.f + 0.5f));
         }
       }
     }

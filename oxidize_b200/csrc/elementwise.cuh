@@ -178,9 +178,9 @@ static __global__ void row_sumsq_kernel(const __nv_bfloat16* __restrict__ X, int
       if (c0 + 128 < H) total += (unsigned long long)(fminf(other, 3.0e10f) * 268435456.f + 0.5f);
     }
   }
-  if (lane == 0) {
-    out[t] = total;
-    if (clear != nullptr) clear[t] = 0ull;
+  if (lane == 0) {  // accumulators of neighbouring tokens are 16 words (128 bytes) apart, see NormArgs
+    out[(size_t)t * 16] = total;
+    if (clear != nullptr) clear[(size_t)t * 16] = 0ull;
   }
 }
 

@@ -79,11 +79,14 @@ constexpr int EPI_SWIGLU = 2;     // weight rows interleaved per tile (64 gate r
 // not depend on the order in which the tiles arrive: every rank and every replay computes the same scale.
 // Two accumulator arrays alternate; the consumer of one clears the other for the producer that follows it.
 constexpr float SUMSQ_FIX = 268435456.f;  // 2^28
+// Accumulators of neighbouring tokens are 128 bytes apart: every column tile of a token adds into the same word, and
+// atomics on one cache line are performed one after the other; with the tokens on separate lines they proceed in parallel.
+constexpr int SUMSQ_STRIDE = 16;  // in 64-bit words
 struct NormArgs {
-  const unsigned long long* sumsq_in;  // consumer: [T] fixed-point sums of squares of the token rows of X, or null
+  const unsigned long long* sumsq_in;  // consumer: [T * SUMSQ_STRIDE] fixed-point sums of squares of the token rows of X, or null
   float inv_dim, eps;                  // scale_t = rsqrt(sum_t * inv_dim + eps)
-  unsigned long long* clear;           // consumer: [T] accumulator to reset for the next producer, or null
-  unsigned long long* sumsq_out;       // producer: [T] accumulator that receives the rows written, or null
+  unsigned long long* clear;           // consumer: accumulator array (same layout) to reset for the next producer, or null
+  unsigned long long* sumsq_out;       // producer: accumulator array (same layout) that receives the rows written, or null
 };
 
 __device__ __forceinline__ void sumsq_add(unsigned long long* dst, float ss) {
@@ -195,7 +198,7 @@ __device__ __forceinline__ void store_tile_rows(const uint8_t* stage, int ntok, 
       }
       if (ssq_out != nullptr) {
         ss = half_warp_sum(ss);
-        if (chunk == 0) sumsq_add(ssq_out + t_first + t, ss);
+        if (chunk == 0) sumsq_add(ssq_out + (size_t)(t_first + t) * SUMSQ_STRIDE, ss);
       }
     }
   }
@@ -563,14 +566,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     if (use_nm) {
       // 1/rms of every token of this tile; computed while the MMAs run, published by the barrier below
       for (int j = etid; j < TN; j += 128) {
-        const float s = t0 + j < T ? (float)__ldcg(nm.sumsq_in + t0 + j) * (1.f / SUMSQ_FIX) : 0.f;
+        const float s = t0 + j < T ? (float)__ldcg(nm.sumsq_in + (size_t)(t0 + j) * SUMSQ_STRIDE) * (1.f / SUMSQ_FIX) : 0.f;
         tok_scale[j] = rsqrtf(s * nm.inv_dim + nm.eps);
       }
     }
     if (nm.clear != nullptr && blockIdx.x == 0 && blockIdx.y == 0) {
       // the accumulator that the next producer adds into: its last reader finished before this grid's dependency
       const int tt = gr.enabled ? T : min(TN, T - t0);
-      for (int j = etid; j < tt; j += 128) nm.clear[t0 + j] = 0ull;
+      for (int j = etid; j < tt; j += 128) nm.clear[(size_t)(t0 + j) * SUMSQ_STRIDE] = 0ull;
     }
     unsigned long long* const ssq_dst = nm.sumsq_out;
     mbar_wait_bounded(accum, 0, abort_flag, OXB_TIMEOUT_ACCUM, blockIdx.x);

@@ -320,6 +320,19 @@ OXB_API int oxb_sample(const float* logits, int R, int V, int ld, const float* t
   return 0;
 }
 
+// Speculative verification of S sequences in one launch (see SpecVerifyArgs in sampling.cuh).
+OXB_API int oxb_spec_verify(const float* target, int ld_t, const float* draft, int ld_d, const int* draft_tokens, const int* row0,
+                            const int* n_draft, const float* temperature, const float* uniforms, int* out_tokens, int* out_count,
+                            int S, int K, int V, int tie_highest, cudaStream_t stream) {
+  if (S <= 0) return 0;
+  if (K < 1 || K > 64 || V <= 0) return (int)cudaErrorInvalidValue;
+  SpecVerifyArgs a{target, draft, draft_tokens, row0, n_draft, temperature, uniforms, out_tokens, out_count, V, K, ld_t, ld_d,
+                   tie_highest};
+  oxb_launch(spec_verify_kernel, dim3(S), dim3(SMP_THREADS), 0, stream, a);
+  OXB_CHECK_LAUNCH();
+  return 0;
+}
+
 // ----------------------------------------------------------------------------- mixture of experts
 #include "moe.cuh"
 

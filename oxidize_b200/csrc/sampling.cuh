@@ -332,4 +332,187 @@ sample_kernel(const float* __restrict__ logits, int V, int ld, const float* __re
   }
 }
 
+// ----------------------------------------------------------------------------- speculative verification
+// One CTA per sequence walks its K drafted tokens against the K+1 rows of target logits that one batched forward
+// produced.  Greedy sequences (temperature <= 0) keep drafts while they equal the target's argmax.  Sampled
+// sequences use the rejection rule that leaves the output distributed exactly as the target's:
+//   accept draft d_i with probability min(1, p_i(d_i) / q_i(d_i));
+//   at the first rejection emit a token drawn from normalise(max(p_i - q_i, 0)) and stop;
+//   if all K were accepted emit a bonus token drawn from p_K.
+// p_i = softmax(target row i / T), q_i = softmax(draft row i / T).  Each decision consumes uniforms handed in by
+// the host: u[2i] for the accept test, u[2i + 1] for the draw, u[2K] for the bonus token.  Draws are inverse-CDF
+// in index order over a block-wide scan, so a given set of uniforms gives one result on any launch.
+// Acceptance rule and bonus token of the reference: speculative_accept (oxidize-core/src/model/sampling.rs:492-623).
+struct SpecVerifyArgs {
+  const float* target;       // [rows, V] target logits, row stride ld_t
+  const float* draft;        // [S * K, V] draft logits, row stride ld_d (row s * K + i); may be null for greedy-only
+  const int* draft_tokens;   // [S, K]
+  const int* row0;           // [S] first target row of each sequence
+  const int* n_draft;        // [S] drafts of each sequence (<= K)
+  const float* temperature;  // [S]
+  const float* uniforms;     // [S, 2K + 1]
+  int* out_tokens;           // [S, K + 1]
+  int* out_count;            // [S] tokens emitted (accepted drafts + 1)
+  int V, K, ld_t, ld_d, tie_highest;
+};
+
+// block-wide (max, argmax) and sum helpers over a logits row
+__device__ __forceinline__ void spec_row_max(const float* row, int V, int tie_highest, float* sv, int* si, float& mx, int& arg) {
+  float best = -INFINITY;
+  int bi = -1;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = row[i];
+    if (v == v && (bi < 0 || v > best || (v == best && tie_highest))) {
+      best = v;
+      bi = i;
+    }
+  }
+  auto better = [&](float v, int i, float bv, int b) {
+    if (i < 0) return false;
+    if (b < 0) return true;
+    return v > bv || (v == bv && (tie_highest ? i > b : i < b));
+  };
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better(ov, oi, best, bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) {
+    sv[warp] = best;
+    si[warp] = bi;
+  }
+  __syncthreads();
+  best = sv[0];
+  bi = si[0];
+  for (int w = 1; w < nw; ++w)
+    if (better(sv[w], si[w], best, bi)) {
+      best = sv[w];
+      bi = si[w];
+    }
+  mx = best;
+  arg = bi < 0 ? 0 : bi;
+}
+
+__device__ __forceinline__ float spec_block_sum(float v, float* sv) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) sv[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int w = 0; w < nw; ++w) t += sv[w];
+  return t;
+}
+
+// Draw from the unnormalised weights w(i) >= 0, i in [0, V), by inverse CDF in index order: each thread owns a
+// contiguous chunk.  `wf(i)` evaluates the weight.  Returns the index (all threads get it).
+template <class WF>
+__device__ __forceinline__ int spec_draw(int V, float u, WF wf, float* sv, int* s_pick, int fallback) {
+  const int per = (V + blockDim.x - 1) / blockDim.x;
+  const int b = threadIdx.x * per, e = min(V, b + per);
+  float local = 0.f;
+  for (int i = b; i < e; ++i) local += wf(i);
+  const float2 sc = BlockScan::run(local, sv);
+  const float total = sc.y;
+  if (threadIdx.x == 0) *s_pick = -1;
+  __syncthreads();
+  if (total > 0.f && total == total) {
+    const float target = u * total;
+    const float before = sc.x - local;
+    // the thread whose chunk contains the target (the last chunk takes what rounding leaves over)
+    const bool mine = local > 0.f && target >= before && (target < sc.x || sc.x >= total);
+    if (mine) {
+      float c = before;
+      int pick = -1;
+      for (int i = b; i < e; ++i) {
+        const float w = wf(i);
+        if (w > 0.f) {
+          pick = i;
+          c += w;
+          if (c > target) break;
+        }
+      }
+      if (pick >= 0) atomicMax(s_pick, pick);
+    }
+  }
+  __syncthreads();
+  const int r = *s_pick;
+  __syncthreads();
+  return r >= 0 ? r : fallback;
+}
+
+static __global__ void __launch_bounds__(SMP_THREADS)
+spec_verify_kernel(const SpecVerifyArgs a) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  __shared__ int s_pick;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int s = blockIdx.x;
+  const int K = a.K, nd = min(a.n_draft[s], K);
+  const float T = a.temperature[s];
+  const float* u = a.uniforms + (size_t)s * (2 * K + 1);
+  int* out = a.out_tokens + (size_t)s * (K + 1);
+  int n_out = 0;
+  bool stopped = false;
+  for (int i = 0; i <= nd && !stopped; ++i) {
+    const float* trow = a.target + (size_t)(a.row0[s] + i) * a.ld_t;
+    float tmax;
+    int targ;
+    spec_row_max(trow, a.V, a.tie_highest, sv, si, tmax, targ);
+    if (T <= 0.f || a.draft == nullptr) {
+      // greedy: the target's argmax decides; a draft is kept only if it is that token
+      if (threadIdx.x == 0) out[n_out] = targ;
+      ++n_out;
+      stopped = i == nd || a.draft_tokens[(size_t)s * K + i] != targ;
+      continue;
+    }
+    const float inv_t = 1.f / T;
+    float zp = 0.f;
+    for (int v = threadIdx.x; v < a.V; v += blockDim.x) zp += __expf((trow[v] - tmax) * inv_t);
+    zp = spec_block_sum(zp, sv);
+    const float inv_zp = 1.f / zp;
+    if (i == nd) {
+      // every draft was accepted: bonus token from the target's own distribution
+      const int tok = spec_draw(a.V, u[2 * K], [&](int v) { return __expf((trow[v] - tmax) * inv_t); }, sv, &s_pick, targ);
+      if (threadIdx.x == 0) out[n_out] = tok;
+      ++n_out;
+      break;
+    }
+    const float* drow = a.draft + (size_t)(s * K + i) * a.ld_d;
+    float dmax;
+    int darg;
+    spec_row_max(drow, a.V, a.tie_highest, sv, si, dmax, darg);
+    float zq = 0.f;
+    for (int v = threadIdx.x; v < a.V; v += blockDim.x) zq += __expf((drow[v] - dmax) * inv_t);
+    zq = spec_block_sum(zq, sv);
+    const float inv_zq = 1.f / zq;
+    const int d = a.draft_tokens[(size_t)s * K + i];
+    const float pd = __expf((trow[d] - tmax) * inv_t) * inv_zp;
+    const float qd = __expf((drow[d] - dmax) * inv_t) * inv_zq;
+    const float ratio = qd > 0.f ? pd / qd : 1.f;
+    if (u[2 * i] < fminf(1.f, ratio)) {
+      if (threadIdx.x == 0) out[n_out] = d;
+      ++n_out;
+      continue;
+    }
+    // rejected: draw from the part of the target's mass that the draft does not cover
+    const int tok = spec_draw(
+        a.V, u[2 * i + 1],
+        [&](int v) { return fmaxf(__expf((trow[v] - tmax) * inv_t) * inv_zp - __expf((drow[v] - dmax) * inv_t) * inv_zq, 0.f); }, sv,
+        &s_pick, targ);
+    if (threadIdx.x == 0) out[n_out] = tok;
+    ++n_out;
+    stopped = true;
+  }
+  if (threadIdx.x == 0) a.out_count[s] = n_out;
+}
+
 }  // namespace oxb

@@ -70,9 +70,12 @@ class RequestOutput:
 
 
 class LLM:
-    def __init__(self, weights: ModelWeights, config: Optional[EngineConfig] = None, comm=None, tokenizer=None):
+    def __init__(self, weights: ModelWeights, config: Optional[EngineConfig] = None, comm=None, tokenizer=None, pipe=None):
         self.config = config or EngineConfig()
         c = self.config
+        self.pipe = pipe  # parallel.pp.StageIO: this process holds one pipeline stage (all stages run this same engine)
+        if (pipe is not None) != (c.pp_size > 1) or (pipe is not None and pipe.world != c.pp_size):
+            raise ValueError("pp_size > 1 needs the stage's StageIO (parallel.pp.make_pipeline_groups) and vice versa")
         self.weights = weights
         self.cfg: ModelConfig = weights.cfg
         if weights.embed.device.type == "cuda" and c.kernel_options is not None:
@@ -80,7 +83,7 @@ class LLM:
 
             _opcuda.configure(c.kernel_options)
         self.model = Transformer(weights, comm, fold_norms=c.fold_norms, fuse_qkv_rope=c.fuse_qkv_rope,
-                                 fuse_swiglu=c.fuse_swiglu)
+                                 fuse_swiglu=c.fuse_swiglu, pipe=pipe)
         self.device = self.model.device
         self.tokenizer = tokenizer
         kv_dtype = c.kv_cache_dtype
@@ -103,7 +106,7 @@ class LLM:
     # ------------------------------------------------------------------ construction helpers
     @classmethod
     def from_gguf(cls, path: Union[str, GGUFFile], config: Optional[EngineConfig] = None, device=None, comm=None,
-                  tp_rank: int = 0, ep_rank: int = 0, rope_pairing: Optional[str] = None) -> "LLM":
+                  tp_rank: int = 0, ep_rank: int = 0, rope_pairing: Optional[str] = None, pipe=None) -> "LLM":
         from ..formats.tokenizer import TokenizerError, load_tokenizer_from_metadata
 
         config = config or EngineConfig()
@@ -118,12 +121,19 @@ class LLM:
             ep_rank = tp_rank  # the expert partition follows the tensor-parallel rank
         if ep_size == 1:
             ep_rank = 0
-        w = load_weights(g, cfg, device, act, tp_rank, config.tp_size, ep_rank, ep_size)
+        layer_range = None
+        if config.pp_size > 1:
+            from ..parallel.pp import split_layers
+
+            if pipe is None:
+                raise ValueError("pp_size > 1 needs the stage's StageIO")
+            layer_range = split_layers(cfg.n_layers, config.pp_size)[pipe.rank]
+        w = load_weights(g, cfg, device, act, tp_rank, config.tp_size, ep_rank, ep_size, layer_range=layer_range)
         try:
             tok = load_tokenizer_from_metadata(g.metadata)
         except TokenizerError:
             tok = None
-        return cls(w, config, comm, tok)
+        return cls(w, config, comm, tok, pipe)
 
     def _auto_blocks(self, spec: KVCacheSpec) -> int:
         c = self.config
@@ -183,15 +193,17 @@ class LLM:
                 if self.scheduler.has_work and not out.preempted:
                     raise RuntimeError("scheduler made no progress: KV pool too small for the waiting request")
                 return []
-            pending = self.runner.launch(out)
-        if self.config.async_decode and spec is None:
+            if self.pipe is not None:
+                return self._step_pipelined(out)
+            pending = self.runner.launch(out, needs_host_logits=bool(spec is not None and spec.needs_logits))
+        if self.config.async_decode and spec is None and self.pipe is None:
             nxt = self._schedule_ahead(out, pending)
             if nxt is not None:
                 self._inflight = (nxt, self.runner.launch(nxt, tokens_on_device=True))
         was_finished = [ss.seq.is_finished for ss in out.scheduled]
         res = self.runner.collect(pending)
         if spec is not None:
-            res.tokens = spec.after_forward(self, out, res.tokens)
+            res.tokens = spec.after_forward(self, out, res.tokens, res.logits)
         now = time.perf_counter()
         done = self.scheduler.postprocess(out, res.tokens, self.eos_token_id, now)
         if spec is not None:
@@ -211,6 +223,42 @@ class LLM:
             if ss.sample or ss.seq.is_finished:
                 outs.append(self._output(ss.seq))
         return outs
+
+    def _step_pipelined(self, out: SchedulerOutput) -> List[RequestOutput]:
+        """One step on a pipeline stage.  The scheduled sequences are cut into as many micro-batches as there are
+        stages (at most two are in flight on the staging buffers); every stage pushes all of them through its layers
+        before it waits for the first one's tokens, so stage i works on micro-batch j+1 while stage i+1 works on j
+        (the reference's pipeline streams positions the same way, ``oxidize-cli/src/pipeline.rs:17-21,302``)."""
+        n = len(out.scheduled)
+        parts = min(2, self.config.pp_size, n)
+        cuts = [n * i // parts for i in range(parts + 1)]
+        subs = []
+        for i in range(parts):
+            sch = out.scheduled[cuts[i] : cuts[i + 1]]
+            so = SchedulerOutput(sch, sum(s.num_tokens for s in sch if s.is_prefill),
+                                 sum(s.num_tokens for s in sch if not s.is_prefill), [], out.cow_copies if i == 0 else [])
+            subs.append(so)
+        pend = [self.runner.launch_forward(so) for so in subs]
+        for p in pend:
+            self.runner.finish(p)
+        tokens: Dict[int, List[int]] = {}
+        h2d = d2h = 0
+        for p in pend:
+            r = self.runner.collect(p)
+            tokens.update(r.tokens)
+            h2d += r.h2d_bytes
+            d2h += r.d2h_bytes
+        res = StepResult(tokens, None, h2d, d2h)
+        now = time.perf_counter()
+        self.scheduler.postprocess(out, res.tokens, self.eos_token_id, now)
+        st = self.stats
+        st["steps"] += 1
+        st["prefill_tokens"] += out.num_prefill_tokens
+        st["decode_tokens"] += out.num_decode_tokens
+        st["h2d_bytes"] += h2d
+        st["d2h_bytes"] += d2h
+        self.last_step = (out, res)
+        return [self._output(ss.seq) for ss in out.scheduled if ss.sample or ss.seq.is_finished]
 
     def drain(self) -> List[RequestOutput]:
         """Finish the step that is in flight, if any, without launching another one ahead of it."""

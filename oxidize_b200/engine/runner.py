@@ -111,6 +111,7 @@ class Pending:
     h2d_bytes: int
     bucket: int = 0  # decode-graph bucket the step replayed, 0 = eager
     seq_ids: tuple = ()  # row order of the step (decode-only steps)
+    finished: bool = True  # the token copy to the host has been enqueued (pipeline stages do that in finish())
 
 
 class ModelRunner:
@@ -122,7 +123,8 @@ class ModelRunner:
         self.page = kv.page_size
         self.max_blocks = (max_model_len + self.page - 1) // self.page
         self.buf = StagingBuffers(max_tokens, max_seqs, self.max_blocks, self.device)
-        self.use_graphs = use_cuda_graphs and self.device.type == "cuda"
+        # (a pipeline stage exchanges activations with its neighbours inside the step: no graph capture)
+        self.use_graphs = use_cuda_graphs and self.device.type == "cuda" and getattr(model, "pipe", None) is None
         self.graphs: Dict[int, "torch.cuda.CUDAGraph"] = {}
         self.graph_out: Dict[int, torch.Tensor] = {}
         self.out_hosts = [torch.zeros(max(max_tokens, max_seqs), dtype=torch.int32, pin_memory=self.device.type == "cuda")
@@ -305,6 +307,8 @@ class ModelRunner:
         if all_greedy and not self.keep_logits:
             return self.model.greedy_tokens(meta, self.kv, tie, feed=feed), None
         logits = self.model.forward(meta, self.kv)
+        if logits is None:
+            return None, None  # not the last pipeline stage: the tokens come from there
         if all_greedy:
             return ops.argmax(logits, tie), logits
         from . import device_sampler
@@ -322,6 +326,30 @@ class ModelRunner:
         """Build, upload and enqueue one step and the copy of its sampled tokens to the host, without waiting for it.
         ``tokens_on_device``: the step continues the decode step launched just before it with the same sequences in
         the same rows, whose kernel left each row's next input id in the device staging buffer."""
+        p = self.launch_forward(out, needs_host_logits, tokens_on_device)
+        return self.finish(p) if p is not None else None
+
+    def finish(self, p: Pending) -> Pending:
+        """Second half of a launch: every pipeline stage obtains the tokens the last stage sampled, and the copy of
+        the tokens to the host is enqueued.  Separate from ``launch_forward`` so that a stage can push several
+        micro-batches into the pipeline before it waits for the first one's tokens."""
+        if p.finished:
+            return p
+        pipe = getattr(self.model, "pipe", None)
+        if pipe is not None:
+            pipe.broadcast_tokens(p.toks)
+        if self.device.type == "cuda":
+            self._out_which ^= 1
+            hb = self.out_hosts[self._out_which]
+            hb[: p.n_out].copy_(p.toks, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            p.host_buf, p.event = hb, ev
+        p.finished = True
+        return p
+
+    def launch_forward(self, out: SchedulerOutput, needs_host_logits: bool = False,
+                       tokens_on_device: bool = False) -> Optional[Pending]:
         scheduled = out.scheduled
         if not scheduled:
             return None
@@ -359,17 +387,11 @@ class ModelRunner:
             meta = self._meta(T, B, nl, max_q, max_len, logits_all=decode_only and nl == T)
             toks, logits = self._forward_sample(meta, all_greedy and not needs_host_logits, tie,
                                                 feed=feed if not needs_host_logits else None)
-        n_out = toks.shape[0]
-        if self.device.type == "cuda":
-            self._out_which ^= 1
-            hb = self.out_hosts[self._out_which]
-            hb[:n_out].copy_(toks, non_blocking=True)
-            ev = torch.cuda.Event()
-            ev.record()
-        else:
-            hb, ev = None, None
-        return Pending(rows, n_out, toks, hb, ev, logits, host_rows, needs_host_logits or self.keep_logits, h2d, bucket,
-                       tuple(ss.seq.seq_id for ss in scheduled) if decode_only else ())
+        if toks is None:  # not the last pipeline stage
+            toks = torch.empty(nl, dtype=torch.int32, device=self.device)
+        toks = toks.to(torch.int32) if toks.dtype != torch.int32 else toks
+        return Pending(rows, toks.shape[0], toks, None, None, logits, host_rows, needs_host_logits or self.keep_logits, h2d,
+                       bucket, tuple(ss.seq.seq_id for ss in scheduled) if decode_only else (), finished=False)
 
     def collect(self, p: Pending) -> StepResult:
         """Wait for a launched step and return its tokens."""
@@ -380,8 +402,15 @@ class ModelRunner:
             host = p.toks.numpy()
         hl = host.tolist()
         result: Dict[int, List[int]] = {ss.seq.seq_id: hl[r0 : r0 + k] for ss, r0, k in p.rows}
+        pipe = getattr(self.model, "pipe", None)
         if p.host_rows:
-            self._host_sample(p.host_rows, p.logits, result)
+            if pipe is None:
+                self._host_sample(p.host_rows, p.logits, result)
+            else:
+                # only the last stage holds the logits: it draws, everybody gets the outcome
+                if pipe.is_last:
+                    self._host_sample(p.host_rows, p.logits, result)
+                result = pipe.broadcast_object(result if pipe.is_last else None)
         return StepResult(result, p.logits if p.keep_logits else None, p.h2d_bytes, p.n_out * 4)
 
     def _host_sample(self, host_rows, logits: torch.Tensor, result: Dict[int, List[int]]) -> None:

@@ -20,7 +20,7 @@ import torch
 from .. import ops
 from .kv_pool import BlockPool, KVCache, KVCacheSpec, make_block_pool
 from .runner import ModelRunner
-from .sampler import GREEDY, SamplingParams
+from .sampler import GREEDY, SamplingParams, probs_from_logits, speculative_accept
 from .scheduler import ScheduledSeq, SchedulerOutput, Sequence
 
 MAX_DRAFT_TOKENS_PER_STEP = 64
@@ -80,11 +80,17 @@ class DraftModelProposer:
         self.runner = ModelRunner(self.model, self.kv, max(2048, max_seqs * (k + 2)), max_seqs, max_model_len, False)
         self.shadow: Dict[int, Sequence] = {}
         self.computed: Dict[int, int] = {}
+        self.draft_logits: Dict[int, torch.Tensor] = {}  # seq_id -> [k, V] fp32 logits behind the sampled drafts
 
     def _shadow(self, seq: Sequence) -> Sequence:
         sh = self.shadow.get(seq.seq_id)
         if sh is None:
-            sh = Sequence([], GREEDY)
+            p = seq.params
+            # a sampled request drafts by sampling from the draft model at the request's temperature (the acceptance
+            # rule needs tokens drawn from the very distribution q it divides by); its own stream of uniforms
+            sp = GREEDY if p.is_greedy else SamplingParams(temperature=p.temperature, max_tokens=1 << 30, ignore_eos=True,
+                                                           seed=None if p.seed is None else p.seed + 7919, tie=p.tie)
+            sh = Sequence([], sp)
             self.shadow[seq.seq_id] = sh
             self.computed[seq.seq_id] = 0
         return sh
@@ -92,6 +98,7 @@ class DraftModelProposer:
     def release(self, seq: Sequence) -> None:
         sh = self.shadow.pop(seq.seq_id, None)
         self.computed.pop(seq.seq_id, None)
+        self.draft_logits.pop(seq.seq_id, None)
         if sh is not None:
             self.pool.release_all(sh.blocks)
 
@@ -110,16 +117,28 @@ class DraftModelProposer:
             done = min(self.computed[s.seq_id], len(sh.prompt) - 1)
             self._ensure(sh, len(sh.prompt) + self.k)
             sched.append(ScheduledSeq(sh, done, len(sh.prompt) - done, True, True))
-        for it in range(self.k):
-            res = self.runner.execute(SchedulerOutput(list(sched)))
-            sched = []
-            for s in seqs:
-                sh = self.shadow[s.seq_id]
-                t = res.tokens[sh.seq_id][0]
-                drafts[s.seq_id].append(t)
-                sh.prompt = sh.prompt + [t]
-                if it + 1 < self.k:
-                    sched.append(ScheduledSeq(sh, len(sh.prompt) - 1, 1, True, True))
+        sampled = [s for s in seqs if not s.params.is_greedy]
+        rows_of: Dict[int, List[torch.Tensor]] = {s.seq_id: [] for s in sampled}
+        keep, self.runner.keep_logits = self.runner.keep_logits, bool(sampled)
+        try:
+            for it in range(self.k):
+                res = self.runner.execute(SchedulerOutput(list(sched)))
+                if sampled:
+                    row_of = {ss.seq.seq_id: r0 + n - 1 for ss, r0, n in self.runner.last_rows}
+                sched = []
+                for s in seqs:
+                    sh = self.shadow[s.seq_id]
+                    t = res.tokens[sh.seq_id][0]
+                    drafts[s.seq_id].append(t)
+                    if s.seq_id in rows_of:
+                        rows_of[s.seq_id].append(res.logits[row_of[sh.seq_id]].float())
+                    sh.prompt = sh.prompt + [t]
+                    if it + 1 < self.k:
+                        sched.append(ScheduledSeq(sh, len(sh.prompt) - 1, 1, True, True))
+        finally:
+            self.runner.keep_logits = keep
+        for sid, rows in rows_of.items():
+            self.draft_logits[sid] = torch.stack(rows)
         for s in seqs:
             # KV is valid for every token fed so far (all but the last draft)
             self.computed[s.seq_id] = len(s.all_tokens) + self.k - 1
@@ -151,6 +170,8 @@ class MtpProposer:
         self.start: Dict[int, int] = {}
         self.hidden: Dict[int, torch.Tensor] = {}  # last verified hidden state per sequence
         self.max_blocks = (max_model_len + page - 1) // page
+        self.draft_logits: Dict[int, torch.Tensor] = {}  # seq_id -> [k, V] fp32 logits behind the sampled drafts
+        self._rng: Dict[int, object] = {}
 
     def observe_hidden(self, seq: Sequence, h: torch.Tensor) -> None:
         self.hidden[seq.seq_id] = h
@@ -159,6 +180,8 @@ class MtpProposer:
         self.pool.release_all(self.blocks.pop(seq.seq_id, []))
         self.hidden.pop(seq.seq_id, None)
         self.start.pop(seq.seq_id, None)
+        self.draft_logits.pop(seq.seq_id, None)
+        self._rng.pop(seq.seq_id, None)
 
     def rollback(self, seq: Sequence, n_valid_tokens: int) -> None:
         pass  # positions are rewritten on the next round
@@ -214,7 +237,25 @@ class MtpProposer:
             logits = ops.linear(xn, head).float()
             if m.w.tp_size > 1 and logits.shape[-1] != cfg.vocab_size:
                 logits = m.comm.all_gather_cat(logits, dim=-1)
-            toks = ops.argmax(logits)
+            temps = [0.0 if s.params.is_greedy else float(s.params.temperature) for s in ready]
+            if any(t > 0 for t in temps):
+                # sampled requests draft by sampling at their own temperature; the logits are kept for the acceptance rule
+                from . import device_sampler
+                from .sampler import RequestRng
+
+                f32 = dict(dtype=torch.float32, device=dev)
+                rnd = [self._rng.setdefault(s.seq_id, RequestRng(None if s.params.seed is None else s.params.seed + 104729)).next()
+                       if t > 0 else 0.0 for s, t in zip(ready, temps)]
+                toks = device_sampler.sample(logits, torch.tensor(temps, **f32), torch.zeros(B, **i32), torch.ones(B, **f32),
+                                             torch.zeros(B, **f32), torch.tensor(rnd, **f32))
+                for i, s in enumerate(ready):
+                    if temps[i] > 0:
+                        prev = self.draft_logits.get(s.seq_id) if it > 0 else None
+                        row = logits[i : i + 1].float()
+                        self.draft_logits[s.seq_id] = row if prev is None else torch.cat([prev, row])
+            else:
+                toks = ops.argmax(logits)
+            toks = toks.to(torch.int32)
             hid = hsum
             for i, s in enumerate(ready):
                 drafts[s.seq_id].append(int(toks[i]))
@@ -228,6 +269,7 @@ class SpecDecoder:
         self.proposer = proposer
         self.k = k
         self.stats = SpecStats()
+        self.needs_logits = False  # this step verifies sampled drafts: the runner must hand back the target logits
 
     def update_health(self, accepted: int, proposed: int) -> None:
         st = self.stats
@@ -238,23 +280,80 @@ class SpecDecoder:
             # far below any useful acceptance: stop paying for drafts
             st.disabled = True
 
+    @staticmethod
+    def drafts_for(p: SamplingParams) -> bool:
+        """Greedy requests, and sampled ones whose distribution is the plain softmax at a temperature (the acceptance
+        rule is exact for those; filters, penalties, Mirostat and grammars are drawn without drafts)."""
+        return p.is_greedy or (p.temperature > 0 and not p.has_filters and not p.needs_host_sampler)
+
     def before_schedule(self, llm) -> None:
+        self.needs_logits = False
         if self.stats.disabled:
             return
-        seqs = [s for s in llm.scheduler.running if s.remaining_prefill == 0 and s.output and s.params.is_greedy
+        seqs = [s for s in llm.scheduler.running if s.remaining_prefill == 0 and s.output and self.drafts_for(s.params)
                 and s.params.max_tokens - len(s.output) > self.k + 1
                 and s.num_tokens + self.k + 1 < llm.config.max_model_len]
         if not seqs:
             return
         drafts = self.proposer.propose(seqs)
+        logits_of = getattr(self.proposer, "draft_logits", {})
         for s in seqs:
             d = drafts.get(s.seq_id) or []
+            if not s.params.is_greedy and (s.seq_id not in logits_of or logits_of[s.seq_id].shape[0] < len(d[: self.k])):
+                d = []  # a sampled draft without its distribution cannot be verified
             s.draft_tokens = d[: self.k]
+            if s.draft_tokens and not s.params.is_greedy:
+                self.needs_logits = True
 
-    def after_forward(self, llm, out: SchedulerOutput, tokens: Dict[int, List[int]]) -> Dict[int, List[int]]:
-        """Turn the target's per-row argmax into the accepted token list per sequence."""
+    def _verify_sampled(self, llm, out: SchedulerOutput, logits: torch.Tensor) -> Dict[int, List[int]]:
+        """min(1, p/q) acceptance with residual resampling for the sampled sequences of this step: one kernel launch
+        on the GPU, the host statement of the same rule on CPU."""
+        rows = {ss.seq.seq_id: (r0, n) for ss, r0, n in getattr(llm.runner, "last_rows", [])}
+        todo = [ss.seq for ss in out.scheduled
+                if not ss.is_prefill and ss.num_tokens > 1 and not ss.seq.params.is_greedy and ss.seq.seq_id in rows]
+        if not todo:
+            return {}
+        K = self.k
+        dl = self.proposer.draft_logits
+        result: Dict[int, List[int]] = {}
+        uni = [[s.rng.next() for _ in range(2 * K + 1)] for s in todo]
+        if logits.is_cuda:
+            from ..ops import cuda as opcuda
+
+            dev = logits.device
+            i32, f32 = dict(dtype=torch.int32, device=dev), dict(dtype=torch.float32, device=dev)
+            V = logits.shape[1]
+            dlog = torch.zeros(len(todo) * K, V, **f32)
+            dtok = torch.zeros(len(todo), K, **i32)
+            for i, s in enumerate(todo):
+                n = len(s.draft_tokens)
+                dlog[i * K : i * K + n] = dl[s.seq_id][:n]
+                dtok[i, :n] = torch.tensor(s.draft_tokens, **i32)
+            toks, cnt = opcuda.spec_verify(logits.float().contiguous(), dlog, dtok,
+                                           torch.tensor([rows[s.seq_id][0] for s in todo], **i32),
+                                           torch.tensor([len(s.draft_tokens) for s in todo], **i32),
+                                           torch.tensor([s.params.temperature for s in todo], **f32),
+                                           torch.tensor(uni, **f32), K, todo[0].params.tie)
+            toks, cnt = toks.cpu().tolist(), cnt.cpu().tolist()
+            for i, s in enumerate(todo):
+                result[s.seq_id] = toks[i][: cnt[i]]
+        else:
+            lg = logits.float().numpy()
+            for s, u in zip(todo, uni):
+                r0, n = rows[s.seq_id]
+                q = [probs_from_logits(dl[s.seq_id][i].numpy(), s.params.temperature) for i in range(len(s.draft_tokens))]
+                # the bonus token is an inverse-CDF draw in index order from row K, like the kernel's
+                emitted, _ = speculative_accept(s.draft_tokens, q, lg[r0 : r0 + n], s.params, u)
+                result[s.seq_id] = emitted
+        return result
+
+    def after_forward(self, llm, out: SchedulerOutput, tokens: Dict[int, List[int]],
+                      logits: Optional[torch.Tensor] = None) -> Dict[int, List[int]]:
+        """Turn the target's rows into the accepted token list per sequence: exact match for greedy sequences (from the
+        per-row argmax), the rejection-sampling rule for sampled ones (from the rows' logits)."""
         self.stats.target_forwards += 1
         acc_total = prop_total = 0
+        sampled = self._verify_sampled(llm, out, logits) if (self.needs_logits and logits is not None) else {}
         for ss in out.scheduled:
             s = ss.seq
             if ss.is_prefill or ss.num_tokens == 1 or s.seq_id not in tokens:
@@ -262,7 +361,7 @@ class SpecDecoder:
                     self.stats.emitted += len(tokens[s.seq_id])
                 continue
             drafts = list(s.draft_tokens)
-            emitted = verify_greedy(drafts, tokens[s.seq_id])
+            emitted = sampled[s.seq_id] if s.seq_id in sampled else verify_greedy(drafts, tokens[s.seq_id])
             tokens[s.seq_id] = emitted
             acc_total += len(emitted) - 1
             prop_total += len(drafts)

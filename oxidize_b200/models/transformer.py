@@ -74,8 +74,10 @@ class SingleRankComm:
 
 class Transformer:
     def __init__(self, weights: ModelWeights, comm=None, act_dtype: Optional[torch.dtype] = None, fold_norms: bool = True,
-                 fuse_qkv_rope: bool = True, fuse_swiglu: bool = True):
+                 fuse_qkv_rope: bool = True, fuse_swiglu: bool = True, pipe=None):
         self.w = weights
+        self.pipe = pipe  # parallel.pp.StageIO when this model holds one pipeline stage's layers
+        self._sends: list = []  # activation sends still on the link
         self.cfg: ModelConfig = weights.cfg
         self.comm = comm or SingleRankComm()
         dev = weights.embed.device
@@ -262,7 +264,8 @@ class Transformer:
                     else:
                         residual = h.contiguous()
                     h = None
-                    acc = torch.empty(2, residual.shape[0], dtype=torch.int64, device=residual.device)
+                    # two accumulator arrays, one 128-byte line per token (ops.cuda.SUMSQ_STRIDE words)
+                    acc = torch.empty(2, residual.shape[0] * opcuda.SUMSQ_STRIDE, dtype=torch.int64, device=residual.device)
                     cur = 0
                     opcuda.row_sumsq(residual, acc[0])
                 cur = self._layer_folded(lw, li, residual, acc, cur, meta, kv)
@@ -289,6 +292,24 @@ class Transformer:
     def embed(self, token_ids: torch.Tensor) -> torch.Tensor:
         return ops.embed(token_ids, self.w.embed, self.act_dtype)
 
+    # ------------------------------------------------------------------ pipeline stages
+    def _stage_input(self, meta: BatchMeta):
+        """(h, residual) entering this stage's layers: the embedding on the first stage, the previous stage's
+        activations otherwise (one [2, T, H] message: h and the residual stream)."""
+        if self.pipe is None or self.pipe.is_first:
+            return self.embed(meta.token_ids), None
+        both = self.pipe.recv_prev((2, int(meta.token_ids.shape[0]), self.cfg.hidden_size), self.act_dtype, self.device)
+        return both[0], both[1]
+
+    def _stage_output(self, h: torch.Tensor, residual: Optional[torch.Tensor]) -> bool:
+        """Hand (h, residual) to the next stage without waiting for the link; True when this was not the last stage."""
+        if self.pipe is None or self.pipe.is_last:
+            return False
+        self._sends = [w for w in self._sends if not w.is_completed()]
+        msg = torch.stack([h, residual if residual is not None else torch.zeros_like(h)])
+        self._sends.append(self.pipe.send_next(msg))
+        return True
+
     def head(self, h: torch.Tensor, residual: Optional[torch.Tensor], logits_indices: torch.Tensor,
              return_hidden: bool = False):
         """Final norm + vocabulary-parallel lm_head on the selected rows; logits float32."""
@@ -307,8 +328,10 @@ class Transformer:
         each rank takes the argmax of its vocabulary shard and only (value, index) pairs are
         exchanged (vocabulary-parallel head, distributed argmax).  ``feed`` (int32, one entry per logits
         row) also receives the tokens: the next decode step's input ids, written where its kernels read them."""
-        h = self.embed(meta.token_ids)
-        h, residual = self.run_layers(h, None, meta, kv)
+        h, residual = self._stage_input(meta)
+        h, residual = self.run_layers(h, residual, meta, kv)
+        if self._stage_output(h, residual):
+            return None  # the tokens arrive from the last stage
         if not meta.logits_all:
             idx = meta.logits_indices.long()
             h = h.index_select(0, idx)
@@ -349,8 +372,10 @@ class Transformer:
         return toks
 
     def forward(self, meta: BatchMeta, kv, return_hidden: bool = False, capture: Optional[dict] = None):
-        h = self.embed(meta.token_ids)
-        h, residual = self.run_layers(h, None, meta, kv, capture=capture)
+        h, residual = self._stage_input(meta)
+        h, residual = self.run_layers(h, residual, meta, kv, capture=capture)
+        if self._stage_output(h, residual):
+            return None
         return self.head(h, residual, meta.logits_indices, return_hidden)
 
 

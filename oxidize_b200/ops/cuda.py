@@ -23,6 +23,8 @@ _lock = threading.Lock()
 QTYPE_CODE = {"F32": 0, "F16": 1, "BF16": 2, "Q8_0": 3, "Q4_0": 4, "Q4_K": 5, "Q5_K": 6, "Q6_K": 7, "NVFP4": 8}
 KV_MODE = {"bf16": 0, "f16": 1, "q8": 2, "q4": 3, "f32": 4}
 
+SUMSQ_STRIDE = 16  # int64 words between the sum-of-squares accumulators of neighbouring tokens (folded RMSNorm)
+
 launch_count = 0  # kernels launched through this module (bench.py reports it)
 
 
@@ -191,7 +193,8 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     """out[T, N] = x[T, K] @ w[N, K]^T on the tcgen05 kernel; ``out`` may be a column slice of a
     wider row-major buffer (pass its row stride as ``ld_out``).
 
-    The three accumulator arguments ([>= T] int64 tensors of 2^-28 fixed-point sums of squares, see :func:`row_sumsq`)
+    The three accumulator arguments (int64 tensors of 2^-28 fixed-point sums of squares, token t at word
+    ``t * SUMSQ_STRIDE``, see :func:`row_sumsq`)
     make the call one half of a folded RMSNorm.  ``sumsq_in``: ``x`` holds un-normalised rows and token t's result is
     scaled by 1/rms(x_t); ``clear`` is zeroed on the way for the producer that follows.  ``sumsq_out``: the epilogue adds
     the sums of squares of the rows it writes (the producer half; the array must have been cleared)."""
@@ -219,7 +222,8 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
 
 
 def row_sumsq(x: torch.Tensor, out: torch.Tensor, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[t] (int64, 2^-28 fixed point) = sum of squares of row t of ``x`` (bf16 [T, H]); ``clear`` is zeroed."""
+    """out[t * SUMSQ_STRIDE] (int64, 2^-28 fixed point) = sum of squares of row t of ``x`` (bf16 [T, H]); the same
+    words of ``clear`` are zeroed."""
     T, H = x.shape
     _check(lib().oxb_row_sumsq(x.data_ptr(), x.stride(0), T, H, out.data_ptr(), _p(clear), _stream()), "oxb_row_sumsq")
     return out
@@ -469,6 +473,29 @@ def argmax_tp(logits: torch.Tensor, tie: str = "lowest", index_offset: int = 0, 
                                _p(feed), index_offset, comm.size, comm.rank, comm._amax_ptrs, comm.amax_ctrl.data_ptr(),
                                comm.argmax_rows, ctypes.c_ulonglong(comm.timeout_ns), _stream()), "oxb_argmax_tp")
     return out
+
+
+def spec_verify(target_logits: torch.Tensor, draft_logits: Optional[torch.Tensor], draft_tokens: torch.Tensor,
+                row0: torch.Tensor, n_draft: torch.Tensor, temperature: torch.Tensor, uniforms: torch.Tensor, K: int,
+                tie: str = "lowest"):
+    """Verify the K drafted tokens of each of S sequences against their K+1 rows of target logits in one launch.
+    Returns (tokens [S, K+1] int32, count [S] int32): count[s] tokens were emitted for sequence s.  Greedy rows
+    (temperature <= 0) use the exact-match rule, sampled rows min(1, p/q) acceptance with residual resampling."""
+    S = int(row0.shape[0])
+    V = int(target_logits.shape[1])
+    assert target_logits.dtype == torch.float32 and (draft_logits is None or draft_logits.dtype == torch.float32)
+    toks = torch.zeros(S, K + 1, dtype=torch.int32, device=target_logits.device)
+    cnt = torch.zeros(S, dtype=torch.int32, device=target_logits.device)
+    L = lib()
+    if not getattr(L, "_spec_verify_declared", False):
+        vp, i32 = ctypes.c_void_p, ctypes.c_int
+        L.oxb_spec_verify.argtypes = [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
+        L._spec_verify_declared = True
+    _check(L.oxb_spec_verify(target_logits.data_ptr(), target_logits.stride(0), _p(draft_logits),
+                             0 if draft_logits is None else draft_logits.stride(0), draft_tokens.data_ptr(), row0.data_ptr(),
+                             n_draft.data_ptr(), temperature.data_ptr(), uniforms.data_ptr(), toks.data_ptr(), cnt.data_ptr(),
+                             S, K, V, 1 if tie == "highest" else 0, _stream()), "oxb_spec_verify")
+    return toks, cnt
 
 
 def sample(logits, temperature, top_k, top_p, min_p, random, tie="lowest"):

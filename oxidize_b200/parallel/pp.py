@@ -34,11 +34,18 @@ def split_layers(n_layers: int, n_stages: int) -> List[Tuple[int, int]]:
 
 @dataclass
 class StageIO:
-    """Blocking / non-blocking tensor hand-off between neighbouring stages."""
+    """Tensor hand-off between neighbouring stages and the token broadcast from the last stage.
+
+    ``rank`` / ``world`` count pipeline stages.  With tensor parallelism inside every stage the job has
+    ``world * tp_size`` processes laid out stage-major (global rank = stage * tp_size + tp_rank): a process talks to
+    the process with the same ``tp_rank`` in the neighbouring stage, and ``group`` (the processes that share this
+    ``tp_rank``) carries the token broadcast."""
 
     rank: int
     world: int
     group: Optional[object] = None
+    tp_size: int = 1
+    tp_rank: int = 0
 
     @property
     def is_first(self) -> bool:
@@ -48,21 +55,53 @@ class StageIO:
     def is_last(self) -> bool:
         return self.rank == self.world - 1
 
+    def _global(self, stage: int) -> int:
+        return stage * self.tp_size + self.tp_rank
+
     def send_next(self, t: torch.Tensor):
-        return dist.isend(t.contiguous(), self.rank + 1, group=self.group)
+        return dist.isend(t.contiguous(), self._global(self.rank + 1))
 
     def recv_prev(self, shape, dtype, device) -> torch.Tensor:
         buf = torch.empty(shape, dtype=dtype, device=device)
-        dist.recv(buf, self.rank - 1, group=self.group)
+        dist.recv(buf, self._global(self.rank - 1))
         return buf
 
     def send_tokens_to_first(self, toks: torch.Tensor):
-        return dist.isend(toks.contiguous(), 0, group=self.group)
+        return dist.isend(toks.contiguous(), self._global(0))
 
     def recv_tokens_from_last(self, n: int, device) -> torch.Tensor:
         buf = torch.empty(n, dtype=torch.int32, device=device)
-        dist.recv(buf, self.world - 1, group=self.group)
+        dist.recv(buf, self._global(self.world - 1))
         return buf
+
+    def broadcast_tokens(self, toks: torch.Tensor) -> torch.Tensor:
+        """Every stage obtains the tokens the last stage sampled (all stages run the same scheduler and need them)."""
+        dist.broadcast(toks, src=self._global(self.world - 1), group=self.group)
+        return toks
+
+    def broadcast_object(self, obj):
+        box = [obj]
+        dist.broadcast_object_list(box, src=self._global(self.world - 1), group=self.group)
+        return box[0]
+
+
+def make_pipeline_groups(world_size: int, rank: int, tp_size: int, pp_size: int):
+    """Process groups of a stage-major pp x tp job.  Returns (StageIO or None, tp_group or None); every process must
+    call this (group creation is collective)."""
+    if tp_size * pp_size != world_size:
+        raise ValueError(f"tp_size ({tp_size}) x pp_size ({pp_size}) must equal the number of processes ({world_size})")
+    tp_group = pp_group = None
+    if pp_size > 1 and tp_size > 1:
+        for st in range(pp_size):
+            g = dist.new_group([st * tp_size + j for j in range(tp_size)])
+            if rank // tp_size == st:
+                tp_group = g
+        for j in range(tp_size):
+            g = dist.new_group([st * tp_size + j for st in range(pp_size)])
+            if rank % tp_size == j:
+                pp_group = g
+    io = StageIO(rank // tp_size, pp_size, pp_group, tp_size, rank % tp_size) if pp_size > 1 else None
+    return io, tp_group
 
 
 class PipelineStage:

@@ -231,6 +231,45 @@ def case_pp_model(dev, comm_kind):
     assert out == want, (out, want)
 
 
+def case_pp_engine(dev, comm_kind):
+    """The engine with pp_size = world (or tp 2 x pp 2 on four ranks): stage-local layers, micro-batched steps,
+    activations over isend / recv, tokens broadcast from the last stage; same tokens as one process."""
+    from oxidize_b200.parallel.pp import make_pipeline_groups
+
+    layout = init_distributed()
+    W, rank = layout.world_size, layout.rank
+    tp = 2 if W == 4 else 1
+    pp = W // tp
+    path = _tiny_file(rank)
+    io, tp_group = make_pipeline_groups(W, rank, tp, pp)
+    assert io is not None and io.world == pp
+    comm = None
+    if tp > 1:
+        if dev.type == "cuda" and comm_kind == "fused":
+            from oxidize_b200.parallel.fused import FusedComm
+
+            comm = FusedComm(dev, max_tokens=1024, hidden=8192, group=tp_group)
+        else:
+            comm = TorchComm(tp_group)
+    ec = dict(max_model_len=128, max_num_seqs=4, num_kv_blocks=64, prefill_chunk_size=16, max_num_batched_tokens=48)
+    llm = LLM.from_gguf(path, EngineConfig(tp_size=tp, pp_size=pp, **ec), device=dev, comm=comm, tp_rank=rank % tp, pipe=io)
+    n_layers = config_from_gguf(load_gguf(path)).n_layers
+    assert len(llm.weights.layers) < n_layers, "a stage must hold only its own layers"
+    prompts = [[4, 8, 15, 16, 23, 42, 7], list(range(3, 40)), [9, 9], [60, 61, 62, 63]]
+    sp = SamplingParams(temperature=0.0, max_tokens=9, ignore_eos=True)
+    got = [o.token_ids for o in llm.generate(prompts, sp)]
+    # a sampled request too: the last stage draws, every stage must learn the same tokens
+    sps = SamplingParams(temperature=0.8, top_k=20, max_tokens=6, ignore_eos=True, seed=5)
+    got_s = [o.token_ids for o in llm.generate(prompts[:2], sps)]
+    one = LLM.from_gguf(path, EngineConfig(**ec), device=dev)
+    want = [o.token_ids for o in one.generate(prompts, sp)]
+    assert got == want, (got, want)
+    box = [None] * W
+    dist.all_gather_object(box, got_s)
+    assert all(b == box[0] for b in box), "stages disagree on the sampled tokens"
+    assert all(len(t) == 6 for t in got_s)
+
+
 def case_tp_graph(dev, comm_kind):
     """Decode under CUDA graphs with the fused collectives gives the same tokens as eager."""
     layout = init_distributed()
@@ -276,7 +315,7 @@ def case_rank_exit(dev, comm_kind):
     hb.stop()
 
 
-CASES = {"gemm_ar": case_gemm_ar, "tp_model": case_tp_model, "tp_graph": case_tp_graph, "rank_exit": case_rank_exit, "ep_model": case_ep_model, "ep1_model": case_ep1_model, "pp_model": case_pp_model}
+CASES = {"gemm_ar": case_gemm_ar, "tp_model": case_tp_model, "tp_graph": case_tp_graph, "rank_exit": case_rank_exit, "ep_model": case_ep_model, "ep1_model": case_ep1_model, "pp_model": case_pp_model, "pp_engine": case_pp_engine}
 
 
 def main():

@@ -475,17 +475,18 @@ def test_gemm_folded_rmsnorm_halves(C, T, N, K):
     w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
     eps = 1e-5
     FIX = float(1 << 28)
-    acc = torch.full((2, T), 12345, dtype=torch.int64, device="cuda")
+    S = C.SUMSQ_STRIDE
+    acc = torch.full((2, T * S), 12345, dtype=torch.int64, device="cuda")
     C.row_sumsq(x, acc[0], clear=acc[1])
     want_ss = x.float().pow(2).sum(-1)
-    assert _rel_err(acc[0].double() / FIX, want_ss.double()) < 1e-5 and int(acc[1].abs().sum()) == 0
+    assert _rel_err(acc[0][::S].double() / FIX, want_ss.double()) < 1e-5 and int(acc[1][::S].abs().sum()) == 0
     rstd = torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + eps)
     want = (x.float() * rstd) @ w.float().t()
     acc[1].fill_(777)
     got = C.gemm_bf16(x, w, sumsq_in=acc[0], eps=eps, clear=acc[1])
     torch.cuda.synchronize()
     assert _rel_err(got, want) < 6e-3
-    assert int(acc[1].abs().sum()) == 0, "the consumer clears the other accumulator"
+    assert int(acc[1][::S].abs().sum()) == 0, "the consumer clears the other accumulator"
     assert torch.equal(got, C.gemm_bf16(x, w, sumsq_in=acc[0], eps=eps))
     # producer: r += x @ w^T, with the sums of squares of the new r added to a cleared accumulator
     r0 = torch.randn(T, N, device="cuda").to(torch.bfloat16)
@@ -494,7 +495,7 @@ def test_gemm_folded_rmsnorm_halves(C, T, N, K):
     torch.cuda.synchronize()
     want_r = r0.float() + x.float() @ w.float().t()
     assert _rel_err(r, want_r) < 6e-3
-    assert _rel_err(acc[1].double() / FIX, r.double().pow(2).sum(-1)) < 1e-5
+    assert _rel_err(acc[1][::S].double() / FIX, r.double().pow(2).sum(-1)) < 1e-5
     _check_status(C)
 
 
@@ -609,4 +610,82 @@ def test_decode_graph_with_padded_rows_after_sequences_finish(C):
     for _ in range(3):
         llm.step()
     torch.cuda.synchronize()
+    _check_status(C)
+
+
+def test_spec_verify_kernel_greedy_and_sampled(C):
+    """Device verification: exact-match rule for greedy rows, min(1, p/q) + residual resampling for sampled rows
+    (first emitted token distributed as the target's p; acceptance rate sum_v min(p, q); bonus token after full
+    acceptance)."""
+    from oxidize_b200.engine.sampler import probs_from_logits
+    from oxidize_b200.engine.spec import verify_greedy
+
+    rng = np.random.default_rng(2)
+    # ---- greedy: K = 3, several sequences, rows packed back to back
+    V, K, S = 1000, 3, 6
+    tl = torch.from_numpy(rng.normal(0, 2, (S * (K + 1), V)).astype(np.float32)).cuda()
+    targ = tl.argmax(-1).view(S, K + 1).cpu().numpy()
+    drafts = targ[:, :K].copy()
+    drafts[1, 0] += 1      # first draft wrong
+    drafts[2, 2] += 1      # last draft wrong
+    drafts[4, 1] += 1
+    drafts %= V
+    i32 = dict(dtype=torch.int32, device="cuda")
+    f32 = dict(dtype=torch.float32, device="cuda")
+    toks, cnt = C.spec_verify(tl, None, torch.tensor(drafts, **i32), torch.arange(S, **i32) * (K + 1),
+                              torch.full((S,), K, **i32), torch.zeros(S, **f32), torch.zeros(S, 2 * K + 1, **f32), K)
+    toks, cnt = toks.cpu().numpy(), cnt.cpu().numpy()
+    for s in range(S):
+        want = verify_greedy(list(drafts[s]), list(targ[s]))
+        assert list(toks[s][: cnt[s]]) == want
+    # ---- sampled: K = 1, one launch of many independent trials over the same two target rows
+    V, K, S, T = 17, 1, 20000, 0.8
+    t2 = rng.normal(0, 1.5, (2, V)).astype(np.float32)
+    d1 = rng.normal(0, 1.5, (1, V)).astype(np.float32)
+    p, q = probs_from_logits(t2[0], T), probs_from_logits(d1[0], T)
+    dtok = rng.choice(V, size=S, p=q).astype(np.int32)
+    uni = rng.random((S, 3)).astype(np.float32)
+    toks, cnt = C.spec_verify(torch.from_numpy(t2).cuda(), torch.from_numpy(np.repeat(d1, S, 0)).cuda(),
+                              torch.from_numpy(dtok).cuda().view(S, 1), torch.zeros(S, **i32), torch.ones(S, **i32),
+                              torch.full((S,), T, **f32), torch.from_numpy(uni).cuda(), K)
+    torch.cuda.synchronize()
+    toks, cnt = toks.cpu().numpy(), cnt.cpu().numpy()
+    first = toks[:, 0]
+    exp = p * S
+    chi2 = float(((np.bincount(first, minlength=V) - exp) ** 2 / np.maximum(exp, 1e-9)).sum())
+    assert chi2 < 45.0, chi2
+    accepted = (first == dtok) & (cnt == 2)
+    assert abs((cnt == 2).mean() - np.minimum(p, q).sum()) < 0.02
+    assert accepted.sum() == (cnt == 2).sum()
+    # the bonus token after a full acceptance follows the second target row
+    bonus = toks[cnt == 2, 1]
+    pb = probs_from_logits(t2[1], T) * len(bonus)
+    assert float(((np.bincount(bonus, minlength=V) - pb) ** 2 / np.maximum(pb, 1e-9)).sum()) < 45.0
+    _check_status(C)
+
+
+def test_sampled_speculation_on_gpu(C, tmp_path):
+    """Draft model + temperature sampling end to end on the GPU: the kernel verifies, every request finishes, a draft
+    equal to the target is almost always accepted; greedy requests in the same batch stay exact."""
+    from oxidize_b200.engine.llm import LLM, EngineConfig
+    from oxidize_b200.engine.sampler import SamplingParams
+    from oxidize_b200.engine.spec import attach_speculation
+    from oxidize_b200.models.config import preset
+    from oxidize_b200.utils.synth import synth_gguf
+
+    cfg = preset("tiny-llama", n_layers=2, vocab_size=512)
+    path = str(tmp_path / "spec_gpu.gguf")
+    synth_gguf(path, cfg, "BF16", seed=0, norm_jitter=0.05)
+    ec = dict(max_model_len=160, max_num_seqs=4, num_kv_blocks=64, prefill_chunk_size=32, max_num_batched_tokens=96)
+    prompts = [[5, 9, 200, 31, 7], list(range(3, 40)), [100, 101]]
+    greedy = SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True)
+    want = [o.token_ids for o in LLM.from_gguf(path, EngineConfig(**ec), device="cuda").generate(prompts[:1], greedy)]
+    llm = LLM.from_gguf(path, EngineConfig(**ec), device="cuda")
+    spec = attach_speculation(llm, path, k=3)
+    sps = [greedy, SamplingParams(temperature=0.9, max_tokens=16, ignore_eos=True, seed=3),
+           SamplingParams(temperature=0.7, max_tokens=16, ignore_eos=True, seed=4)]
+    outs = llm.generate(prompts, sps)
+    assert outs[0].token_ids == want[0]
+    assert all(len(o.token_ids) == 16 and all(0 <= t < 512 for t in o.token_ids) for o in outs)
+    assert spec.stats.proposed > 0 and spec.stats.acceptance_rate > 0.8, spec.stats
     _check_status(C)

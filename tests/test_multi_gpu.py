@@ -42,6 +42,19 @@ def test_expert_parallel_moe_matches_single_rank():
 
 
 @NEED2
+def test_engine_with_two_pipeline_stages_on_gpus():
+    """pp_size = 2 through the engine: stage-local layers on each GPU, micro-batched steps, NCCL p2p hand-off."""
+    r = run_ranks("pp_engine", n=2, device="cuda", comm="nccl", env_extra=ENV)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_engine_with_tp2_x_pp2_on_gpus():
+    r = run_ranks("pp_engine", n=4, device="cuda", comm="fused", env_extra=ENV)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@NEED2
 def test_rank_exit_between_steps_is_detected():
     r = run_ranks("rank_exit", n=2, device="cuda", comm="nccl", env_extra=ENV)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]

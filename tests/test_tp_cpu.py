@@ -75,6 +75,18 @@ def test_pp2_tokens_match_single_process_on_cpu():
     assert r.stdout.count("OK pp_model") == 2
 
 
+def test_engine_with_two_pipeline_stages_on_cpu():
+    r = run_ranks("pp_engine")
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("OK pp_engine") == 2
+
+
+def test_engine_with_tp2_x_pp2_on_cpu():
+    r = run_ranks("pp_engine", n=4)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("OK pp_engine") == 4
+
+
 def test_rank_exit_detected_by_heartbeat():
     r = run_ranks("rank_exit")
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
