@@ -57,6 +57,9 @@ def parse_args():
                     help="skip the whole-workload run (all requests from arrival to their last token)")
     ap.add_argument("--sync-decode", action="store_true", help="do not keep a decode step in flight ahead of the host")
     ap.add_argument("--no-fold-norms", action="store_true", help="keep RMSNorm as stand-alone kernels (A/B measurement)")
+    ap.add_argument("--expert-quant", default=None, help="encoding of the MoE expert matrices when it differs from --quant")
+    ap.add_argument("--draft-model", default=None, help="preset of a draft model: measure speculative decoding as well")
+    ap.add_argument("--draft-tokens", type=int, default=4)
     return ap.parse_args()
 
 
@@ -163,6 +166,8 @@ def main():
     gen_so_far = rng.integers(0, max(1, args.out_tokens - args.steps - args.warmup - 8), size=B)
     ctx = (prompt_lens + gen_so_far).astype(int)
     total_steps = args.steps * 3 + args.warmup * 3 + 8
+    if args.draft_model:
+        total_steps += (args.steps + max(2, args.warmup) + 2) * (args.draft_tokens + 1)
     if not args.no_prefill:
         # sequences that finish their prefill early keep decoding while the others are still prefilling
         total_steps += int(ctx.sum()) // 1900 + 8
@@ -180,7 +185,8 @@ def main():
             comm = FusedComm(dev, max_tokens=max(B, 2048), hidden=cfg.hidden_size)
         else:
             comm = TorchComm()
-    weights = synth_weights(cfg, dev, args.quant, seed=0, tp_rank=rank, tp_size=world, ep_rank=rank, ep_size=world)
+    weights = synth_weights(cfg, dev, args.quant, seed=0, tp_rank=rank, tp_size=world, ep_rank=rank, ep_size=world,
+                            expert_quant=args.expert_quant)
     # The whole-workload run needs KV for every request's prompt and all of its output tokens at once; it is run only
     # where that fits beside the weights (it does not beside 141 GB of bf16 weights on a single GPU).
     run_workload = not (args.no_workload or args.no_prefill or args.shard_sim or args.layers)
@@ -342,6 +348,41 @@ def main():
         bs1_ms = b0.elapsed_time(b1) / args.steps
         llm.scheduler.running = [keep] + parked
 
+    # ---- speculative decoding (draft model of a named shape, random weights): cost structure of draft + verify
+    spec_out = None
+    if args.draft_model:
+        from oxidize_b200.engine.spec import DraftModelProposer, SpecDecoder
+
+        llm.drain()
+        dcfg = preset(args.draft_model, vocab_size=cfg.vocab_size)
+        dw = synth_weights(dcfg, dev, "BF16", seed=1)
+        k = args.draft_tokens
+        llm.spec = SpecDecoder(DraftModelProposer(dw, k, B, max_len), k)
+        llm.spec.update_health = lambda a, p: (setattr(llm.spec.stats, "proposed", llm.spec.stats.proposed + p),
+                                               setattr(llm.spec.stats, "accepted", llm.spec.stats.accepted + a))
+        for _ in range(max(2, args.warmup)):
+            llm.step()
+        barrier()
+        n0 = sum(len(s.output) for s in llm.scheduler.running)
+        st = llm.spec.stats
+        p0, a0, f0 = st.proposed, st.accepted, st.target_forwards
+        s0 = time.perf_counter()
+        for _ in range(args.steps):
+            llm.step()
+        barrier()
+        sp_s = time.perf_counter() - s0
+        emitted = sum(len(s.output) for s in llm.scheduler.running) - n0
+        prop, acc, fw = st.proposed - p0, st.accepted - a0, st.target_forwards - f0
+        tpf = emitted / max(fw, 1) / max(len(llm.scheduler.running), 1)
+        spec_out = {"draft_model": args.draft_model, "draft_tokens": k, "tok_s": round(emitted / sp_s, 2),
+                    "acceptance_rate": round(acc / max(prop, 1), 4), "tokens_per_target_forward": round(tpf, 3),
+                    "target_forwards_per_s": round(fw / sp_s, 2),
+                    # the same step rate if every draft were accepted (k + 1 tokens per sequence and step): the
+                    # ceiling that a trained draft approaches; random-init drafts are accepted by chance only
+                    "tok_s_at_full_acceptance": round(fw / sp_s * (k + 1) * len(llm.scheduler.running), 2),
+                    "acceptance_normalized_tok_s": round(emitted / sp_s / max(tpf, 1e-9), 2)}
+        llm.spec = None
+
     times = torch.tensor([dev_ms, e2e_ms, e2e_wall_ms, bs1_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -358,7 +399,8 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random N(0,0.02) weights, uniform random token ids)",
             "impl": "oxidize_b200",
             "config": {"model": args.model, "global_batch": B, "seq_len": f"prompt U[{args.prompt_min},{args.prompt_max}] + up to {args.out_tokens} generated",
-                       "mean_context": float(ctx.mean()), "parallelism": f"tp{world}", "weights": args.quant,
+                       "mean_context": float(ctx.mean()), "parallelism": f"tp{world}" + (f"+ep{world}" if cfg.is_moe else ""),
+                       "weights": args.quant + (f" (experts {args.expert_quant})" if args.expert_quant else ""),
                        "kv_cache": f"paged, {page}-token pages, {args.kv_dtype}", "comm": args.comm if world > 1 else "none",
                        "l2_policy": "inputs larger than L2 (weight shard + KV pages streamed every step)",
                        "layers": cfg.n_layers, "valid": not bool(args.layers or args.shard_sim),
@@ -367,7 +409,7 @@ def main():
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": int(launches_per_step * args.steps) if graph is not None else int(C.launch_count),
             "clocks": sampler.summary(),
-            "workload": workload, "steady_state_prefill_ttft_p50_s": ttft_p50,
+            "workload": workload, "speculative": spec_out, "steady_state_prefill_ttft_p50_s": ttft_p50,
             "ttft_p50_s": workload["ttft_p50_s"] if workload else ttft_p50, "bs1_tok_s": round(1e3 / bs1_ms, 2) if bs1_ms > 0 else None,
             "bs1_ms_per_step": round(bs1_ms, 4), "load_s": round(load_s, 1),
             "device_status": {"code": code, "detail": detail, "count": count},
@@ -375,12 +417,20 @@ def main():
         print(json.dumps(out))
     sys.stdout.flush()
     sys.stderr.flush()
+    # Orderly shutdown: the step in flight and the captured graphs go first, then the peer mappings (after a barrier),
+    # then the process group.  A watchdog ends the process if a peer has already gone and the teardown cannot finish.
     if world > 1:
-        # The measurements are done and reduced.  Tearing down NCCL communicators that were
-        # captured into CUDA graphs (and the symmetric-memory mappings) can block at exit, so
-        # leave without running the teardown: every rank has finished its collectives.
-        torch.cuda.synchronize()
-        os._exit(0)
+        bye = threading.Timer(30.0, lambda: os._exit(0))
+        bye.daemon = True
+        bye.start()
+    llm.close()
+    if world > 1:
+        if hasattr(comm, "close"):
+            comm.close()
+        else:
+            dist.barrier()
+        del llm
+        dist.destroy_process_group()
     return 0
 
 

@@ -90,6 +90,7 @@ def build_parser() -> argparse.ArgumentParser:
     a("--tp", type=int, default=0)
     a("--ep", type=int, default=0)
     a("--pp", type=int, default=1)
+    a("--dp", type=int, default=1, help="serve: independent engine replicas (one per GPU) behind one front")
     a("--parallelism", default="tensor", choices=["pipeline", "tensor"])
     a("--kv-page-size", type=int, default=16)
     a("--max-running", type=int, default=0)
@@ -159,7 +160,7 @@ def resolve_model(name: Optional[str]) -> str:
     raise SystemExit(f"error: model {name!r} not found")
 
 
-def make_engine(args, passed: set):
+def make_engine(args, passed: set, device_index: Optional[int] = None):
     import torch
 
     from ..engine.llm import LLM, EngineConfig
@@ -219,7 +220,9 @@ def make_engine(args, passed: set):
                 comm = FusedComm(torch.device("cuda", torch.cuda.current_device()), hidden=fp.hidden_size, group=tp_group)
             else:
                 comm = TorchComm(tp_group)
-    dev = "cpu" if backend == "cpu" else f"cuda:{torch.cuda.current_device()}"
+    dev = "cpu" if backend == "cpu" else f"cuda:{torch.cuda.current_device() if device_index is None else device_index}"
+    if backend == "cuda" and device_index is not None:
+        torch.cuda.set_device(device_index)
     llm = LLM.from_gguf(g, ec, device=dev, comm=comm, tp_rank=tp_rank, ep_rank=tp_rank, rope_pairing=args.rope_pairing,
                         pipe=pipe)
     if args.tokenizer_model:
@@ -323,6 +326,18 @@ def cmd_serve(args, passed) -> int:
 
             control = SpmdControl()
         engine = AsyncEngine(llm, control=control)
+        if args.dp > 1:
+            # data parallelism: further complete replicas, each on its own GPU, behind a least-loaded router
+            if control is not None:
+                raise SystemExit("error: --dp replicas are single-GPU engines; do not combine with --tp / --pp")
+            from ..engine.async_engine import ReplicaRouter
+
+            replicas = [engine]
+            for i in range(1, args.dp):
+                other, _ = make_engine(args, passed, device_index=i if llm.device.type == "cuda" else None)
+                install_suppressed_tokens(other)
+                replicas.append(AsyncEngine(other, name=f"oxidize-batch-engine-{i}"))
+            engine = ReplicaRouter(replicas)
     state = ServerState(engine, args.model_id, GenerationDefaults(max_tokens=args.max_tokens or 512,
                                                                   temperature=args.temperature, top_p=args.top_p,
                                                                   top_k=args.top_k), chat_template=tpl)

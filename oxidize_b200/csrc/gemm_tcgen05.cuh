@@ -313,6 +313,11 @@ struct GroupArgs {
   const float* scale;  // [groups, scale_ld] or null (never skip)
   int scale_ld;
   int l2_prefetch_kb;  // weight k-blocks to request into the L2 before the grid dependency (any launch)
+  // Token-gathered groups (mixture-of-experts dispatch): group z multiplies activation rows
+  // [row_offsets[z], row_offsets[z + 1]) (device array, written by the upstream kernel) and writes the same rows
+  // of Y; blockIdx.z = z * t_tiles + token tile, and a CTA whose tile lies past the group's rows leaves at once.
+  const int* row_offsets;
+  int t_tiles;
 };
 
 // QT == QT_BF16: both operands arrive by TMA.  Any other QT: the weight tile is produced by four
@@ -324,8 +329,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
                  int splits, float* __restrict__ ws, int* __restrict__ counters, int epi_mode, const ArArgs ar,
                  const QwArgs qw, const GroupArgs gr, const RopeArgs ro, const NormArgs nm) {
   constexpr bool MMQ = QT != QT_BF16;
-  const int zg = gr.enabled ? (int)blockIdx.z : 0;
-  if (gr.enabled && gr.scale != nullptr) {
+  const bool gathered = gr.enabled && gr.row_offsets != nullptr;
+  const int zg = gr.enabled ? (gathered ? (int)blockIdx.z / gr.t_tiles : (int)blockIdx.z) : 0;
+  int g_row0 = 0;  // first activation / output row of this group (gathered groups)
+  if (gathered) {
+    pdl_wait();  // the row lists come from the upstream kernel
+    g_row0 = gr.row_offsets[zg];
+    T = gr.row_offsets[zg + 1] - g_row0;  // this group's own row count
+    if (((int)blockIdx.z % gr.t_tiles) * TN >= T) {
+      pdl_launch_dependents();
+      return;
+    }
+  }
+  if (gr.enabled && !gathered && gr.scale != nullptr) {
     // the routing weights come from the upstream kernel
     pdl_wait();
     int any = 0;
@@ -335,7 +351,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       return;
     }
   }
-  Y += (size_t)zg * gr.y_stride;
+  Y += gathered ? (size_t)g_row0 * ldY : (size_t)zg * gr.y_stride;
   using Cfg = GemmTile<TN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -354,9 +370,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * GEMM_BM;
   const int split = blockIdx.y;
-  const int t0 = gr.enabled ? 0 : blockIdx.z * TN;
+  const int t0 = gathered ? ((int)blockIdx.z % gr.t_tiles) * TN : (gr.enabled ? 0 : blockIdx.z * TN);
   const int w_row0 = n0 + zg * gr.w_rows;  // first weight row of this tile in the (stacked) matrix
-  const int x_row0 = t0 + zg * gr.x_rows;
+  const int x_row0 = gathered ? g_row0 + t0 : t0 + zg * gr.x_rows;
   const int kb_total = (K + GEMM_BK - 1) / GEMM_BK;
   const int kb_begin = (int)((long long)split * kb_total / splits);
   const int kb_end = (int)((long long)(split + 1) * kb_total / splits);
@@ -587,7 +603,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     const bool ok = ticket[1] != 0;
     tc_fence_after();
     const float b = (bias != nullptr && n < N) ? bias[n] : 0.f;
-    const int tile_id = blockIdx.z * gridDim.x + blockIdx.x;
+    const int tile_id = blockIdx.z * gridDim.x + blockIdx.x;  // (unique per CTA of a split group in every launch mode)
     const bool use_ar = ar.world > 0;
     const int tvalid = min(TN, T - t0);
     // 16-byte output rows: the tile goes through shared memory as bf16 [token][128 rows] and leaves
@@ -889,7 +905,7 @@ template <int TN, int QT = QT_BF16>
 int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y, const float* bias, int N, int T, int K,
                 int ldY, const GemmPlan& p, float* ws, int* counters, int epi_mode, const ArArgs& ar,
                 cudaStream_t stream, const QwArgs& qw = QwArgs{nullptr, 0, nullptr, 0},
-                const GroupArgs& gr = GroupArgs{0, 0, 0, 0, nullptr, 0, 0}, int groups = 1,
+                const GroupArgs& gr = GroupArgs{0, 0, 0, 0, nullptr, 0, 0, nullptr, 1}, int groups = 1,
                 const RopeArgs& ro = RopeArgs{nullptr, nullptr, nullptr, 0, 0, 0, 0, 0, 0, 0, nullptr, nullptr},
                 const NormArgs& nm = NormArgs{nullptr, 0.f, 0.f, nullptr, nullptr}) {
   using Cfg = GemmTile<TN>;
@@ -908,7 +924,7 @@ int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y
     const int mc = gemm_max_cluster<TN, QT>();
     if (splits > mc) splits = mc;
   }
-  dim3 grid(p.n_tiles, splits, gr.enabled ? groups : p.t_tiles);
+  dim3 grid(p.n_tiles, splits, gr.enabled ? (gr.row_offsets != nullptr ? groups * gr.t_tiles : groups) : p.t_tiles);
   const dim3 block(QT == QT_BF16 ? GEMM_THREADS : GEMM_THREADS_MMQ);
   cudaError_t le;
   GroupArgs grl = gr;
@@ -929,7 +945,7 @@ int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y
 template <int QT>
 int gemm_launch_mmq(const CUtensorMap& tmX, __nv_bfloat16* Y, const float* bias, int N, int T, int K, int ldY,
                     const GemmPlan& p, float* ws, int* counters, int epi_mode, const ArArgs& ar, cudaStream_t stream,
-                    const QwArgs& qw, const GroupArgs& gr = GroupArgs{0, 0, 0, 0, nullptr, 0, 0}, int groups = 1,
+                    const QwArgs& qw, const GroupArgs& gr = GroupArgs{0, 0, 0, 0, nullptr, 0, 0, nullptr, 1}, int groups = 1,
                     const CUtensorMap* tmWq = nullptr) {
   // tmWq: byte map of the packed rows (needed by the staged Q4_K path); other formats never touch tmW
   const CUtensorMap& tmW = tmWq != nullptr ? *tmWq : tmX;

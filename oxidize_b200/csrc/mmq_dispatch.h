@@ -13,7 +13,7 @@ namespace oxb {
 #define OXB_MMQ_ARGS_DEFAULTED                                                                                                \
   const CUtensorMap &tmX, __nv_bfloat16 *Y, const float *bias, int N, int T, int K, int ldY, const GemmPlan &p, float *ws,       \
       int *counters, int epi_mode, const ArArgs &ar, cudaStream_t stream, const QwArgs &qw,                                     \
-      const GroupArgs &gr = GroupArgs{0, 0, 0, 0, nullptr, 0, 0}, int groups = 1, const CUtensorMap *tmWq = nullptr
+      const GroupArgs &gr = GroupArgs{0, 0, 0, 0, nullptr, 0, 0, nullptr, 1}, int groups = 1, const CUtensorMap *tmWq = nullptr
 
 int gemm_mmq_q4_k(OXB_MMQ_ARGS_DEFAULTED);
 int gemm_mmq_q6_k(OXB_MMQ_ARGS_DEFAULTED);

@@ -14,6 +14,7 @@
 // the reference routes on the device with k_moe_route<<<1,1>>> (oxidize-c/src/backends/cuda.cu:495).
 #pragma once
 #include "common.cuh"
+#include "comm_fused.cuh"
 
 namespace oxb {
 
@@ -193,6 +194,188 @@ static __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, c
     o.z = pack_bf16x2(acc[4], acc[5]);
     o.w = pack_bf16x2(acc[6], acc[7]);
     *reinterpret_cast<uint4*>(out + (size_t)t * H + i * 8) = o;
+  }
+}
+
+// ----------------------------------------------------------------------------- token dispatch (permute) for the grouped expert GEMM
+// After routing, the rows that the experts held by THIS rank must process are gathered expert by expert into one
+// contiguous matrix, so that the grouped GEMM multiplies every expert with exactly its own tokens (instead of all
+// tokens with every active expert) and the whole layer stays on the device for any token count:
+//   moe_permute_kernel   (ids [T, k]) -> offsets [n_local + 1], perm [T*k] (source token of gathered row r),
+//                        inv [T, k] (gathered row that holds token t's k-th expert output, -1 if that expert
+//                        lives on another rank)
+//   moe_gather_kernel    Xg[r] = X[perm[r]]
+//   grouped GEMMs        rows [offsets[e], offsets[e+1]) x expert e  (GroupArgs::row_offsets)
+//   moe_combine_gathered out[t] = sum_k w[t, k] * Y[inv[t, k]] (+ shared expert)
+// With expert parallelism the tokens are already on every rank (they leave the attention all-reduce replicated),
+// so the dispatch crosses no link; what crosses NVLink is the combine, see moe_combine_exchange_kernel.
+// One CTA: the lists of a step are a few thousand entries at most.
+static __global__ void __launch_bounds__(1024)
+moe_permute_kernel(const int* __restrict__ ids, int T, int k, int first_local, int n_local, int* __restrict__ offsets,
+                   int* __restrict__ perm, int* __restrict__ inv) {
+  __shared__ int cnt[MOE_MAX_EXPERTS];
+  __shared__ int off[MOE_MAX_EXPERTS + 1];
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int e = threadIdx.x; e < n_local; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  const int n = T * k;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = ids[i] - first_local;
+    if (e >= 0 && e < n_local) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int s = 0;
+    for (int e = 0; e < n_local; ++e) {
+      off[e] = s;
+      s += cnt[e];
+    }
+    off[n_local] = s;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= n_local; e += blockDim.x) offsets[e] = off[e];
+  for (int e = threadIdx.x; e < n_local; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  // The order of the rows inside one expert's range depends on thread scheduling; nothing downstream depends on it
+  // (every row is multiplied on its own, and the combine walks inv[] in the order of the routing list).
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = ids[i] - first_local;
+    if (e >= 0 && e < n_local) {
+      const int pos = off[e] + atomicAdd(&cnt[e], 1);
+      perm[pos] = i / k;
+      inv[i] = pos;
+    } else {
+      inv[i] = -1;
+    }
+  }
+}
+
+// Xg[r, :] = X[perm[r], :] for r < offsets[n_local]; 16-byte chunks, grid-stride over rows
+static __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ X, int H, const int* __restrict__ perm,
+                                         const int* __restrict__ n_rows_dev, __nv_bfloat16* __restrict__ Xg) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int R = *n_rows_dev;
+  const int H8 = H >> 3;
+  for (int r = blockIdx.x; r < R; r += gridDim.x) {
+    const uint4* src = reinterpret_cast<const uint4*>(X + (size_t)perm[r] * H);
+    uint4* dst = reinterpret_cast<uint4*>(Xg + (size_t)r * H);
+    for (int i = threadIdx.x; i < H8; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+// SiLU(gate) * up over the first *n_rows_dev rows of a [rows, 2I] matrix
+static __global__ void silu_mul_rows_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                                            const int* __restrict__ n_rows_dev, int I) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int I8 = I >> 3;
+  const size_t total = (size_t)(*n_rows_dev) * I8;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / I8;
+    const int i = (int)(idx % I8) * 8;
+    const uint4 g = *reinterpret_cast<const uint4*>(gu + t * 2 * I + i);
+    const uint4 u = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + i);
+    const uint32_t gs[4] = {g.x, g.y, g.z, g.w}, us[4] = {u.x, u.y, u.z, u.w};
+    uint4 o;
+    uint32_t* os = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 a = unpack_bf16x2(gs[j]), b = unpack_bf16x2(us[j]);
+      os[j] = pack_bf16x2(a.x / (1.f + __expf(-a.x)) * b.x, a.y / (1.f + __expf(-a.y)) * b.y);
+    }
+    *reinterpret_cast<uint4*>(out + t * I + i) = o;
+  }
+}
+
+// weighted sum of one token's expert outputs for 8 columns starting at col
+__device__ __forceinline__ void moe_combine8(const __nv_bfloat16* __restrict__ Y, int H, const int* __restrict__ inv,
+                                             const float* __restrict__ wts, int k, int t, int col,
+                                             const __nv_bfloat16* __restrict__ shared, float (&acc)[8]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  if (shared != nullptr) {
+    const uint4 v = *reinterpret_cast<const uint4*>(shared + (size_t)t * H + col);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(u[j]);
+      acc[2 * j] = f.x;
+      acc[2 * j + 1] = f.y;
+    }
+  }
+  for (int i = 0; i < k; ++i) {  // in the order of the routing list: the same sum on every launch
+    const int r = inv[(size_t)t * k + i];
+    if (r < 0) continue;
+    const float w = wts[(size_t)t * k + i];
+    const uint4 v = *reinterpret_cast<const uint4*>(Y + (size_t)r * H + col);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(u[j]);
+      acc[2 * j] += w * f.x;
+      acc[2 * j + 1] += w * f.y;
+    }
+  }
+}
+
+// out[t] = sum_k w[t, k] * Y[inv[t, k]] (+ shared): the top-k weighted sum over the gathered expert outputs
+static __global__ void moe_combine_gathered_kernel(const __nv_bfloat16* __restrict__ Y, const int* __restrict__ inv,
+                                                   const float* __restrict__ wts, int k, const __nv_bfloat16* __restrict__ shared,
+                                                   __nv_bfloat16* __restrict__ out, int T, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < (H >> 3); i += blockDim.x) {
+    float acc[8];
+    moe_combine8(Y, H, inv, wts, k, t, i * 8, shared, acc);
+    *reinterpret_cast<uint4*>(out + (size_t)t * H + i * 8) = ar_pack8(acc);
+  }
+}
+
+// The same weighted sum fused with the all-reduce over the expert-parallel ranks: every CTA forms one
+// [tg tokens x 128 columns] piece of this rank's partial combine in shared memory and hands it straight to the
+// two-shot exchange over peer memory (ar_exchange), so the combine's result never goes to global memory before it
+// crosses NVLink and there is no separate collective launch.  Grid = (H / 128 column tiles, token groups).
+static __global__ void __launch_bounds__(128)
+moe_combine_exchange_kernel(const ArArgs ar, const __nv_bfloat16* __restrict__ Y, const int* __restrict__ inv,
+                            const float* __restrict__ wts, int k, const __nv_bfloat16* __restrict__ shared,
+                            __nv_bfloat16* __restrict__ out, int T, int H, int tg) {
+  extern __shared__ __align__(16) uint8_t cx_stage[];  // [tg][256] bytes
+  __shared__ int s_call, s_abort;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x;
+  const int n0 = blockIdx.x * 128;
+  const int t0 = blockIdx.y * tg;
+  const int tmax = min(tg, T - t0);
+  const int piece = blockIdx.y * gridDim.x + blockIdx.x;
+  if (tid == 0) {
+    s_call = ar.ctrl[0];
+    s_abort = 0;
+  }
+  const int chunk = tid & 15, trow = tid >> 4;
+  for (int t = trow; t < tmax; t += 8) {
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (n0 + chunk * 8 < H) {
+      float acc[8];
+      moe_combine8(Y, H, inv, wts, k, t0 + t, n0 + chunk * 8, shared, acc);
+      v = ar_pack8(acc);
+    }
+    *reinterpret_cast<uint4*>(cx_stage + t * 256 + chunk * 16) = v;
+  }
+  __syncthreads();
+  ar_exchange(ar, cx_stage, s_call, piece, n0, t0, tmax, H, out, H, &s_abort, tid);
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const int done = atomicAdd(&ar.ctrl[1], 1);
+    if (done == (int)(gridDim.x * gridDim.y) - 1) {
+      ar.ctrl[1] = 0;
+      __threadfence();
+      ar.ctrl[0] = ar.ctrl[0] + 1;
+    }
   }
 }
 

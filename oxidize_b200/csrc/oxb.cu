@@ -363,3 +363,65 @@ OXB_API int oxb_moe_combine(const void* y, const float* scale, int scale_ld, con
   return 0;
 }
 
+
+// ----------------------------------------------------------------------------- mixture of experts: token dispatch / combine
+OXB_API int oxb_moe_permute(const int* ids, int T, int k, int first_local, int n_local, int* offsets, int* perm, int* inv,
+                            cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (n_local < 1 || n_local > MOE_MAX_EXPERTS || k < 1) return (int)cudaErrorInvalidValue;
+  oxb_launch(moe_permute_kernel, dim3(1), dim3(1024), 0, stream, ids, T, k, first_local, n_local, offsets, perm, inv);
+  OXB_CHECK_LAUNCH();
+  return 0;
+}
+
+OXB_API int oxb_moe_gather(const void* X, int H, const int* perm, const int* n_rows_dev, int rows_cap, void* Xg,
+                           cudaStream_t stream) {
+  if (rows_cap <= 0) return 0;
+  if (H % 8 != 0) return (int)cudaErrorInvalidValue;
+  int grid = rows_cap < oxb_sm_count() * 8 ? rows_cap : oxb_sm_count() * 8;
+  oxb_launch(moe_gather_kernel, dim3(grid), dim3(H / 8 < 256 ? ((H / 8 + 31) / 32 * 32) : 256), 0, stream,
+             reinterpret_cast<const __nv_bfloat16*>(X), H, perm, n_rows_dev, reinterpret_cast<__nv_bfloat16*>(Xg));
+  OXB_CHECK_LAUNCH();
+  return 0;
+}
+
+OXB_API int oxb_silu_mul_rows(const void* gu, void* out, const int* n_rows_dev, int rows_cap, int I, cudaStream_t stream) {
+  if (rows_cap <= 0) return 0;
+  if (I % 8 != 0) return (int)cudaErrorInvalidValue;
+  const size_t total = (size_t)rows_cap * (I / 8);
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > oxb_sm_count() * 16) blocks = oxb_sm_count() * 16;
+  oxb_launch(silu_mul_rows_kernel, dim3(blocks), dim3(256), 0, stream, reinterpret_cast<const __nv_bfloat16*>(gu),
+             reinterpret_cast<__nv_bfloat16*>(out), n_rows_dev, I);
+  OXB_CHECK_LAUNCH();
+  return 0;
+}
+
+// out[t] = sum_k wts[t, k] * Y[inv[t, k]] (+ shared).  With world > 1 the partial sums of the expert-parallel ranks are
+// all-reduced inside the same kernel through the symmetric buffers of the fused collectives (arguments as oxb_gemm_ar).
+OXB_API int oxb_moe_combine_gathered(const void* Y, const int* inv, const float* wts, int k, const void* shared, void* out,
+                                     int T, int H, int world, int rank, const uint64_t* data_ptrs, const uint64_t* flag_ptrs,
+                                     int* ctrl, int t_max, int n_max, int max_tiles, unsigned long long timeout_ns,
+                                     cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H % 8 != 0) return (int)cudaErrorInvalidValue;
+  const __nv_bfloat16* y = reinterpret_cast<const __nv_bfloat16*>(Y);
+  const __nv_bfloat16* sh = reinterpret_cast<const __nv_bfloat16*>(shared);
+  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
+  if (world <= 1) {
+    oxb_launch(moe_combine_gathered_kernel, dim3(T), dim3(256), 0, stream, y, inv, wts, k, sh, o, T, H);
+    OXB_CHECK_LAUNCH();
+    return 0;
+  }
+  const int tiles = (H + 127) / 128;
+  const int tg = 16;
+  const int groups = (T + tg - 1) / tg;
+  if (world < g_oxb_ar_ll_min_world || T > t_max || H > n_max || tiles * groups > sm_count() * 8) return (int)cudaErrorInvalidValue;
+  ArArgs ar;
+  int e = fill_ar(ar, world, rank, data_ptrs, flag_ptrs, ctrl, t_max, n_max, max_tiles, timeout_ns, nullptr);
+  if (e) return e;
+  oxb_launch(moe_combine_exchange_kernel, dim3(tiles, groups), dim3(128), (size_t)tg * 256, stream, ar, y, inv, wts, k, sh, o, T,
+             H, tg);
+  OXB_CHECK_LAUNCH();
+  return 0;
+}

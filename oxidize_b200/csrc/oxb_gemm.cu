@@ -50,7 +50,7 @@ static int gemm_bf16_impl(const void* X, const void* W, void* Y, const float* bi
   ArArgs ar;
   memset(&ar, 0, sizeof(ar));
   const QwArgs qw{nullptr, 0, nullptr, 0, 0};
-  const GroupArgs gr{0, 0, 0, 0, nullptr, 0, 0};
+  const GroupArgs gr{0, 0, 0, 0, nullptr, 0, 0, nullptr, 1};
   const RopeArgs ro{nullptr, nullptr, nullptr, 0, 0, 0, 0, 0, 0, 0, nullptr, nullptr};
   switch (p.tn) {
     case 16: return gemm_launch<16>(tmW, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw, gr, 1, ro, nm);
@@ -122,7 +122,7 @@ OXB_API int oxb_gemm_quant(const void* X, const void* Wq, int qtype, size_t row_
       CUtensorMap tmWq;
       const int box = qtype == QT_Q4_K ? MmqStage<QT_Q4_K>::BOX : MmqStage<QT_Q6_K>::BOX;
       if (p.tn <= 64 && oxb_make_tmap_bytes(&tmWq, Wq, (uint64_t)N, row_bytes, GEMM_BM, box) == 0) qw.staged = 1;
-      const GroupArgs g0{0, 0, 0, 0, nullptr, 0, 0};
+      const GroupArgs g0{0, 0, 0, 0, nullptr, 0, 0, nullptr, 1};
       if (qtype == QT_Q4_K)
         return gemm_mmq_q4_k(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw, g0, 1,
                                         qw.staged ? &tmWq : nullptr);
@@ -182,7 +182,7 @@ static int gemm_ar_impl(const void* X, const void* W, void* Y, const void* resid
   __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(Y);
   float* wsf = reinterpret_cast<float*>(ws);
   const QwArgs qw0{nullptr, 0, nullptr, 0, 0};
-  const GroupArgs gr0{0, 0, 0, 0, nullptr, 0, 0};
+  const GroupArgs gr0{0, 0, 0, 0, nullptr, 0, 0, nullptr, 1};
   const RopeArgs ro0{nullptr, nullptr, nullptr, 0, 0, 0, 0, 0, 0, 0, nullptr, nullptr};
   switch (p.tn) {
     case 16: return gemm_launch<16>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw0, gr0, 1, ro0, nm);
@@ -234,7 +234,7 @@ static int gemm_qkv_rope_impl(const void* X, const void* W, int T, int K, const 
               reinterpret_cast<__nv_bfloat16*>(kv_data)};
   __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(q_out);  // only its alignment is looked at
   const QwArgs qw{nullptr, 0, nullptr, 0, 0};
-  const GroupArgs gr{0, 0, 0, 0, nullptr, 0, 0};
+  const GroupArgs gr{0, 0, 0, 0, nullptr, 0, 0, nullptr, 1};
   switch (p.tn) {
     case 16: return gemm_launch<16>(tmW, tmX, y, nullptr, N, T, K, N, p, nullptr, nullptr, EPI_ROPE, ar, stream, qw, gr, 1, ro, nm);
     case 32: return gemm_launch<32>(tmW, tmX, y, nullptr, N, T, K, N, p, nullptr, nullptr, EPI_ROPE, ar, stream, qw, gr, 1, ro, nm);
@@ -345,7 +345,7 @@ OXB_API int oxb_gemm_grouped(const void* X, int x_rows, const void* W, int qtype
   float* wsf = reinterpret_cast<float*>(ws);
   ArArgs ar;
   memset(&ar, 0, sizeof(ar));
-  GroupArgs gr{1, N, x_rows, y_stride, scale, scale_ld, 0};
+  GroupArgs gr{1, N, x_rows, y_stride, scale, scale_ld, 0, nullptr, 1};
   QwArgs qw{reinterpret_cast<const uint8_t*>(W), row_bytes, nullptr, 0, 0};
   if (qtype == QT_BF16) {
     e = oxb_make_tmap_2d(&tmW, W, (uint64_t)groups * N, K, (uint64_t)K * 2, GEMM_BM, GEMM_BK, 2);
@@ -377,3 +377,53 @@ OXB_API int oxb_gemm_grouped(const void* X, int x_rows, const void* W, int qtype
   }
 }
 
+
+// Grouped GEMM over token-gathered groups (mixture-of-experts dispatch): group g multiplies the activation rows
+// [row_offsets[g], row_offsets[g+1]) of X ([rows_cap, K], gathered expert by expert) with its own weights
+// W_g ([N, K] at rows g*N of the stacked matrix) and writes the same rows of Y ([rows_cap, ldY]).  row_offsets is a
+// device array of groups + 1 ints written by the upstream kernel; max_rows bounds the rows of any one group (it sizes
+// the token tile and the grid; CTAs past a group's rows leave at once).
+OXB_API int oxb_gemm_grouped_rows(const void* X, int rows_cap, const void* W, int qtype, size_t row_bytes, void* Y,
+                                  const int* row_offsets, int groups, int max_rows, int N, int K, int ldY,
+                                  cudaStream_t stream) {
+  if (rows_cap <= 0 || max_rows <= 0 || N <= 0 || K <= 0 || groups <= 0) return 0;
+  if (K % 64 != 0 || row_offsets == nullptr) return (int)cudaErrorInvalidValue;
+  GemmPlan p = gemm_plan(max_rows, N, K, 0, sm_count(), 1);
+  if (p.splits > 1 && !p.cluster) p = gemm_plan(max_rows, N, K, 1, sm_count(), 1);
+  CUtensorMap tmW, tmX;
+  int e = oxb_make_tmap_2d(&tmX, X, (uint64_t)rows_cap, K, (uint64_t)K * 2, p.tn, GEMM_BK, 2);
+  if (e) return e;
+  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(Y);
+  ArArgs ar;
+  memset(&ar, 0, sizeof(ar));
+  GroupArgs gr{1, N, 0, 0, nullptr, 0, 0, row_offsets, p.t_tiles};
+  QwArgs qw{reinterpret_cast<const uint8_t*>(W), row_bytes, nullptr, 0, 0};
+  if (qtype == QT_BF16) {
+    e = oxb_make_tmap_2d(&tmW, W, (uint64_t)groups * N, K, (uint64_t)K * 2, GEMM_BM, GEMM_BK, 2);
+    if (e) return e;
+    switch (p.tn) {
+      case 16: return gemm_launch<16>(tmW, tmX, y, nullptr, N, max_rows, K, ldY, p, nullptr, nullptr, 0, ar, stream, qw, gr, groups);
+      case 32: return gemm_launch<32>(tmW, tmX, y, nullptr, N, max_rows, K, ldY, p, nullptr, nullptr, 0, ar, stream, qw, gr, groups);
+      case 64: return gemm_launch<64>(tmW, tmX, y, nullptr, N, max_rows, K, ldY, p, nullptr, nullptr, 0, ar, stream, qw, gr, groups);
+      case 128: return gemm_launch<128>(tmW, tmX, y, nullptr, N, max_rows, K, ldY, p, nullptr, nullptr, 0, ar, stream, qw, gr, groups);
+      default: return gemm_launch<256>(tmW, tmX, y, nullptr, N, max_rows, K, ldY, p, nullptr, nullptr, 0, ar, stream, qw, gr, groups);
+    }
+  }
+  switch (qtype) {
+    case QT_Q4_K:
+    case QT_Q6_K: {
+      CUtensorMap tmWq;
+      const int box = qtype == QT_Q4_K ? MmqStage<QT_Q4_K>::BOX : MmqStage<QT_Q6_K>::BOX;
+      if (p.tn <= 64 && oxb_make_tmap_bytes(&tmWq, W, (uint64_t)groups * N, row_bytes, GEMM_BM, box) == 0) qw.staged = 1;
+      if (qtype == QT_Q4_K)
+        return gemm_mmq_q4_k(tmX, y, nullptr, N, max_rows, K, ldY, p, nullptr, nullptr, 0, ar, stream, qw, gr, groups,
+                             qw.staged ? &tmWq : nullptr);
+      return gemm_mmq_q6_k(tmX, y, nullptr, N, max_rows, K, ldY, p, nullptr, nullptr, 0, ar, stream, qw, gr, groups,
+                           qw.staged ? &tmWq : nullptr);
+    }
+    case QT_Q8_0: return gemm_mmq_q8_0(tmX, y, nullptr, N, max_rows, K, ldY, p, nullptr, nullptr, 0, ar, stream, qw, gr, groups);
+    case QT_Q4_0: return gemm_mmq_q4_0(tmX, y, nullptr, N, max_rows, K, ldY, p, nullptr, nullptr, 0, ar, stream, qw, gr, groups);
+    case QT_NVFP4: return gemm_mmq_nvfp4(tmX, y, nullptr, N, max_rows, K, ldY, p, nullptr, nullptr, 0, ar, stream, qw, gr, groups);
+    default: return (int)cudaErrorInvalidValue;
+  }
+}

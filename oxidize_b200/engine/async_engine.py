@@ -202,6 +202,10 @@ class AsyncEngine:
             self._forget(rid)
 
     def _loop(self) -> None:
+        if self.llm.device.type == "cuda":
+            import torch
+
+            torch.cuda.set_device(self.llm.device)  # this thread launches on the replica's own GPU
         while not self._stop.is_set():
             self._drain_inbox(block=not self.llm.has_unfinished)
             if self.control is not None and (self._step_admits or self._step_aborts or self.llm.has_unfinished):
@@ -219,3 +223,126 @@ class AsyncEngine:
             self.watchdog.end_step()
             for ro in outs:
                 self._route(ro)
+
+
+
+class ReplicaRouter:
+    """Data parallelism for serving: several complete engine replicas (each an :class:`AsyncEngine` with its own model
+    copy, KV pool and GPU or tensor-parallel group) behind one front.  A request goes to the healthy replica with the
+    fewest requests in flight (round robin among equals) and stays there; the router exposes the surface the HTTP layer
+    uses of a single engine.  The reference scales out the same way, one engine per node behind its mesh front
+    (``oxidize-core/src/mesh``); here the replicas share a process and a box."""
+
+    def __init__(self, engines: List[AsyncEngine]):
+        if not engines:
+            raise ValueError("need at least one replica")
+        self.engines = list(engines)
+        self._owner: Dict[str, int] = {}
+        self._inflight = [0] * len(self.engines)
+        self._rr = 0
+        self._lock = threading.Lock()
+        self._ids = 0
+
+    # the HTTP layer reads tokenizer, chat template and pool gauges from `.llm`
+    @property
+    def llm(self) -> LLM:
+        return self.engines[0].llm
+
+    def next_id(self, prefix: str = "req") -> str:
+        with self._lock:
+            self._ids += 1
+            return f"{prefix}-{self._ids}"
+
+    def _pick(self) -> int:
+        with self._lock:
+            n = len(self.engines)
+            order = [(self._rr + i) % n for i in range(n)]
+            live = [i for i in order if self.engines[i].healthy] or order
+            best = min(live, key=lambda i: self._inflight[i])
+            self._rr = (best + 1) % n
+            self._inflight[best] += 1
+            return best
+
+    def submit(self, prompt, params: SamplingParams, sink: Callable[[StreamEvent], None],
+               request_id: Optional[str] = None) -> str:
+        rid = request_id or self.next_id()
+        i = self._pick()
+        with self._lock:
+            self._owner[rid] = i
+
+        def routed(ev: StreamEvent) -> None:
+            if ev.finished:
+                with self._lock:
+                    if self._owner.pop(rid, None) is not None:
+                        self._inflight[i] = max(0, self._inflight[i] - 1)
+            sink(ev)
+
+        return self.engines[i].submit(prompt, params, routed, rid)
+
+    def cancel(self, request_id: str) -> None:
+        with self._lock:
+            i = self._owner.pop(request_id, None)
+            if i is not None:
+                self._inflight[i] = max(0, self._inflight[i] - 1)
+        if i is not None:
+            self.engines[i].cancel(request_id)
+
+    async def stream(self, prompt, params: SamplingParams, request_id: Optional[str] = None):
+        loop = asyncio.get_running_loop()
+        q: "asyncio.Queue[StreamEvent]" = asyncio.Queue()
+        rid = self.submit(prompt, params, lambda ev: loop.call_soon_threadsafe(q.put_nowait, ev), request_id)
+        try:
+            while True:
+                ev = await q.get()
+                yield ev
+                if ev.finished:
+                    return
+        finally:
+            self.cancel(rid)
+
+    def generate_blocking(self, prompt, params: SamplingParams, timeout: Optional[float] = None) -> List[StreamEvent]:
+        done = threading.Event()
+        evs: List[StreamEvent] = []
+
+        def sink(ev: StreamEvent):
+            evs.append(ev)
+            if ev.finished:
+                done.set()
+
+        self.submit(prompt, params, sink)
+        if not done.wait(timeout):
+            raise TimeoutError("generation timed out")
+        return evs
+
+    @property
+    def healthy(self) -> bool:
+        return any(e.healthy for e in self.engines)
+
+    @property
+    def queue_depth(self) -> int:
+        return sum(e.queue_depth for e in self.engines)
+
+    @property
+    def tokens_generated(self) -> int:
+        return sum(e.tokens_generated for e in self.engines)
+
+    @property
+    def prompt_tokens(self) -> int:
+        return sum(e.prompt_tokens for e in self.engines)
+
+    @property
+    def failures(self) -> int:
+        return sum(e.failures for e in self.engines)
+
+    @property
+    def watchdog(self):
+        return self.engines[0].watchdog
+
+    def load(self) -> List[int]:
+        """Requests in flight per replica."""
+        with self._lock:
+            return list(self._inflight)
+
+    def shutdown(self, timeout: float = 5.0) -> None:
+        for e in self.engines:
+            e.shutdown(timeout)

@@ -260,6 +260,20 @@ class LLM:
         self.last_step = (out, res)
         return [self._output(ss.seq) for ss in out.scheduled if ss.sample or ss.seq.is_finished]
 
+    def close(self) -> None:
+        """Release what must go before the process group does: the step in flight, then the captured CUDA graphs.
+        A graph keeps the kernels, buffers and (on the NCCL baseline path) the communicator it captured alive;
+        tearing the communicator down while a graph still refers to it blocks, so the graphs are dropped first and
+        the device is idle when the caller destroys the process group."""
+        try:
+            self.drain()
+        except Exception:
+            self._inflight = None
+        self.runner.graphs.clear()
+        self.runner.graph_out.clear()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+
     def drain(self) -> List[RequestOutput]:
         """Finish the step that is in flight, if any, without launching another one ahead of it."""
         if getattr(self, "_inflight", None) is None:

@@ -236,8 +236,9 @@ class Transformer:
         if x.is_cuda:
             from ..ops import cuda_moe
 
-            out = cuda_moe.moe_layer(x, logits, cfg, lw.router_bias, lw.experts, sh)
-            return self.comm.all_reduce(out) if ep_sharded else out
+            out, reduced = cuda_moe.moe_layer(x, logits, cfg, lw.router_bias, lw.experts, sh,
+                                              self.comm if ep_sharded else None)
+            return self.comm.all_reduce(out) if (ep_sharded and not reduced) else out
         ids, wts = ops.moe_route(logits, cfg, lw.router_bias)
         out = moe_experts_forward(x, ids, wts, lw.experts)
         if sh is not None:

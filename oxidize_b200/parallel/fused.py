@@ -82,6 +82,17 @@ class FusedComm(TorchComm):
         torch.cuda.synchronize(self.device)
         self.barrier()
 
+    def close(self) -> None:
+        """Orderly end of the peer mappings: every rank stops launching, meets at a barrier (no kernel of a peer may
+        still be writing into this rank's buffers) and only then drops its symmetric-memory handles and buffers."""
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        self.barrier()
+        self._handles = []
+        self.data = self.flags = None
+        if hasattr(self, "amax"):
+            self.amax = None
+
     def set_peer_pointers(self, data_ptrs, flag_ptrs, world: Optional[int] = None, rank: Optional[int] = None) -> None:
         """Install the peer pointer tables (also used by tests that emulate an absent peer)."""
         if world is not None:

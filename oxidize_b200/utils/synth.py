@@ -235,7 +235,7 @@ def _rand_matrix(out_f: int, in_f: int, qtype: str, device, gen: torch.Generator
 
 
 def synth_weights(cfg: ModelConfig, device, quant: str = "BF16", seed: int = 0, tp_rank: int = 0, tp_size: int = 1,
-                  ep_rank: int = 0, ep_size: int = 1, layer_range=None) -> ModelWeights:
+                  ep_rank: int = 0, ep_size: int = 1, layer_range=None, expert_quant: Optional[str] = None) -> ModelWeights:
     """Build this rank's shard of a random-init model directly on ``device``.
 
     Every rank draws its own shard from a rank-specific stream; replicated tensors (norms,
@@ -268,8 +268,8 @@ def synth_weights(cfg: ModelConfig, device, quant: str = "BF16", seed: int = 0, 
             lw.router = _rand_matrix(cfg.n_experts, h, "F32" if device.type == "cpu" else "BF16", device, shared)
             e0, e1 = shard_range(cfg.n_experts, ep_rank, ep_size)
             ef = cfg.expert_ffn_size
-            tg = pick_type(quant, "ffn_gate", i, L, h)
-            td = pick_type(quant, "ffn_gate", i, L, ef)
+            tg = pick_type(expert_quant or quant, "ffn_gate", i, L, h)
+            td = pick_type(expert_quant or quant, "ffn_gate", i, L, ef)
             lw.experts = ExpertWeights([_rand_matrix(2 * ef, h, tg, device, own) for _ in range(e0, e1)],
                                        [_rand_matrix(h, ef, td, device, own) for _ in range(e0, e1)], e0)
         else:

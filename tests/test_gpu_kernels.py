@@ -689,3 +689,64 @@ def test_sampled_speculation_on_gpu(C, tmp_path):
     assert all(len(o.token_ids) == 16 and all(0 <= t < 512 for t in o.token_ids) for o in outs)
     assert spec.stats.proposed > 0 and spec.stats.acceptance_rate > 0.8, spec.stats
     _check_status(C)
+
+
+@pytest.mark.parametrize("T,E,k,first,n_local,H,F,qtype", [
+    (64, 8, 2, 0, 8, 256, 128, "BF16"), (1, 8, 2, 0, 8, 256, 128, "BF16"), (600, 16, 4, 4, 8, 512, 192, "BF16"),
+    (300, 128, 8, 32, 16, 256, 64, "BF16"), (37, 8, 2, 2, 3, 256, 256, "Q4_K"), (700, 8, 2, 0, 8, 256, 128, "Q8_0")])
+def test_moe_token_dispatch_grouped_gemm_combine(C, T, E, k, first, n_local, H, F, qtype):
+    """Routing lists -> gathered rows -> grouped GEMMs over each expert's own rows -> top-k weighted combine, against
+    the same sum written with torch on the dense weights; experts outside [first, first + n_local) live elsewhere."""
+    from oxidize_b200.models.weights import ExpertWeights, qtensor_from_dense
+    from oxidize_b200.ops import cuda_moe
+
+    torch.manual_seed(T + E)
+    dev = "cuda"
+    x = torch.randn(T, H, device=dev).to(torch.bfloat16)
+    # skewed routing: some experts get most tokens, some none
+    prob = torch.softmax(torch.randn(E, device=dev) * 2.0, 0)
+    ids = torch.stack([torch.multinomial(prob, k, replacement=False) for _ in range(T)]).to(torch.int32)
+    wts = torch.rand(T, k, device=dev) + 0.1
+    gu = [qtensor_from_dense(torch.randn(2 * F, H) * 0.05, qtype, device=dev) for _ in range(n_local)]
+    dn = [qtensor_from_dense(torch.randn(H, F) * 0.05, qtype, device=dev) for _ in range(n_local)]
+    ex = ExpertWeights(gu, dn, first)
+    assert ex.stack()
+    offsets, perm, inv = cuda_moe.moe_dispatch(ids, first, n_local)
+    torch.cuda.synchronize()
+    off = offsets.cpu().tolist()
+    idc = ids.cpu()
+    counts = [int(((idc - first) == e).sum()) for e in range(n_local)]
+    assert [off[e + 1] - off[e] for e in range(n_local)] == counts
+    pm, iv = perm.cpu(), inv.cpu()
+    for t in range(0, T, max(1, T // 17)):
+        for j in range(k):
+            e = int(idc[t, j]) - first
+            if 0 <= e < n_local:
+                r = int(iv[t, j])
+                assert off[e] <= r < off[e + 1] and int(pm[r]) == t
+            else:
+                assert int(iv[t, j]) == -1
+    L = C.lib()
+    n_rows = offsets[n_local:]
+    xg = torch.zeros(T * k, H, dtype=torch.bfloat16, device=dev)
+    C._check(L.oxb_moe_gather(x.data_ptr(), H, perm.data_ptr(), n_rows.data_ptr(), T * k, xg.data_ptr(), C._stream()), "gather")
+    h = cuda_moe.gemm_grouped_rows(xg, ex.gate_up_stack, offsets, n_local, T)
+    act = torch.zeros(T * k, F, dtype=torch.bfloat16, device=dev)
+    C._check(L.oxb_silu_mul_rows(h.data_ptr(), act.data_ptr(), n_rows.data_ptr(), T * k, F, C._stream()), "silu")
+    y = cuda_moe.gemm_grouped_rows(act, ex.down_stack, offsets, n_local, T)
+    shared = torch.randn(T, H, device=dev).to(torch.bfloat16)
+    out, reduced = cuda_moe.moe_combine_gathered(y, inv, wts, shared, T)
+    torch.cuda.synchronize()
+    assert not reduced
+    want = shared.float().clone()
+    for e in range(n_local):
+        sel = (ids == first + e)
+        rows = sel.any(1).nonzero(as_tuple=True)[0]
+        if rows.numel() == 0:
+            continue
+        w = (wts * sel).sum(1)[rows]
+        a = x[rows].float() @ gu[e].to("cpu").dense_cache().t().to(dev)
+        a = (torch.nn.functional.silu(a[:, :F]) * a[:, F:]).to(torch.bfloat16).float()
+        want[rows] += w[:, None] * (a @ dn[e].to("cpu").dense_cache().t().to(dev))
+    assert _rel_err(out, want) < (2e-2 if qtype != "BF16" else 1.2e-2)
+    _check_status(C)

@@ -158,3 +158,62 @@ def test_guided_choice_and_penalty_fields_with_model(engine):
     r = c.post("/v1/completions", json={"model": "tiny", "prompt": "hello", "max_tokens": 6, "temperature": 0.5, "seed": 1,
                                         "frequency_penalty": 0.5, "presence_penalty": 0.5})
     assert r.status_code == 200 and r.json()["usage"]["completion_tokens"] >= 1
+
+
+def test_data_parallel_replicas_behind_one_front(tmp_path):
+    """Two engine replicas behind the router: requests spread over both, results equal a single engine's (greedy),
+    an unhealthy replica is avoided, and the HTTP layer serves through the router unchanged."""
+    import threading
+
+    from oxidize_b200.engine.async_engine import ReplicaRouter
+    from oxidize_b200.engine.sampler import SamplingParams
+
+    cfg = preset("tiny-llama", n_layers=2, vocab_size=300)
+    p = str(tmp_path / "tiny_dp.gguf")
+    synth_gguf(p, cfg, "F16", seed=0)
+    ec = EngineConfig(max_model_len=256, max_num_seqs=4, num_kv_blocks=96, prefill_chunk_size=32, max_num_batched_tokens=64)
+    engines = [AsyncEngine(LLM.from_gguf(p, ec, device="cpu"), name=f"rep{i}") for i in range(2)]
+    router = ReplicaRouter(engines)
+    try:
+        sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+        prompts = [[5, 9, 200, 31, 7], list(range(3, 40)), [100, 101], [7, 7, 7, 7], [250, 3, 9]]
+        served = []
+        lock = threading.Lock()
+        results = {}
+
+        def run(i):
+            evs = router.generate_blocking(prompts[i], sp, timeout=60)
+            with lock:
+                results[i] = [t for ev in evs for t in ev.new_token_ids]
+
+        orig = [e.submit for e in engines]
+        for k, e in enumerate(engines):
+            e.submit = (lambda k, f: (lambda *a, **kw: (served.append(k), f(*a, **kw))[1]))(k, orig[k])
+        ts = [threading.Thread(target=run, args=(i,)) for i in range(len(prompts))]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join(90)
+        assert sorted(results) == list(range(len(prompts)))
+        assert set(served) == {0, 1}, "both replicas must take requests"
+        single = LLM.from_gguf(p, ec, device="cpu").generate(prompts, sp)
+        assert [results[i] for i in range(len(prompts))] == [o.token_ids for o in single]
+        assert router.load() == [0, 0] and router.healthy
+        # a replica whose watchdog tripped gets no new requests
+        class _Down:
+            healthy = False
+
+            def close(self):
+                pass
+
+        real, engines[0].watchdog = engines[0].watchdog, _Down()
+        served.clear()
+        router.generate_blocking(prompts[0], sp, timeout=60)
+        assert served == [1]
+        engines[0].watchdog = real
+        c = TestClient(create_app(ServerState(router, "tiny", GenerationDefaults(max_tokens=6, temperature=0.0), api_keys=[])))
+        r = c.post("/v1/completions", json={"model": "tiny", "prompt": "hello", "max_tokens": 5})
+        assert r.status_code == 200 and r.json()["usage"]["completion_tokens"] >= 1
+        assert c.get("/readyz").status_code == 200
+    finally:
+        router.shutdown()
