@@ -213,6 +213,43 @@ def small_case(spec: str, launches: int):
         scale = torch.empty(E, T, device="cuda")
         for i in range(launches):
             cuda_moe.moe_route(logits, cfg, None, scale, 0, E)
+    elif kind == "gemmnorm":  # gemmnorm:TxNxK  folded RMSNorm: producer (accumulate-into + sums of squares), then consumer
+        T, N, K = (int(v) for v in rest.split("x"))
+        copies = max(2, int(300e6 // (N * K * 2)) + 1)
+        ws = [(torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(copies)]
+        wc = [(torch.randn(K, N, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(copies)]
+        x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
+        r = torch.randn(T, N, device="cuda").to(torch.bfloat16)
+        acc = torch.zeros(2, T * C.SUMSQ_STRIDE, dtype=torch.int64, device="cuda")
+        for i in range(launches):
+            C.gemm_bf16(x, ws[i % copies], out=r, add_into=True, sumsq_out=acc[0])
+            C.gemm_bf16(r, wc[i % copies], sumsq_in=acc[0], eps=1e-5, clear=acc[1])
+            acc[0].zero_()
+    elif kind == "moelayer":  # moelayer:PRESETxLOCALxT  routed-expert block: route, dispatch, grouped GEMMs, combine
+        from oxidize_b200.models.config import preset
+        from oxidize_b200.models.weights import ExpertWeights, QTensor
+        from oxidize_b200.ops import cuda_moe
+
+        name, nloc, T = rest.split("x")
+        nloc, T = int(nloc), int(T)
+        cfg = preset(name)
+        H, F = cfg.hidden_size, cfg.expert_ffn_size
+        gu = [QTensor("BF16", (torch.randn(2 * F, H, device="cuda") * 0.02).to(torch.bfloat16), (2 * F, H)) for _ in range(nloc)]
+        dn = [QTensor("BF16", (torch.randn(H, F, device="cuda") * 0.02).to(torch.bfloat16), (H, F)) for _ in range(nloc)]
+        ex = ExpertWeights(gu, dn, 0)
+        x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+        logits = torch.randn(T, cfg.n_experts, device="cuda")
+        for i in range(launches):
+            cuda_moe.moe_layer(x, logits, cfg, None, ex, None, None, True)
+    elif kind == "specverify":  # specverify:SxKxV  speculative verification, sampled rows
+        S, K, V = (int(v) for v in rest.split("x"))
+        i32, f32 = dict(dtype=torch.int32, device="cuda"), dict(dtype=torch.float32, device="cuda")
+        tl = torch.randn(S * (K + 1), V, **f32)
+        dl = tl.view(S, K + 1, V)[:, :K].reshape(S * K, V) + 0.3 * torch.randn(S * K, V, **f32)
+        dtok = dl.argmax(-1).view(S, K).to(torch.int32)
+        for i in range(launches):
+            C.spec_verify(tl, dl, dtok, torch.arange(S, **i32) * (K + 1), torch.full((S,), K, **i32), torch.full((S,), 0.8, **f32),
+                          torch.rand(S, 2 * K + 1, **f32), K)
     else:
         raise SystemExit(f"unknown case {spec}")
     torch.cuda.synchronize()

@@ -247,9 +247,8 @@ paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
     return id;
   };
 
-  // (Requesting this warp's stable KV pages into the L2 here, before the dependency resolves, was
-  // measured: it only pays when the upstream kernel leaves HBM idle; behind the qkv GEMM it costs
-  // 5-30 %, so the kernel does not do it.)
+  // (The KV pages are not requested into the L2 ahead of the dependency: behind an HBM-bound kernel such requests
+  // compete with the stream that is still running.)
   pdl_wait();
   ATT_STAMP(1);
   // Q fragments (A operand), straight from global memory

@@ -21,7 +21,7 @@ namespace oxb {
 constexpr int GEMM_BM = 128;  // weight rows per tile (UMMA M)
 constexpr int GEMM_BK = 64;   // bf16 per k-block = one 128-byte swizzle row
 constexpr int GEMM_THREADS = 192;       // TMA warp, MMA warp, 4 epilogue warps
-constexpr int GEMM_THREADS_MMQ = 320;   // + 4 dequant producer warps for packed weights
+constexpr int GEMM_THREADS_MMQ = 448;   // + 8 dequant producer warps for packed weights (two groups of four)
 
 // k-blocks (16 KB of weights each) a CTA requests into the L2 before the grid dependency resolves
 // (GroupArgs::l2_prefetch_kb, set per launch).  Behind an HBM-bound kernel this LOSES 10-20% (the
@@ -481,19 +481,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       cluster_sync_all();
     }
   } else if (warp >= 6) {
-    // ---------------- dequant producers (MMQ only): thread r stages weight row n0 + r
+    // ---------------- dequant producers (MMQ only): two groups of 128 threads; in each, thread r stages weight row
+    // n0 + r.  The groups take alternate k-blocks (each stage's barrier expects the four warps of ONE group), so
+    // twice as many warps share the decode arithmetic of a tile and the ring is fed by two decoders at once.
     if constexpr (MMQ) {
-      const int r = threadIdx.x - 192;
+      const int grp = (threadIdx.x - 192) >> 7;
+      const int r = (threadIdx.x - 192) & 127;
       const int n = n0 + r;
       const uint8_t* rowp = qw.w + ((size_t)zg * gr.w_rows + (size_t)(n < N ? n : 0)) * qw.row_bytes;
       // Each thread walks its own packed row.  Two k-blocks are decoded per iteration, and both are
       // decoded into registers BEFORE the thread waits for their ring slots: the global loads of
       // the two blocks overlap each other and the tensor core's work on the slots still in use
-      // (waiting first and loading afterwards left every k-block with a cold, dependent load:
-      // 95 us instead of the 24 us the same matrix takes in bf16).
-      // straight-line on purpose: no branch between the two decodes, so that the compiler can issue the
+      // (waiting first and loading afterwards leaves every k-block with a cold, dependent load).
+      // Straight-line on purpose: no branch between the two decodes, so that the compiler can issue the
       // loads of both k-blocks before the arithmetic of the first (addresses are clamped to valid
-      // blocks; out-of-range results are zeroed afterwards)
+      // blocks; out-of-range results are zeroed afterwards).
       const int kb_last = (K / GEMM_BK) - 1;
       auto decode = [&](int kb, uint32_t* v) {
         const int kbc = kb < kb_last ? kb : kb_last;
@@ -530,7 +532,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           tma_load_2d(packed_buf + (j & 1) * PBYTES, &tmW, &packed_full[j & 1], ((sb_begin + j) * SB) & ~15, w_row0);
         };
         const int nsb = sb_end - sb_begin;
-        if (r == 0) {
+        if (r == 0 && grp == 0) {
           tma_prefetch_desc(&tmW);
           for (int j = 0; j < 2 && j < nsb; ++j) issue(j);
         }
@@ -543,26 +545,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             const uint8_t* srow = packed_buf + (j & 1) * PBYTES + r * BOX + (((sb_begin + j) * SB) & 15);
             const int kb0 = max(kb_begin, (sb_begin + j) * 4), kb1 = min(kb_end, (sb_begin + j) * 4 + 4);
             for (int kb = kb0; kb < kb1 && alive; ++kb) {
+              if (((kb - kb_begin) & 1) != grp) continue;  // the other group's k-block
               uint32_t v[32];
               dequant64<QT>(srow, (kb & 3) * GEMM_BK, qw, 0, v);  // rows past N were zero-filled by the TMA
               alive = publish(kb - kb_begin, v);
             }
           }
-          // every producer is done with this buffer before it is refilled (all 128 take part, alive or not)
-          asm volatile("bar.sync 2, 128;" ::: "memory");
-          if (r == 0 && alive && j + 2 < nsb) issue(j + 2);
+          // every producer is done with this buffer before it is refilled (all 256 take part, alive or not)
+          asm volatile("bar.sync 2, 256;" ::: "memory");
+          if (r == 0 && grp == 0 && alive && j + 2 < nsb) issue(j + 2);
         }
       }
       if (!staged_done) {
-        for (int i = 0; i < nkb; i += 2) {
+        // group g takes k-blocks g, g + 2, g + 4, ...; two of them are decoded per iteration
+        for (int i = grp; i < nkb; i += 4) {
           uint32_t v0[32], v1[32];
-          const bool two = i + 1 < nkb;
+          const bool two = i + 2 < nkb;
           decode(kb_begin + i, v0);
-          decode(kb_begin + i + 1, v1);
+          decode(kb_begin + i + 2, v1);
           mask(kb_begin + i, v0);
-          mask(kb_begin + i + 1, v1);
+          mask(kb_begin + i + 2, v1);
           if (!publish(i, v0)) break;
-          if (two && !publish(i + 1, v1)) break;
+          if (two && !publish(i + 2, v1)) break;
         }
       }
     }

@@ -62,7 +62,7 @@ __device__ __forceinline__ void scale_min_words(int j, uint32_t s0, uint32_t s1,
 }
 
 // Shared-memory view of the quantized activations of one CTA: for token t
-//   q  [t*K + i]        int8 codes
+//   q  [t*K + ...]      int8 codes, inside each 256-value super-block in the order of gv_act_pos
 //   d  [t*K/32 + i/32]  fp32 scale of each 32-value block
 //   s16[t*K/16 + i/16]  sum of the codes of each 16-value half block
 struct GvAct {
@@ -72,41 +72,111 @@ struct GvAct {
   int K;
 };
 
+// Position of activation value j (inside its 256-value super-block) in the shared-memory copy.  The k-quant layouts
+// interleave their nibbles (a run of bytes holds values j.. in the low nibbles and j+32.. or j+64.. in the high ones), so
+// with the activations in natural order the eight lanes that share a super-block would read 16-byte pieces that are
+// 64 or 128 bytes apart and collide on the shared-memory banks.  The copy is therefore stored in the order in which
+// the weight bytes ask for it: all "low nibble" partners of a super-block first (128 bytes, contiguous across the
+// lanes), then all "high nibble" partners.
+template <int QT>
+__device__ __forceinline__ int gv_act_pos(int j) {
+  if constexpr (QT == QT_Q4_K) {
+    const int c = j >> 6, r = j & 63;           // group of 64 values: 32 low-nibble, then 32 high-nibble ones
+    return r < 32 ? 32 * c + r : 128 + 32 * c + (r - 32);
+  } else if constexpr (QT == QT_Q6_K) {
+    const int h = j >> 7, r = j & 127;          // half of 128 values: 64 low-nibble, then 64 high-nibble ones
+    return r < 64 ? 64 * h + r : 128 + 64 * h + (r - 64);
+  } else {
+    return j;
+  }
+}
+
 // Values of one row covered by one warp iteration, per format.
 template <int QT>
 struct GvSpan {
   static constexpr int VALUES = (QT == QT_Q4_K || QT == QT_Q6_K) ? 1024 : (QT == QT_Q8_0 ? 512 : 1024);
 };
 
-// One lane's share of one warp iteration of one row: returns the contribution to each token's sum.
-template <int QT, int TB>
-__device__ __forceinline__ void gv_lane_dot(const uint8_t* rowp, int it, int lane, int K, const GvAct& act, float (&acc)[TB]) {
+// The packed words one lane needs for its share of one warp iteration of one row.  Loading them (gv_load) is kept
+// apart from using them (gv_dot) so that the loads of several iterations and rows are in flight together: at decode
+// sizes a warp sees only a handful of iterations per row, and a load-use-load-use chain would leave the kernel
+// waiting on one memory latency after the other.
+template <int QT>
+struct GvFrag {
+  uint32_t a[4];   // Q4_K: header words (d|dmin, 12 scale bytes)   Q6_K: ql   Q8_0 / Q4_0: codes
+  uint32_t b[4];   // Q4_K: 16 bytes of nibbles                     Q6_K: qh
+  float d, dlo, dhi;  // Q6_K: d * sub-block scales; Q8_0 / Q4_0: block scale in d
+  bool live;
+};
+
+template <int QT>
+__device__ __forceinline__ void gv_load(const uint8_t* rowp, int it, int lane, int K, GvFrag<QT>& f) {
+  f.live = false;
   if constexpr (QT == QT_Q4_K) {
     const int sb = it * 4 + (lane >> 3);
     if (sb * 256 >= K) return;
-    const int l8 = lane & 7, c = l8 >> 1, hh = l8 & 1;
+    const int l8 = lane & 7;
     const uint8_t* b = rowp + (size_t)sb * 144;
     const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(b));
-    const uint4 qv = __ldg(reinterpret_cast<const uint4*>(b + 16 + 32 * c + 16 * hh));
-    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFF)));
-    const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+    const uint4 qv = __ldg(reinterpret_cast<const uint4*>(b + 16 + 16 * l8));
+    f.a[0] = hdr.x; f.a[1] = hdr.y; f.a[2] = hdr.z; f.a[3] = hdr.w;
+    f.b[0] = qv.x; f.b[1] = qv.y; f.b[2] = qv.z; f.b[3] = qv.w;
+    f.live = true;
+  } else if constexpr (QT == QT_Q6_K) {
+    const int sb = it * 4 + (lane >> 3);
+    if (sb * 256 >= K) return;
+    const int l8 = lane & 7, h = l8 >> 2, i = l8 & 3, q0 = i >> 1, lr = (i & 1) * 16;
+    const uint8_t* b = rowp + (size_t)sb * 210;
+    ld16_align2(b + h * 64 + 16 * i, f.a);
+    ld16_align2(b + 128 + h * 32 + lr, f.b);
+    const int8_t* scp = reinterpret_cast<const int8_t*>(b + 192) + h * 8 + (i & 1) + 2 * q0;
+    const float d = ld_half_raw(b + 208);
+    f.dlo = d * (float)__ldg(scp);
+    f.dhi = d * (float)__ldg(scp + 4);
+    f.live = true;
+  } else if constexpr (QT == QT_Q8_0) {
+    const int blk = it * 16 + (lane >> 1), hh = lane & 1;
+    if (blk * 32 >= K) return;
+    const uint8_t* b = rowp + (size_t)blk * 34;
+    ld16_align2(b + 2 + 16 * hh, f.a);
+    f.d = ld_half_raw(b);
+    f.live = true;
+  } else if constexpr (QT == QT_Q4_0) {
+    const int blk = it * 32 + lane;
+    if (blk * 32 >= K) return;
+    const uint8_t* b = rowp + (size_t)blk * 18;
+    ld16_align2(b + 2, f.a);
+    f.d = ld_half_raw(b);
+    f.live = true;
+  }
+}
+
+// One lane's share of one warp iteration of one row: adds the contribution to each token's sum.
+template <int QT, int TB>
+__device__ __forceinline__ void gv_dot(const GvFrag<QT>& f, int it, int lane, const GvAct& act, float (&acc)[TB]) {
+  if (!f.live) return;
+  if constexpr (QT == QT_Q4_K) {
+    const int sb = it * 4 + (lane >> 3);
+    const int l8 = lane & 7, c = l8 >> 1, hh = l8 & 1;
+    const float d = __half2float(__ushort_as_half((unsigned short)(f.a[0] & 0xFFFF)));
+    const float dmin = __half2float(__ushort_as_half((unsigned short)(f.a[0] >> 16)));
     int sc0, m0, sc1, m1;
-    scale_min_words(2 * c, hdr.y, hdr.z, hdr.w, sc0, m0);
-    scale_min_words(2 * c + 1, hdr.y, hdr.z, hdr.w, sc1, m1);
+    scale_min_words(2 * c, f.a[1], f.a[2], f.a[3], sc0, m0);
+    scale_min_words(2 * c + 1, f.a[1], f.a[2], f.a[3], sc1, m1);
     const float ds0 = d * (float)sc0, dm0 = dmin * (float)m0, ds1 = d * (float)sc1, dm1 = dmin * (float)m1;
-    const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
     const int off = sb * 256 + 64 * c + 16 * hh;  // first value of the low-nibble run; the high-nibble run is 32 further
+    const int xoff = sb * 256 + 16 * l8;          // where those runs sit in the permuted copy (gv_act_pos); high: + 128
 #pragma unroll
     for (int t = 0; t < TB; ++t) {
-      const int8_t* xq = act.q + (size_t)t * act.K + off;
+      const int8_t* xq = act.q + (size_t)t * act.K + xoff;
       const uint4 xl = *reinterpret_cast<const uint4*>(xq);
-      const uint4 xh = *reinterpret_cast<const uint4*>(xq + 32);
+      const uint4 xh = *reinterpret_cast<const uint4*>(xq + 128);
       const uint32_t xlw[4] = {xl.x, xl.y, xl.z, xl.w}, xhw[4] = {xh.x, xh.y, xh.z, xh.w};
       int slo = 0, shi = 0;
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
-        slo = dp4a_ss(qw[w] & 0x0F0F0F0Fu, xlw[w], slo);
-        shi = dp4a_ss((qw[w] >> 4) & 0x0F0F0F0Fu, xhw[w], shi);
+        slo = dp4a_ss(f.b[w] & 0x0F0F0F0Fu, xlw[w], slo);
+        shi = dp4a_ss((f.b[w] >> 4) & 0x0F0F0F0Fu, xhw[w], shi);
       }
       const float* dx = act.d + (size_t)t * (act.K >> 5) + (off >> 5);
       const short* s16 = act.s16 + (size_t)t * (act.K >> 4) + (off >> 4);
@@ -114,27 +184,20 @@ __device__ __forceinline__ void gv_lane_dot(const uint8_t* rowp, int it, int lan
     }
   } else if constexpr (QT == QT_Q6_K) {
     const int sb = it * 4 + (lane >> 3);
-    if (sb * 256 >= K) return;
     const int l8 = lane & 7, h = l8 >> 2, i = l8 & 3, q0 = i >> 1, lr = (i & 1) * 16;
-    const uint8_t* b = rowp + (size_t)sb * 210;
-    uint32_t ql[4], qh[4];
-    ld16_align2(b + h * 64 + 16 * i, ql);
-    ld16_align2(b + 128 + h * 32 + lr, qh);
-    const int8_t* scp = reinterpret_cast<const int8_t*>(b + 192) + h * 8 + (i & 1) + 2 * q0;
-    const float d = ld_half_raw(b + 208);
-    const float dlo = d * (float)__ldg(scp), dhi = d * (float)__ldg(scp + 4);
     uint32_t vlo[4], vhi[4];
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-      vlo[w] = (ql[w] & 0x0F0F0F0Fu) | (((qh[w] >> (2 * q0)) & 0x03030303u) << 4);
-      vhi[w] = ((ql[w] >> 4) & 0x0F0F0F0Fu) | (((qh[w] >> (2 * q0 + 4)) & 0x03030303u) << 4);
+      vlo[w] = (f.a[w] & 0x0F0F0F0Fu) | (((f.b[w] >> (2 * q0)) & 0x03030303u) << 4);
+      vhi[w] = ((f.a[w] >> 4) & 0x0F0F0F0Fu) | (((f.b[w] >> (2 * q0 + 4)) & 0x03030303u) << 4);
     }
     const int off = sb * 256 + h * 128 + q0 * 32 + lr;  // low-nibble run; the high-nibble run is 64 further
+    const int xoff = sb * 256 + 16 * l8;                // in the permuted copy (gv_act_pos); high: + 128
 #pragma unroll
     for (int t = 0; t < TB; ++t) {
-      const int8_t* xq = act.q + (size_t)t * act.K + off;
+      const int8_t* xq = act.q + (size_t)t * act.K + xoff;
       const uint4 xl = *reinterpret_cast<const uint4*>(xq);
-      const uint4 xh = *reinterpret_cast<const uint4*>(xq + 64);
+      const uint4 xh = *reinterpret_cast<const uint4*>(xq + 128);
       const uint32_t xlw[4] = {xl.x, xl.y, xl.z, xl.w}, xhw[4] = {xh.x, xh.y, xh.z, xh.w};
       int slo = 0, shi = 0;
 #pragma unroll
@@ -144,15 +207,10 @@ __device__ __forceinline__ void gv_lane_dot(const uint8_t* rowp, int it, int lan
       }
       const float* dx = act.d + (size_t)t * (act.K >> 5) + (off >> 5);
       const short* s16 = act.s16 + (size_t)t * (act.K >> 4) + (off >> 4);
-      acc[t] += dlo * dx[0] * (float)(slo - 32 * (int)s16[0]) + dhi * dx[2] * (float)(shi - 32 * (int)s16[4]);
+      acc[t] += f.dlo * dx[0] * (float)(slo - 32 * (int)s16[0]) + f.dhi * dx[2] * (float)(shi - 32 * (int)s16[4]);
     }
   } else if constexpr (QT == QT_Q8_0) {
     const int blk = it * 16 + (lane >> 1), hh = lane & 1;
-    if (blk * 32 >= K) return;
-    const uint8_t* b = rowp + (size_t)blk * 34;
-    uint32_t qw[4];
-    ld16_align2(b + 2 + 16 * hh, qw);
-    const float d = ld_half_raw(b);
     const int off = blk * 32 + 16 * hh;
 #pragma unroll
     for (int t = 0; t < TB; ++t) {
@@ -160,16 +218,11 @@ __device__ __forceinline__ void gv_lane_dot(const uint8_t* rowp, int it, int lan
       const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
       int s = 0;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) s = dp4a_ss(qw[w], xw[w], s);
-      acc[t] += d * act.d[(size_t)t * (act.K >> 5) + blk] * (float)s;
+      for (int w = 0; w < 4; ++w) s = dp4a_ss(f.a[w], xw[w], s);
+      acc[t] += f.d * act.d[(size_t)t * (act.K >> 5) + blk] * (float)s;
     }
   } else if constexpr (QT == QT_Q4_0) {
     const int blk = it * 32 + lane;
-    if (blk * 32 >= K) return;
-    const uint8_t* b = rowp + (size_t)blk * 18;
-    uint32_t qw[4];
-    ld16_align2(b + 2, qw);
-    const float d = ld_half_raw(b);
     const int off = blk * 32;
 #pragma unroll
     for (int t = 0; t < TB; ++t) {
@@ -180,18 +233,18 @@ __device__ __forceinline__ void gv_lane_dot(const uint8_t* rowp, int it, int lan
       int s = 0;
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
-        s = dp4a_ss(qw[w] & 0x0F0F0F0Fu, xlw[w], s);
-        s = dp4a_ss((qw[w] >> 4) & 0x0F0F0F0Fu, xhw[w], s);
+        s = dp4a_ss(f.a[w] & 0x0F0F0F0Fu, xlw[w], s);
+        s = dp4a_ss((f.a[w] >> 4) & 0x0F0F0F0Fu, xhw[w], s);
       }
       const short* s16 = act.s16 + (size_t)t * (act.K >> 4) + (off >> 4);
-      acc[t] += d * act.d[(size_t)t * (act.K >> 5) + blk] * (float)(s - 8 * ((int)s16[0] + (int)s16[1]));
+      acc[t] += f.d * act.d[(size_t)t * (act.K >> 5) + blk] * (float)(s - 8 * ((int)s16[0] + (int)s16[1]));
     }
   }
 }
 
 // Quantize X[T, K] (bf16, row stride ldX) into the CTA's shared memory: int8 codes, a scale per 32 values,
 // the code sum per 16 values.  Rows t >= T are zero.  Every thread of the CTA takes part.
-template <int TB>
+template <int QT, int TB>
 __device__ __forceinline__ void gv_quantize_x(const __nv_bfloat16* __restrict__ X, int ldX, int T, int K, int8_t* q, float* d,
                                               short* s16) {
   const int chunks = K >> 3;  // 8 values per thread-step; 4 consecutive lanes share one 32-value block
@@ -230,7 +283,9 @@ __device__ __forceinline__ void gv_quantize_x(const __nv_bfloat16* __restrict__ 
     if (live) {
       const uint32_t w0 = (qi[0] & 0xFF) | ((qi[1] & 0xFF) << 8) | ((qi[2] & 0xFF) << 16) | ((uint32_t)(qi[3] & 0xFF) << 24);
       const uint32_t w1 = (qi[4] & 0xFF) | ((qi[5] & 0xFF) << 8) | ((qi[6] & 0xFF) << 16) | ((uint32_t)(qi[7] & 0xFF) << 24);
-      *reinterpret_cast<uint2*>(q + (size_t)t * K + ch * 8) = make_uint2(w0, w1);
+      // (8 consecutive values stay consecutive under gv_act_pos)
+      const int j = ch * 8;
+      *reinterpret_cast<uint2*>(q + (size_t)t * K + (j & ~255) + gv_act_pos<QT>(j & 255)) = make_uint2(w0, w1);
       if ((ch & 1) == 0) s16[(size_t)t * (K >> 4) + (ch >> 1)] = (short)pair;
       if ((ch & 3) == 0) d[(size_t)t * (K >> 5) + (ch >> 2)] = scale;
     }
@@ -250,7 +305,7 @@ gemv_quant_kernel(const uint8_t* __restrict__ W, size_t row_bytes, const __nv_bf
   short* xs = reinterpret_cast<short*>(gv_smem + (size_t)TB * K + (size_t)TB * (K >> 5) * 4);
   pdl_launch_dependents();
   pdl_wait();  // the activations come from the upstream kernel
-  gv_quantize_x<TB>(X, ldX, T, K, xq, xd, xs);
+  gv_quantize_x<QT, TB>(X, ldX, T, K, xq, xd, xs);
   __syncthreads();
   const GvAct act{xq, xd, xs, K};
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -262,11 +317,23 @@ gemv_quant_kernel(const uint8_t* __restrict__ W, size_t row_bytes, const __nv_bf
     for (int r = 0; r < RPW; ++r)
 #pragma unroll
       for (int t = 0; t < TB; ++t) acc[r][t] = 0.f;
-    for (int it = 0; it < iters; ++it) {
+    // iterations in groups of G: all loads of a group (G iterations x RPW rows) are issued before the first use
+    constexpr int G = 2;
+    for (int it0 = 0; it0 < iters; it0 += G) {
+      GvFrag<QT> fr[G][RPW];
 #pragma unroll
-      for (int r = 0; r < RPW; ++r) {
-        const int row = r0 + r < N ? r0 + r : N - 1;  // a clamped row is computed and dropped
-        gv_lane_dot<QT, TB>(W + (size_t)row * row_bytes, it, lane, K, act, acc[r]);
+      for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+          const int row = r0 + r < N ? r0 + r : N - 1;  // a clamped row is computed and dropped
+          if (it0 + g < iters) gv_load<QT>(W + (size_t)row * row_bytes, it0 + g, lane, K, fr[g][r]);
+          else fr[g][r].live = false;
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) gv_dot<QT, TB>(fr[g][r], it0 + g, lane, act, acc[r]);
       }
     }
 #pragma unroll

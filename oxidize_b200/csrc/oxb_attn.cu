@@ -26,9 +26,8 @@ static int attn_launch(const AttnArgs& a, int B, int G, cudaStream_t stream) {
     configured = true;
   }
   dim3 grid(a.max_mtiles * a.n_cta_splits, a.nkv, B);
-  // (Merging the KV splits of a row tile inside a thread-block cluster was measured and is slower here:
-  // every CTA then waits for the slowest split, 21.7 vs 19.0 us on 64 x 1400-token decode.  The splits
-  // stay independent CTAs; the last one to finish merges.)
+  // (The KV splits of a row tile stay independent CTAs and the last one to finish merges: inside a thread-block
+  // cluster every CTA would wait for the slowest split.)
   if (a.n_cta_splits > 1 && (a.ws_o == nullptr || a.ws_ml == nullptr || a.counters == nullptr)) return (int)cudaErrorInvalidValue;
   oxb_launch(paged_attention_kernel<HD>, grid, dim3(ATT_WARPS * 32), (size_t)smem, stream, a, G);
   OXB_CHECK_LAUNCH();

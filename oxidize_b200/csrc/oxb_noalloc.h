@@ -24,9 +24,15 @@
  *     because each is written before it is read.  Two calls that overlap on the GPU (different
  *     streams, or the same device from two threads) race on the array: serialise them.
  *   - No cudaMalloc, cudaFree or allocating library routine is called.
+ *   - Any device of the process may be used (the address of the array, the SM count and the kernel's
+ *     shared-memory attribute are all kept per device ordinal); each device's first call does its set-up.
  *
- * Returns 0 on success, a positive cudaError_t value if a CUDA call failed, or a negative
- * OXB_NOALLOC_E_* code.
+ * Returns 0 when the kernel was LAUNCHED, a positive cudaError_t value if a CUDA call failed, or a
+ * negative OXB_NOALLOC_E_* code.  A zero return does not say that the kernel completed its work: the
+ * split-K CTAs of a tile wait for one another with a bounded wait, and if other work on the GPU keeps
+ * them from being resident together the wait gives up, Y is left unwritten for that tile and the
+ * library's device status word records OXB_TIMEOUT_SPLITK.  Read it with oxb_status() (declared
+ * below; it synchronises the device) after the call when the result matters.
  */
 #ifndef OXB_NOALLOC_H
 #define OXB_NOALLOC_H
@@ -45,6 +51,10 @@ extern "C" {
 
 int oxb_gemm_bf16_noalloc(const void* X, const void* W, void* Y, const float* bias, int T, int N, int K, int ldY,
                           void* cuda_stream);
+
+/* Device status word of the library: out4 = {code, detail, count, 0}; code 0 = every bounded wait succeeded.
+ * reset != 0 clears it.  Synchronises the device. */
+int oxb_status(int* out4, int reset);
 
 #ifdef __cplusplus
 }

@@ -109,14 +109,30 @@ class DraftModelProposer:
 
     def propose(self, seqs: List[Sequence]) -> Dict[int, List[int]]:
         drafts: Dict[int, List[int]] = {s.seq_id: [] for s in seqs}
-        # catch-up pass: everything the draft has not seen yet, including the last sampled token
-        sched = []
+        # catch-up: everything the draft has not seen yet, including the last sampled token.  A whole prompt can be
+        # pending (first round after the target's prefill), so what does not fit into one batch of the draft's runner
+        # next to the other sequences is fed ahead in unsampled chunks.
+        cap = self.runner.buf.max_tokens
+        done_of = {}
         for s in seqs:
             sh = self._shadow(s)
             sh.prompt = s.all_tokens
-            done = min(self.computed[s.seq_id], len(sh.prompt) - 1)
+            done_of[s.seq_id] = min(self.computed[s.seq_id], len(sh.prompt) - 1)
             self._ensure(sh, len(sh.prompt) + self.k)
-            sched.append(ScheduledSeq(sh, done, len(sh.prompt) - done, True, True))
+        while sum(len(self.shadow[s.seq_id].prompt) - done_of[s.seq_id] for s in seqs) > cap:
+            budget, batch = cap, []
+            for s in seqs:
+                sh = self.shadow[s.seq_id]
+                n = min(len(sh.prompt) - done_of[s.seq_id] - 1, budget)  # the last pending token belongs to the sampled pass
+                if n > 0:
+                    batch.append(ScheduledSeq(sh, done_of[s.seq_id], n, True, False))
+                    done_of[s.seq_id] += n
+                    budget -= n
+            if not batch:
+                break
+            self.runner.execute(SchedulerOutput(batch))
+        sched = [ScheduledSeq(self.shadow[s.seq_id], done_of[s.seq_id], len(self.shadow[s.seq_id].prompt) - done_of[s.seq_id], True,
+                              True) for s in seqs]
         sampled = [s for s in seqs if not s.params.is_greedy]
         rows_of: Dict[int, List[torch.Tensor]] = {s.seq_id: [] for s in sampled}
         keep, self.runner.keep_logits = self.runner.keep_logits, bool(sampled)
@@ -227,11 +243,12 @@ class MtpProposer:
             saved = m.w.layers, m.w.first_layer
             m.w.layers = [w.layer]
             try:
-                win = cfg.sliding_window
+                win, pat = cfg.sliding_window, cfg.sliding_window_pattern
                 cfg.sliding_window = max(1, min((p + it + 1) - self.start[s.seq_id] for s, p in zip(ready, pos0)))
+                cfg.sliding_window_pattern = 0
                 h, res = m.run_layers(x, None, meta, self.kv)
             finally:
-                cfg.sliding_window = win
+                cfg.sliding_window, cfg.sliding_window_pattern = win, pat
                 m.w.layers, m.w.first_layer = saved
             xn, hsum = ops.add_rmsnorm(h, res, w.shared_head_norm, cfg.rms_eps)
             logits = ops.linear(xn, head).float()

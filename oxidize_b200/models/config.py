@@ -63,6 +63,10 @@ class ModelConfig:
     rope_scaling: RopeScaling = field(default_factory=RopeScaling)
     context_length: int = 8192
     sliding_window: int = 0
+    # 0: a configured window applies to every layer (Mistral / Qwen style).  n > 0: every n-th layer attends over the
+    # whole context and the others use the window (interleaved local / global attention; the reference's
+    # ``layer_is_global``, oxidize-core/src/model/inference.rs:304-333).
+    sliding_window_pattern: int = 0
     qk_norm: bool = False
     attn_bias: bool = False
     tie_embeddings: bool = False
@@ -98,6 +102,14 @@ class ModelConfig:
     @property
     def kv_size(self) -> int:
         return self.n_kv_heads * self.head_dim
+
+    def layer_sliding_window(self, layer: int) -> int:
+        """Attention window of one layer: 0 = the whole context."""
+        if self.sliding_window <= 0:
+            return 0
+        if self.sliding_window_pattern > 0 and (layer + 1) % self.sliding_window_pattern == 0:
+            return 0
+        return self.sliding_window
 
     def layer_is_moe(self, layer: int) -> bool:
         return self.is_moe and layer >= self.leading_dense_blocks
@@ -179,6 +191,7 @@ def config_from_gguf(g: GGUFFile) -> ModelConfig:
         )
     c.context_length = int(_scalar(a("context_length"), 8192))
     c.sliding_window = int(_scalar(a("attention.sliding_window"), 0))
+    c.sliding_window_pattern = int(_scalar(a("attention.sliding_window_pattern"), 0))
     c.qk_norm = g.has_tensor("blk.0.attn_q_norm.weight")
     c.attn_bias = g.has_tensor("blk.0.attn_q.bias")
     c.tie_embeddings = not g.has_tensor("output.weight")

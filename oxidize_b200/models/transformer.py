@@ -166,7 +166,7 @@ class Transformer:
         else:
             qkv = opcuda.gemm_bf16(r, wq, sumsq_in=acc[cur], eps=eps, clear=acc[1 - cur])
             q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, self.rope, lw.q_norm, lw.k_norm, eps)
-        attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, cfg.sliding_window)
+        attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, cfg.layer_sliding_window(self.w.first_layer + layer))
         cur = 1 - cur
         self._row_parallel_into(attn.reshape(attn.shape[0], -1), lw.wo, r, acc[cur])
         act = opcuda.linear_swiglu(r, lw.w_gate_up.parts[0].data, sumsq_in=acc[cur], eps=eps, clear=acc[1 - cur])
@@ -197,12 +197,12 @@ class Transformer:
 
             if opcuda.qkv_rope_fusable(lw.wqkv.parts, kv, self.rope, lw.q_norm, lw.k_norm):
                 q = opcuda.linear_qkv_rope(x, lw.wqkv.parts[0].data, meta.positions, meta.slot_mapping, kv, layer, self.rope)
-                attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, cfg.sliding_window)
+                attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, cfg.layer_sliding_window(self.w.first_layer + layer))
                 return self.comm.linear_allreduce(attn.reshape(attn.shape[0], -1), lw.wo)
         qkv = ops.linear(x, lw.wqkv)
         q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, self.rope,
                                  lw.q_norm, lw.k_norm, cfg.rms_eps)
-        attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, cfg.sliding_window)
+        attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, cfg.layer_sliding_window(self.w.first_layer + layer))
         return self.comm.linear_allreduce(attn.reshape(attn.shape[0], -1), lw.wo)
 
     def _dense_ffn(self, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:

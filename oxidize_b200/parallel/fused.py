@@ -24,9 +24,8 @@ from .. import ops
 from .comm import TorchComm
 
 AR_MAX_TOKENS = 4096  # hard limit of the receive buffers (8 bytes x hidden x 2 x (W+1) per token row)
-# Calls with more tokens than this go to GEMM + NCCL by default: the LL wire format doubles the bytes,
-# which wins on latency for decode batches but loses on bandwidth for prefill chunks (measured at 8 GPUs:
-# p50 TTFT 2.29 s with fused prefill chunks against 2.10 s with NCCL).
+# Calls with more tokens than this go to GEMM + NCCL by default: the two-shot wire format carries an epoch beside
+# every 4 bytes of payload, which wins on latency for decode batches and loses on bandwidth for prefill chunks.
 FUSED_MAX_TOKENS = 256
 
 

@@ -18,7 +18,7 @@ from typing import Any, Dict, List, Optional
 from ..formats.gguf import GGUFFile
 from ..models.config import ModelConfig, config_from_gguf
 
-B200_HBM_GBS = 6555.0  # measured copy bandwidth of this pool's B200s
+B200_HBM_GBS = 6555.0  # sustained copy bandwidth of a B200 (HBM3e), GB/s: the bound the decode estimates use
 
 
 @dataclass

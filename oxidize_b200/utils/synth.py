@@ -101,6 +101,8 @@ def write_config_metadata(w: GGUFWriter, cfg: ModelConfig) -> None:
     w.add(f"{a}.rope.dimension_count", cfg.rotary_dim, U)
     if cfg.sliding_window:
         w.add(f"{a}.attention.sliding_window", cfg.sliding_window, U)
+        if cfg.sliding_window_pattern:
+            w.add(f"{a}.attention.sliding_window_pattern", cfg.sliding_window_pattern, U)
     if cfg.rope_scaling.type != "none":
         w.add(f"{a}.rope.scaling.type", cfg.rope_scaling.type)
         w.add(f"{a}.rope.scaling.factor", float(cfg.rope_scaling.factor), GGUFValueType.FLOAT32)

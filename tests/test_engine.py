@@ -672,3 +672,36 @@ def test_run_ahead_decode_survives_abort_and_drain(tmp_path):
                 final[ro.request_id] = ro
     assert len(final[b].token_ids) == 40
     assert llm.pool.num_free == llm.pool.num_blocks
+
+
+def test_interleaved_local_global_attention_layers(tmp_path):
+    """sliding_window_pattern = n: every n-th layer sees the whole context, the others the window."""
+    from oxidize_b200.engine.llm import LLM, EngineConfig
+    from oxidize_b200.engine.sampler import SamplingParams
+    from oxidize_b200.models.config import preset
+    from oxidize_b200.utils.synth import synth_gguf
+
+    base = dict(n_layers=2, vocab_size=97, hidden_size=64, n_heads=4, n_kv_heads=2, head_dim=16, ffn_size=96)
+    ec = dict(max_model_len=96, max_num_seqs=2, num_kv_blocks=32, prefill_chunk_size=64, max_num_batched_tokens=64,
+              kv_page_size=4, enable_prefix_cache=False)
+    sp = SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True)
+    prompt = list(range(3, 43))
+
+    def run(want, **kw):
+        cfg = preset("tiny-llama", **base, **kw)
+        assert [cfg.layer_sliding_window(i) for i in range(2)] == want
+        p = str(tmp_path / f"w_{kw.get('sliding_window', 0)}_{kw.get('sliding_window_pattern', 0)}.gguf")
+        synth_gguf(p, cfg, "F32", seed=9, norm_jitter=0.2)
+        llm = LLM.from_gguf(p, EngineConfig(**ec), device="cpu")
+        llm.runner.keep_logits = True
+        llm.add_request(prompt, sp)
+        llm.step()
+        return llm.last_step[1].logits.float()
+
+    full = run([0, 0])
+    uniform = run([8, 8], sliding_window=8)
+    all_global = run([0, 0], sliding_window=8, sliding_window_pattern=1)
+    mixed = run([8, 0], sliding_window=8, sliding_window_pattern=2)
+    assert torch.allclose(all_global, full, atol=1e-5)
+    assert not torch.allclose(uniform, full, atol=1e-4)
+    assert not torch.allclose(mixed, full, atol=1e-4) and not torch.allclose(mixed, uniform, atol=1e-4)
