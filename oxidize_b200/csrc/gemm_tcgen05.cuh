@@ -44,8 +44,9 @@ struct GemmTile {
 };
 
 // Q4_K and Q6_K weights with decode-sized token tiles are staged through shared memory: one TMA box of
-// 128 rows x one 256-value super-block of every row of the tile per four k-blocks, double buffered; the
-// producer warps decode from there.  (Reading the packed rows straight from global memory, one thread per
+// 128 rows x one 256-value super-block of every row of the tile per four k-blocks, in a ring of RING boxes
+// (one being decoded, the others in flight: a box is small against the latency of its fetch, so the
+// ring, not the decoders, sets how many bytes the SM keeps in flight); the producer warps decode from there.  (Reading the packed rows straight from global memory, one thread per
 // row, makes every warp-wide load touch 32 cache lines.)  A Q6_K super-block is 210 bytes, which TMA cannot
 // address (16-byte rule): its box starts at the 16-byte boundary below the block and is 240 bytes wide, and
 // the decoder starts at the remainder inside the row.  Rows must be 16-byte multiples (QwArgs::staged says
@@ -55,13 +56,27 @@ struct MmqStage {
   static constexpr int SB = QT == QT_Q4_K ? 144 : QT == QT_Q6_K ? 210 : 0;    // super-block bytes
   static constexpr int BOX = QT == QT_Q4_K ? 144 : QT == QT_Q6_K ? 240 : 0;   // bytes fetched per row
   static constexpr int BYTES = GEMM_BM * BOX;
+  static constexpr int RING = QT == QT_Q4_K ? 4 : 3;                          // boxes per CTA (72 / 90 KB)
 };
 template <int TN, int QT>
 struct MmqStaged {
   static constexpr bool value = (QT == QT_Q4_K || QT == QT_Q6_K) && TN <= 64;
 };
+// Ring depth.  bf16 weights: GemmTile's (the weight stream itself fills the ring).  Packed weights with decode-sized
+// tiles: as deep as shared memory allows.  There a k-block carries 3-4x fewer weight bytes, so the CTA has 3-4x less
+// time per k-block, while a stage still takes one activation-tile fetch (an L2 round trip) to turn around; the number
+// of stages, not the decoders, bounds the k-block rate.
 template <int TN, int QT>
-constexpr int gemm_smem_bytes() { return GemmTile<TN>::SMEM_BYTES + (MmqStaged<TN, QT>::value ? 2 * MmqStage<QT>::BYTES : 0); }
+struct GemmStages {
+  static constexpr int FIXED = 1024 + 256 + 1024 + (MmqStaged<TN, QT>::value ? MmqStage<QT>::RING * MmqStage<QT>::BYTES : 0);
+  static constexpr int FIT = (224 * 1024 - FIXED) / GemmTile<TN>::STAGE_BYTES;
+  static constexpr int value = (QT == QT_BF16 || TN > 64) ? GemmTile<TN>::STAGES : (FIT > 8 ? 8 : FIT);
+};
+template <int TN, int QT>
+constexpr int gemm_smem_bytes() {
+  return GemmStages<TN, QT>::value * GemmTile<TN>::STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + 1024 /*token scales*/ +
+         (MmqStaged<TN, QT>::value ? MmqStage<QT>::RING * MmqStage<QT>::BYTES : 0);
+}
 
 // Epilogue modes
 constexpr int EPI_STORE = 0;      // Y = acc (+bias)
@@ -353,7 +368,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   }
   Y += gathered ? (size_t)g_row0 * ldY : (size_t)zg * gr.y_stride;
   using Cfg = GemmTile<TN>;
-  constexpr int STAGES = Cfg::STAGES;
+  constexpr int STAGES = GemmStages<TN, QT>::value;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
@@ -363,9 +378,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* ticket = const_cast<int*>(abort_flag) + 1;
   constexpr bool STAGED = MmqStaged<TN, QT>::value;
-  uint64_t* packed_full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES + 192);  // [2] (STAGED only)
-  uint8_t* packed_buf = smem + STAGES * Cfg::STAGE_BYTES + 256;                                  // [2][128][144]
-  float* tok_scale = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES + 256 + (STAGED ? 2 * MmqStage<QT>::BYTES : 0));  // [TN]
+  constexpr int PRING = STAGED ? MmqStage<QT>::RING : 0;
+  uint64_t* packed_full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES + 192);  // [PRING <= 4] (STAGED only)
+  uint64_t* packed_empty = packed_full + 4;                                                     // [PRING <= 4]
+  uint8_t* packed_buf = smem + STAGES * Cfg::STAGE_BYTES + 256;                                  // [PRING][128][BOX]
+  float* tok_scale = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES + 256 + PRING * MmqStage<QT>::BYTES);  // [TN]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * GEMM_BM;
@@ -387,8 +404,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     }
     mbar_init(accum, 1);
     if constexpr (STAGED) {
-      mbar_init(&packed_full[0], 1);
-      mbar_init(&packed_full[1], 1);
+      for (int i = 0; i < PRING; ++i) {
+        mbar_init(&packed_full[i], 1);
+        mbar_init(&packed_empty[i], (GEMM_THREADS_MMQ - GEMM_THREADS) / 32);  // one arrival per producer warp
+      }
     }
     *abort_flag = 0;
     ticket[0] = 0;
@@ -523,26 +542,36 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       if constexpr (STAGED) if (qw.staged) {
         staged_done = true;
         constexpr int SB = MmqStage<QT>::SB, BOX = MmqStage<QT>::BOX, PBYTES = MmqStage<QT>::BYTES;
-        // Packed super-blocks arrive by TMA (tmW maps the packed rows as bytes): thread 192 keeps two
-        // boxes in flight, all 128 producers decode their own row out of shared memory.  Weights are
-        // static, so none of this waits for the upstream kernel.
+        // Packed super-blocks arrive by TMA (tmW maps the packed rows as bytes): thread 192 keeps PRING - 1
+        // boxes in flight while one is decoded; all producers decode their own row out of shared memory and
+        // every warp releases a box when it is done with it.  Weights are static, so none of this waits for
+        // the upstream kernel.
         const int sb_begin = kb_begin >> 2, sb_end = (kb_end + 3) >> 2;  // super-blocks touched by [kb_begin, kb_end)
-        auto issue = [&](int j) {  // j-th super-block of this CTA -> buffer j & 1
-          mbar_expect_tx(&packed_full[j & 1], PBYTES);
-          tma_load_2d(packed_buf + (j & 1) * PBYTES, &tmW, &packed_full[j & 1], ((sb_begin + j) * SB) & ~15, w_row0);
+        auto issue = [&](int j) {  // j-th super-block of this CTA -> box j % PRING
+          const int b = j % PRING;
+          mbar_expect_tx(&packed_full[b], PBYTES);
+          tma_load_2d(packed_buf + b * PBYTES, &tmW, &packed_full[b], ((sb_begin + j) * SB) & ~15, w_row0);
         };
         const int nsb = sb_end - sb_begin;
-        if (r == 0 && grp == 0) {
+        const bool issuer = r == 0 && grp == 0;
+        if (issuer) {
           tma_prefetch_desc(&tmW);
-          for (int j = 0; j < 2 && j < nsb; ++j) issue(j);
+          for (int j = 0; j < PRING && j < nsb; ++j) issue(j);
         }
         bool alive = true;
         for (int j = 0; j < nsb; ++j) {
+          const int b = j % PRING;
+          // the box of super-block j - 1 is refilled as soon as every warp has let go of it
+          if (issuer && alive && j >= 1 && j - 1 + PRING < nsb) {
+            if (mbar_wait_bounded(&packed_empty[(j - 1) % PRING], ((j - 1) / PRING) & 1, abort_flag, OXB_TIMEOUT_TMA_EMPTY,
+                                  blockIdx.x))
+              issue(j - 1 + PRING);
+          }
           if (alive)
-            alive = __all_sync(0xffffffffu, mbar_wait_bounded(&packed_full[j & 1], (j >> 1) & 1, abort_flag,
+            alive = __all_sync(0xffffffffu, mbar_wait_bounded(&packed_full[b], (j / PRING) & 1, abort_flag,
                                                               OXB_TIMEOUT_TMA_FULL, blockIdx.x));
           if (alive) {
-            const uint8_t* srow = packed_buf + (j & 1) * PBYTES + r * BOX + (((sb_begin + j) * SB) & 15);
+            const uint8_t* srow = packed_buf + b * PBYTES + r * BOX + (((sb_begin + j) * SB) & 15);
             const int kb0 = max(kb_begin, (sb_begin + j) * 4), kb1 = min(kb_end, (sb_begin + j) * 4 + 4);
             for (int kb = kb0; kb < kb1 && alive; ++kb) {
               if (((kb - kb_begin) & 1) != grp) continue;  // the other group's k-block
@@ -551,9 +580,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
               alive = publish(kb - kb_begin, v);
             }
           }
-          // every producer is done with this buffer before it is refilled (all 256 take part, alive or not)
-          asm volatile("bar.sync 2, 256;" ::: "memory");
-          if (r == 0 && grp == 0 && alive && j + 2 < nsb) issue(j + 2);
+          __syncwarp();  // the warp's reads of the box are done (alive or not, so that the issuer never waits in vain)
+          if (lane == 0) mbar_arrive(&packed_empty[b]);
         }
       }
       if (!staged_done) {
