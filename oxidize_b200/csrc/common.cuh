@@ -33,9 +33,34 @@ enum OxbStatus : int {
   OXB_BAD_ARGUMENT = 8,   // a kernel argument outside its documented range (work skipped)
 };
 
-// Device status word (one per loaded library per device); host reads it with oxb_status().
-// Defined once in oxb.cu; the translation units are compiled as relocatable device code and share it.
-extern __device__ int g_oxb_status[4];  // [0]=code, [1]=detail (block / stage / rank), [2]=count
+// Device status word; the host reads it with oxb_status().  The translation units of the library are compiled
+// independently (no relocatable device code: whole-kernel optimisations such as per-warpgroup register budgets need the
+// compiler to see a complete program), so each unit has its own copy and registers a reader for it; oxb_status() merges
+// the copies (first non-zero code, summed count).
+static __device__ int g_oxb_status[4];  // [0]=code, [1]=detail (block / stage / rank), [2]=count
+struct OxbStatusUnit {
+  int (*read)(int* out4, int reset);
+  OxbStatusUnit* next;
+};
+void oxb_register_status_unit(OxbStatusUnit* u);  // oxb.cu
+namespace {
+int oxb_status_of_this_unit(int* out4, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out4, g_oxb_status, 4 * sizeof(int));
+  if (e == cudaSuccess && reset) {
+    const int z[4] = {0, 0, 0, 0};
+    e = cudaMemcpyToSymbol(g_oxb_status, z, sizeof(z));
+  }
+  return (int)e;
+}
+struct OxbStatusRegistration {
+  OxbStatusUnit unit;
+  OxbStatusRegistration() {
+    unit.read = &oxb_status_of_this_unit;
+    unit.next = nullptr;
+    oxb_register_status_unit(&unit);
+  }
+} g_oxb_status_registration;
+}  // namespace
 
 __device__ __forceinline__ void oxb_report(int code, int detail) {
   if (atomicCAS(&g_oxb_status[0], 0, code) == 0) g_oxb_status[1] = detail;

@@ -20,8 +20,24 @@ namespace oxb {
 
 constexpr int GEMM_BM = 128;  // weight rows per tile (UMMA M)
 constexpr int GEMM_BK = 64;   // bf16 per k-block = one 128-byte swizzle row
-constexpr int GEMM_THREADS = 192;       // TMA warp, MMA warp, 4 epilogue warps
-constexpr int GEMM_THREADS_MMQ = 448;   // + 8 dequant producer warps for packed weights (two groups of four)
+// Warp roles.  Warps 0-3: epilogue (TMEM lane quarter = warp % 4).  Warp 4: TMA.  Warp 5: MMA issuer (owns the TMEM
+// allocation).  Packed weights add warps 6-7 (idle: they complete the second warpgroup, so that register budgets can be
+// moved between whole warpgroups) and, from warp 8 on, the dequant producers.
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_WARP_TMA = 4, GEMM_WARP_MMA = 5, GEMM_WARP_PRODUCER0 = 8;
+#ifndef OXB_MMQ_GROUPS
+#define OXB_MMQ_GROUPS 4
+#endif
+constexpr int MMQ_GROUPS = OXB_MMQ_GROUPS;  // producer groups of four warps (one weight row per thread); group g decodes k-blocks g, g + MMQ_GROUPS, ...
+constexpr int GEMM_THREADS_MMQ = 32 * GEMM_WARP_PRODUCER0 + 128 * MMQ_GROUPS;
+// Register budgets of the packed-weight kernel (setmaxnreg): registers per thread at launch, then per warpgroup role.
+// A CTA can only redistribute what it was launched with, so the budgets must add up to exactly that.
+constexpr int MMQ_REGS_LAUNCH = 80, MMQ_REGS_EPILOGUE = 184, MMQ_REGS_CONTROL = 40, MMQ_REGS_PRODUCER = 64;
+static_assert(128 * MMQ_REGS_EPILOGUE + 128 * MMQ_REGS_CONTROL + 128 * MMQ_GROUPS * MMQ_REGS_PRODUCER ==
+                  GEMM_THREADS_MMQ * MMQ_REGS_LAUNCH,
+              "warpgroup register budgets must add up to the launch allocation");
+static_assert(GEMM_THREADS_MMQ * (MMQ_REGS_LAUNCH + 8) > 65536, "launch bounds must pin the kernel to MMQ_REGS_LAUNCH registers");
+
 
 // k-blocks (16 KB of weights each) a CTA requests into the L2 before the grid dependency resolves
 // (GroupArgs::l2_prefetch_kb, set per launch).  Behind an HBM-bound kernel this LOSES 10-20% (the
@@ -39,11 +55,16 @@ struct GemmTile {
   // already stream their weights while this kernel drains, and a split-K grid may hold 2 CTAs per SM.
   static constexpr int STAGES = TN <= 16 ? 6 : TN == 32 ? 5 : TN == 64 ? 4 : (TN == 128 ? 6 : 4);
   static constexpr int CTAS_PER_SM = TN <= 64 ? 2 : 1;
-  static constexpr int TMEM_COLS = TN < 32 ? 32 : TN;
+  // One accumulator per tile.  (Spreading the four k-steps of a k-block over separate accumulators, to break the
+  // dependency chain of back-to-back MMAs, changes nothing measurable: the issue rate at decode sizes is set by how
+  // fast the tensor core can fetch its operands from shared memory, not by the accumulate latency.)
+  static constexpr int NACC = 1;
+  static constexpr int ACC_COLS = TN < 32 ? 32 : TN;  // TMEM columns between accumulators
+  static constexpr int TMEM_COLS = NACC * ACC_COLS;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + 1024 /*token scales*/;
 };
 
-// Q4_K and Q6_K weights with decode-sized token tiles are staged through shared memory: one TMA box of
+// Packed weights with decode-sized token tiles are staged through shared memory: one TMA box of
 // 128 rows x one 256-value super-block of every row of the tile per four k-blocks, in a ring of RING boxes
 // (one being decoded, the others in flight: a box is small against the latency of its fetch, so the
 // ring, not the decoders, sets how many bytes the SM keeps in flight); the producer warps decode from there.  (Reading the packed rows straight from global memory, one thread per
@@ -53,29 +74,38 @@ struct GemmTile {
 // whether the host could build the byte map; otherwise the producers read global memory as before).
 template <int QT>
 struct MmqStage {
-  static constexpr int SB = QT == QT_Q4_K ? 144 : QT == QT_Q6_K ? 210 : 0;    // super-block bytes
-  static constexpr int BOX = QT == QT_Q4_K ? 144 : QT == QT_Q6_K ? 240 : 0;   // bytes fetched per row
+  // bytes of 256 values of one row, and bytes fetched per row (16-byte multiples; never a multiple of 128, which
+  // would put every row of the box on the same shared-memory banks)
+  static constexpr int SB = QT == QT_Q6_K ? 210 : QT == QT_Q8_0 ? 272 : QT == QT_FP8B ? 256 : 144;
+  static constexpr int BOX = QT == QT_Q6_K ? 240 : (QT == QT_Q8_0 || QT == QT_FP8B) ? 272 : 144;
   static constexpr int BYTES = GEMM_BM * BOX;
-  static constexpr int RING = QT == QT_Q4_K ? 4 : 3;                          // boxes per CTA (72 / 90 KB)
+  static constexpr int RING = BOX == 144 ? 4 : 3;  // boxes per CTA (72 / 90 / 102 KB); see MmqRing for wide token tiles
+};
+// bytes fetched per row for a packed format (host side)
+inline int mmq_box_bytes(int qtype) { return qtype == QT_Q6_K ? 240 : (qtype == QT_Q8_0 || qtype == QT_FP8B) ? 272 : 144; }
+// boxes per CTA: the 272-byte formats keep two with 128-token tiles, so that the stage ring stays at four
+template <int TN, int QT>
+struct MmqRing {
+  static constexpr int value = (TN >= 128 && MmqStage<QT>::BOX == 272) ? 2 : MmqStage<QT>::RING;
 };
 template <int TN, int QT>
 struct MmqStaged {
-  static constexpr bool value = (QT == QT_Q4_K || QT == QT_Q6_K) && TN <= 64;
+  static constexpr bool value = QT != QT_BF16;
 };
-// Ring depth.  bf16 weights: GemmTile's (the weight stream itself fills the ring).  Packed weights with decode-sized
-// tiles: as deep as shared memory allows.  There a k-block carries 3-4x fewer weight bytes, so the CTA has 3-4x less
+// Ring depth.  bf16 weights: GemmTile's (the weight stream itself fills the ring).  Packed weights: as deep as
+// shared memory allows beside the ring of packed boxes.  There a k-block carries 3-4x fewer weight bytes, so the CTA has 3-4x less
 // time per k-block, while a stage still takes one activation-tile fetch (an L2 round trip) to turn around; the number
 // of stages, not the decoders, bounds the k-block rate.
 template <int TN, int QT>
 struct GemmStages {
-  static constexpr int FIXED = 1024 + 256 + 1024 + (MmqStaged<TN, QT>::value ? MmqStage<QT>::RING * MmqStage<QT>::BYTES : 0);
+  static constexpr int FIXED = 1024 + 256 + 1024 + (MmqStaged<TN, QT>::value ? MmqRing<TN, QT>::value * MmqStage<QT>::BYTES : 0);
   static constexpr int FIT = (224 * 1024 - FIXED) / GemmTile<TN>::STAGE_BYTES;
-  static constexpr int value = (QT == QT_BF16 || TN > 64) ? GemmTile<TN>::STAGES : (FIT > 8 ? 8 : FIT);
+  static constexpr int value = QT == QT_BF16 ? GemmTile<TN>::STAGES : (FIT > 8 ? 8 : FIT);
 };
 template <int TN, int QT>
 constexpr int gemm_smem_bytes() {
   return GemmStages<TN, QT>::value * GemmTile<TN>::STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + 1024 /*token scales*/ +
-         (MmqStaged<TN, QT>::value ? MmqStage<QT>::RING * MmqStage<QT>::BYTES : 0);
+         (MmqStaged<TN, QT>::value ? MmqRing<TN, QT>::value * MmqStage<QT>::BYTES : 0);
 }
 
 // Epilogue modes
@@ -337,6 +367,39 @@ struct GroupArgs {
 
 // QT == QT_BF16: both operands arrive by TMA.  Any other QT: the weight tile is produced by four
 // dequant warps from packed blocks (see mmq_producer.cuh) and only the activations use TMA.
+// 16 accumulator columns of this warp's TMEM lanes, summed over the NACC accumulators (fixed order)
+template <int NACC, int ACC_COLS>
+__device__ __forceinline__ void tmem_ld16_acc(uint32_t taddr, uint32_t* r) {
+  tmem_ld16(taddr, r);
+  tmem_ld_wait();
+#pragma unroll
+  for (int a = 1; a < NACC; ++a) {
+    uint32_t t[16];
+    tmem_ld16(taddr + a * ACC_COLS, t);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(t[j]));
+  }
+}
+
+#ifdef OXB_MMQ_TRACE
+// Phase trace of one CTA of the packed-weight GEMM (cycles spent in each wait, per role), per translation unit
+static __device__ long long g_oxb_mmq_trace[32];
+#define OXB_TR_DECL long long tr_w0 = 0, tr_w1 = 0, tr_w2 = 0; const long long tr_begin = clock64();
+#define OXB_TR_WAIT(acc, expr) [&]() { const long long t_ = clock64(); const bool ok_ = (expr); acc += clock64() - t_; return ok_; }()
+#define OXB_TR_STORE(slot) if (MMQ && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && blockIdx.z == 0) { \
+    g_oxb_mmq_trace[(slot) * 4 + 0] = clock64() - tr_begin; g_oxb_mmq_trace[(slot) * 4 + 1] = tr_w0; \
+    g_oxb_mmq_trace[(slot) * 4 + 2] = tr_w1; g_oxb_mmq_trace[(slot) * 4 + 3] = tr_w2; }
+#define OXB_TR_BEGIN const long long tr_t_ = clock64();
+#define OXB_TR_END(acc) acc += clock64() - tr_t_;
+#else
+#define OXB_TR_DECL
+#define OXB_TR_WAIT(acc, expr) (expr)
+#define OXB_TR_STORE(slot)
+#define OXB_TR_BEGIN
+#define OXB_TR_END(acc)
+#endif
+
 template <int TN, int QT>
 __global__ void __launch_bounds__(QT == QT_BF16 ? GEMM_THREADS : GEMM_THREADS_MMQ, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
@@ -378,7 +441,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* ticket = const_cast<int*>(abort_flag) + 1;
   constexpr bool STAGED = MmqStaged<TN, QT>::value;
-  constexpr int PRING = STAGED ? MmqStage<QT>::RING : 0;
+  constexpr int PRING = STAGED ? MmqRing<TN, QT>::value : 0;
+  // a producer group may run at most STAGES k-blocks ahead of the slowest one; with more groups than stages it could
+  // be two uses of a stage ahead, which the one-bit phase of the stage's barrier cannot tell apart
+  static_assert(!MMQ || STAGES >= MMQ_GROUPS, "the stage ring must be at least as deep as the number of producer groups");
   uint64_t* packed_full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES + 192);  // [PRING <= 4] (STAGED only)
   uint64_t* packed_empty = packed_full + 4;                                                     // [PRING <= 4]
   uint8_t* packed_buf = smem + STAGES * Cfg::STAGE_BYTES + 256;                                  // [PRING][128][BOX]
@@ -406,14 +472,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     if constexpr (STAGED) {
       for (int i = 0; i < PRING; ++i) {
         mbar_init(&packed_full[i], 1);
-        mbar_init(&packed_empty[i], (GEMM_THREADS_MMQ - GEMM_THREADS) / 32);  // one arrival per producer warp
+        mbar_init(&packed_empty[i], 4 * MMQ_GROUPS);  // one arrival per producer warp
       }
     }
     *abort_flag = 0;
     ticket[0] = 0;
     mbar_fence_init();
   }
-  if (warp == 1) {
+  if (warp == GEMM_WARP_MMA) {
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
@@ -421,11 +487,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  pdl_launch_dependents();  // the next kernel may start its own set-up now
+  // The next kernel may start its own set-up now.  (Packed weights: only after this CTA's registers have been
+  // moved between its warpgroups, see below, so that no CTA of the next kernel can take what a warpgroup released.)
+  if constexpr (!MMQ) pdl_launch_dependents();
 
-  if (warp == 0) {
+  // Packed weights: 768 threads leave 80 registers each.  The decoders need few, the epilogue many: the second
+  // warpgroup (TMA, MMA, idle) and the producers hand registers back, the epilogue warpgroup takes exactly what they
+  // released (a CTA can only redistribute its own launch allocation; the request waits for the other warpgroups'
+  // releases, which are the first instruction of their branches).  Each budget is set at the top of its branch.
+  if (warp >= 4 && warp < GEMM_WARP_PRODUCER0) {
+    if constexpr (MMQ) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(MMQ_REGS_CONTROL));
+  if (warp == GEMM_WARP_TMA) {
     // ---------------- TMA producer
     if (lane == 0) {
+      OXB_TR_DECL
       tma_prefetch_desc(&tmW);
       tma_prefetch_desc(&tmX);
       const uint64_t pol_w = l2_policy_evict_first();  // weights are read once per step
@@ -456,7 +531,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       for (int i = npre; i < nkb; ++i) {
         const int st = i % STAGES;
         const uint32_t ph = (i / STAGES) & 1;
-        if (!mbar_wait_bounded(&empty[st], ph ^ 1, abort_flag, OXB_TIMEOUT_TMA_EMPTY, blockIdx.x)) break;
+        if (!OXB_TR_WAIT(tr_w0, mbar_wait_bounded(&empty[st], ph ^ 1, abort_flag, OXB_TIMEOUT_TMA_EMPTY, blockIdx.x))) break;
         uint8_t* sA = smem + st * Cfg::STAGE_BYTES;
         uint8_t* sB = sA + Cfg::A_BYTES;
         if constexpr (MMQ) {
@@ -467,54 +542,60 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         }
         tma_load_2d_hint(sB, &tmX, &full[st], (kb_begin + i) * GEMM_BK, x_row0, pol_x);
       }
+      OXB_TR_STORE(0)
     }
-    __syncwarp();
-    if (csplit) {
-      cluster_sync_all();
-      cluster_sync_all();
-    }
-  } else if (warp == 1) {
+  } else if (warp == GEMM_WARP_MMA) {
     // ---------------- MMA issuer
     if (lane == 0) {
+      OXB_TR_DECL
       constexpr uint32_t idesc = umma_idesc_bf16(GEMM_BM, TN);
       for (int i = 0; i < nkb; ++i) {
         const int st = i % STAGES;
         const uint32_t ph = (i / STAGES) & 1;
-        if (!mbar_wait_bounded(&full[st], ph, abort_flag, OXB_TIMEOUT_TMA_FULL, blockIdx.x)) break;
+        if (!OXB_TR_WAIT(tr_w0, mbar_wait_bounded(&full[st], ph, abort_flag, OXB_TIMEOUT_TMA_FULL, blockIdx.x))) break;
         tc_fence_after();
         const uint32_t a_addr = smem_u32(smem + st * Cfg::STAGE_BYTES);
         const uint64_t adesc = umma_desc_k_sw128(a_addr);
         const uint64_t bdesc = umma_desc_k_sw128(a_addr + Cfg::A_BYTES);
+        {
+          OXB_TR_BEGIN
 #pragma unroll
-        for (int k = 0; k < GEMM_BK / 16; ++k) {
-          // advance 16 bf16 = 32 bytes inside the swizzle row: +2 in the (addr >> 4) field
-          umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < GEMM_BK / 16; ++k) {
+            // advance 16 bf16 = 32 bytes inside the swizzle row: +2 in the (addr >> 4) field
+            umma_bf16(tmem_base + (k % Cfg::NACC) * Cfg::ACC_COLS, adesc + 2 * k, bdesc + 2 * k, idesc,
+                      (i > 0 || k >= Cfg::NACC) ? 1u : 0u);
+          }
+          OXB_TR_END(tr_w1)
         }
-        umma_commit(&empty[st]);  // frees the stage when these MMAs have read it
+        {
+          OXB_TR_BEGIN
+          umma_commit(&empty[st]);  // frees the stage when these MMAs have read it
+          OXB_TR_END(tr_w2)
+        }
       }
       umma_commit(accum);
+      OXB_TR_STORE(1)
     }
+  }
     __syncwarp();
     if (csplit) {
       cluster_sync_all();
       cluster_sync_all();
     }
-  } else if (warp >= 6) {
-    // ---------------- dequant producers (MMQ only): two groups of 128 threads; in each, thread r stages weight row
+  } else if (warp >= GEMM_WARP_PRODUCER0) {
+    if constexpr (MMQ) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(MMQ_REGS_PRODUCER));
+    // ---------------- dequant producers (MMQ only): MMQ_GROUPS groups of 128 threads; in each, thread r stages weight row
     // n0 + r.  The groups take alternate k-blocks (each stage's barrier expects the four warps of ONE group), so
     // twice as many warps share the decode arithmetic of a tile and the ring is fed by two decoders at once.
     if constexpr (MMQ) {
-      const int grp = (threadIdx.x - 192) >> 7;
-      const int r = (threadIdx.x - 192) & 127;
+      OXB_TR_DECL
+      const int grp = (threadIdx.x - 32 * GEMM_WARP_PRODUCER0) >> 7;
+      const int r = (threadIdx.x - 32 * GEMM_WARP_PRODUCER0) & 127;
       const int n = n0 + r;
       const uint8_t* rowp = qw.w + ((size_t)zg * gr.w_rows + (size_t)(n < N ? n : 0)) * qw.row_bytes;
-      // Each thread walks its own packed row.  Two k-blocks are decoded per iteration, and both are
-      // decoded into registers BEFORE the thread waits for their ring slots: the global loads of
-      // the two blocks overlap each other and the tensor core's work on the slots still in use
-      // (waiting first and loading afterwards leaves every k-block with a cold, dependent load).
-      // Straight-line on purpose: no branch between the two decodes, so that the compiler can issue the
-      // loads of both k-blocks before the arithmetic of the first (addresses are clamped to valid
-      // blocks; out-of-range results are zeroed afterwards).
+      // Fallback when the packed rows cannot be mapped for TMA (rows or base not 16-byte multiples, K not a multiple
+      // of 256): each thread walks its own packed row in global memory.  Addresses are clamped to valid blocks;
+      // out-of-range results are zeroed afterwards.
       const int kb_last = (K / GEMM_BK) - 1;
       auto decode = [&](int kb, uint32_t* v) {
         const int kbc = kb < kb_last ? kb : kb_last;
@@ -530,11 +611,36 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         const int st = i % STAGES;
         const uint32_t ph = (i / STAGES) & 1;
         // warp-uniform verdict: the warp-level synchronisation below must be reached by all 32 lanes or none
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&empty[st], ph ^ 1, abort_flag, OXB_TIMEOUT_TMA_EMPTY, blockIdx.x)))
+        if (!OXB_TR_WAIT(tr_w0, __all_sync(0xffffffffu, mbar_wait_bounded(&empty[st], ph ^ 1, abort_flag, OXB_TIMEOUT_TMA_EMPTY, blockIdx.x))))
           return false;
         store_row_sw128(smem + st * Cfg::STAGE_BYTES, r, v);
         fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
         __syncwarp();              // the warp's 32 rows are written: one arrival per warp instead of 32
+        if (lane == 0) mbar_arrive(&full[st]);
+        return true;
+      };
+      // staged form: wait for the ring slot first, then decode the row out of shared memory straight into it
+      auto publish_from = [&](int i, const uint8_t* srow, int kb) -> bool {
+        const int st = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        if (!OXB_TR_WAIT(tr_w0, __all_sync(0xffffffffu, mbar_wait_bounded(&empty[st], ph ^ 1, abort_flag, OXB_TIMEOUT_TMA_EMPTY, blockIdx.x))))
+          return false;
+        uint8_t* tile = smem + st * Cfg::STAGE_BYTES;
+        {
+        OXB_TR_BEGIN
+        if (n < N) {
+          if constexpr (QT == QT_FP8B)  // scales are indexed by the absolute row and channel
+            dequant64_to_tile<QT>(srow - (size_t)(kb & ~3) * GEMM_BK, kb * GEMM_BK, qw, n, tile, r);
+          else
+            dequant64_to_tile<QT>(srow, (kb & 3) * GEMM_BK, qw, 0, tile, r);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) store_chunk_sw128(tile, r, c, 0u, 0u, 0u, 0u);
+        }
+        OXB_TR_END(tr_w2)
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
         if (lane == 0) mbar_arrive(&full[st]);
         return true;
       };
@@ -550,7 +656,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         auto issue = [&](int j) {  // j-th super-block of this CTA -> box j % PRING
           const int b = j % PRING;
           mbar_expect_tx(&packed_full[b], PBYTES);
-          tma_load_2d(packed_buf + b * PBYTES, &tmW, &packed_full[b], ((sb_begin + j) * SB) & ~15, w_row0);
+          tma_load_2d(packed_buf + b * PBYTES, &tmW, &packed_full[b], (((sb_begin + j) * SB) & ~15) >> 2, w_row0);
         };
         const int nsb = sb_end - sb_begin;
         const bool issuer = r == 0 && grp == 0;
@@ -563,21 +669,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           const int b = j % PRING;
           // the box of super-block j - 1 is refilled as soon as every warp has let go of it
           if (issuer && alive && j >= 1 && j - 1 + PRING < nsb) {
-            if (mbar_wait_bounded(&packed_empty[(j - 1) % PRING], ((j - 1) / PRING) & 1, abort_flag, OXB_TIMEOUT_TMA_EMPTY,
-                                  blockIdx.x))
+            if (OXB_TR_WAIT(tr_w1, mbar_wait_bounded(&packed_empty[(j - 1) % PRING], ((j - 1) / PRING) & 1, abort_flag,
+                                                     OXB_TIMEOUT_TMA_EMPTY, blockIdx.x)))
               issue(j - 1 + PRING);
           }
           if (alive)
-            alive = __all_sync(0xffffffffu, mbar_wait_bounded(&packed_full[b], (j / PRING) & 1, abort_flag,
-                                                              OXB_TIMEOUT_TMA_FULL, blockIdx.x));
+            alive = OXB_TR_WAIT(tr_w1, __all_sync(0xffffffffu, mbar_wait_bounded(&packed_full[b], (j / PRING) & 1, abort_flag,
+                                                                                 OXB_TIMEOUT_TMA_FULL, blockIdx.x)));
           if (alive) {
             const uint8_t* srow = packed_buf + b * PBYTES + r * BOX + (((sb_begin + j) * SB) & 15);
             const int kb0 = max(kb_begin, (sb_begin + j) * 4), kb1 = min(kb_end, (sb_begin + j) * 4 + 4);
             for (int kb = kb0; kb < kb1 && alive; ++kb) {
-              if (((kb - kb_begin) & 1) != grp) continue;  // the other group's k-block
-              uint32_t v[32];
-              dequant64<QT>(srow, (kb & 3) * GEMM_BK, qw, 0, v);  // rows past N were zero-filled by the TMA
-              alive = publish(kb - kb_begin, v);
+              if ((kb - kb_begin) % MMQ_GROUPS != grp) continue;  // another group's k-block
+              alive = publish_from(kb - kb_begin, srow, kb);
             }
           }
           __syncwarp();  // the warp's reads of the box are done (alive or not, so that the issuer never waits in vain)
@@ -585,18 +689,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         }
       }
       if (!staged_done) {
-        // group g takes k-blocks g, g + 2, g + 4, ...; two of them are decoded per iteration
-        for (int i = grp; i < nkb; i += 4) {
-          uint32_t v0[32], v1[32];
-          const bool two = i + 2 < nkb;
+        // group g takes k-blocks g, g + MMQ_GROUPS, ...; a block is decoded into registers BEFORE the thread waits for
+        // its ring slot, so that the global loads overlap the tensor core's work on the slots still in use
+        for (int i = grp; i < nkb; i += MMQ_GROUPS) {
+          uint32_t v0[32];
           decode(kb_begin + i, v0);
-          decode(kb_begin + i + 2, v1);
           mask(kb_begin + i, v0);
-          mask(kb_begin + i + 2, v1);
           if (!publish(i, v0)) break;
-          if (two && !publish(i + 2, v1)) break;
         }
       }
+      if (r == 0) { OXB_TR_STORE(2 + grp) }
     }
     __syncwarp();
     if (csplit) {
@@ -604,11 +706,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       cluster_sync_all();
     }
   } else {
-    // ---------------- epilogue: warps 2..5 own TMEM lane quarters (warp % 4)
+    if constexpr (MMQ) {
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(MMQ_REGS_EPILOGUE));
+      pdl_launch_dependents();
+    }
+    // ---------------- epilogue: warps 0..3 own TMEM lane quarters (warp % 4)
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;  // row inside the 128-row tile
     const int n = n0 + row;
-    const int etid = threadIdx.x - 64;
+    const int etid = threadIdx.x;
     pdl_wait();  // everything below reads or writes global memory shared with the upstream kernel
     const bool use_nm = nm.sumsq_in != nullptr;
     if (use_nm) {
@@ -627,7 +733,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     mbar_wait_bounded(accum, 0, abort_flag, OXB_TIMEOUT_ACCUM, blockIdx.x);
     // agree on one verdict for all 128 epilogue threads before any further named barrier
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (threadIdx.x == 64) {
+    if (threadIdx.x == 0) {
       ticket[1] = (*abort_flag == 0);
       ticket[2] = ar.world > 0 ? ar.ctrl[0] : 0;  // call counter of this collective (buffer parity, epoch)
     }
@@ -649,8 +755,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 #pragma unroll 1
         for (int c = 0; c < TN / 16; ++c) {
           uint32_t r[16];
-          tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
-          tmem_ld_wait();
+          tmem_ld16_acc<Cfg::NACC, Cfg::ACC_COLS>(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const float sc = use_nm ? tok_scale[c * 16 + j] : 1.f;
@@ -671,8 +776,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 #pragma unroll 1
         for (int c = 0; c < TN / 16; ++c) {
           uint32_t r[16];
-          tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
-          tmem_ld_wait();
+          tmem_ld16_acc<Cfg::NACC, Cfg::ACC_COLS>(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
           if (n < N) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -697,8 +801,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 #pragma unroll 1
         for (int c = 0; c < TN / 16; ++c) {
           uint32_t r[16];
-          tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
-          tmem_ld_wait();
+          tmem_ld16_acc<Cfg::NACC, Cfg::ACC_COLS>(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
 #pragma unroll
           for (int j = 0; j < 16; ++j) part[(c * 16 + j) * GEMM_BM + row] = __uint_as_float(r[j]);
         }
@@ -751,8 +854,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 #pragma unroll 1
       for (int c = 0; c < TN / 16; ++c) {
         uint32_t r[16];
-        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
-        tmem_ld_wait();
+        tmem_ld16_acc<Cfg::NACC, Cfg::ACC_COLS>(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
 #pragma unroll
         for (int j = 0; j < 16; ++j) my[(c * 16 + j) * GEMM_BM + row] = __uint_as_float(r[j]);
       }
@@ -762,7 +864,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       // they meet at an arrive counter and then each reduces its own slice of the tile's tokens:
       // the reduction is spread over the CTAs instead of serialised in the last one to arrive.
       int* cnt = counters + 2 * tile_id;  // [arrive, depart]
-      if (threadIdx.x == 64) {
+      if (threadIdx.x == 0) {
         atomicAdd(&cnt[0], 1);
         bool met = false;
         for (unsigned it = 0; it < 20000000u; ++it) {
@@ -810,7 +912,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             ar_exchange(ar, smem, ticket[2], tile_id * splits + split, n0, t0 + jb, je - jb, N, Y, ldY, abort_flag, etid, ssq_dst);
         }
         // the last CTA to leave re-arms the counters for the next launch / graph replay
-        if (threadIdx.x == 64) {
+        if (threadIdx.x == 0) {
           if (atomicAdd(&cnt[1], 1) == splits - 1) {
             cnt[1] = 0;
             cnt[0] = 0;
@@ -818,7 +920,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         }
       }
     }
-    if (use_ar && threadIdx.x == 64) {
+    if (use_ar && threadIdx.x == 0) {
       // the last CTA of the grid advances the call counter (flips the buffer parity)
       __threadfence();
       const int done = atomicAdd(&ar.ctrl[1], 1);
@@ -836,7 +938,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  if (warp == GEMM_WARP_MMA) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
 struct GemmPlan {
@@ -849,12 +951,14 @@ struct GemmPlan {
 extern int g_oxb_cluster_splitk;  // 1 = split-K through clusters / distributed shared memory (default)
 extern int g_oxb_gemm_prefill_tn;  // 0 = pick the token tile of prefill-sized calls by wave count, 128 / 256 = force
 
-// cluster_ok < 0: follow g_oxb_cluster_splitk.  max_ctas > 0 bounds tiles*splits (kernels whose CTAs wait
+// max_tn caps the token tile.  cluster_ok < 0: follow g_oxb_cluster_splitk.  max_ctas > 0 bounds tiles*splits (kernels whose CTAs wait
 // for CTAs of other GPUs must be resident all at once).
-inline GemmPlan gemm_plan(int T, int N, int K, int splits_hint, int sm_count, int cluster_ok = -1, int max_ctas = 0) {
+inline GemmPlan gemm_plan(int T, int N, int K, int splits_hint, int sm_count, int cluster_ok = -1, int max_ctas = 0,
+                          int max_tn = 256) {
   GemmPlan p;
   if (cluster_ok < 0) cluster_ok = g_oxb_cluster_splitk;
   p.tn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+  if (p.tn > max_tn) p.tn = max_tn;  // packed weights: 128-token tiles at most (their ring of packed boxes needs the room)
   p.n_tiles = (N + GEMM_BM - 1) / GEMM_BM;
   if (T > 256 && sm_count > 0) {
     // Prefill-sized calls run one CTA per SM in waves; a nearly empty last wave costs a whole tile time.
@@ -949,6 +1053,15 @@ int gemm_launch(const CUtensorMap& tmW, const CUtensorMap& tmX, __nv_bfloat16* Y
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<TN, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          gemm_smem_bytes<TN, QT>());
     if (e != cudaSuccess) return (int)e;
+    if (QT != QT_BF16) {
+      // The packed-weight kernel moves registers between its warpgroups; the three budgets add up to what the launch
+      // allocates only if the kernel was compiled for exactly MMQ_REGS_LAUNCH registers per thread.  A request for
+      // more than the CTA owns would never be granted, so refuse to launch anything else.
+      cudaFuncAttributes fa;
+      e = cudaFuncGetAttributes(&fa, gemm_bf16_kernel<TN, QT>);
+      if (e != cudaSuccess) return (int)e;
+      if (fa.numRegs != MMQ_REGS_LAUNCH) return (int)cudaErrorInvalidConfiguration;
+    }
     configured[dev] = true;
   }
   int splits = p.splits;
@@ -985,8 +1098,8 @@ int gemm_launch_mmq(const CUtensorMap& tmX, __nv_bfloat16* Y, const float* bias,
     case 16: return gemm_launch<16, QT>(tmW, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
     case 32: return gemm_launch<32, QT>(tmW, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
     case 64: return gemm_launch<64, QT>(tmW, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
-    case 128: return gemm_launch<128, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
-    default: return gemm_launch<256, QT>(tmX, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
+    case 128: return gemm_launch<128, QT>(tmW, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
+    default: return (int)cudaErrorInvalidConfiguration;  // packed weights are planned with max_tn = 128
   }
 }
 

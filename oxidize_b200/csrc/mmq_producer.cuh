@@ -197,6 +197,137 @@ __device__ __forceinline__ void store_row_sw128(uint8_t* tile, int r, const uint
   }
 }
 
+// 16-byte chunk c of row r of the 128B-swizzled tile
+__device__ __forceinline__ void store_chunk_sw128(uint8_t* tile, int r, int c, uint32_t a, uint32_t b, uint32_t cc, uint32_t d) {
+  *reinterpret_cast<uint4*>(tile + r * 128 + ((c ^ (r & 7)) << 4)) = make_uint4(a, b, cc, d);
+}
+
+// 32-bit words at a 2-byte-aligned shared-memory address: N + 1 aligned words, funnel-shifted into place
+template <int N>
+__device__ __forceinline__ void ld_words_align2(const uint8_t* p, uint32_t* out) {
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(reinterpret_cast<uintptr_t>(p) & ~uintptr_t(3));
+  const uint32_t sh = (uint32_t)(reinterpret_cast<uintptr_t>(p) & 2) * 8;
+  uint32_t a[N + 1];
+#pragma unroll
+  for (int i = 0; i <= N; ++i) a[i] = w[i];
+#pragma unroll
+  for (int i = 0; i < N; ++i) out[i] = __funnelshift_r(a[i], a[i + 1], sh);
+}
+
+__device__ __forceinline__ uint32_t bf16x2_bits(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
+__device__ __forceinline__ __nv_bfloat162 bits_bf16x2(uint32_t u) { return *reinterpret_cast<__nv_bfloat162*>(&u); }
+
+// Decode values [k0, k0+64) of the row at `rowp` (shared memory; Q6_K / Q8_0 / Q4_0 rows may start at any even
+// byte) straight into row r of the swizzled tile, 16 bytes at a time: nothing but the chunk in hand lives in
+// registers, so many producer warps fit on an SM.  The integer codes become bf16 through the mantissa of a
+// power of two (0x4300 | q is the bf16 number 128 + q for q < 128): no integer-to-float conversions.
+template <int QT>
+__device__ __forceinline__ void dequant64_to_tile(const uint8_t* rowp, int k0, const QwArgs& qw, int n, uint8_t* tile, int r) {
+  if constexpr (QT == QT_Q4_K) {
+    const uint8_t* b = rowp + (size_t)(k0 >> 8) * 144;  // 16-byte aligned
+    const int c = (k0 & 255) >> 6;
+    const uint4 hdr = *reinterpret_cast<const uint4*>(b);  // d, dmin, 12 bytes of 6-bit scales and minima
+    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFF)));
+    const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+    // sub-blocks 2c and 2c + 1 (c is the same for the whole warp)
+    uint32_t sc2, m2;  // two scales / minima, one per byte
+    if (c < 2) {
+      sc2 = (hdr.y >> (16 * c)) & 0x3F3F;
+      m2 = (hdr.z >> (16 * c)) & 0x3F3F;
+    } else {
+      const uint32_t lo = (hdr.w >> (16 * (c - 2))) & 0xFFFF;  // low nibble: scale, high nibble: minimum
+      sc2 = (lo & 0x0F0F) | (((hdr.y >> (16 * (c - 2))) & 0xC0C0) >> 2);
+      m2 = ((lo >> 4) & 0x0F0F) | (((hdr.z >> (16 * (c - 2))) & 0xC0C0) >> 2);
+    }
+    const float s0 = d * (float)(sc2 & 0xFF), s1 = d * (float)(sc2 >> 8);
+    const float o0 = dmin * (float)(m2 & 0xFF), o1 = dmin * (float)(m2 >> 8);
+    const __nv_bfloat162 k128 = __floats2bfloat162_rn(128.f, 128.f);
+    const __nv_bfloat162 s0b = __floats2bfloat162_rn(s0, s0), s1b = __floats2bfloat162_rn(s1, s1);
+    const __nv_bfloat162 n0b = __floats2bfloat162_rn(-o0, -o0), n1b = __floats2bfloat162_rn(-o1, -o1);
+    auto dq = [&](uint32_t nib4, uint32_t sel, const __nv_bfloat162 sc, const __nv_bfloat162 off) {
+      return bf16x2_bits(__hfma2(__hsub2(bits_bf16x2(__byte_perm(nib4, 0x43434343u, sel)), k128), sc, off));
+    };
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {  // 16 bytes of codes: values 16h .. 16h+15 (low nibbles) and 32 + 16h .. (high nibbles)
+      const uint4 q = *reinterpret_cast<const uint4*>(b + 16 + 32 * c + 16 * h);
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const uint32_t lo0 = w[2 * j] & 0x0F0F0F0Fu, lo1 = w[2 * j + 1] & 0x0F0F0F0Fu;
+        const uint32_t hi0 = (w[2 * j] >> 4) & 0x0F0F0F0Fu, hi1 = (w[2 * j + 1] >> 4) & 0x0F0F0F0Fu;
+        store_chunk_sw128(tile, r, 2 * h + j, dq(lo0, 0x4140, s0b, n0b), dq(lo0, 0x4342, s0b, n0b), dq(lo1, 0x4140, s0b, n0b),
+                          dq(lo1, 0x4342, s0b, n0b));
+        store_chunk_sw128(tile, r, 4 + 2 * h + j, dq(hi0, 0x4140, s1b, n1b), dq(hi0, 0x4342, s1b, n1b),
+                          dq(hi1, 0x4140, s1b, n1b), dq(hi1, 0x4342, s1b, n1b));
+      }
+    }
+  } else if constexpr (QT == QT_Q6_K) {
+    const uint8_t* b = rowp + (size_t)(k0 >> 8) * 210;  // 2-byte aligned
+    const int c = (k0 & 255) >> 6, half = c >> 1, hi_nib = c & 1;
+    uint32_t qh[8], scw[1];
+    ld_words_align2<8>(b + 128 + half * 32, qh);
+    ld_words_align2<1>(b + 192 + half * 8 + 4 * hi_nib, scw);  // the four int8 scales of this k-block
+    const float d = __half2float(__ushort_as_half((unsigned short)ld_u16(b + 208)));
+    const __nv_bfloat162 k160 = __floats2bfloat162_rn(160.f, 160.f);  // 128 (mantissa trick) + 32 (code offset)
+    __nv_bfloat162 scb[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float f = d * (float)(int8_t)((scw[0] >> (8 * i)) & 0xFF);
+      scb[i] = __floats2bfloat162_rn(f, f);
+    }
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {  // quarter kq = 2*hi_nib + s: 32 values
+      uint32_t ql[8];
+      ld_words_align2<8>(b + half * 64 + s * 32, ql);
+      const int kq = 2 * hi_nib + s;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {  // 8 values per chunk
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int l4 = 2 * j + e;
+          const uint32_t lo4 = (ql[l4] >> (4 * hi_nib)) & 0x0F0F0F0Fu;
+          const uint32_t h2 = ((qh[l4] >> (2 * kq)) & 0x03030303u) << 4;
+          const uint32_t code = lo4 | h2;
+          const __nv_bfloat162 sc = scb[2 * s + (l4 >> 2)];
+          o[2 * e] = bf16x2_bits(__hmul2(__hsub2(bits_bf16x2(__byte_perm(code, 0x43434343u, 0x4140)), k160), sc));
+          o[2 * e + 1] = bf16x2_bits(__hmul2(__hsub2(bits_bf16x2(__byte_perm(code, 0x43434343u, 0x4342)), k160), sc));
+        }
+        store_chunk_sw128(tile, r, 4 * s + j, o[0], o[1], o[2], o[3]);
+      }
+    }
+  } else if constexpr (QT == QT_Q8_0) {
+    // two 34-byte blocks (fp16 scale + 32 int8 codes), 2-byte aligned.  A code q in [-127, 127]: t = q & 0x7F is
+    // q for q >= 0 and q + 128 otherwise, so q = (128 + t) - (128 or 256); both terms are exact bf16 numbers.
+    const uint8_t* b = rowp + (size_t)(k0 >> 6) * 68;
+#pragma unroll
+    for (int blk = 0; blk < 2; ++blk) {
+      const float d = __half2float(__ushort_as_half((unsigned short)ld_u16(b + 34 * blk)));
+      const __nv_bfloat162 db = __floats2bfloat162_rn(d, d);
+      uint32_t q[8];
+      ld_words_align2<8>(b + 34 * blk + 2, q);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const uint32_t x = q[2 * j + e];
+          const uint32_t t = x & 0x7F7F7F7Fu, neg = x & 0x80808080u;  // neg byte 0x80 -> subtract 256 (0x4380), else 128 (0x4300)
+          o[2 * e] = bf16x2_bits(__hmul2(__hsub2(bits_bf16x2(__byte_perm(t, 0x43434343u, 0x4140)),
+                                                bits_bf16x2(__byte_perm(neg, 0x43434343u, 0x4140))), db));
+          o[2 * e + 1] = bf16x2_bits(__hmul2(__hsub2(bits_bf16x2(__byte_perm(t, 0x43434343u, 0x4342)),
+                                                    bits_bf16x2(__byte_perm(neg, 0x43434343u, 0x4342))), db));
+        }
+        store_chunk_sw128(tile, r, 4 * blk + j, o[0], o[1], o[2], o[3]);
+      }
+    }
+  } else {
+    uint32_t v[32];
+    dequant64<QT>(rowp, k0, qw, n, v);
+    store_row_sw128(tile, r, v);
+  }
+}
+
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 }  // namespace oxb

@@ -1,7 +1,7 @@
 // liboxb: the sm_100a kernel library of oxidize_b200, exported with a plain C ABI
 // (loaded from Python with ctypes; every launcher takes raw device pointers and a stream and
-// returns a cudaError_t code, 0 on success).  The library is several translation units compiled as
-// relocatable device code and linked into one shared object (oxb.cu: globals, host utilities and the
+// returns a cudaError_t code, 0 on success).  The library is several independently compiled translation units
+// linked into one shared object (oxb.cu: globals, host utilities and the
 // small kernels; oxb_gemm.cu: the tcgen05 GEMM entry points; oxb_mmq_*.cu: one packed-weight format each;
 // oxb_gemv.cu; oxb_attn.cu), so that a rebuild takes the time of the slowest unit.
 #include "common.cuh"
@@ -14,8 +14,15 @@
 #include <string.h>
 using namespace oxb;
 
-// the one device status word of the library (declared in common.cuh)
-__device__ int g_oxb_status[4];
+// readers of every translation unit's copy of the device status word (see common.cuh)
+static OxbStatusUnit*& status_units() {
+  static OxbStatusUnit* head = nullptr;
+  return head;
+}
+void oxb_register_status_unit(OxbStatusUnit* u) {
+  u->next = status_units();
+  status_units() = u;
+}
 
 int g_oxb_pdl = 1;
 int oxb::g_oxb_cluster_splitk = 1;
@@ -106,15 +113,16 @@ int oxb_make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t
 // Byte view of packed weight rows for the staged MMQ path: [rows, row_bytes] uint8, no swizzle.
 int oxb_make_tmap_bytes(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
                         uint32_t box_bytes) {
+  // 32-bit elements: a box may then be up to 1 KB wide (256 elements); coordinates are in words
   PFN_encodeTiled enc = oxb_get_encode_tiled();
   if (enc == nullptr) return (int)cudaErrorNotSupported;
-  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (row_bytes & 15) != 0 || (box_bytes & 15) != 0 || box_bytes > 256)
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (row_bytes & 15) != 0 || (box_bytes & 15) != 0 || box_bytes > 1024)
     return (int)cudaErrorInvalidValue;
-  cuuint64_t dims[2] = {row_bytes, rows};
+  cuuint64_t dims[2] = {row_bytes / 4, rows};
   cuuint64_t strides[1] = {row_bytes};
-  cuuint32_t box[2] = {box_bytes, box_rows};
+  cuuint32_t box[2] = {box_bytes / 4, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
@@ -139,13 +147,18 @@ OXB_API int oxb_version() { return 100; }
 
 // Copy the device status word {code, detail, count, _} to the host (synchronises the device).
 OXB_API int oxb_status(int* out4, int reset) {
-  cudaError_t e = cudaMemcpyFromSymbol(out4, g_oxb_status, 4 * sizeof(int));
-  if (e != cudaSuccess) return (int)e;
-  if (reset) {
-    int z[4] = {0, 0, 0, 0};
-    e = cudaMemcpyToSymbol(g_oxb_status, z, sizeof(z));
+  out4[0] = out4[1] = out4[2] = out4[3] = 0;
+  for (OxbStatusUnit* u = status_units(); u != nullptr; u = u->next) {
+    int s[4] = {0, 0, 0, 0};
+    const int e = u->read(s, reset);
+    if (e != 0) return e;
+    if (out4[0] == 0 && s[0] != 0) {
+      out4[0] = s[0];
+      out4[1] = s[1];
+    }
+    out4[2] += s[2];
   }
-  return (int)e;
+  return 0;
 }
 
 // One-shot all-reduce (sum) of X[T, N] bf16 (row stride ld) into Y through the same symmetric buffers.

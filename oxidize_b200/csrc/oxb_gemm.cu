@@ -90,6 +90,30 @@ OXB_API int oxb_gemm_bf16_norm(const void* X, const void* W, void* Y, const floa
                         make_norm(sumsq_in, norm_dim, eps, clear, sumsq_out));
 }
 
+// Launch the packed-weight GEMM of the given format.  The packed rows are read through a TMA byte map (rows and base
+// must be 16-byte multiples and K a multiple of 256; otherwise the producers read global memory themselves).
+static int launch_mmq(int qtype, const void* W, uint64_t w_rows, const CUtensorMap& tmX, __nv_bfloat16* y, const float* bias,
+                      int N, int T, int K, int ldY, const GemmPlan& p, float* wsf, int* counters, int epi_mode, const ArArgs& ar,
+                      cudaStream_t stream, QwArgs qw, const GroupArgs& gr, int groups) {
+  CUtensorMap tmWq;
+  if (K % 256 == 0 &&
+      oxb_make_tmap_bytes(&tmWq, W, w_rows, qw.row_bytes, GEMM_BM, (uint32_t)mmq_box_bytes(qtype)) == 0)
+    qw.staged = 1;
+  const CUtensorMap* tw = qw.staged ? &tmWq : nullptr;
+  switch (qtype) {
+    case QT_Q4_K: return gemm_mmq_q4_k(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw, gr, groups, tw);
+    case QT_Q6_K: return gemm_mmq_q6_k(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw, gr, groups, tw);
+    case QT_Q8_0: return gemm_mmq_q8_0(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw, gr, groups, tw);
+    case QT_Q4_0: return gemm_mmq_q4_0(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw, gr, groups, tw);
+    case QT_NVFP4: return gemm_mmq_nvfp4(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw, gr, groups, tw);
+    case QT_FP8B:
+      if (qw.scales == nullptr) return (int)cudaErrorInvalidValue;
+      return gemm_mmq_fp8b(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw, gr, groups, tw);
+    default: return (int)cudaErrorInvalidValue;
+  }
+}
+
+
 // Y[T, N] = X[T, K] (bf16) · dequant(Wq)[N, K]^T for packed weights (qtype as in quant_blocks.cuh, or
 // 9 = block-scaled fp8 with `scales` [N, scale_ld]).  The blocks are decoded inside the GEMM by its
 // producer warps; nothing is dequantized to global memory.  K must be a multiple of 64.
@@ -103,10 +127,10 @@ OXB_API int oxb_gemm_quant(const void* X, const void* Wq, int qtype, size_t row_
     return gemv_quant_run(qtype, reinterpret_cast<const uint8_t*>(Wq), row_bytes, reinterpret_cast<const __nv_bfloat16*>(X), K,
                       reinterpret_cast<__nv_bfloat16*>(Y), ldY, bias, T, N, K, epi_mode == EPI_ADD_INTO, sm_count(), stream);
   if (K % 64 != 0) return (int)cudaErrorInvalidValue;
-  GemmPlan p = gemm_plan(T, N, K, splits_hint, sm_count());
+  GemmPlan p = gemm_plan(T, N, K, splits_hint, sm_count(), -1, 0, 128);
   while (p.splits > 1 && !p.cluster && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || ws == nullptr || counters == nullptr ||
                           p.n_tiles * p.t_tiles * p.splits > sm_count()))
-    p = gemm_plan(T, N, K, p.splits - 1, sm_count());
+    p = gemm_plan(T, N, K, p.splits - 1, sm_count(), -1, 0, 128);
   CUtensorMap tmX;
   int e = oxb_make_tmap_2d(&tmX, X, T, K, (uint64_t)K * 2, p.tn, GEMM_BK, 2);
   if (e) return e;
@@ -115,28 +139,8 @@ OXB_API int oxb_gemm_quant(const void* X, const void* Wq, int qtype, size_t row_
   ArArgs ar;
   memset(&ar, 0, sizeof(ar));
   QwArgs qw{reinterpret_cast<const uint8_t*>(Wq), row_bytes, scales, scale_ld, 0};
-  switch (qtype) {
-    case QT_Q4_K:
-    case QT_Q6_K: {
-      // staged path (packed super-blocks by TMA) when the byte map can be built: 16-byte rows and base
-      CUtensorMap tmWq;
-      const int box = qtype == QT_Q4_K ? MmqStage<QT_Q4_K>::BOX : MmqStage<QT_Q6_K>::BOX;
-      if (p.tn <= 64 && oxb_make_tmap_bytes(&tmWq, Wq, (uint64_t)N, row_bytes, GEMM_BM, box) == 0) qw.staged = 1;
-      const GroupArgs g0{0, 0, 0, 0, nullptr, 0, 0, nullptr, 1};
-      if (qtype == QT_Q4_K)
-        return gemm_mmq_q4_k(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw, g0, 1,
-                                        qw.staged ? &tmWq : nullptr);
-      return gemm_mmq_q6_k(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw, g0, 1,
-                                      qw.staged ? &tmWq : nullptr);
-    }
-    case QT_Q8_0: return gemm_mmq_q8_0(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
-    case QT_Q4_0: return gemm_mmq_q4_0(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
-    case QT_NVFP4: return gemm_mmq_nvfp4(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
-    case QT_FP8B:
-      if (scales == nullptr) return (int)cudaErrorInvalidValue;
-      return gemm_mmq_fp8b(tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw);
-    default: return (int)cudaErrorInvalidValue;
-  }
+  const GroupArgs g0{0, 0, 0, 0, nullptr, 0, 0, nullptr, 1};
+  return launch_mmq(qtype, Wq, (uint64_t)N, tmX, y, bias, N, T, K, ldY, p, wsf, counters, epi_mode, ar, stream, qw, g0, 1);
 }
 
 // Row-parallel GEMM fused with a one-shot all-reduce over peer memory:
@@ -327,16 +331,17 @@ extern "C" __attribute__((visibility("default"))) int oxb_gemm_bf16_noalloc(
 //   Y[g] [T, N] = X_g [T, K] · W_g [N, K]^T,   W stacked as [(groups*N), K] (bf16 or packed rows),
 //   X_g = X + g*x_rows rows (x_rows = 0: every group reads the same X),  Y[g] = Y + g*y_stride elements.
 // Groups whose `scale` row (per-token routing weights, [groups, scale_ld]) is all zero are skipped on the
-// device.  T <= 256.
+// device.  T <= 256 (bf16 weights) or 128 (packed weights).
 OXB_API int oxb_gemm_grouped(const void* X, int x_rows, const void* W, int qtype, size_t row_bytes, void* Y,
                              long long y_stride, const float* scale, int scale_ld, int groups, int T, int N, int K,
                              int ldY, void* ws, size_t ws_bytes, int* counters, int n_counters, cudaStream_t stream) {
   if (T <= 0 || N <= 0 || K <= 0 || groups <= 0) return 0;
-  if (T > 256 || K % 64 != 0) return (int)cudaErrorInvalidValue;
-  GemmPlan p = gemm_plan(T, N, K, 0, sm_count());
+  const int max_tn = qtype == QT_BF16 ? 256 : 128;  // one token tile per group
+  if (T > max_tn || K % 64 != 0) return (int)cudaErrorInvalidValue;
+  GemmPlan p = gemm_plan(T, N, K, 0, sm_count(), -1, 0, max_tn);
   while (p.splits > 1 && !p.cluster && (p.ws_bytes * groups > ws_bytes || p.n_counters * groups > n_counters || ws == nullptr ||
                           counters == nullptr || p.n_tiles * p.splits * groups > sm_count()))
-    p = gemm_plan(T, N, K, p.splits - 1, sm_count());
+    p = gemm_plan(T, N, K, p.splits - 1, sm_count(), -1, 0, max_tn);
   CUtensorMap tmW, tmX;
   const uint64_t xr = x_rows > 0 ? (uint64_t)groups * x_rows : (uint64_t)T;
   int e = oxb_make_tmap_2d(&tmX, X, xr, K, (uint64_t)K * 2, p.tn, GEMM_BK, 2);
@@ -358,23 +363,8 @@ OXB_API int oxb_gemm_grouped(const void* X, int x_rows, const void* W, int qtype
       default: return gemm_launch<256>(tmW, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
     }
   }
-  switch (qtype) {
-    case QT_Q4_K:
-    case QT_Q6_K: {
-      CUtensorMap tmWq;
-      const int box = qtype == QT_Q4_K ? MmqStage<QT_Q4_K>::BOX : MmqStage<QT_Q6_K>::BOX;
-      if (p.tn <= 64 && oxb_make_tmap_bytes(&tmWq, W, (uint64_t)groups * N, row_bytes, GEMM_BM, box) == 0) qw.staged = 1;
-      if (qtype == QT_Q4_K)
-        return gemm_mmq_q4_k(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups,
-                                        qw.staged ? &tmWq : nullptr);
-      return gemm_mmq_q6_k(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups,
-                                      qw.staged ? &tmWq : nullptr);
-    }
-    case QT_Q8_0: return gemm_mmq_q8_0(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
-    case QT_Q4_0: return gemm_mmq_q4_0(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
-    case QT_NVFP4: return gemm_mmq_nvfp4(tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
-    default: return (int)cudaErrorInvalidValue;
-  }
+  if (qtype == QT_FP8B) return (int)cudaErrorInvalidValue;
+  return launch_mmq(qtype, W, (uint64_t)groups * N, tmX, y, nullptr, N, T, K, ldY, p, wsf, counters, 0, ar, stream, qw, gr, groups);
 }
 
 
@@ -388,8 +378,9 @@ OXB_API int oxb_gemm_grouped_rows(const void* X, int rows_cap, const void* W, in
                                   cudaStream_t stream) {
   if (rows_cap <= 0 || max_rows <= 0 || N <= 0 || K <= 0 || groups <= 0) return 0;
   if (K % 64 != 0 || row_offsets == nullptr) return (int)cudaErrorInvalidValue;
-  GemmPlan p = gemm_plan(max_rows, N, K, 0, sm_count(), 1);
-  if (p.splits > 1 && !p.cluster) p = gemm_plan(max_rows, N, K, 1, sm_count(), 1);
+  const int max_tn = qtype == QT_BF16 ? 256 : 128;
+  GemmPlan p = gemm_plan(max_rows, N, K, 0, sm_count(), 1, 0, max_tn);
+  if (p.splits > 1 && !p.cluster) p = gemm_plan(max_rows, N, K, 1, sm_count(), 1, 0, max_tn);
   CUtensorMap tmW, tmX;
   int e = oxb_make_tmap_2d(&tmX, X, (uint64_t)rows_cap, K, (uint64_t)K * 2, p.tn, GEMM_BK, 2);
   if (e) return e;
@@ -409,21 +400,7 @@ OXB_API int oxb_gemm_grouped_rows(const void* X, int rows_cap, const void* W, in
       default: return gemm_launch<256>(tmW, tmX, y, nullptr, N, max_rows, K, ldY, p, nullptr, nullptr, 0, ar, stream, qw, gr, groups);
     }
   }
-  switch (qtype) {
-    case QT_Q4_K:
-    case QT_Q6_K: {
-      CUtensorMap tmWq;
-      const int box = qtype == QT_Q4_K ? MmqStage<QT_Q4_K>::BOX : MmqStage<QT_Q6_K>::BOX;
-      if (p.tn <= 64 && oxb_make_tmap_bytes(&tmWq, W, (uint64_t)groups * N, row_bytes, GEMM_BM, box) == 0) qw.staged = 1;
-      if (qtype == QT_Q4_K)
-        return gemm_mmq_q4_k(tmX, y, nullptr, N, max_rows, K, ldY, p, nullptr, nullptr, 0, ar, stream, qw, gr, groups,
-                             qw.staged ? &tmWq : nullptr);
-      return gemm_mmq_q6_k(tmX, y, nullptr, N, max_rows, K, ldY, p, nullptr, nullptr, 0, ar, stream, qw, gr, groups,
-                           qw.staged ? &tmWq : nullptr);
-    }
-    case QT_Q8_0: return gemm_mmq_q8_0(tmX, y, nullptr, N, max_rows, K, ldY, p, nullptr, nullptr, 0, ar, stream, qw, gr, groups);
-    case QT_Q4_0: return gemm_mmq_q4_0(tmX, y, nullptr, N, max_rows, K, ldY, p, nullptr, nullptr, 0, ar, stream, qw, gr, groups);
-    case QT_NVFP4: return gemm_mmq_nvfp4(tmX, y, nullptr, N, max_rows, K, ldY, p, nullptr, nullptr, 0, ar, stream, qw, gr, groups);
-    default: return (int)cudaErrorInvalidValue;
-  }
+  if (qtype == QT_FP8B) return (int)cudaErrorInvalidValue;
+  return launch_mmq(qtype, W, (uint64_t)groups * N, tmX, y, nullptr, N, max_rows, K, ldY, p, nullptr, nullptr, 0, ar, stream, qw, gr,
+                    groups);
 }

@@ -56,6 +56,12 @@ class KernelOptions:
     gemm_prefill_tn: int = 256  # token tile of prefill-sized GEMM calls: 128, 256, or 0 = by wave count
     gemv_max_tokens: int = 4  # packed-weight calls of at most this many tokens take the dp4a GEMV (0 = never)
     ar_ll_min_world: int = 2  # rank counts from which the fused all-reduce uses the two-shot exchange
+    # Packed-weight calls with more tokens than this decode the matrix to a bf16 staging buffer once and run the bf16
+    # GEMM on it (every token tile of the fused kernel decodes the weight tile again); 0 = always the fused kernel.
+    mmq_max_tokens: int = 0
+
+
+mmq_max_tokens = KernelOptions.mmq_max_tokens
 
 
 def configure(opts: "KernelOptions") -> None:
@@ -65,6 +71,8 @@ def configure(opts: "KernelOptions") -> None:
     L.oxb_set_gemm_prefill_tn(int(opts.gemm_prefill_tn))
     L.oxb_set_gemv_max_tokens(int(opts.gemv_max_tokens))
     L.oxb_set_ar_ll_min_world(int(opts.ar_ll_min_world))
+    global mmq_max_tokens
+    mmq_max_tokens = int(opts.mmq_max_tokens)
 
 
 def _declare(L) -> None:

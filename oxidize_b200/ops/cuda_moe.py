@@ -187,7 +187,8 @@ def moe_layer(x: torch.Tensor, router_logits: torch.Tensor, cfg, router_bias, ex
                  "oxb_silu_mul_rows")
         y = gemm_grouped_rows(act, experts.down_stack, offsets, E, T)  # [T*k, H]
         return moe_combine_gathered(y, inv, wts, shared, T, comm)
-    if T <= GROUPED_MAX_TOKENS and stacked:
+    # the dense form runs one token tile per expert: 256 tokens with bf16 experts, 128 with packed ones
+    if stacked and T <= (GROUPED_MAX_TOKENS if experts.gate_up_stack.qtype == "BF16" else GROUPED_MAX_TOKENS // 2):
         scale = torch.empty(E, max(T, 1), dtype=torch.float32, device=x.device)
         moe_route(router_logits, cfg, router_bias, scale, experts.first_expert, E)
         x = x.contiguous()

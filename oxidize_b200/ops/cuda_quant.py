@@ -29,7 +29,8 @@ def _launch(x, data_ptr, qt, row_bytes, scales_ptr, scale_ld, out_view, bias, ld
 
 def linear_quant(x, p, out_view, bias, ld_out):
     n, k = p.shape
-    if p.qtype in FUSED_TYPES and k % 64 == 0:
+    staged_ok = C.mmq_max_tokens > 0 and x.shape[0] > C.mmq_max_tokens and n * k <= (1 << 28)
+    if p.qtype in FUSED_TYPES and k % 64 == 0 and not staged_ok:
         row_bytes = p.data.stride(0) * p.data.element_size()
         return _launch(x, p.data.data_ptr(), FUSED_TYPES[p.qtype], row_bytes, None, 0, out_view, bias, ld_out, n, k)
     buf = C.scratch(x.device).dequant_buf(n * k)[: n * k].view(n, k)
