@@ -56,7 +56,8 @@ def parse_args():
     ap.add_argument("--no-workload", action="store_true",
                     help="skip the whole-workload run (all requests from arrival to their last token)")
     ap.add_argument("--sync-decode", action="store_true", help="do not keep a decode step in flight ahead of the host")
-    ap.add_argument("--no-fold-norms", action="store_true", help="keep RMSNorm as stand-alone kernels (A/B measurement)")
+    ap.add_argument("--fold-norms", action="store_true", help="fold RMSNorm into the GEMM epilogues around it (A/B measurement)")
+    ap.add_argument("--no-fold-norms", action="store_true", help="keep RMSNorm as stand-alone kernels (the default)")
     ap.add_argument("--expert-quant", default=None, help="encoding of the MoE expert matrices when it differs from --quant")
     ap.add_argument("--draft-model", default=None, help="preset of a draft model: measure speculative decoding as well")
     ap.add_argument("--draft-tokens", type=int, default=4)
@@ -206,7 +207,7 @@ def main():
     ec = EngineConfig(kv_cache_dtype=args.kv_dtype, kv_page_size=page, num_kv_blocks=nblocks, max_model_len=max_len,
                       max_num_seqs=B, max_num_batched_tokens=max(B, 2048 if not args.no_prefill else B),
                       prefill_chunk_size=512, enable_prefix_cache=False, tp_size=world, ep_size=world,
-                      fold_norms=not args.no_fold_norms, async_decode=not args.sync_decode)
+                      fold_norms=args.fold_norms and not args.no_fold_norms, async_decode=not args.sync_decode)
     llm = LLM(weights, ec, comm)
     torch.cuda.synchronize()
     load_s = time.time() - t0

@@ -79,11 +79,11 @@ struct MmqStage {
   static constexpr int SB = QT == QT_Q6_K ? 210 : QT == QT_Q8_0 ? 272 : QT == QT_FP8B ? 256 : 144;
   static constexpr int BOX = QT == QT_Q6_K ? 240 : (QT == QT_Q8_0 || QT == QT_FP8B) ? 272 : 144;
   static constexpr int BYTES = GEMM_BM * BOX;
-  static constexpr int RING = BOX == 144 ? 4 : 3;  // boxes per CTA (72 / 90 / 102 KB); see MmqRing for wide token tiles
+  static constexpr int RING = BOX == 144 ? 6 : BOX == 240 ? 4 : 3;  // boxes per CTA (108 / 120 / 102 KB); see MmqRing
 };
 // bytes fetched per row for a packed format (host side)
 inline int mmq_box_bytes(int qtype) { return qtype == QT_Q6_K ? 240 : (qtype == QT_Q8_0 || qtype == QT_FP8B) ? 272 : 144; }
-// boxes per CTA: the 272-byte formats keep two with 128-token tiles, so that the stage ring stays at four
+// boxes per CTA: the 272-byte formats keep two with 128-token tiles, which leaves room for a deeper stage ring
 template <int TN, int QT>
 struct MmqRing {
   static constexpr int value = (TN >= 128 && MmqStage<QT>::BOX == 272) ? 2 : MmqStage<QT>::RING;
@@ -92,19 +92,33 @@ template <int TN, int QT>
 struct MmqStaged {
   static constexpr bool value = QT != QT_BF16;
 };
-// Ring depth.  bf16 weights: GemmTile's (the weight stream itself fills the ring).  Packed weights: as deep as
-// shared memory allows beside the ring of packed boxes.  There a k-block carries 3-4x fewer weight bytes, so the CTA has 3-4x less
-// time per k-block, while a stage still takes one activation-tile fetch (an L2 round trip) to turn around; the number
-// of stages, not the decoders, bounds the k-block rate.
+// Packed weights: the decoded weight tile (the A operand, 128 rows x 64 values per k-block) never touches shared
+// memory.  The producer warps write it into tensor memory (tcgen05.st: row = TMEM lane, two bf16 per 32-bit column)
+// and the MMA takes A from there; a stage of the ring is then one activation tile in shared memory plus 32 TMEM
+// columns.  Shared-memory bandwidth is what bounds this kernel at decode sizes (a 16 KB tile written by the decoders
+// and read again by the tensor core, every k-block, next to the packed boxes and the activation tiles), so taking the
+// A tile off that path is worth more than any saving in the decode arithmetic.
 template <int TN, int QT>
 struct GemmStages {
-  static constexpr int FIXED = 1024 + 256 + 1024 + (MmqStaged<TN, QT>::value ? MmqRing<TN, QT>::value * MmqStage<QT>::BYTES : 0);
-  static constexpr int FIT = (224 * 1024 - FIXED) / GemmTile<TN>::STAGE_BYTES;
-  static constexpr int value = QT == QT_BF16 ? GemmTile<TN>::STAGES : (FIT > 8 ? 8 : FIT);
+  static constexpr bool A_IN_TMEM = QT != QT_BF16;
+  static constexpr int STAGE_BYTES = A_IN_TMEM ? GemmTile<TN>::B_BYTES : GemmTile<TN>::STAGE_BYTES;
+  static constexpr int B_OFFSET = A_IN_TMEM ? 0 : GemmTile<TN>::A_BYTES;  // activation tile inside a stage
+  static constexpr int TMEM_A_COLS = GEMM_BK / 2;                         // 32-bit columns of one decoded k-block
+  // TMEM: accumulator first, then the A ring; the packed-weight kernel takes all 512 columns (it is alone on its SM).
+  // Ring depth: bf16 weights use GemmTile's (the weight stream itself fills the ring).  For packed weights no unit of
+  // the pipeline is saturated at decode sizes (decoders, TMA and MMA warps each wait a third of the time on the
+  // others): what bounds the k-block rate is the number of k-blocks in flight, so the ring is as deep as tensor
+  // memory and shared memory allow, up to 12.
+  static constexpr int TMEM_COLS = A_IN_TMEM ? 512 : GemmTile<TN>::TMEM_COLS;
+  static constexpr int FIT_TMEM = (512 - GemmTile<TN>::ACC_COLS) / TMEM_A_COLS;
+  static constexpr int RING_BYTES = QT == QT_BF16 ? 0 : MmqRing<TN, QT>::value * MmqStage<QT>::BYTES;
+  static constexpr int FIT_SMEM = (224 * 1024 - 1024 - 512 - 1024 - RING_BYTES) / (STAGE_BYTES > 0 ? STAGE_BYTES : 1);
+  static constexpr int FIT = FIT_TMEM < FIT_SMEM ? FIT_TMEM : FIT_SMEM;
+  static constexpr int value = QT == QT_BF16 ? GemmTile<TN>::STAGES : (FIT > 12 ? 12 : FIT);
 };
 template <int TN, int QT>
 constexpr int gemm_smem_bytes() {
-  return GemmStages<TN, QT>::value * GemmTile<TN>::STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + 1024 /*token scales*/ +
+  return GemmStages<TN, QT>::value * GemmStages<TN, QT>::STAGE_BYTES + 1024 /*align slack*/ + 512 /*barriers*/ + 1024 /*token scales*/ +
          (MmqStaged<TN, QT>::value ? MmqRing<TN, QT>::value * MmqStage<QT>::BYTES : 0);
 }
 
@@ -434,21 +448,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   constexpr int STAGES = GemmStages<TN, QT>::value;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  using St = GemmStages<TN, QT>;
+  constexpr int STAGE_BYTES = St::STAGE_BYTES;
+  constexpr bool STAGED = MmqStaged<TN, QT>::value;
+  constexpr int PRING = STAGED ? MmqRing<TN, QT>::value : 0;
+  // layout: stage ring | ring of packed boxes | barriers (512 B) | token scales.  The epilogue stages its tiles from
+  // the start of the buffer and may run over both rings, which are idle by then.
+  uint8_t* packed_buf = smem + STAGES * STAGE_BYTES;                                             // [PRING][128][BOX]
+  uint8_t* bars = packed_buf + PRING * MmqStage<QT>::BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(bars);
   uint64_t* empty = full + STAGES;
   uint64_t* accum = empty + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* ticket = const_cast<int*>(abort_flag) + 1;
-  constexpr bool STAGED = MmqStaged<TN, QT>::value;
-  constexpr int PRING = STAGED ? MmqRing<TN, QT>::value : 0;
   // a producer group may run at most STAGES k-blocks ahead of the slowest one; with more groups than stages it could
   // be two uses of a stage ahead, which the one-bit phase of the stage's barrier cannot tell apart
   static_assert(!MMQ || STAGES >= MMQ_GROUPS, "the stage ring must be at least as deep as the number of producer groups");
-  uint64_t* packed_full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES + 192);  // [PRING <= 4] (STAGED only)
-  uint64_t* packed_empty = packed_full + 4;                                                     // [PRING <= 4]
-  uint8_t* packed_buf = smem + STAGES * Cfg::STAGE_BYTES + 256;                                  // [PRING][128][BOX]
-  float* tok_scale = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES + 256 + PRING * MmqStage<QT>::BYTES);  // [TN]
+  static_assert(STAGES * STAGE_BYTES + PRING * MmqStage<QT>::BYTES >= TN * GEMM_BM * 6,
+                "the epilogue stages fp32 partials and a bf16 tile in the ring memory");
+  static_assert(STAGES <= 12 && PRING <= 8, "barrier block layout");
+  uint64_t* packed_full = reinterpret_cast<uint64_t*>(bars + 256);  // [PRING <= 8] (STAGED only)
+  uint64_t* packed_empty = packed_full + 8;                        // [PRING <= 8]
+  float* tok_scale = reinterpret_cast<float*>(bars + 512);         // [TN]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * GEMM_BM;
@@ -465,7 +487,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) {
-      mbar_init(&full[i], MMQ ? 1 + 4 : 1);  // TMA expect_tx arrival (+ one per producer warp)
+      mbar_init(&full[i], MMQ ? 1 + 4 : 1);  // TMA expect_tx arrival (+ one per producer warp of a group)
       mbar_init(&empty[i], 1);
     }
     mbar_init(accum, 1);
@@ -480,7 +502,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     mbar_fence_init();
   }
   if (warp == GEMM_WARP_MMA) {
-    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_alloc(tmem_slot, St::TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -497,19 +519,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   // releases, which are the first instruction of their branches).  Each budget is set at the top of its branch.
   if (warp >= 4 && warp < GEMM_WARP_PRODUCER0) {
     if constexpr (MMQ) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(MMQ_REGS_CONTROL));
+  // The two control warps run their loops with all 32 lanes (waits, counters and addresses are then warp-uniform and
+  // can live in the uniform datapath, which is where TMA and MMA instructions take their operands from); one elected
+  // lane issues.  With a single thread running the whole loop every operand had to be moved over per instruction, and
+  // the serial latency of that thread's instruction stream, several hundred cycles per k-block, bounded the
+  // packed-weight kernel whatever the decoders did.
   if (warp == GEMM_WARP_TMA) {
     // ---------------- TMA producer
-    if (lane == 0) {
-      OXB_TR_DECL
+    OXB_TR_DECL
+    const bool leader = elect_one();
+    const uint64_t pol_w = l2_policy_evict_first();  // weights are read once per step
+    const uint64_t pol_x = l2_policy_evict_last();   // activations are re-read by every CTA
+    const int npre = nkb < STAGES ? nkb : STAGES;
+    if (leader) {
       tma_prefetch_desc(&tmW);
       tma_prefetch_desc(&tmX);
-      const uint64_t pol_w = l2_policy_evict_first();  // weights are read once per step
-      const uint64_t pol_x = l2_policy_evict_last();   // activations are re-read by every CTA
       // Weights are static: the first ring's worth of weight tiles is requested before waiting for
       // the upstream kernel, so the weight stream overlaps the previous kernel's tail.
-      const int npre = nkb < STAGES ? nkb : STAGES;
       for (int i = 0; i < npre; ++i) {
-        uint8_t* sA = smem + i * Cfg::STAGE_BYTES;
+        uint8_t* sA = smem + i * STAGE_BYTES;
         if constexpr (MMQ) {
           mbar_expect_tx(&full[i], Cfg::B_BYTES);
         } else {
@@ -523,17 +551,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         const int npf = nkb < gr.l2_prefetch_kb ? nkb : gr.l2_prefetch_kb;
         for (int i = npre; i < npf; ++i) tma_prefetch_l2_2d(&tmW, (kb_begin + i) * GEMM_BK, w_row0);
       }
-      pdl_wait();  // activations come from the upstream kernel
+    }
+    pdl_wait();  // activations come from the upstream kernel
+    if (leader) {
       for (int i = 0; i < npre; ++i) {
-        uint8_t* sB = smem + i * Cfg::STAGE_BYTES + Cfg::A_BYTES;
+        uint8_t* sB = smem + i * STAGE_BYTES + St::B_OFFSET;
         tma_load_2d_hint(sB, &tmX, &full[i], (kb_begin + i) * GEMM_BK, x_row0, pol_x);
       }
-      for (int i = npre; i < nkb; ++i) {
-        const int st = i % STAGES;
-        const uint32_t ph = (i / STAGES) & 1;
-        if (!OXB_TR_WAIT(tr_w0, mbar_wait_bounded(&empty[st], ph ^ 1, abort_flag, OXB_TIMEOUT_TMA_EMPTY, blockIdx.x))) break;
-        uint8_t* sA = smem + st * Cfg::STAGE_BYTES;
-        uint8_t* sB = sA + Cfg::A_BYTES;
+    }
+    int st = npre == STAGES ? 0 : npre;  // stage of k-block npre
+    uint32_t ph = 0;                     // parity of the completion of empty[st] that frees it for its next use
+    for (int i = npre; i < nkb; ++i) {
+      const bool ok = OXB_TR_WAIT(tr_w0, mbar_wait_bounded(&empty[st], ph, abort_flag, OXB_TIMEOUT_TMA_EMPTY, blockIdx.x));
+      if (!__all_sync(0xffffffffu, ok)) break;
+      if (leader) {
+        uint8_t* sA = smem + st * STAGE_BYTES;
+        uint8_t* sB = sA + St::B_OFFSET;
         if constexpr (MMQ) {
           mbar_expect_tx(&full[st], Cfg::B_BYTES);
         } else {
@@ -542,28 +575,38 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         }
         tma_load_2d_hint(sB, &tmX, &full[st], (kb_begin + i) * GEMM_BK, x_row0, pol_x);
       }
-      OXB_TR_STORE(0)
+      if (++st == STAGES) {
+        st = 0;
+        ph ^= 1;
+      }
     }
+    if (leader) { OXB_TR_STORE(0) }
   } else if (warp == GEMM_WARP_MMA) {
     // ---------------- MMA issuer
-    if (lane == 0) {
-      OXB_TR_DECL
-      constexpr uint32_t idesc = umma_idesc_bf16(GEMM_BM, TN);
-      for (int i = 0; i < nkb; ++i) {
-        const int st = i % STAGES;
-        const uint32_t ph = (i / STAGES) & 1;
-        if (!OXB_TR_WAIT(tr_w0, mbar_wait_bounded(&full[st], ph, abort_flag, OXB_TIMEOUT_TMA_FULL, blockIdx.x))) break;
-        tc_fence_after();
-        const uint32_t a_addr = smem_u32(smem + st * Cfg::STAGE_BYTES);
+    OXB_TR_DECL
+    const bool leader = elect_one();
+    constexpr uint32_t idesc = umma_idesc_bf16(GEMM_BM, TN);
+    const uint32_t smem_base = smem_u32(smem);
+    int st = 0;
+    uint32_t ph = 0;
+    for (int i = 0; i < nkb; ++i) {
+      const bool ok = OXB_TR_WAIT(tr_w0, mbar_wait_bounded(&full[st], ph, abort_flag, OXB_TIMEOUT_TMA_FULL, blockIdx.x));
+      if (!__all_sync(0xffffffffu, ok)) break;
+      tc_fence_after();
+      if (leader) {
+        const uint32_t a_addr = smem_base + st * STAGE_BYTES;
         const uint64_t adesc = umma_desc_k_sw128(a_addr);
-        const uint64_t bdesc = umma_desc_k_sw128(a_addr + Cfg::A_BYTES);
+        const uint64_t bdesc = umma_desc_k_sw128(a_addr + St::B_OFFSET);
         {
           OXB_TR_BEGIN
 #pragma unroll
           for (int k = 0; k < GEMM_BK / 16; ++k) {
-            // advance 16 bf16 = 32 bytes inside the swizzle row: +2 in the (addr >> 4) field
-            umma_bf16(tmem_base + (k % Cfg::NACC) * Cfg::ACC_COLS, adesc + 2 * k, bdesc + 2 * k, idesc,
-                      (i > 0 || k >= Cfg::NACC) ? 1u : 0u);
+            // advance 16 bf16 = 32 bytes inside the swizzle row: +2 in the (addr >> 4) field; in TMEM 16 bf16 = 8 columns
+            if constexpr (MMQ)
+              umma_bf16_ts(tmem_base, tmem_base + Cfg::ACC_COLS + st * St::TMEM_A_COLS + 8 * k, bdesc + 2 * k, idesc,
+                           (i > 0 || k > 0) ? 1u : 0u);
+            else
+              umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
           }
           OXB_TR_END(tr_w1)
         }
@@ -573,6 +616,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           OXB_TR_END(tr_w2)
         }
       }
+      if (++st == STAGES) {
+        st = 0;
+        ph ^= 1;
+      }
+    }
+    if (leader) {
       umma_commit(accum);
       OXB_TR_STORE(1)
     }
@@ -607,41 +656,49 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           for (int j = 0; j < 32; ++j) v[j] = 0u;
         }
       };
-      auto publish = [&](int i, const uint32_t* v) -> bool {
+      // this thread's row of stage st in TMEM: lane = row (the warp's lane quarter is warp % 4), 32 columns per stage
+      const uint32_t a_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + Cfg::ACC_COLS;
+      auto wait_slot = [&](int i) -> bool {
         const int st = i % STAGES;
         const uint32_t ph = (i / STAGES) & 1;
         // warp-uniform verdict: the warp-level synchronisation below must be reached by all 32 lanes or none
-        if (!OXB_TR_WAIT(tr_w0, __all_sync(0xffffffffu, mbar_wait_bounded(&empty[st], ph ^ 1, abort_flag, OXB_TIMEOUT_TMA_EMPTY, blockIdx.x))))
-          return false;
-        store_row_sw128(smem + st * Cfg::STAGE_BYTES, r, v);
-        fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
-        __syncwarp();              // the warp's 32 rows are written: one arrival per warp instead of 32
-        if (lane == 0) mbar_arrive(&full[st]);
+        const bool ok = OXB_TR_WAIT(tr_w0, __all_sync(0xffffffffu, mbar_wait_bounded(&empty[st], ph ^ 1, abort_flag,
+                                                                                    OXB_TIMEOUT_TMA_EMPTY, blockIdx.x)));
+        if (ok) tc_fence_after();  // the MMAs that read this slot are done: order this thread's TMEM stores after them
+        return ok;
+      };
+      auto signal_slot = [&](int i) {
+        tmem_st_wait();     // this thread's stores have landed in TMEM
+        tc_fence_before();  // ... and are ordered before the MMA thread's reads through the barrier
+        __syncwarp();       // the warp's 32 rows are written: one arrival per warp instead of 32
+        if (lane == 0) mbar_arrive(&full[i % STAGES]);
+      };
+      auto publish = [&](int i, const uint32_t* v) -> bool {  // a k-block decoded into registers beforehand
+        if (!wait_slot(i)) return false;
+        const uint32_t dst = a_lane + (i % STAGES) * St::TMEM_A_COLS;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) tmem_st4(dst + 4 * c, v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+        signal_slot(i);
         return true;
       };
       // staged form: wait for the ring slot first, then decode the row out of shared memory straight into it
       auto publish_from = [&](int i, const uint8_t* srow, int kb) -> bool {
-        const int st = i % STAGES;
-        const uint32_t ph = (i / STAGES) & 1;
-        if (!OXB_TR_WAIT(tr_w0, __all_sync(0xffffffffu, mbar_wait_bounded(&empty[st], ph ^ 1, abort_flag, OXB_TIMEOUT_TMA_EMPTY, blockIdx.x))))
-          return false;
-        uint8_t* tile = smem + st * Cfg::STAGE_BYTES;
+        if (!wait_slot(i)) return false;
+        const uint32_t dst = a_lane + (i % STAGES) * St::TMEM_A_COLS;
+        auto put = [&](int c, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) { tmem_st4(dst + 4 * c, w0, w1, w2, w3); };
         {
-        OXB_TR_BEGIN
-        if (n < N) {
+          OXB_TR_BEGIN
+          // No branch on the row index here: tcgen05.st is a warp-wide instruction (all 32 lanes must execute the same
+          // one), and a tile whose last rows lie past N has warps with both kinds of lanes.  Rows past N decode whatever
+          // the box holds there (zeros past the end of the matrix, the next expert's rows in a stacked one); the
+          // epilogue never stores them.
           if constexpr (QT == QT_FP8B)  // scales are indexed by the absolute row and channel
-            dequant64_to_tile<QT>(srow - (size_t)(kb & ~3) * GEMM_BK, kb * GEMM_BK, qw, n, tile, r);
+            dequant64_chunks<QT>(srow - (size_t)(kb & ~3) * GEMM_BK, kb * GEMM_BK, qw, n < N ? n : 0, put);
           else
-            dequant64_to_tile<QT>(srow, (kb & 3) * GEMM_BK, qw, 0, tile, r);
-        } else {
-#pragma unroll
-          for (int c = 0; c < 8; ++c) store_chunk_sw128(tile, r, c, 0u, 0u, 0u, 0u);
+            dequant64_chunks<QT>(srow, (kb & 3) * GEMM_BK, qw, 0, put);
+          OXB_TR_END(tr_w2)
         }
-        OXB_TR_END(tr_w2)
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&full[st]);
+        signal_slot(i);
         return true;
       };
       bool staged_done = false;
@@ -938,7 +995,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == GEMM_WARP_MMA) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  if (warp == GEMM_WARP_MMA) tmem_dealloc(tmem_base, St::TMEM_COLS);
 }
 
 struct GemmPlan {
@@ -951,14 +1008,14 @@ struct GemmPlan {
 extern int g_oxb_cluster_splitk;  // 1 = split-K through clusters / distributed shared memory (default)
 extern int g_oxb_gemm_prefill_tn;  // 0 = pick the token tile of prefill-sized calls by wave count, 128 / 256 = force
 
-// max_tn caps the token tile.  cluster_ok < 0: follow g_oxb_cluster_splitk.  max_ctas > 0 bounds tiles*splits (kernels whose CTAs wait
+// packed: the packed-weight kernel (one CTA per SM, 128-token tiles at most).  cluster_ok < 0: follow g_oxb_cluster_splitk.  max_ctas > 0 bounds tiles*splits (kernels whose CTAs wait
 // for CTAs of other GPUs must be resident all at once).
 inline GemmPlan gemm_plan(int T, int N, int K, int splits_hint, int sm_count, int cluster_ok = -1, int max_ctas = 0,
-                          int max_tn = 256) {
+                          bool packed = false, int groups = 1) {
   GemmPlan p;
   if (cluster_ok < 0) cluster_ok = g_oxb_cluster_splitk;
   p.tn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
-  if (p.tn > max_tn) p.tn = max_tn;  // packed weights: 128-token tiles at most (their ring of packed boxes needs the room)
+  if (packed && p.tn > 128) p.tn = 128;  // packed weights: 128-token tiles at most (TMEM holds the accumulator and the A ring)
   p.n_tiles = (N + GEMM_BM - 1) / GEMM_BM;
   if (T > 256 && sm_count > 0) {
     // Prefill-sized calls run one CTA per SM in waves; a nearly empty last wave costs a whole tile time.
@@ -989,8 +1046,19 @@ inline GemmPlan gemm_plan(int T, int N, int K, int splits_hint, int sm_count, in
     const int s_max = p.tn <= 64 ? 16 : 4;  // wide tiles have large partials: a deep split costs more than it streams
     for (int s = 1; s <= s_max && s <= max_by_k && (long long)tiles * s <= capacity && (s == 1 || tiles < sm_count); ++s) {
       const int per_cta = (kb_total + s - 1) / s;
-      const int ctas_on_busiest = (tiles * s + sm_count - 1) / sm_count;
-      const long long cost = (long long)ctas_on_busiest * (per_cta + 3) + (s > 1 ? 2 + s / 4 + epi : 0);
+      long long cost;
+      if (packed) {
+        // One CTA per SM, so the grid runs in waves, and every wave pays the CTA's set-up and epilogue (about a dozen
+        // k-block times).  A cluster must fit inside one GPC (18-19 SMs here): s CTAs at a time, the remainder idles.
+        const int per_gpc = (sm_count / 8) / s;
+        const int slots = per_gpc > 0 ? 8 * per_gpc * s : s;
+        const long long ctas = (long long)tiles * groups * s;  // grouped launches: every group has its own tiles
+        const int waves = (int)((ctas + (s > 1 ? slots : sm_count) - 1) / (s > 1 ? slots : sm_count));
+        cost = (long long)waves * (per_cta + 12) + (s > 1 ? 2 + s / 4 + epi : 0);
+      } else {
+        const int ctas_on_busiest = (tiles * s + sm_count - 1) / sm_count;
+        cost = (long long)ctas_on_busiest * (per_cta + 3) + (s > 1 ? 2 + s / 4 + epi : 0);
+      }
       if (best_cost < 0 || cost < best_cost) {
         best_cost = cost;
         splits = s;
@@ -1099,7 +1167,7 @@ int gemm_launch_mmq(const CUtensorMap& tmX, __nv_bfloat16* Y, const float* bias,
     case 32: return gemm_launch<32, QT>(tmW, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
     case 64: return gemm_launch<64, QT>(tmW, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
     case 128: return gemm_launch<128, QT>(tmW, tmX, Y, bias, N, T, K, ldY, p, ws, counters, epi_mode, ar, stream, qw, gr, groups);
-    default: return (int)cudaErrorInvalidConfiguration;  // packed weights are planned with max_tn = 128
+    default: return (int)cudaErrorInvalidConfiguration;  // packed weights are planned with 128-token tiles at most
   }
 }
 

@@ -218,11 +218,11 @@ __device__ __forceinline__ uint32_t bf16x2_bits(__nv_bfloat162 v) { return *rein
 __device__ __forceinline__ __nv_bfloat162 bits_bf16x2(uint32_t u) { return *reinterpret_cast<__nv_bfloat162*>(&u); }
 
 // Decode values [k0, k0+64) of the row at `rowp` (shared memory; Q6_K / Q8_0 / Q4_0 rows may start at any even
-// byte) straight into row r of the swizzled tile, 16 bytes at a time: nothing but the chunk in hand lives in
-// registers, so many producer warps fit on an SM.  The integer codes become bf16 through the mantissa of a
+// byte) and hand them on eight values (four packed words) at a time: put(c, w0, w1, w2, w3) receives values
+// 8c .. 8c+7.  Nothing but the chunk in hand lives in registers, so many producer warps fit on an SM.  The integer codes become bf16 through the mantissa of a
 // power of two (0x4300 | q is the bf16 number 128 + q for q < 128): no integer-to-float conversions.
-template <int QT>
-__device__ __forceinline__ void dequant64_to_tile(const uint8_t* rowp, int k0, const QwArgs& qw, int n, uint8_t* tile, int r) {
+template <int QT, class Put>
+__device__ __forceinline__ void dequant64_chunks(const uint8_t* rowp, int k0, const QwArgs& qw, int n, Put&& put) {
   if constexpr (QT == QT_Q4_K) {
     const uint8_t* b = rowp + (size_t)(k0 >> 8) * 144;  // 16-byte aligned
     const int c = (k0 & 255) >> 6;
@@ -255,9 +255,9 @@ __device__ __forceinline__ void dequant64_to_tile(const uint8_t* rowp, int k0, c
       for (int j = 0; j < 2; ++j) {
         const uint32_t lo0 = w[2 * j] & 0x0F0F0F0Fu, lo1 = w[2 * j + 1] & 0x0F0F0F0Fu;
         const uint32_t hi0 = (w[2 * j] >> 4) & 0x0F0F0F0Fu, hi1 = (w[2 * j + 1] >> 4) & 0x0F0F0F0Fu;
-        store_chunk_sw128(tile, r, 2 * h + j, dq(lo0, 0x4140, s0b, n0b), dq(lo0, 0x4342, s0b, n0b), dq(lo1, 0x4140, s0b, n0b),
+        put(2 * h + j, dq(lo0, 0x4140, s0b, n0b), dq(lo0, 0x4342, s0b, n0b), dq(lo1, 0x4140, s0b, n0b),
                           dq(lo1, 0x4342, s0b, n0b));
-        store_chunk_sw128(tile, r, 4 + 2 * h + j, dq(hi0, 0x4140, s1b, n1b), dq(hi0, 0x4342, s1b, n1b),
+        put(4 + 2 * h + j, dq(hi0, 0x4140, s1b, n1b), dq(hi0, 0x4342, s1b, n1b),
                           dq(hi1, 0x4140, s1b, n1b), dq(hi1, 0x4342, s1b, n1b));
       }
     }
@@ -293,7 +293,7 @@ __device__ __forceinline__ void dequant64_to_tile(const uint8_t* rowp, int k0, c
           o[2 * e] = bf16x2_bits(__hmul2(__hsub2(bits_bf16x2(__byte_perm(code, 0x43434343u, 0x4140)), k160), sc));
           o[2 * e + 1] = bf16x2_bits(__hmul2(__hsub2(bits_bf16x2(__byte_perm(code, 0x43434343u, 0x4342)), k160), sc));
         }
-        store_chunk_sw128(tile, r, 4 * s + j, o[0], o[1], o[2], o[3]);
+        put(4 * s + j, o[0], o[1], o[2], o[3]);
       }
     }
   } else if constexpr (QT == QT_Q8_0) {
@@ -318,13 +318,14 @@ __device__ __forceinline__ void dequant64_to_tile(const uint8_t* rowp, int k0, c
           o[2 * e + 1] = bf16x2_bits(__hmul2(__hsub2(bits_bf16x2(__byte_perm(t, 0x43434343u, 0x4342)),
                                                     bits_bf16x2(__byte_perm(neg, 0x43434343u, 0x4342))), db));
         }
-        store_chunk_sw128(tile, r, 4 * blk + j, o[0], o[1], o[2], o[3]);
+        put(4 * blk + j, o[0], o[1], o[2], o[3]);
       }
     }
   } else {
     uint32_t v[32];
     dequant64<QT>(rowp, k0, qw, n, v);
-    store_row_sw128(tile, r, v);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) put(c, v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
   }
 }
 

@@ -127,10 +127,10 @@ OXB_API int oxb_gemm_quant(const void* X, const void* Wq, int qtype, size_t row_
     return gemv_quant_run(qtype, reinterpret_cast<const uint8_t*>(Wq), row_bytes, reinterpret_cast<const __nv_bfloat16*>(X), K,
                       reinterpret_cast<__nv_bfloat16*>(Y), ldY, bias, T, N, K, epi_mode == EPI_ADD_INTO, sm_count(), stream);
   if (K % 64 != 0) return (int)cudaErrorInvalidValue;
-  GemmPlan p = gemm_plan(T, N, K, splits_hint, sm_count(), -1, 0, 128);
+  GemmPlan p = gemm_plan(T, N, K, splits_hint, sm_count(), -1, 0, true);
   while (p.splits > 1 && !p.cluster && (p.ws_bytes > ws_bytes || p.n_counters > n_counters || ws == nullptr || counters == nullptr ||
                           p.n_tiles * p.t_tiles * p.splits > sm_count()))
-    p = gemm_plan(T, N, K, p.splits - 1, sm_count(), -1, 0, 128);
+    p = gemm_plan(T, N, K, p.splits - 1, sm_count(), -1, 0, true);
   CUtensorMap tmX;
   int e = oxb_make_tmap_2d(&tmX, X, T, K, (uint64_t)K * 2, p.tn, GEMM_BK, 2);
   if (e) return e;
@@ -336,12 +336,12 @@ OXB_API int oxb_gemm_grouped(const void* X, int x_rows, const void* W, int qtype
                              long long y_stride, const float* scale, int scale_ld, int groups, int T, int N, int K,
                              int ldY, void* ws, size_t ws_bytes, int* counters, int n_counters, cudaStream_t stream) {
   if (T <= 0 || N <= 0 || K <= 0 || groups <= 0) return 0;
-  const int max_tn = qtype == QT_BF16 ? 256 : 128;  // one token tile per group
-  if (T > max_tn || K % 64 != 0) return (int)cudaErrorInvalidValue;
-  GemmPlan p = gemm_plan(T, N, K, 0, sm_count(), -1, 0, max_tn);
+  const bool packed = qtype != QT_BF16;
+  if (T > (packed ? 128 : 256) || K % 64 != 0) return (int)cudaErrorInvalidValue;  // one token tile per group
+  GemmPlan p = gemm_plan(T, N, K, 0, sm_count(), -1, 0, packed, groups);
   while (p.splits > 1 && !p.cluster && (p.ws_bytes * groups > ws_bytes || p.n_counters * groups > n_counters || ws == nullptr ||
                           counters == nullptr || p.n_tiles * p.splits * groups > sm_count()))
-    p = gemm_plan(T, N, K, p.splits - 1, sm_count(), -1, 0, max_tn);
+    p = gemm_plan(T, N, K, p.splits - 1, sm_count(), -1, 0, packed, groups);
   CUtensorMap tmW, tmX;
   const uint64_t xr = x_rows > 0 ? (uint64_t)groups * x_rows : (uint64_t)T;
   int e = oxb_make_tmap_2d(&tmX, X, xr, K, (uint64_t)K * 2, p.tn, GEMM_BK, 2);
@@ -378,9 +378,9 @@ OXB_API int oxb_gemm_grouped_rows(const void* X, int rows_cap, const void* W, in
                                   cudaStream_t stream) {
   if (rows_cap <= 0 || max_rows <= 0 || N <= 0 || K <= 0 || groups <= 0) return 0;
   if (K % 64 != 0 || row_offsets == nullptr) return (int)cudaErrorInvalidValue;
-  const int max_tn = qtype == QT_BF16 ? 256 : 128;
-  GemmPlan p = gemm_plan(max_rows, N, K, 0, sm_count(), 1, 0, max_tn);
-  if (p.splits > 1 && !p.cluster) p = gemm_plan(max_rows, N, K, 1, sm_count(), 1, 0, max_tn);
+  const bool packed = qtype != QT_BF16;
+  GemmPlan p = gemm_plan(max_rows, N, K, 0, sm_count(), 1, 0, packed, groups);
+  if (p.splits > 1 && !p.cluster) p = gemm_plan(max_rows, N, K, 1, sm_count(), 1, 0, packed, groups);
   CUtensorMap tmW, tmX;
   int e = oxb_make_tmap_2d(&tmX, X, (uint64_t)rows_cap, K, (uint64_t)K * 2, p.tn, GEMM_BK, 2);
   if (e) return e;

@@ -73,7 +73,7 @@ class SingleRankComm:
 
 
 class Transformer:
-    def __init__(self, weights: ModelWeights, comm=None, act_dtype: Optional[torch.dtype] = None, fold_norms: bool = True,
+    def __init__(self, weights: ModelWeights, comm=None, act_dtype: Optional[torch.dtype] = None, fold_norms: bool = False,
                  fuse_qkv_rope: bool = True, fuse_swiglu: bool = True, pipe=None):
         self.w = weights
         self.pipe = pipe  # parallel.pp.StageIO when this model holds one pipeline stage's layers
