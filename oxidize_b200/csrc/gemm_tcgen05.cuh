@@ -623,8 +623,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     }
     if (leader) {
       umma_commit(accum);
+      // The issuing lane alone polls for the end of the MMAs, then the warp releases the four epilogue warps from a
+      // named barrier: 128 threads spinning on a shared-memory barrier for the whole main loop take issue slots and
+      // shared-memory cycles from the warps that feed the tensor core.  (The wait is bounded; on a timeout the abort
+      // flag is set and the barrier is released all the same.)
+      mbar_wait_bounded(accum, 0, abort_flag, OXB_TIMEOUT_ACCUM, blockIdx.x);
       OXB_TR_STORE(1)
     }
+    __syncwarp();
+    asm volatile("bar.arrive 3, 160;" ::: "memory");
   }
     __syncwarp();
     if (csplit) {
@@ -710,12 +717,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         // every warp releases a box when it is done with it.  Weights are static, so none of this waits for
         // the upstream kernel.
         const int sb_begin = kb_begin >> 2, sb_end = (kb_end + 3) >> 2;  // super-blocks touched by [kb_begin, kb_end)
-        auto issue = [&](int j) {  // j-th super-block of this CTA -> box j % PRING
+        const int nsb = sb_end - sb_begin;
+        auto sb_at = [&](int j) { return sb_begin + j; };  // j-th super-block of this CTA
+        auto issue = [&](int j) {  // j-th super-block in processing order -> box j % PRING
           const int b = j % PRING;
           mbar_expect_tx(&packed_full[b], PBYTES);
-          tma_load_2d(packed_buf + b * PBYTES, &tmW, &packed_full[b], (((sb_begin + j) * SB) & ~15) >> 2, w_row0);
+          tma_load_2d(packed_buf + b * PBYTES, &tmW, &packed_full[b], ((sb_at(j) * SB) & ~15) >> 2, w_row0);
         };
-        const int nsb = sb_end - sb_begin;
         const bool issuer = r == 0 && grp == 0;
         if (issuer) {
           tma_prefetch_desc(&tmW);
@@ -734,11 +742,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             alive = OXB_TR_WAIT(tr_w1, __all_sync(0xffffffffu, mbar_wait_bounded(&packed_full[b], (j / PRING) & 1, abort_flag,
                                                                                  OXB_TIMEOUT_TMA_FULL, blockIdx.x)));
           if (alive) {
-            const uint8_t* srow = packed_buf + b * PBYTES + r * BOX + (((sb_begin + j) * SB) & 15);
-            const int kb0 = max(kb_begin, (sb_begin + j) * 4), kb1 = min(kb_end, (sb_begin + j) * 4 + 4);
+            const int sb = sb_at(j);
+            const uint8_t* srow = packed_buf + b * PBYTES + r * BOX + ((sb * SB) & 15);
+            const int kb0 = max(kb_begin, sb * 4), kb1 = min(kb_end, sb * 4 + 4);
             for (int kb = kb0; kb < kb1 && alive; ++kb) {
-              if ((kb - kb_begin) % MMQ_GROUPS != grp) continue;  // another group's k-block
-              alive = publish_from(kb - kb_begin, srow, kb);
+              const int seq = kb - kb_begin;  // the ring's sequence number
+              if (seq % MMQ_GROUPS != grp) continue;  // another group's k-block
+              alive = publish_from(seq, srow, kb);
             }
           }
           __syncwarp();  // the warp's reads of the box are done (alive or not, so that the issuer never waits in vain)
@@ -787,7 +797,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       for (int j = etid; j < tt; j += 128) nm.clear[(size_t)(t0 + j) * SUMSQ_STRIDE] = 0ull;
     }
     unsigned long long* const ssq_dst = nm.sumsq_out;
-    mbar_wait_bounded(accum, 0, abort_flag, OXB_TIMEOUT_ACCUM, blockIdx.x);
+    asm volatile("bar.sync 3, 160;" ::: "memory");  // released by the MMA warp once the accumulator is complete
     // agree on one verdict for all 128 epilogue threads before any further named barrier
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (threadIdx.x == 0) {

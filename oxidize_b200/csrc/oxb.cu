@@ -50,9 +50,10 @@ OXB_API int oxb_set_cluster_splitk(int on) {
   g_oxb_cluster_splitk = on ? 1 : 0;
   return old;
 }
-// Packed-weight calls of at most this many tokens take the dp4a GEMV (0 = never).  Above 4 tokens the GEMV re-reads
-// its int8 activations from shared memory once per token and falls behind the tensor-core path.
-int g_oxb_gemv_max_t = 4;
+// Packed-weight calls of at most this many tokens take the dp4a GEMV (0 = never).  With one or two tokens it is up to
+// twice as fast as the tensor-core kernel on the tall matrices (qkv, gate_up, lm_head); from three tokens on it processes
+// four at a time and the tensor-core kernel wins (by 2x on the wide ffn_down shape).
+int g_oxb_gemv_max_t = 2;
 OXB_API int oxb_set_gemv_max_tokens(int t) {
   const int old = g_oxb_gemv_max_t;
   g_oxb_gemv_max_t = t < 0 ? 0 : (t > GV_MAX_T ? GV_MAX_T : t);

@@ -121,7 +121,7 @@ OXB_API int oxb_gemm_quant(const void* X, const void* Wq, int qtype, size_t row_
                            void* Y, const float* bias, int T, int N, int K, int ldY, int epi_mode, int splits_hint,
                            void* ws, size_t ws_bytes, int* counters, int n_counters, cudaStream_t stream) {
   if (T <= 0 || N <= 0 || K <= 0) return 0;
-  // Decode batches of up to 8 tokens: the packed bytes go straight into dp4a (gemv_quant.cuh), no tensor-core staging.
+  // One or two tokens (g_oxb_gemv_max_t): the packed bytes go straight into dp4a (gemv_quant.cuh), no tensor-core staging.
   if (g_oxb_gemv_max_t > 0 && T <= g_oxb_gemv_max_t && (epi_mode == EPI_STORE || epi_mode == EPI_ADD_INTO) &&
       gemv_quant_supported(qtype, T, K, row_bytes, Wq, X, K))
     return gemv_quant_run(qtype, reinterpret_cast<const uint8_t*>(Wq), row_bytes, reinterpret_cast<const __nv_bfloat16*>(X), K,

@@ -54,7 +54,7 @@ class KernelOptions:
     pdl: bool = True  # programmatic dependent launch: a kernel's set-up overlaps the tail of the one before it
     cluster_splitk: bool = True  # split-K partials meet in distributed shared memory instead of global scratch
     gemm_prefill_tn: int = 256  # token tile of prefill-sized GEMM calls: 128, 256, or 0 = by wave count
-    gemv_max_tokens: int = 4  # packed-weight calls of at most this many tokens take the dp4a GEMV (0 = never)
+    gemv_max_tokens: int = 2  # packed-weight calls of at most this many tokens take the dp4a GEMV (0 = never)
     ar_ll_min_world: int = 2  # rank counts from which the fused all-reduce uses the two-shot exchange
     # Packed-weight calls with more tokens than this decode the matrix to a bf16 staging buffer once and run the bf16
     # GEMM on it (every token tile of the fused kernel decodes the weight tile again); 0 = always the fused kernel.

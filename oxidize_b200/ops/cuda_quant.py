@@ -1,7 +1,7 @@
 """Linear layers over packed weights (Q4_K / Q6_K / Q8_0 / Q4_0 / NVFP4 GGUF blocks and
 block-scaled fp8) on the GPU.
 
-Everything goes through ``oxb_gemm_quant``.  Decode batches of up to 8 tokens take the dp4a GEMV
+Everything goes through ``oxb_gemm_quant``.  Calls with one or two tokens take the dp4a GEMV
 (``csrc/gemv_quant.cuh``: int8 activations, the packed bytes go straight into the arithmetic); larger
 batches the tcgen05 GEMM whose producer warps decode the blocks into the swizzled shared-memory
 operand tile.  Either way the weights are read from HBM once, in their packed form.  Formats without a
