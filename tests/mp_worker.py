@@ -261,7 +261,12 @@ def case_pp_engine(dev, comm_kind):
     # a sampled request too: the last stage draws, every stage must learn the same tokens
     sps = SamplingParams(temperature=0.8, top_k=20, max_tokens=6, ignore_eos=True, seed=5)
     got_s = [o.token_ids for o in llm.generate(prompts[:2], sps)]
-    one = LLM.from_gguf(path, EngineConfig(**ec), device=dev)
+    if tp == 1:
+        one = LLM.from_gguf(path, EngineConfig(**ec), device=dev)
+    else:
+        # Splitting the layers over stages does not change the arithmetic, splitting the heads over ranks does (bf16
+        # partial sums): the exact reference for tp x pp is the same tensor-parallel group running all layers.
+        one = LLM.from_gguf(path, EngineConfig(tp_size=tp, **ec), device=dev, comm=comm, tp_rank=rank % tp)
     want = [o.token_ids for o in one.generate(prompts, sp)]
     assert got == want, (got, want)
     box = [None] * W

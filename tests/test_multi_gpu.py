@@ -2,7 +2,7 @@
 import pytest
 import torch
 
-from test_tp_cpu import run_ranks
+from test_tp_cpu import fail_text, run_ranks
 
 pytestmark = pytest.mark.gpu
 
@@ -19,45 +19,45 @@ def _ngpu():
 @NEED2
 def test_gemm_allreduce_fused_matches_reference():
     r = run_ranks("gemm_ar", n=_ngpu(), device="cuda", comm="fused", env_extra=ENV)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, fail_text(r)
 
 
 @NEED2
 @pytest.mark.parametrize("comm", ["nccl", "fused"])
 def test_tp_model_matches_single_gpu(comm):
     r = run_ranks("tp_model", n=2, device="cuda", comm=comm, env_extra=ENV)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, fail_text(r)
 
 
 @NEED2
 def test_tp_decode_under_cuda_graphs():
     r = run_ranks("tp_graph", n=2, device="cuda", comm="fused", env_extra=ENV)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, fail_text(r)
 
 
 @NEED2
 def test_expert_parallel_moe_matches_single_rank():
     r = run_ranks("ep_model", n=2, device="cuda", comm="fused", env_extra=ENV)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, fail_text(r)
 
 
 @NEED2
 def test_engine_with_two_pipeline_stages_on_gpus():
     """pp_size = 2 through the engine: stage-local layers on each GPU, micro-batched steps, NCCL p2p hand-off."""
     r = run_ranks("pp_engine", n=2, device="cuda", comm="nccl", env_extra=ENV)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, fail_text(r)
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_engine_with_tp2_x_pp2_on_gpus():
     r = run_ranks("pp_engine", n=4, device="cuda", comm="fused", env_extra=ENV)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, fail_text(r)
 
 
 @NEED2
 def test_rank_exit_between_steps_is_detected():
     r = run_ranks("rank_exit", n=2, device="cuda", comm="nccl", env_extra=ENV)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, fail_text(r)
 
 
 def test_peer_wait_times_out_and_reports():

@@ -20,6 +20,17 @@ def free_port():
     return p
 
 
+def fail_text(r) -> str:
+    """What the ranks themselves printed before the launcher's own failure report (which is long and says nothing)."""
+    err = r.stderr
+    for mark in ("Sending process", "failed (exitcode"):
+        i = err.find(mark)
+        if i >= 0:
+            err = err[:i]
+            break
+    return r.stdout[-2000:] + "\n" + err[-6000:]
+
+
 def run_ranks(case, n=2, device="cpu", comm="nccl", timeout=300, env_extra=None):
     env = dict(os.environ)
     env.update({"OMP_NUM_THREADS": "2"})
@@ -33,25 +44,25 @@ def run_ranks(case, n=2, device="cpu", comm="nccl", timeout=300, env_extra=None)
 
 def test_tp2_logits_match_tp1_on_cpu():
     r = run_ranks("tp_model")
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, fail_text(r)
     assert r.stdout.count("OK tp_model") == 2
 
 
 def test_tp4_logits_match_tp1_on_cpu():
     r = run_ranks("tp_model", n=4)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, fail_text(r)
     assert r.stdout.count("OK tp_model") == 4
 
 
 def test_ep2_moe_logits_match_single_rank_on_cpu():
     r = run_ranks("ep_model")
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, fail_text(r)
     assert r.stdout.count("OK ep_model") == 2
 
 
 def test_tp2_with_replicated_experts_matches_single_rank_on_cpu():
     r = run_ranks("ep1_model")
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, fail_text(r)
     assert r.stdout.count("OK ep1_model") == 2
 
 
@@ -71,25 +82,25 @@ def test_mismatched_expert_partition_is_rejected():
 
 def test_pp2_tokens_match_single_process_on_cpu():
     r = run_ranks("pp_model")
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, fail_text(r)
     assert r.stdout.count("OK pp_model") == 2
 
 
 def test_engine_with_two_pipeline_stages_on_cpu():
     r = run_ranks("pp_engine")
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, fail_text(r)
     assert r.stdout.count("OK pp_engine") == 2
 
 
 def test_engine_with_tp2_x_pp2_on_cpu():
     r = run_ranks("pp_engine", n=4)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, fail_text(r)
     assert r.stdout.count("OK pp_engine") == 4
 
 
 def test_rank_exit_detected_by_heartbeat():
     r = run_ranks("rank_exit")
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, fail_text(r)
     assert r.stdout.count("OK rank_exit") == 2
 
 
