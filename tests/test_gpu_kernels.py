@@ -288,6 +288,34 @@ def test_linear_packed_weights_fused_dequant(C, qtype, T, N, K):
     assert torch.equal(got, C.linear(x, [w]))
 
 
+def test_two_matrices_in_a_row_through_the_dequant_staging_buffer(C):
+    """Formats without a fused decoder are decoded into ONE staging buffer that the bf16 GEMM then reads as its
+    weights; two different matrices back to back must each be multiplied by their own weights (the GEMM must not
+    pick up tiles of the buffer's previous contents before the decode kernel ahead of it has finished).  The same
+    path serves long calls on fused formats when ``mmq_max_tokens`` is set."""
+    from oxidize_b200.models.weights import qtensor_from_dense
+
+    torch.manual_seed(11)
+    N, K, T = 512, 1024, 96
+    wa = qtensor_from_dense(torch.randn(N, K) * 0.05, "Q4_K", device="cuda")
+    wb = qtensor_from_dense(torch.randn(N, K) * 0.05, "Q4_K", device="cuda")
+    x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
+    C.configure(C.KernelOptions(mmq_max_tokens=8))  # T = 96 > 8: both calls take the staging path
+    try:
+        outs = []
+        for _ in range(3):
+            outs.append((C.linear(x, [wa]), C.linear(x, [wb])))
+        torch.cuda.synchronize()
+    finally:
+        C.configure(C.KernelOptions())
+    want_a = x.float().cpu() @ wa.to("cpu").dense_cache().t()
+    want_b = x.float().cpu() @ wb.to("cpu").dense_cache().t()
+    for ya, yb in outs:
+        assert _rel_err(ya.cpu(), want_a) < 8e-3
+        assert _rel_err(yb.cpu(), want_b) < 8e-3
+    _check_status(C)
+
+
 @pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q8_0", "Q4_0"])
 @pytest.mark.parametrize("T,N,K", [(1, 4096, 4096), (1, 1000, 14336), (2, 257, 2048), (3, 520, 1024), (5, 64, 8192), (8, 1280, 4096)])
 def test_gemv_packed_weights_small_batches(C, qtype, T, N, K):
