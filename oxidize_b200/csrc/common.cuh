@@ -290,6 +290,7 @@ int oxb_make_tmap_bytes(CUtensorMap* out, const void* base, uint64_t rows, uint6
                         uint32_t box_bytes);
 extern int g_oxb_ar_ll_min_world;          // rank counts from which the fused all-reduce uses the LL two-shot exchange
 extern int g_oxb_gemv_max_t;               // packed-weight calls of at most this many tokens take the dp4a GEMV
+extern int g_oxb_gemv_wide;                // 1: also for matrices with K >= 2N (default 0: those go to the tensor-core kernel)
 extern unsigned long long* g_oxb_ar_trace;    // optional device buffers for in-kernel phase timestamps
 extern unsigned long long* g_oxb_attn_trace;
 // 2-D row-major tensor [rows, cols] of `elem_bytes` elements, box [box_rows, box_cols], 128B swizzle

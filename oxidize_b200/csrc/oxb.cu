@@ -54,6 +54,12 @@ OXB_API int oxb_set_cluster_splitk(int on) {
 // twice as fast as the tensor-core kernel on the tall matrices (qkv, gate_up, lm_head); from three tokens on it processes
 // four at a time and the tensor-core kernel wins (by 2x on the wide ffn_down shape).
 int g_oxb_gemv_max_t = 2;
+int g_oxb_gemv_wide = 0;
+OXB_API int oxb_set_gemv_wide(int on) {
+  const int old = g_oxb_gemv_wide;
+  g_oxb_gemv_wide = on ? 1 : 0;
+  return old;
+}
 OXB_API int oxb_set_gemv_max_tokens(int t) {
   const int old = g_oxb_gemv_max_t;
   g_oxb_gemv_max_t = t < 0 ? 0 : (t > GV_MAX_T ? GV_MAX_T : t);

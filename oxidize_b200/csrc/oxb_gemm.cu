@@ -122,7 +122,11 @@ OXB_API int oxb_gemm_quant(const void* X, const void* Wq, int qtype, size_t row_
                            void* ws, size_t ws_bytes, int* counters, int n_counters, cudaStream_t stream) {
   if (T <= 0 || N <= 0 || K <= 0) return 0;
   // One or two tokens (g_oxb_gemv_max_t): the packed bytes go straight into dp4a (gemv_quant.cuh), no tensor-core staging.
-  if (g_oxb_gemv_max_t > 0 && T <= g_oxb_gemv_max_t && (epi_mode == EPI_STORE || epi_mode == EPI_ADD_INTO) &&
+  // ... unless the matrix is wide and short (ffn_down: few rows, long K): the GEMV's warps then each walk a long row
+  // with little parallelism across rows, and the split-K tensor-core kernel is ahead even at one token
+  // (4096 x 14336: 23.6 against 25.6 us for Q4_K, 29.9 against 38.2 us for Q6_K).
+  const bool wide = !g_oxb_gemv_wide && (long long)K >= 2LL * N && K % 256 == 0;
+  if (g_oxb_gemv_max_t > 0 && T <= g_oxb_gemv_max_t && !wide && (epi_mode == EPI_STORE || epi_mode == EPI_ADD_INTO) &&
       gemv_quant_supported(qtype, T, K, row_bytes, Wq, X, K))
     return gemv_quant_run(qtype, reinterpret_cast<const uint8_t*>(Wq), row_bytes, reinterpret_cast<const __nv_bfloat16*>(X), K,
                       reinterpret_cast<__nv_bfloat16*>(Y), ldY, bias, T, N, K, epi_mode == EPI_ADD_INTO, sm_count(), stream);

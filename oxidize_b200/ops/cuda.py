@@ -55,6 +55,7 @@ class KernelOptions:
     cluster_splitk: bool = True  # split-K partials meet in distributed shared memory instead of global scratch
     gemm_prefill_tn: int = 256  # token tile of prefill-sized GEMM calls: 128, 256, or 0 = by wave count
     gemv_max_tokens: int = 2  # packed-weight calls of at most this many tokens take the dp4a GEMV (0 = never)
+    gemv_wide: bool = False  # ... also for wide, short matrices (K >= 2N), where the split-K tensor-core kernel is faster
     ar_ll_min_world: int = 2  # rank counts from which the fused all-reduce uses the two-shot exchange
     # Packed-weight calls with more tokens than this decode the matrix to a bf16 staging buffer once and run the bf16
     # GEMM on it (every token tile of the fused kernel decodes the weight tile again); 0 = always the fused kernel.
@@ -70,6 +71,7 @@ def configure(opts: "KernelOptions") -> None:
     L.oxb_set_cluster_splitk(1 if opts.cluster_splitk else 0)
     L.oxb_set_gemm_prefill_tn(int(opts.gemm_prefill_tn))
     L.oxb_set_gemv_max_tokens(int(opts.gemv_max_tokens))
+    L.oxb_set_gemv_wide(1 if opts.gemv_wide else 0)
     L.oxb_set_ar_ll_min_world(int(opts.ar_ll_min_world))
     global mmq_max_tokens
     mmq_max_tokens = int(opts.mmq_max_tokens)
@@ -104,6 +106,7 @@ def _declare(L) -> None:
                                          vp, vp]
     L.oxb_row_sumsq.argtypes = [vp, i32, i32, i32, vp, vp, vp]
     L.oxb_set_gemv_max_tokens.argtypes = [i32]
+    L.oxb_set_gemv_wide.argtypes = [i32]
 
 
 def _check(code: int, what: str) -> None:

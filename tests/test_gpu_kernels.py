@@ -324,7 +324,8 @@ def test_gemv_packed_weights_small_batches(C, qtype, T, N, K):
     from oxidize_b200.models.weights import qtensor_from_dense
 
     L = C.lib()
-    default_max = L.oxb_set_gemv_max_tokens(8)  # the kernel covers up to 8 tokens; the default hands 5..8 to the GEMM
+    default_max = L.oxb_set_gemv_max_tokens(8)  # the kernel covers up to 8 tokens; the default hands 3..8 to the GEMM
+    default_wide = L.oxb_set_gemv_wide(1)       # ... and wide, short matrices at any token count
     torch.manual_seed(T * 7 + N)
     w = qtensor_from_dense(torch.randn(N, K) * 0.05, qtype, device="cuda")
     x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
@@ -350,6 +351,7 @@ def test_gemv_packed_weights_small_batches(C, qtype, T, N, K):
     got2 = C.linear(x2, [w])
     want2 = x2.float().cpu() @ w.to("cpu").dense_cache().t()
     L.oxb_set_gemv_max_tokens(default_max)
+    L.oxb_set_gemv_wide(default_wide)
     assert _rel_err(got2.cpu(), want2) < 1.2e-2
     _check_status(C)
 
