@@ -85,7 +85,7 @@ class LLM:
 
             _opcuda.configure(c.kernel_options)
         self.model = Transformer(weights, comm, fold_norms=c.fold_norms, fuse_qkv_rope=c.fuse_qkv_rope,
-                                 fuse_swiglu=c.fuse_swiglu, pipe=pipe)
+                                 fuse_swiglu=c.fuse_swiglu, pipe=pipe, max_context=c.max_model_len)
         self.device = self.model.device
         self.tokenizer = tokenizer
         kv_dtype = c.kv_cache_dtype

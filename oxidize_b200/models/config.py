@@ -15,12 +15,12 @@ from typing import Any, Dict, List, Optional
 from ..formats.gguf import GGUFFile
 
 # architecture strings accepted (reference arch-string map inference.rs:62-96)
-DENSE_ARCHS = {"llama", "mistral", "qwen2", "qwen3", "deepseek"}
+DENSE_ARCHS = {"llama", "mistral", "qwen2", "qwen3", "deepseek", "phi3"}  # phi3: Llama layers with fused qkv / gate-up tensors
 MOE_ARCHS = {"mixtral", "qwen2moe", "qwen3moe", "deepseek2", "deepseek-moe", "deepseek_moe"}
 # Architectures whose layers need math this engine does not have (GeGLU and embedding scaling, sandwich
-# norms, fused qkv with partial windows, recurrent or convolutional mixers): loading one would run it as
+# norms, parallel attention / MLP blocks, recurrent or convolutional mixers): loading one would run it as
 # a plain Llama and produce wrong tokens, so they are refused by name.
-UNSUPPORTED_ARCHS = {"gemma", "gemma2", "gemma3", "gemma4", "phi3", "phi", "llama4", "qwen35", "qwen3_5_moe", "mamba",
+UNSUPPORTED_ARCHS = {"gemma", "gemma2", "gemma3", "gemma4", "phi", "phi2", "llama4", "qwen35", "qwen3_5_moe", "mamba",
                      "lfm2", "glm4", "falcon", "gpt2", "bert"}
 
 
@@ -60,6 +60,7 @@ class ModelConfig:
     rope_theta: float = 10000.0
     rope_dim: int = 0  # 0 -> head_dim (full rotary)
     rope_pairing: str = "split_half"  # split_half (NeoX; what all reference engines do) | adjacent
+    rope_attn_factor: float = 1.0  # magnitude factor that goes with the long LongRoPE frequency factors (Phi-3)
     rope_scaling: RopeScaling = field(default_factory=RopeScaling)
     context_length: int = 8192
     sliding_window: int = 0
@@ -193,7 +194,8 @@ def config_from_gguf(g: GGUFFile) -> ModelConfig:
     c.sliding_window = int(_scalar(a("attention.sliding_window"), 0))
     c.sliding_window_pattern = int(_scalar(a("attention.sliding_window_pattern"), 0))
     c.qk_norm = g.has_tensor("blk.0.attn_q_norm.weight")
-    c.attn_bias = g.has_tensor("blk.0.attn_q.bias")
+    c.attn_bias = g.has_tensor("blk.0.attn_q.bias") or g.has_tensor("blk.0.attn_qkv.bias")
+    c.rope_attn_factor = float(_scalar(a("rope.scaling.attn_factor"), 1.0))
     c.tie_embeddings = not g.has_tensor("output.weight")
     # MoE
     c.n_experts = int(_scalar(a("expert_count"), 0))

@@ -74,7 +74,7 @@ class SingleRankComm:
 
 class Transformer:
     def __init__(self, weights: ModelWeights, comm=None, act_dtype: Optional[torch.dtype] = None, fold_norms: bool = False,
-                 fuse_qkv_rope: bool = True, fuse_swiglu: bool = True, pipe=None):
+                 fuse_qkv_rope: bool = True, fuse_swiglu: bool = True, pipe=None, max_context: int = 0):
         self.w = weights
         self.pipe = pipe  # parallel.pp.StageIO when this model holds one pipeline stage's layers
         self._sends: list = []  # activation sends still on the link
@@ -95,9 +95,15 @@ class Transformer:
             raise ValueError(f"ep_rank={weights.ep_rank} does not match this rank ({getattr(self.comm, 'rank', 0)})")
         self.n_heads_local = cfg.n_heads // tp
         self.n_kv_local = max(1, cfg.n_kv_heads // tp)
+        # frequency factors stored in the checkpoint; LongRoPE switches to its long set (and its magnitude factor) when
+        # the serving context exceeds the one the model was trained with
+        ff, mscale = weights.rope_freq_factors, opref.rope_mscale(cfg.rope_scaling)
+        orig_ctx = cfg.rope_scaling.original_context_length if cfg.rope_scaling is not None else 0
+        if weights.rope_freq_factors_long is not None and orig_ctx > 0 and (max_context or cfg.context_length) > orig_ctx:
+            ff, mscale = weights.rope_freq_factors_long, mscale * cfg.rope_attn_factor
         self.rope = RopeState(
-            inv_freq=opref.rope_inv_freq(cfg.rotary_dim, cfg.rope_theta, cfg.rope_scaling, device=dev),
-            pairing=cfg.rope_pairing, mscale=opref.rope_mscale(cfg.rope_scaling),
+            inv_freq=opref.rope_inv_freq(cfg.rotary_dim, cfg.rope_theta, cfg.rope_scaling, device=dev, freq_factors=ff),
+            pairing=cfg.rope_pairing, mscale=mscale,
             n_heads=self.n_heads_local, n_kv_heads=self.n_kv_local, head_dim=cfg.head_dim)
         self.attn_scale = cfg.head_dim ** -0.5
         self._fuse_qkv_rope = dev.type == "cuda" and fuse_qkv_rope

@@ -211,6 +211,10 @@ class ModelWeights:
     ep_size: int = 1
     first_layer: int = 0  # pipeline stage range [first_layer, first_layer+len(layers))
     vocab_start: int = 0  # first vocabulary row held by this rank's lm_head shard
+    # per-pair divisors of the rotary frequencies stored in the checkpoint (Llama-3.1 ``rope_freqs.weight``,
+    # Phi-3 LongRoPE ``rope_factors_short / _long.weight``), or None
+    rope_freq_factors: Optional[torch.Tensor] = None
+    rope_freq_factors_long: Optional[torch.Tensor] = None  # LongRoPE: used instead once the context exceeds the original one
 
     def nbytes(self) -> int:
         n = self.embed.nbytes() + self.lm_head.nbytes()
@@ -315,10 +319,20 @@ def _load_layer(src: GGUFWeightSource, cfg: ModelConfig, i: int, tp_rank: int, t
     q0, q1 = shard_range(cfg.n_heads, tp_rank, tp_size)
     k0, k1 = shard_range(cfg.n_kv_heads, tp_rank // kv_rep, kv_shards)
     qr, kr = (q0 * hd, q1 * hd), (k0 * hd, k1 * hd)
-    parts = [src.matrix(f"{p}.attn_q.weight", rows=qr), src.matrix(f"{p}.attn_k.weight", rows=kr),
-             src.matrix(f"{p}.attn_v.weight", rows=kr)]
+    if src.has(f"{p}.attn_qkv.weight"):
+        # one fused tensor (Phi-3): rows are all query heads, then all key heads, then all value heads
+        ko, vo = cfg.n_heads * hd, (cfg.n_heads + cfg.n_kv_heads) * hd
+        parts = [src.matrix(f"{p}.attn_qkv.weight", rows=qr), src.matrix(f"{p}.attn_qkv.weight", rows=(ko + kr[0], ko + kr[1])),
+                 src.matrix(f"{p}.attn_qkv.weight", rows=(vo + kr[0], vo + kr[1]))]
+    else:
+        parts = [src.matrix(f"{p}.attn_q.weight", rows=qr), src.matrix(f"{p}.attn_k.weight", rows=kr),
+                 src.matrix(f"{p}.attn_v.weight", rows=kr)]
     bias = None
-    if src.has(f"{p}.attn_q.bias"):
+    if src.has(f"{p}.attn_qkv.bias"):
+        b = src.vector(f"{p}.attn_qkv.bias")
+        ko, vo = cfg.n_heads * hd, (cfg.n_heads + cfg.n_kv_heads) * hd
+        bias = torch.cat([b[qr[0]:qr[1]], b[ko + kr[0]:ko + kr[1]], b[vo + kr[0]:vo + kr[1]]])
+    elif src.has(f"{p}.attn_q.bias"):
         bias = torch.cat([src.vector(f"{p}.attn_q.bias")[qr[0]:qr[1]], src.vector(f"{p}.attn_k.bias")[kr[0]:kr[1]],
                           src.vector(f"{p}.attn_v.bias")[kr[0]:kr[1]]])
     lw = LayerWeights(
@@ -353,6 +367,13 @@ def _load_layer(src: GGUFWeightSource, cfg: ModelConfig, i: int, tp_rank: int, t
             lw.shared_down = LinearWeight([src.matrix(f"{p}.ffn_down_shexp.weight", cols=(f0, f1))])
             if src.has(f"{p}.ffn_gate_inp_shexp.weight"):
                 lw.shared_gate = src.matrix(f"{p}.ffn_gate_inp_shexp.weight")
+    elif not src.has(f"{p}.ffn_gate.weight"):
+        # fused gate / up tensor (Phi-3): the first half of the rows is the gate, the second half the up projection
+        ffn = src.g.tensors[f"{p}.ffn_up.weight"].shape[0] // 2
+        f0, f1 = shard_range(ffn, tp_rank, tp_size)
+        lw.w_gate_up = LinearWeight(fuse_rows([src.matrix(f"{p}.ffn_up.weight", rows=(f0, f1)),
+                                               src.matrix(f"{p}.ffn_up.weight", rows=(ffn + f0, ffn + f1))]))
+        lw.w_down = LinearWeight([src.matrix(f"{p}.ffn_down.weight", cols=(f0, f1))])
     else:
         ffn = src.g.tensors[f"{p}.ffn_gate.weight"].shape[0]
         f0, f1 = shard_range(ffn, tp_rank, tp_size)
@@ -378,6 +399,12 @@ def load_weights(g: GGUFFile, cfg: ModelConfig, device="cpu", act_dtype: torch.d
     lm_head = LinearWeight([src.matrix(head_name, rows=(v0, v1))])
     mw = ModelWeights(cfg, embed, layers, src.vector("output_norm.weight"), lm_head, [], tp_rank, tp_size,
                       ep_rank, ep_size, l0, v0)
+    if src.has("rope_freqs.weight"):
+        mw.rope_freq_factors = src.vector("rope_freqs.weight")
+    elif src.has("rope_factors_short.weight"):
+        mw.rope_freq_factors = src.vector("rope_factors_short.weight")
+        if src.has("rope_factors_long.weight"):
+            mw.rope_freq_factors_long = src.vector("rope_factors_long.weight")
     for j in range(cfg.nextn_layers):
         L = cfg.n_layers + j
         p = f"blk.{L}.nextn"

@@ -79,8 +79,10 @@ def gelu_mul(gate_up: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------- rope
 
 
-def rope_inv_freq(rotary_dim: int, theta: float, scaling=None, device=None) -> torch.Tensor:
-    """Per-pair inverse frequencies [rotary_dim/2] with optional linear / YaRN scaling."""
+def rope_inv_freq(rotary_dim: int, theta: float, scaling=None, device=None, freq_factors=None) -> torch.Tensor:
+    """Per-pair inverse frequencies [rotary_dim/2] with optional linear / YaRN scaling.  ``freq_factors``
+    ([rotary_dim/2], from a ``rope_freqs.weight`` / ``rope_factors_*.weight`` tensor of the checkpoint) divides each
+    frequency: that is how Llama-3.1-style and LongRoPE context extensions are stored in GGUF files."""
     half = rotary_dim // 2
     idx = torch.arange(half, dtype=torch.float64, device=device)
     inv = theta ** (-2.0 * idx / rotary_dim)
@@ -97,6 +99,11 @@ def rope_inv_freq(rotary_dim: int, theta: float, scaling=None, device=None) -> t
         ramp = ((idx - lo) / max(hi - lo, 1e-3)).clamp(0, 1)
         mix = 1.0 - ramp  # 1 => extrapolate (keep), 0 => interpolate
         inv = inv / scaling.factor * (1 - mix) + inv * mix
+    if freq_factors is not None:
+        ff = torch.as_tensor(freq_factors, dtype=torch.float64, device=inv.device).reshape(-1)
+        if ff.numel() < half:
+            raise ValueError(f"rope frequency factors have {ff.numel()} entries, the rotary half dimension is {half}")
+        inv = inv / ff[:half]
     return inv.float()
 
 

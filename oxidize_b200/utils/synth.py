@@ -124,7 +124,8 @@ def write_config_metadata(w: GGUFWriter, cfg: ModelConfig) -> None:
 
 
 def synth_gguf(path: str, cfg: ModelConfig, quant: str = "Q4_K_M", seed: int = 0, tokenizer: bool = True,
-               norm_jitter: float = 0.0, device=None, embed_type: Optional[str] = None) -> str:
+               norm_jitter: float = 0.0, device=None, embed_type: Optional[str] = None, fused_layout: bool = False,
+               rope_freqs: Optional[np.ndarray] = None) -> str:
     """Write a random-init GGUF of shape ``cfg``; matrices N(0, 0.02) encoded per ``quant``
     (``Q4_K_M`` = llama.cpp-style Q4_K/Q6_K mix), norms f32 ones.
 
@@ -133,7 +134,9 @@ def synth_gguf(path: str, cfg: ModelConfig, quant: str = "Q4_K_M", seed: int = 0
     multi-billion-parameter shape takes into the time of the file write.  ``embed_type`` stores the
     token-embedding table in another type than ``quant`` picks (the reference's CUDA backend has no row
     lookup for a bf16 / f16 table: ``oxidize-c/src/backends/cuda.cu`` ``cuda_embed`` hands every "packed"
-    table to ``oc_cuda_mmq_get_row``, which knows the block-quantized types only)."""
+    table to ``oc_cuda_mmq_get_row``, which knows the block-quantized types only).  ``fused_layout`` writes the
+    Phi-3 tensor layout (one ``attn_qkv`` and one gate-then-up ``ffn_up`` tensor per layer) with the SAME values a
+    plain file of the same seed holds; ``rope_freqs`` adds a ``rope_freqs.weight`` tensor of per-pair divisors."""
     rng = np.random.default_rng(seed)
     dev = torch.device(device) if device is not None else None
     tgen = None
@@ -147,7 +150,7 @@ def synth_gguf(path: str, cfg: ModelConfig, quant: str = "Q4_K_M", seed: int = 0
     h, hd = cfg.hidden_size, cfg.head_dim
     L = cfg.n_layers
 
-    def mat(gname: str, kind: str, layer: int, out_f: int, in_f: int, n_exp: int = 0):
+    def mat(gname: str, kind: str, layer: int, out_f: int, in_f: int, n_exp: int = 0, add: bool = True):
         t = pick_type(quant, kind, layer, L, in_f)
         if kind == "token_embd" and embed_type:
             t = embed_type.upper()
@@ -162,7 +165,18 @@ def synth_gguf(path: str, cfg: ModelConfig, quant: str = "Q4_K_M", seed: int = 0
             x = np.random.default_rng(sd).standard_normal(n, dtype=np.float32) * WEIGHT_STD
             return qref.quantize(t, x)
 
-        w.add_tensor(gname, gen, shape, t)
+        if add:
+            w.add_tensor(gname, gen, shape, t)
+        return gen, t
+
+    def fused(gname: str, pieces, in_f: int):
+        """One tensor whose rows are the rows of `pieces` [(gen, type, out_f)] one after the other."""
+        types = {t for _, t, _ in pieces}
+        if len(types) != 1:
+            raise ValueError(f"{gname}: the fused pieces have different encodings {sorted(types)}")
+        gens = [g_ for g_, _, _ in pieces]
+        w.add_tensor(gname, lambda gens=gens: np.concatenate([np.asarray(g_()).reshape(-1).view(np.uint8) for g_ in gens]),
+                     (sum(o for _, _, o in pieces), in_f), types.pop())
 
     def vec(gname: str, n: int):
         v = np.ones(n, dtype=np.float32)
@@ -174,9 +188,11 @@ def synth_gguf(path: str, cfg: ModelConfig, quant: str = "Q4_K_M", seed: int = 0
     for i in range(L + cfg.nextn_layers):
         p = f"blk.{i}"
         vec(f"{p}.attn_norm.weight", h)
-        mat(f"{p}.attn_q.weight", "attn_q", i, cfg.q_size, h)
-        mat(f"{p}.attn_k.weight", "attn_k", i, cfg.kv_size, h)
-        mat(f"{p}.attn_v.weight", "attn_v", i, cfg.kv_size, h)
+        gq = mat(f"{p}.attn_q.weight", "attn_q", i, cfg.q_size, h, add=not fused_layout)
+        gk = mat(f"{p}.attn_k.weight", "attn_k", i, cfg.kv_size, h, add=not fused_layout)
+        gv = mat(f"{p}.attn_v.weight", "attn_v", i, cfg.kv_size, h, add=not fused_layout)
+        if fused_layout:
+            fused(f"{p}.attn_qkv.weight", [(*gq, cfg.q_size), (*gk, cfg.kv_size), (*gv, cfg.kv_size)], h)
         mat(f"{p}.attn_output.weight", "attn_output", i, h, cfg.q_size)
         if cfg.qk_norm:
             vec(f"{p}.attn_q_norm.weight", hd)
@@ -202,8 +218,10 @@ def synth_gguf(path: str, cfg: ModelConfig, quant: str = "Q4_K_M", seed: int = 0
                     w.add_tensor(f"{p}.ffn_gate_inp_shexp.weight",
                                  (rng.standard_normal((1, h)) * WEIGHT_STD).astype(np.float32), (1, h), "F32")
         else:
-            mat(f"{p}.ffn_gate.weight", "ffn_gate", i, cfg.ffn_size, h)
-            mat(f"{p}.ffn_up.weight", "ffn_up", i, cfg.ffn_size, h)
+            gg = mat(f"{p}.ffn_gate.weight", "ffn_gate", i, cfg.ffn_size, h, add=not fused_layout)
+            gu = mat(f"{p}.ffn_up.weight", "ffn_up", i, cfg.ffn_size, h, add=not fused_layout)
+            if fused_layout:
+                fused(f"{p}.ffn_up.weight", [(*gg, cfg.ffn_size), (*gu, cfg.ffn_size)], h)
             mat(f"{p}.ffn_down.weight", "ffn_down", i, h, cfg.ffn_size)
         if i >= L:
             q = f"{p}.nextn"
@@ -212,6 +230,8 @@ def synth_gguf(path: str, cfg: ModelConfig, quant: str = "Q4_K_M", seed: int = 0
             mat(f"{q}.eh_proj.weight", "attn_q", i, h, 2 * h)
             vec(f"{q}.shared_head_norm.weight", h)
     vec("output_norm.weight", h)
+    if rope_freqs is not None:
+        w.add_tensor("rope_freqs.weight", np.asarray(rope_freqs, dtype=np.float32), (len(rope_freqs),), "F32")
     if not cfg.tie_embeddings:
         mat("output.weight", "output", 0, cfg.vocab_size, h)
     w.write()

@@ -705,3 +705,59 @@ def test_interleaved_local_global_attention_layers(tmp_path):
     assert torch.allclose(all_global, full, atol=1e-5)
     assert not torch.allclose(uniform, full, atol=1e-4)
     assert not torch.allclose(mixed, full, atol=1e-4) and not torch.allclose(mixed, uniform, atol=1e-4)
+
+
+def test_phi3_fused_tensor_layout_gives_the_same_logits_as_the_split_layout(tmp_path):
+    """A Phi-3 checkpoint stores one attn_qkv tensor and one gate-then-up ffn_up tensor per layer; loaded (also
+    sharded two ways) it must compute exactly what the same weights in the Llama layout compute."""
+    import dataclasses
+
+    from oxidize_b200.formats.gguf import load_gguf
+    from oxidize_b200.models.config import config_from_gguf
+    from oxidize_b200.models.weights import load_weights
+
+    cfg = preset("tiny-llama", n_layers=2, vocab_size=97, hidden_size=64, n_heads=4, n_kv_heads=2, head_dim=16, ffn_size=96)
+    plain, fused = str(tmp_path / "plain.gguf"), str(tmp_path / "phi3.gguf")
+    synth_gguf(plain, cfg, "F32", seed=4, norm_jitter=0.2)
+    synth_gguf(fused, dataclasses.replace(cfg, arch="phi3"), "F32", seed=4, norm_jitter=0.2, fused_layout=True)
+    g = load_gguf(fused)
+    assert g.has_tensor("blk.0.attn_qkv.weight") and not g.has_tensor("blk.0.attn_q.weight")
+    assert not g.has_tensor("blk.0.ffn_gate.weight")
+    c2 = config_from_gguf(g)
+    assert c2.arch == "phi3" and c2.ffn_size == 96 and c2.n_kv_heads == 2
+    ec = EngineConfig(max_model_len=64, max_num_seqs=2, num_kv_blocks=32, prefill_chunk_size=32, max_num_batched_tokens=32)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    prompts = [[5, 9, 20, 31, 7], list(range(3, 30))]
+    a = [o.token_ids for o in LLM.from_gguf(plain, ec, device="cpu").generate(prompts, sp)]
+    b = [o.token_ids for o in LLM.from_gguf(fused, ec, device="cpu").generate(prompts, sp)]
+    assert a == b
+    # the shard of a fused tensor is the same rows the split tensors give
+    w_plain = load_weights(load_gguf(plain), cfg, "cpu", torch.float32, 1, 2)
+    w_fused = load_weights(g, c2, "cpu", torch.float32, 1, 2)
+    for la, lb in zip(w_plain.layers, w_fused.layers):
+        for pa, pb in zip(la.wqkv.parts + la.w_gate_up.parts, lb.wqkv.parts + lb.w_gate_up.parts):
+            assert torch.equal(pa.data, pb.data)
+
+
+def test_rope_frequency_factors_of_the_checkpoint_are_applied(tmp_path):
+    """rope_freqs.weight (Llama-3.1 and later) divides the rotary frequencies pair by pair."""
+    from oxidize_b200.ops import ref as opref
+
+    cfg = preset("tiny-llama", n_layers=2, vocab_size=97, hidden_size=64, n_heads=4, n_kv_heads=2, head_dim=16, ffn_size=96)
+    factors = np.array([1.0, 1.0, 1.0, 2.0, 4.0, 8.0, 8.0, 8.0], dtype=np.float32)
+    p0, p1 = str(tmp_path / "plain.gguf"), str(tmp_path / "scaled.gguf")
+    synth_gguf(p0, cfg, "F32", seed=4, norm_jitter=0.2)
+    synth_gguf(p1, cfg, "F32", seed=4, norm_jitter=0.2, rope_freqs=factors)
+    ec = EngineConfig(max_model_len=64, max_num_seqs=2, num_kv_blocks=32, prefill_chunk_size=64, max_num_batched_tokens=64)
+    l0, l1 = LLM.from_gguf(p0, ec, device="cpu"), LLM.from_gguf(p1, ec, device="cpu")
+    base = opref.rope_inv_freq(16, cfg.rope_theta)
+    assert torch.allclose(l0.model.rope.inv_freq, base)
+    assert torch.allclose(l1.model.rope.inv_freq, base / torch.from_numpy(factors))
+    sp = SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True)
+    for llm in (l0, l1):
+        llm.runner.keep_logits = True
+        llm.add_request(list(range(3, 40)), sp)
+        llm.step()
+    assert not torch.allclose(l0.last_step[1].logits.float(), l1.last_step[1].logits.float(), atol=1e-4)
+    with pytest.raises(ValueError):
+        opref.rope_inv_freq(16, 10000.0, freq_factors=[1.0, 2.0])
