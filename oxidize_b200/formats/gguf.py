@@ -560,6 +560,8 @@ _HF_LAYER_MAP = {
     "self_attn.k_proj.weight": "attn_k.weight",
     "self_attn.v_proj.weight": "attn_v.weight",
     "self_attn.o_proj.weight": "attn_output.weight",
+    "self_attn.qkv_proj.weight": "attn_qkv.weight",  # Phi-3: fused projections, kept fused in the file
+    "mlp.gate_up_proj.weight": "ffn_up.weight",      # Phi-3: gate rows then up rows
     "self_attn.q_proj.bias": "attn_q.bias",
     "self_attn.k_proj.bias": "attn_k.bias",
     "self_attn.v_proj.bias": "attn_v.bias",
