@@ -51,6 +51,8 @@ def parse_args():
     ap.add_argument("--shard-sim", type=int, default=0,
                     help="debug only: run ONE rank's shard shapes of an N-way tensor-parallel job on one GPU, without "
                          "collectives (marks the result invalid); used to profile per-GPU kernels of the TP8 config")
+    ap.add_argument("--max-batched-tokens", type=int, default=0,
+                    help="token budget of one engine step (prefill chunks + decode rows); 0 = chosen from the per-rank shapes")
     ap.add_argument("--no-prefill", action="store_true",
                     help="fill the KV cache with random pages instead of running the prompts through prefill")
     ap.add_argument("--no-workload", action="store_true",
@@ -205,7 +207,7 @@ def main():
         else:
             run_workload = False
     ec = EngineConfig(kv_cache_dtype=args.kv_dtype, kv_page_size=page, num_kv_blocks=nblocks, max_model_len=max_len,
-                      max_num_seqs=B, max_num_batched_tokens=max(B, 2048 if not args.no_prefill else B),
+                      max_num_seqs=B, max_num_batched_tokens=(B if args.no_prefill else (max(B, args.max_batched_tokens) if args.max_batched_tokens > 0 else 0)),
                       prefill_chunk_size=512, enable_prefix_cache=False, tp_size=world, ep_size=world,
                       fold_norms=args.fold_norms and not args.no_fold_norms, async_decode=not args.sync_decode)
     llm = LLM(weights, ec, comm)
@@ -245,6 +247,7 @@ def main():
 
     sp = SamplingParams(temperature=0.0, max_tokens=total_steps + 8, ignore_eos=True)
     ttft_p50 = None
+    prefill_s = None
     if args.no_prefill:
         # place every sequence directly in the running state with a random-filled context
         from oxidize_b200.engine.scheduler import SeqStatus, Sequence
@@ -272,6 +275,8 @@ def main():
                 if ro.token_ids and ro.request_id not in first:
                     first[ro.request_id] = time.perf_counter() - t_pf
         ttft_p50 = float(np.median(list(first.values()))) if first else None
+        torch.cuda.synchronize()
+        prefill_s = time.perf_counter() - t_pf
     torch.cuda.synchronize()
 
     def barrier():
@@ -405,12 +410,13 @@ def main():
                        "kv_cache": f"paged, {page}-token pages, {args.kv_dtype}", "comm": args.comm if world > 1 else "none",
                        "l2_policy": "inputs larger than L2 (weight shard + KV pages streamed every step)",
                        "layers": cfg.n_layers, "valid": not bool(args.layers or args.shard_sim),
-                       "async_decode": not args.sync_decode},
+                       "async_decode": not args.sync_decode, "step_token_budget": llm.config.max_num_batched_tokens},
             "e2e": {"value": round(e2e_val, 2), "unit": "tok/s", "ms_per_step": round(max(e2e_ms, e2e_wall_ms) / args.steps, 4),
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": int(launches_per_step * args.steps) if graph is not None else int(C.launch_count),
             "clocks": sampler.summary(),
             "workload": workload, "speculative": spec_out, "steady_state_prefill_ttft_p50_s": ttft_p50,
+            "steady_state_prefill_s": round(prefill_s, 4) if prefill_s else None,
             "ttft_p50_s": workload["ttft_p50_s"] if workload else ttft_p50, "bs1_tok_s": round(1e3 / bs1_ms, 2) if bs1_ms > 0 else None,
             "bs1_ms_per_step": round(bs1_ms, 4), "load_s": round(load_s, 1),
             "device_status": {"code": code, "detail": detail, "count": count},

@@ -94,7 +94,7 @@ def build_parser() -> argparse.ArgumentParser:
     a("--parallelism", default="tensor", choices=["pipeline", "tensor"])
     a("--kv-page-size", type=int, default=16)
     a("--max-running", type=int, default=0)
-    a("--max-batched-tokens", type=int, default=2048)
+    a("--max-batched-tokens", type=int, default=0, help="tokens per engine step; 0 = chosen from the model's shapes")
     a("--fused-comm", default="on", choices=["on", "off"])
     a("--weights-dtype", default="auto", choices=["auto", "bf16", "fp8", "nvfp4"])
     a("--rope-pairing", default=None, choices=["split_half", "adjacent"])

@@ -37,7 +37,7 @@ class EngineConfig:
     gpu_memory_utilization: float = 0.90
     max_model_len: int = 4096
     max_num_seqs: int = 64
-    max_num_batched_tokens: int = 2048
+    max_num_batched_tokens: int = 2048  # tokens per step (prefill chunks + decode rows); 0 = pick by tile waves (autotune)
     prefill_chunk_size: int = 512
     policy: str = "fcfs"
     enable_prefix_cache: bool = True
@@ -80,6 +80,10 @@ class LLM:
             raise ValueError("pp_size > 1 needs the stage's StageIO (parallel.pp.make_pipeline_groups) and vice versa")
         self.weights = weights
         self.cfg: ModelConfig = weights.cfg
+        if c.max_num_batched_tokens <= 0:
+            from ..utils.autotune import prefill_token_budget
+
+            c.max_num_batched_tokens = max(prefill_token_budget(self.cfg, max(c.tp_size, 1)), c.max_num_seqs)
         if weights.embed.device.type == "cuda" and c.kernel_options is not None:
             from ..ops import cuda as _opcuda
 

@@ -203,3 +203,19 @@ def test_decode_profiler_and_value_trace(tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     assert "[trace] layer   1" in r.stderr
     assert "operator" in r.stderr and "linear" in r.stderr and "paged_attention" in r.stderr
+
+
+def test_prefill_token_budget_follows_tile_waves():
+    """The step's token budget is picked so that the projections' tile grids fill whole waves of SMs."""
+    from oxidize_b200.models.config import preset
+    from oxidize_b200.utils.autotune import prefill_token_budget
+
+    big = preset("llama3-70b")
+    # per-rank shapes change with the tensor-parallel degree, and so does the best budget
+    got = {tp: prefill_token_budget(big, tp) for tp in (1, 2, 4, 8)}
+    assert all(2048 <= v <= 3072 and v % 256 == 0 for v in got.values())
+    assert got[1] == 2304  # nine token tiles fill the last wave of every projection better than eight
+    # a toy model whose grids never fill one wave: the wave is paid anyway, so the largest budget is the most efficient
+    tiny = preset("tiny-llama")
+    assert prefill_token_budget(tiny, 1) == 3072
+    assert prefill_token_budget(big, 8, lo=1024, hi=1024) == 1024
