@@ -473,9 +473,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   float* tok_scale = reinterpret_cast<float*>(bars + 512);         // [TN]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * GEMM_BM;
+  // Plain launches with several token tiles walk the tile grid token-major: consecutive CTAs (one wave holds 148 of
+  // them) share a weight tile and differ in the token tile, so a wave touches few weight tiles and all activation
+  // tiles, both of which then stay in the L2, instead of every weight tile of the matrix in every wave.
+  int tile_n = blockIdx.x, tile_t = blockIdx.z;
+  if (!gr.enabled && gridDim.z > 1 && gridDim.y == 1) {
+    const int lin = blockIdx.z * gridDim.x + blockIdx.x;
+    tile_n = lin / (int)gridDim.z;
+    tile_t = lin % (int)gridDim.z;
+  }
+  const int n0 = tile_n * GEMM_BM;
   const int split = blockIdx.y;
-  const int t0 = gathered ? ((int)blockIdx.z % gr.t_tiles) * TN : (gr.enabled ? 0 : blockIdx.z * TN);
+  const int t0 = gathered ? ((int)blockIdx.z % gr.t_tiles) * TN : (gr.enabled ? 0 : tile_t * TN);
   const int w_row0 = n0 + zg * gr.w_rows;  // first weight row of this tile in the (stacked) matrix
   const int x_row0 = gathered ? g_row0 + t0 : t0 + zg * gr.x_rows;
   const int kb_total = (K + GEMM_BK - 1) / GEMM_BK;
@@ -791,7 +800,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         tok_scale[j] = rsqrtf(s * nm.inv_dim + nm.eps);
       }
     }
-    if (nm.clear != nullptr && blockIdx.x == 0 && blockIdx.y == 0) {
+    if (nm.clear != nullptr && tile_n == 0 && blockIdx.y == 0) {
       // the accumulator that the next producer adds into: its last reader finished before this grid's dependency
       const int tt = gr.enabled ? T : min(TN, T - t0);
       for (int j = etid; j < tt; j += 128) nm.clear[(size_t)(t0 + j) * SUMSQ_STRIDE] = 0ull;
