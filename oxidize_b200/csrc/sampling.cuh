@@ -41,6 +41,74 @@ struct BlockScan {
   }
 };
 
+// f(i, row[i]) for every i < V, the block's threads striding over the row.  Rows that start on a 16-byte boundary are
+// read as float4 with four loads in flight per thread: a pass is a stream of the row out of the L2, and one scalar
+// load per iteration leaves every thread waiting out a full memory latency per element.
+template <class F>
+__device__ __forceinline__ void row_for_each(const float* __restrict__ row, int V, F f) {
+  if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const float4* r4 = reinterpret_cast<const float4*>(row);
+    const int n4 = V >> 2;
+#pragma unroll 4
+    for (int q = threadIdx.x; q < n4; q += blockDim.x) {
+      const float4 v = r4[q];
+      f(4 * q, v.x);
+      f(4 * q + 1, v.y);
+      f(4 * q + 2, v.z);
+      f(4 * q + 3, v.w);
+    }
+    for (int i = (n4 << 2) + threadIdx.x; i < V; i += blockDim.x) f(i, row[i]);
+  } else {
+#pragma unroll 4
+    for (int i = threadIdx.x; i < V; i += blockDim.x) f(i, row[i]);
+  }
+}
+
+// First index (in index order) at which the running total of weight(i) exceeds `target`, or 0x7fffffff.  Every thread
+// sums a contiguous slice of the row, ONE block scan orders the slices, and the thread whose slice holds the crossing
+// walks it again: two passes over the row and three block barriers, whatever the vocabulary size (a scan per 1024
+// elements costs 125 scans for a 128 k vocabulary).  *s_out must hold 0x7fffffff on entry (set before a barrier).
+template <class Weight>
+__device__ __forceinline__ int locate_in_index_order(const float* __restrict__ row, int V, float target, Weight weight,
+                                                     float* red, int* s_out) {
+  const int per = (((V + (int)blockDim.x - 1) / (int)blockDim.x) + 3) & ~3;  // slices start on multiples of four
+  const int b = min((int)threadIdx.x * per, V), e = min(b + per, V);
+  const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+  auto slice = [&](auto&& g) {  // g(i, row[i]) over this thread's slice, in index order
+    int i = b;
+    if (vec) {
+#pragma unroll 2
+      for (; i + 4 <= e; i += 4) {
+        const float4 v = *reinterpret_cast<const float4*>(row + i);
+        if (!g(i, v.x) || !g(i + 1, v.y) || !g(i + 2, v.z) || !g(i + 3, v.w)) return;
+      }
+    }
+    for (; i < e; ++i)
+      if (!g(i, row[i])) return;
+  };
+  float local = 0.f;
+  slice([&](int i, float v) {
+    local += weight(i, v);
+    return true;
+  });
+  const float2 sc = BlockScan::run(local, red);
+  const float before = sc.x - local;
+  if (local > 0.f && sc.x > target && before <= target) {
+    float run = before;
+    slice([&](int i, float v) {
+      const float w = weight(i, v);
+      if (w > 0.f && run + w > target) {
+        atomicMin(s_out, i);
+        return false;
+      }
+      run += w;
+      return true;
+    });
+  }
+  __syncthreads();
+  return *s_out;
+}
+
 // monotone map float -> uint32 (larger float -> larger uint); probabilities are >= 0
 __device__ __forceinline__ uint32_t prob_bits(float p) { return __float_as_uint(p); }
 
@@ -73,12 +141,12 @@ __device__ __forceinline__ void radix_pass(const float* __restrict__ row, int V,
       wmass[i] = 0.f;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const float p = __expf((row[i] - mx) * inv_t);
+    row_for_each(row, V, [&](int, float v) {
+      const float p = __expf((v - mx) * inv_t);
       const int bin = min((int)(prob_bits(p) >> 24), 63);
       atomicAdd(&wcnt[warp * 64 + bin], 1);
       atomicAdd(&wmass[warp * 64 + bin], p);
-    }
+    });
     __syncthreads();
     if (threadIdx.x < 64) {
       int c = 0;
@@ -98,15 +166,15 @@ __device__ __forceinline__ void radix_pass(const float* __restrict__ row, int V,
   }
   __syncthreads();
   const int shift = 24 - done_bits;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float p = __expf((row[i] - mx) * inv_t);
+  row_for_each(row, V, [&](int, float v) {
+    const float p = __expf((v - mx) * inv_t);
     const uint32_t b = prob_bits(p);
     if ((b >> (32 - done_bits)) == (prefix >> (32 - done_bits))) {
       const int bin = (b >> shift) & 0xFF;
       atomicAdd(&cnt[bin], 1);
       atomicAdd(&mass[bin], p);
     }
-  }
+  });
   __syncthreads();
 }
 
@@ -121,19 +189,50 @@ __device__ void radix_descend(const float* row, int V, float mx, float inv_t, in
   float ma = 0.f;
   for (int done = 0; done < 32; done += 8) {
     radix_pass(row, V, mx, inv_t, prefix, done, cnt, mass, wcnt, wmass);
-    if (threadIdx.x == 0) {
-      int c = ca;
-      float m = ma;
-      int bin = 255;
-      for (; bin > 0; --bin) {
-        // stop in the first bin (from the top) where the boundary falls
-        if (c + cnt[bin] >= count_limit || m + mass[bin] >= mass_limit) break;
-        c += cnt[bin];
-        m += mass[bin];
+    if (threadIdx.x < 32) {
+      // Walk the 256 bins from the top until the boundary falls inside one; bin 0 ends the walk in any case.  One
+      // warp does it: lane l sums bins 255 - 8l .. 248 - 8l, a shuffle scan gives every lane the totals above its
+      // bins, each lane then looks for the crossing among its own eight, and the lowest lane that finds one wins.
+      const int lane = threadIdx.x;
+      int lc = 0;
+      float lm = 0.f;
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        lc += cnt[255 - (lane * 8 + t)];
+        lm += mass[255 - (lane * 8 + t)];
       }
-      s_i[0] = bin;
-      s_i[1] = c;
-      s_f[0] = m;
+      int pc = lc;
+      float pm = lm;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int yc = __shfl_up_sync(0xffffffffu, pc, o);
+        const float ym = __shfl_up_sync(0xffffffffu, pm, o);
+        if (lane >= o) {
+          pc += yc;
+          pm += ym;
+        }
+      }
+      int c = ca + pc - lc;
+      float m = ma + pm - lm;
+      int found = -1;
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        const int bin = 255 - (lane * 8 + t);
+        if (found < 0) {
+          if (bin == 0 || c + cnt[bin] >= count_limit || m + mass[bin] >= mass_limit) {
+            found = bin;
+          } else {
+            c += cnt[bin];
+            m += mass[bin];
+          }
+        }
+      }
+      const unsigned hit = __ballot_sync(0xffffffffu, found >= 0);
+      if (lane == __ffs(hit) - 1) {
+        s_i[0] = found;
+        s_i[1] = c;
+        s_f[0] = m;
+      }
     }
     __syncthreads();
     prefix |= (uint32_t)s_i[0] << (24 - done);
@@ -167,15 +266,15 @@ sample_kernel(const float* __restrict__ logits, int V, int ld, const float* __re
   // ---- max (and greedy argmax)
   float mx = -INFINITY;
   int bi = -1;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = row[i];
+  row_for_each(row, V, [&](int i, float v) {
+    // a thread visits its indices in increasing order, so "later wins ties" is the highest-index rule
     if (bi < 0 || v > mx || (v == mx && tie_highest)) {
       if (!(v != v)) {
         mx = v;
         bi = i;
       }
     }
-  }
+  });
   {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     __shared__ float sv[32];
@@ -227,7 +326,7 @@ sample_kernel(const float* __restrict__ logits, int V, int ld, const float* __re
   const float inv_t = 1.f / T;
   // ---- total mass
   float part = 0.f;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) part += __expf((row[i] - mx) * inv_t);
+  row_for_each(row, V, [&](int, float v) { part += __expf((v - mx) * inv_t); });
   const float total = block_sum(part, red);
   if (!(total > 0.f) || !isfinite(total)) {
     if (threadIdx.x == 0) out[r] = s_best;
@@ -240,18 +339,8 @@ sample_kernel(const float* __restrict__ logits, int V, int ld, const float* __re
   if (!filtered) {
     // inverse CDF in index order
     const float target = rnd * total;
-    float run = 0.f;
-    for (int base = 0; base < V; base += blockDim.x) {
-      const int i = base + threadIdx.x;
-      const float p = i < V ? __expf((row[i] - mx) * inv_t) : 0.f;
-      const float2 sc = BlockScan::run(p, red);
-      const float incl = run + sc.x;
-      if (i < V && incl > target && incl - p <= target) atomicMin(&s_i[2], i);
-      run += sc.y;
-      __syncthreads();
-      if (s_i[2] != 0x7fffffff) break;
-    }
-    if (threadIdx.x == 0) out[r] = s_i[2] == 0x7fffffff ? V - 1 : s_i[2];
+    const int tok = locate_in_index_order(row, V, target, [&](int, float v) { return __expf((v - mx) * inv_t); }, red, &s_i[2]);
+    if (threadIdx.x == 0) out[r] = tok == 0x7fffffff ? V - 1 : tok;
     return;
   }
   // ---- filtered: find the end of the kept prefix of the descending order
@@ -278,19 +367,17 @@ sample_kernel(const float* __restrict__ logits, int V, int ld, const float* __re
     admit = max(0, min(room_k, by_p));
     if (c_above == 0 && admit == 0) admit = 1;  // always keep the top token
   }
-  // kept sum
+  // kept sum and size of the tie group, one pass
   float ks = 0.f;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float p = __expf((row[i] - mx) * inv_t);
-    if (prob_bits(p) > xb && p >= pmin_keep) ks += p;
-  }
+  int tc = 0;
+  row_for_each(row, V, [&](int, float v) {
+    const float p = __expf((v - mx) * inv_t);
+    const uint32_t pb = prob_bits(p);
+    if (pb > xb && p >= pmin_keep) ks += p;
+    tc += pb == xb;
+  });
   float kept = block_sum(ks, red);
-  int tie_total = 0;
-  {
-    int tc = 0;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) tc += prob_bits(__expf((row[i] - mx) * inv_t)) == xb;
-    tie_total = (int)(block_sum((float)tc, red) + 0.5f);
-  }
+  const int tie_total = (int)(block_sum((float)tc, red) + 0.5f);
   const bool ties_pass_minp = px >= pmin_keep;
   const int tie_kept = ties_pass_minp ? min(admit, tie_total) : 0;
   kept += (float)tie_kept * px;
@@ -314,17 +401,8 @@ sample_kernel(const float* __restrict__ logits, int V, int ld, const float* __re
   // select the j-th token (by index) with bits == yb
   if (threadIdx.x == 0) s_i[2] = 0x7fffffff;
   __syncthreads();
-  int seen = 0;
-  for (int base = 0; base < V; base += blockDim.x) {
-    const int i = base + threadIdx.x;
-    const int hit = (i < V && prob_bits(__expf((row[i] - mx) * inv_t)) == yb) ? 1 : 0;
-    const float2 sc = BlockScan::run((float)hit, red);
-    const int incl = seen + (int)(sc.x + 0.5f);
-    if (hit && incl - 1 == j) s_i[2] = i;
-    seen += (int)(sc.y + 0.5f);
-    __syncthreads();
-    if (s_i[2] != 0x7fffffff) break;
-  }
+  locate_in_index_order(row, V, (float)j + 0.5f,
+                        [&](int, float v) { return prob_bits(__expf((v - mx) * inv_t)) == yb ? 1.f : 0.f; }, red, &s_i[2]);
   if (threadIdx.x == 0) {
     int tok = s_i[2];
     if (tok == 0x7fffffff) tok = s_best;  // numerical corner: fall back to the mode
