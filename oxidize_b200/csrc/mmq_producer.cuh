@@ -209,7 +209,8 @@ __device__ __forceinline__ void ld_words_align2(const uint8_t* p, uint32_t* out)
   const uint32_t sh = (uint32_t)(reinterpret_cast<uintptr_t>(p) & 2) * 8;
   uint32_t a[N + 1];
 #pragma unroll
-  for (int i = 0; i <= N; ++i) a[i] = w[i];
+  for (int i = 0; i < N; ++i) a[i] = w[i];
+  a[N] = sh ? w[N] : 0u;  // an aligned address needs no word past the last one (and must not touch it: end of a buffer)
 #pragma unroll
   for (int i = 0; i < N; ++i) out[i] = __funnelshift_r(a[i], a[i + 1], sh);
 }

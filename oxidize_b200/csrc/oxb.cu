@@ -205,11 +205,45 @@ __global__ void dequant_rows_kernel(const uint8_t* __restrict__ src, int qtype, 
   for (int i = threadIdx.x; i < cols; i += blockDim.x) o[i] = __float2bfloat16(dequant_elem(qtype, row, i));
 }
 
-OXB_API int oxb_dequant_rows(const void* src, int qtype, size_t row_bytes, int rows, int cols, void* dst_bf16,
+// Fast form for the block formats the GEMM's producers decode: one thread per (row, 64-value k-block) runs the same
+// mantissa-trick decoder and writes its 128 bytes with eight 16-byte stores; a warp covers 32 consecutive k-blocks
+// of a row, so the stores of a warp are one contiguous 4 KB run.
+template <int QT>
+static __global__ void dequant_rows_fast_kernel(const uint8_t* __restrict__ src, size_t row_bytes, int rows, int cols,
+                                                __nv_bfloat16* __restrict__ dst) {
+  const int kbs = cols >> 6;
+  const long long total = (long long)rows * kbs;
+  const QwArgs qw{nullptr, row_bytes, nullptr, 0, 0};
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(t / kbs), kb = (int)(t % kbs);
+    uint4* out = reinterpret_cast<uint4*>(dst + (size_t)r * cols + (size_t)kb * 64);
+    dequant64_chunks<QT>(src + (size_t)r * row_bytes, kb * 64, qw, 0,
+                         [&](int c, uint32_t a, uint32_t b, uint32_t cc, uint32_t d) { out[c] = make_uint4(a, b, cc, d); });
+  }
+}
+
+// fast != 0: the vectorised decoder where it applies.  Its scales and offsets enter the arithmetic as bf16, exactly as
+// in the fused GEMM (about 2^-9 of the sub-block's range per value); fast == 0 always takes the exact per-element form.
+OXB_API int oxb_dequant_rows(const void* src, int qtype, size_t row_bytes, int rows, int cols, void* dst_bf16, int fast,
                              cudaStream_t stream) {
   if (rows <= 0) return 0;
-  dequant_rows_kernel<<<rows, 256, 0, stream>>>(reinterpret_cast<const uint8_t*>(src), qtype, row_bytes, cols,
-                                                reinterpret_cast<__nv_bfloat16*>(dst_bf16));
+  const uint8_t* s8 = reinterpret_cast<const uint8_t*>(src);
+  __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(dst_bf16);
+  // Q4_K blocks are read with 16-byte loads, Q6_K / Q8_0 blocks through aligned words from any even address
+  const size_t src_align = qtype == QT_Q4_K ? 16 : 2;
+  const bool aligned = cols % 64 == 0 && (reinterpret_cast<uintptr_t>(dst_bf16) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(src) % src_align) == 0 && row_bytes % src_align == 0 &&
+                       (qtype != QT_Q8_0 || (reinterpret_cast<uintptr_t>(src) & 3) == 0);
+  if (fast && aligned && (qtype == QT_Q4_K || qtype == QT_Q6_K || qtype == QT_Q8_0)) {
+    const long long total = (long long)rows * (cols >> 6);
+    const int blocks = (int)((total + 255) / 256 < (long long)sm_count() * 16 ? (total + 255) / 256 : (long long)sm_count() * 16);
+    if (qtype == QT_Q4_K) dequant_rows_fast_kernel<QT_Q4_K><<<blocks, 256, 0, stream>>>(s8, row_bytes, rows, cols, d);
+    else if (qtype == QT_Q6_K) dequant_rows_fast_kernel<QT_Q6_K><<<blocks, 256, 0, stream>>>(s8, row_bytes, rows, cols, d);
+    else dequant_rows_fast_kernel<QT_Q8_0><<<blocks, 256, 0, stream>>>(s8, row_bytes, rows, cols, d);
+    OXB_CHECK_LAUNCH();
+    return 0;
+  }
+  dequant_rows_kernel<<<rows, 256, 0, stream>>>(s8, qtype, row_bytes, cols, d);
   OXB_CHECK_LAUNCH();
   return 0;
 }

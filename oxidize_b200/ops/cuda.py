@@ -58,8 +58,9 @@ class KernelOptions:
     gemv_wide: bool = False  # ... also for wide, short matrices (K >= 2N), where the split-K tensor-core kernel is faster
     ar_ll_min_world: int = 2  # rank counts from which the fused all-reduce uses the two-shot exchange
     # Packed-weight calls with more tokens than this decode the matrix to a bf16 staging buffer once and run the bf16
-    # GEMM on it (every token tile of the fused kernel decodes the weight tile again); 0 = always the fused kernel.
-    mmq_max_tokens: int = 0
+    # GEMM on it (every token tile of the fused kernel decodes the weight tile again: past ~900 tokens decoding once
+    # wins, 1.4x at 2304 tokens); 0 = always the fused kernel.
+    mmq_max_tokens: int = 1024
 
 
 mmq_max_tokens = KernelOptions.mmq_max_tokens
@@ -83,7 +84,7 @@ def _declare(L) -> None:
     L.oxb_status.argtypes = [ctypes.POINTER(i32), i32]
     L.oxb_gemm_plan.argtypes = [i32, i32, i32, i32, ctypes.POINTER(i32), ctypes.POINTER(sz), ctypes.POINTER(i32)]
     L.oxb_gemm_bf16.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, sz, vp, i32, vp]
-    L.oxb_dequant_rows.argtypes = [vp, i32, sz, i32, i32, vp, vp]
+    L.oxb_dequant_rows.argtypes = [vp, i32, sz, i32, i32, vp, i32, vp]
     L.oxb_embed.argtypes = [vp, vp, i32, sz, i32, i32, f32, vp, i32, vp]
     L.oxb_add_rmsnorm.argtypes = [vp, vp, vp, vp, vp, i32, i32, f32, vp]
     L.oxb_silu_mul.argtypes = [vp, vp, i32, i32, vp]
@@ -258,13 +259,14 @@ class l2_prefetch:
         return False
 
 
-def dequant_rows(w, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Decode a packed QTensor to a dense bf16 [out, in] matrix on the device."""
+def dequant_rows(w, out: Optional[torch.Tensor] = None, fast: bool = False) -> torch.Tensor:
+    """Decode a packed QTensor to a dense bf16 [out, in] matrix on the device.  ``fast`` uses the vectorised decoder of
+    the fused GEMM where it applies (Q4_K / Q6_K / Q8_0; block scales rounded to bf16), else the exact one."""
     n, k = w.shape
     if out is None:
         out = torch.empty(n, k, dtype=torch.bfloat16, device=w.data.device)
     _check(lib().oxb_dequant_rows(w.data.data_ptr(), QTYPE_CODE[w.qtype], w.data.stride(0) * w.data.element_size(), n, k,
-                                  out.data_ptr(), _stream()), "oxb_dequant_rows")
+                                  out.data_ptr(), 1 if fast else 0, _stream()), "oxb_dequant_rows")
     return out
 
 

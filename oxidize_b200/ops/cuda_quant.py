@@ -34,7 +34,7 @@ def linear_quant(x, p, out_view, bias, ld_out):
         row_bytes = p.data.stride(0) * p.data.element_size()
         return _launch(x, p.data.data_ptr(), FUSED_TYPES[p.qtype], row_bytes, None, 0, out_view, bias, ld_out, n, k)
     buf = C.scratch(x.device).dequant_buf(n * k)[: n * k].view(n, k)
-    C.dequant_rows(p, buf)
+    C.dequant_rows(p, buf, fast=True)
     # The GEMM requests its first weight tiles before it waits for the upstream kernel, which is only safe
     # for weights that no kernel writes.  Here the "weights" were written by the launch just before, so this
     # GEMM is launched without programmatic stream serialization (plain stream order).

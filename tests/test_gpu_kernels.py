@@ -780,3 +780,20 @@ def test_moe_token_dispatch_grouped_gemm_combine(C, T, E, k, first, n_local, H, 
         want[rows] += w[:, None] * (a @ dn[e].to("cpu").dense_cache().t().to(dev))
     assert _rel_err(out, want) < (2e-2 if qtype != "BF16" else 1.2e-2)
     _check_status(C)
+
+
+@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q8_0"])
+def test_fast_row_decoder_matches_the_numpy_decoder(C, qtype):
+    """oxb_dequant_rows takes a vectorised path for the formats the GEMM producers decode (64 values per thread);
+    it must give the bf16 rounding of the NumPy decoder's values, also on the last row of the buffer."""
+    from oxidize_b200.models.weights import qtensor_from_dense
+
+    torch.manual_seed(3)
+    for n, k in ((96, 1024), (7, 4096)):
+        w = qtensor_from_dense(torch.randn(n, k) * 0.05, qtype, device="cuda")
+        got = C.dequant_rows(w, fast=True).float().cpu()
+        want = w.to("cpu").dense_cache()
+        assert got.shape == want.shape
+        assert _rel_err(got, want) < 1e-2  # scales and offsets enter the fast decoder as bf16
+        assert _rel_err(C.dequant_rows(w).float().cpu(), want) < 5e-3  # the exact form
+    _check_status(C)
