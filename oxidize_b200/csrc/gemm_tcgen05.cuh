@@ -56,11 +56,9 @@ struct GemmTile {
   static constexpr int STAGES = TN <= 16 ? 6 : TN == 32 ? 5 : TN == 64 ? 4 : (TN == 128 ? 6 : 4);
   static constexpr int CTAS_PER_SM = TN <= 64 ? 2 : 1;
   // One accumulator per tile.  (Spreading the four k-steps of a k-block over separate accumulators, to break the
-  // dependency chain of back-to-back MMAs, changes nothing measurable: the issue rate at decode sizes is set by how
-  // fast the tensor core can fetch its operands from shared memory, not by the accumulate latency.)
-  static constexpr int NACC = 1;
-  static constexpr int ACC_COLS = TN < 32 ? 32 : TN;  // TMEM columns between accumulators
-  static constexpr int TMEM_COLS = NACC * ACC_COLS;
+  // dependency chain of back-to-back MMAs, changed nothing measurable.)
+  static constexpr int ACC_COLS = TN < 32 ? 32 : TN;  // TMEM columns of the accumulator
+  static constexpr int TMEM_COLS = ACC_COLS;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + 1024 /*token scales*/;
 };
 
@@ -379,21 +377,10 @@ struct GroupArgs {
   int t_tiles;
 };
 
-// QT == QT_BF16: both operands arrive by TMA.  Any other QT: the weight tile is produced by four
-// dequant warps from packed blocks (see mmq_producer.cuh) and only the activations use TMA.
-// 16 accumulator columns of this warp's TMEM lanes, summed over the NACC accumulators (fixed order)
-template <int NACC, int ACC_COLS>
-__device__ __forceinline__ void tmem_ld16_acc(uint32_t taddr, uint32_t* r) {
+// 16 accumulator columns of this warp's TMEM lanes
+__device__ __forceinline__ void tmem_ld16_now(uint32_t taddr, uint32_t* r) {
   tmem_ld16(taddr, r);
   tmem_ld_wait();
-#pragma unroll
-  for (int a = 1; a < NACC; ++a) {
-    uint32_t t[16];
-    tmem_ld16(taddr + a * ACC_COLS, t);
-    tmem_ld_wait();
-#pragma unroll
-    for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(t[j]));
-  }
 }
 
 #ifdef OXB_MMQ_TRACE
@@ -414,6 +401,8 @@ static __device__ long long g_oxb_mmq_trace[32];
 #define OXB_TR_END(acc)
 #endif
 
+// QT == QT_BF16: both operands arrive by TMA.  Any other QT: the weight tile is decoded by the producer warps from
+// packed blocks into tensor memory (see mmq_producer.cuh) and only the activations (and the packed boxes) use TMA.
 template <int TN, int QT>
 __global__ void __launch_bounds__(QT == QT_BF16 ? GEMM_THREADS : GEMM_THREADS_MMQ, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
@@ -649,9 +638,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     }
   } else if (warp >= GEMM_WARP_PRODUCER0) {
     if constexpr (MMQ) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(MMQ_REGS_PRODUCER));
-    // ---------------- dequant producers (MMQ only): MMQ_GROUPS groups of 128 threads; in each, thread r stages weight row
-    // n0 + r.  The groups take alternate k-blocks (each stage's barrier expects the four warps of ONE group), so
-    // twice as many warps share the decode arithmetic of a tile and the ring is fed by two decoders at once.
+    // ---------------- dequant producers (MMQ only): MMQ_GROUPS groups of 128 threads; in each, thread r decodes weight row
+    // n0 + r.  Group g takes k-blocks g, g + MMQ_GROUPS, ... (each stage's barrier expects the four warps of ONE
+    // group), so MMQ_GROUPS k-blocks are being decoded at any time.
     if constexpr (MMQ) {
       OXB_TR_DECL
       const int grp = (threadIdx.x - 32 * GEMM_WARP_PRODUCER0) >> 7;
@@ -831,7 +820,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 #pragma unroll 1
         for (int c = 0; c < TN / 16; ++c) {
           uint32_t r[16];
-          tmem_ld16_acc<Cfg::NACC, Cfg::ACC_COLS>(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
+          tmem_ld16_now(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const float sc = use_nm ? tok_scale[c * 16 + j] : 1.f;
@@ -852,7 +841,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 #pragma unroll 1
         for (int c = 0; c < TN / 16; ++c) {
           uint32_t r[16];
-          tmem_ld16_acc<Cfg::NACC, Cfg::ACC_COLS>(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
+          tmem_ld16_now(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
           if (n < N) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -877,7 +866,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 #pragma unroll 1
         for (int c = 0; c < TN / 16; ++c) {
           uint32_t r[16];
-          tmem_ld16_acc<Cfg::NACC, Cfg::ACC_COLS>(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
+          tmem_ld16_now(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
 #pragma unroll
           for (int j = 0; j < 16; ++j) part[(c * 16 + j) * GEMM_BM + row] = __uint_as_float(r[j]);
         }
@@ -930,7 +919,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 #pragma unroll 1
       for (int c = 0; c < TN / 16; ++c) {
         uint32_t r[16];
-        tmem_ld16_acc<Cfg::NACC, Cfg::ACC_COLS>(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
+        tmem_ld16_now(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, r);
 #pragma unroll
         for (int j = 0; j < 16; ++j) my[(c * 16 + j) * GEMM_BM + row] = __uint_as_float(r[j]);
       }

@@ -1,8 +1,8 @@
 // Dequant-fused operand staging for the tcgen05 GEMM ("MMQ"): producer warps read packed
 // weight blocks (Q4_K / Q6_K / Q8_0 / Q4_0 / NVFP4, or block-scaled fp8), decode 64 values of one
-// weight row to bf16 in registers with the scales folded in, and store them straight into the
-// 128-byte-swizzled K-major shared-memory tile that the UMMA descriptor expects — the weights are
-// never materialised as bf16 in global memory.
+// weight row to bf16 in registers with the scales folded in, and hand them on eight values at a time:
+// the GEMM's producers write them into tensor memory (the MMA's A operand), the row decoder writes
+// them to a bf16 matrix.
 //
 // Folding the scales during staging (not in the epilogue) is the lesson of the reference's first
 // tensor-core MMQ revision, whose fp32 scale epilogue took ~75 % of kernel time
@@ -186,22 +186,6 @@ __device__ __forceinline__ void dequant64(const uint8_t* rowp, int k0, const QwA
   }
 }
 
-// Store one row's 64 bf16 (32 packed words) into the 128B-swizzled tile: 16-byte chunk c of row r
-// lives at r*128 + ((c ^ (r & 7)) << 4), the same pattern a 128B-swizzle TMA load produces.
-__device__ __forceinline__ void store_row_sw128(uint8_t* tile, int r, const uint32_t* v) {
-  uint8_t* rowp = tile + r * 128;
-#pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    uint4 u = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
-    *reinterpret_cast<uint4*>(rowp + ((c ^ (r & 7)) << 4)) = u;
-  }
-}
-
-// 16-byte chunk c of row r of the 128B-swizzled tile
-__device__ __forceinline__ void store_chunk_sw128(uint8_t* tile, int r, int c, uint32_t a, uint32_t b, uint32_t cc, uint32_t d) {
-  *reinterpret_cast<uint4*>(tile + r * 128 + ((c ^ (r & 7)) << 4)) = make_uint4(a, b, cc, d);
-}
-
 // 32-bit words at a 2-byte-aligned shared-memory address: N + 1 aligned words, funnel-shifted into place
 template <int N>
 __device__ __forceinline__ void ld_words_align2(const uint8_t* p, uint32_t* out) {
@@ -330,6 +314,5 @@ __device__ __forceinline__ void dequant64_chunks(const uint8_t* rowp, int k0, co
   }
 }
 
-__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 }  // namespace oxb
