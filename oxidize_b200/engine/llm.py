@@ -178,6 +178,17 @@ class LLM:
         return self.scheduler.has_work or getattr(self, "_inflight", None) is not None
 
     def step(self) -> List[RequestOutput]:
+        """One engine iteration (see ``_step``); with ``KernelOptions.checked`` the scratch buffers' canary bands are
+        verified after it."""
+        out = self._step()
+        if self.device.type == "cuda":
+            from ..ops import cuda as _opcuda
+
+            if _opcuda.checked:
+                _opcuda.verify_guards()
+        return out
+
+    def _step(self) -> List[RequestOutput]:
         """One engine iteration: schedule → forward → sample → postprocess.
 
         In the steady state of greedy decoding the engine keeps one step in flight: before it waits for the tokens

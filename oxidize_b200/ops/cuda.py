@@ -61,9 +61,30 @@ class KernelOptions:
     # GEMM on it (every token tile of the fused kernel decodes the weight tile again: past ~900 tokens decoding once
     # wins, 1.4x at 2304 tokens); 0 = always the fused kernel.
     mmq_max_tokens: int = 1024
+    # Checked mode: the op layer's scratch buffers (split-K partials and tickets, split-KV partials, decode staging) sit
+    # between canary bands that ``verify_guards()`` checks (``LLM.step`` does so after every step, the kernel tests
+    # after every test).  Costs a device synchronisation per check: for debugging, not for serving.
+    checked: bool = False
 
 
 mmq_max_tokens = KernelOptions.mmq_max_tokens
+checked = False
+_checked_forced = False
+
+
+def _apply_checked(on: bool) -> None:
+    global checked
+    if on != checked:
+        checked = on
+        _scratch.clear()  # scratch is re-created with (or without) guard bands on next use
+
+
+def set_checked(on: bool) -> None:
+    """Checked mode for the whole process whatever later ``configure`` calls say (test suites)."""
+    global _checked_forced
+    _checked_forced = bool(on)
+    _apply_checked(_checked_forced)
+
 
 
 def configure(opts: "KernelOptions") -> None:
@@ -74,8 +95,9 @@ def configure(opts: "KernelOptions") -> None:
     L.oxb_set_gemv_max_tokens(int(opts.gemv_max_tokens))
     L.oxb_set_gemv_wide(1 if opts.gemv_wide else 0)
     L.oxb_set_ar_ll_min_world(int(opts.ar_ll_min_world))
-    global mmq_max_tokens
+    global mmq_max_tokens, checked
     mmq_max_tokens = int(opts.mmq_max_tokens)
+    _apply_checked(bool(opts.checked) or _checked_forced)
 
 
 def _declare(L) -> None:
@@ -139,14 +161,27 @@ class Scratch:
 
     def __init__(self, device: torch.device):
         self.device = device
-        self.gemm_ws = torch.empty(16 << 20, dtype=torch.float32, device=device)  # 64 MB
-        self.gemm_counters = torch.zeros(8192, dtype=torch.int32, device=device)
+        self.guards = None
+        if checked:
+            from ..utils.guards import GuardedAllocator
+
+            self.guards = GuardedAllocator()
+        self.gemm_ws = self._new(16 << 20, torch.float32, "gemm split-K partials")  # 64 MB
+        self.gemm_counters = self._new(8192, torch.int32, "gemm split-K tickets", zero=True)
         self.attn_o: Optional[torch.Tensor] = None
         self.attn_ml: Optional[torch.Tensor] = None
-        self.attn_counters = torch.zeros(65536, dtype=torch.int32, device=device)
+        self.attn_counters = self._new(65536, torch.int32, "attention split tickets", zero=True)
         self.dequant: Optional[torch.Tensor] = None
         self._cap_attn = None
         self._cap_dequant = None
+
+    def _new(self, n: int, dtype: torch.dtype, name: str, zero: bool = False, old: Optional[torch.Tensor] = None):
+        """A buffer of this scratch; between canary bands in checked mode (never while a stream is capturing)."""
+        if self.guards is not None and not torch.cuda.is_current_stream_capturing():
+            if old is not None:
+                self.guards.forget(old)
+            return self.guards.empty(n, dtype, self.device, name, zero)
+        return (torch.zeros if zero else torch.empty)(n, dtype=dtype, device=self.device)
 
     # The two growable buffers below must never be handed to a CUDA graph: growing them later would
     # free memory that the captured kernels still point to.  While a stream is capturing, the buffers
@@ -161,9 +196,9 @@ class Scratch:
             return a
         self._cap_attn = None
         if self.attn_o is None or self.attn_o.numel() < o_floats:
-            self.attn_o = torch.empty(max(o_floats, 1), dtype=torch.float32, device=self.device)
+            self.attn_o = self._new(max(o_floats, 1), torch.float32, "attention split-KV partial outputs", old=self.attn_o)
         if self.attn_ml is None or self.attn_ml.numel() < ml_floats:
-            self.attn_ml = torch.empty(max(ml_floats, 1), dtype=torch.float32, device=self.device)
+            self.attn_ml = self._new(max(ml_floats, 1), torch.float32, "attention split-KV max / sum", old=self.attn_ml)
         return self.attn_o, self.attn_ml
 
     def dequant_buf(self, n: int) -> torch.Tensor:
@@ -173,7 +208,7 @@ class Scratch:
             return self._cap_dequant
         self._cap_dequant = None
         if self.dequant is None or self.dequant.numel() < n:
-            self.dequant = torch.empty(n, dtype=torch.bfloat16, device=self.device)
+            self.dequant = self._new(n, torch.bfloat16, "packed-weight decode staging", old=self.dequant)
         return self.dequant
 
 
@@ -186,6 +221,15 @@ def scratch(device: torch.device) -> Scratch:
     if s is None:
         s = _scratch[idx] = Scratch(torch.device("cuda", idx))
     return s
+
+
+def verify_guards() -> None:
+    """Checked mode: raise ``utils.guards.MemoryGuardError`` if a kernel wrote outside one of the scratch buffers
+    (synchronises every device that has scratch).  Does nothing otherwise."""
+    for s in _scratch.values():
+        if s.guards is not None:
+            torch.cuda.synchronize(s.device)
+            s.guards.verify()
 
 
 # --------------------------------------------------------------------------- GEMM / linear

@@ -219,3 +219,32 @@ def test_prefill_token_budget_follows_tile_waves():
     tiny = preset("tiny-llama")
     assert prefill_token_budget(tiny, 1) == 3072
     assert prefill_token_budget(big, 8, lo=1024, hi=1024) == 1024
+
+
+def test_guard_bands_catch_writes_outside_a_buffer():
+    """The canary allocator names the buffer that was written before its start or past its end."""
+    import torch
+
+    from oxidize_b200.utils.guards import GUARD_BYTES, GuardedAllocator, MemoryGuardError
+
+    g = GuardedAllocator()
+    a = g.empty(100, torch.float32, "cpu", "partials")
+    b = g.empty(7, torch.int32, "cpu", "tickets", zero=True)
+    assert a.numel() == 100 and b.numel() == 7 and int(b.sum()) == 0 and len(g) == 2
+    a.fill_(1.0)
+    b.fill_(3)
+    g.verify()  # writes inside the payload leave the bands alone
+    # an overrun of three floats past the end of `a` (the storage behind the view is the guarded allocation)
+    raw = torch.tensor([], dtype=torch.uint8).set_(a.untyped_storage())
+    raw[GUARD_BYTES + 400 + 5] = 0
+    with pytest.raises(MemoryGuardError, match="partials: written 5 bytes past its end"):
+        g.verify()
+    raw[GUARD_BYTES + 400 + 5] = 0xA5
+    g.verify()
+    rawb = torch.tensor([], dtype=torch.uint8).set_(b.untyped_storage())
+    rawb[GUARD_BYTES - 1] = 1
+    with pytest.raises(MemoryGuardError, match="tickets: written before its start"):
+        g.verify()
+    g.forget(b)
+    g.verify()
+    assert len(g) == 1

@@ -16,6 +16,17 @@ def C():
     return C
 
 
+@pytest.fixture(autouse=True)
+def _canaries(C):
+    """Every test of this module runs with the scratch buffers between canary bands, verified afterwards."""
+    C.set_checked(True)
+    yield
+    try:
+        C.verify_guards()
+    finally:
+        C.set_checked(False)
+
+
 def _rel_err(a, b):
     a, b = a.float(), b.float()
     return float((a - b).norm() / (b.norm() + 1e-12))
