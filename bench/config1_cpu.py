@@ -33,6 +33,8 @@ def main() -> int:
     ap.add_argument("--prompt-tokens", type=int, default=128)
     ap.add_argument("--decode-tokens", type=int, default=128)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--quant", default="Q4_K", help="encoding of the synthetic checkpoint (Q4_K is the named configuration; "
+                    "F32 takes the reference's int8 activation quantisation out of the comparison)")
     a = ap.parse_args()
     import reference_arm as ra
 
@@ -41,11 +43,11 @@ def main() -> int:
     from oxidize_b200.models.config import preset
     from oxidize_b200.utils.synth import synth_gguf
 
-    path = os.path.join(tempfile.gettempdir(), "oxb_config1_tiny_q4k.gguf")
+    path = os.path.join(tempfile.gettempdir(), f"oxb_config1_tiny_{a.quant.lower()}.gguf")
     if not os.path.exists(path):
-        synth_gguf(path, preset("tiny-llama"), "Q4_K", seed=0)
+        synth_gguf(path, preset("tiny-llama"), a.quant, seed=0)
     text = ra.make_prompt(a.prompt_tokens, seed=0)
-    out = {"config": "tiny Llama Q4_K, CPU, batch 1, %d prompt + %d greedy tokens, f16 KV" % (a.prompt_tokens, a.decode_tokens)}
+    out = {"config": "tiny Llama %s, CPU, batch 1, %d prompt + %d greedy tokens, f16 KV" % (a.quant, a.prompt_tokens, a.decode_tokens)}
     # ---- this engine
     llm = LLM.from_gguf(path, EngineConfig(kv_cache_dtype="f16", max_model_len=512, max_num_seqs=1, num_kv_blocks=64,
                                            prefill_chunk_size=128, max_num_batched_tokens=128, enable_prefix_cache=False),

@@ -193,6 +193,9 @@ def synth_gguf(path: str, cfg: ModelConfig, quant: str = "Q4_K_M", seed: int = 0
         gv = mat(f"{p}.attn_v.weight", "attn_v", i, cfg.kv_size, h, add=not fused_layout)
         if fused_layout:
             fused(f"{p}.attn_qkv.weight", [(*gq, cfg.q_size), (*gk, cfg.kv_size), (*gv, cfg.kv_size)], h)
+        if cfg.attn_bias:  # Qwen2-style q/k/v projection biases
+            for nm, nb in (("attn_q", cfg.q_size), ("attn_k", cfg.kv_size), ("attn_v", cfg.kv_size)):
+                w.add_tensor(f"{p}.{nm}.bias", (rng.standard_normal(nb) * 0.1).astype(np.float32), (nb,), "F32")
         mat(f"{p}.attn_output.weight", "attn_output", i, h, cfg.q_size)
         if cfg.qk_norm:
             vec(f"{p}.attn_q_norm.weight", hd)
