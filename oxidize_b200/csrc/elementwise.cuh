@@ -184,6 +184,15 @@ static __global__ void row_sumsq_kernel(const __nv_bfloat16* __restrict__ X, int
   }
 }
 
+// act(gate) * up over the two halves of a fused [T, 2I] projection.  GELU = false: SiLU (SwiGLU); true: the tanh form of
+// GELU (GeGLU, Gemma): 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) = g * sigmoid(2 sqrt(2/pi) (g + 0.044715 g^3)).
+template <bool GELU>
+static __device__ __forceinline__ float gated_act(float g) {
+  const float z = GELU ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : g;
+  return g / (1.f + __expf(-z));
+}
+
+template <bool GELU>
 static __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int T, int I) {
   pdl_launch_dependents();
   pdl_wait();
@@ -200,7 +209,7 @@ static __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __n
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float2 a = unpack_bf16x2(gs[j]), b = unpack_bf16x2(us[j]);
-      os[j] = pack_bf16x2(a.x / (1.f + __expf(-a.x)) * b.x, a.y / (1.f + __expf(-a.y)) * b.y);
+      os[j] = pack_bf16x2(gated_act<GELU>(a.x) * b.x, gated_act<GELU>(a.y) * b.y);
     }
     *reinterpret_cast<uint4*>(out + t * I + i) = o;
   }

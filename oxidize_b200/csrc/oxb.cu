@@ -299,16 +299,26 @@ OXB_API int oxb_row_sumsq(const void* x, int ldx, int T, int H, void* out, void*
   return 0;
 }
 
-OXB_API int oxb_silu_mul(const void* gu, void* out, int T, int I, cudaStream_t stream) {
+template <bool GELU>
+static int gated_act_mul(const void* gu, void* out, int T, int I, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (I % 8 != 0) return (int)cudaErrorInvalidValue;
   const size_t total = (size_t)T * (I / 8);
   int blocks = (int)((total + 255) / 256);
   if (blocks > sm_count() * 16) blocks = sm_count() * 16;
-  oxb_launch(silu_mul_kernel, dim3(blocks), dim3(256), 0, stream, reinterpret_cast<const __nv_bfloat16*>(gu),
+  oxb_launch(silu_mul_kernel<GELU>, dim3(blocks), dim3(256), 0, stream, reinterpret_cast<const __nv_bfloat16*>(gu),
              reinterpret_cast<__nv_bfloat16*>(out), T, I);
   OXB_CHECK_LAUNCH();
   return 0;
+}
+
+OXB_API int oxb_silu_mul(const void* gu, void* out, int T, int I, cudaStream_t stream) {
+  return gated_act_mul<false>(gu, out, T, I, stream);
+}
+
+// tanh-GELU(gate) * up (GeGLU)
+OXB_API int oxb_gelu_mul(const void* gu, void* out, int T, int I, cudaStream_t stream) {
+  return gated_act_mul<true>(gu, out, T, I, stream);
 }
 
 OXB_API int oxb_qk_rope_kvwrite(const void* qkv, const int* positions, const int* slots, const float* cos_sin,

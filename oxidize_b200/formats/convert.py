@@ -21,7 +21,10 @@ from .safetensors_io import SafeTensorsFile
 
 _ARCH = {"LlamaForCausalLM": "llama", "MistralForCausalLM": "llama", "MixtralForCausalLM": "mixtral",
          "Qwen2ForCausalLM": "qwen2", "Qwen3ForCausalLM": "qwen3", "Qwen3MoeForCausalLM": "qwen3moe",
-         "Qwen2MoeForCausalLM": "qwen2moe", "DeepseekV2ForCausalLM": "deepseek2", "DeepseekV3ForCausalLM": "deepseek2"}
+         "Qwen2MoeForCausalLM": "qwen2moe", "DeepseekV2ForCausalLM": "deepseek2", "DeepseekV3ForCausalLM": "deepseek2",
+         "Phi3ForCausalLM": "phi3", "GemmaForCausalLM": "gemma", "Gemma2ForCausalLM": "gemma2",
+         "Gemma3ForCausalLM": "gemma3", "Gemma3ForConditionalGeneration": "gemma3"}
+GEMMA = ("gemma", "gemma2", "gemma3")
 
 
 def arch_from_config(cfg: Dict[str, Any]) -> str:
@@ -30,11 +33,25 @@ def arch_from_config(cfg: Dict[str, Any]) -> str:
             return _ARCH[a]
     mt = str(cfg.get("model_type", "llama")).lower()
     return {"mistral": "llama", "qwen3_moe": "qwen3moe", "qwen2_moe": "qwen2moe", "deepseek_v2": "deepseek2",
-            "deepseek_v3": "deepseek2"}.get(mt, mt)
+            "deepseek_v3": "deepseek2", "gemma3_text": "gemma3"}.get(mt, mt)
+
+
+def _rope_settings(c: Dict[str, Any]) -> Tuple[float, float, Dict[str, Any]]:
+    """(rotary base, rotary base of the windowed layers or 0, scaling dict) from either config layout: the flat keys
+    (``rope_theta``, ``rope_local_base_freq``, ``rope_scaling``) or the nested ``rope_parameters`` (per attention kind
+    for models with local and global layers)."""
+    rp = c.get("rope_parameters") or {}
+    if "full_attention" in rp or "sliding_attention" in rp:
+        full, local = rp.get("full_attention") or {}, rp.get("sliding_attention") or {}
+        return float(full.get("rope_theta", 10000.0)), float(local.get("rope_theta", 0.0)), full
+    theta = float(rp.get("rope_theta") or c.get("rope_theta") or 10000.0)
+    return theta, float(c.get("rope_local_base_freq") or 0.0), (rp if rp.get("rope_type") else c.get("rope_scaling") or {})
 
 
 def write_hf_metadata(w: GGUFWriter, arch: str, c: Dict[str, Any]) -> None:
     U, F = GGUFValueType.UINT32, GGUFValueType.FLOAT32
+    if "text_config" in c:  # multimodal wrapper: the decoder's settings are nested
+        c = dict(c["text_config"], architectures=c.get("architectures"))
     heads = int(c["num_attention_heads"])
     hidden = int(c["hidden_size"])
     w.add("general.name", str(c.get("_name_or_path") or c.get("model_type") or "converted"))
@@ -49,11 +66,25 @@ def write_hf_metadata(w: GGUFWriter, arch: str, c: Dict[str, Any]) -> None:
     w.add(f"{arch}.attention.key_length", hd, U)
     w.add(f"{arch}.attention.value_length", hd, U)
     w.add(f"{arch}.attention.layer_norm_rms_epsilon", float(c.get("rms_norm_eps", 1e-5)), F)
-    w.add(f"{arch}.rope.freq_base", float(c.get("rope_theta", 10000.0)), F)
+    theta, theta_swa, rs = _rope_settings(c)
+    w.add(f"{arch}.rope.freq_base", theta, F)
     w.add(f"{arch}.rope.dimension_count", int(hd * float(c.get("partial_rotary_factor", 1.0))), U)
     if c.get("sliding_window"):
         w.add(f"{arch}.attention.sliding_window", int(c["sliding_window"]), U)
-    rs = c.get("rope_scaling") or {}
+    if arch in GEMMA:
+        if theta_swa > 0:
+            w.add(f"{arch}.rope.freq_base_swa", theta_swa, F)
+        kinds = c.get("layer_types") or []
+        if "full_attention" in kinds and "sliding_attention" in kinds:
+            # every n-th layer attends over the whole context
+            w.add(f"{arch}.attention.sliding_window_pattern", kinds.index("full_attention") + 1, U)
+        elif c.get("sliding_window_pattern"):
+            w.add(f"{arch}.attention.sliding_window_pattern", int(c["sliding_window_pattern"]), U)
+        if arch == "gemma2":
+            w.add(f"{arch}.attn_logit_softcapping", float(c.get("attn_logit_softcapping") or 0.0), F)
+            w.add(f"{arch}.final_logit_softcapping", float(c.get("final_logit_softcapping") or 0.0), F)
+        if c.get("query_pre_attn_scalar"):
+            w.add(f"{arch}.attention.scale", float(c["query_pre_attn_scalar"]) ** -0.5, F)
     if rs.get("type") or rs.get("rope_type"):
         kind = str(rs.get("type") or rs.get("rope_type"))
         if kind in ("linear", "yarn"):
@@ -97,7 +128,7 @@ def convert_safetensors_to_gguf(src_dir: str, out_path: str, quant: str = "F16",
     experts: Dict[str, Dict[int, Tuple[SafeTensorsFile, str]]] = {}
     for f in files:
         for name in f.keys():
-            m = map_hf_tensor_name(name)
+            m = map_hf_tensor_name(name, arch)
             if m is None:
                 continue
             gname, e = m
@@ -112,6 +143,8 @@ def convert_safetensors_to_gguf(src_dir: str, out_path: str, quant: str = "F16",
 
     def encode(gname: str, arr_f32: np.ndarray):
         if arr_f32.ndim == 1 or "norm" in gname or gname.endswith(".bias") or "ffn_gate_inp" in gname:
+            if arch in GEMMA and gname.endswith("norm.weight"):
+                arr_f32 = arr_f32 + 1.0  # Gemma stores w - 1; files carry the multiplier itself (as llama.cpp's do)
             return arr_f32.astype(np.float32), "F32"
         t = pick_type(quant, _kind_of(gname), layer_of(gname), L, arr_f32.shape[-1])
         return qref.quantize(t, arr_f32.reshape(-1)), t

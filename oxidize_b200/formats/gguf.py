@@ -582,6 +582,13 @@ _HF_LAYER_MAP = {
     "mlp.shared_expert_gate.weight": "ffn_gate_inp_shexp.weight",
     "mlp.gate.e_score_correction_bias": "exp_probs_b.bias",
 }
+# Gemma-2 / Gemma-3 name their four per-layer norms differently: post_attention_layernorm is the norm on the attention
+# branch's OUTPUT there (elsewhere it is the norm in front of the FFN)
+_HF_LAYER_MAP_GEMMA = {
+    "post_attention_layernorm.weight": "post_attention_norm.weight",
+    "pre_feedforward_layernorm.weight": "ffn_norm.weight",
+    "post_feedforward_layernorm.weight": "post_ffw_norm.weight",
+}
 _HF_TOP_MAP = {
     "model.embed_tokens.weight": "token_embd.weight",
     "model.norm.weight": "output_norm.weight",
@@ -592,19 +599,25 @@ _HF_EXPERT_RE = re.compile(r"^(?:mlp|block_sparse_moe)\.experts\.(\d+)\.(gate_pr
 _EXPERT_KIND = {"gate_proj": "gate", "w1": "gate", "up_proj": "up", "w3": "up", "down_proj": "down", "w2": "down"}
 
 
-def map_hf_tensor_name(name: str) -> Optional[Tuple[str, Optional[int]]]:
+def map_hf_tensor_name(name: str, arch: Optional[str] = None) -> Optional[Tuple[str, Optional[int]]]:
     """Map a HF decoder tensor name to ``(gguf_name, expert_index)``.
 
     Per-expert HF tensors map to the stacked ``blk.N.ffn_{gate,up,down}_exps.weight`` and
     return the expert index to stack at; everything else returns ``None`` for the index.
-    Unknown names return ``None``.
+    Unknown names return ``None``.  ``arch`` (the GGUF architecture string) selects the Gemma-2/3 norm names.
     """
+    if name.startswith("language_model."):  # text tower of a multimodal checkpoint
+        name = name[len("language_model."):]
+    elif name.startswith("model.language_model."):
+        name = "model." + name[len("model.language_model."):]
     if name in _HF_TOP_MAP:
         return _HF_TOP_MAP[name], None
     m = _HF_LAYER_RE.match(name)
     if not m:
         return None
     layer, rest = int(m.group(1)), m.group(2)
+    if arch in ("gemma2", "gemma3") and rest in _HF_LAYER_MAP_GEMMA:
+        return f"blk.{layer}.{_HF_LAYER_MAP_GEMMA[rest]}", None
     if rest in _HF_LAYER_MAP:
         return f"blk.{layer}.{_HF_LAYER_MAP[rest]}", None
     e = _HF_EXPERT_RE.match(rest)

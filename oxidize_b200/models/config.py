@@ -15,12 +15,15 @@ from typing import Any, Dict, List, Optional
 from ..formats.gguf import GGUFFile
 
 # architecture strings accepted (reference arch-string map inference.rs:62-96)
-DENSE_ARCHS = {"llama", "mistral", "qwen2", "qwen3", "deepseek", "phi3"}  # phi3: Llama layers with fused qkv / gate-up tensors
+# phi3: Llama layers with fused qkv / gate-up tensors.  gemma / gemma2 / gemma3: GeGLU, scaled embeddings, norms on the
+# branch outputs, soft-capped logits, interleaved local / global attention with two rotary bases.
+DENSE_ARCHS = {"llama", "mistral", "qwen2", "qwen3", "deepseek", "phi3", "gemma", "gemma2", "gemma3"}
+GEMMA_ARCHS = {"gemma", "gemma2", "gemma3"}
 MOE_ARCHS = {"mixtral", "qwen2moe", "qwen3moe", "deepseek2", "deepseek-moe", "deepseek_moe"}
-# Architectures whose layers need math this engine does not have (GeGLU and embedding scaling, sandwich
-# norms, parallel attention / MLP blocks, recurrent or convolutional mixers): loading one would run it as
+# Architectures whose layers need math this engine does not have (two attention geometries in one model,
+# parallel attention / MLP blocks, recurrent or convolutional mixers): loading one would run it as
 # a plain Llama and produce wrong tokens, so they are refused by name.
-UNSUPPORTED_ARCHS = {"gemma", "gemma2", "gemma3", "gemma4", "phi", "phi2", "llama4", "qwen35", "qwen3_5_moe", "mamba",
+UNSUPPORTED_ARCHS = {"gemma4", "phi", "phi2", "llama4", "qwen35", "qwen3_5_moe", "mamba",
                      "lfm2", "glm4", "falcon", "gpt2", "bert"}
 
 
@@ -71,6 +74,15 @@ class ModelConfig:
     qk_norm: bool = False
     attn_bias: bool = False
     tie_embeddings: bool = False
+    # Gemma-family layer semantics (the reference's ``embedding_scale`` / ``gelu_ffn`` / ``sandwich_norm`` /
+    # ``rope_theta_swa``, oxidize-core/src/model/inference.rs:604-636)
+    embedding_scale: float = 1.0  # the embedding rows are multiplied by this (Gemma: sqrt(hidden_size))
+    ffn_act: str = "silu"  # silu (SwiGLU) | gelu_tanh (GeGLU)
+    post_norms: bool = False  # RMSNorm on the attention and FFN branch outputs before they join the residual stream
+    attn_softcap: float = 0.0  # scores = cap * tanh(scores / cap) before the softmax (Gemma-2); 0 = off
+    final_softcap: float = 0.0  # the same on the output logits
+    rope_theta_swa: float = 0.0  # rotary base of the windowed layers (Gemma-3: 10000, unscaled); 0 = same as rope_theta
+    attn_scale: float = 0.0  # softmax scale; 0 = head_dim ** -0.5
     # MoE
     n_experts: int = 0
     n_experts_used: int = 0
@@ -197,6 +209,25 @@ def config_from_gguf(g: GGUFFile) -> ModelConfig:
     c.attn_bias = g.has_tensor("blk.0.attn_q.bias") or g.has_tensor("blk.0.attn_qkv.bias")
     c.rope_attn_factor = float(_scalar(a("rope.scaling.attn_factor"), 1.0))
     c.tie_embeddings = not g.has_tensor("output.weight")
+    if arch in GEMMA_ARCHS:
+        c.embedding_scale = float(c.hidden_size) ** 0.5
+        c.ffn_act = "gelu_tanh"
+        c.post_norms = g.has_tensor("blk.0.post_attention_norm.weight")
+        if arch == "gemma2":
+            # llama.cpp's defaults when a Gemma-2 file does not carry the keys
+            c.attn_softcap = float(_scalar(a("attn_logit_softcapping"), 50.0))
+            c.final_softcap = float(_scalar(a("final_logit_softcapping"), 30.0))
+        if c.sliding_window > 0 and c.sliding_window_pattern <= 0:
+            c.sliding_window_pattern = 2 if arch == "gemma2" else 6 if arch == "gemma3" else 0
+        if arch == "gemma3":
+            c.rope_theta_swa = float(_scalar(a("rope.freq_base_swa"), 10000.0))
+        scale = a("attention.scale")
+        if scale is not None and float(scale) > 0:
+            c.attn_scale = float(scale)
+        elif (arch, c.n_layers) in (("gemma2", 46), ("gemma3", 62)):
+            # the 27B models scale the scores by (hidden_size / heads) ** -0.5 instead of head_dim ** -0.5; the file
+            # format has no key for it, llama.cpp keys it on the model size as well
+            c.attn_scale = float(c.hidden_size // c.n_heads) ** -0.5
     # MoE
     c.n_experts = int(_scalar(a("expert_count"), 0))
     c.n_experts_used = int(_scalar(a("expert_used_count"), 0))
@@ -241,6 +272,12 @@ _PRESETS: Dict[str, Dict[str, Any]] = {
     "qwen3-30b-a3b": dict(arch="qwen3moe", vocab_size=151936, hidden_size=2048, n_layers=48, n_heads=32, n_kv_heads=4,
                           head_dim=128, ffn_size=6144, rope_theta=1000000.0, context_length=32768, qk_norm=True,
                           n_experts=128, n_experts_used=8, expert_ffn_size=768),
+    # Gemma-3-27B: 5 windowed layers (1024 tokens, rotary base 1e4) to every global one (base 1e6, positions / 8)
+    "gemma3-27b": dict(arch="gemma3", vocab_size=262208, hidden_size=5376, n_layers=62, n_heads=32, n_kv_heads=16,
+                       head_dim=128, ffn_size=21504, rms_eps=1e-6, rope_theta=1000000.0, rope_theta_swa=10000.0,
+                       rope_scaling=RopeScaling(type="linear", factor=8.0), context_length=131072, sliding_window=1024,
+                       sliding_window_pattern=6, qk_norm=True, post_norms=True, ffn_act="gelu_tanh",
+                       embedding_scale=5376 ** 0.5, attn_scale=168 ** -0.5, tie_embeddings=True),
     "qwen-draft-0.5b": dict(arch="qwen2", vocab_size=151936, hidden_size=896, n_layers=24, n_heads=14, n_kv_heads=2,
                             head_dim=64, ffn_size=4864, rope_theta=1000000.0, context_length=32768,
                             tie_embeddings=True),

@@ -1,8 +1,9 @@
 """Decoder-only transformer forward over a flat token batch and a paged KV cache.
 
 One code path serves decode (1 query row per sequence), chunked prefill and speculative
-verification (several rows per sequence) for Llama / Mistral / Qwen3 (per-head QK-norm)
-and the MoE families Mixtral / Qwen3-MoE / DeepSeek-MoE (shared expert, sigmoid+bias
+verification (several rows per sequence) for Llama / Mistral / Qwen3 (per-head QK-norm),
+Gemma 1-3 (GeGLU, scaled embeddings, norms on the branch outputs, soft-capped logits, local / global
+layers with two rotary bases; the reference's ``layers.rs:293-304,1323,1515``) and the MoE families Mixtral / Qwen3-MoE / DeepSeek-MoE (shared expert, sigmoid+bias
 routing).  Layer semantics follow the reference's per-token layer loop
 (``oxidize-core/src/model/inference/layers.rs``: attention :893+, MoE + shared expert
 :1420-1475) and MoE math ``moe_ffn_forward_weights`` (``model/inference.rs:1662-1935``); the
@@ -105,7 +106,16 @@ class Transformer:
             inv_freq=opref.rope_inv_freq(cfg.rotary_dim, cfg.rope_theta, cfg.rope_scaling, device=dev, freq_factors=ff),
             pairing=cfg.rope_pairing, mscale=mscale,
             n_heads=self.n_heads_local, n_kv_heads=self.n_kv_local, head_dim=cfg.head_dim)
-        self.attn_scale = cfg.head_dim ** -0.5
+        # windowed layers with a rotary base of their own (Gemma-3): that base, and no context scaling
+        self.rope_swa = None
+        if cfg.rope_theta_swa > 0 and cfg.sliding_window > 0:
+            self.rope_swa = RopeState(
+                inv_freq=opref.rope_inv_freq(cfg.rotary_dim, cfg.rope_theta_swa, None, device=dev),
+                pairing=cfg.rope_pairing, mscale=1.0,
+                n_heads=self.n_heads_local, n_kv_heads=self.n_kv_local, head_dim=cfg.head_dim)
+        self.attn_scale = cfg.attn_scale if cfg.attn_scale > 0 else cfg.head_dim ** -0.5
+        if dev.type == "cuda" and cfg.attn_softcap > 0:
+            raise NotImplementedError("soft-capped attention scores (Gemma-2) are implemented on the CPU path only")
         self._fuse_qkv_rope = dev.type == "cuda" and fuse_qkv_rope
         if dev.type == "cuda" and fuse_swiglu:
             self._interleave_gate_up()
@@ -127,8 +137,9 @@ class Transformer:
                     and w.parts[0].data.is_contiguous())
 
         for lw in self.w.layers:
-            if lw.router is not None or not (bf16_single(lw.wqkv) and bf16_single(lw.wo) and bf16_single(lw.w_gate_up)
-                                            and bf16_single(lw.w_down) and lw.w_gate_up.swiglu_interleaved):
+            if (lw.router is not None or lw.post_attn_norm is not None or lw.post_ffn_norm is not None
+                    or not (bf16_single(lw.wqkv) and bf16_single(lw.wo) and bf16_single(lw.w_gate_up)
+                            and bf16_single(lw.w_down) and lw.w_gate_up.swiglu_interleaved)):
                 continue
             if lw.wo.parts[0].shape[0] % 8 or lw.w_down.parts[0].shape[0] % 8:
                 continue
@@ -166,13 +177,15 @@ class Transformer:
         cfg = self.cfg
         eps = cfg.rms_eps
         wq = lw.wqkv.parts[0].data
-        if self._fuse_qkv_rope and opcuda.qkv_rope_fusable(lw.wqkv.parts, kv, self.rope, lw.q_norm, lw.k_norm):
-            q = opcuda.linear_qkv_rope(r, wq, meta.positions, meta.slot_mapping, kv, layer, self.rope, sumsq_in=acc[cur],
+        window = cfg.layer_sliding_window(self.w.first_layer + layer)
+        rope = self._layer_rope(window)
+        if self._fuse_qkv_rope and opcuda.qkv_rope_fusable(lw.wqkv.parts, kv, rope, lw.q_norm, lw.k_norm):
+            q = opcuda.linear_qkv_rope(r, wq, meta.positions, meta.slot_mapping, kv, layer, rope, sumsq_in=acc[cur],
                                        eps=eps, clear=acc[1 - cur])
         else:
             qkv = opcuda.gemm_bf16(r, wq, sumsq_in=acc[cur], eps=eps, clear=acc[1 - cur])
-            q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, self.rope, lw.q_norm, lw.k_norm, eps)
-        attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, cfg.layer_sliding_window(self.w.first_layer + layer))
+            q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, rope, lw.q_norm, lw.k_norm, eps)
+        attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, window)
         cur = 1 - cur
         self._row_parallel_into(attn.reshape(attn.shape[0], -1), lw.wo, r, acc[cur])
         act = opcuda.linear_swiglu(r, lw.w_gate_up.parts[0].data, sumsq_in=acc[cur], eps=eps, clear=acc[1 - cur])
@@ -185,6 +198,8 @@ class Transformer:
         epilogue of the gate_up GEMM (one kernel and one activation round trip less per layer)."""
         from ..ops import cuda as opcuda
 
+        if self.cfg.ffn_act != "silu":
+            return  # the GEMM epilogue computes SiLU(gate) * up only
         for lw in self.w.layers:
             w = lw.w_gate_up
             if w is None or w.swiglu_interleaved or len(w.parts) != 1 or w.bias is not None:
@@ -196,19 +211,24 @@ class Transformer:
             w.swiglu_interleaved = True
 
     # ------------------------------------------------------------------ blocks
+    def _layer_rope(self, window: int) -> RopeState:
+        """Rotary state of a layer: windowed layers use their own base when the model has one."""
+        return self.rope_swa if (window > 0 and self.rope_swa is not None) else self.rope
+
     def _attention(self, lw: LayerWeights, layer: int, x: torch.Tensor, meta: BatchMeta, kv) -> torch.Tensor:
         cfg = self.cfg
+        window = cfg.layer_sliding_window(self.w.first_layer + layer)
+        rope = self._layer_rope(window)
         if self._fuse_qkv_rope and x.is_cuda and lw.wqkv.bias is None:
             from ..ops import cuda as opcuda
 
-            if opcuda.qkv_rope_fusable(lw.wqkv.parts, kv, self.rope, lw.q_norm, lw.k_norm):
-                q = opcuda.linear_qkv_rope(x, lw.wqkv.parts[0].data, meta.positions, meta.slot_mapping, kv, layer, self.rope)
-                attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, cfg.layer_sliding_window(self.w.first_layer + layer))
+            if opcuda.qkv_rope_fusable(lw.wqkv.parts, kv, rope, lw.q_norm, lw.k_norm):
+                q = opcuda.linear_qkv_rope(x, lw.wqkv.parts[0].data, meta.positions, meta.slot_mapping, kv, layer, rope)
+                attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, window)
                 return self.comm.linear_allreduce(attn.reshape(attn.shape[0], -1), lw.wo)
         qkv = ops.linear(x, lw.wqkv)
-        q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, self.rope,
-                                 lw.q_norm, lw.k_norm, cfg.rms_eps)
-        attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, cfg.layer_sliding_window(self.w.first_layer + layer))
+        q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, rope, lw.q_norm, lw.k_norm, cfg.rms_eps)
+        attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, window, cfg.attn_softcap)
         return self.comm.linear_allreduce(attn.reshape(attn.shape[0], -1), lw.wo)
 
     def _dense_ffn(self, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
@@ -216,6 +236,8 @@ class Transformer:
             from ..ops import cuda as opcuda
 
             act = opcuda.linear_swiglu(x, lw.w_gate_up.parts[0].data)
+        elif self.cfg.ffn_act == "gelu_tanh":
+            act = ops.gelu_mul(ops.linear(x, lw.w_gate_up))
         else:
             act = ops.silu_mul(ops.linear(x, lw.w_gate_up))
         return self.comm.linear_allreduce(act, lw.w_down)
@@ -286,8 +308,12 @@ class Transformer:
                 h, acc = torch.zeros_like(residual), None
             x, residual = ops.add_rmsnorm(h, residual, lw.attn_norm, cfg.rms_eps)
             h = self._attention(lw, li, x, meta, kv)
+            if lw.post_attn_norm is not None:
+                h = ops.rmsnorm(h, lw.post_attn_norm, cfg.rms_eps)
             x, residual = ops.add_rmsnorm(h, residual, lw.ffn_norm, cfg.rms_eps)
             h = self._moe_ffn(lw, x) if lw.router is not None else self._dense_ffn(lw, x)
+            if lw.post_ffn_norm is not None:
+                h = ops.rmsnorm(h, lw.post_ffn_norm, cfg.rms_eps)
             if capture is not None and gl in capture.get("layers", ()):
                 capture.setdefault("hidden", {})[gl] = (h.float() + residual.float())
             if _profiler.TRACE_FWD:
@@ -297,7 +323,7 @@ class Transformer:
         return h, residual
 
     def embed(self, token_ids: torch.Tensor) -> torch.Tensor:
-        return ops.embed(token_ids, self.w.embed, self.act_dtype)
+        return ops.embed(token_ids, self.w.embed, self.act_dtype, self.cfg.embedding_scale)
 
     # ------------------------------------------------------------------ pipeline stages
     def _stage_input(self, meta: BatchMeta):
@@ -328,6 +354,9 @@ class Transformer:
         logits = ops.linear(x, self.w.lm_head).float()
         if self.w.tp_size > 1 and self.w.lm_head.out_features != self.cfg.vocab_size:
             logits = self.comm.all_gather_cat(logits, dim=-1)
+        cap = self.cfg.final_softcap
+        if cap > 0:
+            logits = torch.tanh(logits / cap) * cap
         return (logits, hidden) if return_hidden else logits
 
     def greedy_tokens(self, meta: BatchMeta, kv, tie: str = "lowest", feed: Optional[torch.Tensor] = None) -> torch.Tensor:

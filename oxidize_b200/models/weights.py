@@ -170,6 +170,9 @@ class LayerWeights:
     ffn_norm: torch.Tensor
     q_norm: Optional[torch.Tensor] = None
     k_norm: Optional[torch.Tensor] = None
+    # Gemma-2/3: norms applied to the attention / FFN branch outputs before the residual add
+    post_attn_norm: Optional[torch.Tensor] = None
+    post_ffn_norm: Optional[torch.Tensor] = None
     # dense FFN
     w_gate_up: Optional[LinearWeight] = None
     w_down: Optional[LinearWeight] = None
@@ -344,6 +347,10 @@ def _load_layer(src: GGUFWeightSource, cfg: ModelConfig, i: int, tp_rank: int, t
     if src.has(f"{p}.attn_q_norm.weight"):
         lw.q_norm = src.vector(f"{p}.attn_q_norm.weight")
         lw.k_norm = src.vector(f"{p}.attn_k_norm.weight")
+    if src.has(f"{p}.post_attention_norm.weight"):
+        lw.post_attn_norm = src.vector(f"{p}.post_attention_norm.weight")
+    if src.has(f"{p}.post_ffw_norm.weight"):
+        lw.post_ffn_norm = src.vector(f"{p}.post_ffw_norm.weight")
     if src.has(f"{p}.ffn_gate_inp.weight"):
         lw.router = src.matrix(f"{p}.ffn_gate_inp.weight")
         if src.has(f"{p}.exp_probs_b.bias"):

@@ -66,6 +66,14 @@ def silu_mul(gate_up):
     return ref.silu_mul(gate_up)
 
 
+@instrument("gelu_mul")
+def gelu_mul(gate_up):
+    """tanh-GELU(gate) * up on the halves of a fused [T, 2F] projection (GeGLU)."""
+    if gate_up.is_cuda:
+        return _cuda().gelu_mul(gate_up)
+    return ref.gelu_mul(gate_up)
+
+
 @instrument("qk_rope_kv_write")
 def qk_rope_kv_write(qkv, positions, slot_mapping, kv, layer, rope, q_norm=None, k_norm=None, eps=1e-6):
     """Split fused qkv [T, (nq+2nkv)*hd], optional per-head QK RMSNorm, RoPE on q and k,
@@ -87,10 +95,12 @@ def qk_rope_kv_write(qkv, positions, slot_mapping, kv, layer, rope, q_norm=None,
 
 
 @instrument("paged_attention")
-def paged_attention(q, kv, layer, meta, scale, sliding_window=0):
+def paged_attention(q, kv, layer, meta, scale, sliding_window=0, softcap=0.0):
     if q.is_cuda:
+        if softcap > 0:
+            raise NotImplementedError("soft-capped attention scores (Gemma-2) are implemented on the CPU path only")
         return _cuda().paged_attention(q, kv, layer, meta, scale, sliding_window)
-    return ref.paged_attention(q, kv, layer, meta, scale, sliding_window)
+    return ref.paged_attention(q, kv, layer, meta, scale, sliding_window, softcap)
 
 
 @instrument("moe_route")

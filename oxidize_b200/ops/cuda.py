@@ -110,6 +110,7 @@ def _declare(L) -> None:
     L.oxb_embed.argtypes = [vp, vp, i32, sz, i32, i32, f32, vp, i32, vp]
     L.oxb_add_rmsnorm.argtypes = [vp, vp, vp, vp, vp, i32, i32, f32, vp]
     L.oxb_silu_mul.argtypes = [vp, vp, i32, i32, vp]
+    L.oxb_gelu_mul.argtypes = [vp, vp, i32, i32, vp]
     L.oxb_qk_rope_kvwrite.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, vp, f32, i32, i32, i32, i32, vp, vp, vp, i32,
                                       i32, i32, vp]
     L.oxb_argmax.argtypes = [vp, i32, i32, i32, i32, vp, vp, i32, vp]
@@ -391,6 +392,14 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     T, I2 = gate_up.shape
     out = torch.empty(T, I2 // 2, dtype=gate_up.dtype, device=gate_up.device)
     _check(lib().oxb_silu_mul(gate_up.data_ptr(), out.data_ptr(), T, I2 // 2, _stream()), "oxb_silu_mul")
+    return out
+
+
+def gelu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """tanh-GELU(gate) * up (GeGLU) on a fused bf16 [T, 2F] projection."""
+    T, I2 = gate_up.shape
+    out = torch.empty(T, I2 // 2, dtype=gate_up.dtype, device=gate_up.device)
+    _check(lib().oxb_gelu_mul(gate_up.data_ptr(), out.data_ptr(), T, I2 // 2, _stream()), "oxb_gelu_mul")
     return out
 
 

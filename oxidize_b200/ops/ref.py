@@ -198,12 +198,14 @@ def kv_gather(kv, layer: int, block_table: torch.Tensor, seq_len: int) -> Tuple[
     return d[0], d[1]
 
 
-def paged_attention(q: torch.Tensor, kv, layer: int, meta, scale: float, sliding_window: int = 0) -> torch.Tensor:
+def paged_attention(q: torch.Tensor, kv, layer: int, meta, scale: float, sliding_window: int = 0,
+                    softcap: float = 0.0) -> torch.Tensor:
     """Causal GQA attention of packed query rows against the paged cache.
 
     q: [T, n_heads, hd].  For sequence b the rows ``query_start[b]:query_start[b+1]`` are its
     last ``qlen`` positions (context length ``seq_lens[b]`` already includes them), so one
-    code path covers decode (qlen 1), chunked prefill and speculative verify (qlen K+1)."""
+    code path covers decode (qlen 1), chunked prefill and speculative verify (qlen K+1).
+    ``softcap`` > 0 replaces the scaled scores by ``softcap * tanh(scores / softcap)`` before masking (Gemma-2)."""
     T, nh, hd = q.shape
     out = torch.zeros(T, nh, hd, dtype=torch.float32, device=q.device)
     qs = meta.query_start.tolist()
@@ -219,6 +221,8 @@ def paged_attention(q: torch.Tensor, kv, layer: int, meta, scale: float, sliding
         g = nh // nkv
         qb = q[t0:t1].float().reshape(qlen, nkv, g, hd)
         s = torch.einsum("qkgd,lkd->kgql", qb, K) * scale
+        if softcap > 0:
+            s = torch.tanh(s / softcap) * softcap
         qpos = torch.arange(L - qlen, L, device=q.device)[:, None]
         kpos = torch.arange(L, device=q.device)[None, :]
         mask = kpos <= qpos

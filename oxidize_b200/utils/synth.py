@@ -103,6 +103,14 @@ def write_config_metadata(w: GGUFWriter, cfg: ModelConfig) -> None:
         w.add(f"{a}.attention.sliding_window", cfg.sliding_window, U)
         if cfg.sliding_window_pattern:
             w.add(f"{a}.attention.sliding_window_pattern", cfg.sliding_window_pattern, U)
+    F = GGUFValueType.FLOAT32
+    if cfg.rope_theta_swa > 0:
+        w.add(f"{a}.rope.freq_base_swa", float(cfg.rope_theta_swa), F)
+    if cfg.attn_scale > 0:
+        w.add(f"{a}.attention.scale", float(cfg.attn_scale), F)
+    if a == "gemma2":
+        w.add(f"{a}.attn_logit_softcapping", float(cfg.attn_softcap), F)
+        w.add(f"{a}.final_logit_softcapping", float(cfg.final_softcap), F)
     if cfg.rope_scaling.type != "none":
         w.add(f"{a}.rope.scaling.type", cfg.rope_scaling.type)
         w.add(f"{a}.rope.scaling.factor", float(cfg.rope_scaling.factor), GGUFValueType.FLOAT32)
@@ -201,6 +209,9 @@ def synth_gguf(path: str, cfg: ModelConfig, quant: str = "Q4_K_M", seed: int = 0
             vec(f"{p}.attn_q_norm.weight", hd)
             vec(f"{p}.attn_k_norm.weight", hd)
         vec(f"{p}.ffn_norm.weight", h)
+        if cfg.post_norms:  # Gemma-2/3: norms on the branch outputs
+            vec(f"{p}.post_attention_norm.weight", h)
+            vec(f"{p}.post_ffw_norm.weight", h)
         if cfg.layer_is_moe(min(i, L - 1)):
             w.add_tensor(f"{p}.ffn_gate_inp.weight",
                          (rng.standard_normal((cfg.n_experts, h)) * WEIGHT_STD).astype(np.float32),
@@ -289,6 +300,8 @@ def synth_weights(cfg: ModelConfig, device, quant: str = "BF16", seed: int = 0, 
                           ffn_norm=ones(h))
         if cfg.qk_norm:
             lw.q_norm, lw.k_norm = ones(hd), ones(hd)
+        if cfg.post_norms:
+            lw.post_attn_norm, lw.post_ffn_norm = ones(h), ones(h)
         if cfg.layer_is_moe(i):
             lw.router = _rand_matrix(cfg.n_experts, h, "F32" if device.type == "cpu" else "BF16", device, shared)
             e0, e1 = shard_range(cfg.n_experts, ep_rank, ep_size)

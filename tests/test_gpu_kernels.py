@@ -96,6 +96,17 @@ def test_silu_mul(C):
     assert _rel_err(C.silu_mul(gu), ref.silu_mul(gu)) < 5e-3
 
 
+def test_gelu_mul(C):
+    """tanh-GELU(gate) * up (GeGLU) against the fp32 statement, including large |gate| (no overflow to NaN)."""
+    from oxidize_b200.ops import ref
+
+    gu = torch.randn(37, 2 * 1408, device="cuda").to(torch.bfloat16)
+    gu[0, :8] = torch.tensor([-60.0, -20.0, -6.0, -1.0, 1.0, 6.0, 20.0, 60.0], device="cuda").to(torch.bfloat16)
+    got = C.gelu_mul(gu)
+    assert torch.isfinite(got.float()).all()
+    assert _rel_err(got, ref.gelu_mul(gu)) < 5e-3
+
+
 @pytest.mark.parametrize("qtype", ["BF16", "Q8_0", "Q4_0", "Q4_K", "Q5_K", "Q6_K", "NVFP4"])
 def test_embed_and_dequant(C, qtype):
     from oxidize_b200.models.weights import QTensor, qtensor_from_dense
@@ -266,6 +277,36 @@ def test_model_gpu_matches_cpu(C, tmp_path):
     sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
     cpu = LLM.from_gguf(path, EngineConfig(**ec), device="cpu")
     gpu = LLM.from_gguf(path, EngineConfig(**ec, cuda_graphs=False), device="cuda")
+    cpu.runner.keep_logits = gpu.runner.keep_logits = True
+    for p in prompts:
+        cpu.add_request(p, sp)
+        gpu.add_request(p, sp)
+    for _ in range(4):
+        cpu.step()
+        gpu.step()
+        lc, lg = cpu.last_step[1].logits, gpu.last_step[1].logits
+        assert _rel_err(lg.cpu(), lc) < 3e-2
+    _check_status(C)
+
+
+def test_gemma3_model_gpu_matches_cpu(C, tmp_path):
+    """Gemma-3 layer semantics on the device: scaled embeddings, GeGLU kernel, norms on the branch outputs, QK-norm,
+    windowed layers with their own rotary base, a softmax scale that is not head_dim ** -0.5."""
+    from oxidize_b200.engine.llm import LLM, EngineConfig
+    from oxidize_b200.engine.sampler import SamplingParams
+    from oxidize_b200.models.config import preset
+    from oxidize_b200.utils.synth import synth_gguf
+
+    cfg = preset("gemma3-27b", n_layers=7, vocab_size=512, hidden_size=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn_size=512,
+                 sliding_window=16, embedding_scale=16.0, attn_scale=0.11, context_length=4096)
+    path = str(tmp_path / "gemma3.gguf")
+    synth_gguf(path, cfg, "BF16", seed=0, norm_jitter=0.1)
+    ec = dict(max_model_len=128, max_num_seqs=4, num_kv_blocks=64, prefill_chunk_size=32, max_num_batched_tokens=64)
+    prompts = [[5, 9, 200, 31, 7], list(range(3, 60))]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    cpu = LLM.from_gguf(path, EngineConfig(**ec), device="cpu")
+    gpu = LLM.from_gguf(path, EngineConfig(**ec, cuda_graphs=False), device="cuda")
+    assert gpu.model.cfg.post_norms and gpu.model.rope_swa is not None and gpu.model.cfg.ffn_act == "gelu_tanh"
     cpu.runner.keep_logits = gpu.runner.keep_logits = True
     for p in prompts:
         cpu.add_request(p, sp)

@@ -1,0 +1,108 @@
+"""Model semantics against an independent oracle: the Hugging Face `transformers` implementations, on CPU in float32.
+
+A tiny random-init model of each family is saved as SafeTensors + config.json, converted to GGUF by this package's
+converter, loaded by the engine and run through the ordinary serving path (chunked prefill, paged KV, greedy decode).
+The logits after the prompt and the greedy continuation must agree with the oracle's.  This covers the converter's
+tensor-name map and metadata, the loader, and every family-specific piece of layer math: q/k/v biases (Qwen2), per-head
+QK-norm (Qwen3), fused qkv / gate-up tensors (Phi-3), softmax top-k routing (Mixtral, Qwen3-MoE), and for Gemma 1-3 the
+scaled embeddings, GeGLU, norms on the branch outputs, (w + 1) norm weights, soft-capped scores and logits, the softmax
+scale taken from query_pre_attn_scalar, and local / global layers with a window and two rotary bases.
+"""
+import os
+
+import pytest
+import torch
+
+T = pytest.importorskip("transformers")
+
+from oxidize_b200.engine.llm import LLM, EngineConfig  # noqa: E402
+from oxidize_b200.engine.sampler import SamplingParams  # noqa: E402
+from oxidize_b200.formats.convert import convert_safetensors_to_gguf  # noqa: E402
+from oxidize_b200.formats.gguf import load_gguf  # noqa: E402
+from oxidize_b200.models.config import config_from_gguf  # noqa: E402
+
+VOCAB = 199
+COMMON = dict(vocab_size=VOCAB, hidden_size=64, intermediate_size=96, num_hidden_layers=4, num_attention_heads=4,
+              num_key_value_heads=2, max_position_embeddings=256, attn_implementation="eager")
+
+
+def _build(name: str):
+    c = dict(COMMON)
+    if name == "llama":
+        return T.LlamaForCausalLM(T.LlamaConfig(**c))
+    if name == "qwen2":
+        return T.Qwen2ForCausalLM(T.Qwen2Config(**c))
+    if name == "qwen3":
+        return T.Qwen3ForCausalLM(T.Qwen3Config(**c, head_dim=32))
+    if name == "phi3":
+        return T.Phi3ForCausalLM(T.Phi3Config(**c, pad_token_id=0))
+    if name == "mixtral":
+        return T.MixtralForCausalLM(T.MixtralConfig(**c, num_local_experts=4, num_experts_per_tok=2))
+    if name == "qwen3moe":
+        return T.Qwen3MoeForCausalLM(T.Qwen3MoeConfig(**c, head_dim=32, num_experts=8, num_experts_per_tok=2,
+                                                      moe_intermediate_size=48, norm_topk_prob=True))
+    if name == "gemma":
+        return T.GemmaForCausalLM(T.GemmaConfig(**c, head_dim=32))
+    if name == "gemma2":
+        # window 8 on every other layer, soft caps 50 / 30, softmax scale 24 ** -0.5 (not head_dim ** -0.5)
+        return T.Gemma2ForCausalLM(T.Gemma2Config(**c, head_dim=32, sliding_window=8, query_pre_attn_scalar=24))
+    if name == "gemma3":
+        # 7 layers: five windowed (rotary base 1e4), the sixth global (base 1e6), the seventh windowed again
+        c["num_hidden_layers"] = 7
+        return T.Gemma3ForCausalLM(T.Gemma3TextConfig(**c, head_dim=32, sliding_window=8, query_pre_attn_scalar=40))
+    raise KeyError(name)
+
+
+FAMILIES = ["llama", "qwen2", "qwen3", "phi3", "mixtral", "qwen3moe", "gemma", "gemma2", "gemma3"]
+
+
+@pytest.mark.parametrize("family", FAMILIES)
+def test_logits_and_greedy_tokens_match_transformers(family, tmp_path):
+    try:
+        torch.manual_seed(0)
+        ref = _build(family).eval().float()
+    except (AttributeError, TypeError) as e:  # a transformers build without this family
+        pytest.skip(f"transformers cannot build {family}: {e}")
+    with torch.no_grad():
+        for pname, p in ref.named_parameters():
+            if "norm" in pname:
+                p.add_(torch.randn_like(p) * 0.3)  # norms away from their initial value, so that they matter
+            elif p.ndim == 2:
+                p.mul_(3.0)  # larger weights: logits with more spread than the 0.02-std init gives
+    src = str(tmp_path / "hf")
+    ref.save_pretrained(src, safe_serialization=True)
+    path = convert_safetensors_to_gguf(src, str(tmp_path / "m.gguf"), "F32")
+    cfg = config_from_gguf(load_gguf(path))
+    if family == "gemma2":
+        assert cfg.attn_softcap == 50.0 and cfg.final_softcap == 30.0 and cfg.sliding_window_pattern == 2 and cfg.post_norms
+        assert abs(cfg.attn_scale - 24 ** -0.5) < 1e-6
+    if family == "gemma3":
+        assert cfg.sliding_window_pattern == 6 and cfg.rope_theta_swa == 10000.0 and cfg.rope_theta == 1000000.0
+        assert cfg.qk_norm and cfg.post_norms and cfg.ffn_act == "gelu_tanh" and cfg.embedding_scale == 8.0
+    # prefill in chunks of 16 rows: prompts longer than that cross chunk (and window) boundaries
+    llm = LLM.from_gguf(path, EngineConfig(kv_cache_dtype="f32", max_model_len=128, max_num_seqs=2, num_kv_blocks=32,
+                                           prefill_chunk_size=16, max_num_batched_tokens=16, enable_prefix_cache=False),
+                        device="cpu")
+    llm.runner.keep_logits = True
+    gen = torch.Generator().manual_seed(1)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    for n_prompt in (5, 19, 40):
+        ids = torch.randint(3, VOCAB, (n_prompt,), generator=gen).tolist()
+        with torch.no_grad():
+            want = ref(torch.tensor([ids])).logits[0, -1]
+            want_tokens = ref.generate(torch.tensor([ids]), attention_mask=torch.ones(1, n_prompt, dtype=torch.long),
+                                       max_new_tokens=6, do_sample=False, pad_token_id=0)[0, n_prompt:].tolist()
+        llm.add_request(ids, sp)
+        first, tokens = None, None
+        while llm.has_unfinished:
+            outs = llm.step()
+            lg = llm.last_step[1].logits if llm.last_step is not None else None
+            if first is None and lg is not None and lg.shape[0] == 1:
+                first = lg.float()[0].clone()  # the step that finished the prompt
+            for o in outs:
+                if o.finished:
+                    tokens = o.token_ids
+        err = (first - want).abs().max().item() / want.abs().max().item()
+        assert err < 2e-5, f"{family}, {n_prompt}-token prompt: logits differ by {err:.2e} of their range"
+        assert tokens == want_tokens, f"{family}, {n_prompt}-token prompt: {tokens} != {want_tokens}"
+    assert os.path.getsize(path) > 0
