@@ -95,7 +95,7 @@ class LLM:
         kv_dtype = c.kv_cache_dtype
         if kv_dtype == "auto":
             kv_dtype = "bf16" if self.device.type == "cuda" else "f32"
-        spec = KVCacheSpec(len(weights.layers), self.model.n_kv_local, self.cfg.head_dim, c.kv_page_size, kv_dtype)
+        spec = KVCacheSpec(len(weights.layers), self.model.n_kv_local, self.model.kv_head_dim, c.kv_page_size, kv_dtype)
         nblocks = c.num_kv_blocks or self._auto_blocks(spec)
         self.kv = KVCache(spec, nblocks, self.device)
         self.pool = make_block_pool(nblocks, c.kv_page_size, c.enable_prefix_cache)

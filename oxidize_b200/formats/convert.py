@@ -63,12 +63,19 @@ def write_hf_metadata(w: GGUFWriter, arch: str, c: Dict[str, Any]) -> None:
     w.add(f"{arch}.attention.head_count", heads, U)
     w.add(f"{arch}.attention.head_count_kv", int(c.get("num_key_value_heads", heads)), U)
     hd = int(c.get("head_dim") or hidden // heads)
+    if c.get("kv_lora_rank"):
+        # latent attention: per-head query / key width (position-free + rotary part) and value width
+        hd = int(c["qk_nope_head_dim"]) + int(c["qk_rope_head_dim"])
+        w.add(f"{arch}.attention.kv_lora_rank", int(c["kv_lora_rank"]), U)
+        if c.get("q_lora_rank"):
+            w.add(f"{arch}.attention.q_lora_rank", int(c["q_lora_rank"]), U)
     w.add(f"{arch}.attention.key_length", hd, U)
-    w.add(f"{arch}.attention.value_length", hd, U)
+    w.add(f"{arch}.attention.value_length", int(c.get("v_head_dim") or hd), U)
     w.add(f"{arch}.attention.layer_norm_rms_epsilon", float(c.get("rms_norm_eps", 1e-5)), F)
     theta, theta_swa, rs = _rope_settings(c)
     w.add(f"{arch}.rope.freq_base", theta, F)
-    w.add(f"{arch}.rope.dimension_count", int(hd * float(c.get("partial_rotary_factor", 1.0))), U)
+    w.add(f"{arch}.rope.dimension_count",
+          int(c["qk_rope_head_dim"]) if c.get("kv_lora_rank") else int(hd * float(c.get("partial_rotary_factor", 1.0))), U)
     if c.get("sliding_window"):
         w.add(f"{arch}.attention.sliding_window", int(c["sliding_window"]), U)
     if arch in GEMMA:
@@ -92,17 +99,23 @@ def write_hf_metadata(w: GGUFWriter, arch: str, c: Dict[str, Any]) -> None:
             w.add(f"{arch}.rope.scaling.factor", float(rs.get("factor", 1.0)), F)
             w.add(f"{arch}.rope.scaling.original_context_length",
                   int(rs.get("original_max_position_embeddings", c.get("max_position_embeddings", 0))), U)
+            if kind == "yarn" and c.get("kv_lora_rank"):
+                w.add(f"{arch}.rope.scaling.yarn_log_multiplier", 0.1 * float(rs.get("mscale_all_dim") or 0.0), F)
     n_exp = int(c.get("num_local_experts") or c.get("num_experts") or c.get("n_routed_experts") or 0)
     if n_exp:
         w.add(f"{arch}.expert_count", n_exp, U)
         w.add(f"{arch}.expert_used_count", int(c.get("num_experts_per_tok", 2)), U)
         w.add(f"{arch}.expert_feed_forward_length", int(c.get("moe_intermediate_size") or c.get("intermediate_size")), U)
-        w.add(f"{arch}.expert_gating_func", 2 if c.get("scoring_func") == "sigmoid" else 1, U)
+        # DeepSeek-V3 configs often omit scoring_func: that model always scores with a sigmoid
+        sigmoid = c.get("scoring_func") == "sigmoid" or (c.get("scoring_func") is None and c.get("model_type") == "deepseek_v3")
+        w.add(f"{arch}.expert_gating_func", 2 if sigmoid else 1, U)
         w.add(f"{arch}.expert_weights_scale", float(c.get("routed_scaling_factor", 1.0)), F)
         w.add(f"{arch}.expert_weights_norm", bool(c.get("norm_topk_prob", True)))
         if c.get("n_group"):
             w.add(f"{arch}.expert_group_count", int(c["n_group"]), U)
             w.add(f"{arch}.expert_group_used_count", int(c.get("topk_group", 1)), U)
+        if c.get("n_shared_experts"):
+            w.add(f"{arch}.expert_shared_count", int(c["n_shared_experts"]), U)
         if c.get("first_k_dense_replace"):
             w.add(f"{arch}.leading_dense_block_count", int(c["first_k_dense_replace"]), U)
 

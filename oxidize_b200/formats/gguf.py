@@ -565,6 +565,13 @@ _HF_LAYER_MAP = {
     "self_attn.q_proj.bias": "attn_q.bias",
     "self_attn.k_proj.bias": "attn_k.bias",
     "self_attn.v_proj.bias": "attn_v.bias",
+    # latent attention (DeepSeek-V2/V3)
+    "self_attn.q_a_proj.weight": "attn_q_a.weight",
+    "self_attn.q_a_layernorm.weight": "attn_q_a_norm.weight",
+    "self_attn.q_b_proj.weight": "attn_q_b.weight",
+    "self_attn.kv_a_proj_with_mqa.weight": "attn_kv_a_mqa.weight",
+    "self_attn.kv_a_layernorm.weight": "attn_kv_a_norm.weight",
+    "self_attn.kv_b_proj.weight": "attn_kv_b.weight",
     "self_attn.q_norm.weight": "attn_q_norm.weight",
     "self_attn.k_norm.weight": "attn_k_norm.weight",
     "post_attention_layernorm.weight": "ffn_norm.weight",

@@ -83,6 +83,14 @@ class ModelConfig:
     final_softcap: float = 0.0  # the same on the output logits
     rope_theta_swa: float = 0.0  # rotary base of the windowed layers (Gemma-3: 10000, unscaled); 0 = same as rope_theta
     attn_scale: float = 0.0  # softmax scale; 0 = head_dim ** -0.5
+    # Multi-head latent attention (DeepSeek-V2/V3; the reference's ``deepseek_mla_layer``,
+    # oxidize-core/src/model/inference/layers.rs:1547).  head_dim is the query / key width per head
+    # (qk_nope_dim + rope_dim); keys and values are rebuilt from one shared latent of kv_lora_rank values per token.
+    kv_lora_rank: int = 0  # > 0: the attention layers are latent-attention layers
+    q_lora_rank: int = 0  # 0: one full query projection; > 0: down-projection, norm, up-projection
+    qk_nope_dim: int = 0  # part of every query / key head that carries no position
+    v_head_dim: int = 0  # value width per head
+    yarn_log_multiplier: float = 0.0  # YaRN: the scores are scaled by (1 + this * ln(factor)) ** 2
     # MoE
     n_experts: int = 0
     n_experts_used: int = 0
@@ -103,6 +111,10 @@ class ModelConfig:
     @property
     def is_moe(self) -> bool:
         return self.n_experts > 0
+
+    @property
+    def is_mla(self) -> bool:
+        return self.kv_lora_rank > 0
 
     @property
     def rotary_dim(self) -> int:
@@ -157,9 +169,6 @@ def _scalar(v, default):
 def config_from_gguf(g: GGUFFile) -> ModelConfig:
     arch = g.architecture
     check_architecture(arch)
-    if any(g.has_tensor(f"blk.{i}.attn_kv_a_mqa.weight") for i in (0, 1)):
-        raise UnsupportedArchitecture("multi-head latent attention (attn_kv_a_mqa / attn_kv_b tensors) is not implemented; "
-                                      "only the grouped-query DeepSeek-MoE variants load")
     a = g.arch_get
     c = ModelConfig(arch=arch, name=str(g.get("general.name", "")))
     emb = g.tensors.get("token_embd.weight")
@@ -209,6 +218,22 @@ def config_from_gguf(g: GGUFFile) -> ModelConfig:
     c.attn_bias = g.has_tensor("blk.0.attn_q.bias") or g.has_tensor("blk.0.attn_qkv.bias")
     c.rope_attn_factor = float(_scalar(a("rope.scaling.attn_factor"), 1.0))
     c.tie_embeddings = not g.has_tensor("output.weight")
+    if g.has_tensor("blk.0.attn_kv_a_mqa.weight"):
+        # latent attention.  Two metadata conventions exist: key_length / value_length are the per-head widths
+        # (nope + rope, v) and head_count_kv = heads; or they describe the cached latent (kv_lora + rope, kv_lora) with one
+        # KV head, and key_length_mla / value_length_mla carry the per-head widths.
+        c.kv_lora_rank = int(_scalar(a("attention.kv_lora_rank"), g.tensors["blk.0.attn_kv_a_norm.weight"].shape[-1]))
+        c.q_lora_rank = int(_scalar(a("attention.q_lora_rank"), 0)) if g.has_tensor("blk.0.attn_q_a.weight") else 0
+        rope = int(_scalar(a("rope.dimension_count"), 0)) or g.tensors["blk.0.attn_kv_a_mqa.weight"].shape[0] - c.kv_lora_rank
+        qk = int(_scalar(a("attention.key_length_mla"), 0)) or int(key_len or 0)
+        vd = int(_scalar(a("attention.value_length_mla"), 0)) or int(_scalar(a("attention.value_length"), 0))
+        if g.has_tensor("blk.0.attn_kv_b.weight") and (qk <= rope or vd <= 0):
+            per_head = g.tensors["blk.0.attn_kv_b.weight"].shape[0] // c.n_heads  # nope + v, equal in all released models
+            qk, vd = qk if qk > rope else per_head // 2 + rope, vd or per_head // 2
+        c.head_dim, c.rope_dim, c.qk_nope_dim, c.v_head_dim = qk, rope, qk - rope, vd
+        c.n_kv_heads = c.n_heads
+        c.rope_pairing = "adjacent"  # the rotary part is stored with interleaved pairs and files keep that order
+        c.yarn_log_multiplier = float(_scalar(a("rope.scaling.yarn_log_multiplier"), 0.0))
     if arch in GEMMA_ARCHS:
         c.embedding_scale = float(c.hidden_size) ** 0.5
         c.ffn_act = "gelu_tanh"
@@ -278,6 +303,15 @@ _PRESETS: Dict[str, Dict[str, Any]] = {
                        rope_scaling=RopeScaling(type="linear", factor=8.0), context_length=131072, sliding_window=1024,
                        sliding_window_pattern=6, qk_norm=True, post_norms=True, ffn_act="gelu_tanh",
                        embedding_scale=5376 ** 0.5, attn_scale=168 ** -0.5, tie_embeddings=True),
+    # DeepSeek-V3: latent attention (512-wide latent + 64 rotary values cached per token), 3 dense layers, then 256 routed
+    # experts (8 of them per token, out of 4 of 8 groups) and a shared expert
+    "deepseek-v3": dict(arch="deepseek2", vocab_size=129280, hidden_size=7168, n_layers=61, n_heads=128, n_kv_heads=128,
+                        head_dim=192, rope_dim=64, qk_nope_dim=128, v_head_dim=128, kv_lora_rank=512, q_lora_rank=1536,
+                        ffn_size=18432, rms_eps=1e-6, rope_theta=10000.0, rope_pairing="adjacent", context_length=163840,
+                        rope_scaling=RopeScaling(type="yarn", factor=40.0, original_context_length=4096),
+                        yarn_log_multiplier=0.1, n_experts=256, n_experts_used=8, expert_ffn_size=2048,
+                        expert_gating="sigmoid", expert_weights_scale=2.5, expert_group_count=8, expert_group_used_count=4,
+                        leading_dense_blocks=3, n_shared_experts=1, shared_expert_ffn_size=2048, router_bias=True),
     "qwen-draft-0.5b": dict(arch="qwen2", vocab_size=151936, hidden_size=896, n_layers=24, n_heads=14, n_kv_heads=2,
                             head_dim=64, ffn_size=4864, rope_theta=1000000.0, context_length=32768,
                             tie_embeddings=True),

@@ -3,7 +3,8 @@
 One code path serves decode (1 query row per sequence), chunked prefill and speculative
 verification (several rows per sequence) for Llama / Mistral / Qwen3 (per-head QK-norm),
 Gemma 1-3 (GeGLU, scaled embeddings, norms on the branch outputs, soft-capped logits, local / global
-layers with two rotary bases; the reference's ``layers.rs:293-304,1323,1515``) and the MoE families Mixtral / Qwen3-MoE / DeepSeek-MoE (shared expert, sigmoid+bias
+layers with two rotary bases; the reference's ``layers.rs:293-304,1323,1515``), DeepSeek-V2/V3 latent
+attention (``deepseek_mla_layer`` ``layers.rs:1547``; here with the latent itself in the cache) and the MoE families Mixtral / Qwen3-MoE / DeepSeek-MoE (shared expert, sigmoid+bias
 routing).  Layer semantics follow the reference's per-token layer loop
 (``oxidize-core/src/model/inference/layers.rs``: attention :893+, MoE + shared expert
 :1420-1475) and MoE math ``moe_ffn_forward_weights`` (``model/inference.rs:1662-1935``); the
@@ -114,6 +115,24 @@ class Transformer:
                 pairing=cfg.rope_pairing, mscale=1.0,
                 n_heads=self.n_heads_local, n_kv_heads=self.n_kv_local, head_dim=cfg.head_dim)
         self.attn_scale = cfg.attn_scale if cfg.attn_scale > 0 else cfg.head_dim ** -0.5
+        self.kv_head_dim = cfg.head_dim  # width of one cached key / value row
+        if cfg.is_mla:
+            # One cached row per token, shared by all heads: the normalised latent followed by the rotary key.
+            self.n_kv_local = 1
+            self.kv_head_dim = cfg.kv_lora_rank + cfg.rotary_dim
+            self.rope.n_kv_heads = 1
+            if cfg.rope_scaling.type == "yarn" and cfg.rope_scaling.factor > 1:
+                # DeepSeek's YaRN: the magnitude correction goes into the softmax scale (squared: it would have
+                # multiplied queries and keys), not into the rotary table
+                import math
+
+                m = 1.0 + cfg.yarn_log_multiplier * math.log(cfg.rope_scaling.factor)
+                self.rope.mscale = 1.0
+                self.attn_scale *= m * m
+            if dev.type == "cuda":
+                raise NotImplementedError("latent attention (DeepSeek-V2/V3) is implemented on the CPU path only: the "
+                                          "attention kernel has 64- and 128-wide heads, the latent cache row is "
+                                          f"{self.kv_head_dim} wide")
         if dev.type == "cuda" and cfg.attn_softcap > 0:
             raise NotImplementedError("soft-capped attention scores (Gemma-2) are implemented on the CPU path only")
         self._fuse_qkv_rope = dev.type == "cuda" and fuse_qkv_rope
@@ -215,8 +234,38 @@ class Transformer:
         """Rotary state of a layer: windowed layers use their own base when the model has one."""
         return self.rope_swa if (window > 0 and self.rope_swa is not None) else self.rope
 
+    def _mla_attention(self, lw: LayerWeights, layer: int, x: torch.Tensor, meta: BatchMeta, kv) -> torch.Tensor:
+        """Latent attention in its "absorbed" form.  Per token the cache holds ONE row shared by all heads:
+        [norm(latent) (kv_lora), rope(k_pe) (rope)].  A head's key would be [W_uk latent, k_pe] and its value W_uv latent;
+        instead of rebuilding them for every cached token, the query's position-free part is multiplied by W_uk once
+        (q_nope . (W_uk c) = (W_uk^T q_nope) . c), attention runs as multi-query attention over the latent rows, and the
+        attended latent is multiplied by W_uv afterwards.  Same function, kv_lora + rope cached values per token instead of
+        heads * (nope + rope + v)."""
+        cfg, m = self.cfg, lw.mla
+        T, H = x.shape[0], self.n_heads_local
+        nope, rot, c = cfg.qk_nope_dim, cfg.rotary_dim, cfg.kv_lora_rank
+        if m.q_a is not None:
+            q = ops.linear(ops.rmsnorm(ops.linear(x, m.q_a), m.q_a_norm, cfg.rms_eps), m.q_b)
+        else:
+            q = ops.linear(x, m.q)
+        q = q.reshape(T, H, nope + rot)
+        ckv = ops.linear(x, m.kv_a)
+        latent = ops.rmsnorm(ckv[:, :c].contiguous(), m.kv_a_norm, cfg.rms_eps)
+        rope = self.rope
+        k_pe = opref.apply_rope(ckv[:, c:].reshape(T, 1, rot), meta.positions, rope.inv_freq, rope.pairing, rope.mscale)
+        q_pe = opref.apply_rope(q[:, :, nope:], meta.positions, rope.inv_freq, rope.pairing, rope.mscale)
+        q_lat = torch.einsum("thn,hnc->thc", q[:, :, :nope].float(), m.w_uk.float()).to(x.dtype)
+        row = torch.cat([latent[:, None, :], k_pe], dim=-1)  # [T, 1, c + rot]
+        opref.kv_write(kv, layer, row, row, meta.slot_mapping)
+        o = ops.paged_attention(torch.cat([q_lat, q_pe], dim=-1), kv, layer, meta, self.attn_scale,
+                                cfg.layer_sliding_window(self.w.first_layer + layer))
+        out = torch.einsum("thc,hvc->thv", o[:, :, :c].float(), m.w_uv.float()).to(x.dtype)
+        return self.comm.linear_allreduce(out.reshape(T, -1), lw.wo)
+
     def _attention(self, lw: LayerWeights, layer: int, x: torch.Tensor, meta: BatchMeta, kv) -> torch.Tensor:
         cfg = self.cfg
+        if lw.mla is not None:
+            return self._mla_attention(lw, layer, x, meta, kv)
         window = cfg.layer_sliding_window(self.w.first_layer + layer)
         rope = self._layer_rope(window)
         if self._fuse_qkv_rope and x.is_cuda and lw.wqkv.bias is None:

@@ -163,13 +163,30 @@ class ExpertWeights:
 
 
 @dataclass
+class MLAWeights:
+    """Latent-attention projections of one layer (this rank's heads).  The up-projection of the shared latent is kept
+    per head and dense, split into its key part ``w_uk`` and value part ``w_uv``: the forward pass multiplies the queries
+    by ``w_uk`` and the attention output by ``w_uv`` instead of rebuilding per-head keys and values."""
+
+    kv_a: QTensor  # [kv_lora + rope, hidden]: latent and the shared rotary key
+    kv_a_norm: torch.Tensor
+    w_uk: torch.Tensor  # [heads, nope, kv_lora]
+    w_uv: torch.Tensor  # [heads, v, kv_lora]
+    q: Optional[LinearWeight] = None  # full query projection, or
+    q_a: Optional[QTensor] = None  # down-projection,
+    q_a_norm: Optional[torch.Tensor] = None
+    q_b: Optional[LinearWeight] = None  # up-projection [heads * (nope + rope), q_lora]
+
+
+@dataclass
 class LayerWeights:
     attn_norm: torch.Tensor
-    wqkv: LinearWeight
+    wqkv: Optional[LinearWeight]  # None in a latent-attention layer (``mla`` holds its projections)
     wo: LinearWeight
     ffn_norm: torch.Tensor
     q_norm: Optional[torch.Tensor] = None
     k_norm: Optional[torch.Tensor] = None
+    mla: Optional[MLAWeights] = None
     # Gemma-2/3: norms applied to the attention / FFN branch outputs before the residual add
     post_attn_norm: Optional[torch.Tensor] = None
     post_ffn_norm: Optional[torch.Tensor] = None
@@ -312,6 +329,31 @@ class GGUFWeightSource:
         return QTensor(t.name, _np_to_torch(raw, self.device), new_shape)
 
 
+def _load_mla(src: GGUFWeightSource, cfg: ModelConfig, p: str, h0: int, h1: int) -> MLAWeights:
+    """Latent-attention tensors of heads [h0, h1): ``attn_kv_b`` (rows = per head nope key rows, then value rows) or its
+    split form ``attn_k_b`` ([head, kv_lora, nope], i.e. stored transposed) + ``attn_v_b`` ([head, v, kv_lora])."""
+    from ..ops import ref as opref
+
+    nope, vd, c, qk = cfg.qk_nope_dim, cfg.v_head_dim, cfg.kv_lora_rank, cfg.head_dim
+    dt = src.act_dtype
+    if src.has(f"{p}.attn_kv_b.weight"):
+        kvb = opref.dequantize_weight(src.matrix(f"{p}.attn_kv_b.weight", rows=(h0 * (nope + vd), h1 * (nope + vd))))
+        kvb = kvb.reshape(h1 - h0, nope + vd, c)
+        w_uk, w_uv = kvb[:, :nope, :], kvb[:, nope:, :]
+    else:
+        w_uk = torch.stack([opref.dequantize_weight(src.matrix(f"{p}.attn_k_b.weight", expert=h)).t() for h in range(h0, h1)])
+        w_uv = torch.stack([opref.dequantize_weight(src.matrix(f"{p}.attn_v_b.weight", expert=h)) for h in range(h0, h1)])
+    m = MLAWeights(kv_a=src.matrix(f"{p}.attn_kv_a_mqa.weight"), kv_a_norm=src.vector(f"{p}.attn_kv_a_norm.weight"),
+                   w_uk=w_uk.to(dt).contiguous(), w_uv=w_uv.to(dt).contiguous())
+    if src.has(f"{p}.attn_q_a.weight"):
+        m.q_a = src.matrix(f"{p}.attn_q_a.weight")
+        m.q_a_norm = src.vector(f"{p}.attn_q_a_norm.weight")
+        m.q_b = LinearWeight([src.matrix(f"{p}.attn_q_b.weight", rows=(h0 * qk, h1 * qk))])
+    else:
+        m.q = LinearWeight([src.matrix(f"{p}.attn_q.weight", rows=(h0 * qk, h1 * qk))])
+    return m
+
+
 def _load_layer(src: GGUFWeightSource, cfg: ModelConfig, i: int, tp_rank: int, tp_size: int,
                 ep_rank: int, ep_size: int, prefix: Optional[str] = None) -> LayerWeights:
     p = prefix or f"blk.{i}"
@@ -322,7 +364,11 @@ def _load_layer(src: GGUFWeightSource, cfg: ModelConfig, i: int, tp_rank: int, t
     q0, q1 = shard_range(cfg.n_heads, tp_rank, tp_size)
     k0, k1 = shard_range(cfg.n_kv_heads, tp_rank // kv_rep, kv_shards)
     qr, kr = (q0 * hd, q1 * hd), (k0 * hd, k1 * hd)
-    if src.has(f"{p}.attn_qkv.weight"):
+    mla = None
+    if src.has(f"{p}.attn_kv_a_mqa.weight"):
+        mla = _load_mla(src, cfg, p, q0, q1)
+        parts = []
+    elif src.has(f"{p}.attn_qkv.weight"):
         # one fused tensor (Phi-3): rows are all query heads, then all key heads, then all value heads
         ko, vo = cfg.n_heads * hd, (cfg.n_heads + cfg.n_kv_heads) * hd
         parts = [src.matrix(f"{p}.attn_qkv.weight", rows=qr), src.matrix(f"{p}.attn_qkv.weight", rows=(ko + kr[0], ko + kr[1])),
@@ -338,11 +384,13 @@ def _load_layer(src: GGUFWeightSource, cfg: ModelConfig, i: int, tp_rank: int, t
     elif src.has(f"{p}.attn_q.bias"):
         bias = torch.cat([src.vector(f"{p}.attn_q.bias")[qr[0]:qr[1]], src.vector(f"{p}.attn_k.bias")[kr[0]:kr[1]],
                           src.vector(f"{p}.attn_v.bias")[kr[0]:kr[1]]])
+    vd = cfg.v_head_dim if mla is not None else hd
     lw = LayerWeights(
         attn_norm=src.vector(f"{p}.attn_norm.weight"),
-        wqkv=LinearWeight(fuse_rows(parts), bias),
-        wo=LinearWeight([src.matrix(f"{p}.attn_output.weight", cols=qr)]),
+        wqkv=LinearWeight(fuse_rows(parts), bias) if mla is None else None,
+        wo=LinearWeight([src.matrix(f"{p}.attn_output.weight", cols=(q0 * vd, q1 * vd))]),
         ffn_norm=src.vector(f"{p}.ffn_norm.weight"),
+        mla=mla,
     )
     if src.has(f"{p}.attn_q_norm.weight"):
         lw.q_norm = src.vector(f"{p}.attn_q_norm.weight")

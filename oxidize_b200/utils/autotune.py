@@ -96,7 +96,9 @@ def fingerprint(g: GGUFFile, cfg: Optional[ModelConfig] = None) -> ModelFingerpr
         by_type[info.type.name] = by_type.get(info.type.name, 0) + info.nbytes
         total += info.nbytes
     dom = max(by_type, key=by_type.get) if by_type else "F32"
-    return ModelFingerprint(cfg.arch, cfg.n_layers, cfg.hidden_size, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim,
+    # what one token's cache row holds: KV heads x head_dim, or with latent attention one shared (latent + rotary key) row
+    kv_heads, kv_dim = (1, cfg.kv_lora_rank + cfg.rotary_dim) if cfg.is_mla else (cfg.n_kv_heads, cfg.head_dim)
+    return ModelFingerprint(cfg.arch, cfg.n_layers, cfg.hidden_size, cfg.n_heads, kv_heads, kv_dim,
                             cfg.is_moe, cfg.n_experts, total, cfg.context_length, cfg.nextn_layers > 0, dom)
 
 

@@ -95,7 +95,13 @@ def write_config_metadata(w: GGUFWriter, cfg: ModelConfig) -> None:
     w.add(f"{a}.attention.head_count", cfg.n_heads, U)
     w.add(f"{a}.attention.head_count_kv", cfg.n_kv_heads, U)
     w.add(f"{a}.attention.key_length", cfg.head_dim, U)
-    w.add(f"{a}.attention.value_length", cfg.head_dim, U)
+    w.add(f"{a}.attention.value_length", cfg.v_head_dim if cfg.is_mla else cfg.head_dim, U)
+    if cfg.is_mla:
+        w.add(f"{a}.attention.kv_lora_rank", cfg.kv_lora_rank, U)
+        if cfg.q_lora_rank:
+            w.add(f"{a}.attention.q_lora_rank", cfg.q_lora_rank, U)
+        if cfg.yarn_log_multiplier:
+            w.add(f"{a}.rope.scaling.yarn_log_multiplier", float(cfg.yarn_log_multiplier), GGUFValueType.FLOAT32)
     w.add(f"{a}.attention.layer_norm_rms_epsilon", float(cfg.rms_eps), GGUFValueType.FLOAT32)
     w.add(f"{a}.rope.freq_base", float(cfg.rope_theta), GGUFValueType.FLOAT32)
     w.add(f"{a}.rope.dimension_count", cfg.rotary_dim, U)
@@ -196,15 +202,26 @@ def synth_gguf(path: str, cfg: ModelConfig, quant: str = "Q4_K_M", seed: int = 0
     for i in range(L + cfg.nextn_layers):
         p = f"blk.{i}"
         vec(f"{p}.attn_norm.weight", h)
-        gq = mat(f"{p}.attn_q.weight", "attn_q", i, cfg.q_size, h, add=not fused_layout)
-        gk = mat(f"{p}.attn_k.weight", "attn_k", i, cfg.kv_size, h, add=not fused_layout)
-        gv = mat(f"{p}.attn_v.weight", "attn_v", i, cfg.kv_size, h, add=not fused_layout)
-        if fused_layout:
-            fused(f"{p}.attn_qkv.weight", [(*gq, cfg.q_size), (*gk, cfg.kv_size), (*gv, cfg.kv_size)], h)
+        if cfg.is_mla:  # latent attention: low-rank (or full) queries, shared latent + rotary key, per-head up-projection
+            if cfg.q_lora_rank:
+                mat(f"{p}.attn_q_a.weight", "attn_q", i, cfg.q_lora_rank, h)
+                vec(f"{p}.attn_q_a_norm.weight", cfg.q_lora_rank)
+                mat(f"{p}.attn_q_b.weight", "attn_q", i, cfg.q_size, cfg.q_lora_rank)
+            else:
+                mat(f"{p}.attn_q.weight", "attn_q", i, cfg.q_size, h)
+            mat(f"{p}.attn_kv_a_mqa.weight", "attn_k", i, cfg.kv_lora_rank + cfg.rotary_dim, h)
+            vec(f"{p}.attn_kv_a_norm.weight", cfg.kv_lora_rank)
+            mat(f"{p}.attn_kv_b.weight", "attn_v", i, cfg.n_heads * (cfg.qk_nope_dim + cfg.v_head_dim), cfg.kv_lora_rank)
+        else:
+            gq = mat(f"{p}.attn_q.weight", "attn_q", i, cfg.q_size, h, add=not fused_layout)
+            gk = mat(f"{p}.attn_k.weight", "attn_k", i, cfg.kv_size, h, add=not fused_layout)
+            gv = mat(f"{p}.attn_v.weight", "attn_v", i, cfg.kv_size, h, add=not fused_layout)
+            if fused_layout:
+                fused(f"{p}.attn_qkv.weight", [(*gq, cfg.q_size), (*gk, cfg.kv_size), (*gv, cfg.kv_size)], h)
         if cfg.attn_bias:  # Qwen2-style q/k/v projection biases
             for nm, nb in (("attn_q", cfg.q_size), ("attn_k", cfg.kv_size), ("attn_v", cfg.kv_size)):
                 w.add_tensor(f"{p}.{nm}.bias", (rng.standard_normal(nb) * 0.1).astype(np.float32), (nb,), "F32")
-        mat(f"{p}.attn_output.weight", "attn_output", i, h, cfg.q_size)
+        mat(f"{p}.attn_output.weight", "attn_output", i, h, cfg.n_heads * cfg.v_head_dim if cfg.is_mla else cfg.q_size)
         if cfg.qk_norm:
             vec(f"{p}.attn_q_norm.weight", hd)
             vec(f"{p}.attn_k_norm.weight", hd)

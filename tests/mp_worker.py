@@ -131,6 +131,45 @@ def case_tp_model(dev, comm_kind):
             assert comm.fused_calls > 0
 
 
+def case_tp_families(dev, comm_kind):
+    """Tensor-parallel shards of a Gemma-3 model (branch-output norms, two rotary bases) and of a latent-attention
+    DeepSeek model (heads of the per-head up-projection split over the ranks, latent cache replicated) give the
+    single-rank logits."""
+    layout = init_distributed()
+    small = dict(n_layers=3, vocab_size=512, hidden_size=64, context_length=4096)
+    cfgs = {
+        "gemma3": preset("gemma3-27b", **small, n_heads=4, n_kv_heads=2, head_dim=16, ffn_size=128, sliding_window=16,
+                         embedding_scale=8.0, attn_scale=0.2, sliding_window_pattern=2),
+        "mla": preset("deepseek-v3", **small, n_heads=4, n_kv_heads=4, head_dim=24, rope_dim=8, qk_nope_dim=16, v_head_dim=24,
+                      kv_lora_rank=32, q_lora_rank=48, ffn_size=96, n_experts=8, n_experts_used=2, expert_ffn_size=48,
+                      expert_group_count=4, expert_group_used_count=2, leading_dense_blocks=1, shared_expert_ffn_size=48),
+    }
+    ec = dict(max_model_len=128, max_num_seqs=4, num_kv_blocks=64, prefill_chunk_size=32, max_num_batched_tokens=64,
+              cuda_graphs=False, kv_cache_dtype="f32")
+    for name, cfg0 in cfgs.items():
+        path = os.path.join(tempfile.gettempdir(), f"oxb_tp_{name}_{os.environ.get('MASTER_PORT', '0')}.gguf")
+        if layout.rank == 0:
+            synth_gguf(path, cfg0, "F32", seed=3, norm_jitter=0.2)
+        dist.barrier()
+        g = load_gguf(path)
+        cfg = config_from_gguf(g)
+        w_tp = load_weights(g, cfg, dev, torch.float32, layout.rank, layout.world_size, ep_rank=0, ep_size=1)
+        w_1 = load_weights(g, cfg, dev, torch.float32, 0, 1)
+        tp = LLM(w_tp, EngineConfig(tp_size=layout.world_size, **ec), TorchComm())
+        one = LLM(w_1, EngineConfig(**ec))
+        tp.runner.keep_logits = one.runner.keep_logits = True
+        sp = SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True)
+        for p in ([5, 9, 200, 31, 7], list(range(3, 50))):
+            tp.add_request(p, sp)
+            one.add_request(p, sp)
+        while tp.has_unfinished:
+            tp.step()
+            one.step()
+            a, b = tp.last_step[1].logits, one.last_step[1].logits
+            assert a.shape == b.shape and rel_err(a, b) < 1e-4, (name, rel_err(a, b))
+        dist.barrier()
+
+
 def case_ep1_model(dev, comm_kind):
     """Tensor parallelism with every expert replicated on every rank (ep_size = 1) == single rank."""
     return case_ep_model(dev, comm_kind, replicate_experts=True)
@@ -320,7 +359,7 @@ def case_rank_exit(dev, comm_kind):
     hb.stop()
 
 
-CASES = {"gemm_ar": case_gemm_ar, "tp_model": case_tp_model, "tp_graph": case_tp_graph, "rank_exit": case_rank_exit, "ep_model": case_ep_model, "ep1_model": case_ep1_model, "pp_model": case_pp_model, "pp_engine": case_pp_engine}
+CASES = {"gemm_ar": case_gemm_ar, "tp_model": case_tp_model, "tp_families": case_tp_families, "tp_graph": case_tp_graph, "rank_exit": case_rank_exit, "ep_model": case_ep_model, "ep1_model": case_ep1_model, "pp_model": case_pp_model, "pp_engine": case_pp_engine}
 
 
 def main():

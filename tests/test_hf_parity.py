@@ -6,7 +6,9 @@ The logits after the prompt and the greedy continuation must agree with the orac
 tensor-name map and metadata, the loader, and every family-specific piece of layer math: q/k/v biases (Qwen2), per-head
 QK-norm (Qwen3), fused qkv / gate-up tensors (Phi-3), softmax top-k routing (Mixtral, Qwen3-MoE), and for Gemma 1-3 the
 scaled embeddings, GeGLU, norms on the branch outputs, (w + 1) norm weights, soft-capped scores and logits, the softmax
-scale taken from query_pre_attn_scalar, and local / global layers with a window and two rotary bases.
+scale taken from query_pre_attn_scalar, and local / global layers with a window and two rotary bases; for DeepSeek-V2/V3
+the latent attention (low-rank and full-rank queries, shared rotary key, interleaved rotary pairs, YaRN), softmax and
+sigmoid group-limited routing with a selection bias, the shared expert and the leading dense layer.
 """
 import os
 
@@ -50,10 +52,25 @@ def _build(name: str):
         # 7 layers: five windowed (rotary base 1e4), the sixth global (base 1e6), the seventh windowed again
         c["num_hidden_layers"] = 7
         return T.Gemma3ForCausalLM(T.Gemma3TextConfig(**c, head_dim=32, sliding_window=8, query_pre_attn_scalar=40))
+    # DeepSeek: latent attention (32-wide latent, 16 position-free + 8 rotary query / key values per head, 24-wide values),
+    # one dense layer then routed experts + a shared expert
+    ds = dict(c, moe_intermediate_size=48, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2, first_k_dense_replace=1,
+              kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=24, num_key_value_heads=4)
+    if name == "deepseek_v2":  # softmax scores, plain top-k, weights not renormalised, scaled by 1.5
+        return T.DeepseekV2ForCausalLM(T.DeepseekV2Config(**ds, q_lora_rank=48, n_group=1, topk_group=1, routed_scaling_factor=1.5,
+                                                          topk_method="greedy"))
+    if name == "deepseek_v3":  # sigmoid scores, 2 of 4 expert groups, low-rank queries
+        return T.DeepseekV3ForCausalLM(T.DeepseekV3Config(**ds, q_lora_rank=48, n_group=4, topk_group=2, routed_scaling_factor=2.5,
+                                                          norm_topk_prob=True))
+    if name == "deepseek_v3_yarn":  # full-rank queries, YaRN-scaled rotary part (its magnitude term goes into the softmax scale)
+        yarn = {"rope_type": "yarn", "factor": 8.0, "original_max_position_embeddings": 32, "mscale": 1.0, "mscale_all_dim": 1.0,
+                "beta_fast": 32.0, "beta_slow": 1.0, "rope_theta": 10000.0}
+        return T.DeepseekV3ForCausalLM(T.DeepseekV3Config(**ds, q_lora_rank=None, n_group=2, topk_group=1, rope_parameters=yarn))
     raise KeyError(name)
 
 
-FAMILIES = ["llama", "qwen2", "qwen3", "phi3", "mixtral", "qwen3moe", "gemma", "gemma2", "gemma3"]
+FAMILIES = ["llama", "qwen2", "qwen3", "phi3", "mixtral", "qwen3moe", "gemma", "gemma2", "gemma3", "deepseek_v2", "deepseek_v3",
+            "deepseek_v3_yarn"]
 
 
 @pytest.mark.parametrize("family", FAMILIES)
@@ -61,7 +78,7 @@ def test_logits_and_greedy_tokens_match_transformers(family, tmp_path):
     try:
         torch.manual_seed(0)
         ref = _build(family).eval().float()
-    except (AttributeError, TypeError) as e:  # a transformers build without this family
+    except (AttributeError, TypeError, KeyError) as e:  # a transformers build without this family
         pytest.skip(f"transformers cannot build {family}: {e}")
     with torch.no_grad():
         for pname, p in ref.named_parameters():
@@ -76,6 +93,10 @@ def test_logits_and_greedy_tokens_match_transformers(family, tmp_path):
     if family == "gemma2":
         assert cfg.attn_softcap == 50.0 and cfg.final_softcap == 30.0 and cfg.sliding_window_pattern == 2 and cfg.post_norms
         assert abs(cfg.attn_scale - 24 ** -0.5) < 1e-6
+    if family.startswith("deepseek"):
+        assert cfg.is_mla and (cfg.kv_lora_rank, cfg.qk_nope_dim, cfg.rope_dim, cfg.v_head_dim, cfg.head_dim) == (32, 16, 8, 24, 24)
+        assert cfg.rope_pairing == "adjacent" and cfg.n_shared_experts == 1 and cfg.leading_dense_blocks == 1
+        assert cfg.expert_gating == ("softmax" if family == "deepseek_v2" else "sigmoid")
     if family == "gemma3":
         assert cfg.sliding_window_pattern == 6 and cfg.rope_theta_swa == 10000.0 and cfg.rope_theta == 1000000.0
         assert cfg.qk_norm and cfg.post_norms and cfg.ffn_act == "gelu_tanh" and cfg.embedding_scale == 8.0

@@ -54,6 +54,11 @@ def test_tp4_logits_match_tp1_on_cpu():
     assert r.stdout.count("OK tp_model") == 4
 
 
+def test_tp2_gemma3_and_latent_attention_match_single_rank_on_cpu():
+    r = run_ranks("tp_families", 2)
+    assert r.returncode == 0, fail_text(r)
+
+
 def test_ep2_moe_logits_match_single_rank_on_cpu():
     r = run_ranks("ep_model")
     assert r.returncode == 0, fail_text(r)
