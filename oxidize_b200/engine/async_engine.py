@@ -80,6 +80,20 @@ class AsyncEngine:
     def cancel(self, request_id: str) -> None:
         self._inbox.put(("cancel", request_id))
 
+    def call(self, fn: Callable[[LLM], Any], timeout: Optional[float] = None) -> Any:
+        """Run ``fn(llm)`` on the engine thread between two steps (the engine, its pools and its CUDA stream belong to
+        that thread) and return its result; an exception raised by ``fn`` is raised here."""
+        import concurrent.futures
+
+        fut: "concurrent.futures.Future" = concurrent.futures.Future()
+        self._inbox.put(("call", fn, fut))
+        return fut.result(timeout)
+
+    def embed(self, prompts, pooling: str = "mean"):
+        if self.control is not None:
+            raise NotImplementedError("embeddings are served by single-rank engines")
+        return self.call(lambda llm: llm.embed(prompts, pooling))
+
     @property
     def healthy(self) -> bool:
         return self.watchdog.healthy and self._thread.is_alive()
@@ -155,6 +169,13 @@ class AsyncEngine:
                     self._forget(rid)
                     if self.control is not None:
                         self._step_aborts.append(rid)
+            elif isinstance(item, tuple) and item[0] == "call":
+                _, fn, fut = item
+                if fut.set_running_or_notify_cancel():
+                    try:
+                        fut.set_result(fn(self.llm))
+                    except BaseException as e:  # noqa: BLE001 - handed to the caller
+                        fut.set_exception(e)
             try:
                 item = self._inbox.get_nowait()
             except queue.Empty:
@@ -278,6 +299,13 @@ class ReplicaRouter:
             sink(ev)
 
         return self.engines[i].submit(prompt, params, routed, rid)
+
+    def embed(self, prompts, pooling: str = "mean"):
+        with self._lock:
+            live = [e for e in self.engines if e.healthy] or self.engines
+            self._rr += 1
+            eng = live[self._rr % len(live)]
+        return eng.embed(prompts, pooling)
 
     def cancel(self, request_id: str) -> None:
         with self._lock:

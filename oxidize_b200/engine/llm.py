@@ -139,7 +139,11 @@ class LLM:
             tok = load_tokenizer_from_metadata(g.metadata)
         except TokenizerError:
             tok = None
-        return cls(w, config, comm, tok, pipe)
+        llm = cls(w, config, comm, tok, pipe)
+        from ..formats.tokenizer import chat_template_from_metadata
+
+        llm.chat_template = chat_template_from_metadata(g.metadata)  # None when the file carries none
+        return llm
 
     def _auto_blocks(self, spec: KVCacheSpec) -> int:
         c = self.config
@@ -379,6 +383,44 @@ class LLM:
         finally:
             self.runner.keep_logits = keep
         return np.stack([got[i] for i in ids])
+
+    def embed(self, prompts: Iterable[Union[str, Seq[int]]], pooling: str = "mean", normalize: bool = True) -> "np.ndarray":
+        """Text embeddings [n, hidden] float32: the final-norm hidden states of each prompt, pooled over its tokens
+        (``mean``) or taken at its last token (``last``), L2-normalised.  Runs outside the scheduler on a cache of its own
+        that lives for the call, so it neither takes blocks from nor waits for running requests; single-rank engines only
+        (the other ranks of a tensor- or pipeline-parallel group would have to run the same forward)."""
+        import numpy as np
+
+        from ..models.transformer import BatchMeta
+
+        if self.model.w.tp_size > 1 or self.pipe is not None:
+            raise NotImplementedError("embeddings are served by single-rank engines")
+        if pooling not in ("mean", "last"):
+            raise ValueError("pooling must be 'mean' or 'last'")
+        dev, m = self.device, self.model
+        i32 = dict(dtype=torch.int32, device=dev)
+        page = self.config.kv_page_size
+        out = []
+        for p in prompts:
+            ids = self.tokenizer.encode(p) if isinstance(p, str) else list(p)
+            if not ids:
+                raise ValueError("cannot embed an empty prompt")
+            ids = ids[: self.config.max_model_len]
+            n = len(ids)
+            nblk = (n + page - 1) // page
+            kv = KVCache(KVCacheSpec(len(m.w.layers), m.n_kv_local, m.kv_head_dim, page, self.kv.spec.dtype_name), nblk, dev)
+            pos = torch.arange(n, **i32)
+            meta = BatchMeta(torch.tensor(ids, **i32), pos, pos.clone(), torch.tensor([0, n], **i32), torch.tensor([n], **i32),
+                             torch.arange(nblk, **i32)[None, :], torch.arange(n, **i32), n, n, 1, logits_all=True)
+            h, residual = m.run_layers(m.embed(meta.token_ids), None, meta, kv)
+            from .. import ops
+
+            x = ops.add_rmsnorm(h, residual, m.w.out_norm, m.cfg.rms_eps)[0].float()
+            v = x.mean(dim=0) if pooling == "mean" else x[-1]
+            if normalize:
+                v = v / v.norm().clamp_min(1e-12)
+            out.append(v.cpu().numpy())
+        return np.stack(out)
 
     def beam_search(self, prompt: Union[str, Seq[int]], beam_width: int = 4, max_tokens: int = 32,
                     length_penalty: float = 1.0):

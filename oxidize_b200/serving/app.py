@@ -6,7 +6,7 @@ Route set, request fields and response shapes follow the reference server
 (``oxidize-server/src/app.rs:47-63``, ``schema.rs:7-131``, ``routes/responses.rs:19-59,134-198``):
 ``n`` / ``best_of`` > 1 are rejected, ``stop`` may be a string or a list, the final SSE chunk
 carries ``finish_reason`` and is followed by ``data: [DONE]``, ``/readyz`` answers 503 until a
-model is loaded, ``/v1/embeddings`` returns an empty vector, and without a model the completion
+model is loaded, ``/v1/embeddings`` returns an empty vector without a model (pooled hidden states with one), and without a model the completion
 routes answer with placeholder text (``AGENTS.md:220``).  Middleware order is limits → API key →
 metrics → logging, as at ``app.rs:64-76``.
 """
@@ -223,10 +223,23 @@ def create_app(state: Optional[ServerState] = None) -> FastAPI:
 
     @app.post("/v1/embeddings")
     async def embeddings(req: EmbeddingsRequest):
-        inputs = [req.input] if isinstance(req.input, str) else req.input
+        inputs = [req.input] if isinstance(req.input, str) else list(req.input)
+        if state.engine is None:
+            vecs, n_tok = [[] for _ in inputs], 0
+        else:
+            if not inputs or any(not isinstance(t, str) or not t for t in inputs):
+                return _error(400, "input must be a non-empty string or a list of non-empty strings")
+            tok = state.engine.llm.tokenizer
+            n_tok = sum(len(tok.encode(t)) for t in inputs) if tok is not None else 0
+            try:
+                # mean-pooled, L2-normalised final hidden states, computed on the engine thread between two steps
+                arr = await asyncio.get_running_loop().run_in_executor(None, state.engine.embed, inputs)
+            except NotImplementedError as e:
+                return _error(501, str(e))
+            vecs = [v.tolist() for v in arr]
         return {"object": "list", "model": req.model,
-                "data": [{"object": "embedding", "index": i, "embedding": []} for i, _ in enumerate(inputs)],
-                "usage": {"prompt_tokens": 0, "total_tokens": 0}}
+                "data": [{"object": "embedding", "index": i, "embedding": v} for i, v in enumerate(vecs)],
+                "usage": {"prompt_tokens": n_tok, "total_tokens": n_tok}}
 
     # ------------------------------------------------------------------ completions
     def _validate(req: _Common) -> Optional[JSONResponse]:

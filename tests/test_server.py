@@ -3,6 +3,7 @@
 import io
 import json
 
+import numpy as np
 import pytest
 from starlette.testclient import TestClient
 
@@ -96,6 +97,21 @@ def test_completion_with_model(engine):
     assert "oxidize_tokens_generated_total" in c.get("/metrics").text
     r = c.post("/v1/completions", json={"model": "tiny", "prompt": "x", "top_p": 2.0})
     assert r.status_code == 400
+
+
+def test_embeddings_with_model(engine):
+    """/v1/embeddings returns pooled, L2-normalised hidden states of the loaded model, computed on the engine thread."""
+    c = TestClient(create_app(ServerState(engine, "tiny", GenerationDefaults(), api_keys=[])))
+    r = c.post("/v1/embeddings", json={"model": "tiny", "input": ["hello world", "something else entirely", "hello world"]})
+    assert r.status_code == 200
+    body = r.json()
+    vecs = [np.asarray(d["embedding"], dtype=np.float64) for d in body["data"]]
+    assert [d["index"] for d in body["data"]] == [0, 1, 2] and body["usage"]["prompt_tokens"] > 0
+    assert all(v.shape == (512,) and abs(np.linalg.norm(v) - 1.0) < 1e-4 for v in vecs)
+    assert np.allclose(vecs[0], vecs[2]) and not np.allclose(vecs[0], vecs[1], atol=1e-3)
+    assert c.post("/v1/embeddings", json={"model": "tiny", "input": ""}).status_code == 400
+    # a generation request still works afterwards (the call ran between engine steps, on a cache of its own)
+    assert c.post("/v1/completions", json={"model": "tiny", "prompt": "hello", "max_tokens": 3}).status_code == 200
 
 
 def test_chat_stream_with_model(engine):
