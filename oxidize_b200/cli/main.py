@@ -440,8 +440,29 @@ def cmd_gpu_cluster(args) -> int:
     return 0
 
 
+# offline checkpoint tools: each has its own flag set (the reference ships them as separate binaries,
+# oxidize-quantize / oxidize-prune / oxidize-merge / oxidize-convert / oxidize-finetuning)
+TOOL_VERBS = {"quantize": "oxidize_b200.offline.requantize", "prune": "oxidize_b200.offline.prune",
+              "merge": "oxidize_b200.offline.merge", "lora-merge": "oxidize_b200.offline.lora",
+              "finetune": "oxidize_b200.offline.finetune"}
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0] in TOOL_VERBS:
+        import importlib
+
+        return importlib.import_module(TOOL_VERBS[argv[0]]).main(argv[1:])
+    if argv and argv[0] == "convert":
+        from ..formats.convert import convert_safetensors_to_gguf
+
+        ap = argparse.ArgumentParser(prog="oxidize convert", description="HF SafeTensors directory -> GGUF")
+        ap.add_argument("src")
+        ap.add_argument("out")
+        ap.add_argument("--quant", default="F16")
+        a = ap.parse_args(argv[1:])
+        print(convert_safetensors_to_gguf(a.src, a.out, a.quant))
+        return 0
     argv = rewrite_args(argv)
     passed = user_passed(argv)
     args = build_parser().parse_args(argv)
