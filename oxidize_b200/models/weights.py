@@ -276,7 +276,7 @@ class GGUFWeightSource:
 
     def __init__(self, g: GGUFFile, device, act_dtype: torch.dtype):
         self.g = g
-        self.device = device
+        self.device = torch.device(device)
         self.act_dtype = act_dtype
 
     def has(self, name: str) -> bool:
