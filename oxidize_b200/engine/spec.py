@@ -394,6 +394,14 @@ class SpecDecoder:
                 n = len(tokens.get(ss.seq.seq_id, []))
                 if n and r0 + n - 1 < hid.shape[0]:
                     observe(ss.seq, hid[r0 + n - 1].detach().clone())
+        observe_f = getattr(self.proposer, "observe_features", None)
+        feats = getattr(llm.model, "last_features", None)
+        if observe_f is not None and feats is not None:
+            # the capture layers' hidden states at the same position: the context of a hidden-conditioned draft
+            for ss, r0, k in getattr(llm.runner, "last_rows", []):
+                n = len(tokens.get(ss.seq.seq_id, []))
+                if n and r0 + n - 1 < feats.shape[0]:
+                    observe_f(ss.seq, feats[r0 + n - 1].detach().clone())
         return tokens
 
     def on_finished(self, seq: Sequence) -> None:
@@ -409,6 +417,16 @@ def attach_speculation(llm, draft_model_path: Optional[str], k: int = 4, use_mtp
         from ..models.weights import load_weights
 
         g = load_gguf(draft_model_path)
+        if any(n in g.tensors for n in ("fc.weight", "dflash_fc.weight", "model.fc.weight")):
+            # a hidden-conditioned draft (DFlash-style): it reads the target's hidden states besides the tokens
+            from .feature_draft import FeatureDraftProposer, load_feature_draft
+
+            if llm.config.tp_size > 1 or llm.config.pp_size > 1:
+                raise ValueError("hidden-conditioned drafts run with single-rank engines")
+            act = torch.bfloat16 if llm.device.type == "cuda" else torch.float32
+            fw = load_feature_draft(draft_model_path, llm.device, act, llm.cfg.n_layers)
+            llm.spec = SpecDecoder(FeatureDraftProposer(fw, llm.model, k, c.max_num_seqs, c.max_model_len), k)
+            return llm.spec
         dcfg = config_from_gguf(g)
         if dcfg.vocab_size != llm.cfg.vocab_size:
             raise ValueError(f"draft vocabulary {dcfg.vocab_size} != target vocabulary {llm.cfg.vocab_size}")

@@ -79,6 +79,10 @@ class Transformer:
                  fuse_qkv_rope: bool = True, fuse_swiglu: bool = True, pipe=None, max_context: int = 0):
         self.w = weights
         self.pipe = pipe  # parallel.pp.StageIO when this model holds one pipeline stage's layers
+        # layers whose outputs (hidden states of the logits rows, concatenated) are kept in ``last_features`` after every
+        # forward: the input of a hidden-conditioned draft model
+        self.capture_layers: Optional[List[int]] = None
+        self.last_features: Optional[torch.Tensor] = None
         self._sends: list = []  # activation sends still on the link
         self.cfg: ModelConfig = weights.cfg
         self.comm = comm or SingleRankComm()
@@ -371,6 +375,13 @@ class Transformer:
             return residual, None
         return h, residual
 
+    def _keep_features(self, capture: Optional[dict], idx: Optional[torch.Tensor]) -> None:
+        if not self.capture_layers or capture is None or "hidden" not in capture:
+            return
+        hs = [capture["hidden"][l] for l in self.capture_layers if l in capture["hidden"]]
+        if len(hs) == len(self.capture_layers):
+            self.last_features = torch.cat([h if idx is None else h.index_select(0, idx) for h in hs], dim=-1)
+
     def embed(self, token_ids: torch.Tensor) -> torch.Tensor:
         return ops.embed(token_ids, self.w.embed, self.act_dtype, self.cfg.embedding_scale)
 
@@ -414,13 +425,16 @@ class Transformer:
         exchanged (vocabulary-parallel head, distributed argmax).  ``feed`` (int32, one entry per logits
         row) also receives the tokens: the next decode step's input ids, written where its kernels read them."""
         h, residual = self._stage_input(meta)
-        h, residual = self.run_layers(h, residual, meta, kv)
+        cap = {"layers": set(self.capture_layers)} if self.capture_layers else None
+        h, residual = self.run_layers(h, residual, meta, kv, capture=cap)
         if self._stage_output(h, residual):
             return None  # the tokens arrive from the last stage
+        idx = None
         if not meta.logits_all:
             idx = meta.logits_indices.long()
             h = h.index_select(0, idx)
             residual = residual.index_select(0, idx) if residual is not None else None
+        self._keep_features(cap, idx)
         x, hid = ops.add_rmsnorm(h, residual, self.w.out_norm, self.cfg.rms_eps)
         self.last_hidden = hid  # pre-norm hidden of the logits rows (input of an MTP head)
         logits = ops.linear(x, self.w.lm_head)
@@ -458,9 +472,12 @@ class Transformer:
 
     def forward(self, meta: BatchMeta, kv, return_hidden: bool = False, capture: Optional[dict] = None):
         h, residual = self._stage_input(meta)
+        if capture is None and self.capture_layers:
+            capture = {"layers": set(self.capture_layers)}
         h, residual = self.run_layers(h, residual, meta, kv, capture=capture)
         if self._stage_output(h, residual):
             return None
+        self._keep_features(capture, None if meta.logits_indices is None else meta.logits_indices.long())
         return self.head(h, residual, meta.logits_indices, return_hidden)
 
 
