@@ -358,7 +358,10 @@ class ModelRunner:
         # the scheduler's own counts settle the common case without a scan of the rows
         decode_only = ((out.num_prefill_tokens == 0 and out.num_decode_tokens == len(scheduled))
                        or all((not s.is_prefill) and s.num_tokens == 1 for s in scheduled))
-        graphable = self.use_graphs and decode_only and not needs_host_logits and not self.keep_logits
+        # (a model that records layer outputs for a hidden-conditioned draft runs eagerly: the recorded tensors must be
+        # this step's own, not a captured graph's private buffers)
+        graphable = (self.use_graphs and decode_only and not needs_host_logits and not self.keep_logits
+                     and not getattr(self.model, "capture_layers", None))
         pad_to = _bucket(len(scheduled)) if graphable else None
         if pad_to is not None and pad_to > self.buf.max_seqs:
             pad_to, graphable = None, False
