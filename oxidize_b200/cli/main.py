@@ -194,7 +194,8 @@ def make_engine(args, passed: set, device_index: Optional[int] = None):
                       max_model_len=args.ctx_size or plan.ctx_size, max_num_seqs=args.max_running or plan.max_num_seqs,
                       max_num_batched_tokens=args.max_batched_tokens, prefill_chunk_size=args.prefill_batch_size,
                       cuda_graphs=not args.no_cuda_graphs, tp_size=tp, ep_size=args.ep or tp, pp_size=max(1, args.pp),
-                      fused_comm=args.fused_comm == "on")
+                      fused_comm=args.fused_comm == "on",
+                      resident_layers=max(1, args.layer_cache) if args.layer_wise else 0)
     pp = ec.pp_size
     if ec.ep_size not in (1, tp):
         raise SystemExit(f"error: --ep must be 1 (experts replicated) or equal to --tp ({tp})")

@@ -56,6 +56,9 @@ class EngineConfig:
     fuse_swiglu: bool = True  # SiLU(gate) * up as the gate_up GEMM's epilogue for dense bf16 FFNs
     kernel_options: Optional[object] = None  # ops.cuda.KernelOptions; None = the library's defaults
     eos_token_id: Optional[int] = None
+    # > 0: keep only this many decoder layers loaded, streaming the others from the file mapping as the forward pass
+    # reaches them (for checkpoints larger than the memory left beside the KV cache)
+    resident_layers: int = 0
 
 
 @dataclass
@@ -102,7 +105,8 @@ class LLM:
         self.scheduler = Scheduler(SchedulerConfig(c.max_num_batched_tokens, c.prefill_chunk_size, c.max_num_seqs,
                                                    c.policy, c.enable_prefix_cache, c.max_model_len), self.pool)
         self.runner = ModelRunner(self.model, self.kv, max(c.max_num_batched_tokens, c.max_num_seqs), c.max_num_seqs,
-                                  c.max_model_len, c.cuda_graphs and not _profiler.PROFILE and not _profiler.TRACE_FWD)
+                                  c.max_model_len, c.cuda_graphs and not _profiler.PROFILE and not _profiler.TRACE_FWD
+                                  and isinstance(weights.layers, list))  # a captured graph would pin evicted layers' addresses
         self.eos_token_id = c.eos_token_id
         if self.eos_token_id is None and tokenizer is not None:
             self.eos_token_id = tokenizer.special_tokens.eos
@@ -134,7 +138,8 @@ class LLM:
             if pipe is None:
                 raise ValueError("pp_size > 1 needs the stage's StageIO")
             layer_range = split_layers(cfg.n_layers, config.pp_size)[pipe.rank]
-        w = load_weights(g, cfg, device, act, tp_rank, config.tp_size, ep_rank, ep_size, layer_range=layer_range)
+        w = load_weights(g, cfg, device, act, tp_rank, config.tp_size, ep_rank, ep_size, layer_range=layer_range,
+                         resident_layers=config.resident_layers)
         try:
             tok = load_tokenizer_from_metadata(g.metadata)
         except TokenizerError:

@@ -140,9 +140,11 @@ class Transformer:
         if dev.type == "cuda" and cfg.attn_softcap > 0:
             raise NotImplementedError("soft-capped attention scores (Gemma-2) are implemented on the CPU path only")
         self._fuse_qkv_rope = dev.type == "cuda" and fuse_qkv_rope
-        if dev.type == "cuda" and fuse_swiglu:
+        # (load-time re-layouts walk every layer: not for a model that streams its layers from the file)
+        streamed = not isinstance(weights.layers, list)
+        if dev.type == "cuda" and fuse_swiglu and not streamed:
             self._interleave_gate_up()
-        if dev.type == "cuda" and fold_norms:
+        if dev.type == "cuda" and fold_norms and not streamed:
             self._fold_norm_weights()
 
     def _fold_norm_weights(self) -> None:

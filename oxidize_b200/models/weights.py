@@ -203,6 +203,51 @@ class LayerWeights:
     norms_folded: bool = False  # attn_norm / ffn_norm were multiplied into wqkv / w_gate_up (Transformer._fold_norm_weights)
 
 
+class StreamedLayers:
+    """The decoder layers of a checkpoint held as a list that loads a layer from the file mapping when it is indexed
+    and keeps at most ``capacity`` of them resident (least recently used goes first): a model whose layers do not fit
+    next to the KV cache still runs, at the price of re-reading layers every step (the reference's layer-wise model,
+    ``oxidize-core/src/model/layer_wise.rs``, with its LRU layer cache)."""
+
+    def __init__(self, load, n_layers: int, capacity: int):
+        from collections import OrderedDict
+
+        if capacity < 1:
+            raise ValueError("at least one layer has to be resident")
+        self._load, self._n, self.capacity = load, n_layers, capacity
+        self._cache: "OrderedDict[int, LayerWeights]" = OrderedDict()
+        self.loads = 0
+        self.evictions = 0
+
+    def __len__(self) -> int:
+        return self._n
+
+    def __getitem__(self, i: int) -> "LayerWeights":
+        if isinstance(i, slice):
+            raise TypeError("streamed layers are indexed one at a time")
+        if i < 0:
+            i += self._n
+        if not 0 <= i < self._n:
+            raise IndexError(i)
+        lw = self._cache.get(i)
+        if lw is not None:
+            self._cache.move_to_end(i)
+            return lw
+        while len(self._cache) >= self.capacity:
+            self._cache.popitem(last=False)
+            self.evictions += 1
+        lw = self._load(i)
+        self._cache[i] = lw
+        self.loads += 1
+        return lw
+
+    def __iter__(self):
+        return (self[i] for i in range(self._n))
+
+    def resident(self) -> List["LayerWeights"]:
+        return list(self._cache.values())
+
+
 @dataclass
 class MtpWeights:
     """``blk.L.nextn.*`` tensors of an in-GGUF multi-token-prediction head
@@ -238,7 +283,7 @@ class ModelWeights:
 
     def nbytes(self) -> int:
         n = self.embed.nbytes() + self.lm_head.nbytes()
-        for l in self.layers:
+        for l in (self.layers.resident() if isinstance(self.layers, StreamedLayers) else self.layers):
             for lw in (l.wqkv, l.wo, l.w_gate_up, l.w_down, l.shared_gate_up, l.shared_down):
                 if lw is not None:
                     n += lw.nbytes()
@@ -440,14 +485,19 @@ def _load_layer(src: GGUFWeightSource, cfg: ModelConfig, i: int, tp_rank: int, t
 
 def load_weights(g: GGUFFile, cfg: ModelConfig, device="cpu", act_dtype: torch.dtype = torch.float32,
                  tp_rank: int = 0, tp_size: int = 1, ep_rank: int = 0, ep_size: int = 1,
-                 layer_range: Optional[Tuple[int, int]] = None) -> ModelWeights:
+                 layer_range: Optional[Tuple[int, int]] = None, resident_layers: int = 0) -> ModelWeights:
     """Load this rank's shard of a GGUF checkpoint.
 
     ``layer_range`` selects a pipeline stage (only its own tensors are read, unlike the
-    reference's two-node pipeline where both nodes map the whole file, pipeline.rs:23)."""
+    reference's two-node pipeline where both nodes map the whole file, pipeline.rs:23).
+    ``resident_layers`` > 0 keeps only that many decoder layers loaded at a time (:class:`StreamedLayers`)."""
     src = GGUFWeightSource(g, device, act_dtype)
     l0, l1 = layer_range if layer_range is not None else (0, cfg.n_layers)
-    layers = [_load_layer(src, cfg, i, tp_rank, tp_size, ep_rank, ep_size) for i in range(l0, l1)]
+    if resident_layers > 0 and resident_layers < l1 - l0:
+        layers = StreamedLayers(lambda i: _load_layer(src, cfg, l0 + i, tp_rank, tp_size, ep_rank, ep_size), l1 - l0,
+                                resident_layers)
+    else:
+        layers = [_load_layer(src, cfg, i, tp_rank, tp_size, ep_rank, ep_size) for i in range(l0, l1)]
     embed = src.matrix("token_embd.weight")
     v0, v1 = shard_range(cfg.vocab_size, tp_rank, tp_size) if cfg.vocab_size % tp_size == 0 else (0, cfg.vocab_size)
     head_name = "output.weight" if src.has("output.weight") else "token_embd.weight"

@@ -761,3 +761,28 @@ def test_rope_frequency_factors_of_the_checkpoint_are_applied(tmp_path):
     assert not torch.allclose(l0.last_step[1].logits.float(), l1.last_step[1].logits.float(), atol=1e-4)
     with pytest.raises(ValueError):
         opref.rope_inv_freq(16, 10000.0, freq_factors=[1.0, 2.0])
+
+
+def test_streamed_layers_give_the_same_tokens_with_bounded_residency(tmp_path):
+    """Layer-wise execution: only `resident_layers` decoder layers are loaded at a time, the rest stream from the file
+    mapping as the forward pass reaches them."""
+    from oxidize_b200.models.weights import StreamedLayers
+
+    path = str(tmp_path / "m.gguf")
+    synth_gguf(path, preset("tiny-llama", n_layers=5, vocab_size=300, hidden_size=64, n_heads=4, n_kv_heads=2, head_dim=16,
+                            ffn_size=96), "Q8_0", seed=2, norm_jitter=0.1)
+    ec = dict(max_model_len=64, max_num_seqs=2, num_kv_blocks=32, prefill_chunk_size=32, max_num_batched_tokens=32)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    prompts = [[5, 9, 20, 31, 7], list(range(3, 30))]
+    full = LLM.from_gguf(path, EngineConfig(**ec), device="cpu")
+    want = [o.token_ids for o in full.generate(prompts, sp)]
+    llm = LLM.from_gguf(path, EngineConfig(**ec, resident_layers=2), device="cpu")
+    layers = llm.weights.layers
+    assert isinstance(layers, StreamedLayers) and len(layers) == 5 and layers.loads == 0
+    assert [o.token_ids for o in llm.generate(prompts, sp)] == want
+    assert len(layers.resident()) == 2 and layers.evictions > 0 and layers.loads == layers.evictions + 2
+    assert llm.weights.nbytes() < full.weights.nbytes()
+    # a cache as large as the model is the ordinary resident list
+    assert isinstance(LLM.from_gguf(path, EngineConfig(**ec, resident_layers=5), device="cpu").weights.layers, list)
+    with pytest.raises(IndexError):
+        layers[5]
