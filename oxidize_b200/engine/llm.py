@@ -102,8 +102,10 @@ class LLM:
         nblocks = c.num_kv_blocks or self._auto_blocks(spec)
         self.kv = KVCache(spec, nblocks, self.device)
         self.pool = make_block_pool(nblocks, c.kv_page_size, c.enable_prefix_cache)
+        # a window that applies to every layer lets the scheduler hand pages back as they fall out of it
+        uniform_window = self.cfg.sliding_window if (self.cfg.sliding_window > 0 and self.cfg.sliding_window_pattern == 0) else 0
         self.scheduler = Scheduler(SchedulerConfig(c.max_num_batched_tokens, c.prefill_chunk_size, c.max_num_seqs,
-                                                   c.policy, c.enable_prefix_cache, c.max_model_len), self.pool)
+                                                   c.policy, c.enable_prefix_cache, c.max_model_len, uniform_window), self.pool)
         self.runner = ModelRunner(self.model, self.kv, max(c.max_num_batched_tokens, c.max_num_seqs), c.max_num_seqs,
                                   c.max_model_len, c.cuda_graphs and not _profiler.PROFILE and not _profiler.TRACE_FWD
                                   and isinstance(weights.layers, list))  # a captured graph would pin evicted layers' addresses

@@ -40,6 +40,10 @@ class SchedulerConfig:
     policy: str = "fcfs"  # fcfs | sjf
     enable_prefix_cache: bool = True
     max_model_len: int = 1 << 20
+    # > 0: every layer attends over at most this many latest positions, so pages that lie wholly before the window of the
+    # next query are handed back to the pool while the sequence runs (the reference keeps a ring of `window` rows per layer,
+    # oxidize-core/src/compute/kv_cache/cache.rs; with pages the ring becomes "free what fell out of the window")
+    attention_window: int = 0
 
 
 class Sequence:
@@ -64,6 +68,9 @@ class Sequence:
         self._published = 0  # number of blocks published to the prefix cache
         self.draft_tokens: List[int] = []  # speculative rows scheduled this step
         self.num_cached_tokens = 0
+        # leading pages already returned to the pool (sliding-window models); their slots in `blocks` repeat the id of the
+        # first live page so that the block table stays a table of valid ids
+        self._released = 0
 
     @property
     def num_tokens(self) -> int:
@@ -148,8 +155,8 @@ class Scheduler:
             return
         seq.status = SeqStatus.FINISHED
         seq.finish_reason = reason
-        self.pool.release_all(seq.blocks)
-        seq.blocks = []
+        self.pool.release_all(seq.blocks[seq._released:])
+        seq.blocks, seq._released = [], 0
         if seq in self.running:
             self.running.remove(seq)
         try:
@@ -159,8 +166,8 @@ class Scheduler:
         self.finished.append(seq)
 
     def _preempt(self, seq: Sequence) -> None:
-        self.pool.release_all(seq.blocks)
-        seq.blocks = []
+        self.pool.release_all(seq.blocks[seq._released:])
+        seq.blocks, seq._released = [], 0
         seq.num_computed = 0
         seq._hash_state = FNV_OFFSET
         seq._published = 0
@@ -335,6 +342,8 @@ class Scheduler:
                 seq.draft_tokens = []
             if publish and seq._published < len(seq.prompt) // ps:
                 self._publish_full_blocks(seq)
+            if self.config.attention_window > 0:
+                self._release_outside_window(seq)
             if not ss.sample:
                 continue
             for t in toks:
@@ -350,6 +359,19 @@ class Scheduler:
             if seq.status is not FINISHED and (len(seq.blocks) - 1) * ps >= len(seq.prompt) + len(seq.output):
                 self._trim_blocks(seq)  # more pages than the tokens need (speculative rows that were rejected)
         return done
+
+    def _release_outside_window(self, seq: Sequence) -> None:
+        """Return the pages no later query of ``seq`` can see: the next query sits at position ``num_computed`` and sees
+        keys at positions > num_computed - window, so a page whose last position is <= num_computed - window is dead."""
+        ps = self.pool.page_size
+        dead = min(max(0, (seq.num_computed - self.config.attention_window) // ps), len(seq.blocks) - 1)
+        if dead <= seq._released:
+            return
+        keep = seq.blocks[dead]
+        for i in range(seq._released, dead):
+            self.pool.release(seq.blocks[i])  # a page published to the prefix cache stays findable there until evicted
+        seq.blocks[:dead] = [keep] * dead  # every dead slot names a page this sequence still owns
+        seq._released = dead
 
     def _trim_blocks(self, seq: Sequence) -> None:
         """Free tail pages past what the accepted tokens need (speculative rollback)."""

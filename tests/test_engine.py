@@ -786,3 +786,39 @@ def test_streamed_layers_give_the_same_tokens_with_bounded_residency(tmp_path):
     assert isinstance(LLM.from_gguf(path, EngineConfig(**ec, resident_layers=5), device="cpu").weights.layers, list)
     with pytest.raises(IndexError):
         layers[5]
+
+
+def test_pages_outside_a_uniform_attention_window_return_to_the_pool(tmp_path):
+    """Sliding-window model (every layer windowed): a running sequence keeps only the pages its window still reaches;
+    the tokens are those of an engine that keeps everything; interleaved local / global models keep everything."""
+    path = str(tmp_path / "swa.gguf")
+    synth_gguf(path, preset("tiny-llama", arch="mistral", n_layers=2, vocab_size=300, hidden_size=64, n_heads=4, n_kv_heads=2,
+                            head_dim=16, ffn_size=96, sliding_window=24), "F32", seed=5, norm_jitter=0.1)
+    ec = dict(max_model_len=256, max_num_seqs=2, num_kv_blocks=40, prefill_chunk_size=32, max_num_batched_tokens=64)
+    sp = SamplingParams(temperature=0.0, max_tokens=100, ignore_eos=True)
+    prompts = [list(range(3, 73)), [5, 9, 20, 31, 7]]
+    keep_all = LLM.from_gguf(path, EngineConfig(**ec), device="cpu")
+    assert keep_all.scheduler.config.attention_window == 24
+    keep_all.scheduler.config.attention_window = 0
+    want = [o.token_ids for o in keep_all.generate(prompts, sp)]
+    llm = LLM.from_gguf(path, EngineConfig(**ec), device="cpu")
+    for p in prompts:
+        llm.add_request(p, sp)
+    peak_live, total = 0, llm.pool.num_free
+    while llm.has_unfinished:
+        llm.step()
+        for s in llm.scheduler.running:
+            live = len(s.blocks) - s._released
+            peak_live = max(peak_live, live)
+            assert len(set(s.blocks[: s._released + 1])) <= 1  # released slots repeat the first live page's id
+    assert peak_live <= 24 // 16 + 3  # window pages + the page being filled + chunk slack, not 170 / 16 = 11
+    assert llm.pool.num_free == total  # everything came back, nothing twice
+    llm2 = LLM.from_gguf(path, EngineConfig(**ec), device="cpu")
+    assert [o.token_ids for o in llm2.generate(prompts, sp)] == want
+    # a pool too small for whole sequences is enough once dead pages return: 2 x 170 tokens need 22 pages, 12 suffice
+    small = LLM.from_gguf(path, EngineConfig(**{**ec, "num_kv_blocks": 12}), device="cpu")
+    assert [o.token_ids for o in small.generate(prompts, sp)] == want and small.scheduler.num_preemptions == 0
+    mixed = str(tmp_path / "mixed.gguf")
+    synth_gguf(mixed, preset("tiny-llama", n_layers=2, vocab_size=300, hidden_size=64, n_heads=4, n_kv_heads=2, head_dim=16,
+                             ffn_size=96, sliding_window=24, sliding_window_pattern=2), "F32", seed=5)
+    assert LLM.from_gguf(mixed, EngineConfig(**ec), device="cpu").scheduler.config.attention_window == 0
