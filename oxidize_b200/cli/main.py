@@ -123,7 +123,8 @@ def build_parser() -> argparse.ArgumentParser:
     a("--pipe-listen", default=None)
     a("--pipe-max-tokens", type=int, default=64)
     a("--vision", action="store_true")
-    a("--image", default=None)
+    a("--image", default=None, help="image file shown to the model (needs --mmproj); '<image>' in the prompt marks its place")
+    a("--mmproj", default=None, help="vision tower + projector file (clip.vision.* metadata, v.* / mm.* tensors)")
     for f in ("--cpu-optimized", "--ram-offload", "--mmap-prefetch", "--mmap-hugepages", "--layer-wise"):
         a(f, action="store_true")
     a("--ram-offload-threads", type=int, default=0)
@@ -253,6 +254,8 @@ def cmd_run(args, passed) -> int:
         prompt = args.prompt
         if llm.tokenizer is None:
             raise SystemExit("error: the model has no tokenizer metadata; pass --tokens 1,2,3")
+    if args.image:
+        prompt = image_prompt(llm, args.mmproj, args.image, prompt if isinstance(prompt, str) else "")
     det = llm.tokenizer.streaming_detokenizer() if llm.tokenizer is not None else None
     printed = [0]
 
@@ -272,6 +275,27 @@ def cmd_run(args, passed) -> int:
     n = len(out.token_ids)
     print(f"generation stats: tokens={n} speed={n / max(dt, 1e-9):.2f} tok/s", file=sys.stderr)
     return 0
+
+
+def image_prompt(llm, mmproj: Optional[str], image_path: str, text: str):
+    """(token ids, embedding positions, embedding rows) for a prompt with one image: the image's tokens go where the text
+    says ``<image>``, else in front of it."""
+    if not mmproj:
+        raise SystemExit("error: --image needs --mmproj (the vision tower and projector file)")
+    if llm.tokenizer is None:
+        raise SystemExit("error: an image prompt needs a tokenizer in the GGUF")
+    from PIL import Image
+
+    from ..vision import ImagePreprocessor, MultimodalPrompt, load_vision_encoder
+
+    enc = load_vision_encoder(mmproj, llm.device)
+    if enc.config.projection_dim != llm.cfg.hidden_size:
+        raise SystemExit(f"error: the projector makes {enc.config.projection_dim}-wide tokens, the model wants {llm.cfg.hidden_size}")
+    rows = enc.encode(ImagePreprocessor(enc.config)(Image.open(image_path).convert("RGB")))
+    before, _, after = text.partition("<image>") if "<image>" in text else ("", "", text)
+    st = llm.tokenizer.special_tokens
+    placeholder = st.unk if st.unk is not None and st.unk >= 0 else 0
+    return MultimodalPrompt().add_text(before).add_image(rows).add_text(after).build(llm.tokenizer, placeholder)
 
 
 def cmd_chat(args, passed) -> int:

@@ -164,7 +164,10 @@ class LLM:
 
     # ------------------------------------------------------------------ request API
     def add_request(self, prompt: Union[str, Seq[int]], params: Optional[SamplingParams] = None,
-                    request_id: Optional[str] = None) -> str:
+                    request_id: Optional[str] = None, input_embeds: Optional[torch.Tensor] = None,
+                    embed_positions: Optional[Seq[int]] = None) -> str:
+        """Queue a request.  ``input_embeds`` [n, hidden] with ``embed_positions`` (n ascending prompt positions) replaces
+        the token embeddings at those positions: image tokens of a multimodal prompt (see ``vision.MultimodalPrompt``)."""
         params = params or SamplingParams()
         params.validate()
         if isinstance(prompt, str):
@@ -177,6 +180,15 @@ class LLM:
         if bad:
             raise ValueError(f"token id {bad[0]} outside vocabulary of {self.cfg.vocab_size}")
         seq = Sequence(ids, params, request_id, arrival=time.perf_counter())
+        if input_embeds is not None:
+            pos = [int(p) for p in (embed_positions or [])]
+            if input_embeds.ndim != 2 or input_embeds.shape[0] != len(pos) or input_embeds.shape[1] != self.cfg.hidden_size:
+                raise ValueError(f"input_embeds must be [len(embed_positions), {self.cfg.hidden_size}]")
+            if any(b <= a for a, b in zip(pos, pos[1:])) or (pos and not 0 <= pos[0] <= pos[-1] < len(ids)):
+                raise ValueError("embed_positions must be ascending positions inside the prompt")
+            if getattr(self, "spec", None) is not None:
+                raise ValueError("requests with input embeddings are not drafted for: run them on an engine without speculation")
+            seq.input_embeds, seq.embed_positions = input_embeds.to(self.device), pos
         self.scheduler.add(seq)
         self._seqs[seq.request_id] = seq
         return seq.request_id
@@ -445,7 +457,9 @@ class LLM:
             plist = [params or SamplingParams()] * len(prompts)
         else:
             plist = list(params)
-        ids = [self.add_request(p, sp) for p, sp in zip(prompts, plist)]
+        # a prompt may also be (token ids, embedding positions, embedding rows): see add_request / vision.MultimodalPrompt
+        ids = [self.add_request(p[0], sp, input_embeds=p[2], embed_positions=p[1]) if isinstance(p, tuple)
+               else self.add_request(p, sp) for p, sp in zip(prompts, plist)]
         final: Dict[str, RequestOutput] = {}
         while self.has_unfinished:
             for ro in self.step():

@@ -302,6 +302,25 @@ class ModelRunner:
             block_tables=b.d("block_tables").view(b.max_seqs, self.max_blocks)[:B],
             logits_indices=b.d("logits_indices", nl), max_query_len=max_q, max_seq_len=max_len, num_seqs=B)
 
+    def _embed_overrides(self, scheduled: Sequence[ScheduledSeq], meta: BatchMeta) -> None:
+        """Prompt positions of this step's prefill rows whose embedding is given by the request (image tokens) instead of
+        the token table: collected as (batch rows, embedding rows) for the model's embedding stage."""
+        rows: List[int] = []
+        vecs: List[torch.Tensor] = []
+        t = 0
+        for ss in scheduled:
+            emb = getattr(ss.seq, "input_embeds", None)
+            if emb is not None and ss.is_prefill:
+                lo, hi = ss.start, ss.start + ss.num_tokens
+                for j, p in enumerate(ss.seq.embed_positions):
+                    if lo <= p < hi:
+                        rows.append(t + p - lo)
+                        vecs.append(emb[j])
+            t += ss.num_tokens
+        if rows:
+            meta.extra["embed_overrides"] = (torch.tensor(rows, dtype=torch.int64, device=self.device),
+                                             torch.stack(vecs).to(self.device))
+
     # ------------------------------------------------------------------ execution
     def _forward_sample(self, meta: BatchMeta, all_greedy: bool, tie: str, feed: Optional[torch.Tensor] = None):
         if all_greedy and not self.keep_logits:
@@ -388,6 +407,8 @@ class ModelRunner:
             bucket = B
         else:
             meta = self._meta(T, B, nl, max_q, max_len, logits_all=decode_only and nl == T)
+            if not decode_only:
+                self._embed_overrides(scheduled, meta)
             toks, logits = self._forward_sample(meta, all_greedy and not needs_host_logits, tie,
                                                 feed=feed if not needs_host_logits else None)
         if toks is None:  # not the last pipeline stage

@@ -71,6 +71,10 @@ class Sequence:
         # leading pages already returned to the pool (sliding-window models); their slots in `blocks` repeat the id of the
         # first live page so that the block table stays a table of valid ids
         self._released = 0
+        # prompt positions whose embedding comes from the request (image tokens) and the rows [n, hidden] that go there;
+        # such a sequence neither reads nor feeds the prefix cache (its placeholder tokens do not identify its content)
+        self.embed_positions: List[int] = []
+        self.input_embeds = None
 
     @property
     def num_tokens(self) -> int:
@@ -207,7 +211,7 @@ class Scheduler:
         return True
 
     def _publish_full_blocks(self, seq: Sequence) -> None:
-        if not self.config.enable_prefix_cache:
+        if not self.config.enable_prefix_cache or seq.input_embeds is not None:
             return
         ps = self.pool.page_size
         n_prompt_full = len(seq.prompt) // ps
@@ -220,7 +224,7 @@ class Scheduler:
 
     def _admit(self, seq: Sequence) -> None:
         """Attach cached prefix blocks to a sequence entering prefill."""
-        if seq.num_computed == 0 and not seq.blocks and self.config.enable_prefix_cache:
+        if seq.num_computed == 0 and not seq.blocks and self.config.enable_prefix_cache and seq.input_embeds is None:
             blocks, covered = self.pool.match_prefix(seq.prompt)
             if blocks:
                 seq.blocks = blocks

@@ -50,8 +50,6 @@ def _rope_settings(c: Dict[str, Any]) -> Tuple[float, float, Dict[str, Any]]:
 
 def write_hf_metadata(w: GGUFWriter, arch: str, c: Dict[str, Any]) -> None:
     U, F = GGUFValueType.UINT32, GGUFValueType.FLOAT32
-    if "text_config" in c:  # multimodal wrapper: the decoder's settings are nested
-        c = dict(c["text_config"], architectures=c.get("architectures"))
     heads = int(c["num_attention_heads"])
     hidden = int(c["hidden_size"])
     w.add("general.name", str(c.get("_name_or_path") or c.get("model_type") or "converted"))
@@ -128,6 +126,13 @@ def _kind_of(gname: str) -> str:
 def convert_safetensors_to_gguf(src_dir: str, out_path: str, quant: str = "F16", tokenizer_metadata: Dict = None) -> str:
     with open(os.path.join(src_dir, "config.json")) as f:
         cfg = json.load(f)
+    if "text_config" in cfg:
+        # multimodal wrapper (LLaVA, Gemma-3 with vision): the language model's settings are nested and only its tensors
+        # are converted; the vision tower goes into a projector file of its own (vision.convert_vision_tower)
+        wrapper = cfg
+        cfg = dict(wrapper["text_config"])
+        if cfg.get("model_type") == "gemma3_text" or "Gemma3" in "".join(wrapper.get("architectures") or []):
+            cfg.setdefault("architectures", ["Gemma3ForCausalLM"])
     arch = arch_from_config(cfg)
     files = [SafeTensorsFile(p) for p in sorted(glob.glob(os.path.join(src_dir, "*.safetensors")))]
     if not files:

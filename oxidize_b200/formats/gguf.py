@@ -613,10 +613,10 @@ def map_hf_tensor_name(name: str, arch: Optional[str] = None) -> Optional[Tuple[
     return the expert index to stack at; everything else returns ``None`` for the index.
     Unknown names return ``None``.  ``arch`` (the GGUF architecture string) selects the Gemma-2/3 norm names.
     """
-    if name.startswith("language_model."):  # text tower of a multimodal checkpoint
-        name = name[len("language_model."):]
-    elif name.startswith("model.language_model."):
-        name = "model." + name[len("model.language_model."):]
+    if "language_model." in name:  # text tower of a multimodal checkpoint, under one of several wrappers
+        name = name.replace("language_model.", "")
+        while name.startswith("model.model."):
+            name = name[len("model."):]
     if name in _HF_TOP_MAP:
         return _HF_TOP_MAP[name], None
     m = _HF_LAYER_RE.match(name)

@@ -392,7 +392,11 @@ class Transformer:
         """(h, residual) entering this stage's layers: the embedding on the first stage, the previous stage's
         activations otherwise (one [2, T, H] message: h and the residual stream)."""
         if self.pipe is None or self.pipe.is_first:
-            return self.embed(meta.token_ids), None
+            h = self.embed(meta.token_ids)
+            ov = meta.extra.get("embed_overrides")
+            if ov is not None:  # rows whose embedding the request supplied (image tokens)
+                h.index_copy_(0, ov[0], ov[1].to(h.dtype))
+            return h, None
         both = self.pipe.recv_prev((2, int(meta.token_ids.shape[0]), self.cfg.hidden_size), self.act_dtype, self.device)
         return both[0], both[1]
 
