@@ -126,6 +126,7 @@ constexpr int EPI_ADD_INTO = 1;   // Y += acc (residual accumulate, bf16 read-mo
 constexpr int EPI_ROPE = 3;       // fused qkv projection: RoPE on q/k heads, q -> q_out, k/v -> paged KV cache (RopeArgs)
 constexpr int EPI_SWIGLU = 2;     // weight rows interleaved per tile (64 gate rows, then their 64 up rows):
                                   // Y[t, n0/2 + c] = silu(acc[c]) * acc[64 + c], Y has N/2 columns
+constexpr int EPI_GEGLU = 4;      // the same with the tanh form of GELU on the gate (Gemma)
 
 // RMSNorm folded into the GEMMs around it.  The norm weight is multiplied into the consuming projection's
 // columns when the model is loaded; what remains of the norm is one scalar per token, 1/rms(x_t), which
@@ -263,8 +264,14 @@ __device__ __forceinline__ void store_tile_rows(const uint8_t* stage, int ntok, 
 
 // SwiGLU epilogue: the staged tile holds 64 gate columns followed by the 64 matching up columns of each
 // token; writes the 64 activations with 16-byte stores (128 threads: 8 chunks x 16 token rows per pass).
+// gelu: act(g) = g * sigmoid(2 sqrt(2/pi) (g + 0.044715 g^3)) (= 0.5 g (1 + tanh(...))) instead of g * sigmoid(g).
+__device__ __forceinline__ float glu_gate(float g, bool gelu) {
+  const float z = gelu ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : g;
+  return g / (1.f + __expf(-z));
+}
+
 __device__ __forceinline__ void store_tile_rows_swiglu(const uint8_t* stage, int ntok, int t_first, int n0,
-                                                       __nv_bfloat16* Y, int ldY, int tid) {
+                                                       __nv_bfloat16* Y, int ldY, int tid, bool gelu) {
   const int chunk = tid & 7, trow = tid >> 3;
   for (int t = trow; t < ntok; t += 16) {
     const uint4 g = *reinterpret_cast<const uint4*>(stage + t * 256 + chunk * 16);
@@ -274,7 +281,7 @@ __device__ __forceinline__ void store_tile_rows_swiglu(const uint8_t* stage, int
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float2 a = unpack_bf16x2(gv[j]), b = unpack_bf16x2(uv[j]);
-      o[j] = pack_bf16x2(a.x / (1.f + __expf(-a.x)) * b.x, a.y / (1.f + __expf(-a.y)) * b.y);
+      o[j] = pack_bf16x2(glu_gate(a.x, gelu) * b.x, glu_gate(a.y, gelu) * b.y);
     }
     *reinterpret_cast<uint4*>(Y + (size_t)(t_first + t) * ldY + (n0 >> 1) + chunk * 8) = make_uint4(o[0], o[1], o[2], o[3]);
   }
@@ -830,8 +837,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (use_ar) {
           ar_exchange(ar, smem, ticket[2], tile_id, n0, t0, tvalid, N, Y, ldY, abort_flag, etid, ssq_dst);
-        } else if (epi_mode == EPI_SWIGLU) {
-          store_tile_rows_swiglu(smem, tvalid, t0, n0, Y, ldY, etid);
+        } else if (epi_mode == EPI_SWIGLU || epi_mode == EPI_GEGLU) {
+          store_tile_rows_swiglu(smem, tvalid, t0, n0, Y, ldY, etid, epi_mode == EPI_GEGLU);
         } else if (epi_mode == EPI_ROPE) {
           store_tile_rows_rope(smem, tvalid, t0, n0, ro, etid);
         } else {
@@ -896,8 +903,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       if (ok && je > jb) {
         if (use_ar) {
           ar_exchange(ar, stage_b, ticket[2], tile_id * splits + split, n0, t0 + jb, je - jb, N, Y, ldY, abort_flag, etid, ssq_dst);
-        } else if (epi_mode == EPI_SWIGLU) {
-          store_tile_rows_swiglu(stage_b, je - jb, t0 + jb, n0, Y, ldY, etid);
+        } else if (epi_mode == EPI_SWIGLU || epi_mode == EPI_GEGLU) {
+          store_tile_rows_swiglu(stage_b, je - jb, t0 + jb, n0, Y, ldY, etid, epi_mode == EPI_GEGLU);
         } else if (epi_mode == EPI_ROPE) {
           store_tile_rows_rope(stage_b, je - jb, t0 + jb, n0, ro, etid);
         } else if (vec_ok) {

@@ -28,10 +28,10 @@ static int gemm_bf16_impl(const void* X, const void* W, void* Y, const float* bi
                           cudaStream_t stream, const NormArgs& nm) {
   if (T <= 0 || N <= 0 || K <= 0) return 0;
   // the per-row sums of squares come out of the vector-store epilogues only
-  if (nm.sumsq_out != nullptr && (N % 8 != 0 || ldY % 8 != 0 || (reinterpret_cast<uintptr_t>(Y) & 15) != 0 || epi_mode == EPI_SWIGLU))
+  const bool swiglu = epi_mode == EPI_SWIGLU || epi_mode == EPI_GEGLU;  // gated-activation epilogues: SiLU or tanh-GELU on the gate
+  if (nm.sumsq_out != nullptr && (N % 8 != 0 || ldY % 8 != 0 || (reinterpret_cast<uintptr_t>(Y) & 15) != 0 || swiglu))
     return (int)cudaErrorInvalidValue;
   if (K % 8 != 0) return (int)cudaErrorInvalidValue;  // TMA rows must be 16-byte multiples
-  const bool swiglu = epi_mode == EPI_SWIGLU;
   // the SwiGLU epilogue exists on the staged (vector-store) paths only: whole 128-row tiles, 16-byte output rows
   if (swiglu && (N % GEMM_BM != 0 || ldY % 8 != 0 || (reinterpret_cast<uintptr_t>(Y) & 15) != 0 || bias != nullptr))
     return (int)cudaErrorInvalidValue;

@@ -213,7 +213,8 @@ class Transformer:
         attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, window)
         cur = 1 - cur
         self._row_parallel_into(attn.reshape(attn.shape[0], -1), lw.wo, r, acc[cur])
-        act = opcuda.linear_swiglu(r, lw.w_gate_up.parts[0].data, sumsq_in=acc[cur], eps=eps, clear=acc[1 - cur])
+        act = opcuda.linear_swiglu(r, lw.w_gate_up.parts[0].data, sumsq_in=acc[cur], eps=eps, clear=acc[1 - cur],
+                                   gelu=cfg.ffn_act == "gelu_tanh")
         cur = 1 - cur
         self._row_parallel_into(act, lw.w_down, r, acc[cur])
         return cur
@@ -223,8 +224,6 @@ class Transformer:
         epilogue of the gate_up GEMM (one kernel and one activation round trip less per layer)."""
         from ..ops import cuda as opcuda
 
-        if self.cfg.ffn_act != "silu":
-            return  # the GEMM epilogue computes SiLU(gate) * up only
         for lw in self.w.layers:
             w = lw.w_gate_up
             if w is None or w.swiglu_interleaved or len(w.parts) != 1 or w.bias is not None:
@@ -290,7 +289,7 @@ class Transformer:
         if lw.w_gate_up.swiglu_interleaved:
             from ..ops import cuda as opcuda
 
-            act = opcuda.linear_swiglu(x, lw.w_gate_up.parts[0].data)
+            act = opcuda.linear_swiglu(x, lw.w_gate_up.parts[0].data, gelu=self.cfg.ffn_act == "gelu_tanh")
         elif self.cfg.ffn_act == "gelu_tanh":
             act = ops.gelu_mul(ops.linear(x, lw.w_gate_up))
         else:

@@ -246,7 +246,7 @@ def gemm_plan(T: int, N: int, K: int, splits_hint: int = 0):
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
               ld_out: Optional[int] = None, add_into: bool = False, splits: int = 0, swiglu: bool = False,
               sumsq_in: Optional[torch.Tensor] = None, eps: float = 0.0, clear: Optional[torch.Tensor] = None,
-              sumsq_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+              sumsq_out: Optional[torch.Tensor] = None, gelu: bool = False) -> torch.Tensor:
     """out[T, N] = x[T, K] @ w[N, K]^T on the tcgen05 kernel; ``out`` may be a column slice of a
     wider row-major buffer (pass its row stride as ``ld_out``).
 
@@ -265,7 +265,7 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     elif ld_out is None:
         ld_out = out.stride(0)
     s = scratch(x.device)
-    epi = 2 if swiglu else (1 if add_into else 0)
+    epi = (4 if gelu else 2) if swiglu else (1 if add_into else 0)  # EPI_GEGLU / EPI_SWIGLU / EPI_ADD_INTO / EPI_STORE
     if sumsq_in is None and sumsq_out is None:
         _check(lib().oxb_gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), _p(bias), T, N, K, ld_out, epi, splits,
                                    s.gemm_ws.data_ptr(), s.gemm_ws.numel() * 4, s.gemm_counters.data_ptr(),
@@ -357,11 +357,12 @@ def interleave_gate_up(w: torch.Tensor) -> torch.Tensor:
 
 
 def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, sumsq_in: Optional[torch.Tensor] = None,
-                  eps: float = 0.0, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """silu(x W_gate^T) * (x W_up^T) in ONE kernel: the activation is the GEMM's epilogue."""
+                  eps: float = 0.0, clear: Optional[torch.Tensor] = None, gelu: bool = False) -> torch.Tensor:
+    """act(x W_gate^T) * (x W_up^T) in ONE kernel: the activation (SiLU, or tanh-GELU with ``gelu``) is the GEMM's
+    epilogue."""
     if x.dtype != torch.bfloat16:
         x = x.to(torch.bfloat16)
-    return gemm_bf16(x.contiguous(), w_interleaved, swiglu=True, sumsq_in=sumsq_in, eps=eps, clear=clear)
+    return gemm_bf16(x.contiguous(), w_interleaved, swiglu=True, sumsq_in=sumsq_in, eps=eps, clear=clear, gelu=gelu)
 
 
 # --------------------------------------------------------------------------- glue ops

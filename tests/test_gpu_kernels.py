@@ -545,6 +545,10 @@ def test_gemm_swiglu_epilogue(C, T, F, K):
     assert _rel_err(got, want) < 1e-2
     unfused = C.silu_mul(C.gemm_bf16(x, w))
     assert _rel_err(got, unfused) < 1e-2
+    # the tanh-GELU form of the same epilogue (GeGLU)
+    got_g = C.linear_swiglu(x, C.interleave_gate_up(w), gelu=True)
+    assert _rel_err(got_g, torch.nn.functional.gelu(g, approximate="tanh") * u) < 1e-2
+    assert _rel_err(got_g, C.gelu_mul(C.gemm_bf16(x, w))) < 1e-2 and _rel_err(got_g, got) > 5e-2
     _check_status(C)
 
 
