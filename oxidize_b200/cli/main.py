@@ -472,12 +472,53 @@ TOOL_VERBS = {"quantize": "oxidize_b200.offline.requantize", "prune": "oxidize_b
               "finetune": "oxidize_b200.offline.finetune"}
 
 
+def cmd_perplexity(argv: List[str]) -> int:
+    """``oxidize perplexity MODEL --file TEXT``: perplexity of a text file under a checkpoint, in windows of --ctx tokens
+    (what the reference's benchmark suite reports for its datasets; handy for judging a requantized or pruned file)."""
+    import math
+
+    ap = argparse.ArgumentParser(prog="oxidize perplexity")
+    ap.add_argument("model")
+    ap.add_argument("--file", required=True)
+    ap.add_argument("--ctx", type=int, default=512, help="tokens per window")
+    ap.add_argument("--max-windows", type=int, default=0)
+    ap.add_argument("--backend", default="auto", choices=["auto", "cpu", "cuda"])
+    ap.add_argument("--json", action="store_true")
+    a = ap.parse_args(argv)
+    import torch
+
+    from ..engine.llm import LLM, EngineConfig
+
+    dev = "cuda" if (a.backend == "cuda" or (a.backend == "auto" and torch.cuda.is_available())) else "cpu"
+    llm = LLM.from_gguf(resolve_model(a.model),
+                        EngineConfig(max_model_len=a.ctx, max_num_seqs=1, num_kv_blocks=(a.ctx + 15) // 16 + 2), device=dev)
+    if llm.tokenizer is None:
+        raise SystemExit("error: perplexity needs a tokenizer in the GGUF")
+    with open(a.file, encoding="utf-8") as f:
+        ids = llm.tokenizer.encode_with_special_tokens(f.read())
+    windows = [ids[i : i + a.ctx] for i in range(0, len(ids), a.ctx)]
+    windows = [w for w in windows if len(w) >= 2][: a.max_windows or None]
+    if not windows:
+        raise SystemExit("error: the file has fewer than two tokens")
+    total, count = 0.0, 0
+    for w in windows:
+        lp = llm.token_logprobs(w)
+        total += float(-lp.sum())
+        count += len(lp)
+    ppl = math.exp(total / count)
+    print(json.dumps({"perplexity": ppl, "tokens": count, "windows": len(windows), "ctx": a.ctx}) if a.json
+          else f"perplexity {ppl:.4f} over {count} tokens ({len(windows)} windows of {a.ctx})")
+    return 0
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     if argv and argv[0] in TOOL_VERBS:
         import importlib
 
         return importlib.import_module(TOOL_VERBS[argv[0]]).main(argv[1:])
+    if argv and argv[0] == "perplexity":
+        return cmd_perplexity(argv[1:])
     if argv and argv[0] == "convert":
         from ..formats.convert import convert_safetensors_to_gguf
 

@@ -441,6 +441,43 @@ class LLM:
             out.append(v.cpu().numpy())
         return np.stack(out)
 
+    def token_logprobs(self, tokens: Seq[int], chunk: int = 256) -> "np.ndarray":
+        """log p(tokens[i] | tokens[:i]) for i = 1 .. n-1, float64 [n - 1]: one pass over the text in chunks of ``chunk`` rows
+        on a cache of its own, the head applied to every row (the quantity behind perplexity; single-rank engines)."""
+        import numpy as np
+
+        from ..models.transformer import BatchMeta
+
+        if self.model.w.tp_size > 1 or self.pipe is not None:
+            raise NotImplementedError("scoring runs on single-rank engines")
+        ids = [int(t) for t in tokens]
+        if len(ids) < 2:
+            raise ValueError("need at least two tokens to score")
+        dev, m = self.device, self.model
+        i32 = dict(dtype=torch.int32, device=dev)
+        page = self.config.kv_page_size
+        n = len(ids)
+        nblk = (n + page - 1) // page
+        kv = KVCache(KVCacheSpec(len(m.w.layers), m.n_kv_local, m.kv_head_dim, page, self.kv.spec.dtype_name), nblk, dev)
+        bt = torch.arange(nblk, **i32)[None, :]
+        out = np.empty(n - 1, dtype=np.float64)
+        for lo in range(0, n - 1, chunk):
+            hi = min(lo + chunk, n - 1)  # rows lo .. hi-1 predict tokens lo+1 .. hi
+            pos = torch.arange(lo, hi, **i32)
+            meta = BatchMeta(torch.tensor(ids[lo:hi], **i32), pos, pos.clone(), torch.tensor([0, hi - lo], **i32),
+                             torch.tensor([hi], **i32), bt, torch.arange(hi - lo, **i32), hi - lo, hi, 1, logits_all=True)
+            lp = torch.log_softmax(m.forward(meta, kv).float(), dim=-1)
+            tgt = torch.tensor(ids[lo + 1 : hi + 1], dtype=torch.int64, device=dev)
+            out[lo:hi] = lp.gather(1, tgt[:, None]).squeeze(1).double().cpu().numpy()
+        return out
+
+    def perplexity(self, text: Union[str, Seq[int]], chunk: int = 256) -> float:
+        """exp(-mean log p) of a text under the model (``max_model_len`` tokens at most)."""
+        import numpy as np
+
+        ids = self.tokenizer.encode_with_special_tokens(text) if isinstance(text, str) else list(text)
+        return float(np.exp(-self.token_logprobs(ids[: self.config.max_model_len], chunk).mean()))
+
     def beam_search(self, prompt: Union[str, Seq[int]], beam_width: int = 4, max_tokens: int = 32,
                     length_penalty: float = 1.0):
         """Width-``beam_width`` search; returns [(generated token ids, normalised log-probability)], best first."""

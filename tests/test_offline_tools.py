@@ -191,3 +191,29 @@ def test_lora_merge_from_a_peft_directory(base, tmp_path):
     save_file({"base_model.model.model.layers.9.self_attn.q_proj.lora_A.weight": A,
                "base_model.model.model.layers.9.self_attn.q_proj.lora_B.weight": B}, str(ad / "adapter_model.safetensors"))
     assert cli_main(["lora-merge", "--base", base, "--adapter", str(ad), "--output", out]) == 2
+
+
+def test_perplexity_orders_checkpoints_by_damage(base, tmp_path, capsys):
+    """token_logprobs agrees with next_token_logits, and perplexity of a text the model itself wrote rises as the
+    checkpoint is pruned harder."""
+    llm = LLM.from_gguf(base, EngineConfig(**EC), device="cpu")
+    text = llm.generate([[5, 9, 20, 31, 7]], SamplingParams(temperature=0.0, max_tokens=60, ignore_eos=True))[0]
+    ids = text.prompt_token_ids + text.token_ids
+    lp = llm.token_logprobs(ids, chunk=16)  # several chunks
+    assert lp.shape == (len(ids) - 1,)
+    row = torch.log_softmax(torch.from_numpy(llm.next_token_logits([ids[:10]]))[0].double(), -1)
+    assert abs(float(row[ids[10]]) - lp[9]) < 1e-4
+    assert np.allclose(lp, llm.token_logprobs(ids, chunk=256), atol=1e-5)
+    ppl = {0.0: llm.perplexity(ids)}
+    for sp_ in (0.5, 0.9):
+        out = str(tmp_path / f"p{sp_}.gguf")
+        prune.prune_gguf(base, out, "magnitude", sparsity=sp_)
+        ppl[sp_] = LLM.from_gguf(out, EngineConfig(**EC), device="cpu").perplexity(ids)
+    assert ppl[0.0] < ppl[0.5] < ppl[0.9]
+    f = tmp_path / "t.txt"
+    f.write_text(llm.tokenizer.decode_without_special_tokens(ids))
+    assert cli_main(["perplexity", base, "--file", str(f), "--ctx", "32", "--backend", "cpu", "--json"]) == 0
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rep["windows"] >= 2 and rep["perplexity"] > 1.0
+    with pytest.raises(ValueError):
+        llm.token_logprobs([1])
