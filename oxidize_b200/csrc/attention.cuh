@@ -34,6 +34,9 @@ struct AttnArgs {
   int n_cta_splits, max_mtiles, window;
   int num_blocks;  // pages in the KV pool: block ids are checked against it
   float scale_log2;
+  // soft-capped scores (Gemma-2): score = cap * tanh(q.k * scale / cap).  cap_log2 = cap * log2(e) (0 = off),
+  // cap_arg = scale / cap
+  float cap_log2, cap_arg;
   float* ws_o;   // [B*nkv*max_mtiles*n_cta_splits, 16, hd]
   float* ws_ml;  // [.., 16, 2]
   int* counters; // [B*nkv*max_mtiles] zero-initialised tickets (CTA splits only)
@@ -317,7 +320,7 @@ paged_attention_kernel(const AttnArgs a, int G /*q heads per kv head*/) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int key = key0 + nt * 8 + 2 * t4 + e;
-          float v = s[nt][2 * i + e] * a.scale_log2;
+          float v = a.cap_log2 > 0.f ? a.cap_log2 * tanhf(s[nt][2 * i + e] * a.cap_arg) : s[nt][2 * i + e] * a.scale_log2;
           const bool ok = rvalid[i] && key <= qpos[i] && (a.window <= 0 || key > qpos[i] - a.window);
           v = ok ? v : -INFINITY;
           s[nt][2 * i + e] = v;

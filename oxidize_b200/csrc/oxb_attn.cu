@@ -37,8 +37,8 @@ static int attn_launch(const AttnArgs& a, int B, int G, cudaStream_t stream) {
 OXB_API int oxb_paged_attention(const void* q, void* out, const void* kv_data, const float* kv_scales,
                                 const int* block_tables, const int* seq_lens, const int* query_start, int B,
                                 int max_blocks, int nq, int nkv, int hd, int kv_mode, int max_query_len,
-                                int n_cta_splits, int window, float scale, float* ws_o, float* ws_ml, int* counters,
-                                int num_blocks, cudaStream_t stream) {
+                                int n_cta_splits, int window, float scale, float softcap, float* ws_o, float* ws_ml,
+                                int* counters, int num_blocks, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (nq % nkv != 0) return (int)cudaErrorInvalidValue;
   const int G = nq / nkv;
@@ -58,6 +58,8 @@ OXB_API int oxb_paged_attention(const void* q, void* out, const void* kv_data, c
   a.max_mtiles = (max_query_len * G + 15) / 16;
   a.window = window;
   a.scale_log2 = scale * 1.4426950408889634f;
+  a.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+  a.cap_arg = softcap > 0.f ? scale / softcap : 0.f;
   a.ws_o = ws_o;
   a.ws_ml = ws_ml;
   a.counters = counters;

@@ -137,8 +137,6 @@ class Transformer:
                 raise NotImplementedError("latent attention (DeepSeek-V2/V3) is implemented on the CPU path only: the "
                                           "attention kernel has 64- and 128-wide heads, the latent cache row is "
                                           f"{self.kv_head_dim} wide")
-        if dev.type == "cuda" and cfg.attn_softcap > 0:
-            raise NotImplementedError("soft-capped attention scores (Gemma-2) are implemented on the CPU path only")
         self._fuse_qkv_rope = dev.type == "cuda" and fuse_qkv_rope
         # (load-time re-layouts walk every layer: not for a model that streams its layers from the file)
         streamed = not isinstance(weights.layers, list)
@@ -210,7 +208,7 @@ class Transformer:
         else:
             qkv = opcuda.gemm_bf16(r, wq, sumsq_in=acc[cur], eps=eps, clear=acc[1 - cur])
             q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, rope, lw.q_norm, lw.k_norm, eps)
-        attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, window)
+        attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, window, cfg.attn_softcap)
         cur = 1 - cur
         self._row_parallel_into(attn.reshape(attn.shape[0], -1), lw.wo, r, acc[cur])
         act = opcuda.linear_swiglu(r, lw.w_gate_up.parts[0].data, sumsq_in=acc[cur], eps=eps, clear=acc[1 - cur],
@@ -278,7 +276,7 @@ class Transformer:
 
             if opcuda.qkv_rope_fusable(lw.wqkv.parts, kv, rope, lw.q_norm, lw.k_norm):
                 q = opcuda.linear_qkv_rope(x, lw.wqkv.parts[0].data, meta.positions, meta.slot_mapping, kv, layer, rope)
-                attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, window)
+                attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, window, cfg.attn_softcap)
                 return self.comm.linear_allreduce(attn.reshape(attn.shape[0], -1), lw.wo)
         qkv = ops.linear(x, lw.wqkv)
         q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, rope, lw.q_norm, lw.k_norm, cfg.rms_eps)

@@ -97,9 +97,7 @@ def qk_rope_kv_write(qkv, positions, slot_mapping, kv, layer, rope, q_norm=None,
 @instrument("paged_attention")
 def paged_attention(q, kv, layer, meta, scale, sliding_window=0, softcap=0.0):
     if q.is_cuda:
-        if softcap > 0:
-            raise NotImplementedError("soft-capped attention scores (Gemma-2) are implemented on the CPU path only")
-        return _cuda().paged_attention(q, kv, layer, meta, scale, sliding_window)
+        return _cuda().paged_attention(q, kv, layer, meta, scale, sliding_window, softcap=softcap)
     return ref.paged_attention(q, kv, layer, meta, scale, sliding_window, softcap)
 
 

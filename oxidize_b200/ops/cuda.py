@@ -114,8 +114,8 @@ def _declare(L) -> None:
     L.oxb_qk_rope_kvwrite.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, vp, f32, i32, i32, i32, i32, vp, vp, vp, i32,
                                       i32, i32, vp]
     L.oxb_argmax.argtypes = [vp, i32, i32, i32, i32, vp, vp, i32, vp]
-    L.oxb_paged_attention.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp,
-                                      vp, vp, i32, vp]
+    L.oxb_paged_attention.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32,
+                                      vp, vp, vp, i32, vp]
     L.oxb_sample.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, vp, i32, vp, vp]
     L.oxb_gemm_quant.argtypes =[vp, vp, i32, sz, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, sz, vp, i32, vp]
     u64p, ull = ctypes.POINTER(ctypes.c_uint64), ctypes.c_ulonglong
@@ -486,7 +486,7 @@ def attn_splits(B: int, nkv: int, mtiles: int, max_seq_len: int, sms: int) -> in
     return max(1, min(want, cap, 16))
 
 
-def paged_attention(q, kv, layer, meta, scale, sliding_window=0, splits: Optional[int] = None):
+def paged_attention(q, kv, layer, meta, scale, sliding_window=0, splits: Optional[int] = None, softcap: float = 0.0):
     T, nq, hd = q.shape
     nkv = kv.spec.n_kv_heads
     B = meta.seq_lens.shape[0]
@@ -505,7 +505,8 @@ def paged_attention(q, kv, layer, meta, scale, sliding_window=0, splits: Optiona
     _check(lib().oxb_paged_attention(q.data_ptr(), out.data_ptr(), kv.data[layer].data_ptr(), _p(kv.scales[layer]),
                                      meta.block_tables.data_ptr(), meta.seq_lens.data_ptr(), meta.query_start.data_ptr(),
                                      B, meta.block_tables.stride(0), nq, nkv, hd, KV_MODE[kv.dtype_name],
-                                     max(1, meta.max_query_len), splits, sliding_window, scale, _p(ws_o), _p(ws_ml),
+                                     max(1, meta.max_query_len), splits, sliding_window, scale, float(softcap), _p(ws_o),
+                                     _p(ws_ml),
                                      _p(cnt), kv.num_blocks, _stream()), "oxb_paged_attention")
     return out
 

@@ -248,6 +248,10 @@ def test_paged_attention(C, kvd, hd, nq, nkv, qlens, ctx, splits, window):
     want = ref.paged_attention(q.cpu().float(), kv_c, 0, mc, scale, window)
     assert _rel_err(got.cpu(), want) < 1.5e-2
     assert torch.isfinite(got.float()).all()
+    # soft-capped scores (cap small enough to bend them: |q.k| * scale reaches several units here)
+    capped = C.paged_attention(q, kv, 0, meta, scale, window, splits=splits, softcap=2.0)
+    want_c = ref.paged_attention(q.cpu().float(), kv_c, 0, mc, scale, window, 2.0)
+    assert _rel_err(capped.cpu(), want_c) < 1.5e-2 and _rel_err(capped.cpu(), want) > 1e-2
 
 
 def test_argmax(C):
@@ -286,6 +290,37 @@ def test_model_gpu_matches_cpu(C, tmp_path):
         gpu.step()
         lc, lg = cpu.last_step[1].logits, gpu.last_step[1].logits
         assert _rel_err(lg.cpu(), lc) < 3e-2
+    _check_status(C)
+
+
+def test_gemma2_model_gpu_matches_cpu(C, tmp_path):
+    """Gemma-2 on the device: soft-capped attention scores inside the attention kernel, soft-capped logits, GeGLU epilogue,
+    every other layer windowed."""
+    from oxidize_b200.engine.llm import LLM, EngineConfig
+    from oxidize_b200.engine.sampler import SamplingParams
+    from oxidize_b200.models.config import preset
+    from oxidize_b200.utils.synth import synth_gguf
+
+    cfg = preset("tiny-llama", arch="gemma2", n_layers=4, vocab_size=512, hidden_size=256, n_heads=4, n_kv_heads=2, head_dim=64,
+                 ffn_size=512, sliding_window=16, sliding_window_pattern=2, embedding_scale=16.0, attn_scale=0.15, ffn_act="gelu_tanh",
+                 post_norms=True, attn_softcap=5.0, final_softcap=3.0, tie_embeddings=True)
+    path = str(tmp_path / "gemma2.gguf")
+    synth_gguf(path, cfg, "BF16", seed=0, norm_jitter=0.1)
+    ec = dict(max_model_len=128, max_num_seqs=4, num_kv_blocks=64, prefill_chunk_size=32, max_num_batched_tokens=64)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    cpu = LLM.from_gguf(path, EngineConfig(**ec), device="cpu")
+    gpu = LLM.from_gguf(path, EngineConfig(**ec, cuda_graphs=False), device="cuda")
+    assert gpu.model.cfg.attn_softcap == 5.0 and gpu.model.cfg.final_softcap == 3.0
+    cpu.runner.keep_logits = gpu.runner.keep_logits = True
+    for p in ([5, 9, 200, 31, 7], list(range(3, 60))):
+        cpu.add_request(p, sp)
+        gpu.add_request(p, sp)
+    for _ in range(4):
+        cpu.step()
+        gpu.step()
+        lc, lg = cpu.last_step[1].logits, gpu.last_step[1].logits
+        assert _rel_err(lg.cpu(), lc) < 3e-2
+        assert float(lg.abs().max()) <= 3.0 + 1e-3
     _check_status(C)
 
 
