@@ -363,9 +363,17 @@ def cmd_serve(args, passed) -> int:
                 install_suppressed_tokens(other)
                 replicas.append(AsyncEngine(other, name=f"oxidize-batch-engine-{i}"))
             engine = ReplicaRouter(replicas)
+    vision = None
+    if args.mmproj:
+        from ..vision import load_vision_encoder
+
+        vision = load_vision_encoder(args.mmproj, llm.device)
+        if vision.config.projection_dim != llm.cfg.hidden_size:
+            raise SystemExit(f"error: the projector makes {vision.config.projection_dim}-wide tokens, the model wants "
+                             f"{llm.cfg.hidden_size}")
     state = ServerState(engine, args.model_id, GenerationDefaults(max_tokens=args.max_tokens or 512,
                                                                   temperature=args.temperature, top_p=args.top_p,
-                                                                  top_k=args.top_k), chat_template=tpl)
+                                                                  top_k=args.top_k), chat_template=tpl, vision=vision)
     host = args.host if "host" in passed else args.api_host
     port = args.port if "port" in passed else args.api_port
     uvicorn.run(create_app(state), host=host, port=port, log_level="info")

@@ -170,6 +170,8 @@ class LLM:
         the token embeddings at those positions: image tokens of a multimodal prompt (see ``vision.MultimodalPrompt``)."""
         params = params or SamplingParams()
         params.validate()
+        if isinstance(prompt, tuple):  # (token ids, embedding positions, embedding rows), as vision.MultimodalPrompt builds
+            prompt, embed_positions, input_embeds = prompt
         if isinstance(prompt, str):
             if self.tokenizer is None:
                 raise ValueError("text prompt given but the model has no tokenizer; pass token ids")
@@ -495,8 +497,7 @@ class LLM:
         else:
             plist = list(params)
         # a prompt may also be (token ids, embedding positions, embedding rows): see add_request / vision.MultimodalPrompt
-        ids = [self.add_request(p[0], sp, input_embeds=p[2], embed_positions=p[1]) if isinstance(p, tuple)
-               else self.add_request(p, sp) for p, sp in zip(prompts, plist)]
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, plist)]
         final: Dict[str, RequestOutput] = {}
         while self.has_unfinished:
             for ro in self.step():

@@ -33,8 +33,9 @@ PLACEHOLDER_TEXT = "This is a placeholder response: no model is loaded."
 
 class ChatMessage(BaseModel):
     role: str
-    content: str = ""
-    images: Optional[List[str]] = None
+    # a string, or OpenAI-style parts: {"type": "text", "text": ...} / {"type": "image_url", "image_url": {"url": "data:..."}}
+    content: Union[str, List[Dict[str, Any]]] = ""
+    images: Optional[List[str]] = None  # base64 images shown in front of the message's text
 
 
 class _Common(BaseModel):
@@ -88,8 +89,9 @@ class ServerState:
     def __init__(self, engine: Optional[AsyncEngine] = None, model_id: str = "oxidize-default",
                  defaults: Optional[GenerationDefaults] = None, api_keys: Optional[List[str]] = None,
                  limits: Optional[LimitConfig] = None, audit: Optional[AuditLogger] = None,
-                 chat_template: Optional[str] = None):
+                 chat_template: Optional[str] = None, vision=None):
         self.engine = engine
+        self.vision = vision  # vision.VisionEncoder: image parts of chat messages become image tokens
         self.model_id = model_id
         self.defaults = defaults or GenerationDefaults()
         self.api_keys = load_api_keys() if api_keys is None else api_keys
@@ -255,11 +257,67 @@ def create_app(state: Optional[ServerState] = None) -> FastAPI:
             return "{}"
         return PLACEHOLDER_TEXT
 
-    def _chat_prompt(messages: List[ChatMessage]) -> str:
+    IMAGE_MARK = "<image>"
+
+    def _decode_image(src: str):
+        """A data URL or bare base64 → RGB array.  Remote URLs are not fetched."""
+        import base64
+        import io
+
+        from PIL import Image
+
+        if src.startswith("data:"):
+            src = src.split(",", 1)[1] if "," in src else ""
+        elif src.startswith(("http://", "https://", "file:")):
+            raise ValueError("image URLs are not fetched: send the image as a base64 data URL")
+        try:
+            return Image.open(io.BytesIO(base64.b64decode(src, validate=False))).convert("RGB")
+        except Exception as e:  # noqa: BLE001 - any decoder error is the client's
+            raise ValueError(f"cannot decode image: {e}") from None
+
+    def _chat_prompt(messages: List[ChatMessage]):
+        """The rendered prompt: a string, or with images (token ids, embedding positions, embedding rows)."""
         tpl = state.chat_template
         if tpl is None and state.engine is not None:
             tpl = getattr(state.engine.llm, "chat_template", None)
-        return render_chat_template(tpl, [{"role": m.role, "content": m.content} for m in messages], True)
+        flat, images = [], []
+        for m in messages:
+            text = ""
+            for im in m.images or []:
+                images.append(im)
+                text += IMAGE_MARK
+            if isinstance(m.content, str):
+                text += m.content
+            else:
+                for part in m.content:
+                    kind = part.get("type")
+                    if kind == "text":
+                        text += str(part.get("text", ""))
+                    elif kind == "image_url":
+                        url = part.get("image_url")
+                        images.append(url.get("url", "") if isinstance(url, dict) else str(url or ""))
+                        text += IMAGE_MARK
+                    else:
+                        raise ValueError(f"unsupported content part type {kind!r}")
+            flat.append({"role": m.role, "content": text})
+        prompt = render_chat_template(tpl, flat, True)
+        if not images or state.engine is None:
+            return prompt
+        if state.vision is None:
+            raise ValueError("this server was started without a vision tower (--mmproj): image parts cannot be read")
+        from ..vision import ImagePreprocessor, MultimodalPrompt
+
+        enc, llm = state.vision, state.engine.llm
+        pre = ImagePreprocessor(enc.config)
+        pieces = prompt.split(IMAGE_MARK)
+        if len(pieces) != len(images) + 1:
+            raise ValueError("the text contains the image marker itself")
+        mp = MultimodalPrompt().add_text(pieces[0])
+        for src, after in zip(images, pieces[1:]):
+            mp.add_image(enc.encode(pre(_decode_image(src))))
+            mp.add_text(after)
+        st = llm.tokenizer.special_tokens
+        return mp.build(llm.tokenizer, st.unk if st.unk is not None and st.unk >= 0 else 0)
 
     async def _run(req: _Common, prompt: str, chat: bool, request: Request, max_tokens: Optional[int], echo: str = ""):
         rid = ("chatcmpl-" if chat else "cmpl-") + uuid.uuid4().hex[:24]
@@ -365,7 +423,12 @@ def create_app(state: Optional[ServerState] = None) -> FastAPI:
             return bad
         if not req.messages:
             return _error(400, "messages must not be empty")
-        return await _run(req, _chat_prompt(req.messages), True, request, req.max_completion_tokens or req.max_tokens)
+        try:
+            # (image decoding and the vision tower run off the event loop)
+            prompt = await asyncio.get_running_loop().run_in_executor(None, _chat_prompt, req.messages)
+        except ValueError as e:
+            return _error(400, str(e))
+        return await _run(req, prompt, True, request, req.max_completion_tokens or req.max_tokens)
 
     @app.post("/v1/completions")
     async def completions(req: CompletionRequest, request: Request):

@@ -162,3 +162,52 @@ def test_cli_image_prompt(llava, tmp_path):
     assert other.prompt_token_ids == ids
     with pytest.raises(SystemExit):
         image_prompt(llm, None, img, "x")
+
+
+def test_chat_completions_with_image_parts(llava, tmp_path):
+    """OpenAI-style image parts (base64 data URLs) and the `images` field reach the model as image tokens."""
+    import base64
+    import io
+
+    from fastapi.testclient import TestClient
+    from PIL import Image
+
+    from oxidize_b200.engine.async_engine import AsyncEngine
+    from oxidize_b200.models.config import preset
+    from oxidize_b200.serving.app import GenerationDefaults, ServerState, create_app
+    from oxidize_b200.utils.synth import synth_gguf
+
+    _, _, mmproj, _ = llava
+    p = str(tmp_path / "lm.gguf")
+    synth_gguf(p, preset("tiny-llama", arch="qwen2", n_layers=1, vocab_size=300, hidden_size=64, n_heads=4, n_kv_heads=2, head_dim=16,
+                         ffn_size=96), "F32", seed=0)
+    llm = LLM.from_gguf(p, EngineConfig(max_model_len=256, max_num_seqs=2, num_kv_blocks=64), device="cpu")
+    eng = AsyncEngine(llm)
+    try:
+        def b64(seed):
+            buf = io.BytesIO()
+            Image.fromarray(np.random.default_rng(seed).integers(0, 256, (30, 30, 3), dtype=np.uint8)).save(buf, format="PNG")
+            return base64.b64encode(buf.getvalue()).decode()
+
+        def ask(client, content, **extra):
+            return client.post("/v1/chat/completions", json={"model": "m", "max_tokens": 4, "temperature": 0,
+                                                             "messages": [{"role": "user", "content": content, **extra}]})
+
+        with_vision = TestClient(create_app(ServerState(eng, "m", GenerationDefaults(), api_keys=[], vision=load_vision_encoder(mmproj))))
+        parts = [{"type": "text", "text": "what is "}, {"type": "image_url", "image_url": {"url": "data:image/png;base64," + b64(1)}},
+                 {"type": "text", "text": " ?"}]
+        r = with_vision.post("/v1/chat/completions", json={"model": "m", "max_tokens": 4, "temperature": 0,
+                                                          "messages": [{"role": "user", "content": parts}]})
+        assert r.status_code == 200
+        text_only = ask(with_vision, "what is  ?").json()
+        # 16 image tokens entered the prompt (the text around them is tokenized in two pieces, which may cost a token)
+        assert abs(r.json()["usage"]["prompt_tokens"] - text_only["usage"]["prompt_tokens"] - 16) <= 2
+        r2 = ask(with_vision, "describe", images=[b64(2)])
+        assert r2.status_code == 200 and r2.json()["usage"]["prompt_tokens"] > 16
+        assert ask(with_vision, [{"type": "image_url", "image_url": {"url": "https://example.com/x.png"}}]).status_code == 400
+        assert ask(with_vision, [{"type": "image_url", "image_url": {"url": "data:image/png;base64,AAAA"}}]).status_code == 400
+        assert ask(with_vision, [{"type": "audio", "audio": "x"}]).status_code == 400
+        no_vision = TestClient(create_app(ServerState(eng, "m", GenerationDefaults(), api_keys=[])))
+        assert ask(no_vision, parts).status_code == 400 and ask(no_vision, "plain text").status_code == 200
+    finally:
+        eng.shutdown()
