@@ -17,6 +17,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence as Seq
 
+import numpy as np
 import torch
 
 from .. import ops
@@ -292,4 +293,201 @@ class FeatureDraftProposer:
         # the catch-up pass of the next round, now possibly with context)
         for s in seqs:
             self.rollback(s, len(s.all_tokens))
+        return drafts
+
+
+# --------------------------------------------------------------------------- EAGLE-3
+
+
+@dataclass
+class Eagle3Weights:
+    model: ModelConfig
+    extract_layers: List[int]
+    norm_before_residual: bool
+    fc: QTensor
+    layer: LayerWeights  # q / k / v take [norm(embedding) ; norm(g)]: 2 x hidden inputs
+    attn_norm_2: torch.Tensor
+    out_norm: torch.Tensor
+    head: LinearWeight  # [draft vocabulary, hidden]
+    d2t: Optional[torch.Tensor]  # target id = draft id + d2t[draft id]
+    embed: Optional[QTensor]
+
+
+def default_eagle3_extract_layers(n_target_layers: int) -> List[int]:
+    """Early, middle and late layer of the target (the reference's default, ``eagle3.rs:266-276``)."""
+    return [0, 0, 0] if n_target_layers < 4 else [2, n_target_layers // 2, max(0, n_target_layers - 3)]
+
+
+def load_eagle3(path: str, device, act_dtype: torch.dtype, n_target_layers: int, target_hidden: int) -> Eagle3Weights:
+    """EAGLE-3 draft head from a GGUF file (``eagle3.rs:663-770``: ``fc``, ``d2t``, one block ``blk.0.*`` with a second
+    input norm ``attn_norm_2``, ``output_norm``, ``output`` over the draft vocabulary, optional ``token_embd``)."""
+    g = load_gguf(path)
+    spaces = [g.architecture, "eagle3"]
+
+    def get(*names, default=None):
+        for ns in spaces:
+            for n in names:
+                v = g.metadata.get(f"{ns}.{n}")
+                if v is not None:
+                    return v
+        return default
+
+    if "fc.weight" not in g.tensors or "blk.0.attn_norm_2.weight" not in g.tensors:
+        raise ValueError("not an EAGLE-3 draft file: fc.weight / blk.0.attn_norm_2.weight missing")
+    fc = g.tensors["fc.weight"]
+    hidden = int(get("hidden_size", "embedding_length", default=fc.shape[0]))
+    heads = int(get("num_attention_heads", "attention.head_count", default=32))
+    q = g.tensors["blk.0.attn_q.weight"]
+    head_dim = int(get("head_dim", "attention.key_length", default=q.shape[0] // heads))
+    kvh = int(get("num_key_value_heads", "attention.head_count_kv", default=g.tensors["blk.0.attn_k.weight"].shape[0] // head_dim))
+    cfg = ModelConfig(arch="llama", name="eagle3", hidden_size=hidden, n_layers=1, n_heads=heads, n_kv_heads=kvh, head_dim=head_dim,
+                      ffn_size=int(g.tensors["blk.0.ffn_gate.weight"].shape[0]),
+                      rms_eps=float(get("rms_norm_eps", "attention.layer_norm_rms_epsilon", default=1e-5)),
+                      rope_theta=float(get("rope_theta", "rope.freq_base", default=10000.0)),
+                      vocab_size=int(g.tensors["output.weight"].shape[0]))
+    layers = get("extract_layers", "target_layers", default=None)
+    layers = [int(i) for i in layers] if layers is not None else default_eagle3_extract_layers(n_target_layers)
+    if any(i < 0 or i >= n_target_layers for i in layers):
+        raise ValueError(f"extract_layers {layers} outside the target's {n_target_layers} layers")
+    if fc.shape[1] != len(layers) * target_hidden:
+        raise ValueError(f"fc expects {fc.shape[1]} features, the target gives {len(layers)} x {target_hidden}")
+    src = GGUFWeightSource(g, device, act_dtype)
+    d2t = None
+    if src.has("d2t"):
+        d2t = torch.from_numpy(np.asarray(g.tensor("d2t")).astype(np.int64).reshape(-1).copy()).to(src.device)
+    return Eagle3Weights(cfg, layers, bool(get("norm_before_residual", default=False)), src.matrix("fc.weight"),
+                         _load_layer(src, cfg, 0, 0, 1, 0, 1), src.vector("blk.0.attn_norm_2.weight"),
+                         src.vector("output_norm.weight"), LinearWeight([src.matrix("output.weight")]), d2t,
+                         src.matrix("token_embd.weight") if src.has("token_embd.weight") else None)
+
+
+@dataclass
+class _EagleState:
+    blocks: List[int] = field(default_factory=list)
+    first: int = -1  # index (in the sequence) of the first token that has a cache entry
+    entries: int = 0
+
+
+class Eagle3Proposer:
+    """EAGLE-3 drafting (``eagle3.rs:444-660``): ``g = fc(target features)`` at the last verified position; every draft step
+    feeds ``[norm(embed(token)) ; norm_2(g)]`` to one decoder block whose output becomes the next step's ``g`` and, through
+    ``output_norm`` and the draft head, the next token (mapped to the target vocabulary by ``d2t``).  The block's cache holds
+    the tokens fed so far in this and earlier rounds (verified ones only survive a round); the prompt itself is not
+    replayed through the draft."""
+
+    def __init__(self, weights: Eagle3Weights, target_model, k: int, max_seqs: int, max_model_len: int):
+        self.k, self.w, self.m = k, weights, target_model
+        cfg = weights.model
+        dev = target_model.device
+        self.cfg, self.dev, self.act = cfg, dev, target_model.act_dtype
+        if weights.embed is None and cfg.hidden_size != target_model.cfg.hidden_size:
+            raise ValueError("a draft head without its own embedding table must have the target's hidden size")
+        self.embed_table = weights.embed if weights.embed is not None else target_model.w.embed
+        target_model.capture_layers = list(weights.extract_layers)
+        self.rope = RopeState(opref.rope_inv_freq(cfg.rotary_dim, cfg.rope_theta, None, device=dev), cfg.rope_pairing, 1.0,
+                              cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
+        self.scale = cfg.head_dim ** -0.5
+        per_seq = (max_model_len + PAGE - 1) // PAGE + 1
+        kvd = "bf16" if dev.type == "cuda" else "f32"
+        self.kv = KVCache(KVCacheSpec(1, cfg.n_kv_heads, cfg.head_dim, PAGE, kvd), max_seqs * per_seq, dev)
+        self.pool = make_block_pool(max_seqs * per_seq, PAGE, enable_prefix_cache=False)
+        self.max_blocks = per_seq
+        self.state: Dict[int, _EagleState] = {}
+        self.features: Dict[int, torch.Tensor] = {}
+        self.draft_logits: Dict[int, torch.Tensor] = {}
+        self.vocab = target_model.cfg.vocab_size
+
+    def observe_features(self, seq: Sequence, feats: torch.Tensor) -> None:
+        self.features[seq.seq_id] = feats
+
+    def release(self, seq: Sequence) -> None:
+        st = self.state.pop(seq.seq_id, None)
+        if st is not None:
+            self.pool.release_all(st.blocks)
+        self.features.pop(seq.seq_id, None)
+        self.draft_logits.pop(seq.seq_id, None)
+
+    def rollback(self, seq: Sequence, n_valid_tokens: int) -> None:
+        st = self.state.get(seq.seq_id)
+        if st is not None and st.first >= 0:
+            st.entries = max(0, min(st.entries, n_valid_tokens - st.first))
+
+    def _step(self, seqs: Seq[Sequence], toks: List[int], pos: List[int], g: torch.Tensor):
+        """One decoder step for one token per sequence; returns (hidden [B, h], logits over the draft vocabulary)."""
+        cfg, dev, lw = self.cfg, self.dev, self.w.layer
+        i32 = dict(dtype=torch.int32, device=dev)
+        B = len(seqs)
+        slots, lens = [], []
+        bt = torch.zeros(B, self.max_blocks, **i32)
+        for i, s in enumerate(seqs):
+            st = self.state[s.seq_id]
+            while len(st.blocks) * PAGE < st.entries + 1:
+                st.blocks.append(self.pool.allocate())
+            slots.append(st.blocks[st.entries // PAGE] * PAGE + st.entries % PAGE)
+            st.entries += 1
+            lens.append(st.entries)
+            bt[i, : len(st.blocks)] = torch.tensor(st.blocks, **i32)
+        tok_t, pos_t = torch.tensor(toks, **i32), torch.tensor(pos, **i32)
+        e = ops.rmsnorm(ops.embed(tok_t, self.embed_table, self.act), lw.attn_norm, cfg.rms_eps)
+        gn = ops.rmsnorm(g, self.w.attn_norm_2, cfg.rms_eps)
+        residual = gn if self.w.norm_before_residual else g
+        qkv = ops.linear(torch.cat([e, gn], dim=-1), lw.wqkv)
+        q = ops.qk_rope_kv_write(qkv, pos_t, torch.tensor(slots, **i32), self.kv, 0, self.rope, None, None, cfg.rms_eps)
+        meta = BatchMeta(tok_t, pos_t, torch.tensor(slots, **i32), torch.arange(B + 1, **i32), torch.tensor(lens, **i32), bt,
+                         None, 1, max(lens), B)
+        attn = ops.paged_attention(q.contiguous(), self.kv, 0, meta, self.scale, 0)
+        hidden = ops.linear(attn.reshape(B, -1), lw.wo) + residual
+        h2 = ops.rmsnorm(hidden, lw.ffn_norm, cfg.rms_eps)
+        hidden = hidden + ops.linear(ops.silu_mul(ops.linear(h2, lw.w_gate_up)), lw.w_down)
+        logits = ops.linear(ops.rmsnorm(hidden, self.w.out_norm, cfg.rms_eps), self.w.head).float()
+        return hidden, logits
+
+    def _to_target_vocab(self, draft_ids: torch.Tensor) -> torch.Tensor:
+        return draft_ids if self.w.d2t is None else draft_ids + self.w.d2t[draft_ids.long()].to(draft_ids.dtype)
+
+    def propose(self, seqs: List[Sequence]) -> Dict[int, List[int]]:
+        drafts: Dict[int, List[int]] = {s.seq_id: [] for s in seqs}
+        ready = [s for s in seqs if s.seq_id in self.features]
+        if not ready:
+            return drafts
+        g = ops.linear(torch.stack([self.features[s.seq_id] for s in ready]).to(self.act), self.w.fc)
+        for s in ready:
+            st = self.state.setdefault(s.seq_id, _EagleState())
+            n = len(s.all_tokens)
+            if st.first < 0 or st.first + st.entries < n - 1 - 1:
+                # nothing cached yet, or more than one verified token was never fed: start the cache at the newest token
+                st.first, st.entries = n - 1, 0
+        # a verified token that was never fed (the last draft of a fully accepted round) goes in first, with this round's g
+        gap = [s for s in ready if self.state[s.seq_id].first + self.state[s.seq_id].entries == len(s.all_tokens) - 2]
+        if gap:
+            idx = [ready.index(s) for s in gap]
+            self._step(gap, [s.all_tokens[-2] for s in gap], [len(s.all_tokens) - 2 for s in gap], g[idx])
+        toks = [s.all_tokens[-1] for s in ready]
+        pos = [len(s.all_tokens) - 1 for s in ready]
+        sampled = [not s.params.is_greedy for s in ready]
+        rows: Dict[int, List[torch.Tensor]] = {s.seq_id: [] for s, smp in zip(ready, sampled) if smp}
+        for _ in range(self.k):
+            g, logits = self._step(ready, toks, pos, g)
+            nxt = torch.argmax(logits, dim=-1)
+            if any(sampled):
+                from .sampler import probs_from_logits
+
+                for i, s in enumerate(ready):
+                    if sampled[i]:
+                        full = torch.full((self.vocab,), float("-inf"))
+                        ids = self._to_target_vocab(torch.arange(logits.shape[1], device=self.dev)).cpu()
+                        full[ids] = logits[i].cpu()
+                        p = torch.from_numpy(probs_from_logits(full.numpy(), s.params.temperature))
+                        t = int(torch.searchsorted(torch.cumsum(p, 0), torch.tensor(s.rng.next())).clamp(max=p.numel() - 1))
+                        nxt[i] = int((ids == t).nonzero()[0]) if bool((ids == t).any()) else nxt[i]
+                        rows[s.seq_id].append(full)
+            tgt = self._to_target_vocab(nxt)
+            for i, s in enumerate(ready):
+                drafts[s.seq_id].append(int(tgt[i]))
+            toks = [int(t) for t in tgt]
+            pos = [p + 1 for p in pos]
+        for sid, r in rows.items():
+            self.draft_logits[sid] = torch.stack(r).to(self.dev)
+        for s in ready:
+            self.rollback(s, len(s.all_tokens))  # drafted tokens are not verified yet
         return drafts

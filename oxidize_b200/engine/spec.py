@@ -417,6 +417,16 @@ def attach_speculation(llm, draft_model_path: Optional[str], k: int = 4, use_mtp
         from ..models.weights import load_weights
 
         g = load_gguf(draft_model_path)
+        if "fc.weight" in g.tensors and "blk.0.attn_norm_2.weight" in g.tensors:
+            # an EAGLE-3 head: one block fed with [embedding ; fused target features]
+            from .feature_draft import Eagle3Proposer, load_eagle3
+
+            if llm.config.tp_size > 1 or llm.config.pp_size > 1:
+                raise ValueError("hidden-conditioned drafts run with single-rank engines")
+            act = torch.bfloat16 if llm.device.type == "cuda" else torch.float32
+            ew = load_eagle3(draft_model_path, llm.device, act, llm.cfg.n_layers, llm.cfg.hidden_size)
+            llm.spec = SpecDecoder(Eagle3Proposer(ew, llm.model, k, c.max_num_seqs, c.max_model_len), k)
+            return llm.spec
         if any(n in g.tensors for n in ("fc.weight", "dflash_fc.weight", "model.fc.weight")):
             # a hidden-conditioned draft (DFlash-style): it reads the target's hidden states besides the tokens
             from .feature_draft import FeatureDraftProposer, load_feature_draft

@@ -177,3 +177,121 @@ def test_speculation_with_a_feature_draft_is_exact(setup, temperature):
         attach_speculation(llm2, draft, k=3)
         b = [o.token_ids for o in llm2.generate(prompts, sps)]
         assert a == b and all(len(x) == 16 and all(0 <= t < 300 for t in x) for x in a)
+
+
+# --------------------------------------------------------------------------- EAGLE-3
+
+DV = 100  # draft vocabulary; target id = 3 * draft id
+
+
+def _eagle_file(path, seed=1, scale=0.15, norm_before_residual=False):
+    rng = np.random.default_rng(seed)
+    w = GGUFWriter(path, arch="eagle3")
+    U = GGUFValueType.UINT32
+    for k, v in (("hidden_size", H), ("num_attention_heads", HEADS), ("num_key_value_heads", KV), ("head_dim", HD)):
+        w.add(f"eagle3.{k}", v, U)
+    w.add("eagle3.extract_layers", [0, 1, 2])
+    w.add("eagle3.norm_before_residual", bool(norm_before_residual))
+    t = {}
+
+    def mat(name, o, i):
+        t[name] = (rng.standard_normal((o, i)) * scale).astype(np.float32)
+        w.add_tensor(name, t[name], (o, i), "F32")
+
+    def vec(name, n):
+        t[name] = (1.0 + 0.2 * rng.standard_normal(n)).astype(np.float32)
+        w.add_tensor(name, t[name], (n,), "F32")
+
+    mat("fc.weight", H, 3 * H)
+    w.add_tensor("d2t", (2 * np.arange(DV)).astype(np.int64), (DV,), "I64")
+    p = "blk.0"
+    vec(f"{p}.attn_norm.weight", H); vec(f"{p}.attn_norm_2.weight", H); vec(f"{p}.ffn_norm.weight", H)
+    mat(f"{p}.attn_q.weight", HEADS * HD, 2 * H); mat(f"{p}.attn_k.weight", KV * HD, 2 * H); mat(f"{p}.attn_v.weight", KV * HD, 2 * H)
+    mat(f"{p}.attn_output.weight", H, HEADS * HD)
+    mat(f"{p}.ffn_gate.weight", FFN, H); mat(f"{p}.ffn_up.weight", FFN, H); mat(f"{p}.ffn_down.weight", H, FFN)
+    vec("output_norm.weight", H)
+    mat("output.weight", DV, H)
+    w.write()
+    return {k: torch.from_numpy(v) for k, v in t.items()}
+
+
+def _eagle_dense(t, embed, tokens, first_pos, feats, norm_before_residual=False):
+    """eagle3.rs:444-660 in plain torch: g = fc(features); per token [norm(embed) ; norm_2(g)] -> block -> g."""
+    inv = opref.rope_inv_freq(HD, 10000.0)
+    g = t["fc.weight"] @ feats
+    ks, vs, out = [], [], []
+    p = "blk.0"
+    for j, tok in enumerate(tokens):
+        pos = torch.tensor([first_pos + j])
+        e = _norm(embed[tok], t[f"{p}.attn_norm.weight"])
+        gn = _norm(g, t[f"{p}.attn_norm_2.weight"])
+        x2 = torch.cat([e, gn])
+        q = opref.apply_rope((t[f"{p}.attn_q.weight"] @ x2).reshape(1, HEADS, HD), pos, inv)[0]
+        ks.append(opref.apply_rope((t[f"{p}.attn_k.weight"] @ x2).reshape(1, KV, HD), pos, inv)[0])
+        vs.append((t[f"{p}.attn_v.weight"] @ x2).reshape(KV, HD))
+        K, V = torch.stack(ks), torch.stack(vs)
+        s = torch.einsum("kgd,lkd->kgl", q.reshape(KV, HEADS // KV, HD), K) * HD ** -0.5
+        o = torch.einsum("kgl,lkd->kgd", torch.softmax(s, -1), V).reshape(HEADS * HD)
+        hidden = t[f"{p}.attn_output.weight"] @ o + (gn if norm_before_residual else g)
+        n2 = _norm(hidden, t[f"{p}.ffn_norm.weight"])
+        hidden = hidden + t[f"{p}.ffn_down.weight"] @ (torch.nn.functional.silu(t[f"{p}.ffn_gate.weight"] @ n2) * (t[f"{p}.ffn_up.weight"] @ n2))
+        g = hidden
+        out.append((hidden, t["output.weight"] @ _norm(hidden, t["output_norm.weight"])))
+    return out
+
+
+@pytest.mark.parametrize("nbr", [False, True])
+def test_eagle3_steps_match_the_dense_statement(setup, tmp_path, nbr):
+    from oxidize_b200.engine.feature_draft import Eagle3Proposer, _EagleState, load_eagle3
+
+    target, _, _ = setup
+    path = str(tmp_path / "eagle.gguf")
+    t = _eagle_file(path, norm_before_residual=nbr)
+    llm = LLM.from_gguf(target, EngineConfig(max_model_len=128, max_num_seqs=4, num_kv_blocks=64), device="cpu")
+    ew = load_eagle3(path, "cpu", torch.float32, 3, H)
+    assert ew.extract_layers == [0, 1, 2] and ew.norm_before_residual == nbr and ew.model.vocab_size == DV and ew.embed is None
+    prop = Eagle3Proposer(ew, llm.model, 3, 4, 128)
+    assert llm.model.capture_layers == [0, 1, 2]
+    embed = llm.model.w.embed.dense_cache()
+    gen = torch.Generator().manual_seed(0)
+    fa, fb = torch.randn(3 * H, generator=gen), torch.randn(3 * H, generator=gen)
+    a, b = Sequence([1] * 20 + [41], SamplingParams(temperature=0.0)), Sequence([2, 3, 57], SamplingParams(temperature=0.0))
+    for s, pos0 in ((a, 20), (b, 2)):
+        prop.state[s.seq_id] = _EagleState(first=pos0)
+    g = torch.stack([t["fc.weight"] @ fa, t["fc.weight"] @ fb])
+    g1, l1 = prop._step([a, b], [41, 57], [20, 2], g)
+    g2, l2 = prop._step([a, b], [77, 78], [21, 3], g1)
+    wa = _eagle_dense(t, embed, [41, 77], 20, fa, nbr)
+    wb = _eagle_dense(t, embed, [57, 78], 2, fb, nbr)
+    assert torch.allclose(g1[0], wa[0][0], atol=2e-5) and torch.allclose(l2[0], wa[1][1], atol=2e-5)
+    assert torch.allclose(g2[1], wb[1][0], atol=2e-5) and torch.allclose(l1[1], wb[0][1], atol=2e-5)
+    assert prop._to_target_vocab(torch.tensor([0, 5, 99])).tolist() == [0, 15, 297]
+    with pytest.raises(ValueError):
+        load_eagle3(path, "cpu", torch.float32, 2, H)  # layer 2 of a 2-layer target
+    with pytest.raises(ValueError):
+        load_eagle3(path, "cpu", torch.float32, 3, H + 8)
+
+
+def test_speculation_with_an_eagle3_head_is_exact(setup, tmp_path):
+    from oxidize_b200.engine.feature_draft import Eagle3Proposer
+
+    target, _, _ = setup
+    path = str(tmp_path / "eagle.gguf")
+    _eagle_file(path)
+    ec = dict(max_model_len=128, max_num_seqs=4, num_kv_blocks=64, prefill_chunk_size=32, max_num_batched_tokens=64)
+    prompts = [[5, 9, 200, 31, 7], list(range(3, 40))]
+    sp = SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True)
+    plain = [o.token_ids for o in LLM.from_gguf(target, EngineConfig(**ec), device="cpu").generate(prompts, sp)]
+    llm = LLM.from_gguf(target, EngineConfig(**ec), device="cpu")
+    spec = attach_speculation(llm, path, k=3)
+    assert isinstance(spec.proposer, Eagle3Proposer)
+    assert [o.token_ids for o in llm.generate(prompts, sp)] == plain
+    assert spec.stats.proposed > 0 and not spec.proposer.state
+    # sampled requests: reproducible with a seed, drafts come from the draft vocabulary's image in the target's
+    sps = SamplingParams(temperature=0.8, max_tokens=12, ignore_eos=True, seed=5)
+    llm2 = LLM.from_gguf(target, EngineConfig(**ec), device="cpu")
+    attach_speculation(llm2, path, k=3)
+    a = [o.token_ids for o in llm2.generate(prompts, sps)]
+    llm3 = LLM.from_gguf(target, EngineConfig(**ec), device="cpu")
+    attach_speculation(llm3, path, k=3)
+    assert a == [o.token_ids for o in llm3.generate(prompts, sps)] and all(len(x) == 12 for x in a)
