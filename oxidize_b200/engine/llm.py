@@ -108,7 +108,8 @@ class LLM:
                                                    c.policy, c.enable_prefix_cache, c.max_model_len, uniform_window), self.pool)
         self.runner = ModelRunner(self.model, self.kv, max(c.max_num_batched_tokens, c.max_num_seqs), c.max_num_seqs,
                                   c.max_model_len, c.cuda_graphs and not _profiler.PROFILE and not _profiler.TRACE_FWD
-                                  and isinstance(weights.layers, list))  # a captured graph would pin evicted layers' addresses
+                                  and isinstance(weights.layers, list)  # a captured graph would pin evicted layers' addresses
+                                  and not self.cfg.is_mla)  # latent attention's device step sizes its gather on the host
         self.eos_token_id = c.eos_token_id
         if self.eos_token_id is None and tokenizer is not None:
             self.eos_token_id = tokenizer.special_tokens.eos

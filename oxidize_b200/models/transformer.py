@@ -124,6 +124,7 @@ class Transformer:
             # One cached row per token, shared by all heads: the normalised latent followed by the rotary key.
             self.n_kv_local = 1
             self.kv_head_dim = cfg.kv_lora_rank + cfg.rotary_dim
+            self.latent_statement = dev.type == "cuda"  # attention over latent rows as batched torch products
             self.rope.n_kv_heads = 1
             if cfg.rope_scaling.type == "yarn" and cfg.rope_scaling.factor > 1:
                 # DeepSeek's YaRN: the magnitude correction goes into the softmax scale (squared: it would have
@@ -133,10 +134,6 @@ class Transformer:
                 m = 1.0 + cfg.yarn_log_multiplier * math.log(cfg.rope_scaling.factor)
                 self.rope.mscale = 1.0
                 self.attn_scale *= m * m
-            if dev.type == "cuda":
-                raise NotImplementedError("latent attention (DeepSeek-V2/V3) is implemented on the CPU path only: the "
-                                          "attention kernel has 64- and 128-wide heads, the latent cache row is "
-                                          f"{self.kv_head_dim} wide")
         self._fuse_qkv_rope = dev.type == "cuda" and fuse_qkv_rope
         # (load-time re-layouts walk every layer: not for a model that streams its layers from the file)
         streamed = not isinstance(weights.layers, list)
@@ -260,9 +257,14 @@ class Transformer:
         q_lat = torch.einsum("thn,hnc->thc", q[:, :, :nope].float(), m.w_uk.float()).to(x.dtype)
         row = torch.cat([latent[:, None, :], k_pe], dim=-1)  # [T, 1, c + rot]
         opref.kv_write(kv, layer, row, row, meta.slot_mapping)
-        o = ops.paged_attention(torch.cat([q_lat, q_pe], dim=-1), kv, layer, meta, self.attn_scale,
-                                cfg.layer_sliding_window(self.w.first_layer + layer))
-        out = torch.einsum("thc,hvc->thv", o[:, :, :c].float(), m.w_uv.float()).to(x.dtype)
+        qq = torch.cat([q_lat, q_pe], dim=-1)
+        if self.latent_statement:
+            # the attention kernel has 64- and 128-wide heads; over the (kv_lora + rope)-wide latent rows the attention
+            # step runs as batched matrix products (torch) on the device
+            o = opref.latent_attention(qq, kv, layer, meta, self.attn_scale, c)
+        else:
+            o = ops.paged_attention(qq, kv, layer, meta, self.attn_scale, 0)[:, :, :c]
+        out = torch.einsum("thc,hvc->thv", o.float(), m.w_uv.float()).to(x.dtype)
         return self.comm.linear_allreduce(out.reshape(T, -1), lw.wo)
 
     def _attention(self, lw: LayerWeights, layer: int, x: torch.Tensor, meta: BatchMeta, kv) -> torch.Tensor:

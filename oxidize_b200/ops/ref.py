@@ -235,6 +235,48 @@ def paged_attention(q: torch.Tensor, kv, layer: int, meta, scale: float, sliding
     return out.to(q.dtype)
 
 
+def latent_attention(q: torch.Tensor, kv, layer: int, meta, scale: float, latent_dim: int) -> torch.Tensor:
+    """Multi-query attention over latent cache rows (DeepSeek latent attention in absorbed form).
+
+    q: [T, H, latent_dim + rope]; the cache holds one row of that width per token, shared by all heads, and the value of
+    a row is its first ``latent_dim`` entries.  Returns [T, H, latent_dim].  A decode step (one row per sequence) is one
+    batched gather + two batched matrix products over all sequences; other steps go sequence by sequence.  Device-agnostic
+    torch: this is what runs on a GPU too, where the attention kernel has no 576-wide head."""
+    T, H, D = q.shape
+    B = int(meta.seq_lens.shape[0])
+    page = kv.page_size
+    quant = kv.dtype_name in ("q8", "q4")
+
+    def rows_of(blocks: torch.Tensor) -> torch.Tensor:  # [..., nb] block ids -> [..., nb * page, D] float32 key rows
+        d = kv.data[layer][blocks]  # [..., nb, 1, 2, page, D or packed]
+        if quant:
+            d = kv_dequantize(d, kv.scales[layer][blocks], 8 if kv.dtype_name == "q8" else 4)
+        d = d[..., 0, 0, :, :].float()
+        return d.reshape(*d.shape[:-3], d.shape[-3] * page, d.shape[-1])
+
+    if T == B and meta.max_query_len == 1:
+        max_len = int(meta.max_seq_len) or int(meta.seq_lens.max())
+        nb = (max_len + page - 1) // page
+        K = rows_of(meta.block_tables[:, :nb].long())[:, :max_len]  # [B, L, D]
+        s = torch.einsum("bhd,bld->bhl", q.float(), K) * scale
+        live = torch.arange(max_len, device=q.device)[None, :] < meta.seq_lens.long()[:, None]
+        s = s.masked_fill(~live[:, None, :], float("-inf"))
+        return torch.einsum("bhl,blc->bhc", torch.softmax(s, dim=-1), K[..., :latent_dim]).to(q.dtype)
+    out = torch.zeros(T, H, latent_dim, dtype=torch.float32, device=q.device)
+    qs, sl = meta.query_start.tolist(), meta.seq_lens.tolist()
+    for b in range(B):
+        t0, t1 = qs[b], qs[b + 1]
+        n, L = t1 - t0, sl[b]
+        if n == 0:
+            continue
+        K = rows_of(meta.block_tables[b, : (L + page - 1) // page].long())[:L]  # [L, D]
+        s = torch.einsum("qhd,ld->hql", q[t0:t1].float(), K) * scale
+        causal = torch.arange(L, device=q.device)[None, :] <= torch.arange(L - n, L, device=q.device)[:, None]
+        s = s.masked_fill(~causal[None], float("-inf"))
+        out[t0:t1] = torch.einsum("hql,lc->qhc", torch.softmax(s, dim=-1), K[:, :latent_dim])
+    return out.to(q.dtype)
+
+
 # --------------------------------------------------------------------------- MoE routing
 
 

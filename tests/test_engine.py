@@ -822,3 +822,54 @@ def test_pages_outside_a_uniform_attention_window_return_to_the_pool(tmp_path):
     synth_gguf(mixed, preset("tiny-llama", n_layers=2, vocab_size=300, hidden_size=64, n_heads=4, n_kv_heads=2, head_dim=16,
                              ffn_size=96, sliding_window=24, sliding_window_pattern=2), "F32", seed=5)
     assert LLM.from_gguf(mixed, EngineConfig(**ec), device="cpu").scheduler.config.attention_window == 0
+
+
+def test_latent_attention_batched_statement_matches_the_paged_reference():
+    """ops.ref.latent_attention (what a GPU runs for DeepSeek latent attention) against the generic paged reference on
+    the same cache: decode steps (batched path), chunked prefill rows, f32 and q8 caches."""
+    from oxidize_b200.engine.kv_pool import KVCache, KVCacheSpec
+    from oxidize_b200.models.transformer import BatchMeta
+    from oxidize_b200.ops import ref as opref
+
+    torch.manual_seed(0)
+    c, r, H, page = 64, 32, 4, 16
+    for kvd, tol in (("f32", 1e-5), ("q8", 1e-5)):
+        kv = KVCache(KVCacheSpec(1, 1, c + r, page, kvd), 16, "cpu")
+        lens = [37, 5, 64]
+        tables = torch.tensor([[0, 1, 2, 0], [3, 0, 0, 0], [4, 5, 6, 7]], dtype=torch.int32)
+        for b, L in enumerate(lens):
+            rows = torch.randn(L, 1, c + r)
+            slots = torch.tensor([int(tables[b, p // page]) * page + p % page for p in range(L)], dtype=torch.int32)
+            opref.kv_write(kv, 0, rows, rows, slots)
+        i32 = dict(dtype=torch.int32)
+        # decode: one row per sequence
+        q = torch.randn(3, H, c + r)
+        meta = BatchMeta(None, None, None, torch.tensor([0, 1, 2, 3], **i32), torch.tensor(lens, **i32), tables, None, 1, 64, 3)
+        want = opref.paged_attention(q, kv, 0, meta, 0.1)[:, :, :c]
+        assert torch.allclose(opref.latent_attention(q, kv, 0, meta, 0.1, c), want, atol=tol)
+        # mixed step: 7 prefill rows of sequence 0, 1 row of sequence 1, 3 rows of sequence 2
+        q = torch.randn(11, H, c + r)
+        meta = BatchMeta(None, None, None, torch.tensor([0, 7, 8, 11], **i32), torch.tensor(lens, **i32), tables, None, 7, 64, 3)
+        want = opref.paged_attention(q, kv, 0, meta, 0.1)[:, :, :c]
+        assert torch.allclose(opref.latent_attention(q, kv, 0, meta, 0.1, c), want, atol=tol)
+
+
+def test_latent_attention_model_gives_the_same_logits_through_the_batched_statement(tmp_path):
+    """The DeepSeek model path a GPU takes (ops.ref.latent_attention inside the layer) against the CPU's paged reference:
+    prefill chunks and decode steps, two sequences."""
+    path = str(tmp_path / "ds.gguf")
+    cfg = preset("deepseek-v3", n_layers=3, vocab_size=512, hidden_size=64, n_heads=4, n_kv_heads=4, head_dim=48, rope_dim=32,
+                 qk_nope_dim=16, v_head_dim=24, kv_lora_rank=32, q_lora_rank=48, ffn_size=96, n_experts=8, n_experts_used=2,
+                 expert_ffn_size=48, expert_group_count=4, expert_group_used_count=2, leading_dense_blocks=1,
+                 shared_expert_ffn_size=48, context_length=4096)
+    synth_gguf(path, cfg, "F32", seed=0, norm_jitter=0.1)
+    ec = dict(max_model_len=128, max_num_seqs=4, num_kv_blocks=64, prefill_chunk_size=16, max_num_batched_tokens=32)
+    prompts = [[5, 9, 200, 31, 7], list(range(3, 60))]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    outs = []
+    for statement in (False, True):
+        for kvd in ("f32", "q8"):
+            llm = LLM.from_gguf(path, EngineConfig(**ec, kv_cache_dtype=kvd), device="cpu")
+            llm.model.latent_statement = statement
+            outs.append([o.token_ids for o in llm.generate(prompts, sp)])
+    assert outs[0] == outs[2] and outs[1] == outs[3]

@@ -142,3 +142,27 @@ def test_hidden_conditioned_draft_on_the_device(tmp_path):
         same = next((i for i, (x, y) in enumerate(zip(a, b)) if x != y), len(a))
         assert same >= 8, (a, b)
     _status_ok()
+
+
+def test_latent_attention_model_on_the_device(tmp_path):
+    """DeepSeek-style latent attention + sigmoid group-limited routing + shared expert on the device: teacher-forced logits
+    against the CPU path over prefill and short continuation steps."""
+    path = str(tmp_path / "ds.gguf")
+    cfg = preset("deepseek-v3", n_layers=3, vocab_size=512, hidden_size=256, n_heads=4, n_kv_heads=4, head_dim=96, rope_dim=32,
+                 qk_nope_dim=64, v_head_dim=64, kv_lora_rank=64, q_lora_rank=128, ffn_size=512, n_experts=8, n_experts_used=2,
+                 expert_ffn_size=128, expert_group_count=4, expert_group_used_count=2, leading_dense_blocks=1,
+                 shared_expert_ffn_size=128, context_length=4096)
+    synth_gguf(path, cfg, "BF16", seed=0, norm_jitter=0.1)
+    cpu = LLM.from_gguf(path, EngineConfig(**EC), device="cpu")
+    gpu = LLM.from_gguf(path, EngineConfig(**EC), device="cuda")
+    assert gpu.model.latent_statement and gpu.kv.spec.head_dim == 96 and gpu.kv.spec.n_kv_heads == 1
+    prompts = [list(p) for p in PROMPTS]
+    for _ in range(3):
+        lc = torch.from_numpy(cpu.next_token_logits(prompts))
+        lg = torch.from_numpy(gpu.next_token_logits(prompts))
+        assert _rel(lg, lc) < 4e-2
+        prompts = [p + [int(lc[i].argmax())] for i, p in enumerate(prompts)]
+    # free-running greedy decode on the device (decode steps take the batched path)
+    out = gpu.generate(PROMPTS, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    assert all(len(o.token_ids) == 8 for o in out)
+    _status_ok()
