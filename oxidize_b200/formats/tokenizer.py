@@ -517,11 +517,34 @@ def _expand_vars(body: str, msg: Mapping[str, str], extra: Mapping[str, str]) ->
     return _VAR_RE.sub(sub, body)
 
 
+def _render_jinja(template: str, messages, add_generation_prompt: bool, bos_token: str, eos_token: str) -> Optional[str]:
+    """The template through a sandboxed Jinja environment set up the way checkpoints expect (``trim_blocks``,
+    ``lstrip_blocks``, a ``raise_exception`` helper); None when Jinja is missing or the template does not render."""
+    try:
+        import jinja2
+        from jinja2.sandbox import ImmutableSandboxedEnvironment
+    except ImportError:
+        return None
+
+    def raise_exception(message):
+        raise jinja2.TemplateError(message)
+
+    try:
+        env = ImmutableSandboxedEnvironment(trim_blocks=True, lstrip_blocks=True)
+        env.globals["raise_exception"] = raise_exception
+        return env.from_string(template).render(messages=[dict(m) for m in messages], add_generation_prompt=add_generation_prompt,
+                                                bos_token=bos_token, eos_token=eos_token)
+    except Exception:  # noqa: BLE001 - syntax the sandbox refuses, a role order the template rejects ...
+        return None
+
+
 def render_chat_template(template: Optional[str], messages: Sequence[Mapping[str, str]],
-                         add_generation_prompt: bool = True, bos_token: str = "", eos_token: str = "") -> str:
-    """Render ``messages`` with the reference's two-rule contract: any template mentioning
-    ``<|im_start|>`` produces canonical ChatML; otherwise the body of the message loop is
-    expanded once per message by plain string substitution."""
+                         add_generation_prompt: bool = True, bos_token: str = "", eos_token: str = "",
+                         jinja: bool = True) -> str:
+    """Render ``messages``.  Any template mentioning ``<|im_start|>`` produces canonical ChatML (the reference's first
+    rule).  Other templates are rendered by Jinja when it is available (real checkpoints' templates use variables, nested
+    conditions and filters); where that fails, or with ``jinja=False``, the reference's second rule applies: the body of the
+    message loop is expanded once per message by plain string substitution (``format/tokenizer.rs:315-452``)."""
     if template is None:
         template = CHATML_SENTINEL
     if CHATML_SENTINEL in template:
@@ -529,6 +552,10 @@ def render_chat_template(template: Optional[str], messages: Sequence[Mapping[str
         if add_generation_prompt:
             out += "<|im_start|>assistant\n"
         return out
+    if jinja and ("{%" in template or "{{" in template):
+        rendered = _render_jinja(template, messages, add_generation_prompt, bos_token, eos_token)
+        if rendered is not None:
+            return rendered
     extra = {"bos_token": bos_token, "eos_token": eos_token}
     m = _FOR_RE.search(template)
     if not m:

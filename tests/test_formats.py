@@ -238,6 +238,28 @@ def test_chat_templates():
     assert T.render_chat_template(llama3, msgs[1:], False).endswith("<|eot_id|>")
     assert T.chat_template_from_metadata({}, "qwen3") == T.CHATML_SENTINEL
     assert T.chat_template_from_metadata({}, "llama") is None
+    # both renderers agree on that template; the plain-substitution one is the fallback
+    assert T.render_chat_template(llama3, msgs, True, jinja=False) == T.render_chat_template(llama3, msgs, True)
+    # the template Llama-3 checkpoints actually ship: a variable, a loop index, a filter, set statements
+    real = ("{% set loop_messages = messages %}{% for message in loop_messages %}{% set content = '<|start_header_id|>' + "
+            "message['role'] + '<|end_header_id|>\n\n'+ message['content'] | trim + '<|eot_id|>' %}{% if loop.index0 == 0 %}"
+            "{% set content = bos_token + content %}{% endif %}{{ content }}{% endfor %}{% if add_generation_prompt %}"
+            "{{ '<|start_header_id|>assistant<|end_header_id|>\n\n' }}{% endif %}")
+    out = T.render_chat_template(real, [{"role": "system", "content": " be brief "}, {"role": "user", "content": "hi"}], True,
+                                 bos_token="<|begin_of_text|>")
+    assert out == ("<|begin_of_text|><|start_header_id|>system<|end_header_id|>\n\nbe brief<|eot_id|><|start_header_id|>user"
+                   "<|end_header_id|>\n\nhi<|eot_id|><|start_header_id|>assistant<|end_header_id|>\n\n")
+    # Mistral-style: roles must alternate (the template raises otherwise -> falls back), [INST] wrapping
+    mistral = ("{{ bos_token }}{% for message in messages %}{% if (message['role'] == 'user') != (loop.index0 % 2 == 0) %}"
+               "{{ raise_exception('Conversation roles must alternate user/assistant/user/assistant/...') }}{% endif %}"
+               "{% if message['role'] == 'user' %}{{ '[INST] ' + message['content'] + ' [/INST]' }}{% elif message['role'] == "
+               "'assistant' %}{{ message['content'] + eos_token}}{% endif %}{% endfor %}")
+    conv = [{"role": "user", "content": "a"}, {"role": "assistant", "content": "b"}, {"role": "user", "content": "c"}]
+    assert T.render_chat_template(mistral, conv, True, "<s>", "</s>") == "<s>[INST] a [/INST]b</s>[INST] c [/INST]"
+    assert "a" in T.render_chat_template(mistral, [{"role": "assistant", "content": "a"}], True)  # rejected by the template: fallback
+    # a template cannot reach outside the sandbox
+    assert "__class__" not in T.render_chat_template("{{ ''.__class__.__mro__ }}x{% for message in messages %}{{ message.content }}{% endfor %}",
+                                                     [{"role": "user", "content": "q"}], False)
 
 
 def test_codebook_iquants_decode_through_gguf_package():
