@@ -873,3 +873,53 @@ def test_latent_attention_model_gives_the_same_logits_through_the_batched_statem
             llm.model.latent_statement = statement
             outs.append([o.token_ids for o in llm.generate(prompts, sp)])
     assert outs[0] == outs[2] and outs[1] == outs[3]
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_random_traffic_on_a_small_pool_with_window_release(tmp_path, seed):
+    """Random arrivals, lengths and aborts on a sliding-window model with a pool that forces preemption: every request
+    finishes with the tokens a roomy, keep-everything engine gives, and the pool is whole again at the end (no page freed
+    twice or lost across release, preemption, prefix sharing and abort)."""
+    import random
+
+    rnd = random.Random(seed)
+    path = str(tmp_path / "swa.gguf")
+    synth_gguf(path, preset("tiny-llama", arch="mistral", n_layers=2, vocab_size=300, hidden_size=64, n_heads=4, n_kv_heads=2,
+                            head_dim=16, ffn_size=96, sliding_window=20), "F32", seed=7, norm_jitter=0.1)
+    shared = [rnd.randrange(3, 290) for _ in range(40)]  # a common prefix: prefix-cache sharing among requests
+    reqs = []
+    for i in range(10):
+        prompt = (shared[: rnd.choice([0, 16, 32, 40])] + [rnd.randrange(3, 290) for _ in range(rnd.randrange(1, 50))])
+        reqs.append((prompt, rnd.randrange(1, 60)))
+    ec = dict(max_model_len=160, max_num_seqs=4, prefill_chunk_size=16, max_num_batched_tokens=48)
+    roomy = LLM.from_gguf(path, EngineConfig(**ec, num_kv_blocks=128), device="cpu")
+    roomy.scheduler.config.attention_window = 0
+    want = {}
+    for i, (p, n) in enumerate(reqs):
+        want[f"r{i}"] = roomy.generate([p], SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True))[0].token_ids
+    llm = LLM.from_gguf(path, EngineConfig(**ec, num_kv_blocks=7), device="cpu")
+    assert llm.scheduler.config.attention_window == 20
+    pending = list(enumerate(reqs))
+    got, aborted = {}, set()
+    steps = 0
+    while pending or llm.has_unfinished:
+        for _ in range(rnd.randrange(0, 3)):
+            if pending:
+                i, (p, n) = pending.pop(0)
+                llm.add_request(p, SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True), request_id=f"r{i}")
+        if steps == 25 and llm.scheduler.running:
+            victim = llm.scheduler.running[0].request_id  # one request is cancelled in mid-flight
+            llm.abort(victim)
+            aborted.add(victim)
+        for o in llm.step():
+            if o.finished:
+                got[o.request_id] = o.token_ids
+        steps += 1
+        assert steps < 5000
+    for rid, toks in want.items():
+        if rid not in aborted:
+            assert got[rid] == toks, rid
+    assert not llm.scheduler.running and not llm.scheduler.waiting
+    # every page is free or held only by the prefix cache (refcount zero): a fresh request can take the whole pool
+    assert llm.pool.can_allocate(7)
+    assert llm.scheduler.num_preemptions > 0  # the pool was small enough to make the scheduler evict and recompute
