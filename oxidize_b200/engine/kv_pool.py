@@ -200,6 +200,9 @@ class KVCache:
 
     def copy_block(self, src: int, dst: int) -> None:
         """Copy-on-write support: duplicate one page in every layer."""
+        aux = getattr(self, "conv", None)  # the convolution layers' rows of a hybrid model live in a second cache
+        if aux is not None:
+            aux.copy_block(src, dst)
         for l in range(self.spec.n_layers):
             self.data[l][dst].copy_(self.data[l][src])
             if self.scales[l] is not None:

@@ -98,9 +98,11 @@ class LLM:
         kv_dtype = c.kv_cache_dtype
         if kv_dtype == "auto":
             kv_dtype = "bf16" if self.device.type == "cuda" else "f32"
-        spec = KVCacheSpec(len(weights.layers), self.model.n_kv_local, self.model.kv_head_dim, c.kv_page_size, kv_dtype)
-        nblocks = c.num_kv_blocks or self._auto_blocks(spec)
-        self.kv = KVCache(spec, nblocks, self.device)
+        spec = KVCacheSpec(max(1, self.model.n_kv_layers), self.model.n_kv_local, self.model.kv_head_dim, c.kv_page_size, kv_dtype)
+        # (a hybrid model's convolution layers keep one hidden-sized row per token as well)
+        conv_bytes = self.model.n_conv_layers * c.kv_page_size * self.cfg.hidden_size * (2 if self.device.type == "cuda" else 4)
+        nblocks = c.num_kv_blocks or self._auto_blocks(spec, conv_bytes)
+        self.kv = self.model.new_cache(nblocks, c.kv_page_size, kv_dtype)
         self.pool = make_block_pool(nblocks, c.kv_page_size, c.enable_prefix_cache)
         # a window that applies to every layer lets the scheduler hand pages back as they fall out of it
         uniform_window = self.cfg.sliding_window if (self.cfg.sliding_window > 0 and self.cfg.sliding_window_pattern == 0) else 0
@@ -109,7 +111,8 @@ class LLM:
         self.runner = ModelRunner(self.model, self.kv, max(c.max_num_batched_tokens, c.max_num_seqs), c.max_num_seqs,
                                   c.max_model_len, c.cuda_graphs and not _profiler.PROFILE and not _profiler.TRACE_FWD
                                   and isinstance(weights.layers, list)  # a captured graph would pin evicted layers' addresses
-                                  and not self.cfg.is_mla)  # latent attention's device step sizes its gather on the host
+                                  and not self.cfg.is_mla  # latent attention's device step sizes its gather on the host
+                                  and not self.model.n_conv_layers)  # so does the convolution layers' row gather
         self.eos_token_id = c.eos_token_id
         if self.eos_token_id is None and tokenizer is not None:
             self.eos_token_id = tokenizer.special_tokens.eos
@@ -153,14 +156,14 @@ class LLM:
         llm.chat_template = chat_template_from_metadata(g.metadata)  # None when the file carries none
         return llm
 
-    def _auto_blocks(self, spec: KVCacheSpec) -> int:
+    def _auto_blocks(self, spec: KVCacheSpec, extra_bytes_per_block: int = 0) -> int:
         c = self.config
         want = c.max_num_seqs * ((c.max_model_len + spec.page_size - 1) // spec.page_size + 1)
         if self.device.type != "cuda":
             return max(16, min(want, 4096))
         free, total = torch.cuda.mem_get_info(self.device)
         budget = int(free - (1.0 - c.gpu_memory_utilization) * total)
-        fit = max(16, budget // max(spec.bytes_per_block(), 1))
+        fit = max(16, budget // max(spec.bytes_per_block() + extra_bytes_per_block, 1))
         return int(min(want, fit))
 
     # ------------------------------------------------------------------ request API
@@ -430,7 +433,7 @@ class LLM:
             ids = ids[: self.config.max_model_len]
             n = len(ids)
             nblk = (n + page - 1) // page
-            kv = KVCache(KVCacheSpec(len(m.w.layers), m.n_kv_local, m.kv_head_dim, page, self.kv.spec.dtype_name), nblk, dev)
+            kv = m.new_cache(nblk, page, self.kv.spec.dtype_name)
             pos = torch.arange(n, **i32)
             meta = BatchMeta(torch.tensor(ids, **i32), pos, pos.clone(), torch.tensor([0, n], **i32), torch.tensor([n], **i32),
                              torch.arange(nblk, **i32)[None, :], torch.arange(n, **i32), n, n, 1, logits_all=True)
@@ -461,7 +464,7 @@ class LLM:
         page = self.config.kv_page_size
         n = len(ids)
         nblk = (n + page - 1) // page
-        kv = KVCache(KVCacheSpec(len(m.w.layers), m.n_kv_local, m.kv_head_dim, page, self.kv.spec.dtype_name), nblk, dev)
+        kv = m.new_cache(nblk, page, self.kv.spec.dtype_name)
         bt = torch.arange(nblk, **i32)[None, :]
         out = np.empty(n - 1, dtype=np.float64)
         for lo in range(0, n - 1, chunk):

@@ -75,7 +75,7 @@ class DraftModelProposer:
         page = 16
         nblocks = num_blocks or max_seqs * ((max_model_len + page - 1) // page + 1)
         kvd = "bf16" if dev.type == "cuda" else "f32"
-        self.kv = KVCache(KVCacheSpec(len(draft_weights.layers), self.model.n_kv_local, self.model.kv_head_dim, page, kvd), nblocks, dev)
+        self.kv = self.model.new_cache(nblocks, page, kvd)
         self.pool = make_block_pool(nblocks, page, enable_prefix_cache=False)
         self.runner = ModelRunner(self.model, self.kv, max(2048, max_seqs * (k + 2)), max_seqs, max_model_len, False)
         self.shadow: Dict[int, Sequence] = {}

@@ -23,7 +23,7 @@ _ARCH = {"LlamaForCausalLM": "llama", "MistralForCausalLM": "llama", "MixtralFor
          "Qwen2ForCausalLM": "qwen2", "Qwen3ForCausalLM": "qwen3", "Qwen3MoeForCausalLM": "qwen3moe",
          "Qwen2MoeForCausalLM": "qwen2moe", "DeepseekV2ForCausalLM": "deepseek2", "DeepseekV3ForCausalLM": "deepseek2",
          "Phi3ForCausalLM": "phi3", "GemmaForCausalLM": "gemma", "Gemma2ForCausalLM": "gemma2",
-         "Gemma3ForCausalLM": "gemma3", "Gemma3ForConditionalGeneration": "gemma3"}
+         "Gemma3ForCausalLM": "gemma3", "Gemma3ForConditionalGeneration": "gemma3", "Lfm2ForCausalLM": "lfm2"}
 GEMMA = ("gemma", "gemma2", "gemma3")
 
 
@@ -57,9 +57,24 @@ def write_hf_metadata(w: GGUFWriter, arch: str, c: Dict[str, Any]) -> None:
     w.add(f"{arch}.embedding_length", hidden, U)
     w.add(f"{arch}.block_count", int(c["num_hidden_layers"]), U)
     w.add(f"{arch}.context_length", int(c.get("max_position_embeddings", 4096)), U)
-    w.add(f"{arch}.feed_forward_length", int(c.get("intermediate_size", 0)), U)
+    ffn = int(c.get("intermediate_size", 0))
+    if arch == "lfm2" and c.get("block_auto_adjust_ff_dim"):
+        # the checkpoint's MLP width is derived from intermediate_size (two thirds, scaled, rounded up to a multiple)
+        ffn = int(2 * ffn / 3)
+        if c.get("block_ffn_dim_multiplier"):
+            ffn = int(float(c["block_ffn_dim_multiplier"]) * ffn)
+        mult = int(c.get("block_multiple_of", 256))
+        ffn = mult * ((ffn + mult - 1) // mult)
+    w.add(f"{arch}.feed_forward_length", ffn, U)
     w.add(f"{arch}.attention.head_count", heads, U)
-    w.add(f"{arch}.attention.head_count_kv", int(c.get("num_key_value_heads", heads)), U)
+    kvh = int(c.get("num_key_value_heads", heads))
+    if arch == "lfm2":
+        # one entry per layer, 0 for the convolution layers (as llama.cpp's converter writes it)
+        kinds = c.get("layer_types") or []
+        w.add(f"{arch}.attention.head_count_kv", [kvh if k == "full_attention" else 0 for k in kinds] or kvh)
+        w.add(f"{arch}.shortconv.l_cache", int(c.get("conv_L_cache", 3)), U)
+    else:
+        w.add(f"{arch}.attention.head_count_kv", kvh, U)
     hd = int(c.get("head_dim") or hidden // heads)
     if c.get("kv_lora_rank"):
         # latent attention: per-head query / key width (position-free + rotary part) and value width
@@ -69,7 +84,7 @@ def write_hf_metadata(w: GGUFWriter, arch: str, c: Dict[str, Any]) -> None:
             w.add(f"{arch}.attention.q_lora_rank", int(c["q_lora_rank"]), U)
     w.add(f"{arch}.attention.key_length", hd, U)
     w.add(f"{arch}.attention.value_length", int(c.get("v_head_dim") or hd), U)
-    w.add(f"{arch}.attention.layer_norm_rms_epsilon", float(c.get("rms_norm_eps", 1e-5)), F)
+    w.add(f"{arch}.attention.layer_norm_rms_epsilon", float(c.get("rms_norm_eps") or c.get("norm_eps") or 1e-5), F)
     theta, theta_swa, rs = _rope_settings(c)
     w.add(f"{arch}.rope.freq_base", theta, F)
     w.add(f"{arch}.rope.dimension_count",
@@ -169,6 +184,11 @@ def convert_safetensors_to_gguf(src_dir: str, out_path: str, quant: str = "F16",
 
     for gname, f, name in plain:
         shape = f.shape(name)
+        if gname.endswith("shortconv.conv.weight"):  # [channels, 1, taps] -> [channels, taps], kept in f32
+            shape = (shape[0], shape[-1])
+            w.add_tensor(gname, (lambda f=f, name=name, shape=shape: f.tensor_f32(name).reshape(shape).astype(np.float32)),
+                         shape, "F32")
+            continue
 
         def gen(f=f, name=name, gname=gname):
             return encode(gname, f.tensor_f32(name))[0]

@@ -596,6 +596,20 @@ _HF_LAYER_MAP_GEMMA = {
     "pre_feedforward_layernorm.weight": "ffn_norm.weight",
     "post_feedforward_layernorm.weight": "post_ffw_norm.weight",
 }
+# LFM2: operator norm, short-convolution tensors, w1 / w3 / w2 feed-forward names, RMSNorm on q / k heads
+_HF_LAYER_MAP_LFM2 = {
+    "operator_norm.weight": "attn_norm.weight",
+    "ffn_norm.weight": "ffn_norm.weight",
+    "self_attn.out_proj.weight": "attn_output.weight",
+    "self_attn.q_layernorm.weight": "attn_q_norm.weight",
+    "self_attn.k_layernorm.weight": "attn_k_norm.weight",
+    "feed_forward.w1.weight": "ffn_gate.weight",
+    "feed_forward.w3.weight": "ffn_up.weight",
+    "feed_forward.w2.weight": "ffn_down.weight",
+    "conv.in_proj.weight": "shortconv.in_proj.weight",
+    "conv.conv.weight": "shortconv.conv.weight",
+    "conv.out_proj.weight": "shortconv.out_proj.weight",
+}
 _HF_TOP_MAP = {
     "model.embed_tokens.weight": "token_embd.weight",
     "model.norm.weight": "output_norm.weight",
@@ -619,12 +633,16 @@ def map_hf_tensor_name(name: str, arch: Optional[str] = None) -> Optional[Tuple[
             name = name[len("model."):]
     if name in _HF_TOP_MAP:
         return _HF_TOP_MAP[name], None
+    if arch == "lfm2" and name == "model.embedding_norm.weight":
+        return "token_embd_norm.weight", None  # the norm in front of the head (the name llama.cpp's converter gives it)
     m = _HF_LAYER_RE.match(name)
     if not m:
         return None
     layer, rest = int(m.group(1)), m.group(2)
     if arch in ("gemma2", "gemma3") and rest in _HF_LAYER_MAP_GEMMA:
         return f"blk.{layer}.{_HF_LAYER_MAP_GEMMA[rest]}", None
+    if arch == "lfm2" and rest in _HF_LAYER_MAP_LFM2:
+        return f"blk.{layer}.{_HF_LAYER_MAP_LFM2[rest]}", None
     if rest in _HF_LAYER_MAP:
         return f"blk.{layer}.{_HF_LAYER_MAP[rest]}", None
     e = _HF_EXPERT_RE.match(rest)

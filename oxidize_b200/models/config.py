@@ -17,14 +17,15 @@ from ..formats.gguf import GGUFFile
 # architecture strings accepted (reference arch-string map inference.rs:62-96)
 # phi3: Llama layers with fused qkv / gate-up tensors.  gemma / gemma2 / gemma3: GeGLU, scaled embeddings, norms on the
 # branch outputs, soft-capped logits, interleaved local / global attention with two rotary bases.
-DENSE_ARCHS = {"llama", "mistral", "qwen2", "qwen3", "deepseek", "phi3", "gemma", "gemma2", "gemma3"}
+# lfm2: short-convolution mixers interleaved with grouped-query attention layers.
+DENSE_ARCHS = {"llama", "mistral", "qwen2", "qwen3", "deepseek", "phi3", "gemma", "gemma2", "gemma3", "lfm2"}
 GEMMA_ARCHS = {"gemma", "gemma2", "gemma3"}
 MOE_ARCHS = {"mixtral", "qwen2moe", "qwen3moe", "deepseek2", "deepseek-moe", "deepseek_moe"}
 # Architectures whose layers need math this engine does not have (two attention geometries in one model,
 # parallel attention / MLP blocks, recurrent or convolutional mixers): loading one would run it as
 # a plain Llama and produce wrong tokens, so they are refused by name.
 UNSUPPORTED_ARCHS = {"gemma4", "phi", "phi2", "llama4", "qwen35", "qwen3_5_moe", "mamba",
-                     "lfm2", "glm4", "falcon", "gpt2", "bert"}
+                     "glm4", "falcon", "gpt2", "bert"}
 
 
 class UnsupportedArchitecture(ValueError):
@@ -91,6 +92,10 @@ class ModelConfig:
     qk_nope_dim: int = 0  # part of every query / key head that carries no position
     v_head_dim: int = 0  # value width per head
     yarn_log_multiplier: float = 0.0  # YaRN: the scores are scaled by (1 + this * ln(factor)) ** 2
+    # Short-convolution mixer layers (LFM2; the reference's short-conv layer, model/inference/layers.rs:313): in those
+    # layers a gated depthwise causal convolution over the last conv_l_cache positions takes the place of attention.
+    conv_layers: List[int] = field(default_factory=list)  # indices of the convolution layers
+    conv_l_cache: int = 0  # kernel length
     # MoE
     n_experts: int = 0
     n_experts_used: int = 0
@@ -234,6 +239,12 @@ def config_from_gguf(g: GGUFFile) -> ModelConfig:
         c.n_kv_heads = c.n_heads
         c.rope_pairing = "adjacent"  # the rotary part is stored with interleaved pairs and files keep that order
         c.yarn_log_multiplier = float(_scalar(a("rope.scaling.yarn_log_multiplier"), 0.0))
+    if arch == "lfm2":
+        c.conv_l_cache = int(_scalar(a("shortconv.l_cache"), 3))
+        c.conv_layers = [i for i in range(c.n_layers) if g.has_tensor(f"blk.{i}.shortconv.conv.weight")]
+        first_attn = next((i for i in range(c.n_layers) if i not in c.conv_layers), 0)
+        c.qk_norm = g.has_tensor(f"blk.{first_attn}.attn_q_norm.weight")
+        c.tie_embeddings = not g.has_tensor("output.weight")
     if arch in GEMMA_ARCHS:
         c.embedding_scale = float(c.hidden_size) ** 0.5
         c.ffn_act = "gelu_tanh"

@@ -120,6 +120,16 @@ class Transformer:
                 n_heads=self.n_heads_local, n_kv_heads=self.n_kv_local, head_dim=cfg.head_dim)
         self.attn_scale = cfg.attn_scale if cfg.attn_scale > 0 else cfg.head_dim ** -0.5
         self.kv_head_dim = cfg.head_dim  # width of one cached key / value row
+        # which cache layer a decoder layer writes: attention layers count through the KV cache, convolution layers (hybrid
+        # models) through a second cache that holds their gated inputs; the reference's ``kv_layer_map`` (load.rs:470-480)
+        conv = set(i - weights.first_layer for i in cfg.conv_layers)
+        self.kv_index, self.conv_index = [], []
+        for li in range(len(weights.layers)):
+            is_conv = li in conv
+            self.kv_index.append(-1 if is_conv else sum(1 for j in range(li) if j not in conv))
+            self.conv_index.append(sum(1 for j in range(li) if j in conv) if is_conv else -1)
+        self.n_kv_layers = sum(1 for i in self.kv_index if i >= 0)
+        self.n_conv_layers = len(weights.layers) - self.n_kv_layers
         if cfg.is_mla:
             # One cached row per token, shared by all heads: the normalised latent followed by the rotary key.
             self.n_kv_local = 1
@@ -230,6 +240,48 @@ class Transformer:
             w.swiglu_interleaved = True
 
     # ------------------------------------------------------------------ blocks
+    def new_cache(self, num_blocks: int, page_size: int, dtype_name: str):
+        """A paged cache shaped for this model: KV rows for the attention layers and, for a hybrid model, a second cache
+        (same pages, same block ids) whose rows are the convolution layers' gated inputs, split over its K and V halves."""
+        from ..engine.kv_pool import KVCache, KVCacheSpec
+
+        kv = KVCache(KVCacheSpec(max(1, self.n_kv_layers), self.n_kv_local, self.kv_head_dim, page_size, dtype_name),
+                     num_blocks, self.device)
+        if self.n_conv_layers:
+            if self.cfg.hidden_size % 2:
+                raise ValueError("convolution layers need an even hidden size")
+            plain = "bf16" if self.device.type == "cuda" else "f32"  # never quantized: the rows are convolved, not attended
+            kv.conv = KVCache(KVCacheSpec(self.n_conv_layers, 1, self.cfg.hidden_size // 2, page_size, plain), num_blocks,
+                              self.device)
+        return kv
+
+    def _short_conv(self, lw: LayerWeights, layer: int, x: torch.Tensor, meta: BatchMeta, kv) -> torch.Tensor:
+        """LFM2 mixer: (B, C, v) = in_proj(x); u = B * v; y_t = C_t * sum_j w[:, j] u_{t - (L-1) + j}; out_proj(y).  The rows u
+        go into the convolution cache at the token's slot, and the L-1 earlier rows a token needs are read back through
+        its sequence's block table: earlier chunks, cached prefixes and rows of this very step alike."""
+        cfg = self.cfg
+        h, L = cfg.hidden_size, cfg.conv_l_cache
+        cache, idx = kv.conv, self.conv_index[layer]
+        bcx = ops.linear(x, lw.conv_in).float()
+        gate_b, gate_c, v = bcx[:, :h], bcx[:, h : 2 * h], bcx[:, 2 * h :]
+        u = gate_b * v
+        opref.kv_write(cache, idx, u[:, None, : h // 2], u[:, None, h // 2 :], meta.slot_mapping)
+        qs = meta.query_start.long()
+        row_seq = torch.repeat_interleave(torch.arange(qs.numel() - 1, device=x.device), qs[1:] - qs[:-1])
+        pos = meta.positions.long()
+        page = cache.page_size
+        w = lw.conv_kernel.float()
+        acc = w[:, L - 1] * u
+        data = cache.data[idx]
+        for j in range(1, L):
+            q = pos - j
+            ok = q >= 0
+            qc = q.clamp(min=0)
+            blk = meta.block_tables[row_seq, qc // page].long()
+            prev = torch.cat([data[blk, 0, 0, qc % page], data[blk, 0, 1, qc % page]], dim=-1).float()
+            acc = acc + w[:, L - 1 - j] * prev * ok[:, None]
+        return ops.linear((gate_c * acc).to(x.dtype), lw.conv_out)
+
     def _layer_rope(self, window: int) -> RopeState:
         """Rotary state of a layer: windowed layers use their own base when the model has one."""
         return self.rope_swa if (window > 0 and self.rope_swa is not None) else self.rope
@@ -269,9 +321,13 @@ class Transformer:
 
     def _attention(self, lw: LayerWeights, layer: int, x: torch.Tensor, meta: BatchMeta, kv) -> torch.Tensor:
         cfg = self.cfg
+        if lw.conv_in is not None:
+            return self._short_conv(lw, layer, x, meta, kv)
+        window_of = self.w.first_layer + layer  # the window pattern counts decoder layers, the cache counts attention layers
+        layer = self.kv_index[layer]
         if lw.mla is not None:
             return self._mla_attention(lw, layer, x, meta, kv)
-        window = cfg.layer_sliding_window(self.w.first_layer + layer)
+        window = cfg.layer_sliding_window(window_of)
         rope = self._layer_rope(window)
         if self._fuse_qkv_rope and x.is_cuda and lw.wqkv.bias is None:
             from ..ops import cuda as opcuda

@@ -181,12 +181,17 @@ class MLAWeights:
 @dataclass
 class LayerWeights:
     attn_norm: torch.Tensor
-    wqkv: Optional[LinearWeight]  # None in a latent-attention layer (``mla`` holds its projections)
-    wo: LinearWeight
+    wqkv: Optional[LinearWeight]  # None in a latent-attention layer (``mla`` holds its projections) or a convolution layer
+    wo: Optional[LinearWeight]
     ffn_norm: torch.Tensor
     q_norm: Optional[torch.Tensor] = None
     k_norm: Optional[torch.Tensor] = None
     mla: Optional[MLAWeights] = None
+    # short-convolution mixer (LFM2) instead of attention: in_proj [3 hidden, hidden] (rows: B, C, x), depthwise kernel
+    # [hidden, l_cache] (oldest tap first), out_proj [hidden, hidden]
+    conv_in: Optional[QTensor] = None
+    conv_kernel: Optional[torch.Tensor] = None
+    conv_out: Optional[LinearWeight] = None
     # Gemma-2/3: norms applied to the attention / FFN branch outputs before the residual add
     post_attn_norm: Optional[torch.Tensor] = None
     post_ffn_norm: Optional[torch.Tensor] = None
@@ -410,6 +415,17 @@ def _load_layer(src: GGUFWeightSource, cfg: ModelConfig, i: int, tp_rank: int, t
     k0, k1 = shard_range(cfg.n_kv_heads, tp_rank // kv_rep, kv_shards)
     qr, kr = (q0 * hd, q1 * hd), (k0 * hd, k1 * hd)
     mla = None
+    if src.has(f"{p}.shortconv.conv.weight"):
+        if tp_size > 1:
+            raise ValueError("short-convolution layers are not sharded: run this model with tp_size = 1")
+        lw = LayerWeights(attn_norm=src.vector(f"{p}.attn_norm.weight"), wqkv=None, wo=None,
+                          ffn_norm=src.vector(f"{p}.ffn_norm.weight"), conv_in=src.matrix(f"{p}.shortconv.in_proj.weight"),
+                          conv_kernel=src.vector(f"{p}.shortconv.conv.weight").reshape(cfg.hidden_size, -1),
+                          conv_out=LinearWeight([src.matrix(f"{p}.shortconv.out_proj.weight")]))
+        ffn = src.g.tensors[f"{p}.ffn_gate.weight"].shape[0]
+        lw.w_gate_up = LinearWeight(fuse_rows([src.matrix(f"{p}.ffn_gate.weight"), src.matrix(f"{p}.ffn_up.weight")]))
+        lw.w_down = LinearWeight([src.matrix(f"{p}.ffn_down.weight")])
+        return lw
     if src.has(f"{p}.attn_kv_a_mqa.weight"):
         mla = _load_mla(src, cfg, p, q0, q1)
         parts = []
@@ -502,7 +518,8 @@ def load_weights(g: GGUFFile, cfg: ModelConfig, device="cpu", act_dtype: torch.d
     v0, v1 = shard_range(cfg.vocab_size, tp_rank, tp_size) if cfg.vocab_size % tp_size == 0 else (0, cfg.vocab_size)
     head_name = "output.weight" if src.has("output.weight") else "token_embd.weight"
     lm_head = LinearWeight([src.matrix(head_name, rows=(v0, v1))])
-    mw = ModelWeights(cfg, embed, layers, src.vector("output_norm.weight"), lm_head, [], tp_rank, tp_size,
+    norm_name = "output_norm.weight" if src.has("output_norm.weight") else "token_embd_norm.weight"  # LFM2 files use the latter
+    mw = ModelWeights(cfg, embed, layers, src.vector(norm_name), lm_head, [], tp_rank, tp_size,
                       ep_rank, ep_size, l0, v0)
     if src.has("rope_freqs.weight"):
         mw.rope_freq_factors = src.vector("rope_freqs.weight")

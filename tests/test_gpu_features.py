@@ -166,3 +166,34 @@ def test_latent_attention_model_on_the_device(tmp_path):
     out = gpu.generate(PROMPTS, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
     assert all(len(o.token_ids) == 8 for o in out)
     _status_ok()
+
+
+def test_short_convolution_model_on_the_device(tmp_path):
+    """LFM2 (gated short convolutions + attention with normalised q / k heads) on the device against the CPU path,
+    teacher-forced; the checkpoint comes from a random-init `transformers` model through the converter."""
+    T = pytest.importorskip("transformers")
+    from oxidize_b200.formats.convert import convert_safetensors_to_gguf
+
+    torch.manual_seed(0)
+    ref = T.Lfm2ForCausalLM(T.Lfm2Config(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=4,
+                                         num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=256, conv_L_cache=3,
+                                         block_auto_adjust_ff_dim=False, layer_types=["conv", "full_attention", "conv", "full_attention"]))
+    with torch.no_grad():
+        for n, p in ref.named_parameters():
+            if p.ndim == 2:
+                p.mul_(2.0)
+    src = str(tmp_path / "hf")
+    ref.save_pretrained(src, safe_serialization=True)
+    path = convert_safetensors_to_gguf(src, str(tmp_path / "lfm2.gguf"), "BF16")
+    cpu = LLM.from_gguf(path, EngineConfig(**EC), device="cpu")
+    gpu = LLM.from_gguf(path, EngineConfig(**EC), device="cuda")
+    assert gpu.model.n_conv_layers == 2 and gpu.model.n_kv_layers == 2 and gpu.kv.conv.spec.head_dim == 128
+    prompts = [list(p) for p in PROMPTS]
+    for _ in range(3):
+        lc = torch.from_numpy(cpu.next_token_logits(prompts))
+        lg = torch.from_numpy(gpu.next_token_logits(prompts))
+        assert _rel(lg, lc) < 4e-2
+        prompts = [p + [int(lc[i].argmax())] for i, p in enumerate(prompts)]
+    out = gpu.generate(PROMPTS, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    assert all(len(o.token_ids) == 8 for o in out)
+    _status_ok()

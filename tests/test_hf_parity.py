@@ -8,7 +8,8 @@ QK-norm (Qwen3), fused qkv / gate-up tensors (Phi-3), softmax top-k routing (Mix
 scaled embeddings, GeGLU, norms on the branch outputs, (w + 1) norm weights, soft-capped scores and logits, the softmax
 scale taken from query_pre_attn_scalar, and local / global layers with a window and two rotary bases; for DeepSeek-V2/V3
 the latent attention (low-rank and full-rank queries, shared rotary key, interleaved rotary pairs, YaRN), softmax and
-sigmoid group-limited routing with a selection bias, the shared expert and the leading dense layer.
+sigmoid group-limited routing with a selection bias, the shared expert and the leading dense layer; for LFM2 the gated
+short-convolution layers, whose history lives in a second paged cache and crosses prefill chunks.
 """
 import os
 
@@ -52,6 +53,9 @@ def _build(name: str):
         # 7 layers: five windowed (rotary base 1e4), the sixth global (base 1e6), the seventh windowed again
         c["num_hidden_layers"] = 7
         return T.Gemma3ForCausalLM(T.Gemma3TextConfig(**c, head_dim=32, sliding_window=8, query_pre_attn_scalar=40))
+    if name == "lfm2":  # convolution layers (kernel of 3 taps) around two attention layers with RMSNorm on q / k heads
+        return T.Lfm2ForCausalLM(T.Lfm2Config(**c, conv_L_cache=3, block_auto_adjust_ff_dim=False,
+                                              layer_types=["conv", "conv", "full_attention", "conv"]))
     # DeepSeek: latent attention (32-wide latent, 16 position-free + 8 rotary query / key values per head, 24-wide values),
     # one dense layer then routed experts + a shared expert
     ds = dict(c, moe_intermediate_size=48, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2, first_k_dense_replace=1,
@@ -70,7 +74,7 @@ def _build(name: str):
 
 
 FAMILIES = ["llama", "qwen2", "qwen3", "phi3", "mixtral", "qwen3moe", "gemma", "gemma2", "gemma3", "deepseek_v2", "deepseek_v3",
-            "deepseek_v3_yarn"]
+            "deepseek_v3_yarn", "lfm2"]
 
 
 @pytest.mark.parametrize("family", FAMILIES)
@@ -97,6 +101,8 @@ def test_logits_and_greedy_tokens_match_transformers(family, tmp_path):
         assert cfg.is_mla and (cfg.kv_lora_rank, cfg.qk_nope_dim, cfg.rope_dim, cfg.v_head_dim, cfg.head_dim) == (32, 16, 8, 24, 24)
         assert cfg.rope_pairing == "adjacent" and cfg.n_shared_experts == 1 and cfg.leading_dense_blocks == 1
         assert cfg.expert_gating == ("softmax" if family == "deepseek_v2" else "sigmoid")
+    if family == "lfm2":
+        assert cfg.conv_layers == [0, 1, 3] and cfg.conv_l_cache == 3 and cfg.qk_norm and cfg.n_kv_heads == 2
     if family == "gemma3":
         assert cfg.sliding_window_pattern == 6 and cfg.rope_theta_swa == 10000.0 and cfg.rope_theta == 1000000.0
         assert cfg.qk_norm and cfg.post_norms and cfg.ffn_act == "gelu_tanh" and cfg.embedding_scale == 8.0
