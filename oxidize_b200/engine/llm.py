@@ -103,16 +103,19 @@ class LLM:
         conv_bytes = self.model.n_conv_layers * c.kv_page_size * self.cfg.hidden_size * (2 if self.device.type == "cuda" else 4)
         nblocks = c.num_kv_blocks or self._auto_blocks(spec, conv_bytes)
         self.kv = self.model.new_cache(nblocks, c.kv_page_size, kv_dtype)
-        self.pool = make_block_pool(nblocks, c.kv_page_size, c.enable_prefix_cache)
+        # a recurrent state cannot be rebuilt from shared pages: state-space models run without the prefix cache
+        prefix_cache = c.enable_prefix_cache and not self.cfg.is_ssm
+        self.pool = make_block_pool(nblocks, c.kv_page_size, prefix_cache)
         # a window that applies to every layer lets the scheduler hand pages back as they fall out of it
         uniform_window = self.cfg.sliding_window if (self.cfg.sliding_window > 0 and self.cfg.sliding_window_pattern == 0) else 0
         self.scheduler = Scheduler(SchedulerConfig(c.max_num_batched_tokens, c.prefill_chunk_size, c.max_num_seqs,
-                                                   c.policy, c.enable_prefix_cache, c.max_model_len, uniform_window), self.pool)
+                                                   c.policy, prefix_cache, c.max_model_len, uniform_window), self.pool)
         self.runner = ModelRunner(self.model, self.kv, max(c.max_num_batched_tokens, c.max_num_seqs), c.max_num_seqs,
                                   c.max_model_len, c.cuda_graphs and not _profiler.PROFILE and not _profiler.TRACE_FWD
                                   and isinstance(weights.layers, list)  # a captured graph would pin evicted layers' addresses
                                   and not self.cfg.is_mla  # latent attention's device step sizes its gather on the host
-                                  and not self.model.n_conv_layers)  # so does the convolution layers' row gather
+                                  and not self.model.n_conv_layers  # so does the convolution layers' row gather
+                                  and not self.cfg.is_ssm)  # the recurrence runs from the host, token by token
         self.eos_token_id = c.eos_token_id
         if self.eos_token_id is None and tokenizer is not None:
             self.eos_token_id = tokenizer.special_tokens.eos

@@ -411,6 +411,8 @@ class SpecDecoder:
 def attach_speculation(llm, draft_model_path: Optional[str], k: int = 4, use_mtp: bool = False, device=None) -> SpecDecoder:
     """Enable speculative decoding on an engine: a draft GGUF if given, else the model's MTP head."""
     c = llm.config
+    if llm.cfg.is_ssm:
+        raise ValueError("speculative decoding needs a cache that can be rolled back: not available for state-space models")
     if draft_model_path:
         from ..formats.gguf import load_gguf
         from ..models.config import config_from_gguf

@@ -23,7 +23,8 @@ _ARCH = {"LlamaForCausalLM": "llama", "MistralForCausalLM": "llama", "MixtralFor
          "Qwen2ForCausalLM": "qwen2", "Qwen3ForCausalLM": "qwen3", "Qwen3MoeForCausalLM": "qwen3moe",
          "Qwen2MoeForCausalLM": "qwen2moe", "DeepseekV2ForCausalLM": "deepseek2", "DeepseekV3ForCausalLM": "deepseek2",
          "Phi3ForCausalLM": "phi3", "GemmaForCausalLM": "gemma", "Gemma2ForCausalLM": "gemma2",
-         "Gemma3ForCausalLM": "gemma3", "Gemma3ForConditionalGeneration": "gemma3", "Lfm2ForCausalLM": "lfm2"}
+         "Gemma3ForCausalLM": "gemma3", "Gemma3ForConditionalGeneration": "gemma3", "Lfm2ForCausalLM": "lfm2",
+         "MambaForCausalLM": "mamba"}
 GEMMA = ("gemma", "gemma2", "gemma3")
 
 
@@ -48,8 +49,26 @@ def _rope_settings(c: Dict[str, Any]) -> Tuple[float, float, Dict[str, Any]]:
     return theta, float(c.get("rope_local_base_freq") or 0.0), (rp if rp.get("rope_type") else c.get("rope_scaling") or {})
 
 
+def write_mamba_metadata(w: GGUFWriter, c: Dict[str, Any]) -> None:
+    U, F = GGUFValueType.UINT32, GGUFValueType.FLOAT32
+    hidden = int(c["hidden_size"])
+    w.add("general.name", str(c.get("_name_or_path") or "mamba"))
+    w.add("mamba.vocab_size", int(c["vocab_size"]), U)
+    w.add("mamba.embedding_length", hidden, U)
+    w.add("mamba.block_count", int(c["num_hidden_layers"]), U)
+    w.add("mamba.context_length", int(c.get("max_position_embeddings", 1 << 20)), U)
+    w.add("mamba.ssm.conv_kernel", int(c.get("conv_kernel", 4)), U)
+    w.add("mamba.ssm.inner_size", int(c.get("intermediate_size") or int(c.get("expand", 2)) * hidden), U)
+    w.add("mamba.ssm.state_size", int(c.get("state_size", 16)), U)
+    rank = c.get("time_step_rank", "auto")
+    w.add("mamba.ssm.time_step_rank", -(-hidden // 16) if rank == "auto" else int(rank), U)
+    w.add("mamba.attention.layer_norm_rms_epsilon", float(c.get("layer_norm_epsilon", 1e-5)), F)
+
+
 def write_hf_metadata(w: GGUFWriter, arch: str, c: Dict[str, Any]) -> None:
     U, F = GGUFValueType.UINT32, GGUFValueType.FLOAT32
+    if arch == "mamba":
+        return write_mamba_metadata(w, c)
     heads = int(c["num_attention_heads"])
     hidden = int(c["hidden_size"])
     w.add("general.name", str(c.get("_name_or_path") or c.get("model_type") or "converted"))
@@ -156,7 +175,7 @@ def convert_safetensors_to_gguf(src_dir: str, out_path: str, quant: str = "F16",
     write_hf_metadata(w, arch, cfg)
     for k, v in (tokenizer_metadata or {}).items():
         w.add(k, v)
-    L = int(cfg["num_hidden_layers"])
+    L = int(cfg.get("num_hidden_layers") or cfg.get("n_layer"))
     plain: List[Tuple[str, SafeTensorsFile, str]] = []
     experts: Dict[str, Dict[int, Tuple[SafeTensorsFile, str]]] = {}
     for f in files:
@@ -175,7 +194,7 @@ def convert_safetensors_to_gguf(src_dir: str, out_path: str, quant: str = "F16",
         return int(parts[1]) if parts[0] == "blk" else 0
 
     def encode(gname: str, arr_f32: np.ndarray):
-        if arr_f32.ndim == 1 or "norm" in gname or gname.endswith(".bias") or "ffn_gate_inp" in gname:
+        if arr_f32.ndim == 1 or "norm" in gname or gname.endswith(".bias") or "ffn_gate_inp" in gname or gname.endswith("ssm_d"):
             if arch in GEMMA and gname.endswith("norm.weight"):
                 arr_f32 = arr_f32 + 1.0  # Gemma stores w - 1; files carry the multiplier itself (as llama.cpp's do)
             return arr_f32.astype(np.float32), "F32"
@@ -184,7 +203,10 @@ def convert_safetensors_to_gguf(src_dir: str, out_path: str, quant: str = "F16",
 
     for gname, f, name in plain:
         shape = f.shape(name)
-        if gname.endswith("shortconv.conv.weight"):  # [channels, 1, taps] -> [channels, taps], kept in f32
+        if gname.endswith("ssm_a"):  # the checkpoint stores log(-A); files carry A itself
+            w.add_tensor(gname, (lambda f=f, name=name: (-np.exp(f.tensor_f32(name))).astype(np.float32)), shape, "F32")
+            continue
+        if gname.endswith(("ssm_conv1d.weight", "shortconv.conv.weight")):  # [channels, 1, taps] -> [channels, taps], kept in f32
             shape = (shape[0], shape[-1])
             w.add_tensor(gname, (lambda f=f, name=name, shape=shape: f.tensor_f32(name).reshape(shape).astype(np.float32)),
                          shape, "F32")

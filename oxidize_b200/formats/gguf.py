@@ -610,6 +610,22 @@ _HF_LAYER_MAP_LFM2 = {
     "conv.conv.weight": "shortconv.conv.weight",
     "conv.out_proj.weight": "shortconv.out_proj.weight",
 }
+# Mamba (``backbone.layers.N.*``): the norm in front of the mixer and the mixer's tensors
+_HF_MAMBA_TOP = {"backbone.embeddings.weight": "token_embd.weight", "backbone.norm_f.weight": "output_norm.weight",
+                 "lm_head.weight": "output.weight"}
+_HF_MAMBA_LAYER = {
+    "norm.weight": "attn_norm.weight",
+    "mixer.in_proj.weight": "ssm_in.weight",
+    "mixer.conv1d.weight": "ssm_conv1d.weight",
+    "mixer.conv1d.bias": "ssm_conv1d.bias",
+    "mixer.x_proj.weight": "ssm_x.weight",
+    "mixer.dt_proj.weight": "ssm_dt.weight",
+    "mixer.dt_proj.bias": "ssm_dt.bias",
+    "mixer.A_log": "ssm_a",
+    "mixer.D": "ssm_d",
+    "mixer.out_proj.weight": "ssm_out.weight",
+}
+_HF_MAMBA_RE = re.compile(r"^backbone\.layers\.(\d+)\.(.+)$")
 _HF_TOP_MAP = {
     "model.embed_tokens.weight": "token_embd.weight",
     "model.norm.weight": "output_norm.weight",
@@ -631,6 +647,11 @@ def map_hf_tensor_name(name: str, arch: Optional[str] = None) -> Optional[Tuple[
         name = name.replace("language_model.", "")
         while name.startswith("model.model."):
             name = name[len("model."):]
+    if arch == "mamba":
+        if name in _HF_MAMBA_TOP:
+            return _HF_MAMBA_TOP[name], None
+        mm = _HF_MAMBA_RE.match(name)
+        return (f"blk.{mm.group(1)}.{_HF_MAMBA_LAYER[mm.group(2)]}", None) if mm and mm.group(2) in _HF_MAMBA_LAYER else None
     if name in _HF_TOP_MAP:
         return _HF_TOP_MAP[name], None
     if arch == "lfm2" and name == "model.embedding_norm.weight":

@@ -18,13 +18,14 @@ from ..formats.gguf import GGUFFile
 # phi3: Llama layers with fused qkv / gate-up tensors.  gemma / gemma2 / gemma3: GeGLU, scaled embeddings, norms on the
 # branch outputs, soft-capped logits, interleaved local / global attention with two rotary bases.
 # lfm2: short-convolution mixers interleaved with grouped-query attention layers.
-DENSE_ARCHS = {"llama", "mistral", "qwen2", "qwen3", "deepseek", "phi3", "gemma", "gemma2", "gemma3", "lfm2"}
+# mamba: selective state-space layers only (no attention, no feed-forward block).
+DENSE_ARCHS = {"llama", "mistral", "qwen2", "qwen3", "deepseek", "phi3", "gemma", "gemma2", "gemma3", "lfm2", "mamba"}
 GEMMA_ARCHS = {"gemma", "gemma2", "gemma3"}
 MOE_ARCHS = {"mixtral", "qwen2moe", "qwen3moe", "deepseek2", "deepseek-moe", "deepseek_moe"}
 # Architectures whose layers need math this engine does not have (two attention geometries in one model,
 # parallel attention / MLP blocks, recurrent or convolutional mixers): loading one would run it as
 # a plain Llama and produce wrong tokens, so they are refused by name.
-UNSUPPORTED_ARCHS = {"gemma4", "phi", "phi2", "llama4", "qwen35", "qwen3_5_moe", "mamba",
+UNSUPPORTED_ARCHS = {"gemma4", "phi", "phi2", "llama4", "qwen35", "qwen3_5_moe", "mamba2", "jamba",
                      "glm4", "falcon", "gpt2", "bert"}
 
 
@@ -96,6 +97,12 @@ class ModelConfig:
     # layers a gated depthwise causal convolution over the last conv_l_cache positions takes the place of attention.
     conv_layers: List[int] = field(default_factory=list)  # indices of the convolution layers
     conv_l_cache: int = 0  # kernel length
+    # Selective state-space layers (Mamba; the reference's SSM layer, model/inference/layers.rs:377): every layer is
+    # norm -> mixer -> residual; the mixer keeps a convolution window and a [d_inner, d_state] state per sequence.
+    ssm_d_inner: int = 0  # > 0: the layers are state-space layers
+    ssm_d_state: int = 0
+    ssm_d_conv: int = 0
+    ssm_dt_rank: int = 0
     # MoE
     n_experts: int = 0
     n_experts_used: int = 0
@@ -120,6 +127,10 @@ class ModelConfig:
     @property
     def is_mla(self) -> bool:
         return self.kv_lora_rank > 0
+
+    @property
+    def is_ssm(self) -> bool:
+        return self.ssm_d_inner > 0
 
     @property
     def rotary_dim(self) -> int:
@@ -187,6 +198,18 @@ def config_from_gguf(g: GGUFFile) -> ModelConfig:
     if a("vocab_size") is None and emb is None and toks:
         c.vocab_size = len(toks)
     c.n_layers = int(_scalar(a("block_count"), c.n_layers))
+    if arch == "mamba":
+        c.ssm_d_inner = int(_scalar(a("ssm.inner_size"), g.tensors["blk.0.ssm_in.weight"].shape[0] // 2))
+        c.ssm_d_state = int(_scalar(a("ssm.state_size"), g.tensors["blk.0.ssm_a"].shape[-1]))
+        c.ssm_d_conv = int(_scalar(a("ssm.conv_kernel"), g.tensors["blk.0.ssm_conv1d.weight"].shape[-1]))
+        c.ssm_dt_rank = int(_scalar(a("ssm.time_step_rank"), g.tensors["blk.0.ssm_dt.weight"].shape[-1]))
+        c.rms_eps = float(_scalar(a("attention.layer_norm_rms_epsilon"), 1e-5))
+        c.context_length = int(_scalar(a("context_length"), 1 << 20))
+        c.n_heads = c.n_kv_heads = 1
+        c.head_dim = 32  # no attention: only sizes a token cache that is never written
+        c.ffn_size = 0
+        c.tie_embeddings = not g.has_tensor("output.weight")
+        return c
     c.nextn_layers = int(_scalar(a("nextn_predict_layers"), 0))
     c.n_heads = int(_scalar(a("attention.head_count"), c.n_heads))
     kvh = a("attention.head_count_kv")

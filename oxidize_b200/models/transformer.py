@@ -130,6 +130,13 @@ class Transformer:
             self.conv_index.append(sum(1 for j in range(li) if j in conv) if is_conv else -1)
         self.n_kv_layers = sum(1 for i in self.kv_index if i >= 0)
         self.n_conv_layers = len(weights.layers) - self.n_kv_layers
+        # state-space layers: per-sequence recurrent state (convolution window + [d_inner, d_state] state per layer), in
+        # slots found through the sequence's first page (see _ssm_slot)
+        self._ssm_slots: dict = {}
+        self._ssm_conv = self._ssm_state = None
+        self._ssm_clock = 0
+        if cfg.is_ssm:
+            self.n_kv_layers = 0
         if cfg.is_mla:
             # One cached row per token, shared by all heads: the normalised latent followed by the rotary key.
             self.n_kv_local = 1
@@ -254,6 +261,73 @@ class Transformer:
             kv.conv = KVCache(KVCacheSpec(self.n_conv_layers, 1, self.cfg.hidden_size // 2, page_size, plain), num_blocks,
                               self.device)
         return kv
+
+    def _ssm_slot(self, kv, first_block: int, position: int) -> int:
+        """State slot of the sequence whose first page is ``first_block`` in cache ``kv``.  A sequence keeps its first page
+        for as long as it runs (prefix sharing is off for these models), a new or restarted sequence shows up at position 0
+        and gets a cleared slot; slots not touched for many steps are handed to newcomers."""
+        cfg = self.cfg
+        key = (id(kv), first_block)
+        ent = self._ssm_slots.get(key)
+        if ent is None or position == 0:
+            if ent is None:
+                used = {v[0] for v in self._ssm_slots.values()}
+                n = 0 if self._ssm_state is None else self._ssm_state.shape[0]
+                slot = next((i for i in range(n) if i not in used), None)
+                if slot is None:
+                    stale = [k for k, v in self._ssm_slots.items() if self._ssm_clock - v[1] > 4096]
+                    if stale:
+                        slot = self._ssm_slots.pop(stale[0])[0]
+                    else:  # grow by one block of slots
+                        L, di = len(self.w.layers), cfg.ssm_d_inner
+                        add_c = torch.zeros(16, L, di, max(1, cfg.ssm_d_conv - 1), dtype=torch.float32, device=self.device)
+                        add_s = torch.zeros(16, L, di, cfg.ssm_d_state, dtype=torch.float32, device=self.device)
+                        self._ssm_conv = add_c if self._ssm_conv is None else torch.cat([self._ssm_conv, add_c])
+                        self._ssm_state = add_s if self._ssm_state is None else torch.cat([self._ssm_state, add_s])
+                        slot = n
+                ent = [slot, self._ssm_clock]
+                self._ssm_slots[key] = ent
+            if position == 0:
+                self._ssm_conv[ent[0]].zero_()
+                self._ssm_state[ent[0]].zero_()
+        ent[1] = self._ssm_clock
+        return ent[0]
+
+    def _mamba(self, lw: LayerWeights, layer: int, x: torch.Tensor, meta: BatchMeta, kv) -> torch.Tensor:
+        """Selective state-space mixer, sequence by sequence and token by token (the recurrence is sequential):
+        (u, z) = in_proj(x); u = silu(conv(u)); (dt, B, C) = x_proj(u); dt = softplus(dt_proj(dt) + b);
+        h = exp(A dt) h + dt B u; y = (h C + D u) silu(z); out_proj(y)."""
+        cfg, m = self.cfg, lw.ssm
+        di, N, K, R = cfg.ssm_d_inner, cfg.ssm_d_state, cfg.ssm_d_conv, cfg.ssm_dt_rank
+        xz = ops.linear(x, m.in_proj).float()
+        u_all, z_all = xz[:, :di], xz[:, di:]
+        qs, first = meta.query_start.tolist(), meta.block_tables[:, 0].tolist()
+        pos0 = meta.positions.tolist()
+        w, A, D = m.conv_kernel.float(), m.a.float(), m.d.float()
+        y = torch.empty_like(u_all)
+        if layer == 0:
+            self._ssm_clock += 1
+        for b in range(len(qs) - 1):
+            t0, t1 = qs[b], qs[b + 1]
+            if t1 == t0:
+                continue
+            slot = self._ssm_slot(kv, first[b], pos0[t0] if layer == 0 else -1)
+            win = torch.cat([self._ssm_conv[slot, layer], u_all[t0:t1].t()], dim=1)  # [di, K-1 + n]
+            conv = sum(w[:, j : j + 1] * win[:, j : j + (t1 - t0)] for j in range(K))
+            if m.conv_bias is not None:
+                conv = conv + m.conv_bias.float()[:, None]
+            uc = torch.nn.functional.silu(conv).t().contiguous()  # [n, di]
+            self._ssm_conv[slot, layer] = win[:, -(K - 1):] if K > 1 else win[:, :0]
+            par = ops.linear(uc.to(x.dtype), m.x_proj).float()
+            # (the step-size projection is a few dozen columns wide: a plain product on the decoded matrix)
+            dt = torch.nn.functional.softplus(par[:, :R] @ m.dt_proj.dense_cache().float().t() + m.dt_bias.float())
+            Bm, Cm = par[:, R : R + N], par[:, R + N :]
+            h = self._ssm_state[slot, layer]
+            for i in range(t1 - t0):
+                h = torch.exp(A * dt[i][:, None]) * h + (dt[i] * uc[i])[:, None] * Bm[i][None, :]
+                y[t0 + i] = h @ Cm[i] + D * uc[i]
+            self._ssm_state[slot, layer] = h
+        return ops.linear((y * torch.nn.functional.silu(z_all)).to(x.dtype), m.out_proj)
 
     def _short_conv(self, lw: LayerWeights, layer: int, x: torch.Tensor, meta: BatchMeta, kv) -> torch.Tensor:
         """LFM2 mixer: (B, C, v) = in_proj(x); u = B * v; y_t = C_t * sum_j w[:, j] u_{t - (L-1) + j}; out_proj(y).  The rows u
@@ -417,6 +491,11 @@ class Transformer:
                 # leave the folded form: h + residual must again be the hidden state
                 h, acc = torch.zeros_like(residual), None
             x, residual = ops.add_rmsnorm(h, residual, lw.attn_norm, cfg.rms_eps)
+            if lw.ssm is not None:  # norm -> mixer -> residual; no feed-forward block
+                h = self._mamba(lw, li, x, meta, kv)
+                if capture is not None and gl in capture.get("layers", ()):
+                    capture.setdefault("hidden", {})[gl] = (h.float() + residual.float())
+                continue
             h = self._attention(lw, li, x, meta, kv)
             if lw.post_attn_norm is not None:
                 h = ops.rmsnorm(h, lw.post_attn_norm, cfg.rms_eps)

@@ -179,11 +179,27 @@ class MLAWeights:
 
 
 @dataclass
+class SSMWeights:
+    """Mamba mixer: in_proj [2 d_inner, hidden] (rows: x then gate), depthwise kernel [d_inner, d_conv] + bias, x_proj
+    [dt_rank + 2 d_state, d_inner], dt_proj [d_inner, dt_rank] + bias, A [d_inner, d_state] (already -exp(A_log)), D, out_proj."""
+
+    in_proj: QTensor
+    conv_kernel: torch.Tensor
+    conv_bias: Optional[torch.Tensor]
+    x_proj: QTensor
+    dt_proj: QTensor
+    dt_bias: torch.Tensor
+    a: torch.Tensor
+    d: torch.Tensor
+    out_proj: LinearWeight
+
+
+@dataclass
 class LayerWeights:
     attn_norm: torch.Tensor
     wqkv: Optional[LinearWeight]  # None in a latent-attention layer (``mla`` holds its projections) or a convolution layer
     wo: Optional[LinearWeight]
-    ffn_norm: torch.Tensor
+    ffn_norm: Optional[torch.Tensor]
     q_norm: Optional[torch.Tensor] = None
     k_norm: Optional[torch.Tensor] = None
     mla: Optional[MLAWeights] = None
@@ -192,6 +208,7 @@ class LayerWeights:
     conv_in: Optional[QTensor] = None
     conv_kernel: Optional[torch.Tensor] = None
     conv_out: Optional[LinearWeight] = None
+    ssm: Optional[SSMWeights] = None  # a state-space layer: no attention and no feed-forward block
     # Gemma-2/3: norms applied to the attention / FFN branch outputs before the residual add
     post_attn_norm: Optional[torch.Tensor] = None
     post_ffn_norm: Optional[torch.Tensor] = None
@@ -415,6 +432,16 @@ def _load_layer(src: GGUFWeightSource, cfg: ModelConfig, i: int, tp_rank: int, t
     k0, k1 = shard_range(cfg.n_kv_heads, tp_rank // kv_rep, kv_shards)
     qr, kr = (q0 * hd, q1 * hd), (k0 * hd, k1 * hd)
     mla = None
+    if src.has(f"{p}.ssm_in.weight"):
+        if tp_size > 1:
+            raise ValueError("state-space layers are not sharded: run this model with tp_size = 1")
+        di = cfg.ssm_d_inner
+        ssm = SSMWeights(in_proj=src.matrix(f"{p}.ssm_in.weight"), conv_kernel=src.vector(f"{p}.ssm_conv1d.weight").reshape(di, -1),
+                         conv_bias=src.vector(f"{p}.ssm_conv1d.bias") if src.has(f"{p}.ssm_conv1d.bias") else None,
+                         x_proj=src.matrix(f"{p}.ssm_x.weight"), dt_proj=src.matrix(f"{p}.ssm_dt.weight"),
+                         dt_bias=src.vector(f"{p}.ssm_dt.bias"), a=src.vector(f"{p}.ssm_a").reshape(di, -1),
+                         d=src.vector(f"{p}.ssm_d"), out_proj=LinearWeight([src.matrix(f"{p}.ssm_out.weight")]))
+        return LayerWeights(attn_norm=src.vector(f"{p}.attn_norm.weight"), wqkv=None, wo=None, ffn_norm=None, ssm=ssm)
     if src.has(f"{p}.shortconv.conv.weight"):
         if tp_size > 1:
             raise ValueError("short-convolution layers are not sharded: run this model with tp_size = 1")

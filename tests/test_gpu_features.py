@@ -197,3 +197,32 @@ def test_short_convolution_model_on_the_device(tmp_path):
     out = gpu.generate(PROMPTS, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
     assert all(len(o.token_ids) == 8 for o in out)
     _status_ok()
+
+
+def test_state_space_model_on_the_device(tmp_path):
+    """Mamba on the device (projections on the GEMM kernels, the recurrence as torch products driven from the host)
+    against the CPU path, teacher-forced, then free-running decode of two sequences."""
+    T = pytest.importorskip("transformers")
+    from oxidize_b200.formats.convert import convert_safetensors_to_gguf
+
+    torch.manual_seed(0)
+    ref = T.MambaForCausalLM(T.MambaConfig(vocab_size=512, hidden_size=256, state_size=16, num_hidden_layers=3, conv_kernel=4,
+                                           expand=2, time_step_rank=64))
+    with torch.no_grad():
+        for n, p in ref.named_parameters():
+            if p.ndim == 2:
+                p.mul_(2.0)
+    src = str(tmp_path / "hf")
+    ref.save_pretrained(src, safe_serialization=True)
+    path = convert_safetensors_to_gguf(src, str(tmp_path / "mamba.gguf"), "BF16")
+    cpu = LLM.from_gguf(path, EngineConfig(**EC), device="cpu")
+    gpu = LLM.from_gguf(path, EngineConfig(**EC), device="cuda")
+    prompts = [list(p) for p in PROMPTS]
+    for _ in range(3):
+        lc = torch.from_numpy(cpu.next_token_logits(prompts))
+        lg = torch.from_numpy(gpu.next_token_logits(prompts))
+        assert _rel(lg, lc) < 5e-2
+        prompts = [p + [int(lc[i].argmax())] for i, p in enumerate(prompts)]
+    out = gpu.generate(PROMPTS, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    assert all(len(o.token_ids) == 8 for o in out)
+    _status_ok()

@@ -9,7 +9,8 @@ scaled embeddings, GeGLU, norms on the branch outputs, (w + 1) norm weights, sof
 scale taken from query_pre_attn_scalar, and local / global layers with a window and two rotary bases; for DeepSeek-V2/V3
 the latent attention (low-rank and full-rank queries, shared rotary key, interleaved rotary pairs, YaRN), softmax and
 sigmoid group-limited routing with a selection bias, the shared expert and the leading dense layer; for LFM2 the gated
-short-convolution layers, whose history lives in a second paged cache and crosses prefill chunks.
+short-convolution layers, whose history lives in a second paged cache and crosses prefill chunks; for Mamba the selective
+state-space recurrence with its per-sequence state carried across chunks and decode steps.
 """
 import os
 
@@ -53,6 +54,9 @@ def _build(name: str):
         # 7 layers: five windowed (rotary base 1e4), the sixth global (base 1e6), the seventh windowed again
         c["num_hidden_layers"] = 7
         return T.Gemma3ForCausalLM(T.Gemma3TextConfig(**c, head_dim=32, sliding_window=8, query_pre_attn_scalar=40))
+    if name == "mamba":  # selective state-space layers only: convolution window of 4, 8-wide state, no attention, no MLP
+        return T.MambaForCausalLM(T.MambaConfig(vocab_size=VOCAB, hidden_size=64, state_size=8, num_hidden_layers=3, conv_kernel=4,
+                                                expand=2, time_step_rank=8))
     if name == "lfm2":  # convolution layers (kernel of 3 taps) around two attention layers with RMSNorm on q / k heads
         return T.Lfm2ForCausalLM(T.Lfm2Config(**c, conv_L_cache=3, block_auto_adjust_ff_dim=False,
                                               layer_types=["conv", "conv", "full_attention", "conv"]))
@@ -74,7 +78,7 @@ def _build(name: str):
 
 
 FAMILIES = ["llama", "qwen2", "qwen3", "phi3", "mixtral", "qwen3moe", "gemma", "gemma2", "gemma3", "deepseek_v2", "deepseek_v3",
-            "deepseek_v3_yarn", "lfm2"]
+            "deepseek_v3_yarn", "lfm2", "mamba"]
 
 
 @pytest.mark.parametrize("family", FAMILIES)
@@ -101,6 +105,8 @@ def test_logits_and_greedy_tokens_match_transformers(family, tmp_path):
         assert cfg.is_mla and (cfg.kv_lora_rank, cfg.qk_nope_dim, cfg.rope_dim, cfg.v_head_dim, cfg.head_dim) == (32, 16, 8, 24, 24)
         assert cfg.rope_pairing == "adjacent" and cfg.n_shared_experts == 1 and cfg.leading_dense_blocks == 1
         assert cfg.expert_gating == ("softmax" if family == "deepseek_v2" else "sigmoid")
+    if family == "mamba":
+        assert cfg.is_ssm and (cfg.ssm_d_inner, cfg.ssm_d_state, cfg.ssm_d_conv, cfg.ssm_dt_rank) == (128, 8, 4, 8)
     if family == "lfm2":
         assert cfg.conv_layers == [0, 1, 3] and cfg.conv_l_cache == 3 and cfg.qk_norm and cfg.n_kv_heads == 2
     if family == "gemma3":
@@ -133,3 +139,47 @@ def test_logits_and_greedy_tokens_match_transformers(family, tmp_path):
         assert err < 2e-5, f"{family}, {n_prompt}-token prompt: logits differ by {err:.2e} of their range"
         assert tokens == want_tokens, f"{family}, {n_prompt}-token prompt: {tokens} != {want_tokens}"
     assert os.path.getsize(path) > 0
+
+
+def test_state_space_model_through_the_scheduler(tmp_path):
+    """Mamba's per-sequence state under continuous batching: batched == one at a time, a pool small enough to preempt ==
+    a roomy one (a restarted sequence recomputes its state from position 0), more sequential requests than state slots,
+    no prefix sharing, no speculation."""
+    torch.manual_seed(1)
+    ref = _build("mamba").eval().float()
+    with torch.no_grad():
+        for pname, p in ref.named_parameters():
+            if p.ndim == 2:
+                p.mul_(2.0)
+    src = str(tmp_path / "hf")
+    ref.save_pretrained(src, safe_serialization=True)
+    path = convert_safetensors_to_gguf(src, str(tmp_path / "m.gguf"), "F32")
+    ec = dict(kv_cache_dtype="f32", max_model_len=128, max_num_seqs=4, prefill_chunk_size=16, max_num_batched_tokens=32)
+    gen = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(3, VOCAB, (n,), generator=gen).tolist() for n in (5, 33, 18, 50, 7, 26)]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    roomy = LLM.from_gguf(path, EngineConfig(**ec, num_kv_blocks=64), device="cpu")
+    assert not roomy.scheduler.config.enable_prefix_cache
+    one_by_one = [roomy.generate([p], sp)[0].token_ids for p in prompts]
+    assert [o.token_ids for o in roomy.generate(prompts, sp)] == one_by_one
+    with torch.no_grad():
+        want0 = ref.generate(torch.tensor([prompts[1]]), max_new_tokens=12, do_sample=False)[0, len(prompts[1]):].tolist()
+    assert one_by_one[1] == want0
+    # short prompts that grow: all four are admitted, then the pool runs dry and the scheduler evicts and recomputes
+    growers = [p[:14] for p in prompts if len(p) >= 14]
+    long_sp = SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True)
+    want_long = [o.token_ids for o in roomy.generate(growers, long_sp)]
+    small = LLM.from_gguf(path, EngineConfig(**ec, num_kv_blocks=10), device="cpu")
+    assert [o.token_ids for o in small.generate(growers, long_sp)] == want_long and small.scheduler.num_preemptions > 0
+    # the same prompt twice in a row: identical (nothing of the first run's state leaks into the second)
+    again = [roomy.generate([prompts[3]], sp)[0].token_ids for _ in range(2)]
+    assert again[0] == again[1] == one_by_one[3]
+    # more requests over time than one block of state slots
+    for i in range(20):
+        assert roomy.generate([prompts[i % 6]], SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))[0].token_ids \
+            == one_by_one[i % 6][:2]
+    assert roomy.model._ssm_state.shape[0] <= 32
+    from oxidize_b200.engine.spec import attach_speculation
+
+    with pytest.raises(ValueError):
+        attach_speculation(roomy, path, k=2)
