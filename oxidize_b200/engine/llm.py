@@ -443,6 +443,7 @@ class LLM:
             h, residual = m.run_layers(m.embed(meta.token_ids), None, meta, kv)
             from .. import ops
 
+            m.release_state(kv)
             x = ops.add_rmsnorm(h, residual, m.w.out_norm, m.cfg.rms_eps)[0].float()
             v = x.mean(dim=0) if pooling == "mean" else x[-1]
             if normalize:
@@ -478,6 +479,7 @@ class LLM:
             lp = torch.log_softmax(m.forward(meta, kv).float(), dim=-1)
             tgt = torch.tensor(ids[lo + 1 : hi + 1], dtype=torch.int64, device=dev)
             out[lo:hi] = lp.gather(1, tgt[:, None]).squeeze(1).double().cpu().numpy()
+        m.release_state(kv)
         return out
 
     def perplexity(self, text: Union[str, Seq[int]], chunk: int = 256) -> float:

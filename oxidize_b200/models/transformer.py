@@ -269,6 +269,9 @@ class Transformer:
         cfg = self.cfg
         key = (id(kv), first_block)
         ent = self._ssm_slots.get(key)
+        if ent is None and position != 0:
+            raise RuntimeError("the recurrent state of a running sequence is gone (its slot was handed on after "
+                               "thousands of steps without a row of that sequence)")
         if ent is None or position == 0:
             if ent is None:
                 used = {v[0] for v in self._ssm_slots.values()}
@@ -292,6 +295,11 @@ class Transformer:
                 self._ssm_state[ent[0]].zero_()
         ent[1] = self._ssm_clock
         return ent[0]
+
+    def release_state(self, kv) -> None:
+        """Forget the state slots of every sequence of cache ``kv`` (a cache that lived for one call)."""
+        for key in [k for k in self._ssm_slots if k[0] == id(kv)]:
+            del self._ssm_slots[key]
 
     def _mamba(self, lw: LayerWeights, layer: int, x: torch.Tensor, meta: BatchMeta, kv) -> torch.Tensor:
         """Selective state-space mixer, sequence by sequence and token by token (the recurrence is sequential):

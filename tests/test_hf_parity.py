@@ -179,6 +179,16 @@ def test_state_space_model_through_the_scheduler(tmp_path):
         assert roomy.generate([prompts[i % 6]], SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))[0].token_ids \
             == one_by_one[i % 6][:2]
     assert roomy.model._ssm_state.shape[0] <= 32
+    # calls that bring a cache of their own (embeddings, scoring) give their state slots back
+    n_keys = len(roomy.model._ssm_slots)
+    for _ in range(40):
+        roomy.embed([prompts[0]])
+    lp = roomy.token_logprobs(prompts[1] + one_by_one[1], chunk=16)
+    assert len(roomy.model._ssm_slots) == n_keys and roomy.model._ssm_state.shape[0] <= 32
+    with torch.no_grad():
+        full = torch.tensor([prompts[1] + one_by_one[1]])
+        ref_lp = torch.log_softmax(ref(full).logits[0, :-1].double(), -1).gather(1, full[0, 1:, None])[:, 0]
+    assert torch.allclose(torch.from_numpy(lp), ref_lp, atol=1e-4)
     from oxidize_b200.engine.spec import attach_speculation
 
     with pytest.raises(ValueError):
