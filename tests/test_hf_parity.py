@@ -54,6 +54,12 @@ def _build(name: str):
         # 7 layers: five windowed (rotary base 1e4), the sixth global (base 1e6), the seventh windowed again
         c["num_hidden_layers"] = 7
         return T.Gemma3ForCausalLM(T.Gemma3TextConfig(**c, head_dim=32, sliding_window=8, query_pre_attn_scalar=40))
+    if name == "mistral_swa":  # every layer windowed (8 tokens): the engine also returns pages that fell out of the window
+        return T.MistralForCausalLM(T.MistralConfig(**c, sliding_window=8))
+    if name == "qwen2moe":  # routed experts without renormalised weights + a sigmoid-gated shared expert, q/k/v biases
+        return T.Qwen2MoeForCausalLM(T.Qwen2MoeConfig(**c, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=48,
+                                                      shared_expert_intermediate_size=80, norm_topk_prob=False,
+                                                      decoder_sparse_step=1, mlp_only_layers=[]))
     if name == "mamba":  # selective state-space layers only: convolution window of 4, 8-wide state, no attention, no MLP
         return T.MambaForCausalLM(T.MambaConfig(vocab_size=VOCAB, hidden_size=64, state_size=8, num_hidden_layers=3, conv_kernel=4,
                                                 expand=2, time_step_rank=8))
@@ -78,7 +84,7 @@ def _build(name: str):
 
 
 FAMILIES = ["llama", "qwen2", "qwen3", "phi3", "mixtral", "qwen3moe", "gemma", "gemma2", "gemma3", "deepseek_v2", "deepseek_v3",
-            "deepseek_v3_yarn", "lfm2", "mamba"]
+            "deepseek_v3_yarn", "lfm2", "mamba", "mistral_swa", "qwen2moe"]
 
 
 @pytest.mark.parametrize("family", FAMILIES)
@@ -105,6 +111,11 @@ def test_logits_and_greedy_tokens_match_transformers(family, tmp_path):
         assert cfg.is_mla and (cfg.kv_lora_rank, cfg.qk_nope_dim, cfg.rope_dim, cfg.v_head_dim, cfg.head_dim) == (32, 16, 8, 24, 24)
         assert cfg.rope_pairing == "adjacent" and cfg.n_shared_experts == 1 and cfg.leading_dense_blocks == 1
         assert cfg.expert_gating == ("softmax" if family == "deepseek_v2" else "sigmoid")
+    if family == "mistral_swa":
+        assert cfg.sliding_window == 8 and cfg.sliding_window_pattern == 0
+    if family == "qwen2moe":
+        assert cfg.n_shared_experts == 1 and cfg.shared_expert_gate and cfg.shared_expert_ffn_size == 80 and cfg.attn_bias
+        assert not cfg.expert_weights_norm
     if family == "mamba":
         assert cfg.is_ssm and (cfg.ssm_d_inner, cfg.ssm_d_state, cfg.ssm_d_conv, cfg.ssm_dt_rank) == (128, 8, 4, 8)
     if family == "lfm2":
