@@ -49,6 +49,40 @@ def _rope_settings(c: Dict[str, Any]) -> Tuple[float, float, Dict[str, Any]]:
     return theta, float(c.get("rope_local_base_freq") or 0.0), (rp if rp.get("rope_type") else c.get("rope_scaling") or {})
 
 
+def rope_factor_tensors(c: Dict[str, Any]) -> Dict[str, np.ndarray]:
+    """Per-frequency divisors that a checkpoint's rotary scaling implies, as the tensors files carry them:
+    ``rope_freqs.weight`` for the Llama-3.1 rule (low frequencies divided by ``factor``, high ones kept, a smooth ramp
+    between), ``rope_factors_short / _long.weight`` for LongRoPE (Phi-3)."""
+    import math
+
+    _, _, rs = _rope_settings(c)
+    kind = str(rs.get("rope_type") or rs.get("type") or "")
+    if kind not in ("llama3", "longrope", "su", "yarn_long"):
+        return {}
+    heads = int(c["num_attention_heads"])
+    hd = int(c.get("head_dim") or int(c["hidden_size"]) // heads)
+    rot = int(hd * float(c.get("partial_rotary_factor", 1.0)))
+    if kind == "llama3":
+        theta = float(rs.get("rope_theta") or c.get("rope_theta") or 10000.0)
+        factor, lo, hi = float(rs.get("factor", 8.0)), float(rs.get("low_freq_factor", 1.0)), float(rs.get("high_freq_factor", 4.0))
+        orig = float(rs.get("original_max_position_embeddings", 8192))
+        out = []
+        for i in range(0, rot, 2):
+            wavelen = 2 * math.pi * theta ** (i / rot)
+            if wavelen < orig / hi:
+                out.append(1.0)
+            elif wavelen > orig / lo:
+                out.append(factor)
+            else:
+                smooth = (orig / wavelen - lo) / (hi - lo)
+                out.append(1.0 / ((1.0 - smooth) / factor + smooth))
+        return {"rope_freqs.weight": np.asarray(out, dtype=np.float32)}
+    if kind in ("longrope", "su", "yarn_long") and rs.get("short_factor") is not None:
+        return {"rope_factors_short.weight": np.asarray(rs["short_factor"], dtype=np.float32),
+                "rope_factors_long.weight": np.asarray(rs["long_factor"], dtype=np.float32)}
+    return {}
+
+
 def write_mamba_metadata(w: GGUFWriter, c: Dict[str, Any]) -> None:
     U, F = GGUFValueType.UINT32, GGUFValueType.FLOAT32
     hidden = int(c["hidden_size"])
@@ -126,6 +160,18 @@ def write_hf_metadata(w: GGUFWriter, arch: str, c: Dict[str, Any]) -> None:
             w.add(f"{arch}.attention.scale", float(c["query_pre_attn_scalar"]) ** -0.5, F)
     if rs.get("type") or rs.get("rope_type"):
         kind = str(rs.get("type") or rs.get("rope_type"))
+        if kind in ("longrope", "su") and rs.get("short_factor") is not None:
+            # LongRoPE: the factor tensors carry the scaling; the metadata says where the long set takes over and by how
+            # much the rotated vectors are magnified then
+            import math
+
+            orig = int(rs.get("original_max_position_embeddings") or c.get("original_max_position_embeddings")
+                       or c.get("max_position_embeddings", 0))
+            scale = float(c.get("max_position_embeddings", orig)) / max(orig, 1)
+            w.add(f"{arch}.rope.scaling.original_context_length", orig, U)
+            att = rs.get("attention_factor")
+            w.add(f"{arch}.rope.scaling.attn_factor",
+                  float(att) if att else (math.sqrt(1 + math.log(scale) / math.log(orig)) if scale > 1 else 1.0), F)
         if kind in ("linear", "yarn"):
             w.add(f"{arch}.rope.scaling.type", kind)
             w.add(f"{arch}.rope.scaling.factor", float(rs.get("factor", 1.0)), F)
@@ -217,6 +263,8 @@ def convert_safetensors_to_gguf(src_dir: str, out_path: str, quant: str = "F16",
 
         t = encode(gname, np.zeros(shape[-1:] if len(shape) == 1 else (1, shape[-1]), dtype=np.float32))[1]
         w.add_tensor(gname, gen, shape, t)
+    for tname, arr in rope_factor_tensors(cfg).items():
+        w.add_tensor(tname, arr, arr.shape, "F32")
     for gname, per in experts.items():
         n = max(per) + 1
         f0, n0 = per[0]

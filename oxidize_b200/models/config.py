@@ -239,6 +239,9 @@ def config_from_gguf(g: GGUFFile) -> ModelConfig:
             factor=float(_scalar(a("rope.scaling.factor"), 1.0)),
             original_context_length=int(_scalar(a("rope.scaling.original_context_length"), 0)),
         )
+    elif a("rope.scaling.original_context_length"):
+        # LongRoPE files: no scaling rule, only the context length up to which the short frequency factors apply
+        c.rope_scaling = RopeScaling(original_context_length=int(_scalar(a("rope.scaling.original_context_length"), 0)))
     c.context_length = int(_scalar(a("context_length"), 8192))
     c.sliding_window = int(_scalar(a("attention.sliding_window"), 0))
     c.sliding_window_pattern = int(_scalar(a("attention.sliding_window_pattern"), 0))
