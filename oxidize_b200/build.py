@@ -69,7 +69,7 @@ def build_kernels(force: bool = False, verbose: bool = False) -> str:
 def build_runtime(force: bool = False) -> str:
     out = os.path.join(CSRC, "liboxbrt.so")
     srcs = _sources((".cpp", ".hpp", ".h"))
-    cpps = [s for s in srcs if s.endswith(".cpp")]
+    cpps = [s for s in srcs if s.endswith(".cpp") and os.path.basename(s) != "ffi.cpp"]  # ffi.cpp: build_ffi
     if not cpps:
         return ""
     if not force and _newer(out, srcs):
@@ -82,8 +82,32 @@ def build_runtime(force: bool = False) -> str:
     return out
 
 
+def build_ffi(force: bool = False) -> str:
+    """``liboxidize_ffi.so``: the C ABI over the whole engine (``csrc/oxidize_ffi.h``), a shim that embeds this Python
+    interpreter.  The interpreter's path and the package's location are compiled in as defaults."""
+    import sysconfig
+
+    src = os.path.join(CSRC, "ffi.cpp")
+    out = os.path.join(CSRC, "liboxidize_ffi.so")
+    inc = sysconfig.get_config_var("INCLUDEPY") or ""
+    if not os.path.exists(src) or not os.path.exists(os.path.join(inc, "Python.h")):
+        return ""  # no interpreter headers on this machine: the engine itself does not need the shim
+    if not force and _newer(out, [src, os.path.join(CSRC, "oxidize_ffi.h")]):
+        return out
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    libdir = sysconfig.get_config_var("LIBDIR") or ""
+    cxx = shutil.which("g++") or "g++"
+    cmd = [cxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-o", out, src, f"-I{inc}", f"-L{libdir}",
+           f"-lpython{sysconfig.get_config_var('LDVERSION')}", f"-Wl,-rpath,{libdir}",
+           f'-DOXIDIZE_DEFAULT_PYTHON="{sys.executable}"', f'-DOXIDIZE_DEFAULT_ROOT="{root}"']
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("g++ (ffi) failed:\n" + r.stdout + r.stderr)
+    return out
+
+
 def build_all(force: bool = False, verbose: bool = False):
-    return build_kernels(force, verbose), build_runtime(force)
+    return build_kernels(force, verbose), build_runtime(force), build_ffi(force)
 
 
 if __name__ == "__main__":
