@@ -2,7 +2,7 @@
  *
  * The library embeds the Python interpreter the package was built with; the first call starts it (or joins the one that
  * is already running when the library is loaded from Python).  OXIDIZE_PYTHON names another interpreter,
- * OXIDIZE_PACKAGE_ROOT another checkout of the package.  All functions may be called from any thread; calls are
+ * OXIDIZE_PACKAGE_ROOT another checkout of the package, OXIDIZE_FFI_DEVICE ("cpu", "cuda:1", ...) the device models load on.  All functions may be called from any thread; calls are
  * serialised by the interpreter lock.
  */
 #ifndef OXIDIZE_FFI_H

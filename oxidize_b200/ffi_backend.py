@@ -29,7 +29,9 @@ class Session:
 def model_load(path: str, device: Optional[str] = None):
     from .engine.llm import LLM, EngineConfig
 
-    device = device or ("cuda" if torch.cuda.is_available() else "cpu")
+    import os
+
+    device = device or os.environ.get("OXIDIZE_FFI_DEVICE") or ("cuda" if torch.cuda.is_available() else "cpu")
     return LLM.from_gguf(path, EngineConfig(max_num_seqs=1, num_kv_blocks=8, cuda_graphs=False), device=device)
 
 

@@ -50,7 +50,7 @@ def _lib():
 
 
 def test_c_abi_in_process(model_path, monkeypatch):
-    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    monkeypatch.setenv("OXIDIZE_FFI_DEVICE", "cpu")
     L = _lib()
     assert b"oxidize" in L.oxidize_ffi_version()
     m = L.oxidize_model_load(model_path.encode())
@@ -131,7 +131,7 @@ def test_c_program_embeds_the_interpreter(model_path, tmp_path):
     src.write_text(C_PROGRAM)
     exe = str(tmp_path / "main")
     subprocess.run([cc, "-O1", "-o", exe, str(src), f"-I{CSRC}", f"-L{CSRC}", "-loxidize_ffi", f"-Wl,-rpath,{CSRC}"], check=True)
-    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OXIDIZE_PYTHON=sys.executable)
+    env = dict(os.environ, OXIDIZE_FFI_DEVICE="cpu", OXIDIZE_PYTHON=sys.executable)
     r = subprocess.run([exe, model_path], capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0, r.stderr[-2000:]
     got = [int(x) for x in r.stdout.split()]
