@@ -12,8 +12,10 @@ Adapters are written in the PEFT layout (``adapter_model.safetensors`` + ``adapt
 
     python -m oxidize_b200.offline.finetune --model base.gguf --data sft.jsonl --output out_dir --steps 200 \\
         [--qlora] [--resume-from out_dir/round-0003] [--self-train-rounds 2 --prompts prompts.txt] [--merge-output merged.gguf]
+        [--dpo-data prefs.jsonl --dpo-beta 0.1]
 
-Data: JSON lines with ``{"prompt": ..., "completion": ...}`` (loss on the completion only), ``{"text": ...}`` (loss on
+Preference training (``dpo.rs`` in the reference) is direct preference optimisation with the adapter-free base as the
+reference policy.  Data: JSON lines with ``{"prompt": ..., "completion": ...}`` (loss on the completion only), ``{"text": ...}`` (loss on
 every token) or ``{"messages": [...]}`` (rendered with the model's chat template; loss on the last assistant turn).
 """
 from __future__ import annotations
@@ -126,9 +128,11 @@ class LoraModel(torch.nn.Module):
         i, t = key.split("_", 1)
         return f"base_model.model.model.layers.{i}.{_HF_MODULE[t]}"
 
+    adapters_on = True  # False: the forward is the frozen base model (the reference policy of preference training)
+
     def _delta(self, layer: int, target: str, x: torch.Tensor) -> Optional[torch.Tensor]:
         key = f"{layer}_{target}"
-        if key not in self.A:
+        if key not in self.A or not self.adapters_on:
             return None
         if self.training and self.lora.dropout > 0:
             x = F.dropout(x, self.lora.dropout)
@@ -203,7 +207,7 @@ class LoraModel(torch.nn.Module):
             x = x + f
         x = self._norm(x, w.out_norm, cfg.rms_eps)
         logits = x @ self._dense(w.lm_head).t()
-        if "head" in self.A:
+        if "head" in self.A and self.adapters_on:
             logits = logits + (x @ self.A["head"].t()) @ self.B["head"].t() * self.lora.scale
         if cfg.final_softcap > 0:
             logits = torch.tanh(logits / cfg.final_softcap) * cfg.final_softcap
@@ -290,6 +294,73 @@ def batch_loss(model: LoraModel, batch: Sequence[Example]) -> torch.Tensor:
     return F.cross_entropy(logits.reshape(-1, logits.shape[-1]), tgt.reshape(-1), ignore_index=-100)
 
 
+# --------------------------------------------------------------------------- preference pairs (DPO)
+
+
+@dataclass
+class PreferencePair:
+    chosen: Example
+    rejected: Example
+
+
+def load_preference_pairs(path: str, tokenizer, max_seq_len: int) -> List[PreferencePair]:
+    """JSON lines ``{"prompt": ..., "chosen": ..., "rejected": ...}``."""
+    out: List[PreferencePair] = []
+    eos = tokenizer.special_tokens.eos
+    tail = [eos] if eos is not None and eos >= 0 else []
+    with open(path) as f:
+        for ln, line in enumerate(f, 1):
+            line = line.strip()
+            if not line:
+                continue
+            rec = json.loads(line)
+            if not all(k in rec for k in ("prompt", "chosen", "rejected")):
+                raise ValueError(f"{path}:{ln}: want prompt, chosen and rejected")
+            p = tokenizer.encode(str(rec["prompt"]))
+            pair = []
+            for key in ("chosen", "rejected"):
+                toks = (p + tokenizer.encode(str(rec[key])) + tail)[:max_seq_len]
+                if len(toks) <= len(p):
+                    break
+                pair.append(Example(toks, max(1, len(p))))
+            if len(pair) == 2:
+                out.append(PreferencePair(*pair))
+    if not out:
+        raise ValueError(f"{path}: no usable preference pairs")
+    return out
+
+
+def sequence_logprobs(model: "LoraModel", examples: Sequence[Example]) -> torch.Tensor:
+    """Sum of the target tokens' log-probabilities of every example, [len(examples)] (right-padded batch)."""
+    S = max(len(e.tokens) for e in examples)
+    toks = torch.zeros(len(examples), S, dtype=torch.int64)
+    tgt = torch.zeros(len(examples), S, dtype=torch.int64)
+    mask = torch.zeros(len(examples), S)
+    for b, e in enumerate(examples):
+        n = len(e.tokens)
+        toks[b, :n] = torch.tensor(e.tokens)
+        tgt[b, e.loss_from - 1 : n - 1] = torch.tensor(e.tokens[e.loss_from :])
+        mask[b, e.loss_from - 1 : n - 1] = 1.0
+    lp = torch.log_softmax(model(toks), dim=-1).gather(2, tgt[:, :, None]).squeeze(2)
+    return (lp * mask).sum(dim=1)
+
+
+def dpo_loss(model: "LoraModel", pairs: Sequence[PreferencePair], beta: float = 0.1) -> Tuple[torch.Tensor, float]:
+    """Direct preference optimisation (Rafailov et al. 2023): -log sigmoid(beta * ((pi_w - pi_l) - (ref_w - ref_l))) with
+    the adapter-free base model as the reference policy.  Returns (loss, fraction of pairs the policy already ranks right)."""
+    ex = [p.chosen for p in pairs] + [p.rejected for p in pairs]
+    pol = sequence_logprobs(model, ex)
+    model.adapters_on = False
+    try:
+        with torch.no_grad():
+            ref = sequence_logprobs(model, ex)
+    finally:
+        model.adapters_on = True
+    n = len(pairs)
+    margin = (pol[:n] - pol[n:]) - (ref[:n] - ref[n:])
+    return -F.logsigmoid(beta * margin).mean(), float((margin > 0).float().mean())
+
+
 # --------------------------------------------------------------------------- training
 
 
@@ -314,7 +385,9 @@ class Trainer:
             return c.lr * (step + 1) / c.warmup_steps
         return c.lr
 
-    def train(self, examples: Sequence[Example], steps: Optional[int] = None, checkpoint_dir: Optional[str] = None) -> List[float]:
+    def train(self, examples: Sequence, steps: Optional[int] = None, checkpoint_dir: Optional[str] = None,
+              dpo_beta: Optional[float] = None) -> List[float]:
+        """``examples``: supervised :class:`Example` s, or with ``dpo_beta`` :class:`PreferencePair` s."""
         c = self.cfg
         self.model.train()
         done: List[float] = []
@@ -323,7 +396,8 @@ class Trainer:
             for gp in self.opt.param_groups:
                 gp["lr"] = self._lr(self.state.step)
             self.opt.zero_grad(set_to_none=True)
-            loss = batch_loss(self.model, [examples[i] for i in idx])
+            batch = [examples[i] for i in idx]
+            loss = dpo_loss(self.model, batch, dpo_beta)[0] if dpo_beta is not None else batch_loss(self.model, batch)
             loss.backward()
             if c.grad_clip > 0:
                 torch.nn.utils.clip_grad_norm_(list(self.model.A.values()) + list(self.model.B.values()), c.grad_clip)
@@ -424,6 +498,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--prompts", help="text file, one prompt per line (self-training)")
     ap.add_argument("--self-train-max-new", type=int, default=64)
     ap.add_argument("--self-train-match", help="regular expression an answer must match to be kept")
+    ap.add_argument("--dpo-data", help="JSONL of prompt / chosen / rejected: preference training (DPO) after any --data pass")
+    ap.add_argument("--dpo-beta", type=float, default=0.1)
     ap.add_argument("--merge-output", help="also write the base with the adapter folded in, as a GGUF")
     a = ap.parse_args(argv)
     try:
@@ -444,6 +520,12 @@ def main(argv: Optional[List[str]] = None) -> int:
             ex = load_examples(a.data, tok, chat_template_from_metadata(g.metadata), a.max_seq_len)
             losses = trainer.train(ex, a.steps, a.output)
             print(f"trained {len(losses)} steps on {len(ex)} examples: loss {losses[0]:.4f} -> {losses[-1]:.4f}")
+            trainer.save_checkpoint(os.path.join(a.output, f"round-{trainer.state.round:04d}"))
+        if a.dpo_data:
+            pairs = load_preference_pairs(a.dpo_data, tok, a.max_seq_len)
+            losses = trainer.train(pairs, a.steps, a.output, dpo_beta=a.dpo_beta)
+            trainer.state.round += 1
+            print(f"preference training, {len(losses)} steps on {len(pairs)} pairs: loss {losses[0]:.4f} -> {losses[-1]:.4f}")
             trainer.save_checkpoint(os.path.join(a.output, f"round-{trainer.state.round:04d}"))
         if a.self_train_rounds:
             if not a.prompts:

@@ -143,3 +143,34 @@ def test_self_training_round_and_cli(tmp_path):
     moe = str(tmp_path / "moe.gguf")
     synth_gguf(moe, preset("mixtral-8x7b", **SMALL, n_experts=4, n_experts_used=2, expert_ffn_size=32), "F32", seed=0)
     assert cli_main(["finetune", "--model", moe, "--data", data, "--output", out]) == 2
+
+
+def test_preference_training_moves_the_policy_toward_the_chosen_answers(tmp_path):
+    path, tok, _ = _overfit_setup(tmp_path)
+    prefs = tmp_path / "prefs.jsonl"
+    prefs.write_text("\n".join(json.dumps(r) for r in [
+        {"prompt": "hello there ", "chosen": "general kenobi", "rejected": "go away"},
+        {"prompt": "a b c ", "chosen": "d e f", "rejected": "x y z"}]) + "\n")
+    pairs = ft.load_preference_pairs(str(prefs), tok, 64)
+    assert len(pairs) == 2 and pairs[0].chosen.loss_from == pairs[0].rejected.loss_from
+    model, _ = _model(path, ft.LoraConfig(r=8, alpha=16, targets=("q_proj", "v_proj", "down_proj", "lm_head")))
+    loss0, acc0 = ft.dpo_loss(model, pairs, beta=0.5)
+    # before training the policy IS the reference: zero margin, loss log 2
+    assert abs(float(loss0) - np.log(2)) < 1e-5 and acc0 == 0.0
+    tr = ft.Trainer(model, ft.TrainConfig(batch_size=2, lr=5e-3, seed=0))
+    losses = tr.train(pairs, 40, dpo_beta=0.5)
+    loss1, acc1 = ft.dpo_loss(model, pairs, beta=0.5)
+    assert losses[-1] < 0.5 * losses[0] and acc1 == 1.0 and float(loss1) < 0.35
+    # the reference policy did not move: with the adapters off the model is still the base
+    model.adapters_on = False
+    with torch.no_grad():
+        base_lp = ft.sequence_logprobs(model, [pairs[0].chosen])
+    model.adapters_on = True
+    fresh, _ = _model(path, ft.LoraConfig(r=8, alpha=16, targets=("q_proj",)))
+    with torch.no_grad():
+        assert torch.allclose(base_lp, ft.sequence_logprobs(fresh, [pairs[0].chosen]), atol=1e-5)
+    out = str(tmp_path / "run")
+    assert cli_main(["finetune", "--model", path, "--dpo-data", str(prefs), "--output", out, "--steps", "2", "--batch-size", "2"]) == 0
+    bad = tmp_path / "bad.jsonl"
+    bad.write_text(json.dumps({"prompt": "x", "chosen": "y"}) + "\n")
+    assert cli_main(["finetune", "--model", path, "--dpo-data", str(bad), "--output", out]) == 2
