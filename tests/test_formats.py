@@ -292,3 +292,27 @@ def test_codebook_iquants_decode_through_gguf_package():
         assert out.shape == (3 * t.block_size,)
     with pytest.raises(Exception):
         qref.dequantize("IQ2_XS", np.zeros(10, dtype=np.uint8))
+
+
+def test_turboquant_weight_codec():
+    from oxidize_b200.quant import turbo
+
+    rng = np.random.default_rng(0)
+    w = rng.standard_normal((7, 100)).astype(np.float32)  # a ragged last block
+    x = rng.standard_normal(100).astype(np.float32)
+    for bits, tol in ((8, 0.02), (4, 0.3)):
+        d = turbo.quantize(w, bits)
+        back = turbo.dequantize(d)
+        assert back.shape == w.shape
+        # error bounded by half a step of each block's scale
+        step = np.repeat(d.scales, turbo.BLOCK, axis=1)[:, :100]
+        assert (np.abs(back - w) <= 0.5 * step + 1e-6).all()
+        assert np.allclose(turbo.gemv(d, x), back @ x, atol=1e-4)
+        assert np.abs(turbo.gemv(d, x) - w @ x).max() < tol * np.abs(w @ x).max() + tol
+    assert turbo.quantize(w, 4).nbytes <= 0.2 * w.nbytes  # 20 bytes per 32 values (padding of the ragged block included)
+    z = turbo.quantize(np.zeros((2, 32), dtype=np.float32), 4)
+    assert (turbo.dequantize(z) == 0).all()
+    with pytest.raises(ValueError):
+        turbo.quantize(w, 3)
+    with pytest.raises(ValueError):
+        turbo.gemv(turbo.quantize(w, 8), x[:50])
