@@ -316,3 +316,37 @@ def test_turboquant_weight_codec():
         turbo.quantize(w, 3)
     with pytest.raises(ValueError):
         turbo.gemv(turbo.quantize(w, 8), x[:50])
+
+
+def test_bpe_tokenizer_training_round_trips_and_compresses(tmp_path):
+    from oxidize_b200.formats import tokenizer_train as TT
+
+    corpus = ("the quick brown fox jumps over the lazy dog. " * 40 + "pack my box with five dozen liquor jugs! " * 30
+              + "naïve café — déjà vu, 東京 is far. " * 10)
+    md = TT.train_bpe([corpus], 400)
+    toks, merges = md["tokenizer.ggml.tokens"], md["tokenizer.ggml.merges"]
+    assert len(toks) <= 400 and len(set(toks)) == len(toks) and len(merges) == len(toks) - 256 - 2
+    assert md["tokenizer.ggml.bos_token_id"] == len(toks) - 2 and md["tokenizer.ggml.eos_token_id"] == len(toks) - 1
+    assert md == TT.train_bpe([corpus], 400)  # deterministic
+    tok = T.load_tokenizer_from_metadata(md)
+    for text in ("the quick brown fox", "liquor jugs! déjà vu 東京", "unseen wörds & bytes \x00\x7f"):
+        ids = tok.encode(text)
+        assert tok.decode(ids) == text
+    # frequent words became single tokens; the trained vocabulary beats bytes by a wide margin on its own corpus
+    assert len(tok.encode(" quick")) == 1 and len(tok.encode(" the")) == 1
+    assert len(tok.encode(corpus)) < 0.3 * len(corpus.encode("utf-8"))
+    # every merge's parts were known when it was made
+    known = set(toks[:256])
+    for m in merges:
+        a, b = m.split(" ")
+        assert a in known and b in known
+        known.add(a + b)
+    with pytest.raises(ValueError):
+        TT.train_bpe([corpus], 100)
+    f = tmp_path / "c.txt"
+    f.write_text(corpus)
+    out = tmp_path / "tok.json"
+    assert TT.main([str(f), "--vocab-size", "300", "--output", str(out)]) == 0
+    import json as _json
+
+    assert len(_json.loads(out.read_text())["tokenizer.ggml.tokens"]) <= 300
