@@ -477,7 +477,8 @@ def cmd_gpu_cluster(args) -> int:
 # oxidize-quantize / oxidize-prune / oxidize-merge / oxidize-convert / oxidize-finetuning)
 TOOL_VERBS = {"quantize": "oxidize_b200.offline.requantize", "prune": "oxidize_b200.offline.prune",
               "merge": "oxidize_b200.offline.merge", "lora-merge": "oxidize_b200.offline.lora",
-              "finetune": "oxidize_b200.offline.finetune", "train-tokenizer": "oxidize_b200.formats.tokenizer_train"}
+              "finetune": "oxidize_b200.offline.finetune", "train-tokenizer": "oxidize_b200.formats.tokenizer_train",
+              "pretrain": "oxidize_b200.offline.pretrain"}
 
 
 def cmd_perplexity(argv: List[str]) -> int:

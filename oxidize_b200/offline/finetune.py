@@ -374,8 +374,8 @@ class TrainState:
 class Trainer:
     def __init__(self, model: LoraModel, cfg: TrainConfig):
         self.model, self.cfg = model, cfg
-        params = list(model.A.values()) + list(model.B.values())
-        self.opt = torch.optim.AdamW(params, lr=cfg.lr, weight_decay=cfg.weight_decay)
+        self.params = [p for p in model.parameters() if p.requires_grad]
+        self.opt = torch.optim.AdamW(self.params, lr=cfg.lr, weight_decay=cfg.weight_decay)
         self.state = TrainState()
         self.rng = np.random.default_rng(cfg.seed)
 
@@ -400,7 +400,7 @@ class Trainer:
             loss = dpo_loss(self.model, batch, dpo_beta)[0] if dpo_beta is not None else batch_loss(self.model, batch)
             loss.backward()
             if c.grad_clip > 0:
-                torch.nn.utils.clip_grad_norm_(list(self.model.A.values()) + list(self.model.B.values()), c.grad_clip)
+                torch.nn.utils.clip_grad_norm_(self.params, c.grad_clip)
             self.opt.step()
             self.state.step += 1
             self.state.losses.append(float(loss.detach()))

@@ -174,3 +174,37 @@ def test_preference_training_moves_the_policy_toward_the_chosen_answers(tmp_path
     bad = tmp_path / "bad.jsonl"
     bad.write_text(json.dumps({"prompt": "x", "chosen": "y"}) + "\n")
     assert cli_main(["finetune", "--model", path, "--dpo-data", str(bad), "--output", out]) == 2
+
+
+def test_training_from_scratch_writes_a_checkpoint_the_engine_serves(tmp_path):
+    """train-tokenizer -> pretrain -> GGUF -> engine: the loss falls, the exported file computes what the trainer's forward
+    computes, and the served model continues a memorised phrase."""
+    from oxidize_b200.formats import tokenizer_train as TT
+    from oxidize_b200.offline import pretrain as PT
+
+    corpus = tmp_path / "corpus.txt"
+    corpus.write_text("the cat sat on the mat. the dog sat on the log. " * 60)
+    tokj = tmp_path / "tok.json"
+    assert TT.main([str(corpus), "--vocab-size", "300", "--output", str(tokj)]) == 0
+    out = str(tmp_path / "tiny.gguf")
+    rc = cli_main(["pretrain", "--corpus", str(corpus), "--tokenizer", str(tokj), "--output", out, "--hidden", "64", "--layers", "2",
+                   "--heads", "4", "--kv-heads", "2", "--ffn", "128", "--seq-len", "32", "--steps", "120", "--batch-size", "8",
+                   "--lr", "1e-2", "--warmup-steps", "5"])
+    assert rc == 0
+    llm = LLM.from_gguf(out, EngineConfig(**EC), device="cpu")
+    assert llm.cfg.tie_embeddings and llm.tokenizer is not None
+    text = llm.generate(["the cat sat on"], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))[0].text
+    assert "the mat" in text
+    assert llm.perplexity("the cat sat on the mat. the dog sat on the log. " * 3) < 3.0
+    # the exported file is the trained function: the trainer's forward on the loaded weights gives the engine's logits
+    model, _ = _model(out)
+    ids = llm.tokenizer.encode("the dog sat on the")
+    with torch.no_grad():
+        mine = model(torch.tensor([ids]))[0, -1]
+    want = torch.from_numpy(llm.next_token_logits([ids]))[0]
+    assert (mine - want).abs().max() / want.abs().max() < 1e-4
+    # continue from the file, exporting 8-bit matrices
+    out2 = str(tmp_path / "more.gguf")
+    rc = cli_main(["pretrain", "--corpus", str(corpus), "--tokenizer", str(tokj), "--output", out2, "--init", out, "--seq-len", "32",
+                   "--steps", "3", "--quant", "Q8_0"])
+    assert rc == 0 and load_gguf(out2).tensors["blk.0.attn_q.weight"].type.name == "Q8_0"
