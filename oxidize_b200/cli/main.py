@@ -478,7 +478,7 @@ def cmd_gpu_cluster(args) -> int:
 TOOL_VERBS = {"quantize": "oxidize_b200.offline.requantize", "prune": "oxidize_b200.offline.prune",
               "merge": "oxidize_b200.offline.merge", "lora-merge": "oxidize_b200.offline.lora",
               "finetune": "oxidize_b200.offline.finetune", "train-tokenizer": "oxidize_b200.formats.tokenizer_train",
-              "pretrain": "oxidize_b200.offline.pretrain"}
+              "pretrain": "oxidize_b200.offline.pretrain", "train-classifier": "oxidize_b200.offline.classifier"}
 
 
 def cmd_perplexity(argv: List[str]) -> int:

@@ -217,3 +217,34 @@ def test_perplexity_orders_checkpoints_by_damage(base, tmp_path, capsys):
     assert rep["windows"] >= 2 and rep["perplexity"] > 1.0
     with pytest.raises(ValueError):
         llm.token_logprobs([1])
+
+
+def test_csv_classifier(tmp_path, capsys):
+    from oxidize_b200.offline import classifier as CL
+
+    rng = np.random.default_rng(0)
+    centers = {"red": (2.0, 0.0, 50.0), "green": (-2.0, 1.0, 10.0), "blue": (0.0, -3.0, 90.0)}
+    lines = ["x,y,z,colour"]
+    for name, c in centers.items():
+        for _ in range(60):
+            p = rng.normal(c, (0.5, 0.5, 5.0))
+            lines.append(f"{p[0]:.4f},{p[1]:.4f},{p[2]:.4f},{name}")
+    rng.shuffle(lines[1:])
+    f = tmp_path / "d.csv"
+    f.write_text("\n".join(lines) + "\n")
+    data = CL.load_csv_dataset(str(f))
+    assert data.inputs.shape == (180, 3) and sorted(data.classes) == ["blue", "green", "red"]
+    model, hist = CL.train_classifier(data, epochs=30, hidden_size=32, learning_rate=1e-2)
+    acc, loss = CL.evaluate_classifier(model, data)
+    assert hist[-1] < 0.3 * hist[0] and acc > 0.97
+    assert data.classes[int(model.predict(np.array([[2.0, 0.0, 50.0]]))[0])] == "red"
+    assert cli_main(["train-classifier", "--train-csv", str(f), "--epochs", "5", "--eval-csv", str(f), "--save", str(tmp_path / "m.pt")]) == 0
+    assert "accuracy" in capsys.readouterr().out and (tmp_path / "m.pt").exists()
+    # label in the first column, integer labels, no header
+    g = tmp_path / "n.csv"
+    g.write_text("\n".join(f"{i % 2},{(i % 2) * 2 - 1 + rng.normal(0, 0.1):.3f}" for i in range(40)) + "\n")
+    d2 = CL.load_csv_dataset(str(g), label_column=0)
+    assert d2.inputs.shape == (40, 1) and len(d2.classes) == 2
+    bad = tmp_path / "bad.csv"
+    bad.write_text("1,2,a\n3,x,a\n")
+    assert cli_main(["train-classifier", "--train-csv", str(bad)]) == 2
