@@ -124,6 +124,8 @@ def build_parser() -> argparse.ArgumentParser:
     a("--pipe-max-tokens", type=int, default=64)
     a("--vision", action="store_true")
     a("--image", default=None, help="image file shown to the model (needs --mmproj); '<image>' in the prompt marks its place")
+    a("--config", default=None, help="YAML file: CLI flag names (dashes or underscores) with their values, and under "
+                                     "'engine:' fields of EngineConfig; explicit flags win over it, it wins over the autotune plan")
     a("--mmproj", default=None, help="vision tower + projector file (clip.vision.* metadata, v.* / mm.* tensors)")
     for f in ("--cpu-optimized", "--ram-offload", "--mmap-prefetch", "--mmap-hugepages", "--layer-wise"):
         a(f, action="store_true")
@@ -147,6 +149,46 @@ def build_parser() -> argparse.ArgumentParser:
 
 def user_passed(argv: List[str]) -> set:
     return {a.split("=")[0].lstrip("-").replace("-", "_") for a in argv if a.startswith("--")}
+
+
+def apply_config_file(args, passed: set, parser: argparse.ArgumentParser) -> dict:
+    """Layered configuration: defaults < autotune plan < YAML file < ``OXIDIZE_CFG_<FLAG>`` environment variables < flags
+    given on the command line.  Values from the file and the environment are written into ``args`` and counted as "passed"
+    (so the plan does not override them); the file's ``engine:`` mapping is returned for EngineConfig fields that have no
+    flag of their own."""
+    known = {a.dest: a for a in parser._actions if a.dest not in ("help", "config", "verb")}
+    engine_extra: dict = {}
+    values: dict = {}
+    if args.config:
+        import yaml
+
+        with open(args.config) as f:
+            doc = yaml.safe_load(f) or {}
+        if not isinstance(doc, dict):
+            raise SystemExit(f"error: {args.config}: the top level must be a mapping")
+        engine_extra = dict(doc.pop("engine", None) or {})
+        for k, v in doc.items():
+            key = str(k).lstrip("-").replace("-", "_")
+            if key not in known:
+                raise SystemExit(f"error: {args.config}: unknown option {k!r}")
+            values[key] = v
+    for key in known:
+        env = os.environ.get("OXIDIZE_CFG_" + key.upper())
+        if env is not None:
+            values[key] = env
+    for key, v in values.items():
+        if key in passed:
+            continue  # explicit beats implicit
+        act = known[key]
+        if isinstance(v, str) and act.type is not None:
+            v = act.type(v)
+        elif isinstance(v, str) and isinstance(act.default, bool):
+            v = v.strip().lower() in ("1", "true", "yes", "on")
+        if act.choices and v not in act.choices:
+            raise SystemExit(f"error: option {key} = {v!r} is not one of {sorted(act.choices)}")
+        setattr(args, key, v)
+        passed.add(key)
+    return engine_extra
 
 
 def resolve_model(name: Optional[str]) -> str:
@@ -197,6 +239,10 @@ def make_engine(args, passed: set, device_index: Optional[int] = None):
                       cuda_graphs=not args.no_cuda_graphs, tp_size=tp, ep_size=args.ep or tp, pp_size=max(1, args.pp),
                       fused_comm=args.fused_comm == "on",
                       resident_layers=max(1, args.layer_cache) if args.layer_wise else 0)
+    for k, v in (getattr(args, "engine_extra", None) or {}).items():  # EngineConfig fields without a flag (config file)
+        if not hasattr(ec, k):
+            raise SystemExit(f"error: config file: EngineConfig has no field {k!r}")
+        setattr(ec, k, v)
     pp = ec.pp_size
     if ec.ep_size not in (1, tp):
         raise SystemExit(f"error: --ep must be 1 (experts replicated) or equal to --tp ({tp})")
@@ -540,7 +586,9 @@ def main(argv: Optional[List[str]] = None) -> int:
         return 0
     argv = rewrite_args(argv)
     passed = user_passed(argv)
-    args = build_parser().parse_args(argv)
+    parser = build_parser()
+    args = parser.parse_args(argv)
+    args.engine_extra = apply_config_file(args, passed, parser)
     if args.profile == "torch":
         import torch
 

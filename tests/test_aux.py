@@ -248,3 +248,41 @@ def test_guard_bands_catch_writes_outside_a_buffer():
     g.forget(b)
     g.verify()
     assert len(g) == 1
+
+
+def test_config_file_and_environment_layers(tmp_path, monkeypatch):
+    """defaults < plan < YAML < OXIDIZE_CFG_* < explicit flags; the file's engine: section reaches EngineConfig."""
+    from oxidize_b200.cli import main as M
+
+    cfgf = tmp_path / "serve.yaml"
+    cfgf.write_text("ctx-size: 96\nmax_running: 3\ntemperature: 0.25\nkv-cache-dtype: q8\nengine:\n  async_decode: false\n  resident_layers: 1\n")
+    parser = M.build_parser()
+    argv = M.rewrite_args(["run", "m.gguf", "hi", "--config", str(cfgf), "--temperature", "0.9"])
+    passed = M.user_passed(argv)
+    args = parser.parse_args(argv)
+    monkeypatch.setenv("OXIDIZE_CFG_MAX_RUNNING", "5")
+    extra = M.apply_config_file(args, passed, parser)
+    assert args.ctx_size == 96 and args.kv_cache_dtype == "q8"
+    assert args.max_running == 5  # the environment beats the file
+    assert args.temperature == 0.9  # the command line beats both
+    assert {"ctx_size", "max_running", "kv_cache_dtype"} <= passed and extra == {"async_decode": False, "resident_layers": 1}
+    bad = tmp_path / "bad.yaml"
+    bad.write_text("no-such-flag: 1\n")
+    args2 = parser.parse_args(M.rewrite_args(["run", "m.gguf", "hi", "--config", str(bad)]))
+    with pytest.raises(SystemExit):
+        M.apply_config_file(args2, set(), parser)
+    # end to end: the engine section lands in the engine's configuration
+    from oxidize_b200.models.config import preset
+    from oxidize_b200.utils.synth import synth_gguf
+
+    monkeypatch.delenv("OXIDIZE_CFG_MAX_RUNNING")
+    model = str(tmp_path / "m.gguf")
+    synth_gguf(model, preset("tiny-llama", n_layers=2, vocab_size=300, hidden_size=64, n_heads=2, n_kv_heads=2, head_dim=32, ffn_size=96),
+               "F32", seed=0)
+    argv = M.rewrite_args(["run", model, "hi", "--config", str(cfgf), "--backend", "cpu"])
+    passed = M.user_passed(argv)
+    args = parser.parse_args(argv)
+    args.engine_extra = M.apply_config_file(args, passed, parser)
+    llm, _ = M.make_engine(args, passed)
+    assert llm.config.max_model_len == 96 and llm.config.max_num_seqs == 3 and llm.config.async_decode is False
+    assert llm.config.resident_layers == 1 and llm.kv.spec.dtype_name == "q8"
