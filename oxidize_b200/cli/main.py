@@ -124,6 +124,8 @@ def build_parser() -> argparse.ArgumentParser:
     a("--pipe-max-tokens", type=int, default=64)
     a("--vision", action="store_true")
     a("--image", default=None, help="image file shown to the model (needs --mmproj); '<image>' in the prompt marks its place")
+    a("--experts-per-tok", type=int, default=0, help="route every token to this many experts instead of the checkpoint's count")
+    a("--cors-origin", default=None, help="answer cross-origin requests from this origin ('*' for any)")
     a("--config", default=None, help="YAML file: CLI flag names (dashes or underscores) with their values, and under "
                                      "'engine:' fields of EngineConfig; explicit flags win over it, it wins over the autotune plan")
     a("--mmproj", default=None, help="vision tower + projector file (clip.vision.* metadata, v.* / mm.* tensors)")
@@ -272,7 +274,7 @@ def make_engine(args, passed: set, device_index: Optional[int] = None):
     if backend == "cuda" and device_index is not None:
         torch.cuda.set_device(device_index)
     llm = LLM.from_gguf(g, ec, device=dev, comm=comm, tp_rank=tp_rank, ep_rank=tp_rank, rope_pairing=args.rope_pairing,
-                        pipe=pipe)
+                        pipe=pipe, experts_per_token=args.experts_per_tok)
     if args.tokenizer_model:
         from ..formats.tokenizer import load_tokenizer_from_gguf
 
@@ -419,7 +421,8 @@ def cmd_serve(args, passed) -> int:
                              f"{llm.cfg.hidden_size}")
     state = ServerState(engine, args.model_id, GenerationDefaults(max_tokens=args.max_tokens or 512,
                                                                   temperature=args.temperature, top_p=args.top_p,
-                                                                  top_k=args.top_k), chat_template=tpl, vision=vision)
+                                                                  top_k=args.top_k), chat_template=tpl, vision=vision,
+                        cors_origin=args.cors_origin)
     host = args.host if "host" in passed else args.api_host
     port = args.port if "port" in passed else args.api_port
     uvicorn.run(create_app(state), host=host, port=port, log_level="info")

@@ -125,7 +125,8 @@ class LLM:
     # ------------------------------------------------------------------ construction helpers
     @classmethod
     def from_gguf(cls, path: Union[str, GGUFFile], config: Optional[EngineConfig] = None, device=None, comm=None,
-                  tp_rank: int = 0, ep_rank: int = 0, rope_pairing: Optional[str] = None, pipe=None) -> "LLM":
+                  tp_rank: int = 0, ep_rank: int = 0, rope_pairing: Optional[str] = None, pipe=None,
+                  experts_per_token: int = 0) -> "LLM":
         from ..formats.tokenizer import TokenizerError, load_tokenizer_from_metadata
 
         config = config or EngineConfig()
@@ -133,6 +134,11 @@ class LLM:
         cfg = config_from_gguf(g)
         if rope_pairing:
             cfg.rope_pairing = rope_pairing
+        if experts_per_token:
+            # route every token to this many experts instead of the checkpoint's count (the C port's --experts-per-tok)
+            if not cfg.is_moe or not 1 <= experts_per_token <= cfg.n_experts:
+                raise ValueError(f"experts_per_token must be between 1 and the model's {cfg.n_experts} experts")
+            cfg.n_experts_used = experts_per_token
         device = torch.device(device if device is not None else ("cuda" if torch.cuda.is_available() else "cpu"))
         act = torch.bfloat16 if device.type == "cuda" else torch.float32
         ep_size = config.ep_size or config.tp_size

@@ -89,9 +89,10 @@ class ServerState:
     def __init__(self, engine: Optional[AsyncEngine] = None, model_id: str = "oxidize-default",
                  defaults: Optional[GenerationDefaults] = None, api_keys: Optional[List[str]] = None,
                  limits: Optional[LimitConfig] = None, audit: Optional[AuditLogger] = None,
-                 chat_template: Optional[str] = None, vision=None):
+                 chat_template: Optional[str] = None, vision=None, cors_origin: Optional[str] = None):
         self.engine = engine
         self.vision = vision  # vision.VisionEncoder: image parts of chat messages become image tokens
+        self.cors_origin = cors_origin  # origin allowed to call the API from a browser ("*": any); None: no CORS headers
         self.model_id = model_id
         self.defaults = defaults or GenerationDefaults()
         self.api_keys = load_api_keys() if api_keys is None else api_keys
@@ -155,6 +156,11 @@ def create_app(state: Optional[ServerState] = None) -> FastAPI:
     state = state or ServerState()
     app = FastAPI(title="oxidize-b200", version="0.1.0", openapi_url="/openapi.json", docs_url=None, redoc_url=None)
     app.state.server = state
+    if state.cors_origin:
+        from fastapi.middleware.cors import CORSMiddleware
+
+        app.add_middleware(CORSMiddleware, allow_origins=[state.cors_origin], allow_methods=["GET", "POST", "OPTIONS"],
+                           allow_headers=["authorization", "content-type", "x-api-key"])
 
     # ------------------------------------------------------------------ middleware (outermost last)
     @app.middleware("http")

@@ -923,3 +923,17 @@ def test_random_traffic_on_a_small_pool_with_window_release(tmp_path, seed):
     # every page is free or held only by the prefix cache (refcount zero): a fresh request can take the whole pool
     assert llm.pool.can_allocate(7)
     assert llm.scheduler.num_preemptions > 0  # the pool was small enough to make the scheduler evict and recompute
+
+
+def test_experts_per_token_override(tmp_path):
+    path = str(tmp_path / "moe.gguf")
+    synth_gguf(path, preset("mixtral-8x7b", n_layers=2, vocab_size=300, hidden_size=64, n_heads=4, n_kv_heads=2, head_dim=16,
+                            ffn_size=96, n_experts=4, n_experts_used=2, expert_ffn_size=32), "F32", seed=0)
+    ec = dict(max_model_len=64, max_num_seqs=2, num_kv_blocks=16)
+    base = LLM.from_gguf(path, EngineConfig(**ec), device="cpu")
+    more = LLM.from_gguf(path, EngineConfig(**ec), device="cpu", experts_per_token=4)
+    assert base.cfg.n_experts_used == 2 and more.cfg.n_experts_used == 4
+    a, b = base.next_token_logits([[5, 9, 20]]), more.next_token_logits([[5, 9, 20]])
+    assert not np.allclose(a, b, atol=1e-5)
+    with pytest.raises(ValueError):
+        LLM.from_gguf(path, EngineConfig(**ec), device="cpu", experts_per_token=5)

@@ -233,3 +233,15 @@ def test_data_parallel_replicas_behind_one_front(tmp_path):
         assert c.get("/readyz").status_code == 200
     finally:
         router.shutdown()
+
+
+def test_cors_origin():
+    c = TestClient(create_app(ServerState(api_keys=[], cors_origin="https://app.example")))
+    r = c.options("/v1/chat/completions", headers={"origin": "https://app.example", "access-control-request-method": "POST",
+                                                    "access-control-request-headers": "content-type"})
+    assert r.status_code == 200 and r.headers["access-control-allow-origin"] == "https://app.example"
+    r = c.get("/healthz", headers={"origin": "https://app.example"})
+    assert r.headers.get("access-control-allow-origin") == "https://app.example"
+    assert "access-control-allow-origin" not in c.get("/healthz", headers={"origin": "https://other.example"}).headers
+    plain = TestClient(create_app(ServerState(api_keys=[])))
+    assert "access-control-allow-origin" not in plain.get("/healthz", headers={"origin": "https://app.example"}).headers
