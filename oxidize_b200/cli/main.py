@@ -193,12 +193,38 @@ def apply_config_file(args, passed: set, parser: argparse.ArgumentParser) -> dic
     return engine_extra
 
 
+def convert_on_the_fly(src_dir: str, quant: str = "BF16") -> str:
+    """A Hugging Face directory (config.json + SafeTensors) given where a GGUF is expected: converted once into the model
+    directory, under a name made from the directory's path and the newest modification time of its files, and reused after
+    that (the reference's resolver does the same, ``oxidize-cli/src/main/model_resolution.rs:177``)."""
+    import glob
+    import hashlib
+
+    files = sorted(glob.glob(os.path.join(src_dir, "*.safetensors")))
+    if not files:
+        raise SystemExit(f"error: {src_dir} has a config.json but no .safetensors files")
+    stamp = max(os.path.getmtime(p) for p in files + [os.path.join(src_dir, "config.json")])
+    tag = hashlib.sha1(f"{os.path.abspath(src_dir)}:{stamp}:{quant}".encode()).hexdigest()[:16]
+    out = os.path.join(MODEL_DIR, f"{os.path.basename(os.path.normpath(src_dir))}-{tag}.gguf")
+    if not os.path.isfile(out):
+        from ..formats.convert import convert_safetensors_to_gguf, tokenizer_metadata_from_hf
+
+        os.makedirs(MODEL_DIR, exist_ok=True)
+        print(f"converting {src_dir} -> {out}", file=sys.stderr)
+        tmp = out + ".part"
+        convert_safetensors_to_gguf(src_dir, tmp, quant, tokenizer_metadata_from_hf(src_dir))
+        os.replace(tmp, out)
+    return out
+
+
 def resolve_model(name: Optional[str]) -> str:
     if not name:
         raise SystemExit("error: no model given (oxidize run MODEL.gguf \"prompt\")")
     for cand in (name, os.path.join(MODEL_DIR, name), os.path.join(MODEL_DIR, name + ".gguf")):
         if os.path.isfile(cand):
             return cand
+    if os.path.isdir(name) and os.path.isfile(os.path.join(name, "config.json")):
+        return convert_on_the_fly(name)
     if name.startswith("hf://") or "/" in name and not os.path.exists(name):
         raise SystemExit(f"error: {name!r} is not a local file and this build has no network access; "
                          f"place the GGUF under {MODEL_DIR} or pass a path")
@@ -578,14 +604,14 @@ def main(argv: Optional[List[str]] = None) -> int:
     if argv and argv[0] == "perplexity":
         return cmd_perplexity(argv[1:])
     if argv and argv[0] == "convert":
-        from ..formats.convert import convert_safetensors_to_gguf
+        from ..formats.convert import convert_safetensors_to_gguf, tokenizer_metadata_from_hf
 
         ap = argparse.ArgumentParser(prog="oxidize convert", description="HF SafeTensors directory -> GGUF")
         ap.add_argument("src")
         ap.add_argument("out")
         ap.add_argument("--quant", default="F16")
         a = ap.parse_args(argv[1:])
-        print(convert_safetensors_to_gguf(a.src, a.out, a.quant))
+        print(convert_safetensors_to_gguf(a.src, a.out, a.quant, tokenizer_metadata_from_hf(a.src)))
         return 0
     argv = rewrite_args(argv)
     passed = user_passed(argv)

@@ -288,4 +288,70 @@ if __name__ == "__main__":
     ap.add_argument("out")
     ap.add_argument("--quant", default="F16")
     a = ap.parse_args()
-    print(convert_safetensors_to_gguf(a.src, a.out, a.quant))
+    print(convert_safetensors_to_gguf(a.src, a.out, a.quant, tokenizer_metadata_from_hf(a.src)))
+
+
+def tokenizer_metadata_from_hf(src_dir: str) -> Dict[str, Any]:
+    """GGUF tokenizer metadata from a Hugging Face directory's ``tokenizer.json`` (+ ``tokenizer_config.json`` for the
+    special tokens and the chat template): byte-level BPE becomes ``tokenizer.ggml.model = gpt2`` (tokens, merges), a
+    Unigram model becomes ``llama`` (tokens, scores).  Other tokenizer kinds give an empty mapping: the model then loads
+    without a tokenizer and wants token ids, or ``--tokenizer-model`` with a GGUF that has one."""
+    tj = os.path.join(src_dir, "tokenizer.json")
+    if not os.path.isfile(tj):
+        return {}
+    with open(tj, encoding="utf-8") as f:
+        t = json.load(f)
+    model = t.get("model") or {}
+    kind = model.get("type")
+    added = {int(a["id"]): a for a in t.get("added_tokens") or []}
+
+    def uses_byte_level(node) -> bool:
+        if isinstance(node, dict):
+            return node.get("type") == "ByteLevel" or any(uses_byte_level(v) for v in node.values())
+        if isinstance(node, list):
+            return any(uses_byte_level(v) for v in node)
+        return False
+
+    md: Dict[str, Any] = {}
+    if kind == "BPE" and uses_byte_level(t.get("pre_tokenizer")) and not model.get("byte_fallback"):
+        vocab = model.get("vocab") or {}
+        n = max(list(vocab.values()) + list(added) + [-1]) + 1
+        tokens = [f"[PAD{i}]" for i in range(n)]
+        for tok, i in vocab.items():
+            tokens[int(i)] = tok
+        for i, a in added.items():
+            tokens[i] = a["content"]
+        merges = [m if isinstance(m, str) else " ".join(m) for m in model.get("merges") or []]
+        types = [3 if (i in added and added[i].get("special")) else 1 for i in range(n)]
+        md = {"tokenizer.ggml.model": "gpt2", "tokenizer.ggml.tokens": tokens, "tokenizer.ggml.merges": merges,
+              "tokenizer.ggml.token_type": types}
+    elif kind == "Unigram":
+        pieces = model.get("vocab") or []
+        tokens = [p[0] for p in pieces]
+        scores = [float(p[1]) for p in pieces]
+        for i, a in added.items():
+            if i < len(tokens):
+                tokens[i] = a["content"]
+        types = [3 if (i in added and added[i].get("special")) else 1 for i in range(len(tokens))]
+        md = {"tokenizer.ggml.model": "llama", "tokenizer.ggml.tokens": tokens, "tokenizer.ggml.scores": scores,
+              "tokenizer.ggml.token_type": types}
+        if model.get("unk_id") is not None:
+            md["tokenizer.ggml.unknown_token_id"] = int(model["unk_id"])
+    if not md:
+        return {}
+    ids = {tok: i for i, tok in enumerate(md["tokenizer.ggml.tokens"])}
+    cfgp = os.path.join(src_dir, "tokenizer_config.json")
+    if os.path.isfile(cfgp):
+        with open(cfgp, encoding="utf-8") as f:
+            tc = json.load(f)
+        for key, name in (("bos_token", "bos_token_id"), ("eos_token", "eos_token_id"), ("unk_token", "unknown_token_id"),
+                          ("pad_token", "padding_token_id")):
+            v = tc.get(key)
+            v = v.get("content") if isinstance(v, dict) else v
+            if isinstance(v, str) and v in ids:
+                md[f"tokenizer.ggml.{name}"] = ids[v]
+        if isinstance(tc.get("chat_template"), str):
+            md["tokenizer.chat_template"] = tc["chat_template"]
+        if tc.get("add_bos_token") is not None:
+            md["tokenizer.ggml.add_bos_token"] = bool(tc["add_bos_token"])
+    return md

@@ -286,3 +286,67 @@ def test_config_file_and_environment_layers(tmp_path, monkeypatch):
     llm, _ = M.make_engine(args, passed)
     assert llm.config.max_model_len == 96 and llm.config.max_num_seqs == 3 and llm.config.async_decode is False
     assert llm.config.resident_layers == 1 and llm.kv.spec.dtype_name == "q8"
+
+
+def test_hf_directory_is_converted_on_the_fly_with_its_tokenizer(tmp_path, monkeypatch):
+    """`oxidize run HF_DIR "..."`: SafeTensors + config.json + tokenizer.json become a GGUF in the model directory once;
+    the converted tokenizer encodes like the `tokenizers` library does on the same file."""
+    T = pytest.importorskip("transformers")
+    import json
+
+    from oxidize_b200.cli import main as M
+    from oxidize_b200.formats import tokenizer_train as TT
+    from oxidize_b200.formats.convert import tokenizer_metadata_from_hf
+    from oxidize_b200.formats.tokenizer import load_tokenizer_from_metadata
+
+    corpus = "the quick brown fox jumps over the lazy dog. " * 30 + "déjà vu café. " * 10
+    md = TT.train_bpe([corpus], 320)
+    toks, merges = md["tokenizer.ggml.tokens"], md["tokenizer.ggml.merges"]
+    src = tmp_path / "hf"
+    torch_seed = 0
+    import torch
+
+    torch.manual_seed(torch_seed)
+    T.LlamaForCausalLM(T.LlamaConfig(vocab_size=len(toks), hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                                     num_attention_heads=4, num_key_value_heads=2)).save_pretrained(str(src), safe_serialization=True)
+    n_special = 2
+    (src / "tokenizer.json").write_text(json.dumps({
+        "version": "1.0", "truncation": None, "padding": None,
+        "added_tokens": [{"id": len(toks) - n_special + i, "content": toks[len(toks) - n_special + i], "single_word": False,
+                          "lstrip": False, "rstrip": False, "normalized": False, "special": True} for i in range(n_special)],
+        "normalizer": None, "pre_tokenizer": {"type": "ByteLevel", "add_prefix_space": False, "trim_offsets": True, "use_regex": True},
+        "post_processor": None, "decoder": {"type": "ByteLevel", "add_prefix_space": True, "trim_offsets": True, "use_regex": True},
+        "model": {"type": "BPE", "dropout": None, "unk_token": None, "continuing_subword_prefix": None, "end_of_word_suffix": None,
+                  "fuse_unk": False, "byte_fallback": False, "vocab": {t: i for i, t in enumerate(toks[: len(toks) - n_special])},
+                  "merges": merges}}))
+    (src / "tokenizer_config.json").write_text(json.dumps({"bos_token": "<|bos|>", "eos_token": {"content": "<|eos|>"},
+                                                           "chat_template": "{% for message in messages %}{{ message.content }}{% endfor %}"}))
+    got = tokenizer_metadata_from_hf(str(src))
+    assert got["tokenizer.ggml.tokens"] == toks and got["tokenizer.ggml.merges"] == merges
+    assert got["tokenizer.ggml.eos_token_id"] == len(toks) - 1 and got["tokenizer.ggml.bos_token_id"] == len(toks) - 2
+    assert "chat_template" in "".join(got)
+    mine = load_tokenizer_from_metadata(got)
+    try:
+        from tokenizers import Tokenizer
+
+        theirs = Tokenizer.from_file(str(src / "tokenizer.json"))
+        for text in ("the quick brown fox", "a lazy café, déjà vu!"):
+            assert mine.encode(text) == theirs.encode(text, add_special_tokens=False).ids
+    except ImportError:
+        pass
+    monkeypatch.setattr(M, "MODEL_DIR", str(tmp_path / "models"))
+    path = M.resolve_model(str(src))
+    assert path.endswith(".gguf") and os.path.dirname(path) == str(tmp_path / "models")
+    assert M.resolve_model(str(src)) == path and len(os.listdir(tmp_path / "models")) == 1  # reused, not converted again
+    from oxidize_b200.engine.llm import LLM, EngineConfig
+    from oxidize_b200.engine.sampler import SamplingParams
+
+    llm = LLM.from_gguf(path, EngineConfig(max_model_len=64, max_num_seqs=1, num_kv_blocks=8), device="cpu")
+    assert llm.tokenizer is not None and llm.eos_token_id == len(toks) - 1 and llm.chat_template
+    out = llm.generate(["the quick brown"], SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True))[0]
+    assert len(out.token_ids) == 3
+    empty = tmp_path / "empty"
+    empty.mkdir()
+    (empty / "config.json").write_text("{}")
+    with pytest.raises(SystemExit):
+        M.resolve_model(str(empty))
