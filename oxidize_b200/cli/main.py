@@ -242,6 +242,8 @@ def make_engine(args, passed: set, device_index: Optional[int] = None):
         raise SystemExit(f"error: backend {args.backend!r} is not available in this build; use cpu or cuda")
     path = resolve_model(args.model)
     g = load_gguf(path)
+    if args.mmap_prefetch or args.mmap_hugepages:
+        g.advise(willneed=args.mmap_prefetch, hugepages=args.mmap_hugepages)
     inv = autotune.detect()
     fp = autotune.fingerprint(g)
     plan = autotune.plan(inv, fp, args.ctx_size, args.max_running)
@@ -267,6 +269,22 @@ def make_engine(args, passed: set, device_index: Optional[int] = None):
                       cuda_graphs=not args.no_cuda_graphs, tp_size=tp, ep_size=args.ep or tp, pp_size=max(1, args.pp),
                       fused_comm=args.fused_comm == "on",
                       resident_layers=max(1, args.layer_cache) if args.layer_wise else 0)
+    if args.ram_offload and not args.layer_wise:
+        # keep as many layers loaded as fit beside the cache, stream the rest from the file mapping
+        import psutil
+
+        n = max(1, fp.n_layers)
+        layer_bytes = sum(t.nbytes for name, t in g.tensors.items() if name.startswith("blk.")) // n
+        fixed = sum(t.nbytes for name, t in g.tensors.items() if not name.startswith("blk."))
+        kv = autotune.kv_bytes_per_token(fp, "bf16" if backend == "cuda" else "f32", tp) * ec.max_model_len * min(ec.max_num_seqs, 8)
+        if backend == "cuda":
+            free, _total = torch.cuda.mem_get_info()
+            budget = int(free * ec.gpu_memory_utilization)
+        else:
+            budget = int(psutil.virtual_memory().available * 0.8)
+        ec.resident_layers = autotune.plan_resident_layers(n, layer_bytes // max(tp, 1), fixed // max(tp, 1), kv, budget)
+        if ec.resident_layers:
+            print(f"ram-offload: {ec.resident_layers} of {n} layers resident", file=sys.stderr)
     for k, v in (getattr(args, "engine_extra", None) or {}).items():  # EngineConfig fields without a flag (config file)
         if not hasattr(ec, k):
             raise SystemExit(f"error: config file: EngineConfig has no field {k!r}")

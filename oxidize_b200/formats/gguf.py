@@ -295,6 +295,27 @@ class GGUFFile:
             return raw.view({"I8": "i1", "I16": "<i2", "I32": "<i4", "I64": "<i8"}[t]).reshape(info.shape)
         return raw.reshape(info.shape[:-1] + (info.row_nbytes,))
 
+    def advise(self, willneed: bool = False, hugepages: bool = False) -> List[str]:
+        """Hints to the kernel about the file mapping (the reference's ``--mmap-prefetch`` / ``--mmap-hugepages``,
+        ``format/gguf.rs:192``): read the pages ahead of their first use, back the mapping with huge pages where the
+        system allows.  Returns the hints that were accepted; a refused hint is not an error."""
+        import mmap as _mmap
+
+        done = []
+        for owner in [self] + list(self._shards):
+            mm = owner._mmap
+            if mm is None:
+                continue
+            for flag, name, const in ((willneed, "willneed", "MADV_WILLNEED"), (hugepages, "hugepages", "MADV_HUGEPAGE")):
+                if flag and hasattr(_mmap, const):
+                    try:
+                        mm.madvise(getattr(_mmap, const))
+                        if name not in done:
+                            done.append(name)
+                    except OSError:
+                        pass
+        return done
+
     def close(self) -> None:
         for s in self._shards:
             s.close()

@@ -204,6 +204,16 @@ def apply_plan(args: Dict[str, Any], user_set: set, p: TuningPlan) -> Dict[str, 
 # --------------------------------------------------------------------------- prefill token budget
 
 
+def plan_resident_layers(n_layers: int, layer_bytes: int, fixed_bytes: int, kv_bytes: int, budget_bytes: int) -> int:
+    """How many decoder layers to keep loaded when the whole model may not fit beside its cache (``--ram-offload``; the
+    reference's offload planner, ``model/offload.rs:66-95``): 0 = everything fits, otherwise the largest count that leaves
+    room for the embedding / head (``fixed_bytes``), the KV cache and one layer in flight; at least one."""
+    if n_layers * layer_bytes + fixed_bytes + kv_bytes <= budget_bytes:
+        return 0
+    room = budget_bytes - fixed_bytes - kv_bytes - layer_bytes  # one more layer's worth while the next one loads
+    return max(1, min(n_layers - 1, room // max(layer_bytes, 1)))
+
+
 def prefill_token_budget(cfg: ModelConfig, tp: int = 1, sm_count: int = 148, lo: int = 2048, hi: int = 3072,
                          token_tile: int = 256, row_tile: int = 128) -> int:
     """Tokens per engine step (prefill chunks + decode rows) that waste the fewest tensor-core tiles.

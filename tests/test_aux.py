@@ -350,3 +350,22 @@ def test_hf_directory_is_converted_on_the_fly_with_its_tokenizer(tmp_path, monke
     (empty / "config.json").write_text("{}")
     with pytest.raises(SystemExit):
         M.resolve_model(str(empty))
+
+
+def test_offload_planner_and_mapping_hints(tmp_path):
+    from oxidize_b200.formats.gguf import load_gguf
+    from oxidize_b200.models.config import preset
+    from oxidize_b200.utils import autotune
+    from oxidize_b200.utils.synth import synth_gguf
+
+    GB = 1 << 30
+    assert autotune.plan_resident_layers(80, 2 * GB, 4 * GB, 20 * GB, 200 * GB) == 0  # fits
+    assert autotune.plan_resident_layers(80, 2 * GB, 4 * GB, 20 * GB, 100 * GB) == 37  # (100 - 4 - 20 - 2) / 2
+    assert autotune.plan_resident_layers(80, 2 * GB, 4 * GB, 20 * GB, 10 * GB) == 1  # never less than one
+    assert autotune.plan_resident_layers(4, 2 * GB, 1 * GB, 1 * GB, 9 * GB) == 2
+    p = str(tmp_path / "m.gguf")
+    synth_gguf(p, preset("tiny-llama", n_layers=1, vocab_size=300, hidden_size=64, n_heads=4, n_kv_heads=2, head_dim=16, ffn_size=96),
+               "F32", seed=0)
+    g = load_gguf(p)
+    assert "willneed" in g.advise(willneed=True, hugepages=True)  # huge pages may be refused for a file mapping: not an error
+    assert g.advise() == []
