@@ -323,7 +323,11 @@ def make_engine(args, passed: set, device_index: Optional[int] = None):
         from ..formats.tokenizer import load_tokenizer_from_gguf
 
         llm.tokenizer = load_tokenizer_from_gguf(args.tokenizer_model)
-    if args.draft_model or (fp.has_mtp and not args.no_mtp):
+    if args.quantspec and not args.draft_model:
+        from ..engine.spec import attach_speculation
+
+        attach_speculation(llm, None, args.draft_tokens, quantspec=True)
+    elif args.draft_model or (fp.has_mtp and not args.no_mtp):
         from ..engine.spec import attach_speculation
 
         attach_speculation(llm, args.draft_model, args.draft_tokens, use_mtp=fp.has_mtp and not args.no_mtp, device=dev)

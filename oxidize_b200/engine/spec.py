@@ -65,7 +65,8 @@ def verify_greedy(drafts: List[int], target: List[int]) -> List[int]:
 class DraftModelProposer:
     """Runs a small draft model with its own paged KV; one shadow sequence per target sequence."""
 
-    def __init__(self, draft_weights, k: int, max_seqs: int, max_model_len: int, num_blocks: int = 0, comm=None):
+    def __init__(self, draft_weights, k: int, max_seqs: int, max_model_len: int, num_blocks: int = 0, comm=None,
+                 kv_dtype: Optional[str] = None):
         from ..models.transformer import Transformer
 
         self.k = k
@@ -74,7 +75,7 @@ class DraftModelProposer:
         cfg = draft_weights.cfg
         page = 16
         nblocks = num_blocks or max_seqs * ((max_model_len + page - 1) // page + 1)
-        kvd = "bf16" if dev.type == "cuda" else "f32"
+        kvd = kv_dtype or ("bf16" if dev.type == "cuda" else "f32")
         self.kv = self.model.new_cache(nblocks, page, kvd)
         self.pool = make_block_pool(nblocks, page, enable_prefix_cache=False)
         self.runner = ModelRunner(self.model, self.kv, max(2048, max_seqs * (k + 2)), max_seqs, max_model_len, False)
@@ -408,9 +409,21 @@ class SpecDecoder:
         self.proposer.release(seq)
 
 
-def attach_speculation(llm, draft_model_path: Optional[str], k: int = 4, use_mtp: bool = False, device=None) -> SpecDecoder:
-    """Enable speculative decoding on an engine: a draft GGUF if given, else the model's MTP head."""
+def attach_speculation(llm, draft_model_path: Optional[str], k: int = 4, use_mtp: bool = False, device=None,
+                       quantspec: bool = False) -> SpecDecoder:
+    """Enable speculative decoding on an engine: a draft GGUF if given, else the model's MTP head; with ``quantspec`` the
+    model drafts for itself over a 4-bit copy of its KV cache (the reference's ``--quantspec``,
+    ``SpeculativeGenerationConfig::quantspec_draft_kv``): the draft reads a quarter of the cache bytes, which is what a
+    long-context decode step is bound by, and the target's verification keeps the output exact."""
     c = llm.config
+    if quantspec and not draft_model_path:
+        if llm.cfg.is_ssm or llm.cfg.is_mla:
+            raise ValueError("self-speculation over a 4-bit cache needs ordinary attention layers")
+        if llm.model.kv_head_dim % 32:
+            raise ValueError("a 4-bit cache needs a head width that is a multiple of 32")
+        prop = DraftModelProposer(llm.weights, k, c.max_num_seqs, c.max_model_len, comm=llm.model.comm, kv_dtype="q4")
+        llm.spec = SpecDecoder(prop, k)
+        return llm.spec
     if llm.cfg.is_ssm:
         raise ValueError("speculative decoding needs a cache that can be rolled back: not available for state-space models")
     if draft_model_path:

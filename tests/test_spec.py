@@ -139,3 +139,26 @@ def test_sampled_speculation_runs_through_the_engine(target_path, tmp_path):
     spec3 = attach_speculation(llm3, target_path, k=3)
     llm3.generate(PROMPTS, SamplingParams(temperature=0.9, top_k=5, max_tokens=8, ignore_eos=True, seed=1))
     assert spec3.stats.proposed == 0
+
+
+def test_self_speculation_over_a_4bit_cache(tmp_path):
+    """--quantspec: the model drafts for itself over a q4 copy of its cache; the output is the plain greedy output and
+    nearly every draft is accepted (the draft is the target up to cache rounding)."""
+    from oxidize_b200.engine.llm import LLM, EngineConfig
+    from oxidize_b200.engine.sampler import SamplingParams
+    from oxidize_b200.engine.spec import attach_speculation
+    from oxidize_b200.models.config import preset
+    from oxidize_b200.utils.synth import synth_gguf
+
+    path = str(tmp_path / "m.gguf")
+    synth_gguf(path, preset("tiny-llama", n_layers=2, vocab_size=300, hidden_size=128, n_heads=4, n_kv_heads=2, head_dim=32, ffn_size=256),
+               "F32", seed=2, norm_jitter=0.1)
+    ec = dict(max_model_len=128, max_num_seqs=4, num_kv_blocks=64, prefill_chunk_size=32, max_num_batched_tokens=64)
+    prompts = [[5, 9, 200, 31, 7], list(range(3, 40))]
+    sp = SamplingParams(temperature=0.0, max_tokens=30, ignore_eos=True)
+    plain = [o.token_ids for o in LLM.from_gguf(path, EngineConfig(**ec), device="cpu").generate(prompts, sp)]
+    llm = LLM.from_gguf(path, EngineConfig(**ec), device="cpu")
+    spec = attach_speculation(llm, None, k=4, quantspec=True)
+    assert spec.proposer.kv.spec.dtype_name == "q4" and spec.proposer.model.w is llm.weights
+    assert [o.token_ids for o in llm.generate(prompts, sp)] == plain
+    assert spec.stats.acceptance_rate > 0.7 and spec.stats.tokens_per_target_forward > 2.5
