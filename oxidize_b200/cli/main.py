@@ -82,7 +82,8 @@ def build_parser() -> argparse.ArgumentParser:
     a("--kv-cache-dtype", default="auto", choices=["auto", "f32", "f16", "bf16", "q8", "q4"])
     a("--turboquant-kv", action="store_true")
     a("--no-turboquant-kv", action="store_true")
-    a("--turboquant", action="store_true")
+    a("--turboquant", action="store_true", help="re-encode float weight matrices as block-wise int8 (Q8_0) while loading")
+    a("--turboquant-bits", type=int, default=8, choices=[4, 8])
     a("--no-turboquant", action="store_true")
     a("--threads", type=int, default=0)
     a("--n-gpu-layers", type=int, default=0)
@@ -268,7 +269,9 @@ def make_engine(args, passed: set, device_index: Optional[int] = None):
                       max_num_batched_tokens=args.max_batched_tokens, prefill_chunk_size=args.prefill_batch_size,
                       cuda_graphs=not args.no_cuda_graphs, tp_size=tp, ep_size=args.ep or tp, pp_size=max(1, args.pp),
                       fused_comm=args.fused_comm == "on",
-                      resident_layers=max(1, args.layer_cache) if args.layer_wise else 0)
+                      resident_layers=max(1, args.layer_cache) if args.layer_wise else 0,
+                      weight_transcode=("Q4_0" if args.turboquant_bits == 4 else "Q8_0")
+                      if (args.turboquant and not args.no_turboquant) else "")
     if args.ram_offload and not args.layer_wise:
         # keep as many layers loaded as fit beside the cache, stream the rest from the file mapping
         import psutil

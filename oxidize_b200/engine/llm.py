@@ -59,6 +59,9 @@ class EngineConfig:
     # > 0: keep only this many decoder layers loaded, streaming the others from the file mapping as the forward pass
     # reaches them (for checkpoints larger than the memory left beside the KV cache)
     resident_layers: int = 0
+    # "Q8_0" / "Q4_0": float weight matrices are re-encoded in that block format while loading (the reference's
+    # --turboquant: block-wise int8 / int4 weights with per-block scales); "" = keep the checkpoint's encodings
+    weight_transcode: str = ""
 
 
 @dataclass
@@ -154,7 +157,7 @@ class LLM:
                 raise ValueError("pp_size > 1 needs the stage's StageIO")
             layer_range = split_layers(cfg.n_layers, config.pp_size)[pipe.rank]
         w = load_weights(g, cfg, device, act, tp_rank, config.tp_size, ep_rank, ep_size, layer_range=layer_range,
-                         resident_layers=config.resident_layers)
+                         resident_layers=config.resident_layers, transcode=config.weight_transcode)
         try:
             tok = load_tokenizer_from_metadata(g.metadata)
         except TokenizerError:

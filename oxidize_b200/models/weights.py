@@ -341,8 +341,10 @@ def _np_to_torch(a: np.ndarray, device, dtype=None) -> torch.Tensor:
 class GGUFWeightSource:
     """Reads (slices of) tensors from a GGUF mapping into device QTensors."""
 
-    def __init__(self, g: GGUFFile, device, act_dtype: torch.dtype):
+    def __init__(self, g: GGUFFile, device, act_dtype: torch.dtype, transcode: str = ""):
         self.g = g
+        # "Q8_0" / "Q4_0": weight matrices stored as floats are re-encoded in that block format on the way in
+        self.transcode = transcode.upper()
         self.device = torch.device(device)
         self.act_dtype = act_dtype
 
@@ -374,6 +376,13 @@ class GGUFWeightSource:
                 raise ValueError(f"{name}: column shard [{c0},{c1}) not on {t.name} block boundary {t.block_size}")
             raw = raw[:, c0 // t.block_size * t.type_size : c1 // t.block_size * t.type_size]
         new_shape = (r1 - r0, c1 - c0)
+        if (self.transcode and t.name in ("F32", "F16", "BF16") and new_shape[1] % 32 == 0 and new_shape[0] > 1
+                and "token_embd" not in name and "ffn_gate_inp" not in name):
+            x = qref.dequantize(t.name, np.ascontiguousarray(raw).reshape(-1), new_shape[0] * new_shape[1])
+            tt = ggml_type(self.transcode)
+            packed = qref.quantize(self.transcode, np.asarray(x, dtype=np.float32).reshape(-1))
+            packed = np.ascontiguousarray(packed).view(np.uint8).reshape(new_shape[0], new_shape[1] // tt.block_size * tt.type_size)
+            return QTensor(tt.name, _np_to_torch(packed, self.device), new_shape)
         if t.name == "F32":
             x = np.ascontiguousarray(raw).view("<f4")
             dt = torch.float32 if self.act_dtype == torch.float32 else torch.bfloat16
@@ -528,13 +537,15 @@ def _load_layer(src: GGUFWeightSource, cfg: ModelConfig, i: int, tp_rank: int, t
 
 def load_weights(g: GGUFFile, cfg: ModelConfig, device="cpu", act_dtype: torch.dtype = torch.float32,
                  tp_rank: int = 0, tp_size: int = 1, ep_rank: int = 0, ep_size: int = 1,
-                 layer_range: Optional[Tuple[int, int]] = None, resident_layers: int = 0) -> ModelWeights:
+                 layer_range: Optional[Tuple[int, int]] = None, resident_layers: int = 0, transcode: str = "") -> ModelWeights:
     """Load this rank's shard of a GGUF checkpoint.
 
     ``layer_range`` selects a pipeline stage (only its own tensors are read, unlike the
     reference's two-node pipeline where both nodes map the whole file, pipeline.rs:23).
     ``resident_layers`` > 0 keeps only that many decoder layers loaded at a time (:class:`StreamedLayers`)."""
-    src = GGUFWeightSource(g, device, act_dtype)
+    if transcode and transcode.upper() not in ("Q8_0", "Q4_0"):
+        raise ValueError("weights can be re-encoded at load time as Q8_0 or Q4_0")
+    src = GGUFWeightSource(g, device, act_dtype, transcode)
     l0, l1 = layer_range if layer_range is not None else (0, cfg.n_layers)
     if resident_layers > 0 and resident_layers < l1 - l0:
         layers = StreamedLayers(lambda i: _load_layer(src, cfg, l0 + i, tp_rank, tp_size, ep_rank, ep_size), l1 - l0,

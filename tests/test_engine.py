@@ -937,3 +937,22 @@ def test_experts_per_token_override(tmp_path):
     assert not np.allclose(a, b, atol=1e-5)
     with pytest.raises(ValueError):
         LLM.from_gguf(path, EngineConfig(**ec), device="cpu", experts_per_token=5)
+
+
+def test_weights_are_transcoded_at_load_time_on_request(tmp_path):
+    path = str(tmp_path / "m.gguf")
+    synth_gguf(path, preset("tiny-llama", n_layers=2, vocab_size=300, hidden_size=64, n_heads=4, n_kv_heads=2, head_dim=16,
+                            ffn_size=96), "F32", seed=2, norm_jitter=0.1)
+    ec = dict(max_model_len=64, max_num_seqs=2, num_kv_blocks=16)
+    f32 = LLM.from_gguf(path, EngineConfig(**ec), device="cpu")
+    q8 = LLM.from_gguf(path, EngineConfig(**ec, weight_transcode="Q8_0"), device="cpu")
+    q4 = LLM.from_gguf(path, EngineConfig(**ec, weight_transcode="q4_0"), device="cpu")
+    lw = q8.weights.layers[0]
+    assert {p.qtype for p in lw.wqkv.parts + lw.wo.parts + lw.w_gate_up.parts + lw.w_down.parts} == {"Q8_0"}
+    assert q8.weights.embed.qtype == "F32" and q4.weights.layers[1].w_down.parts[0].qtype == "Q4_0"
+    assert q4.weights.nbytes() < q8.weights.nbytes() < f32.weights.nbytes()
+    a, b, c = (m.next_token_logits([[5, 9, 20, 31]])[0] for m in (f32, q8, q4))
+    e8, e4 = np.abs(a - b).max() / np.abs(a).max(), np.abs(a - c).max() / np.abs(a).max()
+    assert 0 < e8 < 0.02 and e8 < e4 < 0.3
+    with pytest.raises(ValueError):
+        LLM.from_gguf(path, EngineConfig(**ec, weight_transcode="Q6_K"), device="cpu")
