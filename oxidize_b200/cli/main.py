@@ -243,6 +243,11 @@ def make_engine(args, passed: set, device_index: Optional[int] = None):
         raise SystemExit(f"error: backend {args.backend!r} is not available in this build; use cpu or cuda")
     path = resolve_model(args.model)
     g = load_gguf(path)
+    if args.cpu_optimized and args.backend != "cuda":
+        # the CPU path is torch's: use every core for the matrix products, flush denormals (the reference pins its own
+        # thread pool instead, oxidize-cli/src/main.rs:306)
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
+        torch.set_flush_denormal(True)
     if args.mmap_prefetch or args.mmap_hugepages:
         g.advise(willneed=args.mmap_prefetch, hugepages=args.mmap_hugepages)
     inv = autotune.detect()
