@@ -24,7 +24,7 @@ _ARCH = {"LlamaForCausalLM": "llama", "MistralForCausalLM": "llama", "MixtralFor
          "Qwen2MoeForCausalLM": "qwen2moe", "DeepseekV2ForCausalLM": "deepseek2", "DeepseekV3ForCausalLM": "deepseek2",
          "Phi3ForCausalLM": "phi3", "GemmaForCausalLM": "gemma", "Gemma2ForCausalLM": "gemma2",
          "Gemma3ForCausalLM": "gemma3", "Gemma3ForConditionalGeneration": "gemma3", "Lfm2ForCausalLM": "lfm2",
-         "MambaForCausalLM": "mamba"}
+         "Lfm2MoeForCausalLM": "lfm2moe", "MambaForCausalLM": "mamba"}
 GEMMA = ("gemma", "gemma2", "gemma3")
 
 
@@ -121,7 +121,7 @@ def write_hf_metadata(w: GGUFWriter, arch: str, c: Dict[str, Any]) -> None:
     w.add(f"{arch}.feed_forward_length", ffn, U)
     w.add(f"{arch}.attention.head_count", heads, U)
     kvh = int(c.get("num_key_value_heads", heads))
-    if arch == "lfm2":
+    if arch in ("lfm2", "lfm2moe"):
         # one entry per layer, 0 for the convolution layers (as llama.cpp's converter writes it)
         kinds = c.get("layer_types") or []
         w.add(f"{arch}.attention.head_count_kv", [kvh if k == "full_attention" else 0 for k in kinds] or kvh)
@@ -185,7 +185,8 @@ def write_hf_metadata(w: GGUFWriter, arch: str, c: Dict[str, Any]) -> None:
         w.add(f"{arch}.expert_used_count", int(c.get("num_experts_per_tok", 2)), U)
         w.add(f"{arch}.expert_feed_forward_length", int(c.get("moe_intermediate_size") or c.get("intermediate_size")), U)
         # DeepSeek-V3 configs often omit scoring_func: that model always scores with a sigmoid
-        sigmoid = c.get("scoring_func") == "sigmoid" or (c.get("scoring_func") is None and c.get("model_type") == "deepseek_v3")
+        sigmoid = c.get("scoring_func") == "sigmoid" or (c.get("scoring_func") is None
+                                                         and c.get("model_type") in ("deepseek_v3", "lfm2_moe"))
         w.add(f"{arch}.expert_gating_func", 2 if sigmoid else 1, U)
         w.add(f"{arch}.expert_weights_scale", float(c.get("routed_scaling_factor", 1.0)), F)
         w.add(f"{arch}.expert_weights_norm", bool(c.get("norm_topk_prob", True)))
@@ -194,8 +195,9 @@ def write_hf_metadata(w: GGUFWriter, arch: str, c: Dict[str, Any]) -> None:
             w.add(f"{arch}.expert_group_used_count", int(c.get("topk_group", 1)), U)
         if c.get("n_shared_experts"):
             w.add(f"{arch}.expert_shared_count", int(c["n_shared_experts"]), U)
-        if c.get("first_k_dense_replace"):
-            w.add(f"{arch}.leading_dense_block_count", int(c["first_k_dense_replace"]), U)
+        dense = c.get("first_k_dense_replace") or c.get("num_dense_layers")
+        if dense:
+            w.add(f"{arch}.leading_dense_block_count", int(dense), U)
 
 
 def _kind_of(gname: str) -> str:

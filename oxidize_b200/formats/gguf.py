@@ -630,6 +630,9 @@ _HF_LAYER_MAP_LFM2 = {
     "conv.in_proj.weight": "shortconv.in_proj.weight",
     "conv.conv.weight": "shortconv.conv.weight",
     "conv.out_proj.weight": "shortconv.out_proj.weight",
+    # LFM2-MoE: router, and the per-expert bias that only steers which experts are picked
+    "feed_forward.gate.weight": "ffn_gate_inp.weight",
+    "feed_forward.expert_bias": "exp_probs_b.bias",
 }
 # Mamba (``backbone.layers.N.*``): the norm in front of the mixer and the mixer's tensors
 _HF_MAMBA_TOP = {"backbone.embeddings.weight": "token_embd.weight", "backbone.norm_f.weight": "output_norm.weight",
@@ -653,7 +656,7 @@ _HF_TOP_MAP = {
     "lm_head.weight": "output.weight",
 }
 _HF_LAYER_RE = re.compile(r"^model\.layers\.(\d+)\.(.+)$")
-_HF_EXPERT_RE = re.compile(r"^(?:mlp|block_sparse_moe)\.experts\.(\d+)\.(gate_proj|up_proj|down_proj|w1|w2|w3)\.weight$")
+_HF_EXPERT_RE = re.compile(r"^(?:mlp|block_sparse_moe|feed_forward)\.experts\.(\d+)\.(gate_proj|up_proj|down_proj|w1|w2|w3)\.weight$")
 _EXPERT_KIND = {"gate_proj": "gate", "w1": "gate", "up_proj": "up", "w3": "up", "down_proj": "down", "w2": "down"}
 
 
@@ -675,7 +678,7 @@ def map_hf_tensor_name(name: str, arch: Optional[str] = None) -> Optional[Tuple[
         return (f"blk.{mm.group(1)}.{_HF_MAMBA_LAYER[mm.group(2)]}", None) if mm and mm.group(2) in _HF_MAMBA_LAYER else None
     if name in _HF_TOP_MAP:
         return _HF_TOP_MAP[name], None
-    if arch == "lfm2" and name == "model.embedding_norm.weight":
+    if arch in ("lfm2", "lfm2moe") and name == "model.embedding_norm.weight":
         return "token_embd_norm.weight", None  # the norm in front of the head (the name llama.cpp's converter gives it)
     m = _HF_LAYER_RE.match(name)
     if not m:
@@ -683,7 +686,7 @@ def map_hf_tensor_name(name: str, arch: Optional[str] = None) -> Optional[Tuple[
     layer, rest = int(m.group(1)), m.group(2)
     if arch in ("gemma2", "gemma3") and rest in _HF_LAYER_MAP_GEMMA:
         return f"blk.{layer}.{_HF_LAYER_MAP_GEMMA[rest]}", None
-    if arch == "lfm2" and rest in _HF_LAYER_MAP_LFM2:
+    if arch in ("lfm2", "lfm2moe") and rest in _HF_LAYER_MAP_LFM2:
         return f"blk.{layer}.{_HF_LAYER_MAP_LFM2[rest]}", None
     if rest in _HF_LAYER_MAP:
         return f"blk.{layer}.{_HF_LAYER_MAP[rest]}", None

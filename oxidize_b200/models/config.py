@@ -17,11 +17,12 @@ from ..formats.gguf import GGUFFile
 # architecture strings accepted (reference arch-string map inference.rs:62-96)
 # phi3: Llama layers with fused qkv / gate-up tensors.  gemma / gemma2 / gemma3: GeGLU, scaled embeddings, norms on the
 # branch outputs, soft-capped logits, interleaved local / global attention with two rotary bases.
-# lfm2: short-convolution mixers interleaved with grouped-query attention layers.
+# lfm2 / lfm2moe: short-convolution mixers interleaved with grouped-query attention layers (lfm2moe: routed experts
+# after the leading dense layers, sigmoid scores, a per-expert bias used for the choice only).
 # mamba: selective state-space layers only (no attention, no feed-forward block).
 DENSE_ARCHS = {"llama", "mistral", "qwen2", "qwen3", "deepseek", "phi3", "gemma", "gemma2", "gemma3", "lfm2", "mamba"}
 GEMMA_ARCHS = {"gemma", "gemma2", "gemma3"}
-MOE_ARCHS = {"mixtral", "qwen2moe", "qwen3moe", "deepseek2", "deepseek-moe", "deepseek_moe"}
+MOE_ARCHS = {"mixtral", "qwen2moe", "qwen3moe", "deepseek2", "deepseek-moe", "deepseek_moe", "lfm2moe"}
 # Architectures whose layers need math this engine does not have (two attention geometries in one model,
 # parallel attention / MLP blocks, recurrent or convolutional mixers): loading one would run it as
 # a plain Llama and produce wrong tokens, so they are refused by name.
@@ -265,7 +266,7 @@ def config_from_gguf(g: GGUFFile) -> ModelConfig:
         c.n_kv_heads = c.n_heads
         c.rope_pairing = "adjacent"  # the rotary part is stored with interleaved pairs and files keep that order
         c.yarn_log_multiplier = float(_scalar(a("rope.scaling.yarn_log_multiplier"), 0.0))
-    if arch == "lfm2":
+    if arch in ("lfm2", "lfm2moe"):
         c.conv_l_cache = int(_scalar(a("shortconv.l_cache"), 3))
         c.conv_layers = [i for i in range(c.n_layers) if g.has_tensor(f"blk.{i}.shortconv.conv.weight")]
         first_attn = next((i for i in range(c.n_layers) if i not in c.conv_layers), 0)

@@ -430,72 +430,9 @@ def _load_mla(src: GGUFWeightSource, cfg: ModelConfig, p: str, h0: int, h1: int)
     return m
 
 
-def _load_layer(src: GGUFWeightSource, cfg: ModelConfig, i: int, tp_rank: int, tp_size: int,
-                ep_rank: int, ep_size: int, prefix: Optional[str] = None) -> LayerWeights:
-    p = prefix or f"blk.{i}"
-    hd = cfg.head_dim
-    # attention heads are sharded by KV head; with fewer KV heads than ranks they replicate
-    kv_rep = max(1, tp_size // cfg.n_kv_heads)
-    kv_shards = min(tp_size, cfg.n_kv_heads)
-    q0, q1 = shard_range(cfg.n_heads, tp_rank, tp_size)
-    k0, k1 = shard_range(cfg.n_kv_heads, tp_rank // kv_rep, kv_shards)
-    qr, kr = (q0 * hd, q1 * hd), (k0 * hd, k1 * hd)
-    mla = None
-    if src.has(f"{p}.ssm_in.weight"):
-        if tp_size > 1:
-            raise ValueError("state-space layers are not sharded: run this model with tp_size = 1")
-        di = cfg.ssm_d_inner
-        ssm = SSMWeights(in_proj=src.matrix(f"{p}.ssm_in.weight"), conv_kernel=src.vector(f"{p}.ssm_conv1d.weight").reshape(di, -1),
-                         conv_bias=src.vector(f"{p}.ssm_conv1d.bias") if src.has(f"{p}.ssm_conv1d.bias") else None,
-                         x_proj=src.matrix(f"{p}.ssm_x.weight"), dt_proj=src.matrix(f"{p}.ssm_dt.weight"),
-                         dt_bias=src.vector(f"{p}.ssm_dt.bias"), a=src.vector(f"{p}.ssm_a").reshape(di, -1),
-                         d=src.vector(f"{p}.ssm_d"), out_proj=LinearWeight([src.matrix(f"{p}.ssm_out.weight")]))
-        return LayerWeights(attn_norm=src.vector(f"{p}.attn_norm.weight"), wqkv=None, wo=None, ffn_norm=None, ssm=ssm)
-    if src.has(f"{p}.shortconv.conv.weight"):
-        if tp_size > 1:
-            raise ValueError("short-convolution layers are not sharded: run this model with tp_size = 1")
-        lw = LayerWeights(attn_norm=src.vector(f"{p}.attn_norm.weight"), wqkv=None, wo=None,
-                          ffn_norm=src.vector(f"{p}.ffn_norm.weight"), conv_in=src.matrix(f"{p}.shortconv.in_proj.weight"),
-                          conv_kernel=src.vector(f"{p}.shortconv.conv.weight").reshape(cfg.hidden_size, -1),
-                          conv_out=LinearWeight([src.matrix(f"{p}.shortconv.out_proj.weight")]))
-        ffn = src.g.tensors[f"{p}.ffn_gate.weight"].shape[0]
-        lw.w_gate_up = LinearWeight(fuse_rows([src.matrix(f"{p}.ffn_gate.weight"), src.matrix(f"{p}.ffn_up.weight")]))
-        lw.w_down = LinearWeight([src.matrix(f"{p}.ffn_down.weight")])
-        return lw
-    if src.has(f"{p}.attn_kv_a_mqa.weight"):
-        mla = _load_mla(src, cfg, p, q0, q1)
-        parts = []
-    elif src.has(f"{p}.attn_qkv.weight"):
-        # one fused tensor (Phi-3): rows are all query heads, then all key heads, then all value heads
-        ko, vo = cfg.n_heads * hd, (cfg.n_heads + cfg.n_kv_heads) * hd
-        parts = [src.matrix(f"{p}.attn_qkv.weight", rows=qr), src.matrix(f"{p}.attn_qkv.weight", rows=(ko + kr[0], ko + kr[1])),
-                 src.matrix(f"{p}.attn_qkv.weight", rows=(vo + kr[0], vo + kr[1]))]
-    else:
-        parts = [src.matrix(f"{p}.attn_q.weight", rows=qr), src.matrix(f"{p}.attn_k.weight", rows=kr),
-                 src.matrix(f"{p}.attn_v.weight", rows=kr)]
-    bias = None
-    if src.has(f"{p}.attn_qkv.bias"):
-        b = src.vector(f"{p}.attn_qkv.bias")
-        ko, vo = cfg.n_heads * hd, (cfg.n_heads + cfg.n_kv_heads) * hd
-        bias = torch.cat([b[qr[0]:qr[1]], b[ko + kr[0]:ko + kr[1]], b[vo + kr[0]:vo + kr[1]]])
-    elif src.has(f"{p}.attn_q.bias"):
-        bias = torch.cat([src.vector(f"{p}.attn_q.bias")[qr[0]:qr[1]], src.vector(f"{p}.attn_k.bias")[kr[0]:kr[1]],
-                          src.vector(f"{p}.attn_v.bias")[kr[0]:kr[1]]])
-    vd = cfg.v_head_dim if mla is not None else hd
-    lw = LayerWeights(
-        attn_norm=src.vector(f"{p}.attn_norm.weight"),
-        wqkv=LinearWeight(fuse_rows(parts), bias) if mla is None else None,
-        wo=LinearWeight([src.matrix(f"{p}.attn_output.weight", cols=(q0 * vd, q1 * vd))]),
-        ffn_norm=src.vector(f"{p}.ffn_norm.weight"),
-        mla=mla,
-    )
-    if src.has(f"{p}.attn_q_norm.weight"):
-        lw.q_norm = src.vector(f"{p}.attn_q_norm.weight")
-        lw.k_norm = src.vector(f"{p}.attn_k_norm.weight")
-    if src.has(f"{p}.post_attention_norm.weight"):
-        lw.post_attn_norm = src.vector(f"{p}.post_attention_norm.weight")
-    if src.has(f"{p}.post_ffw_norm.weight"):
-        lw.post_ffn_norm = src.vector(f"{p}.post_ffw_norm.weight")
+def _load_ffn(src: "GGUFWeightSource", cfg: ModelConfig, p: str, lw: "LayerWeights", tp_rank: int, tp_size: int,
+              ep_rank: int, ep_size: int) -> None:
+    """The feed-forward half of layer ``p``: router + this rank's experts (+ shared expert), or one gated MLP."""
     if src.has(f"{p}.ffn_gate_inp.weight"):
         lw.router = src.matrix(f"{p}.ffn_gate_inp.weight")
         if src.has(f"{p}.exp_probs_b.bias"):
@@ -532,6 +469,73 @@ def _load_layer(src: GGUFWeightSource, cfg: ModelConfig, i: int, tp_rank: int, t
         lw.w_gate_up = LinearWeight(fuse_rows([src.matrix(f"{p}.ffn_gate.weight", rows=(f0, f1)),
                                                src.matrix(f"{p}.ffn_up.weight", rows=(f0, f1))]))
         lw.w_down = LinearWeight([src.matrix(f"{p}.ffn_down.weight", cols=(f0, f1))])
+
+
+def _load_layer(src: GGUFWeightSource, cfg: ModelConfig, i: int, tp_rank: int, tp_size: int,
+                ep_rank: int, ep_size: int, prefix: Optional[str] = None) -> LayerWeights:
+    p = prefix or f"blk.{i}"
+    hd = cfg.head_dim
+    # attention heads are sharded by KV head; with fewer KV heads than ranks they replicate
+    kv_rep = max(1, tp_size // cfg.n_kv_heads)
+    kv_shards = min(tp_size, cfg.n_kv_heads)
+    q0, q1 = shard_range(cfg.n_heads, tp_rank, tp_size)
+    k0, k1 = shard_range(cfg.n_kv_heads, tp_rank // kv_rep, kv_shards)
+    qr, kr = (q0 * hd, q1 * hd), (k0 * hd, k1 * hd)
+    mla = None
+    if src.has(f"{p}.ssm_in.weight"):
+        if tp_size > 1:
+            raise ValueError("state-space layers are not sharded: run this model with tp_size = 1")
+        di = cfg.ssm_d_inner
+        ssm = SSMWeights(in_proj=src.matrix(f"{p}.ssm_in.weight"), conv_kernel=src.vector(f"{p}.ssm_conv1d.weight").reshape(di, -1),
+                         conv_bias=src.vector(f"{p}.ssm_conv1d.bias") if src.has(f"{p}.ssm_conv1d.bias") else None,
+                         x_proj=src.matrix(f"{p}.ssm_x.weight"), dt_proj=src.matrix(f"{p}.ssm_dt.weight"),
+                         dt_bias=src.vector(f"{p}.ssm_dt.bias"), a=src.vector(f"{p}.ssm_a").reshape(di, -1),
+                         d=src.vector(f"{p}.ssm_d"), out_proj=LinearWeight([src.matrix(f"{p}.ssm_out.weight")]))
+        return LayerWeights(attn_norm=src.vector(f"{p}.attn_norm.weight"), wqkv=None, wo=None, ffn_norm=None, ssm=ssm)
+    if src.has(f"{p}.shortconv.conv.weight"):
+        if tp_size > 1:
+            raise ValueError("short-convolution layers are not sharded: run this model with tp_size = 1")
+        lw = LayerWeights(attn_norm=src.vector(f"{p}.attn_norm.weight"), wqkv=None, wo=None,
+                          ffn_norm=src.vector(f"{p}.ffn_norm.weight"), conv_in=src.matrix(f"{p}.shortconv.in_proj.weight"),
+                          conv_kernel=src.vector(f"{p}.shortconv.conv.weight").reshape(cfg.hidden_size, -1),
+                          conv_out=LinearWeight([src.matrix(f"{p}.shortconv.out_proj.weight")]))
+        _load_ffn(src, cfg, p, lw, tp_rank, tp_size, ep_rank, ep_size)  # dense, or routed experts (LFM2-MoE)
+        return lw
+    if src.has(f"{p}.attn_kv_a_mqa.weight"):
+        mla = _load_mla(src, cfg, p, q0, q1)
+        parts = []
+    elif src.has(f"{p}.attn_qkv.weight"):
+        # one fused tensor (Phi-3): rows are all query heads, then all key heads, then all value heads
+        ko, vo = cfg.n_heads * hd, (cfg.n_heads + cfg.n_kv_heads) * hd
+        parts = [src.matrix(f"{p}.attn_qkv.weight", rows=qr), src.matrix(f"{p}.attn_qkv.weight", rows=(ko + kr[0], ko + kr[1])),
+                 src.matrix(f"{p}.attn_qkv.weight", rows=(vo + kr[0], vo + kr[1]))]
+    else:
+        parts = [src.matrix(f"{p}.attn_q.weight", rows=qr), src.matrix(f"{p}.attn_k.weight", rows=kr),
+                 src.matrix(f"{p}.attn_v.weight", rows=kr)]
+    bias = None
+    if src.has(f"{p}.attn_qkv.bias"):
+        b = src.vector(f"{p}.attn_qkv.bias")
+        ko, vo = cfg.n_heads * hd, (cfg.n_heads + cfg.n_kv_heads) * hd
+        bias = torch.cat([b[qr[0]:qr[1]], b[ko + kr[0]:ko + kr[1]], b[vo + kr[0]:vo + kr[1]]])
+    elif src.has(f"{p}.attn_q.bias"):
+        bias = torch.cat([src.vector(f"{p}.attn_q.bias")[qr[0]:qr[1]], src.vector(f"{p}.attn_k.bias")[kr[0]:kr[1]],
+                          src.vector(f"{p}.attn_v.bias")[kr[0]:kr[1]]])
+    vd = cfg.v_head_dim if mla is not None else hd
+    lw = LayerWeights(
+        attn_norm=src.vector(f"{p}.attn_norm.weight"),
+        wqkv=LinearWeight(fuse_rows(parts), bias) if mla is None else None,
+        wo=LinearWeight([src.matrix(f"{p}.attn_output.weight", cols=(q0 * vd, q1 * vd))]),
+        ffn_norm=src.vector(f"{p}.ffn_norm.weight"),
+        mla=mla,
+    )
+    if src.has(f"{p}.attn_q_norm.weight"):
+        lw.q_norm = src.vector(f"{p}.attn_q_norm.weight")
+        lw.k_norm = src.vector(f"{p}.attn_k_norm.weight")
+    if src.has(f"{p}.post_attention_norm.weight"):
+        lw.post_attn_norm = src.vector(f"{p}.post_attention_norm.weight")
+    if src.has(f"{p}.post_ffw_norm.weight"):
+        lw.post_ffn_norm = src.vector(f"{p}.post_ffw_norm.weight")
+    _load_ffn(src, cfg, p, lw, tp_rank, tp_size, ep_rank, ep_size)
     return lw
 
 

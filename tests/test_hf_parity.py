@@ -74,6 +74,14 @@ def _build(name: str):
     if name == "lfm2":  # convolution layers (kernel of 3 taps) around two attention layers with RMSNorm on q / k heads
         return T.Lfm2ForCausalLM(T.Lfm2Config(**c, conv_L_cache=3, block_auto_adjust_ff_dim=False,
                                               layer_types=["conv", "conv", "full_attention", "conv"]))
+    if name == "lfm2moe":  # one dense layer, then 8 routed experts: sigmoid scores, a bias that only steers the choice, weights * 1.5
+        m = T.Lfm2MoeForCausalLM(T.Lfm2MoeConfig(**c, conv_L_cache=3, moe_intermediate_size=48, num_experts=8, num_experts_per_tok=2,
+                                                 num_dense_layers=1, use_expert_bias=True, routed_scaling_factor=1.5,
+                                                 layer_types=["conv", "full_attention", "conv", "full_attention"]))
+        with torch.no_grad():
+            for layer in m.model.layers[1:]:
+                layer.feed_forward.expert_bias.copy_(torch.randn(8) * 0.3)
+        return m
     # DeepSeek: latent attention (32-wide latent, 16 position-free + 8 rotary query / key values per head, 24-wide values),
     # one dense layer then routed experts + a shared expert
     ds = dict(c, moe_intermediate_size=48, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2, first_k_dense_replace=1,
@@ -92,7 +100,7 @@ def _build(name: str):
 
 
 FAMILIES = ["llama", "qwen2", "qwen3", "phi3", "mixtral", "qwen3moe", "gemma", "gemma2", "gemma3", "deepseek_v2", "deepseek_v3",
-            "deepseek_v3_yarn", "lfm2", "mamba", "mistral_swa", "qwen2moe",
+            "deepseek_v3_yarn", "lfm2", "lfm2moe", "mamba", "mistral_swa", "qwen2moe",
             "llama31_rope", "phi3_longrope"]
 
 
@@ -129,6 +137,9 @@ def test_logits_and_greedy_tokens_match_transformers(family, tmp_path):
         assert cfg.is_ssm and (cfg.ssm_d_inner, cfg.ssm_d_state, cfg.ssm_d_conv, cfg.ssm_dt_rank) == (128, 8, 4, 8)
     if family == "lfm2":
         assert cfg.conv_layers == [0, 1, 3] and cfg.conv_l_cache == 3 and cfg.qk_norm and cfg.n_kv_heads == 2
+    if family == "lfm2moe":
+        assert cfg.conv_layers == [0, 2] and cfg.n_experts == 8 and cfg.leading_dense_blocks == 1 and cfg.expert_gating == "sigmoid"
+        assert cfg.expert_weights_scale == 1.5 and cfg.expert_ffn_size == 48
     if family == "gemma3":
         assert cfg.sliding_window_pattern == 6 and cfg.rope_theta_swa == 10000.0 and cfg.rope_theta == 1000000.0
         assert cfg.qk_norm and cfg.post_norms and cfg.ffn_act == "gelu_tanh" and cfg.embedding_scale == 8.0
