@@ -24,7 +24,8 @@ _ARCH = {"LlamaForCausalLM": "llama", "MistralForCausalLM": "llama", "MixtralFor
          "Qwen2MoeForCausalLM": "qwen2moe", "DeepseekV2ForCausalLM": "deepseek2", "DeepseekV3ForCausalLM": "deepseek2",
          "Phi3ForCausalLM": "phi3", "GemmaForCausalLM": "gemma", "Gemma2ForCausalLM": "gemma2",
          "Gemma3ForCausalLM": "gemma3", "Gemma3ForConditionalGeneration": "gemma3", "Lfm2ForCausalLM": "lfm2",
-         "Lfm2MoeForCausalLM": "lfm2moe", "MambaForCausalLM": "mamba"}
+         "Lfm2MoeForCausalLM": "lfm2moe", "Glm4MoeForCausalLM": "glm4moe", "Glm4ForCausalLM": "glm4",
+         "HunYuanMoEV1ForCausalLM": "hunyuan-moe", "HunYuanDenseV1ForCausalLM": "hunyuan-dense", "MambaForCausalLM": "mamba"}
 GEMMA = ("gemma", "gemma2", "gemma3")
 
 
@@ -46,6 +47,10 @@ def _rope_settings(c: Dict[str, Any]) -> Tuple[float, float, Dict[str, Any]]:
         full, local = rp.get("full_attention") or {}, rp.get("sliding_attention") or {}
         return float(full.get("rope_theta", 10000.0)), float(local.get("rope_theta", 0.0)), full
     theta = float(rp.get("rope_theta") or c.get("rope_theta") or 10000.0)
+    if rp.get("rope_type") == "dynamic" and rp.get("alpha") and str(c.get("model_type", "")).startswith("hunyuan"):
+        # Hunyuan's fixed NTK stretch: the base grows by alpha ** (d / (d - 2)); files carry the grown base
+        hd = int(c.get("head_dim") or int(c["hidden_size"]) // int(c["num_attention_heads"]))
+        return theta * float(rp["alpha"]) ** (hd / (hd - 2)), 0.0, {}
     return theta, float(c.get("rope_local_base_freq") or 0.0), (rp if rp.get("rope_type") else c.get("rope_scaling") or {})
 
 
@@ -141,7 +146,7 @@ def write_hf_metadata(w: GGUFWriter, arch: str, c: Dict[str, Any]) -> None:
     theta, theta_swa, rs = _rope_settings(c)
     w.add(f"{arch}.rope.freq_base", theta, F)
     w.add(f"{arch}.rope.dimension_count",
-          int(c["qk_rope_head_dim"]) if c.get("kv_lora_rank") else int(hd * float(c.get("partial_rotary_factor", 1.0))), U)
+          int(c["qk_rope_head_dim"]) if c.get("kv_lora_rank") else int(hd * float(c.get("partial_rotary_factor") or (c.get("rope_parameters") or {}).get("partial_rotary_factor") or 1.0)), U)
     if c.get("sliding_window"):
         w.add(f"{arch}.attention.sliding_window", int(c["sliding_window"]), U)
     if arch in GEMMA:
@@ -180,13 +185,13 @@ def write_hf_metadata(w: GGUFWriter, arch: str, c: Dict[str, Any]) -> None:
             if kind == "yarn" and c.get("kv_lora_rank"):
                 w.add(f"{arch}.rope.scaling.yarn_log_multiplier", 0.1 * float(rs.get("mscale_all_dim") or 0.0), F)
     n_exp = int(c.get("num_local_experts") or c.get("num_experts") or c.get("n_routed_experts") or 0)
-    if n_exp:
+    if n_exp > 1 or (n_exp and not arch.startswith("hunyuan")):
         w.add(f"{arch}.expert_count", n_exp, U)
-        w.add(f"{arch}.expert_used_count", int(c.get("num_experts_per_tok", 2)), U)
+        w.add(f"{arch}.expert_used_count", int(c.get("num_experts_per_tok") or c.get("moe_topk") or 2), U)
         w.add(f"{arch}.expert_feed_forward_length", int(c.get("moe_intermediate_size") or c.get("intermediate_size")), U)
         # DeepSeek-V3 configs often omit scoring_func: that model always scores with a sigmoid
         sigmoid = c.get("scoring_func") == "sigmoid" or (c.get("scoring_func") is None
-                                                         and c.get("model_type") in ("deepseek_v3", "lfm2_moe"))
+                                                         and c.get("model_type") in ("deepseek_v3", "lfm2_moe", "glm4_moe"))
         w.add(f"{arch}.expert_gating_func", 2 if sigmoid else 1, U)
         w.add(f"{arch}.expert_weights_scale", float(c.get("routed_scaling_factor", 1.0)), F)
         w.add(f"{arch}.expert_weights_norm", bool(c.get("norm_topk_prob", True)))

@@ -617,6 +617,21 @@ _HF_LAYER_MAP_GEMMA = {
     "pre_feedforward_layernorm.weight": "ffn_norm.weight",
     "post_feedforward_layernorm.weight": "post_ffw_norm.weight",
 }
+# GLM-4: norms on both branch outputs as well, gate and up projection in one tensor (gate rows first)
+_HF_LAYER_MAP_GLM4 = {
+    "post_self_attn_layernorm.weight": "post_attention_norm.weight",
+    "post_mlp_layernorm.weight": "post_ffw_norm.weight",
+    "mlp.gate_up_proj.weight": "ffn_up.weight",
+}
+# Hunyuan: norms on the rotated q / k heads, router under gate.wg, an always-on shared MLP
+_HF_LAYER_MAP_HUNYUAN = {
+    "self_attn.query_layernorm.weight": "attn_q_norm.weight",
+    "self_attn.key_layernorm.weight": "attn_k_norm.weight",
+    "mlp.gate.wg.weight": "ffn_gate_inp.weight",
+    "mlp.shared_mlp.gate_proj.weight": "ffn_gate_shexp.weight",
+    "mlp.shared_mlp.up_proj.weight": "ffn_up_shexp.weight",
+    "mlp.shared_mlp.down_proj.weight": "ffn_down_shexp.weight",
+}
 # LFM2: operator norm, short-convolution tensors, w1 / w3 / w2 feed-forward names, RMSNorm on q / k heads
 _HF_LAYER_MAP_LFM2 = {
     "operator_norm.weight": "attn_norm.weight",
@@ -688,6 +703,10 @@ def map_hf_tensor_name(name: str, arch: Optional[str] = None) -> Optional[Tuple[
         return f"blk.{layer}.{_HF_LAYER_MAP_GEMMA[rest]}", None
     if arch in ("lfm2", "lfm2moe") and rest in _HF_LAYER_MAP_LFM2:
         return f"blk.{layer}.{_HF_LAYER_MAP_LFM2[rest]}", None
+    if arch and arch.startswith("hunyuan") and rest in _HF_LAYER_MAP_HUNYUAN:
+        return f"blk.{layer}.{_HF_LAYER_MAP_HUNYUAN[rest]}", None
+    if arch == "glm4" and rest in _HF_LAYER_MAP_GLM4:
+        return f"blk.{layer}.{_HF_LAYER_MAP_GLM4[rest]}", None
     if rest in _HF_LAYER_MAP:
         return f"blk.{layer}.{_HF_LAYER_MAP[rest]}", None
     e = _HF_EXPERT_RE.match(rest)

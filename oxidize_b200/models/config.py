@@ -19,15 +19,21 @@ from ..formats.gguf import GGUFFile
 # branch outputs, soft-capped logits, interleaved local / global attention with two rotary bases.
 # lfm2 / lfm2moe: short-convolution mixers interleaved with grouped-query attention layers (lfm2moe: routed experts
 # after the leading dense layers, sigmoid scores, a per-expert bias used for the choice only).
+# glm4: Llama layers with norms on both branch outputs too, a fused gate-up tensor, and half of each head rotated over
+# pairs of neighbouring values.
+# hunyuan-dense / hunyuan-moe: RMSNorm on the q / k heads AFTER the rotation; the MoE form adds an always-on shared MLP.
+# glm4moe: grouped-query attention over half-rotated heads, DeepSeek-V3 style routing (sigmoid scores, correction bias, groups).
 # mamba: selective state-space layers only (no attention, no feed-forward block).
-DENSE_ARCHS = {"llama", "mistral", "qwen2", "qwen3", "deepseek", "phi3", "gemma", "gemma2", "gemma3", "lfm2", "mamba"}
+DENSE_ARCHS = {"llama", "mistral", "qwen2", "qwen3", "deepseek", "phi3", "gemma", "gemma2", "gemma3", "lfm2", "mamba", "glm4",
+               "hunyuan-dense", "hunyuan_dense"}
 GEMMA_ARCHS = {"gemma", "gemma2", "gemma3"}
-MOE_ARCHS = {"mixtral", "qwen2moe", "qwen3moe", "deepseek2", "deepseek-moe", "deepseek_moe", "lfm2moe"}
+MOE_ARCHS = {"mixtral", "qwen2moe", "qwen3moe", "deepseek2", "deepseek-moe", "deepseek_moe", "lfm2moe", "glm4moe",
+             "hunyuan-moe", "hunyuan_moe"}
 # Architectures whose layers need math this engine does not have (two attention geometries in one model,
 # parallel attention / MLP blocks, recurrent or convolutional mixers): loading one would run it as
 # a plain Llama and produce wrong tokens, so they are refused by name.
 UNSUPPORTED_ARCHS = {"gemma4", "phi", "phi2", "llama4", "qwen35", "qwen3_5_moe", "mamba2", "jamba",
-                     "glm4", "falcon", "gpt2", "bert"}
+                     "falcon", "gpt2", "bert"}
 
 
 class UnsupportedArchitecture(ValueError):
@@ -65,6 +71,7 @@ class ModelConfig:
     rms_eps: float = 1e-5
     rope_theta: float = 10000.0
     rope_dim: int = 0  # 0 -> head_dim (full rotary)
+    qk_norm_after_rope: bool = False  # Hunyuan: the per-head q / k norms act on the rotated vectors
     rope_pairing: str = "split_half"  # split_half (NeoX; what all reference engines do) | adjacent
     rope_attn_factor: float = 1.0  # magnitude factor that goes with the long LongRoPE frequency factors (Phi-3)
     rope_scaling: RopeScaling = field(default_factory=RopeScaling)
@@ -272,6 +279,11 @@ def config_from_gguf(g: GGUFFile) -> ModelConfig:
         first_attn = next((i for i in range(c.n_layers) if i not in c.conv_layers), 0)
         c.qk_norm = g.has_tensor(f"blk.{first_attn}.attn_q_norm.weight")
         c.tie_embeddings = not g.has_tensor("output.weight")
+    if arch.startswith("hunyuan"):
+        c.qk_norm_after_rope = c.qk_norm
+    if arch == "glm4":
+        c.rope_pairing = "adjacent"
+        c.post_norms = g.has_tensor("blk.0.post_attention_norm.weight")
     if arch in GEMMA_ARCHS:
         c.embedding_scale = float(c.hidden_size) ** 0.5
         c.ffn_act = "gelu_tanh"

@@ -174,7 +174,7 @@ class Transformer:
                     and w.parts[0].data.is_contiguous())
 
         for lw in self.w.layers:
-            if (lw.router is not None or lw.post_attn_norm is not None or lw.post_ffn_norm is not None
+            if (lw.router is not None or lw.post_attn_norm is not None or lw.post_ffn_norm is not None or cfg.qk_norm_after_rope
                     or not (bf16_single(lw.wqkv) and bf16_single(lw.wo) and bf16_single(lw.w_gate_up)
                             and bf16_single(lw.w_down) and lw.w_gate_up.swiglu_interleaved)):
                 continue
@@ -412,7 +412,7 @@ class Transformer:
             return self._mla_attention(lw, layer, x, meta, kv)
         window = cfg.layer_sliding_window(window_of)
         rope = self._layer_rope(window)
-        if self._fuse_qkv_rope and x.is_cuda and lw.wqkv.bias is None:
+        if self._fuse_qkv_rope and x.is_cuda and lw.wqkv.bias is None and not cfg.qk_norm_after_rope:
             from ..ops import cuda as opcuda
 
             if opcuda.qkv_rope_fusable(lw.wqkv.parts, kv, rope, lw.q_norm, lw.k_norm):
@@ -420,7 +420,8 @@ class Transformer:
                 attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, window, cfg.attn_softcap)
                 return self.comm.linear_allreduce(attn.reshape(attn.shape[0], -1), lw.wo)
         qkv = ops.linear(x, lw.wqkv)
-        q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, rope, lw.q_norm, lw.k_norm, cfg.rms_eps)
+        q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, rope, lw.q_norm, lw.k_norm, cfg.rms_eps,
+                                 norm_after=cfg.qk_norm_after_rope)
         attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, window, cfg.attn_softcap)
         return self.comm.linear_allreduce(attn.reshape(attn.shape[0], -1), lw.wo)
 

@@ -81,7 +81,7 @@ class LoraModel(torch.nn.Module):
     def __init__(self, weights: ModelWeights, lora: LoraConfig, qlora: bool = False, seed: int = 0):
         super().__init__()
         cfg = weights.cfg
-        if cfg.is_moe or cfg.is_mla:
+        if cfg.is_moe or cfg.is_mla or cfg.is_ssm or cfg.conv_layers or cfg.qk_norm_after_rope:
             raise NotImplementedError("the trainer covers the dense grouped-query decoder families")
         if weights.tp_size != 1 or weights.first_layer != 0:
             raise ValueError("the trainer wants the whole model on one rank")

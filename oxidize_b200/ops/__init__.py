@@ -75,21 +75,26 @@ def gelu_mul(gate_up):
 
 
 @instrument("qk_rope_kv_write")
-def qk_rope_kv_write(qkv, positions, slot_mapping, kv, layer, rope, q_norm=None, k_norm=None, eps=1e-6):
+def qk_rope_kv_write(qkv, positions, slot_mapping, kv, layer, rope, q_norm=None, k_norm=None, eps=1e-6, norm_after=False):
     """Split fused qkv [T, (nq+2nkv)*hd], optional per-head QK RMSNorm, RoPE on q and k,
-    write K/V into the paged cache.  Returns rotated q as [T, nq, hd]."""
-    if qkv.is_cuda:
+    write K/V into the paged cache.  Returns rotated q as [T, nq, hd].  ``norm_after``: the norms act on the rotated
+    vectors (Hunyuan); that order runs as torch operations on either device."""
+    norm_after = norm_after and q_norm is not None
+    if qkv.is_cuda and not norm_after:
         return _cuda().qk_rope_kv_write(qkv, positions, slot_mapping, kv, layer, rope, q_norm, k_norm, eps)
     nq, nkv, hd = rope.n_heads, rope.n_kv_heads, rope.head_dim
     T = qkv.shape[0]
     q = qkv[:, : nq * hd].reshape(T, nq, hd)
     k = qkv[:, nq * hd : (nq + nkv) * hd].reshape(T, nkv, hd)
     v = qkv[:, (nq + nkv) * hd :].reshape(T, nkv, hd)
-    if q_norm is not None:
+    if q_norm is not None and not norm_after:
         q = ref.rmsnorm(q, q_norm, eps)
         k = ref.rmsnorm(k, k_norm, eps)
     q = ref.apply_rope(q, positions, rope.inv_freq, rope.pairing, rope.mscale)
     k = ref.apply_rope(k, positions, rope.inv_freq, rope.pairing, rope.mscale)
+    if norm_after:
+        q = ref.rmsnorm(q, q_norm, eps).to(qkv.dtype)
+        k = ref.rmsnorm(k, k_norm, eps).to(qkv.dtype)
     ref.kv_write(kv, layer, k, v, slot_mapping)
     return q
 

@@ -82,6 +82,23 @@ def _build(name: str):
             for layer in m.model.layers[1:]:
                 layer.feed_forward.expert_bias.copy_(torch.randn(8) * 0.3)
         return m
+    if name == "hunyuan_moe":  # norms on the rotated q / k heads, softmax routing over 8 experts + an always-on shared MLP, NTK-stretched base
+        return T.HunYuanMoEV1ForCausalLM(T.HunYuanMoEV1Config(**c, head_dim=16, num_experts=8, moe_topk=2,
+                                                              rope_parameters={"rope_type": "dynamic", "rope_theta": 10000.0, "alpha": 50.0, "factor": 1.0}))
+    if name == "hunyuan_dense":
+        return T.HunYuanDenseV1ForCausalLM(T.HunYuanDenseV1Config(**c, head_dim=16))
+    if name == "glm4":  # norms on both sides of both branches, fused gate-up, neighbouring values rotated over half of each head
+        return T.Glm4ForCausalLM(T.Glm4Config(**c, head_dim=16, pad_token_id=0, attention_bias=True,
+                                              rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5}))
+    if name == "glm4moe":  # half of each head rotated, q/k/v biases, norms on q / k heads, DeepSeek-V3 style routing after a dense layer
+        m = T.Glm4MoeForCausalLM(T.Glm4MoeConfig(**c, moe_intermediate_size=48, n_routed_experts=8, n_shared_experts=1,
+                                                 num_experts_per_tok=2, first_k_dense_replace=1, n_group=2, topk_group=1,
+                                                 routed_scaling_factor=1.5, norm_topk_prob=True, use_qk_norm=True, attention_bias=True,
+                                                 rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5}))
+        with torch.no_grad():
+            for layer in m.model.layers[1:]:
+                layer.mlp.gate.e_score_correction_bias.copy_(torch.randn(8) * 0.3)
+        return m
     # DeepSeek: latent attention (32-wide latent, 16 position-free + 8 rotary query / key values per head, 24-wide values),
     # one dense layer then routed experts + a shared expert
     ds = dict(c, moe_intermediate_size=48, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2, first_k_dense_replace=1,
@@ -100,7 +117,7 @@ def _build(name: str):
 
 
 FAMILIES = ["llama", "qwen2", "qwen3", "phi3", "mixtral", "qwen3moe", "gemma", "gemma2", "gemma3", "deepseek_v2", "deepseek_v3",
-            "deepseek_v3_yarn", "lfm2", "lfm2moe", "mamba", "mistral_swa", "qwen2moe",
+            "deepseek_v3_yarn", "lfm2", "lfm2moe", "glm4", "glm4moe", "hunyuan_moe", "hunyuan_dense", "mamba", "mistral_swa", "qwen2moe",
             "llama31_rope", "phi3_longrope"]
 
 
@@ -137,6 +154,16 @@ def test_logits_and_greedy_tokens_match_transformers(family, tmp_path):
         assert cfg.is_ssm and (cfg.ssm_d_inner, cfg.ssm_d_state, cfg.ssm_d_conv, cfg.ssm_dt_rank) == (128, 8, 4, 8)
     if family == "lfm2":
         assert cfg.conv_layers == [0, 1, 3] and cfg.conv_l_cache == 3 and cfg.qk_norm and cfg.n_kv_heads == 2
+    if family.startswith("hunyuan"):
+        assert cfg.qk_norm and cfg.qk_norm_after_rope
+    if family == "hunyuan_moe":
+        assert cfg.n_experts == 8 and cfg.n_shared_experts == 1 and not cfg.shared_expert_gate and cfg.expert_gating == "softmax"
+        assert abs(cfg.rope_theta - 10000.0 * 50.0 ** (16 / 14)) < 1.0
+    if family == "glm4":
+        assert cfg.rope_pairing == "adjacent" and cfg.rope_dim == 8 and cfg.post_norms and cfg.attn_bias
+    if family == "glm4moe":
+        assert cfg.rope_dim == 8 and cfg.qk_norm and cfg.attn_bias and cfg.expert_gating == "sigmoid" and cfg.expert_group_count == 2
+        assert cfg.n_shared_experts == 1 and cfg.leading_dense_blocks == 1
     if family == "lfm2moe":
         assert cfg.conv_layers == [0, 2] and cfg.n_experts == 8 and cfg.leading_dense_blocks == 1 and cfg.expert_gating == "sigmoid"
         assert cfg.expert_weights_scale == 1.5 and cfg.expert_ffn_size == 48
