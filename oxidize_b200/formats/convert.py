@@ -25,6 +25,8 @@ _ARCH = {"LlamaForCausalLM": "llama", "MistralForCausalLM": "llama", "MixtralFor
          "Phi3ForCausalLM": "phi3", "GemmaForCausalLM": "gemma", "Gemma2ForCausalLM": "gemma2",
          "Gemma3ForCausalLM": "gemma3", "Gemma3ForConditionalGeneration": "gemma3", "Lfm2ForCausalLM": "lfm2",
          "Lfm2MoeForCausalLM": "lfm2moe", "Glm4MoeForCausalLM": "glm4moe", "Glm4ForCausalLM": "glm4",
+         "Qwen3_5ForCausalLM": "qwen35", "Qwen3_5ForConditionalGeneration": "qwen35",
+         "Qwen3_5MoeForCausalLM": "qwen35moe", "Qwen3_5MoeForConditionalGeneration": "qwen35moe",
          "HunYuanMoEV1ForCausalLM": "hunyuan-moe", "HunYuanDenseV1ForCausalLM": "hunyuan-dense", "MambaForCausalLM": "mamba"}
 GEMMA = ("gemma", "gemma2", "gemma3")
 
@@ -147,6 +149,16 @@ def write_hf_metadata(w: GGUFWriter, arch: str, c: Dict[str, Any]) -> None:
     w.add(f"{arch}.rope.freq_base", theta, F)
     w.add(f"{arch}.rope.dimension_count",
           int(c["qk_rope_head_dim"]) if c.get("kv_lora_rank") else int(hd * float(c.get("partial_rotary_factor") or (c.get("rope_parameters") or {}).get("partial_rotary_factor") or 1.0)), U)
+    if arch in ("qwen35", "qwen35moe"):
+        vh, vd = int(c.get("linear_num_value_heads", 0)), int(c.get("linear_value_head_dim", 0))
+        w.add(f"{arch}.ssm.conv_kernel", int(c.get("linear_conv_kernel_dim", 4)), U)
+        w.add(f"{arch}.ssm.state_size", int(c.get("linear_key_head_dim", vd)), U)
+        w.add(f"{arch}.ssm.group_count", int(c.get("linear_num_key_heads", vh)), U)
+        w.add(f"{arch}.ssm.time_step_rank", vh, U)
+        w.add(f"{arch}.ssm.inner_size", vh * vd, U)
+        kinds = c.get("layer_types") or []
+        if "full_attention" in kinds:
+            w.add(f"{arch}.full_attention_interval", kinds.index("full_attention") + 1, U)
     if c.get("sliding_window"):
         w.add(f"{arch}.attention.sliding_window", int(c["sliding_window"]), U)
     if arch in GEMMA:
@@ -247,9 +259,10 @@ def convert_safetensors_to_gguf(src_dir: str, out_path: str, quant: str = "F16",
         return int(parts[1]) if parts[0] == "blk" else 0
 
     def encode(gname: str, arr_f32: np.ndarray):
-        if arr_f32.ndim == 1 or "norm" in gname or gname.endswith(".bias") or "ffn_gate_inp" in gname or gname.endswith("ssm_d"):
-            if arch in GEMMA and gname.endswith("norm.weight"):
-                arr_f32 = arr_f32 + 1.0  # Gemma stores w - 1; files carry the multiplier itself (as llama.cpp's do)
+        if (arr_f32.ndim == 1 or "norm" in gname or gname.endswith(".bias") or "ffn_gate_inp" in gname or gname.endswith("ssm_d")
+                or "ssm_alpha" in gname or "ssm_beta" in gname):
+            if (arch in GEMMA or (arch in ("qwen35", "qwen35moe") and not gname.endswith("ssm_norm.weight"))) and gname.endswith("norm.weight"):
+                arr_f32 = arr_f32 + 1.0  # Gemma and Qwen3.5 store w - 1; files carry the multiplier itself (as llama.cpp's do)
             return arr_f32.astype(np.float32), "F32"
         t = pick_type(quant, _kind_of(gname), layer_of(gname), L, arr_f32.shape[-1])
         return qref.quantize(t, arr_f32.reshape(-1)), t

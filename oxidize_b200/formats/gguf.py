@@ -632,6 +632,18 @@ _HF_LAYER_MAP_HUNYUAN = {
     "mlp.shared_mlp.up_proj.weight": "ffn_up_shexp.weight",
     "mlp.shared_mlp.down_proj.weight": "ffn_down_shexp.weight",
 }
+# Qwen3.5 gated-delta-rule layers, under the names llama.cpp's converter gives them
+_HF_LAYER_MAP_QWEN35 = {
+    "linear_attn.in_proj_qkv.weight": "attn_qkv.weight",
+    "linear_attn.in_proj_z.weight": "attn_gate.weight",
+    "linear_attn.in_proj_a.weight": "ssm_alpha.weight",
+    "linear_attn.in_proj_b.weight": "ssm_beta.weight",
+    "linear_attn.conv1d.weight": "ssm_conv1d.weight",
+    "linear_attn.dt_bias": "ssm_dt.bias",
+    "linear_attn.A_log": "ssm_a",
+    "linear_attn.norm.weight": "ssm_norm.weight",
+    "linear_attn.out_proj.weight": "ssm_out.weight",
+}
 # LFM2: operator norm, short-convolution tensors, w1 / w3 / w2 feed-forward names, RMSNorm on q / k heads
 _HF_LAYER_MAP_LFM2 = {
     "operator_norm.weight": "attn_norm.weight",
@@ -705,6 +717,8 @@ def map_hf_tensor_name(name: str, arch: Optional[str] = None) -> Optional[Tuple[
         return f"blk.{layer}.{_HF_LAYER_MAP_LFM2[rest]}", None
     if arch and arch.startswith("hunyuan") and rest in _HF_LAYER_MAP_HUNYUAN:
         return f"blk.{layer}.{_HF_LAYER_MAP_HUNYUAN[rest]}", None
+    if arch in ("qwen35", "qwen35moe") and rest in _HF_LAYER_MAP_QWEN35:
+        return f"blk.{layer}.{_HF_LAYER_MAP_QWEN35[rest]}", None
     if arch == "glm4" and rest in _HF_LAYER_MAP_GLM4:
         return f"blk.{layer}.{_HF_LAYER_MAP_GLM4[rest]}", None
     if rest in _HF_LAYER_MAP:

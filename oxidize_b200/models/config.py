@@ -23,16 +23,20 @@ from ..formats.gguf import GGUFFile
 # pairs of neighbouring values.
 # hunyuan-dense / hunyuan-moe: RMSNorm on the q / k heads AFTER the rotation; the MoE form adds an always-on shared MLP.
 # glm4moe: grouped-query attention over half-rotated heads, DeepSeek-V3 style routing (sigmoid scores, correction bias, groups).
+# qwen35: three gated-delta-rule layers (linear attention with a per-sequence matrix state) to every attention layer, whose
+# output passes a sigmoid gate computed beside the queries; norm weights stored as w - 1.
 # mamba: selective state-space layers only (no attention, no feed-forward block).
 DENSE_ARCHS = {"llama", "mistral", "qwen2", "qwen3", "deepseek", "phi3", "gemma", "gemma2", "gemma3", "lfm2", "mamba", "glm4",
+               "qwen35", "qwen3_5", "qwen3_5_text", "qwen35_text",
                "hunyuan-dense", "hunyuan_dense"}
 GEMMA_ARCHS = {"gemma", "gemma2", "gemma3"}
-MOE_ARCHS = {"mixtral", "qwen2moe", "qwen3moe", "deepseek2", "deepseek-moe", "deepseek_moe", "lfm2moe", "glm4moe",
+MOE_ARCHS = {"mixtral", "qwen2moe", "qwen3moe", "deepseek2", "deepseek-moe", "deepseek_moe", "lfm2moe", "glm4moe", "qwen35moe", "qwen3_5_moe", "qwen3_5_moe_text",
              "hunyuan-moe", "hunyuan_moe"}
 # Architectures whose layers need math this engine does not have (two attention geometries in one model,
 # parallel attention / MLP blocks, recurrent or convolutional mixers): loading one would run it as
 # a plain Llama and produce wrong tokens, so they are refused by name.
-UNSUPPORTED_ARCHS = {"gemma4", "phi", "phi2", "llama4", "qwen35", "qwen3_5_moe", "mamba2", "jamba",
+QWEN35_ARCHS = {"qwen35", "qwen3_5", "qwen3_5_text", "qwen35_text", "qwen35moe", "qwen3_5_moe", "qwen3_5_moe_text"}
+UNSUPPORTED_ARCHS = {"gemma4", "phi", "phi2", "llama4", "mamba2", "jamba",
                      "falcon", "gpt2", "bert"}
 
 
@@ -71,6 +75,15 @@ class ModelConfig:
     rms_eps: float = 1e-5
     rope_theta: float = 10000.0
     rope_dim: int = 0  # 0 -> head_dim (full rotary)
+    # Gated-delta-rule layers (Qwen3.5; the reference's run_mamba_layer, model/layer_wise/ssm.rs:82): which layers, key /
+    # value head counts and widths, taps of the causal convolution in front of q / k / v
+    gdn_layers: List[int] = field(default_factory=list)
+    gdn_k_heads: int = 0
+    gdn_v_heads: int = 0
+    gdn_k_dim: int = 0
+    gdn_v_dim: int = 0
+    gdn_conv: int = 4
+    attn_out_gate: bool = False  # q_proj also yields a per-head gate; attention output * sigmoid(gate)
     qk_norm_after_rope: bool = False  # Hunyuan: the per-head q / k norms act on the rotated vectors
     rope_pairing: str = "split_half"  # split_half (NeoX; what all reference engines do) | adjacent
     rope_attn_factor: float = 1.0  # magnitude factor that goes with the long LongRoPE frequency factors (Phi-3)
@@ -138,7 +151,7 @@ class ModelConfig:
 
     @property
     def is_ssm(self) -> bool:
-        return self.ssm_d_inner > 0
+        return self.ssm_d_inner > 0 or bool(self.gdn_layers)
 
     @property
     def rotary_dim(self) -> int:
@@ -279,6 +292,21 @@ def config_from_gguf(g: GGUFFile) -> ModelConfig:
         first_attn = next((i for i in range(c.n_layers) if i not in c.conv_layers), 0)
         c.qk_norm = g.has_tensor(f"blk.{first_attn}.attn_q_norm.weight")
         c.tie_embeddings = not g.has_tensor("output.weight")
+    if arch in QWEN35_ARCHS:
+        c.gdn_layers = [i for i in range(c.n_layers) if g.has_tensor(f"blk.{i}.ssm_alpha.weight")]
+        c.attn_out_gate = True
+        attn = next((i for i in range(c.n_layers) if i not in c.gdn_layers), None)
+        if attn is not None:
+            c.qk_norm = g.has_tensor(f"blk.{attn}.attn_q_norm.weight")
+        if c.gdn_layers:
+            i0 = c.gdn_layers[0]
+            c.gdn_conv = int(_scalar(a("ssm.conv_kernel"), g.tensors[f"blk.{i0}.ssm_conv1d.weight"].shape[-1]))
+            c.gdn_v_heads = int(_scalar(a("ssm.time_step_rank"), g.tensors[f"blk.{i0}.ssm_a"].n_elements))
+            inner = int(_scalar(a("ssm.inner_size"), g.tensors[f"blk.{i0}.attn_gate.weight"].shape[0]))
+            c.gdn_v_dim = inner // c.gdn_v_heads
+            c.gdn_k_dim = int(_scalar(a("ssm.state_size"), c.gdn_v_dim))
+            kdim = (g.tensors[f"blk.{i0}.attn_qkv.weight"].shape[0] - inner) // 2
+            c.gdn_k_heads = int(_scalar(a("ssm.group_count"), kdim // c.gdn_k_dim))
     if arch.startswith("hunyuan"):
         c.qk_norm_after_rope = c.qk_norm
     if arch == "glm4":

@@ -123,19 +123,23 @@ class Transformer:
         # which cache layer a decoder layer writes: attention layers count through the KV cache, convolution layers (hybrid
         # models) through a second cache that holds their gated inputs; the reference's ``kv_layer_map`` (load.rs:470-480)
         conv = set(i - weights.first_layer for i in cfg.conv_layers)
+        gdn = set(i - weights.first_layer for i in cfg.gdn_layers)
         self.kv_index, self.conv_index = [], []
         for li in range(len(weights.layers)):
             is_conv = li in conv
-            self.kv_index.append(-1 if is_conv else sum(1 for j in range(li) if j not in conv))
+            self.kv_index.append(-1 if (is_conv or li in gdn) else sum(1 for j in range(li) if j not in conv and j not in gdn))
             self.conv_index.append(sum(1 for j in range(li) if j in conv) if is_conv else -1)
         self.n_kv_layers = sum(1 for i in self.kv_index if i >= 0)
-        self.n_conv_layers = len(weights.layers) - self.n_kv_layers
+        self.n_conv_layers = sum(1 for i in self.conv_index if i >= 0)
+        # layers with a recurrent state, numbered among themselves
+        rec = sorted(gdn) if gdn else (list(range(len(weights.layers))) if cfg.ssm_d_inner > 0 else [])
+        self.rec_index = {li: n for n, li in enumerate(rec)}
         # state-space layers: per-sequence recurrent state (convolution window + [d_inner, d_state] state per layer), in
         # slots found through the sequence's first page (see _ssm_slot)
         self._ssm_slots: dict = {}
         self._ssm_conv = self._ssm_state = None
         self._ssm_clock = 0
-        if cfg.is_ssm:
+        if cfg.ssm_d_inner > 0:
             self.n_kv_layers = 0
         if cfg.is_mla:
             # One cached row per token, shared by all heads: the normalised latent followed by the rotary key.
@@ -175,6 +179,7 @@ class Transformer:
 
         for lw in self.w.layers:
             if (lw.router is not None or lw.post_attn_norm is not None or lw.post_ffn_norm is not None or cfg.qk_norm_after_rope
+                    or cfg.attn_out_gate
                     or not (bf16_single(lw.wqkv) and bf16_single(lw.wo) and bf16_single(lw.w_gate_up)
                             and bf16_single(lw.w_down) and lw.w_gate_up.swiglu_interleaved)):
                 continue
@@ -282,9 +287,14 @@ class Transformer:
                     if stale:
                         slot = self._ssm_slots.pop(stale[0])[0]
                     else:  # grow by one block of slots
-                        L, di = len(self.w.layers), cfg.ssm_d_inner
-                        add_c = torch.zeros(16, L, di, max(1, cfg.ssm_d_conv - 1), dtype=torch.float32, device=self.device)
-                        add_s = torch.zeros(16, L, di, cfg.ssm_d_state, dtype=torch.float32, device=self.device)
+                        L = len(self.rec_index)
+                        if cfg.gdn_layers:  # convolution window over q / k / v rows, one [key, value] matrix per value head
+                            rows = 2 * cfg.gdn_k_heads * cfg.gdn_k_dim + cfg.gdn_v_heads * cfg.gdn_v_dim
+                            c_shape, s_shape = (rows, max(1, cfg.gdn_conv - 1)), (cfg.gdn_v_heads, cfg.gdn_k_dim, cfg.gdn_v_dim)
+                        else:
+                            c_shape, s_shape = (cfg.ssm_d_inner, max(1, cfg.ssm_d_conv - 1)), (cfg.ssm_d_inner, cfg.ssm_d_state)
+                        add_c = torch.zeros(16, L, *c_shape, dtype=torch.float32, device=self.device)
+                        add_s = torch.zeros(16, L, *s_shape, dtype=torch.float32, device=self.device)
                         self._ssm_conv = add_c if self._ssm_conv is None else torch.cat([self._ssm_conv, add_c])
                         self._ssm_state = add_s if self._ssm_state is None else torch.cat([self._ssm_state, add_s])
                         slot = n
@@ -337,6 +347,57 @@ class Transformer:
                 y[t0 + i] = h @ Cm[i] + D * uc[i]
             self._ssm_state[slot, layer] = h
         return ops.linear((y * torch.nn.functional.silu(z_all)).to(x.dtype), m.out_proj)
+
+    def _gated_delta(self, lw: LayerWeights, layer: int, x: torch.Tensor, meta: BatchMeta, kv) -> torch.Tensor:
+        """Gated delta rule (Qwen3.5's linear attention), sequence by sequence and token by token:
+        (q, k, v) = silu(conv(in_qkv(x))), q and k scaled to unit length per head; per value head a [key, value] matrix S:
+        S = exp(g) S; S += k (beta (v - S^T k))^T; o = S^T q / sqrt(d_k), with g = A softplus(in_a(x) + dt_bias) and
+        beta = sigmoid(in_b(x)); out_proj(rmsnorm(o) * silu(in_z(x))).  The reference's run_mamba_layer
+        (model/layer_wise/ssm.rs:82) is the same recurrence on one token."""
+        cfg, m = self.cfg, lw.gdn
+        Hk, Hv, dk, dv, K = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_k_dim, cfg.gdn_v_dim, cfg.gdn_conv
+        kdim = Hk * dk
+        F = torch.nn.functional
+        T = x.shape[0]
+        mixed = ops.linear(x, m.in_qkv).float()
+        z = ops.linear(x, m.in_z).float().reshape(T, Hv, dv)
+        # decay and write strength steer an exponential recurrence: these two narrow projections stay in float32
+        xf = x.float()
+        beta_all = torch.sigmoid(xf @ m.in_b.dense_cache().float().t())
+        g_all = m.a.float() * F.softplus(xf @ m.in_a.dense_cache().float().t() + m.dt_bias.float())
+        qs, first = meta.query_start.tolist(), meta.block_tables[:, 0].tolist()
+        pos0 = meta.positions.tolist()
+        w = m.conv_kernel.float()
+        ri = self.rec_index[layer]
+        if ri == 0:
+            self._ssm_clock += 1
+        out = torch.empty(T, Hv, dv, dtype=torch.float32, device=x.device)
+        for b in range(len(qs) - 1):
+            t0, t1 = qs[b], qs[b + 1]
+            if t1 == t0:
+                continue
+            n = t1 - t0
+            slot = self._ssm_slot(kv, first[b], pos0[t0] if ri == 0 else -1)
+            win = torch.cat([self._ssm_conv[slot, ri], mixed[t0:t1].t()], dim=1)  # [rows, K-1 + n]
+            qkv = F.silu(sum(w[:, j : j + 1] * win[:, j : j + n] for j in range(K))).t()  # [n, rows]
+            self._ssm_conv[slot, ri] = win[:, -(K - 1):] if K > 1 else win[:, :0]
+            q = qkv[:, :kdim].reshape(n, Hk, dk)
+            k = qkv[:, kdim : 2 * kdim].reshape(n, Hk, dk)
+            v = qkv[:, 2 * kdim :].reshape(n, Hv, dv)
+            q = q * torch.rsqrt((q * q).sum(-1, keepdim=True) + 1e-6) * dk ** -0.5
+            k = k * torch.rsqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+            if Hv != Hk:  # consecutive value heads share a key head
+                q, k = q.repeat_interleave(Hv // Hk, dim=1), k.repeat_interleave(Hv // Hk, dim=1)
+            decay, beta = torch.exp(g_all[t0:t1]), beta_all[t0:t1]
+            S = self._ssm_state[slot, ri]  # [Hv, dk, dv]
+            for i in range(n):
+                S = S * decay[i][:, None, None]
+                delta = (v[i] - (S * k[i][:, :, None]).sum(1)) * beta[i][:, None]
+                S = S + k[i][:, :, None] * delta[:, None, :]
+                out[t0 + i] = (S * q[i][:, :, None]).sum(1)
+            self._ssm_state[slot, ri] = S
+        y = out * torch.rsqrt(out.pow(2).mean(-1, keepdim=True) + cfg.rms_eps) * m.norm.float() * F.silu(z)
+        return ops.linear(y.reshape(T, Hv * dv).to(x.dtype), m.out_proj)
 
     def _short_conv(self, lw: LayerWeights, layer: int, x: torch.Tensor, meta: BatchMeta, kv) -> torch.Tensor:
         """LFM2 mixer: (B, C, v) = in_proj(x); u = B * v; y_t = C_t * sum_j w[:, j] u_{t - (L-1) + j}; out_proj(y).  The rows u
@@ -406,13 +467,15 @@ class Transformer:
         cfg = self.cfg
         if lw.conv_in is not None:
             return self._short_conv(lw, layer, x, meta, kv)
+        if lw.gdn is not None:
+            return self._gated_delta(lw, layer, x, meta, kv)
         window_of = self.w.first_layer + layer  # the window pattern counts decoder layers, the cache counts attention layers
         layer = self.kv_index[layer]
         if lw.mla is not None:
             return self._mla_attention(lw, layer, x, meta, kv)
         window = cfg.layer_sliding_window(window_of)
         rope = self._layer_rope(window)
-        if self._fuse_qkv_rope and x.is_cuda and lw.wqkv.bias is None and not cfg.qk_norm_after_rope:
+        if self._fuse_qkv_rope and x.is_cuda and lw.wqkv.bias is None and not cfg.qk_norm_after_rope and not cfg.attn_out_gate:
             from ..ops import cuda as opcuda
 
             if opcuda.qkv_rope_fusable(lw.wqkv.parts, kv, rope, lw.q_norm, lw.k_norm):
@@ -420,9 +483,18 @@ class Transformer:
                 attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, window, cfg.attn_softcap)
                 return self.comm.linear_allreduce(attn.reshape(attn.shape[0], -1), lw.wo)
         qkv = ops.linear(x, lw.wqkv)
+        gate = None
+        if cfg.attn_out_gate:
+            # the query block holds, per head, the query and then that head's output gate: pull the gates out
+            nq, hd = self.n_heads_local, cfg.head_dim
+            qg = qkv[:, : nq * 2 * hd].reshape(-1, nq, 2 * hd)
+            gate = qg[:, :, hd:].reshape(-1, nq * hd)
+            qkv = torch.cat([qg[:, :, :hd].reshape(-1, nq * hd), qkv[:, nq * 2 * hd :]], dim=-1)
         q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, rope, lw.q_norm, lw.k_norm, cfg.rms_eps,
                                  norm_after=cfg.qk_norm_after_rope)
         attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, window, cfg.attn_softcap)
+        if gate is not None:
+            attn = (attn.reshape(attn.shape[0], -1) * torch.sigmoid(gate.float())).to(attn.dtype)
         return self.comm.linear_allreduce(attn.reshape(attn.shape[0], -1), lw.wo)
 
     def _dense_ffn(self, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:

@@ -195,6 +195,23 @@ class SSMWeights:
 
 
 @dataclass
+class GDNWeights:
+    """Gated-delta-rule mixer (Qwen3.5): in_qkv [2 key_dim + value_dim, hidden], in_z [value_dim, hidden] (output gate),
+    in_a / in_b [v_heads, hidden] (decay and write-strength inputs), depthwise kernel [2 key_dim + value_dim, taps],
+    dt_bias and A (already -exp(A_log)) per value head, the gated norm's weight [head_v_dim], out_proj."""
+
+    in_qkv: QTensor
+    in_z: QTensor
+    in_a: QTensor
+    in_b: QTensor
+    conv_kernel: torch.Tensor
+    dt_bias: torch.Tensor
+    a: torch.Tensor
+    norm: torch.Tensor
+    out_proj: LinearWeight
+
+
+@dataclass
 class LayerWeights:
     attn_norm: torch.Tensor
     wqkv: Optional[LinearWeight]  # None in a latent-attention layer (``mla`` holds its projections) or a convolution layer
@@ -208,6 +225,7 @@ class LayerWeights:
     conv_in: Optional[QTensor] = None
     conv_kernel: Optional[torch.Tensor] = None
     conv_out: Optional[LinearWeight] = None
+    gdn: Optional[GDNWeights] = None  # a gated-delta-rule layer in place of attention (the feed-forward block stays)
     ssm: Optional[SSMWeights] = None  # a state-space layer: no attention and no feed-forward block
     # Gemma-2/3: norms applied to the attention / FFN branch outputs before the residual add
     post_attn_norm: Optional[torch.Tensor] = None
@@ -492,6 +510,20 @@ def _load_layer(src: GGUFWeightSource, cfg: ModelConfig, i: int, tp_rank: int, t
                          dt_bias=src.vector(f"{p}.ssm_dt.bias"), a=src.vector(f"{p}.ssm_a").reshape(di, -1),
                          d=src.vector(f"{p}.ssm_d"), out_proj=LinearWeight([src.matrix(f"{p}.ssm_out.weight")]))
         return LayerWeights(attn_norm=src.vector(f"{p}.attn_norm.weight"), wqkv=None, wo=None, ffn_norm=None, ssm=ssm)
+    # the norm in front of the feed-forward block; Qwen3.5 files name it post_attention_norm
+    ffn_norm_name = f"{p}.ffn_norm.weight" if src.has(f"{p}.ffn_norm.weight") or not cfg.attn_out_gate else f"{p}.post_attention_norm.weight"
+    if src.has(f"{p}.ssm_alpha.weight"):
+        if tp_size > 1:
+            raise ValueError("gated-delta-rule layers are not sharded: run this model with tp_size = 1")
+        rows = src.g.tensors[f"{p}.attn_qkv.weight"].shape[0]
+        gdn = GDNWeights(in_qkv=src.matrix(f"{p}.attn_qkv.weight"), in_z=src.matrix(f"{p}.attn_gate.weight"),
+                         in_a=src.matrix(f"{p}.ssm_alpha.weight"), in_b=src.matrix(f"{p}.ssm_beta.weight"),
+                         conv_kernel=src.vector(f"{p}.ssm_conv1d.weight").reshape(rows, -1),
+                         dt_bias=src.vector(f"{p}.ssm_dt.bias"), a=src.vector(f"{p}.ssm_a").reshape(-1),
+                         norm=src.vector(f"{p}.ssm_norm.weight"), out_proj=LinearWeight([src.matrix(f"{p}.ssm_out.weight")]))
+        lw = LayerWeights(attn_norm=src.vector(f"{p}.attn_norm.weight"), wqkv=None, wo=None, ffn_norm=src.vector(ffn_norm_name), gdn=gdn)
+        _load_ffn(src, cfg, p, lw, tp_rank, tp_size, ep_rank, ep_size)
+        return lw
     if src.has(f"{p}.shortconv.conv.weight"):
         if tp_size > 1:
             raise ValueError("short-convolution layers are not sharded: run this model with tp_size = 1")
@@ -509,6 +541,11 @@ def _load_layer(src: GGUFWeightSource, cfg: ModelConfig, i: int, tp_rank: int, t
         ko, vo = cfg.n_heads * hd, (cfg.n_heads + cfg.n_kv_heads) * hd
         parts = [src.matrix(f"{p}.attn_qkv.weight", rows=qr), src.matrix(f"{p}.attn_qkv.weight", rows=(ko + kr[0], ko + kr[1])),
                  src.matrix(f"{p}.attn_qkv.weight", rows=(vo + kr[0], vo + kr[1]))]
+    elif cfg.attn_out_gate:
+        if tp_size > 1:
+            raise ValueError("gated attention is not sharded: run this model with tp_size = 1")
+        # per head: the query rows, then the rows of that head's output gate
+        parts = [src.matrix(f"{p}.attn_q.weight"), src.matrix(f"{p}.attn_k.weight", rows=kr), src.matrix(f"{p}.attn_v.weight", rows=kr)]
     else:
         parts = [src.matrix(f"{p}.attn_q.weight", rows=qr), src.matrix(f"{p}.attn_k.weight", rows=kr),
                  src.matrix(f"{p}.attn_v.weight", rows=kr)]
@@ -525,13 +562,13 @@ def _load_layer(src: GGUFWeightSource, cfg: ModelConfig, i: int, tp_rank: int, t
         attn_norm=src.vector(f"{p}.attn_norm.weight"),
         wqkv=LinearWeight(fuse_rows(parts), bias) if mla is None else None,
         wo=LinearWeight([src.matrix(f"{p}.attn_output.weight", cols=(q0 * vd, q1 * vd))]),
-        ffn_norm=src.vector(f"{p}.ffn_norm.weight"),
+        ffn_norm=src.vector(ffn_norm_name),
         mla=mla,
     )
     if src.has(f"{p}.attn_q_norm.weight"):
         lw.q_norm = src.vector(f"{p}.attn_q_norm.weight")
         lw.k_norm = src.vector(f"{p}.attn_k_norm.weight")
-    if src.has(f"{p}.post_attention_norm.weight"):
+    if src.has(f"{p}.post_attention_norm.weight") and ffn_norm_name.endswith("ffn_norm.weight"):
         lw.post_attn_norm = src.vector(f"{p}.post_attention_norm.weight")
     if src.has(f"{p}.post_ffw_norm.weight"):
         lw.post_ffn_norm = src.vector(f"{p}.post_ffw_norm.weight")

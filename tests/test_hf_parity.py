@@ -87,6 +87,17 @@ def _build(name: str):
                                                               rope_parameters={"rope_type": "dynamic", "rope_theta": 10000.0, "alpha": 50.0, "factor": 1.0}))
     if name == "hunyuan_dense":
         return T.HunYuanDenseV1ForCausalLM(T.HunYuanDenseV1Config(**c, head_dim=16))
+    if name == "qwen35":  # three gated-delta-rule layers (4 value heads over 2 key heads, 4 taps) to one gated attention layer
+        return T.Qwen3_5ForCausalLM(T.Qwen3_5TextConfig(**c, head_dim=16, linear_conv_kernel_dim=4, linear_key_head_dim=8,
+                                                        linear_value_head_dim=12, linear_num_key_heads=2, linear_num_value_heads=4,
+                                                        layer_types=["linear_attention", "linear_attention", "full_attention",
+                                                                     "linear_attention"]))
+    if name == "qwen35moe":  # the same mixers in front of routed experts + a sigmoid-gated shared expert
+        return T.Qwen3_5MoeForCausalLM(T.Qwen3_5MoeTextConfig(**{k: v for k, v in c.items() if k != "intermediate_size"}, head_dim=16,
+                                                              linear_conv_kernel_dim=4, linear_key_head_dim=8, linear_value_head_dim=8,
+                                                              linear_num_key_heads=2, linear_num_value_heads=2, num_experts=8,
+                                                              num_experts_per_tok=2, moe_intermediate_size=48, shared_expert_intermediate_size=80,
+                                                              layer_types=["linear_attention", "full_attention", "linear_attention", "full_attention"]))
     if name == "glm4":  # norms on both sides of both branches, fused gate-up, neighbouring values rotated over half of each head
         return T.Glm4ForCausalLM(T.Glm4Config(**c, head_dim=16, pad_token_id=0, attention_bias=True,
                                               rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5}))
@@ -117,7 +128,7 @@ def _build(name: str):
 
 
 FAMILIES = ["llama", "qwen2", "qwen3", "phi3", "mixtral", "qwen3moe", "gemma", "gemma2", "gemma3", "deepseek_v2", "deepseek_v3",
-            "deepseek_v3_yarn", "lfm2", "lfm2moe", "glm4", "glm4moe", "hunyuan_moe", "hunyuan_dense", "mamba", "mistral_swa", "qwen2moe",
+            "deepseek_v3_yarn", "lfm2", "lfm2moe", "glm4", "glm4moe", "hunyuan_moe", "hunyuan_dense", "qwen35", "qwen35moe", "mamba", "mistral_swa", "qwen2moe",
             "llama31_rope", "phi3_longrope"]
 
 
@@ -159,6 +170,11 @@ def test_logits_and_greedy_tokens_match_transformers(family, tmp_path):
     if family == "hunyuan_moe":
         assert cfg.n_experts == 8 and cfg.n_shared_experts == 1 and not cfg.shared_expert_gate and cfg.expert_gating == "softmax"
         assert abs(cfg.rope_theta - 10000.0 * 50.0 ** (16 / 14)) < 1.0
+    if family == "qwen35moe":
+        assert cfg.gdn_layers == [0, 2] and cfg.n_experts == 8 and cfg.n_shared_experts == 1 and cfg.shared_expert_gate
+    if family == "qwen35":
+        assert cfg.gdn_layers == [0, 1, 3] and cfg.attn_out_gate and cfg.qk_norm and cfg.rope_dim == 4 and cfg.is_ssm
+        assert (cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_k_dim, cfg.gdn_v_dim, cfg.gdn_conv) == (2, 4, 8, 12, 4)
     if family == "glm4":
         assert cfg.rope_pairing == "adjacent" and cfg.rope_dim == 8 and cfg.post_norms and cfg.attn_bias
     if family == "glm4moe":
@@ -202,12 +218,13 @@ def test_logits_and_greedy_tokens_match_transformers(family, tmp_path):
     assert os.path.getsize(path) > 0
 
 
-def test_state_space_model_through_the_scheduler(tmp_path):
-    """Mamba's per-sequence state under continuous batching: batched == one at a time, a pool small enough to preempt ==
+@pytest.mark.parametrize("family", ["mamba", "qwen35"])
+def test_state_space_model_through_the_scheduler(family, tmp_path):
+    """A per-sequence recurrent state (Mamba; Qwen3.5's gated-delta-rule layers beside attention layers) under continuous batching: batched == one at a time, a pool small enough to preempt ==
     a roomy one (a restarted sequence recomputes its state from position 0), more sequential requests than state slots,
     no prefix sharing, no speculation."""
     torch.manual_seed(1)
-    ref = _build("mamba").eval().float()
+    ref = _build(family).eval().float()
     with torch.no_grad():
         for pname, p in ref.named_parameters():
             if p.ndim == 2:
@@ -224,7 +241,8 @@ def test_state_space_model_through_the_scheduler(tmp_path):
     one_by_one = [roomy.generate([p], sp)[0].token_ids for p in prompts]
     assert [o.token_ids for o in roomy.generate(prompts, sp)] == one_by_one
     with torch.no_grad():
-        want0 = ref.generate(torch.tensor([prompts[1]]), max_new_tokens=12, do_sample=False)[0, len(prompts[1]):].tolist()
+        want0 = ref.generate(torch.tensor([prompts[1]]), attention_mask=torch.ones(1, len(prompts[1]), dtype=torch.long),
+                             max_new_tokens=12, do_sample=False, pad_token_id=0)[0, len(prompts[1]):].tolist()
     assert one_by_one[1] == want0
     # short prompts that grow: all four are admitted, then the pool runs dry and the scheduler evicts and recomputes
     growers = [p[:14] for p in prompts if len(p) >= 14]
