@@ -24,7 +24,7 @@ _ARCH = {"LlamaForCausalLM": "llama", "MistralForCausalLM": "llama", "MixtralFor
          "Qwen2MoeForCausalLM": "qwen2moe", "DeepseekV2ForCausalLM": "deepseek2", "DeepseekV3ForCausalLM": "deepseek2",
          "Phi3ForCausalLM": "phi3", "GemmaForCausalLM": "gemma", "Gemma2ForCausalLM": "gemma2",
          "Gemma3ForCausalLM": "gemma3", "Gemma3ForConditionalGeneration": "gemma3", "Lfm2ForCausalLM": "lfm2",
-         "Lfm2MoeForCausalLM": "lfm2moe", "Glm4MoeForCausalLM": "glm4moe", "Glm4ForCausalLM": "glm4",
+         "Lfm2MoeForCausalLM": "lfm2moe", "Glm4MoeForCausalLM": "glm4moe", "Glm4ForCausalLM": "glm4", "MiniMaxM2ForCausalLM": "minimax-m2",
          "Qwen3_5ForCausalLM": "qwen35", "Qwen3_5ForConditionalGeneration": "qwen35",
          "Qwen3_5MoeForCausalLM": "qwen35moe", "Qwen3_5MoeForConditionalGeneration": "qwen35moe",
          "HunYuanMoEV1ForCausalLM": "hunyuan-moe", "HunYuanDenseV1ForCausalLM": "hunyuan-dense", "MambaForCausalLM": "mamba"}
@@ -148,7 +148,7 @@ def write_hf_metadata(w: GGUFWriter, arch: str, c: Dict[str, Any]) -> None:
     theta, theta_swa, rs = _rope_settings(c)
     w.add(f"{arch}.rope.freq_base", theta, F)
     w.add(f"{arch}.rope.dimension_count",
-          int(c["qk_rope_head_dim"]) if c.get("kv_lora_rank") else int(hd * float(c.get("partial_rotary_factor") or (c.get("rope_parameters") or {}).get("partial_rotary_factor") or 1.0)), U)
+          int(c["qk_rope_head_dim"]) if c.get("kv_lora_rank") else int(c["rotary_dim"]) if c.get("rotary_dim") else int(hd * float(c.get("partial_rotary_factor") or (c.get("rope_parameters") or {}).get("partial_rotary_factor") or 1.0)), U)
     if arch in ("qwen35", "qwen35moe"):
         vh, vd = int(c.get("linear_num_value_heads", 0)), int(c.get("linear_value_head_dim", 0))
         w.add(f"{arch}.ssm.conv_kernel", int(c.get("linear_conv_kernel_dim", 4)), U)
@@ -203,7 +203,7 @@ def write_hf_metadata(w: GGUFWriter, arch: str, c: Dict[str, Any]) -> None:
         w.add(f"{arch}.expert_feed_forward_length", int(c.get("moe_intermediate_size") or c.get("intermediate_size")), U)
         # DeepSeek-V3 configs often omit scoring_func: that model always scores with a sigmoid
         sigmoid = c.get("scoring_func") == "sigmoid" or (c.get("scoring_func") is None
-                                                         and c.get("model_type") in ("deepseek_v3", "lfm2_moe", "glm4_moe"))
+                                                         and c.get("model_type") in ("deepseek_v3", "lfm2_moe", "glm4_moe", "minimax_m2"))
         w.add(f"{arch}.expert_gating_func", 2 if sigmoid else 1, U)
         w.add(f"{arch}.expert_weights_scale", float(c.get("routed_scaling_factor", 1.0)), F)
         w.add(f"{arch}.expert_weights_norm", bool(c.get("norm_topk_prob", True)))

@@ -609,6 +609,7 @@ _HF_LAYER_MAP = {
     "mlp.shared_experts.down_proj.weight": "ffn_down_shexp.weight",
     "mlp.shared_expert_gate.weight": "ffn_gate_inp_shexp.weight",
     "mlp.gate.e_score_correction_bias": "exp_probs_b.bias",
+    "block_sparse_moe.e_score_correction_bias": "exp_probs_b.bias",
 }
 # Gemma-2 / Gemma-3 name their four per-layer norms differently: post_attention_layernorm is the norm on the attention
 # branch's OUTPUT there (elsewhere it is the norm in front of the FFN)

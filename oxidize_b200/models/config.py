@@ -22,6 +22,8 @@ from ..formats.gguf import GGUFFile
 # glm4: Llama layers with norms on both branch outputs too, a fused gate-up tensor, and half of each head rotated over
 # pairs of neighbouring values.
 # hunyuan-dense / hunyuan-moe: RMSNorm on the q / k heads AFTER the rotation; the MoE form adds an always-on shared MLP.
+# minimax-m2: q and k normalised over the whole projection (all heads at once) before the rotation, sigmoid routing with a
+# correction bias.
 # glm4moe: grouped-query attention over half-rotated heads, DeepSeek-V3 style routing (sigmoid scores, correction bias, groups).
 # qwen35: three gated-delta-rule layers (linear attention with a per-sequence matrix state) to every attention layer, whose
 # output passes a sigmoid gate computed beside the queries; norm weights stored as w - 1.
@@ -30,7 +32,7 @@ DENSE_ARCHS = {"llama", "mistral", "qwen2", "qwen3", "deepseek", "phi3", "gemma"
                "qwen35", "qwen3_5", "qwen3_5_text", "qwen35_text",
                "hunyuan-dense", "hunyuan_dense"}
 GEMMA_ARCHS = {"gemma", "gemma2", "gemma3"}
-MOE_ARCHS = {"mixtral", "qwen2moe", "qwen3moe", "deepseek2", "deepseek-moe", "deepseek_moe", "lfm2moe", "glm4moe", "qwen35moe", "qwen3_5_moe", "qwen3_5_moe_text",
+MOE_ARCHS = {"mixtral", "qwen2moe", "qwen3moe", "deepseek2", "deepseek-moe", "deepseek_moe", "lfm2moe", "glm4moe", "minimax-m2", "minimax_m2", "minimax", "qwen35moe", "qwen3_5_moe", "qwen3_5_moe_text",
              "hunyuan-moe", "hunyuan_moe"}
 # Architectures whose layers need math this engine does not have (two attention geometries in one model,
 # parallel attention / MLP blocks, recurrent or convolutional mixers): loading one would run it as
@@ -84,6 +86,7 @@ class ModelConfig:
     gdn_v_dim: int = 0
     gdn_conv: int = 4
     attn_out_gate: bool = False  # q_proj also yields a per-head gate; attention output * sigmoid(gate)
+    qk_norm_full: bool = False  # MiniMax-M2: one RMSNorm over all of q (and of k), not one per head
     qk_norm_after_rope: bool = False  # Hunyuan: the per-head q / k norms act on the rotated vectors
     rope_pairing: str = "split_half"  # split_half (NeoX; what all reference engines do) | adjacent
     rope_attn_factor: float = 1.0  # magnitude factor that goes with the long LongRoPE frequency factors (Phi-3)
@@ -292,6 +295,8 @@ def config_from_gguf(g: GGUFFile) -> ModelConfig:
         first_attn = next((i for i in range(c.n_layers) if i not in c.conv_layers), 0)
         c.qk_norm = g.has_tensor(f"blk.{first_attn}.attn_q_norm.weight")
         c.tie_embeddings = not g.has_tensor("output.weight")
+    qn = g.tensors.get("blk.0.attn_q_norm.weight")
+    c.qk_norm_full = qn is not None and qn.n_elements > c.head_dim
     if arch in QWEN35_ARCHS:
         c.gdn_layers = [i for i in range(c.n_layers) if g.has_tensor(f"blk.{i}.ssm_alpha.weight")]
         c.attn_out_gate = True

@@ -179,7 +179,7 @@ class Transformer:
 
         for lw in self.w.layers:
             if (lw.router is not None or lw.post_attn_norm is not None or lw.post_ffn_norm is not None or cfg.qk_norm_after_rope
-                    or cfg.attn_out_gate
+                    or cfg.attn_out_gate or cfg.qk_norm_full
                     or not (bf16_single(lw.wqkv) and bf16_single(lw.wo) and bf16_single(lw.w_gate_up)
                             and bf16_single(lw.w_down) and lw.w_gate_up.swiglu_interleaved)):
                 continue
@@ -475,7 +475,8 @@ class Transformer:
             return self._mla_attention(lw, layer, x, meta, kv)
         window = cfg.layer_sliding_window(window_of)
         rope = self._layer_rope(window)
-        if self._fuse_qkv_rope and x.is_cuda and lw.wqkv.bias is None and not cfg.qk_norm_after_rope and not cfg.attn_out_gate:
+        if (self._fuse_qkv_rope and x.is_cuda and lw.wqkv.bias is None and not cfg.qk_norm_after_rope and not cfg.attn_out_gate
+                and not cfg.qk_norm_full):
             from ..ops import cuda as opcuda
 
             if opcuda.qkv_rope_fusable(lw.wqkv.parts, kv, rope, lw.q_norm, lw.k_norm):
@@ -490,7 +491,16 @@ class Transformer:
             qg = qkv[:, : nq * 2 * hd].reshape(-1, nq, 2 * hd)
             gate = qg[:, :, hd:].reshape(-1, nq * hd)
             qkv = torch.cat([qg[:, :, :hd].reshape(-1, nq * hd), qkv[:, nq * 2 * hd :]], dim=-1)
-        q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, rope, lw.q_norm, lw.k_norm, cfg.rms_eps,
+        q_norm, k_norm = lw.q_norm, lw.k_norm
+        if cfg.qk_norm_full and q_norm is not None:
+            # one norm over all heads of q and one over all heads of k, ahead of the head split
+            if self.w.tp_size > 1:
+                raise ValueError("a norm over all heads is not sharded: run this model with tp_size = 1")
+            nq, nk = self.n_heads_local * cfg.head_dim, self.n_kv_local * cfg.head_dim
+            qkv = torch.cat([opref.rmsnorm(qkv[:, :nq], q_norm, cfg.rms_eps).to(qkv.dtype),
+                             opref.rmsnorm(qkv[:, nq : nq + nk], k_norm, cfg.rms_eps).to(qkv.dtype), qkv[:, nq + nk :]], dim=-1)
+            q_norm = k_norm = None
+        q = ops.qk_rope_kv_write(qkv, meta.positions, meta.slot_mapping, kv, layer, rope, q_norm, k_norm, cfg.rms_eps,
                                  norm_after=cfg.qk_norm_after_rope)
         attn = ops.paged_attention(q, kv, layer, meta, self.attn_scale, window, cfg.attn_softcap)
         if gate is not None:

@@ -98,6 +98,13 @@ def _build(name: str):
                                                               linear_num_key_heads=2, linear_num_value_heads=2, num_experts=8,
                                                               num_experts_per_tok=2, moe_intermediate_size=48, shared_expert_intermediate_size=80,
                                                               layer_types=["linear_attention", "full_attention", "linear_attention", "full_attention"]))
+    if name == "minimax_m2":  # q and k normalised over all heads at once, half of each head rotated, sigmoid routing with a bias
+        m = T.MiniMaxM2ForCausalLM(T.MiniMaxM2Config(**c, head_dim=16, num_local_experts=8, num_experts_per_tok=2,
+                                                     rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5}))
+        with torch.no_grad():
+            for layer in m.model.layers:
+                layer.mlp.e_score_correction_bias.copy_(torch.randn(8) * 0.3)
+        return m
     if name == "glm4":  # norms on both sides of both branches, fused gate-up, neighbouring values rotated over half of each head
         return T.Glm4ForCausalLM(T.Glm4Config(**c, head_dim=16, pad_token_id=0, attention_bias=True,
                                               rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5}))
@@ -128,7 +135,7 @@ def _build(name: str):
 
 
 FAMILIES = ["llama", "qwen2", "qwen3", "phi3", "mixtral", "qwen3moe", "gemma", "gemma2", "gemma3", "deepseek_v2", "deepseek_v3",
-            "deepseek_v3_yarn", "lfm2", "lfm2moe", "glm4", "glm4moe", "hunyuan_moe", "hunyuan_dense", "qwen35", "qwen35moe", "mamba", "mistral_swa", "qwen2moe",
+            "deepseek_v3_yarn", "lfm2", "lfm2moe", "glm4", "glm4moe", "hunyuan_moe", "hunyuan_dense", "qwen35", "qwen35moe", "minimax_m2", "mamba", "mistral_swa", "qwen2moe",
             "llama31_rope", "phi3_longrope"]
 
 
@@ -175,6 +182,8 @@ def test_logits_and_greedy_tokens_match_transformers(family, tmp_path):
     if family == "qwen35":
         assert cfg.gdn_layers == [0, 1, 3] and cfg.attn_out_gate and cfg.qk_norm and cfg.rope_dim == 4 and cfg.is_ssm
         assert (cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_k_dim, cfg.gdn_v_dim, cfg.gdn_conv) == (2, 4, 8, 12, 4)
+    if family == "minimax_m2":
+        assert cfg.qk_norm and cfg.qk_norm_full and cfg.expert_gating == "sigmoid" and cfg.rope_dim == 8 and cfg.n_experts == 8
     if family == "glm4":
         assert cfg.rope_pairing == "adjacent" and cfg.rope_dim == 8 and cfg.post_norms and cfg.attn_bias
     if family == "glm4moe":
