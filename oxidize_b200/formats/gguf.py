@@ -644,6 +644,7 @@ _HF_LAYER_MAP_QWEN35 = {
     "linear_attn.A_log": "ssm_a",
     "linear_attn.norm.weight": "ssm_norm.weight",
     "linear_attn.out_proj.weight": "ssm_out.weight",
+    "post_attention_layernorm.weight": "post_attention_norm.weight",  # the norm in front of the feed-forward block
 }
 # LFM2: operator norm, short-convolution tensors, w1 / w3 / w2 feed-forward names, RMSNorm on q / k heads
 _HF_LAYER_MAP_LFM2 = {
